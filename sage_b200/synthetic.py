@@ -1,0 +1,78 @@
+"""Seeded synthetic SAGE-packed weights (inputs for tests and benchmarks).
+
+Produces the five packed buffers of one SAGE linear with the value
+distributions of the reference's `synthetic_sage`
+(weight_vq/checkpoint.py:54-89 in the reference project): the Adaptive Bit
+Split is drawn from the seed (6, 7 or 8 direction bits, i.e. 64/128/256
+codebook entries and 4/3/2 radius bits), the codebook is a row-normalised
+U[0,1) matrix, every code/radius bit pattern is legal and drawn uniformly,
+the (min, step) grid is U[0,1)*sqrt(8/K) with the step divided by the number
+of radius levels minus one, pad rows of the last 16-row tile are zero, and the
+input-channel permutation is a random permutation of K.
+
+The draw order matches the reference generator, so for the same torch version
+and seed the buffers are identical to the reference's; `tests/golden` pins that.
+"""
+
+from __future__ import annotations
+
+import math
+
+import torch
+
+PACKED_KEYS = ("packed_codes", "radius_codes", "radius_grid", "codebook", "permutation")
+
+
+def synthetic_sage(
+    in_features: int,
+    out_features: int,
+    seed: int = 0,
+    *,
+    permuted: bool = True,
+    direction_bits: int | None = None,
+) -> dict[str, torch.Tensor]:
+    """Return CPU tensors {packed_codes, radius_codes, radius_grid, codebook, permutation}.
+
+    `direction_bits` (6, 7 or 8) forces the bit split; by default the seed
+    chooses it exactly as the reference does (seed 0 -> 8, 1 -> 7, 2 -> 6).
+    """
+    if in_features <= 0 or in_features % 128 or out_features <= 0:
+        raise ValueError("SAGE requires positive N and K divisible by 128")
+    if direction_bits not in (None, 6, 7, 8):
+        raise ValueError("direction_bits must be 6, 7 or 8")
+    gen = torch.Generator().manual_seed(seed)
+    drawn = int(torch.randint(6, 9, (), generator=gen))
+    dbits = drawn if direction_bits is None else direction_bits
+    entries = 1 << dbits
+    levels = 1 << (10 - dbits)
+    tiles = (out_features + 15) // 16
+    groups = in_features // 128
+
+    directions = torch.rand(entries, 8, generator=gen)
+    directions = torch.nn.functional.normalize(directions, dim=-1)
+    lo, hi = -(2**31), 2**31
+    packed_codes = torch.randint(lo, hi, (tiles, groups, 16, 8), generator=gen, dtype=torch.int32)
+    radius_codes = torch.randint(lo, hi, (tiles, groups, 16), generator=gen, dtype=torch.int32)
+    radius_grid = torch.rand(tiles, groups, 16, 2, generator=gen) * math.sqrt(8 / in_features)
+    radius_grid[..., 1] /= levels - 1
+    tail = out_features % 16
+    if tail:
+        for buffer in (packed_codes, radius_codes, radius_grid):
+            buffer[-1, :, tail:] = 0
+    if permuted:
+        permutation = torch.randperm(in_features, generator=gen, dtype=torch.int32)
+    else:
+        permutation = torch.empty(0, dtype=torch.int32)
+    # plane p of the stored codebook holds dims (2p, 2p+1) of every entry
+    codebook = directions.half().reshape(entries, 4, 2).permute(1, 0, 2).contiguous()
+    return {
+        "packed_codes": packed_codes,
+        "radius_codes": radius_codes,
+        "radius_grid": radius_grid.half(),
+        "codebook": codebook,
+        "permutation": permutation,
+    }
+
+
+def packed_to(packed: dict[str, torch.Tensor], device) -> dict[str, torch.Tensor]:
+    return {key: value.to(device) for key, value in packed.items()}
