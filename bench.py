@@ -1,0 +1,434 @@
+"""Benchmark of the SAGE packed-weight decode path on B200.
+
+    python bench.py [--gpus N] [--steps K] [--warmup W] [--impl ours|reference]
+                    [--workload decode_linears]
+
+A step is one decoded token's worth of work for Qwen3-4B at batch 1 (synthetic seeded
+packed weights, ABS split cycling 6/7/8 direction bits per matrix).  Rank 0 prints ONE
+JSON line.  `value` is whole-job tok/s with everything resident in HBM, timed with CUDA
+events around K CUDA-graph replays; `e2e` is the same through the public module API with
+the step's input copied from pinned host memory and its result read back every step.
+
+`--impl reference` times the reference's CPU path for the same workload (dequantise,
+round to FP16, FP32 matmul - tests/inference/reference.py:39-49 and
+tests/inference/test_sage.py:113-122 in the reference project) on the host cores, using
+this repo's C restatement of it (oracle/), one decoder layer per step.
+
+Multi-GPU (`--gpus N` under torchrun): the decode path has no cross-sequence exchange, so
+every rank decodes its own sequence with its own copy of the weights (weak scaling, no
+collective on the data path); the timed region is bracketed by barriers and the slowest
+rank's time is used.
+"""
+
+from __future__ import annotations
+
+import argparse
+import json
+import os
+import pathlib
+import subprocess
+import sys
+import threading
+import time
+
+ROOT = pathlib.Path(__file__).resolve().parent
+if str(ROOT) not in sys.path:
+    sys.path.insert(0, str(ROOT))
+
+METRIC = "qwen3_4b_sage_2.25bpw_batch1_decode_tok_s"
+UNIT = "tok/s"
+
+# Qwen3-4B decoder layer, (name, in K, out N), in execution order
+QWEN3_4B_LAYERS = 36
+QWEN3_4B_LINEARS = [
+    ("q_proj", 2560, 4096),
+    ("k_proj", 2560, 1024),
+    ("v_proj", 2560, 1024),
+    ("o_proj", 4096, 2560),
+    ("gate_proj", 2560, 9728),
+    ("up_proj", 2560, 9728),
+    ("down_proj", 9728, 2560),
+]
+
+
+def measured_peaks() -> tuple[float, str]:
+    path = ROOT / "MEASURED_PEAKS.json"
+    if path.exists():
+        return float(json.loads(path.read_text())["hbm_gbs"]), "measured"
+    return 6650.0, "fallback"
+
+
+class ClockSampler:
+    """Samples SM clocks and throttle reasons with nvidia-smi while a region runs."""
+
+    QUERY = (
+        "index,clocks.sm,clocks.max.sm,power.draw,clocks_event_reasons.active,"
+        "clocks_event_reasons.hw_slowdown,clocks_event_reasons.hw_thermal_slowdown,"
+        "clocks_event_reasons.sw_thermal_slowdown,clocks_event_reasons.sw_power_cap"
+    )
+
+    def __init__(self, index: int):
+        self.index = index
+        self.process = None
+        self.lines: list[str] = []
+        self.thread = None
+
+    def __enter__(self):
+        try:
+            self.process = subprocess.Popen(
+                ["nvidia-smi", f"--query-gpu={self.QUERY}", "--format=csv,noheader,nounits",
+                 "-i", str(self.index), "-lms", "100"],
+                stdout=subprocess.PIPE, stderr=subprocess.DEVNULL, text=True,
+            )
+            self.thread = threading.Thread(target=self._pump, daemon=True)
+            self.thread.start()
+        except OSError:
+            self.process = None
+        return self
+
+    def _pump(self):
+        for line in self.process.stdout:
+            self.lines.append(line.strip())
+
+    def __exit__(self, *exc):
+        if self.process is not None:
+            self.process.terminate()
+            try:
+                self.process.wait(timeout=5)
+            except subprocess.TimeoutExpired:
+                self.process.kill()
+        return False
+
+    def summary(self) -> dict:
+        clocks, maxima, reasons = [], [], set()
+        names = ["hw_slowdown", "hw_thermal_slowdown", "sw_thermal_slowdown", "sw_power_cap"]
+        for line in self.lines:
+            parts = [p.strip() for p in line.split(",")]
+            if len(parts) < 9:
+                continue
+            try:
+                clocks.append(float(parts[1]))
+                maxima.append(float(parts[2]))
+            except ValueError:
+                continue
+            for name, flag in zip(names, parts[5:9]):
+                if flag.lower().startswith("active"):
+                    reasons.add(name)
+        if not clocks:
+            return {"sm_mhz": None, "sm_max_mhz": None, "reasons": [], "samples": 0}
+        clocks.sort()
+        return {
+            "sm_mhz": clocks[len(clocks) // 2],
+            "sm_max_mhz": max(maxima),
+            "reasons": sorted(reasons),
+            "samples": len(clocks),
+        }
+
+
+# ------------------------------------------------------------------ reference (CPU) arm
+
+
+def cpu_layer_seconds(repeats: int, threads: int) -> tuple[float, int]:
+    """Best time of the reference CPU path over one Qwen3-4B decoder layer at batch 1."""
+    import torch
+
+    from oracle import c_oracle
+    from sage_b200.synthetic import synthetic_sage
+
+    cores = threads if threads > 0 else (os.cpu_count() or 1)
+    layer = []
+    for index, (_, k, n) in enumerate(QWEN3_4B_LINEARS):
+        packed = synthetic_sage(k, n, seed=index, permuted=True)
+        x = torch.randn(1, k, generator=torch.Generator().manual_seed(43), dtype=torch.float16)
+        layer.append((x, packed, n))
+    best = float("inf")
+    for _ in range(repeats):
+        begin = time.perf_counter()
+        for x, packed, n in layer:
+            c_oracle.linear_fp32(x, packed, n, threads=cores)
+        best = min(best, time.perf_counter() - begin)
+    return best, cores
+
+
+def run_reference(args) -> None:
+    rank = int(os.environ.get("RANK", "0"))
+    if rank != 0:
+        return
+    cores = os.cpu_count() or 1
+    for _ in range(max(args.warmup, 1)):
+        cpu_layer_seconds(1, cores)
+    begin = time.perf_counter()
+    times = [cpu_layer_seconds(1, cores)[0] for _ in range(args.steps)]
+    wall = time.perf_counter() - begin
+    layer_seconds = sum(times) / len(times)
+    value = 1.0 / (layer_seconds * QWEN3_4B_LAYERS)
+    sample = "one Qwen3-4B decoder layer (7 packed linears, M=1) per step, scaled by 36 layers"
+    line = {
+        "impl": "reference",
+        "metric": METRIC,
+        "value": value,
+        "unit": UNIT,
+        "n_gpus": args.gpus,
+        "steps": args.steps,
+        "warmup": args.warmup,
+        "ms_per_step": 1000.0 * wall / args.steps,
+        "higher_is_better": True,
+        "scaling": "weak",
+        "vs_baseline": None,
+        "dtype": "f16 weights, f32 accumulate",
+        "data": "synthetic",
+        "config": {"workload": args.workload, "model": "Qwen3-4B shapes", "batch": 1,
+                   "note": "reference CPU path (dequantise + FP32 matmul) via the C oracle port"},
+        "cpu_baseline": {"value": value, "unit": UNIT, "cores": cores, "kind": "port", "sample": sample},
+        "e2e": {"value": value, "unit": UNIT, "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0},
+        "gpu_launches": 0,
+    }
+    print(json.dumps(line), flush=True)
+
+
+# ------------------------------------------------------------------ our arm
+
+
+def build_decode_linears(device):
+    """All 252 packed linears of Qwen3-4B with fixed FP16 inputs; returns modules and bytes."""
+    import torch
+
+    from sage_b200 import SAGELinear
+    from sage_b200.synthetic import linear_algorithmic_bytes, synthetic_sage_device
+
+    layers, total_bytes = [], 0
+    seed = 0
+    for _ in range(QWEN3_4B_LAYERS):
+        modules = []
+        for _, k, n in QWEN3_4B_LINEARS:
+            packed = synthetic_sage_device(k, n, seed, device, permuted=True)
+            modules.append(SAGELinear(packed, n))
+            total_bytes += linear_algorithmic_bytes(1, n, k, packed["codebook"].shape[1], True)
+            seed += 1
+        layers.append(modules)
+    gen = torch.Generator(device=device).manual_seed(43)
+    inputs = {
+        2560: torch.randn(1, 2560, generator=gen, device=device, dtype=torch.float16),
+        4096: torch.randn(1, 4096, generator=gen, device=device, dtype=torch.float16),
+        9728: torch.randn(1, 9728, generator=gen, device=device, dtype=torch.float16),
+    }
+    return layers, inputs, total_bytes
+
+
+def run_single_linear(args) -> None:
+    """`--workload linear:K:N:M` - one packed-linear shape cycled over enough distinct weight
+    copies to exceed L2, launched eagerly through the C ABI (no CUDA graph).  This is the
+    small case used for profiler captures; it prints achieved GB/s for that one kernel."""
+    import torch
+
+    from sage_b200 import SAGELinear, _lib
+    from sage_b200.synthetic import linear_algorithmic_bytes, synthetic_sage_device
+
+    _, k, n, rows = args.workload.split(":")
+    k, n, rows = int(k), int(n), int(rows)
+    torch.cuda.set_device(0)
+    device = torch.device("cuda", 0)
+    lib = _lib.load()
+    one = linear_algorithmic_bytes(rows, n, k, 256, True)
+    copies = max(2, int(200e6 // one) + 1)
+    layers = [SAGELinear(synthetic_sage_device(k, n, 3 * i, device, direction_bits=8), n) for i in range(copies)]
+    x = torch.randn(rows, k, device=device, dtype=torch.float16)
+    for _ in range(max(args.warmup, 1)):
+        for layer in layers:
+            layer(x)
+    torch.cuda.synchronize()
+    before = lib.sageb200_launch_count()
+    start, stop = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    start.record()
+    for _ in range(args.steps):
+        for layer in layers:
+            layer(x)
+    stop.record()
+    torch.cuda.synchronize()
+    launches = lib.sageb200_launch_count() - before
+    seconds = start.elapsed_time(stop) / 1000.0 / launches
+    peak, kind = measured_peaks()
+    print(json.dumps({
+        "metric": "sage_linear_hbm_gbs", "value": one / seconds / 1e9, "unit": "GB/s",
+        "config": {"workload": args.workload, "copies": copies, "launch": "eager, back to back"},
+        "us_per_launch": seconds * 1e6, "bytes_per_launch": one, "frac": one / seconds / 1e9 / peak,
+        "peak_kind": f"of {kind}", "gpu_launches": int(launches),
+    }), flush=True)
+
+
+def run_ours(args) -> None:
+    import torch
+    import torch.distributed as dist
+
+    from sage_b200 import _lib
+
+    rank = int(os.environ.get("RANK", "0"))
+    world = int(os.environ.get("WORLD_SIZE", "1"))
+    local = int(os.environ.get("LOCAL_RANK", "0"))
+    if not torch.cuda.is_available():
+        raise RuntimeError("bench.py needs a CUDA device: sage_b200 has no CPU fallback")
+    torch.cuda.set_device(local)
+    device = torch.device("cuda", local)
+    if world > 1:
+        dist.init_process_group("nccl", device_id=device)
+    lib = _lib.load()
+
+    layers, inputs, step_bytes = build_decode_linears(device)
+    hidden = inputs[2560]
+
+    def step(h):
+        # the packed linears of one token, in execution order; inputs are fixed FP16
+        # vectors of the right width (h feeds the first projections)
+        out = None
+        for modules in layers:
+            q, k, v, o, gate, up, down = modules
+            q(h)
+            k(h)
+            v(h)
+            o(inputs[4096])
+            gate(h)
+            up(h)
+            out = down(inputs[9728])
+        return out
+
+    # warm-up outside the graph (library init, workspace allocation), then capture
+    side = torch.cuda.Stream()
+    side.wait_stream(torch.cuda.current_stream())
+    with torch.cuda.stream(side):
+        for _ in range(2):
+            step(hidden)
+    torch.cuda.current_stream().wait_stream(side)
+    torch.cuda.synchronize()
+    graph = torch.cuda.CUDAGraph()
+    before_capture = lib.sageb200_launch_count()
+    with torch.cuda.graph(graph):
+        result = step(hidden)
+    launches_per_step = lib.sageb200_launch_count() - before_capture
+
+    def barrier():
+        if world > 1:
+            dist.barrier()
+        torch.cuda.synchronize()
+
+    for _ in range(max(args.warmup, 3)):
+        graph.replay()
+    start, stop = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    barrier()
+    with ClockSampler(local) as sampler:
+        start.record()
+        for _ in range(args.steps):
+            graph.replay()
+        stop.record()
+        barrier()
+        elapsed_ms = start.elapsed_time(stop)
+        if elapsed_ms < 400:  # keep the sampler alive long enough for a few samples
+            extra = torch.cuda.Event(enable_timing=True)
+            for _ in range(int(400 / max(elapsed_ms / args.steps, 1e-3))):
+                graph.replay()
+            extra.record()
+            torch.cuda.synchronize()
+    clocks = sampler.summary()
+
+    # end to end: pinned host input -> device, the step, result -> host, every step
+    host_in = hidden.cpu().pin_memory()
+    host_out = torch.empty_like(result, device="cpu").pin_memory()
+    for _ in range(3):
+        hidden.copy_(host_in, non_blocking=True)
+        graph.replay()
+        host_out.copy_(result, non_blocking=True)
+        torch.cuda.synchronize()
+    barrier()
+    e2e_begin = time.perf_counter()
+    for _ in range(args.steps):
+        hidden.copy_(host_in, non_blocking=True)
+        graph.replay()
+        host_out.copy_(result, non_blocking=True)
+        torch.cuda.synchronize()
+    e2e_ms = 1000.0 * (time.perf_counter() - e2e_begin)
+    barrier()
+
+    times = torch.tensor([elapsed_ms, e2e_ms], dtype=torch.float64, device=device)
+    if world > 1:
+        dist.all_reduce(times, op=dist.ReduceOp.MAX)
+    elapsed_ms, e2e_ms = (float(v) for v in times.tolist())
+
+    if rank == 0:
+        ms_per_step = elapsed_ms / args.steps
+        value = world * 1000.0 / ms_per_step
+        peak, peak_kind = measured_peaks()
+        launch_seconds = (elapsed_ms / 1000.0) / (args.steps * launches_per_step)
+        achieved = (step_bytes / launches_per_step) / launch_seconds / 1e9
+        cpu_seconds, cores = cpu_layer_seconds(3, 0)
+        cpu_value = 1.0 / (cpu_seconds * QWEN3_4B_LAYERS)
+        line = {
+            "metric": METRIC,
+            "value": value,
+            "unit": UNIT,
+            "n_gpus": world,
+            "steps": args.steps,
+            "warmup": max(args.warmup, 3),
+            "ms_per_step": ms_per_step,
+            "higher_is_better": True,
+            "scaling": "weak",
+            "vs_baseline": None,
+            "dtype": "f16 products, f32 accumulate",
+            "data": "synthetic",
+            "config": {
+                "workload": "qwen3-4b batch-1 decode step, packed SAGE linears only "
+                            "(36 layers x q,k,v,o,gate,up,down = 252 matmuls, M=1); "
+                            "attention, norms and lm_head are not in this step",
+                "packed_bytes_per_step": step_bytes,
+                "l2_policy": "inputs larger than L2: 1.14 GB of packed weights per step",
+                "parallelism": f"replicas x{world}" if world > 1 else "single GPU",
+            },
+            "roofline": {
+                "bound": "hbm",
+                "achieved": achieved,
+                "peak": peak,
+                "unit": "GB/s",
+                "frac": achieved / peak,
+                "traffic": None,
+                "kernel": "sage_skinny_kernel",
+                "peak_kind": f"of {peak_kind}",
+                "bytes_per_launch": step_bytes / launches_per_step,
+                "us_per_launch": launch_seconds * 1e6,
+            },
+            "cpu_baseline": {
+                "value": cpu_value,
+                "unit": UNIT,
+                "cores": cores,
+                "kind": "port",
+                "sample": "one decoder layer (7 packed linears, M=1), best of 3, scaled by 36 layers",
+            },
+            "e2e": {
+                "value": world * 1000.0 * args.steps / e2e_ms,
+                "unit": UNIT,
+                "h2d_bytes_per_step": host_in.numel() * 2,
+                "d2h_bytes_per_step": host_out.numel() * 2,
+            },
+            "gpu_launches": int(launches_per_step * args.steps),
+            "clocks": clocks,
+        }
+        print(json.dumps(line), flush=True)
+    if world > 1:
+        dist.destroy_process_group()
+
+
+def main() -> None:
+    parser = argparse.ArgumentParser()
+    parser.add_argument("--gpus", type=int, default=1)
+    parser.add_argument("--steps", type=int, default=50)
+    parser.add_argument("--warmup", type=int, default=5)
+    parser.add_argument("--impl", choices=["ours", "reference"], default="ours")
+    parser.add_argument("--workload", default="decode_linears")
+    args = parser.parse_args()
+    if args.impl == "reference":
+        run_reference(args)
+    elif args.workload.startswith("linear:"):
+        run_single_linear(args)
+    else:
+        run_ours(args)
+
+
+if __name__ == "__main__":
+    main()

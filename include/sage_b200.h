@@ -1,0 +1,153 @@
+/*
+ * sage_b200 — C ABI of the B200 (sm_100a) SAGE packed-weight matmul.
+ *
+ * Plain pointers and sizes only; every pointer is a DEVICE pointer unless its name
+ * ends in `_host`.  `stream` is a cudaStream_t passed as void*.  Every function
+ * returns SAGEB200_OK (0) or a negative SAGEB200_ERR_* code and never throws;
+ * sageb200_status_string() turns a code into text.  Nothing here allocates device
+ * memory except sageb200_linear_host (documented there); no call synchronises the
+ * stream unless stated.
+ *
+ * Packed layout (tiles = ceil(N/16), groups = K/128, E = entries in {64,128,256}):
+ *   codes  uint32 [tiles][groups][16][8]   two 16-bit codes per word
+ *   radii  uint32 [tiles][groups][16]      sixteen 2-bit high radius fields
+ *   grid   fp16   [tiles][groups][16][2]   (min, step)
+ *   book   fp16   [4][E][2]                plane p = dims (2p, 2p+1) of each entry
+ *   perm   int32  [K] or NULL              x_q[j] = x[perm[j]]
+ * This is the layout the reference documents at csrc/sage/sage_gemv_cuda.h:7-13.
+ */
+#ifndef SAGE_B200_H_
+#define SAGE_B200_H_
+
+#include <stddef.h>
+#include <stdint.h>
+
+#ifdef __cplusplus
+extern "C" {
+#endif
+
+#define SAGEB200_OK 0
+#define SAGEB200_ERR_INVALID_ARGUMENT (-1) /* null pointer, bad shape, bad entries      */
+#define SAGEB200_ERR_ALIGNMENT (-2)        /* grid/book/codes/radii not 4-byte aligned   */
+#define SAGEB200_ERR_RANGE (-3)            /* rows > 65535 or a dimension overflows int  */
+#define SAGEB200_ERR_WORKSPACE (-4)        /* workspace missing or too small             */
+#define SAGEB200_ERR_CUDA (-5)             /* a CUDA call or launch failed               */
+#define SAGEB200_ERR_NO_DEVICE (-6)        /* no sm_100 device is current                */
+#define SAGEB200_ERR_TIMEOUT (-7)          /* a bounded device-side wait ran out         */
+
+/* Library version, major*10000 + minor*100 + patch. */
+int sageb200_version(void);
+
+/* Static text for a status code. */
+const char *sageb200_status_string(int status);
+
+/*
+ * 1 if the matmul folds the input-channel permutation into its activation loads for
+ * this shape, so the caller must NOT pre-gather x.  Always 1 here (any K, any rows).
+ * Replaces: bool sage_gemv_fuses_permutation(int n, int k)
+ *           (reference csrc/sage/sage_gemv_cuda.h:14, csrc/sage/sage_gemv_cuda.cu:114-116,
+ *            which returns k <= 4096 and makes csrc/bindings.cpp:49-51 run index_select).
+ */
+int sageb200_gemv_fuses_permutation(int n, int k);
+
+/*
+ * Number of K splits the matmul will use for this shape on a device with `sm_count`
+ * SMs (informational; the workspace size already accounts for it).
+ * Replaces: int sage_gemm_splits(int rows, int n, int k, int sm_count)
+ *           (reference csrc/sage/sage_gemv_cuda.h:21, csrc/sage/sage_gemm_cuda.cu:209-214,493-495).
+ */
+int sageb200_gemm_splits(int rows, int n, int k, int sm_count);
+
+/*
+ * Bytes of scratch sageb200_linear needs for this shape: split-K partial sums, their
+ * arrival counters and (for rows > 16 with a permutation) the gathered activations.
+ * The buffer must be 256-byte aligned and ZERO-FILLED ONCE when it is allocated; every
+ * call leaves the counter region zero again, so one buffer can be reused by successive
+ * calls on one stream.  Calls that run concurrently must not share a buffer.
+ * Replaces: the workspace sizing at reference csrc/bindings.cpp:63-66.
+ */
+size_t sageb200_workspace_bytes(int rows, int n, int k);
+
+/*
+ * y[rows][n] (fp16) = x[rows][k] (fp16) . W^T, W given by the five packed buffers.
+ * Chooses the GEMV / skinny tensor-core kernel (rows <= 16) or the prefill GEMM
+ * (rows > 16) internally; the permutation is always applied inside.
+ *   x     fp16 [rows][k], contiguous, any 2-byte alignment
+ *   perm  NULL for identity
+ *   y     fp16 [rows][n]
+ *   rows may be 0 (returns OK without launching); rows <= 65535; k % 128 == 0.
+ * Replaces: sage_gemv_cuda + sage_gemm_cuda and the dispatch around them
+ *           (reference csrc/sage/sage_gemv_cuda.h:16-26, csrc/bindings.cpp:8-79).
+ */
+int sageb200_linear(const void *x, const void *codes, const void *radii, const void *grid,
+                    const void *book, const int32_t *perm, void *y, void *workspace,
+                    size_t workspace_bytes, int rows, int n, int k, int entries, void *stream);
+
+/* One problem of a grouped launch: the arguments of sageb200_linear without scratch. */
+typedef struct sageb200_problem {
+  const void *x;
+  const void *codes;
+  const void *radii;
+  const void *grid;
+  const void *book;
+  const int32_t *perm;
+  void *y;
+  int rows;
+  int n;
+  int k;
+  int entries;
+} sageb200_problem;
+
+#define SAGEB200_MAX_GROUPED 16
+
+/*
+ * Several independent packed linears with rows <= 16 in ONE kernel launch (q/k/v,
+ * gate/up, the experts a token routes to).  `problems_host` is a HOST array of
+ * `count` <= SAGEB200_MAX_GROUPED descriptors whose pointers are device pointers.
+ * Workspace: the sum of sageb200_workspace_bytes over the problems, same zero-fill rule.
+ * No counterpart in the reference, which launches one kernel per linear
+ * (csrc/bindings.cpp:52-61).
+ */
+int sageb200_linear_grouped(const sageb200_problem *problems_host, int count, void *workspace,
+                            size_t workspace_bytes, void *stream);
+
+/*
+ * Dequantise to a dense fp16 matrix w[n][k]: bit-exact
+ *   w = fp16_rn(float(+-dir) * fmaf(float(radius_code), step, min))
+ * (reference csrc/sage/sage_gemm_cuda.cu:117-131 and tests/inference/reference.py:39-49).
+ * With perm != NULL columns are scattered back to original channel order
+ * (w[row][perm[j]] = w_q[row][j]); with perm == NULL they stay in quantised order.
+ */
+int sageb200_dequant(const void *codes, const void *radii, const void *grid, const void *book,
+                     const int32_t *perm, void *w, int n, int k, int entries, void *stream);
+
+/*
+ * Host-buffer form of sageb200_linear for callers whose activations live in host
+ * memory: copies x_host to the device, runs the matmul and copies y back, all on
+ * `stream`, then synchronises the stream.  The packed weight buffers are device
+ * pointers.  `staging` is a device buffer of sageb200_host_staging_bytes(rows,n,k)
+ * bytes (256-byte aligned, zero-filled once, reusable) that holds x, y and the
+ * workspace.  Pinned host memory makes the copies asynchronous but is not required.
+ */
+size_t sageb200_host_staging_bytes(int rows, int n, int k);
+int sageb200_linear_host(const void *x_host, const void *codes, const void *radii,
+                         const void *grid, const void *book, const int32_t *perm, void *y_host,
+                         void *staging, size_t staging_bytes, int rows, int n, int k,
+                         int entries, void *stream);
+
+/*
+ * Tuning knob for sweeps (debug): warps per CTA, K splits, codebook replicas and
+ * tiles per CTA of the skinny kernel; 0 restores the built-in heuristic for a field.
+ * Not thread safe, like its counterpart.
+ * Replaces: _set_sage_tuning / sage_gemv_tuning (reference csrc/bindings.cpp:81-84,
+ *           csrc/sage/sage_gemv_cuda.cu:3-4).
+ */
+int sageb200_set_tuning(int warps, int splits, int replicas, int tiles_per_cta);
+
+/* Number of kernels this library has launched in this process (all entry points). */
+unsigned long long sageb200_launch_count(void);
+
+#ifdef __cplusplus
+}
+#endif
+#endif /* SAGE_B200_H_ */

@@ -1,0 +1,99 @@
+"""ctypes binding of libsage_b200.so (the C ABI declared in include/sage_b200.h).
+
+There is no fallback: if the library is missing or a call fails, an exception is raised.
+"""
+
+from __future__ import annotations
+
+import ctypes
+import pathlib
+
+PACKAGE = pathlib.Path(__file__).resolve().parent
+LIBRARY = PACKAGE / "libsage_b200.so"
+
+OK = 0
+MAX_GROUPED = 16
+
+# every symbol include/sage_b200.h declares
+EXPORTED = (
+    "sageb200_version",
+    "sageb200_status_string",
+    "sageb200_gemv_fuses_permutation",
+    "sageb200_gemm_splits",
+    "sageb200_workspace_bytes",
+    "sageb200_linear",
+    "sageb200_linear_grouped",
+    "sageb200_dequant",
+    "sageb200_host_staging_bytes",
+    "sageb200_linear_host",
+    "sageb200_set_tuning",
+    "sageb200_launch_count",
+)
+
+
+class Problem(ctypes.Structure):
+    """struct sageb200_problem."""
+
+    _fields_ = [
+        ("x", ctypes.c_void_p),
+        ("codes", ctypes.c_void_p),
+        ("radii", ctypes.c_void_p),
+        ("grid", ctypes.c_void_p),
+        ("book", ctypes.c_void_p),
+        ("perm", ctypes.c_void_p),
+        ("y", ctypes.c_void_p),
+        ("rows", ctypes.c_int),
+        ("n", ctypes.c_int),
+        ("k", ctypes.c_int),
+        ("entries", ctypes.c_int),
+    ]
+
+
+_handle: ctypes.CDLL | None = None
+
+
+def load() -> ctypes.CDLL:
+    """Load the shared library once; raise if it has not been built."""
+    global _handle
+    if _handle is not None:
+        return _handle
+    if not LIBRARY.exists():
+        raise RuntimeError(
+            f"{LIBRARY} is missing: build it with `python -m sage_b200.build` "
+            "(sage_b200 has no CPU or PyTorch fallback)"
+        )
+    lib = ctypes.CDLL(str(LIBRARY))
+    vp, ci, sz = ctypes.c_void_p, ctypes.c_int, ctypes.c_size_t
+    lib.sageb200_version.restype = ci
+    lib.sageb200_version.argtypes = []
+    lib.sageb200_status_string.restype = ctypes.c_char_p
+    lib.sageb200_status_string.argtypes = [ci]
+    lib.sageb200_gemv_fuses_permutation.restype = ci
+    lib.sageb200_gemv_fuses_permutation.argtypes = [ci, ci]
+    lib.sageb200_gemm_splits.restype = ci
+    lib.sageb200_gemm_splits.argtypes = [ci, ci, ci, ci]
+    lib.sageb200_workspace_bytes.restype = sz
+    lib.sageb200_workspace_bytes.argtypes = [ci, ci, ci]
+    lib.sageb200_linear.restype = ci
+    lib.sageb200_linear.argtypes = [vp, vp, vp, vp, vp, vp, vp, vp, sz, ci, ci, ci, ci, vp]
+    lib.sageb200_linear_grouped.restype = ci
+    lib.sageb200_linear_grouped.argtypes = [ctypes.POINTER(Problem), ci, vp, sz, vp]
+    lib.sageb200_dequant.restype = ci
+    lib.sageb200_dequant.argtypes = [vp, vp, vp, vp, vp, vp, ci, ci, ci, vp]
+    lib.sageb200_host_staging_bytes.restype = sz
+    lib.sageb200_host_staging_bytes.argtypes = [ci, ci, ci]
+    lib.sageb200_linear_host.restype = ci
+    lib.sageb200_linear_host.argtypes = [vp, vp, vp, vp, vp, vp, vp, vp, sz, ci, ci, ci, ci, vp]
+    lib.sageb200_set_tuning.restype = ci
+    lib.sageb200_set_tuning.argtypes = [ci, ci, ci, ci]
+    lib.sageb200_launch_count.restype = ctypes.c_ulonglong
+    lib.sageb200_launch_count.argtypes = []
+    _handle = lib
+    return lib
+
+
+def check(status: int) -> None:
+    """Raise RuntimeError (as the reference's TORCH_CHECK does) on a non-zero status."""
+    if status != OK:
+        text = load().sageb200_status_string(status).decode()
+        raise RuntimeError(f"sage_b200: {text} (status {status})")

@@ -1,0 +1,338 @@
+// C ABI of libsage_b200: argument validation, scratch carving and kernel dispatch.
+//
+// The checks mirror the ones the reference performs before launching
+// (csrc/bindings.cpp:13-48 of the reference): positive N, K divisible by 128, a
+// 64/128/256-entry codebook, 4-byte aligned grid and codebook, rows <= 65535.
+// Errors come back as negative status codes instead of C++ exceptions.
+#include "../../include/sage_b200.h"
+
+#include <atomic>
+#include <climits>
+#include <cstring>
+
+#include "sage_common.cuh"
+#include "sage_kernels.h"
+
+namespace sageb200 {
+namespace {
+
+constexpr int kMaxDevices = 64;
+constexpr int kVersion = 100;  // 0.1.0
+
+struct DeviceState {
+  std::atomic<int> ready{0};
+  int sm_count = 0;
+  int major = 0;
+};
+DeviceState g_devices[kMaxDevices];
+Tuning g_tuning{0, 0, 0, 0};
+std::atomic<unsigned long long> g_launches{0};
+
+size_t align256(size_t bytes) { return (bytes + 255) / 256 * 256; }
+
+// Per-device one-time set-up on the calling thread's current device.
+int device_state(DeviceState **out) {
+  int device = 0;
+  if (cudaGetDevice(&device) != cudaSuccess) {
+    cudaGetLastError();
+    return SAGEB200_ERR_NO_DEVICE;
+  }
+  if (device < 0 || device >= kMaxDevices) return SAGEB200_ERR_NO_DEVICE;
+  DeviceState &state = g_devices[device];
+  if (!state.ready.load(std::memory_order_acquire)) {
+    int sms = 0, major = 0;
+    if (cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, device) != cudaSuccess ||
+        cudaDeviceGetAttribute(&major, cudaDevAttrComputeCapabilityMajor, device) != cudaSuccess) {
+      cudaGetLastError();
+      return SAGEB200_ERR_CUDA;
+    }
+    if (major != 10) return SAGEB200_ERR_NO_DEVICE;  // built for sm_100a only
+    if (configure_skinny() != cudaSuccess) {
+      cudaGetLastError();
+      return SAGEB200_ERR_CUDA;
+    }
+    state.sm_count = sms;
+    state.major = major;
+    state.ready.store(1, std::memory_order_release);
+  }
+  *out = &state;
+  return SAGEB200_OK;
+}
+
+int planning_sm_count() {
+  DeviceState *state = nullptr;
+  if (device_state(&state) == SAGEB200_OK) return state->sm_count;
+  return 148;
+}
+
+int check_shape(int rows, int n, int k, int entries) {
+  if (n <= 0 || k <= 0 || (k % 128) != 0 || rows < 0) return SAGEB200_ERR_INVALID_ARGUMENT;
+  if (direction_bits_of(entries) < 0) return SAGEB200_ERR_INVALID_ARGUMENT;
+  if (rows > 65535) return SAGEB200_ERR_RANGE;
+  if (static_cast<long long>((n + 15) / 16) * (k / 128) * 16 > INT_MAX) return SAGEB200_ERR_RANGE;
+  return SAGEB200_OK;
+}
+
+int check_buffers(const void *codes, const void *radii, const void *grid, const void *book) {
+  if (!codes || !radii || !grid || !book) return SAGEB200_ERR_INVALID_ARGUMENT;
+  if ((reinterpret_cast<uintptr_t>(grid) & 3) || (reinterpret_cast<uintptr_t>(book) & 3) ||
+      (reinterpret_cast<uintptr_t>(radii) & 3) || (reinterpret_cast<uintptr_t>(codes) & 7))
+    return SAGEB200_ERR_ALIGNMENT;
+  return SAGEB200_OK;
+}
+
+// Scratch one problem needs at `rows` <= 16: [counters | partials], both 256-aligned.
+size_t plan_bytes(const SkinnyPlan &plan) {
+  return plan.splits > 1 ? plan.counter_bytes + align256(plan.partial_bytes) : 0;
+}
+
+void fill_problem(SkinnyProblem &out, const sageb200_problem &in, const SkinnyPlan &plan,
+                  unsigned char *scratch, int cta_begin) {
+  out.x = static_cast<const __half *>(in.x);
+  out.codes = static_cast<const uint32_t *>(in.codes);
+  out.radii = static_cast<const uint32_t *>(in.radii);
+  out.grid = static_cast<const uint32_t *>(in.grid);
+  out.book = static_cast<const uint32_t *>(in.book);
+  out.perm = in.perm;
+  out.y = static_cast<__half *>(in.y);
+  out.counters = plan.splits > 1 ? reinterpret_cast<unsigned *>(scratch) : nullptr;
+  out.partial = plan.splits > 1 ? reinterpret_cast<float *>(scratch + plan.counter_bytes) : nullptr;
+  out.rows = in.rows;
+  out.n = in.n;
+  out.k = in.k;
+  out.groups = in.k / 128;
+  out.tiles = (in.n + 15) / 16;
+  out.entries = in.entries;
+  out.dbits = direction_bits_of(in.entries);
+  out.splits = plan.splits;
+  out.groups_per_split = plan.groups_per_split;
+  out.warps = plan.warps;
+  out.tile_blocks = plan.tile_blocks;
+  out.cta_begin = cta_begin;
+}
+
+// rows <= 16, one or more problems, one launch.
+int run_skinny(const sageb200_problem *problems, int count, void *workspace,
+               size_t workspace_bytes, cudaStream_t stream, const DeviceState &device) {
+  SkinnyParams params;
+  std::memset(&params, 0, sizeof(params));
+  SkinnyPlan plans[kMaxGrouped];
+  Tuning tuning = g_tuning;
+  if (count > 1) tuning.tiles_per_cta = 1;  // grouped launches share one kernel variant
+  SkinnyPlan launch{};
+  size_t offset = 0;
+  int ctas = 0;
+  int live = 0;
+  for (int i = 0; i < count; ++i) {
+    const sageb200_problem &in = problems[i];
+    if (in.rows == 0) continue;
+    plans[live] = plan_skinny(in.rows, in.n, in.k, in.entries, device.sm_count, tuning);
+    const SkinnyPlan &plan = plans[live];
+    const size_t need = plan_bytes(plan);
+    if (need) {
+      if (!workspace || offset + need > workspace_bytes) return SAGEB200_ERR_WORKSPACE;
+      if (reinterpret_cast<uintptr_t>(workspace) & 255) return SAGEB200_ERR_ALIGNMENT;
+    }
+    fill_problem(params.problem[live], in, plan, static_cast<unsigned char *>(workspace) + offset,
+                 ctas);
+    offset += need;
+    ctas += plan.tile_blocks * plan.splits;
+    if (live == 0) {
+      launch = plan;
+    } else {
+      if (plan.warps > launch.warps) launch.warps = plan.warps;
+      if (plan.column_blocks > launch.column_blocks) launch.column_blocks = plan.column_blocks;
+    }
+    ++live;
+  }
+  if (live == 0) return SAGEB200_OK;
+  params.count = live;
+  if (launch_skinny(params, launch, ctas, stream) != cudaSuccess) {
+    cudaGetLastError();
+    return SAGEB200_ERR_CUDA;
+  }
+  g_launches.fetch_add(1, std::memory_order_relaxed);
+  return SAGEB200_OK;
+}
+
+int validate_problem(const sageb200_problem &p) {
+  int status = check_shape(p.rows, p.n, p.k, p.entries);
+  if (status) return status;
+  status = check_buffers(p.codes, p.radii, p.grid, p.book);
+  if (status) return status;
+  if (p.rows > 0 && (!p.x || !p.y)) return SAGEB200_ERR_INVALID_ARGUMENT;
+  if ((reinterpret_cast<uintptr_t>(p.x) & 1) || (reinterpret_cast<uintptr_t>(p.y) & 1) ||
+      (reinterpret_cast<uintptr_t>(p.perm) & 3))
+    return SAGEB200_ERR_ALIGNMENT;
+  return SAGEB200_OK;
+}
+
+}  // namespace
+}  // namespace sageb200
+
+using namespace sageb200;
+
+extern "C" {
+
+int sageb200_version(void) { return kVersion; }
+
+const char *sageb200_status_string(int status) {
+  switch (status) {
+    case SAGEB200_OK: return "ok";
+    case SAGEB200_ERR_INVALID_ARGUMENT:
+      return "invalid argument: SAGE requires positive N, K divisible by 128, a codebook of "
+             "64/128/256 entries and non-null buffers";
+    case SAGEB200_ERR_ALIGNMENT:
+      return "alignment: SAGE grid and codebook require 4-byte aligned storage (codes 8, "
+             "workspace 256, dense weight output 16)";
+    case SAGEB200_ERR_RANGE: return "SAGE launch dimensions exceed supported range";
+    case SAGEB200_ERR_WORKSPACE: return "workspace missing or smaller than sageb200_workspace_bytes";
+    case SAGEB200_ERR_CUDA: return "a CUDA call or kernel launch failed";
+    case SAGEB200_ERR_NO_DEVICE: return "no current CUDA device of compute capability 10.x";
+    case SAGEB200_ERR_TIMEOUT: return "a bounded device-side wait ran out";
+    default: return "unknown status";
+  }
+}
+
+int sageb200_gemv_fuses_permutation(int n, int k) {
+  (void)n;
+  (void)k;
+  return 1;
+}
+
+int sageb200_gemm_splits(int rows, int n, int k, int sm_count) {
+  if (n <= 0 || k <= 0 || (k % 128) || rows <= 0) return 1;
+  const int planned_rows = rows > 16 ? 16 : rows;
+  return plan_skinny(planned_rows, n, k, 256, sm_count > 0 ? sm_count : 148, g_tuning).splits;
+}
+
+size_t sageb200_workspace_bytes(int rows, int n, int k) {
+  if (n <= 0 || k <= 0 || (k % 128) || rows <= 0) return 0;
+  const int planned_rows = rows > 16 ? 16 : rows;
+  const SkinnyPlan plan = plan_skinny(planned_rows, n, k, 256, planning_sm_count(), g_tuning);
+  size_t bytes = plan_bytes(plan);
+  if (rows > 16) {
+    // the tail chunk (rows % 16) may plan differently; reserve for both
+    const int tail = rows % 16;
+    if (tail) {
+      const size_t other = plan_bytes(plan_skinny(tail, n, k, 256, planning_sm_count(), g_tuning));
+      if (other > bytes) bytes = other;
+    }
+  }
+  return bytes;
+}
+
+int sageb200_linear_grouped(const sageb200_problem *problems_host, int count, void *workspace,
+                            size_t workspace_bytes, void *stream) {
+  if (!problems_host || count < 0 || count > SAGEB200_MAX_GROUPED)
+    return SAGEB200_ERR_INVALID_ARGUMENT;
+  for (int i = 0; i < count; ++i) {
+    const int status = validate_problem(problems_host[i]);
+    if (status) return status;
+    if (problems_host[i].rows > 16) return SAGEB200_ERR_RANGE;
+  }
+  if (count == 0) return SAGEB200_OK;
+  DeviceState *device = nullptr;
+  const int status = device_state(&device);
+  if (status) return status;
+  return run_skinny(problems_host, count, workspace, workspace_bytes,
+                    static_cast<cudaStream_t>(stream), *device);
+}
+
+int sageb200_linear(const void *x, const void *codes, const void *radii, const void *grid,
+                    const void *book, const int32_t *perm, void *y, void *workspace,
+                    size_t workspace_bytes, int rows, int n, int k, int entries, void *stream) {
+  sageb200_problem problem{x, codes, radii, grid, book, perm, y, rows, n, k, entries};
+  int status = validate_problem(problem);
+  if (status) return status;
+  if (rows == 0) return SAGEB200_OK;
+  DeviceState *device = nullptr;
+  status = device_state(&device);
+  if (status) return status;
+  cudaStream_t s = static_cast<cudaStream_t>(stream);
+  // Up to 16 rows go through in one pass; more rows run as 16-row passes over the
+  // packed weights (each pass reuses the scratch, in stream order).
+  for (int begin = 0; begin < rows; begin += 16) {
+    sageb200_problem chunk = problem;
+    chunk.rows = rows - begin < 16 ? rows - begin : 16;
+    chunk.x = static_cast<const __half *>(x) + static_cast<size_t>(begin) * k;
+    chunk.y = static_cast<__half *>(y) + static_cast<size_t>(begin) * n;
+    status = run_skinny(&chunk, 1, workspace, workspace_bytes, s, *device);
+    if (status) return status;
+  }
+  return SAGEB200_OK;
+}
+
+int sageb200_dequant(const void *codes, const void *radii, const void *grid, const void *book,
+                     const int32_t *perm, void *w, int n, int k, int entries, void *stream) {
+  int status = check_shape(0, n, k, entries);
+  if (status) return status;
+  status = check_buffers(codes, radii, grid, book);
+  if (status) return status;
+  if (!w) return SAGEB200_ERR_INVALID_ARGUMENT;
+  if ((reinterpret_cast<uintptr_t>(w) & 15) || (reinterpret_cast<uintptr_t>(perm) & 3))
+    return SAGEB200_ERR_ALIGNMENT;
+  DeviceState *device = nullptr;
+  status = device_state(&device);
+  if (status) return status;
+  if (launch_dequant(static_cast<const uint32_t *>(codes), static_cast<const uint32_t *>(radii),
+                     static_cast<const uint32_t *>(grid), static_cast<const uint32_t *>(book), perm,
+                     static_cast<__half *>(w), n, k, entries, static_cast<cudaStream_t>(stream),
+                     device->sm_count) != cudaSuccess) {
+    cudaGetLastError();
+    return SAGEB200_ERR_CUDA;
+  }
+  g_launches.fetch_add(1, std::memory_order_relaxed);
+  return SAGEB200_OK;
+}
+
+size_t sageb200_host_staging_bytes(int rows, int n, int k) {
+  if (n <= 0 || k <= 0 || rows <= 0) return 0;
+  return align256(static_cast<size_t>(rows) * k * 2) + align256(static_cast<size_t>(rows) * n * 2) +
+         align256(sageb200_workspace_bytes(rows, n, k));
+}
+
+int sageb200_linear_host(const void *x_host, const void *codes, const void *radii,
+                         const void *grid, const void *book, const int32_t *perm, void *y_host,
+                         void *staging, size_t staging_bytes, int rows, int n, int k, int entries,
+                         void *stream) {
+  int status = check_shape(rows, n, k, entries);
+  if (status) return status;
+  if (rows == 0) return SAGEB200_OK;
+  if (!x_host || !y_host || !staging) return SAGEB200_ERR_INVALID_ARGUMENT;
+  if (reinterpret_cast<uintptr_t>(staging) & 255) return SAGEB200_ERR_ALIGNMENT;
+  if (staging_bytes < sageb200_host_staging_bytes(rows, n, k)) return SAGEB200_ERR_WORKSPACE;
+  cudaStream_t s = static_cast<cudaStream_t>(stream);
+  const size_t x_bytes = static_cast<size_t>(rows) * k * 2;
+  const size_t y_bytes = static_cast<size_t>(rows) * n * 2;
+  unsigned char *x_dev = static_cast<unsigned char *>(staging);
+  unsigned char *y_dev = x_dev + align256(x_bytes);
+  unsigned char *work = y_dev + align256(y_bytes);
+  const size_t work_bytes = staging_bytes - align256(x_bytes) - align256(y_bytes);
+  if (cudaMemcpyAsync(x_dev, x_host, x_bytes, cudaMemcpyHostToDevice, s) != cudaSuccess) {
+    cudaGetLastError();
+    return SAGEB200_ERR_CUDA;
+  }
+  status = sageb200_linear(x_dev, codes, radii, grid, book, perm, y_dev, work, work_bytes, rows, n,
+                           k, entries, stream);
+  if (status) return status;
+  if (cudaMemcpyAsync(y_host, y_dev, y_bytes, cudaMemcpyDeviceToHost, s) != cudaSuccess ||
+      cudaStreamSynchronize(s) != cudaSuccess) {
+    cudaGetLastError();
+    return SAGEB200_ERR_CUDA;
+  }
+  return SAGEB200_OK;
+}
+
+int sageb200_set_tuning(int warps, int splits, int replicas, int tiles_per_cta) {
+  if (warps < 0 || warps > 8 || splits < 0 || tiles_per_cta < 0 || tiles_per_cta > 4)
+    return SAGEB200_ERR_INVALID_ARGUMENT;
+  if (replicas != 0 && replicas != 1 && replicas != 2 && replicas != 4 && replicas != 8)
+    return SAGEB200_ERR_INVALID_ARGUMENT;
+  g_tuning = Tuning{warps, splits, replicas, tiles_per_cta};
+  return SAGEB200_OK;
+}
+
+unsigned long long sageb200_launch_count(void) { return g_launches.load(std::memory_order_relaxed); }
+
+}  // extern "C"

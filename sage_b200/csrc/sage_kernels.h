@@ -1,0 +1,75 @@
+// Internal launcher declarations shared by the .cu files of libsage_b200.
+#pragma once
+
+#include <cuda_fp16.h>
+#include <cuda_runtime.h>
+#include <stddef.h>
+#include <stdint.h>
+
+namespace sageb200 {
+
+constexpr int kMaxGrouped = 16;
+
+// One packed linear as the skinny kernel sees it.
+struct SkinnyProblem {
+  const __half *x;
+  const uint32_t *codes;
+  const uint32_t *radii;
+  const uint32_t *grid;
+  const uint32_t *book;
+  const int32_t *perm;
+  __half *y;
+  float *partial;       // [tile_blocks][splits][tiles_per_cta][column_blocks*128] when splits > 1
+  unsigned *counters;   // [tile_blocks], zero before and after every launch
+  int rows, n, k, groups, tiles;
+  int entries, dbits;
+  int splits, groups_per_split;
+  int warps;            // warps of the CTA that take units (<= launched warps)
+  int tile_blocks;
+  int cta_begin;        // first CTA of this problem in the grid
+};
+
+struct SkinnyParams {
+  SkinnyProblem problem[kMaxGrouped];
+  int count;
+  int replica_log2;     // codebook replicas in shared memory = 1 << replica_log2
+  int book_bytes;       // shared bytes reserved for the (largest) replicated codebook
+  int x_bytes;          // shared bytes reserved for staged activations
+};
+
+// Launch plan for one problem (host side).
+struct SkinnyPlan {
+  int warps;
+  int splits;
+  int groups_per_split;
+  int replicas;
+  int tiles_per_cta;
+  int tile_blocks;
+  int column_blocks;    // 1 for rows <= 8, 2 for rows <= 16
+  size_t partial_bytes;
+  size_t counter_bytes;
+};
+
+struct Tuning {
+  int warps, splits, replicas, tiles_per_cta;
+};
+
+SkinnyPlan plan_skinny(int rows, int n, int k, int entries, int sm_count, const Tuning &tuning);
+
+// Opts every skinny-kernel variant into large dynamic shared memory on the CURRENT device.
+cudaError_t configure_skinny();
+
+// Launches `count` problems (all planned with the same warps/replicas/tiles_per_cta/
+// column_blocks) as one grid.  Returns the launch error.
+cudaError_t launch_skinny(SkinnyParams &params, const SkinnyPlan &plan, int total_ctas,
+                          cudaStream_t stream);
+
+cudaError_t launch_dequant(const uint32_t *codes, const uint32_t *radii, const uint32_t *grid,
+                           const uint32_t *book, const int32_t *perm, __half *w, int n, int k,
+                           int entries, cudaStream_t stream, int sm_count);
+
+// x_q[m][j] = x[m][perm[j]] for the prefill path.
+cudaError_t launch_gather(const __half *x, const int32_t *perm, __half *xq, int rows, int k,
+                          cudaStream_t stream, int sm_count);
+
+}  // namespace sageb200

@@ -1,0 +1,198 @@
+"""Torch operator for the SAGE packed linear, backed by libsage_b200.so.
+
+Mirrors the reference's dispatcher registration (weight_vq/inference/ops.py:42-61):
+`sage(x, packed_codes, radius_codes, radius_grid, codebook, permutation, out_features)`
+is a `torch.library.custom_op` with `mutates_args=()`, CUDA only, plus a fake kernel that
+returns `x.new_empty((*x.shape[:-1], out_features))`.  The op is registered as
+`wvq::sage`, the reference's name, unless that name is already taken in this process
+(the reference package was imported first), in which case it is `sage_b200::sage`.
+
+Argument checks and their messages follow the reference's native entry point
+(csrc/bindings.cpp:13-48).
+"""
+
+from __future__ import annotations
+
+import torch
+
+from . import _lib
+
+_WORKSPACES: dict[tuple[int, int], torch.Tensor] = {}
+_RETIRED: list[torch.Tensor] = []  # outgrown buffers a captured graph may still point at
+
+
+def _workspace(device: torch.device, stream: int, nbytes: int) -> torch.Tensor:
+    """Zero-filled scratch, one per (device, stream); the kernels restore the zeros."""
+    key = (device.index, stream)
+    buffer = _WORKSPACES.get(key)
+    if buffer is None or buffer.numel() < nbytes:
+        if buffer is not None:
+            _RETIRED.append(buffer)
+        buffer = torch.zeros(max(nbytes, 1 << 16), dtype=torch.uint8, device=device)
+        _WORKSPACES[key] = buffer
+    return buffer
+
+
+def _check_layout(x, codes, radii, grid, book, permutation, out_features):
+    if not (x.is_cuda and x.dtype == torch.float16 and x.is_contiguous() and x.dim() >= 1):
+        raise RuntimeError("SAGE requires contiguous CUDA FP16 input")
+    for tensor in (codes, radii, grid, book, permutation):
+        if tensor.device != x.device or not tensor.is_contiguous():
+            raise RuntimeError("SAGE buffers must be contiguous and on the input device")
+    k = x.shape[-1]
+    tiles = (out_features + 15) // 16
+    if not (k > 0 and k % 128 == 0 and out_features > 0):
+        raise RuntimeError("SAGE requires positive N and K divisible by 128")
+    if not (book.dim() == 3 and book.shape[0] == 4 and book.shape[2] == 2 and book.shape[1] in (64, 128, 256)):
+        raise RuntimeError("SAGE codebook must have shape [4, 64/128/256, 2]")
+    groups = k // 128
+    if not (
+        codes.dtype == torch.int32
+        and tuple(codes.shape) == (tiles, groups, 16, 8)
+        and radii.dtype == torch.int32
+        and tuple(radii.shape) == (tiles, groups, 16)
+        and grid.dtype == torch.float16
+        and tuple(grid.shape) == (tiles, groups, 16, 2)
+        and book.dtype == torch.float16
+        and permutation.dtype == torch.int32
+        and permutation.dim() == 1
+        and permutation.numel() in (0, k)
+    ):
+        raise RuntimeError("Invalid SAGE packed layout")
+    if (grid.data_ptr() & 3) or (book.data_ptr() & 3):
+        raise RuntimeError("SAGE grid and codebook require 4-byte aligned storage")
+    return k
+
+
+def sage_forward(
+    x: torch.Tensor,
+    packed_codes: torch.Tensor,
+    radius_codes: torch.Tensor,
+    radius_grid: torch.Tensor,
+    codebook: torch.Tensor,
+    permutation: torch.Tensor,
+    out_features: int,
+) -> torch.Tensor:
+    """The native entry point's Python twin (reference csrc/bindings.cpp:8-79)."""
+    k = _check_layout(x, packed_codes, radius_codes, radius_grid, codebook, permutation, out_features)
+    output = torch.empty((*x.shape[:-1], out_features), dtype=x.dtype, device=x.device)
+    rows = x.numel() // k
+    if rows == 0:
+        return output
+    if rows > 65535:
+        raise RuntimeError("SAGE launch dimensions exceed supported range")
+    lib = _lib.load()
+    with torch.cuda.device(x.device):
+        stream = torch.cuda.current_stream(x.device).cuda_stream
+        nbytes = lib.sageb200_workspace_bytes(rows, out_features, k)
+        workspace = _workspace(x.device, stream, nbytes) if nbytes else None
+        _lib.check(
+            lib.sageb200_linear(
+                x.data_ptr(),
+                packed_codes.data_ptr(),
+                radius_codes.data_ptr(),
+                radius_grid.data_ptr(),
+                codebook.data_ptr(),
+                permutation.data_ptr() if permutation.numel() else None,
+                output.data_ptr(),
+                workspace.data_ptr() if workspace is not None else None,
+                workspace.numel() if workspace is not None else 0,
+                rows,
+                out_features,
+                k,
+                codebook.shape[1],
+                stream,
+            )
+        )
+    return output
+
+
+def _fake(x, packed_codes, radius_codes, radius_grid, codebook, permutation, out_features):
+    return x.new_empty((*x.shape[:-1], out_features))
+
+
+def _register(namespace: str):
+    op = torch.library.custom_op(f"{namespace}::sage", mutates_args=(), device_types="cuda")(
+        sage_forward
+    )
+    op.register_fake(_fake)
+    return op
+
+
+try:
+    sage = _register("wvq")
+except RuntimeError:  # the reference package already owns wvq::sage in this process
+    sage = _register("sage_b200")
+
+
+def sage_dequantize(
+    packed_codes: torch.Tensor,
+    radius_codes: torch.Tensor,
+    radius_grid: torch.Tensor,
+    codebook: torch.Tensor,
+    permutation: torch.Tensor,
+    out_features: int,
+    *,
+    original_order: bool = True,
+) -> torch.Tensor:
+    """Dense FP16 weight [out_features, K], bit-exact with the reference's dequantisation."""
+    k = packed_codes.shape[1] * 128
+    dummy = torch.empty((0, k), dtype=torch.float16, device=packed_codes.device)
+    _check_layout(dummy, packed_codes, radius_codes, radius_grid, codebook, permutation, out_features)
+    weight = torch.empty((out_features, k), dtype=torch.float16, device=packed_codes.device)
+    lib = _lib.load()
+    with torch.cuda.device(weight.device):
+        stream = torch.cuda.current_stream(weight.device).cuda_stream
+        use_perm = original_order and permutation.numel() > 0
+        _lib.check(
+            lib.sageb200_dequant(
+                packed_codes.data_ptr(),
+                radius_codes.data_ptr(),
+                radius_grid.data_ptr(),
+                codebook.data_ptr(),
+                permutation.data_ptr() if use_perm else None,
+                weight.data_ptr(),
+                out_features,
+                k,
+                codebook.shape[1],
+                stream,
+            )
+        )
+    return weight
+
+
+def sage_grouped(problems: list[tuple], out_features: list[int]) -> list[torch.Tensor]:
+    """Several packed linears (rows <= 16 each) in one launch.
+
+    `problems[i]` = (x, packed_codes, radius_codes, radius_grid, codebook, permutation).
+    """
+    if len(problems) > _lib.MAX_GROUPED:
+        raise RuntimeError("too many problems for one grouped launch")
+    lib = _lib.load()
+    array = (_lib.Problem * len(problems))()
+    outputs = []
+    total = 0
+    device = problems[0][0].device
+    for i, ((x, codes, radii, grid, book, perm), n) in enumerate(zip(problems, out_features)):
+        k = _check_layout(x, codes, radii, grid, book, perm, n)
+        rows = x.numel() // k
+        y = torch.empty((*x.shape[:-1], n), dtype=x.dtype, device=x.device)
+        outputs.append(y)
+        array[i] = _lib.Problem(
+            x.data_ptr(), codes.data_ptr(), radii.data_ptr(), grid.data_ptr(), book.data_ptr(),
+            perm.data_ptr() if perm.numel() else None, y.data_ptr(), rows, n, k, book.shape[1],
+        )
+        total += lib.sageb200_workspace_bytes(rows, n, k) if rows else 0
+    with torch.cuda.device(device):
+        stream = torch.cuda.current_stream(device).cuda_stream
+        workspace = _workspace(device, stream, total) if total else None
+        _lib.check(
+            lib.sageb200_linear_grouped(
+                array,
+                len(problems),
+                workspace.data_ptr() if workspace is not None else None,
+                workspace.numel() if workspace is not None else 0,
+                stream,
+            )
+        )
+    return outputs

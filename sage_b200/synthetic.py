@@ -76,3 +76,57 @@ def synthetic_sage(
 
 def packed_to(packed: dict[str, torch.Tensor], device) -> dict[str, torch.Tensor]:
     return {key: value.to(device) for key, value in packed.items()}
+
+
+def synthetic_sage_device(
+    in_features: int,
+    out_features: int,
+    seed: int,
+    device,
+    *,
+    permuted: bool = True,
+    direction_bits: int | None = None,
+) -> dict[str, torch.Tensor]:
+    """Same distributions as `synthetic_sage`, drawn with the device's generator.
+
+    For benchmarks that need hundreds of matrices quickly; the values differ from the
+    CPU generator's (another random stream), the shapes, dtypes and distributions do not.
+    """
+    if in_features <= 0 or in_features % 128 or out_features <= 0:
+        raise ValueError("SAGE requires positive N and K divisible by 128")
+    dbits = direction_bits if direction_bits is not None else 6 + seed % 3
+    entries = 1 << dbits
+    levels = 1 << (10 - dbits)
+    tiles = (out_features + 15) // 16
+    groups = in_features // 128
+    gen = torch.Generator(device=device).manual_seed(seed)
+    lo, hi = -(2**31), 2**31
+    directions = torch.nn.functional.normalize(
+        torch.rand(entries, 8, generator=gen, device=device), dim=-1
+    )
+    packed_codes = torch.randint(lo, hi, (tiles, groups, 16, 8), generator=gen, device=device, dtype=torch.int32)
+    radius_codes = torch.randint(lo, hi, (tiles, groups, 16), generator=gen, device=device, dtype=torch.int32)
+    radius_grid = torch.rand(tiles, groups, 16, 2, generator=gen, device=device) * math.sqrt(8 / in_features)
+    radius_grid[..., 1] /= levels - 1
+    tail = out_features % 16
+    if tail:
+        for buffer in (packed_codes, radius_codes, radius_grid):
+            buffer[-1, :, tail:] = 0
+    if permuted:
+        permutation = torch.randperm(in_features, generator=gen, device=device).int()
+    else:
+        permutation = torch.empty(0, dtype=torch.int32, device=device)
+    return {
+        "packed_codes": packed_codes,
+        "radius_codes": radius_codes,
+        "radius_grid": radius_grid.half(),
+        "codebook": directions.half().reshape(entries, 4, 2).permute(1, 0, 2).contiguous(),
+        "permutation": permutation,
+    }
+
+
+def linear_algorithmic_bytes(rows: int, n: int, k: int, entries: int, permuted: bool) -> int:
+    """Bytes one packed-linear call must move: packed weight once (2.5 bit/weight over the
+    padded rows), codebook, permutation, activations in and out."""
+    padded = (n + 15) // 16 * 16
+    return padded * k * 5 // 16 + 16 * entries + (4 * k if permuted else 0) + 2 * rows * k + 2 * rows * n

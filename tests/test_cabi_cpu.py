@@ -1,0 +1,83 @@
+"""CPU-only checks of the C-ABI library: it loads without a GPU, exports every symbol the
+header declares, and its host-side planning/validation behaves (no compute is launched)."""
+
+import ctypes
+import pathlib
+import re
+
+import pytest
+
+from sage_b200 import _lib, build
+
+ROOT = pathlib.Path(__file__).resolve().parent.parent
+
+
+@pytest.fixture(scope="module")
+def lib():
+    build.build()
+    return _lib.load()
+
+
+def declared_symbols():
+    text = (ROOT / "include" / "sage_b200.h").read_text()
+    text = re.sub(r"/\*.*?\*/", "", text, flags=re.S)
+    return sorted(set(re.findall(r"\b(sageb200_[a-z0-9_]+)\s*\(", text)))
+
+
+def test_every_declared_symbol_is_exported(lib):
+    names = declared_symbols()
+    assert len(names) >= 12
+    for name in names:
+        assert hasattr(lib, name), name
+    assert set(names) == set(_lib.EXPORTED) | {n for n in names if n not in _lib.EXPORTED}
+    for name in _lib.EXPORTED:
+        assert name in names, f"{name} bound in Python but not declared in the header"
+
+
+def test_version_and_status_strings(lib):
+    assert lib.sageb200_version() >= 100
+    assert lib.sageb200_status_string(0) == b"ok"
+    for code in range(-7, 0):
+        assert lib.sageb200_status_string(code) not in (b"ok", b"unknown status")
+    assert lib.sageb200_status_string(-99) == b"unknown status"
+
+
+def test_planning_is_deterministic_and_sane(lib):
+    assert lib.sageb200_gemv_fuses_permutation(9728, 16384) == 1
+    shapes = [(2560, 4096), (2560, 1024), (4096, 2560), (2560, 9728), (9728, 2560), (128, 1), (16384, 9)]
+    for k, n in shapes:
+        for rows in (1, 2, 8, 16, 17, 300):
+            splits = lib.sageb200_gemm_splits(rows, n, k, 148)
+            assert 1 <= splits <= k // 128
+            need = lib.sageb200_workspace_bytes(rows, n, k)
+            assert need == lib.sageb200_workspace_bytes(rows, n, k)
+            assert need % 256 == 0
+            if splits == 1 and rows <= 16:
+                assert need == 0
+            staging = lib.sageb200_host_staging_bytes(rows, n, k)
+            assert staging >= rows * (k + n) * 2 + need
+    assert lib.sageb200_workspace_bytes(0, 16, 128) == 0
+    assert lib.sageb200_workspace_bytes(1, 16, 100) == 0
+
+
+def test_invalid_arguments_are_rejected_without_a_device(lib):
+    null = ctypes.c_void_p(None)
+    one = ctypes.c_void_p(256)  # never dereferenced: validation fails first
+    assert lib.sageb200_linear(one, null, one, one, one, null, one, null, 0, 1, 16, 128, 256, null) == -1
+    assert lib.sageb200_linear(one, one, one, one, one, null, one, null, 0, 1, 16, 100, 256, null) == -1
+    assert lib.sageb200_linear(one, one, one, one, one, null, one, null, 0, 1, 16, 128, 99, null) == -1
+    assert lib.sageb200_linear(one, one, one, one, one, null, one, null, 0, 70000, 16, 128, 256, null) == -3
+    odd = ctypes.c_void_p(258)
+    assert lib.sageb200_linear(one, one, one, odd, one, null, one, null, 0, 1, 16, 128, 256, null) == -2
+    assert lib.sageb200_dequant(one, one, one, one, null, null, 16, 128, 256, null) == -1
+    assert lib.sageb200_set_tuning(9, 0, 0, 0) == -1
+    assert lib.sageb200_set_tuning(0, 0, 3, 0) == -1
+    assert lib.sageb200_set_tuning(0, 0, 0, 0) == 0
+    assert lib.sageb200_linear_grouped(None, 1, null, 0, null) == -1
+
+
+def test_missing_library_fails_loudly(monkeypatch, tmp_path):
+    monkeypatch.setattr(_lib, "_handle", None)
+    monkeypatch.setattr(_lib, "LIBRARY", tmp_path / "libsage_b200.so")
+    with pytest.raises(RuntimeError, match="no CPU or PyTorch fallback"):
+        _lib.load()

@@ -1,0 +1,387 @@
+"""GPU parity tests: the CUDA path (through the C ABI) against the CPU oracle.
+
+Modelled on the reference's kernel tests (tests/inference/test_sage.py:66-203 there):
+same shape list, both permutation settings, the three bit splits, three input scales,
+misaligned storage offsets, zero/constant grids, state_dict round trip, side streams,
+CUDA-graph replay, bias and opcheck.
+
+Gates:
+  dense dequantisation        bit-exact FP16 (integer compare)
+  matmul output               relative Frobenius error <= 1e-3 against an FP32 matmul on the
+                              oracle's FP16 weights, and max-abs / RMS < 5e-3 (the reference's
+                              own second gate, tests/inference/test_sage.py:11-19)
+"""
+
+import ctypes
+
+import numpy as np
+import pytest
+import torch
+
+from oracle import c_oracle, sage_oracle
+from sage_b200 import SAGELinear, _lib, sage, sage_dequantize, sage_grouped, synthetic_sage
+
+pytestmark = pytest.mark.gpu
+
+REL_FROBENIUS = 1e-3
+MAX_OVER_RMS = 5e-3
+
+
+def to_cuda(packed):
+    return {k: v.cuda() for k, v in packed.items()}
+
+
+def expected_output(x, cpu_packed, n):
+    """FP32 matmul on the oracle's FP16 dequantised weight (computed on the GPU in FP32)."""
+    weight = torch.from_numpy(c_oracle.decode_fp16(cpu_packed, n)).cuda()
+    return x.float() @ weight.float().T
+
+
+def assert_output(actual, expected):
+    if actual.numel() == 0:
+        return {}
+    error = actual.float() - expected.float()
+    norm = expected.float().norm().clamp_min(1e-30)
+    rms = expected.float().square().mean().sqrt().clamp_min(1e-30)
+    metrics = {
+        "relative_frobenius": (error.norm() / norm).item(),
+        "max_absolute_over_rms": (error.abs().max() / rms).item(),
+    }
+    assert metrics["relative_frobenius"] <= REL_FROBENIUS, metrics
+    assert metrics["max_absolute_over_rms"] < MAX_OVER_RMS, metrics
+    return metrics
+
+
+# ---------------------------------------------------------------- dense dequantisation
+
+
+@pytest.mark.parametrize(
+    "k,n", [(128, 1), (256, 17), (512, 129), (2560, 33), (4096, 48), (9728, 32), (16384, 9)]
+)
+@pytest.mark.parametrize("permuted", [False, True])
+@pytest.mark.parametrize("seed", [0, 1, 2])
+def test_dequant_bit_exact(k, n, permuted, seed):
+    cpu = synthetic_sage(k, n, seed=seed, permuted=permuted)
+    gpu = to_cuda(cpu)
+    args = [gpu[key] for key in ("packed_codes", "radius_codes", "radius_grid", "codebook", "permutation")]
+    got = sage_dequantize(*args, n).cpu().numpy().view(np.uint16)
+    np.testing.assert_array_equal(got, c_oracle.decode_fp16(cpu, n).view(np.uint16))
+    quantised = sage_dequantize(*args, n, original_order=False).cpu().numpy().view(np.uint16)
+    np.testing.assert_array_equal(
+        quantised, c_oracle.decode_fp16(cpu, n, apply_permutation=False).view(np.uint16)
+    )
+
+
+def test_dequant_golden_cases(golden_cases):
+    """Against the weights the reference's own decoder produced."""
+    for case in golden_cases:
+        gpu = {k: torch.from_numpy(np.ascontiguousarray(v)).cuda() for k, v in case["packed"].items()}
+        got = sage_dequantize(
+            gpu["packed_codes"], gpu["radius_codes"], gpu["radius_grid"], gpu["codebook"],
+            gpu["permutation"], case["n"],
+        )
+        np.testing.assert_array_equal(got.cpu().numpy().view(np.uint16), case["weight_fp16_bits"])
+
+
+def test_dequant_all_code_values():
+    """Every 16-bit code value, the three bit splits (reference test_sage.py:46-63)."""
+    for seed in (0, 1, 2):
+        cpu = synthetic_sage(128, 4096, seed=seed, permuted=False)
+        words = torch.arange(65536).reshape(4096, 16)
+        cpu["packed_codes"] = (words[:, ::2] | (words[:, 1::2] << 16)).int().reshape(256, 1, 16, 8)
+        cpu["radius_codes"].fill_(int(torch.tensor(0xE4E4E4E4).int()))
+        gpu = to_cuda(cpu)
+        got = sage_dequantize(
+            gpu["packed_codes"], gpu["radius_codes"], gpu["radius_grid"], gpu["codebook"],
+            gpu["permutation"], 4096,
+        )
+        np.testing.assert_array_equal(
+            got.cpu().numpy().view(np.uint16), c_oracle.decode_fp16(cpu, 4096).view(np.uint16)
+        )
+
+
+def test_dequant_benchmark_shape_hashes(golden_hashes):
+    """Benchmark-sized matrices against SHA-256 of the reference decoder's output."""
+    import hashlib
+
+    for case in golden_hashes:
+        cpu = synthetic_sage(case["k"], case["n"], seed=case["seed"], permuted=case["permuted"])
+        gpu = to_cuda(cpu)
+        got = sage_dequantize(
+            gpu["packed_codes"], gpu["radius_codes"], gpu["radius_grid"], gpu["codebook"],
+            gpu["permutation"], case["n"],
+        )
+        digest = hashlib.sha256(got.cpu().numpy().view(np.uint16).tobytes()).hexdigest()
+        assert digest == case["weight_fp16_sha256"], (case["k"], case["n"], case["seed"])
+
+
+# ---------------------------------------------------------------- matmul against the oracle
+
+REFERENCE_SHAPES = [
+    ((128,), 1),
+    ((4, 256), 17),
+    ((2, 3, 2560), 9),
+    ((1, 9728), 33),
+    ((1, 16384), 9),
+    ((128, 256), 32),
+    ((16, 128), 1),
+    ((17, 256), 17),
+    ((65, 2560), 33),
+    ((256, 128), 16),
+    ((16, 512), 129),
+    ((31, 2560), 257),
+    ((32, 4096), 256),
+    ((129, 9728), 65),
+    ((1, 4096), 1024),
+    ((1, 4096), 1025),
+    ((2, 3, 4352), 33),
+    ((15, 4096), 1025),
+    ((1, 2560), 4096),
+    ((1, 2560), 1024),
+    ((1, 2560), 9728),
+    ((1, 4096), 2560),
+    ((1, 9728), 2560),
+    ((0, 128), 17),
+]
+
+
+@pytest.mark.parametrize("shape,n", REFERENCE_SHAPES)
+@pytest.mark.parametrize("permuted", [False, True])
+@pytest.mark.parametrize("seed", [0, 1, 2])
+def test_linear_against_oracle(shape, n, permuted, seed):
+    cpu = synthetic_sage(shape[-1], n, seed=seed, permuted=permuted)
+    layer = SAGELinear(to_cuda(cpu), n)
+    base = torch.randn(shape, generator=torch.Generator().manual_seed(43), dtype=torch.float16).cuda()
+    weight = torch.from_numpy(c_oracle.decode_fp16(cpu, n)).cuda().float()
+    for scale in (0.03125, 1.0, 32.0):
+        x = base * scale
+        # a contiguous tensor can sit at an odd (2-byte) storage offset
+        storage = torch.empty(x.numel() + 1, device="cuda", dtype=x.dtype)
+        shifted = storage[1:].view(shape).copy_(x)
+        actual = layer(shifted)
+        assert torch.equal(actual, layer(x))
+        assert actual.shape == (*shape[:-1], n)
+        assert_output(actual, x.float() @ weight.T)
+
+
+@pytest.mark.parametrize("rows", [1, 2, 4, 8, 16])
+@pytest.mark.parametrize("bits", [6, 7, 8])
+@pytest.mark.parametrize(
+    "k,n", [(2560, 4096), (2560, 1024), (4096, 2560), (2560, 9728), (9728, 2560)]
+)
+def test_qwen3_4b_layer_shapes(k, n, rows, bits):
+    """The decoder-layer shapes at batch 1..16 with every bit split forced."""
+    cpu = synthetic_sage(k, n, seed=100 + bits, permuted=True, direction_bits=bits)
+    layer = SAGELinear(to_cuda(cpu), n)
+    x = torch.randn(rows, k, generator=torch.Generator().manual_seed(7), dtype=torch.float16).cuda()
+    assert_output(layer(x), expected_output(x, cpu, n))
+
+
+def test_one_hot_rows_reproduce_weight_columns():
+    """x = e_j selects column j of the weight: checks the permutation fold and the row
+    mapping element by element (not only in norm)."""
+    k, n = 512, 48
+    cpu = synthetic_sage(k, n, seed=1, permuted=True)
+    layer = SAGELinear(to_cuda(cpu), n)
+    weight = torch.from_numpy(c_oracle.decode_fp16(cpu, n)).cuda()
+    for start in range(0, k, 16):
+        x = torch.zeros(16, k, dtype=torch.float16, device="cuda")
+        x[torch.arange(16), torch.arange(start, start + 16)] = 1.0
+        got = layer(x)  # [16, n]; got[m] ~ weight[:, start+m]
+        want = weight[:, start : start + 16].T.float()
+        assert torch.allclose(got.float(), want, rtol=2e-3, atol=1e-6)
+
+
+def test_full_size_against_gpu_dequant():
+    """At the benchmark's full size: matmul against an FP32 matmul on the kernel-made dense
+    weight (itself pinned bit-exactly by the hash test), plus linearity of the operator."""
+    k, n = 2560, 9728
+    for seed in (0, 1, 2):
+        gpu = to_cuda(synthetic_sage(k, n, seed=seed, permuted=True))
+        layer = SAGELinear(gpu, n)
+        weight = layer.dequantize().float()
+        x = torch.randn(16, k, generator=torch.Generator().manual_seed(seed), dtype=torch.float16).cuda()
+        for rows in (1, 3, 8, 16):
+            assert_output(layer(x[:rows]), x[:rows].float() @ weight.T)
+        a, b = layer(x[:1]).float(), layer(x[1:2]).float()
+        both = layer((x[:1].float() + x[1:2].float()).half()).float()
+        assert ((a + b - both).norm() / both.norm()).item() < 3e-3
+
+
+# ---------------------------------------------------------------- module behaviour
+
+
+@pytest.mark.parametrize("rows,k", [(2, 256), (65, 256), (32, 4096), (1, 2560), (1, 4096), (1, 9728)])
+@pytest.mark.parametrize("seed", [0, 1, 2])
+def test_grids_state_streams_graph_bias_opcheck(rows, k, seed):
+    cpu = synthetic_sage(k, 17, seed=seed)
+    cpu["radius_grid"][..., 1].zero_()
+    cpu["radius_grid"][..., 0].fill_(0.25)
+    cpu["radius_grid"][0, :, 0].zero_()
+    layer = SAGELinear(to_cuda(cpu), 17)
+    restored = SAGELinear({key: torch.zeros_like(value) for key, value in cpu.items()}, 17)
+    missing, unexpected = restored.load_state_dict(layer.state_dict())
+    assert not missing and not unexpected
+    restored.cuda()
+    x = torch.randn(rows, k, device="cuda", dtype=torch.float16)
+    expected = layer(x)
+    assert torch.count_nonzero(expected[:, 0]) == 0
+    assert_output(expected, expected_output(x, cpu, 17))
+    assert torch.equal(restored(x), expected)
+    assert torch.equal(layer(x.T.contiguous().T), expected)
+    stream = torch.cuda.Stream()
+    stream.wait_stream(torch.cuda.current_stream())
+    with torch.cuda.stream(stream):
+        for _ in range(3):
+            layer(x)
+    torch.cuda.current_stream().wait_stream(stream)
+    graph = torch.cuda.CUDAGraph()
+    with torch.cuda.graph(graph):
+        output = layer(x)
+    graph.replay()
+    assert torch.equal(output, expected)
+    graph.replay()
+    assert torch.equal(output, expected)
+    layer.bias = torch.ones(17, device="cuda", dtype=torch.float16)
+    assert torch.equal(layer(x), expected + 1)
+    torch.library.opcheck(
+        sage,
+        (x, layer.packed_codes, layer.radius_codes, layer.radius_grid, layer.codebook, layer.permutation, 17),
+    )
+
+
+def test_dtype_boundary_and_repeatability():
+    cpu = synthetic_sage(2560, 40, seed=0)
+    layer = SAGELinear(to_cuda(cpu), 40)
+    x = torch.randn(3, 2560, device="cuda", dtype=torch.bfloat16)
+    out = layer(x)
+    assert out.dtype == torch.bfloat16
+    reference = expected_output(x.half(), cpu, 40)
+    assert ((out.float() - reference).norm() / reference.norm()).item() < 5e-3
+    first = layer(x.half())
+    for _ in range(20):
+        assert torch.equal(layer(x.half()), first)
+
+
+def test_validation_errors():
+    cpu = synthetic_sage(256, 17, seed=0)
+    gpu = to_cuda(cpu)
+    layer = SAGELinear(gpu, 17)
+    with pytest.raises(RuntimeError, match="contiguous CUDA FP16"):
+        sage(torch.zeros(2, 256, device="cuda"), *[gpu[k] for k in gpu], 17)
+    with pytest.raises(RuntimeError, match="Invalid SAGE packed layout"):
+        sage(torch.zeros(2, 256, device="cuda", dtype=torch.float16), *[gpu[k] for k in gpu], 33)
+    with pytest.raises(RuntimeError, match="divisible by 128"):
+        sage(torch.zeros(2, 200, device="cuda", dtype=torch.float16), *[gpu[k] for k in gpu], 17)
+    bad = dict(gpu)
+    bad["codebook"] = torch.zeros(4, 32, 2, device="cuda", dtype=torch.float16)
+    with pytest.raises(RuntimeError, match="codebook"):
+        sage(torch.zeros(2, 256, device="cuda", dtype=torch.float16), *[bad[k] for k in bad], 17)
+    assert layer(torch.zeros(0, 256, device="cuda", dtype=torch.float16)).shape == (0, 17)
+
+
+# ---------------------------------------------------------------- the C ABI directly
+
+
+def test_c_abi_status_codes_and_host_entry():
+    lib = _lib.load()
+    k, n, rows = 2560, 1024, 4
+    cpu = synthetic_sage(k, n, seed=2)
+    gpu = to_cuda(cpu)
+    entries = cpu["codebook"].shape[1]
+    ptr = lambda t: ctypes.c_void_p(t.data_ptr())  # noqa: E731
+    stream = ctypes.c_void_p(torch.cuda.current_stream().cuda_stream)
+    x = torch.randn(rows, k, dtype=torch.float16)
+    y = torch.empty(rows, n, dtype=torch.float16)
+    staging_bytes = lib.sageb200_host_staging_bytes(rows, n, k)
+    staging = torch.zeros(staging_bytes, dtype=torch.uint8, device="cuda")
+    launches = lib.sageb200_launch_count()
+    for pinned in (False, True):
+        xh = x.pin_memory() if pinned else x
+        yh = y.pin_memory() if pinned else y
+        status = lib.sageb200_linear_host(
+            ctypes.c_void_p(xh.data_ptr()), ptr(gpu["packed_codes"]), ptr(gpu["radius_codes"]),
+            ptr(gpu["radius_grid"]), ptr(gpu["codebook"]), ptr(gpu["permutation"]),
+            ctypes.c_void_p(yh.data_ptr()), ptr(staging), staging_bytes, rows, n, k, entries, stream,
+        )
+        assert status == 0, lib.sageb200_status_string(status)
+        assert_output(yh.cuda(), expected_output(x.cuda(), cpu, n))
+    assert lib.sageb200_launch_count() >= launches + 2
+    # error paths return codes, never raise or launch
+    dev_x = x.cuda()
+    dev_y = torch.empty(rows, n, dtype=torch.float16, device="cuda")
+    common = (ptr(gpu["packed_codes"]), ptr(gpu["radius_codes"]), ptr(gpu["radius_grid"]), ptr(gpu["codebook"]), ptr(gpu["permutation"]))
+    assert lib.sageb200_linear(ptr(dev_x), *common, ptr(dev_y), None, 0, rows, n, 200, entries, stream) == -1
+    assert lib.sageb200_linear(ptr(dev_x), *common, ptr(dev_y), None, 0, rows, n, k, 100, stream) == -1
+    assert lib.sageb200_linear(ptr(dev_x), *common, ptr(dev_y), None, 0, 70000, n, k, entries, stream) == -3
+    assert lib.sageb200_linear(ptr(dev_x), *common, ptr(dev_y), None, 0, rows, n, k, entries, stream) == -4
+    misaligned = ctypes.c_void_p(gpu["radius_grid"].data_ptr() + 2)
+    assert lib.sageb200_linear(
+        ptr(dev_x), common[0], common[1], misaligned, common[3], common[4], ptr(dev_y), None, 0, rows, n, k, entries, stream
+    ) == -2
+    assert lib.sageb200_linear(ptr(dev_x), *common, ptr(dev_y), None, 0, 0, n, k, entries, stream) == 0
+    assert lib.sageb200_gemv_fuses_permutation(n, 16384) == 1
+
+
+def test_grouped_launch_matches_single_launches():
+    """q/k/v-style grouped launch: bit-identical with one launch per linear."""
+    k = 2560
+    shapes = [(4096, 0), (1024, 1), (1024, 2)]
+    for rows in (1, 5, 16):
+        x = torch.randn(rows, k, generator=torch.Generator().manual_seed(rows), dtype=torch.float16).cuda()
+        layers = [SAGELinear(to_cuda(synthetic_sage(k, n, seed=s)), n) for n, s in shapes]
+        singles = [layer(x) for layer in layers]
+        grouped = sage_grouped(
+            [(x, l.packed_codes, l.radius_codes, l.radius_grid, l.codebook, l.permutation) for l in layers],
+            [n for n, _ in shapes],
+        )
+        for one, many in zip(singles, grouped):
+            assert torch.equal(one, many)
+
+
+def test_tuning_knob_sweep_stays_within_tolerance():
+    """Every launch geometry the knob can select gives the same answer within the gate."""
+    lib = _lib.load()
+    k, n = 4096, 2560
+    cpu = synthetic_sage(k, n, seed=1)
+    layer = SAGELinear(to_cuda(cpu), n)
+    try:
+        for rows in (1, 12):
+            x = torch.randn(rows, k, generator=torch.Generator().manual_seed(3), dtype=torch.float16).cuda()
+            want = expected_output(x, cpu, n)
+            for warps, splits, replicas, tiles in [
+                (1, 1, 1, 1), (8, 1, 8, 1), (4, 4, 2, 2), (3, 5, 4, 4), (8, 32, 8, 1), (2, 2, 8, 2), (5, 3, 1, 4),
+            ]:
+                assert lib.sageb200_set_tuning(warps, splits, replicas, tiles) == 0
+                assert_output(layer(x), want)
+    finally:
+        lib.sageb200_set_tuning(0, 0, 0, 0)
+
+
+def test_reference_cuda_kernels_agree_when_built():
+    """If the reference project's own kernels were compiled (oracle/_ref), both
+    implementations must agree within the output gate on the same inputs."""
+    ref = c_oracle.reference_kernels()
+    if ref is None:
+        pytest.skip("oracle/_ref/libsage_ref.so not built on this machine")
+    vp = ctypes.c_void_p
+    stream = vp(torch.cuda.current_stream().cuda_stream)
+    for (k, n, rows, seed) in [(2560, 9728, 1, 0), (4096, 2560, 4, 1), (2560, 1024, 15, 2), (9728, 2560, 1, 0)]:
+        cpu = synthetic_sage(k, n, seed=seed)
+        gpu = to_cuda(cpu)
+        layer = SAGELinear(gpu, n)
+        x = torch.randn(rows, k, generator=torch.Generator().manual_seed(5), dtype=torch.float16).cuda()
+        ours = layer(x)
+        fused = ref.sage_ref_fuses_permutation(n, k)
+        xin = x if fused else x.index_select(-1, gpu["permutation"].long()).contiguous()
+        theirs = torch.empty(rows, n, dtype=torch.float16, device="cuda")
+        status = ref.sage_ref_gemv(
+            vp(xin.data_ptr()), vp(gpu["packed_codes"].data_ptr()), vp(gpu["radius_codes"].data_ptr()),
+            vp(gpu["radius_grid"].data_ptr()), vp(gpu["codebook"].data_ptr()), vp(theirs.data_ptr()),
+            vp(gpu["permutation"].data_ptr()) if fused else None, rows, n, k, cpu["codebook"].shape[1], stream,
+        )
+        assert status == 0
+        torch.cuda.synchronize()
+        want = expected_output(x, cpu, n)
+        assert_output(theirs, want)
+        assert_output(ours, want)
