@@ -61,9 +61,11 @@ int sageb200_gemm_splits(int rows, int n, int k, int sm_count);
 /*
  * Bytes of scratch sageb200_linear needs for this shape: split-K partial sums, their
  * arrival counters and (for rows > 16 with a permutation) the gathered activations.
- * The buffer must be 256-byte aligned and ZERO-FILLED ONCE when it is allocated; every
- * call leaves the counter region zero again, so one buffer can be reused by successive
- * calls on one stream.  Calls that run concurrently must not share a buffer.
+ * Returns 0 when the shape needs none.  The buffer must be 256-byte aligned and
+ * ZERO-FILLED ONCE when it is allocated.  Its first 64 KiB hold the arrival counters and
+ * nothing else; every call leaves them zero again, so one buffer (sized for the largest
+ * shape) can be reused by successive calls of any shapes on one stream.  Calls that may
+ * run concurrently must not share a buffer.
  * Replaces: the workspace sizing at reference csrc/bindings.cpp:63-66.
  */
 size_t sageb200_workspace_bytes(int rows, int n, int k);

@@ -23,7 +23,11 @@ struct DeviceState {
   std::atomic<int> ready{0};
   int sm_count = 0;
   int major = 0;
+  int *status = nullptr;  // pinned, device-mapped word the kernels write on a timed-out wait
 };
+
+// Activation rows from which the tcgen05 prefill GEMM takes over from 16-row skinny passes.
+constexpr int kGemmMinRows = 33;
 DeviceState g_devices[kMaxDevices];
 Tuning g_tuning{0, 0, 0, 0};
 std::atomic<unsigned long long> g_launches{0};
@@ -47,15 +51,24 @@ int device_state(DeviceState **out) {
       return SAGEB200_ERR_CUDA;
     }
     if (major != 10) return SAGEB200_ERR_NO_DEVICE;  // built for sm_100a only
-    if (configure_skinny() != cudaSuccess) {
+    if (configure_skinny() != cudaSuccess || configure_gemm_tc() != cudaSuccess) {
       cudaGetLastError();
       return SAGEB200_ERR_CUDA;
     }
+    // one word of pinned host memory per device, allocated once at set-up
+    if (cudaHostAlloc(reinterpret_cast<void **>(&state.status), sizeof(int), cudaHostAllocMapped) !=
+        cudaSuccess) {
+      cudaGetLastError();
+      return SAGEB200_ERR_CUDA;
+    }
+    *state.status = 0;
     state.sm_count = sms;
     state.major = major;
     state.ready.store(1, std::memory_order_release);
   }
   *out = &state;
+  // a kernel of an earlier call reported a timed-out wait
+  if (*static_cast<volatile int *>(state.status) != 0) return SAGEB200_ERR_TIMEOUT;
   return SAGEB200_OK;
 }
 
@@ -81,13 +94,19 @@ int check_buffers(const void *codes, const void *radii, const void *grid, const 
   return SAGEB200_OK;
 }
 
-// Scratch one problem needs at `rows` <= 16: [counters | partials], both 256-aligned.
+// Scratch layout: a FIXED counter region at the front (arrival counters, zero between
+// launches) followed by split-K partial sums.  The counter region never holds anything
+// else, so one buffer can serve calls of different shapes one after another.
+constexpr size_t kCounterRegionBytes = 64 * 1024;
+constexpr int kCounterCapacity = static_cast<int>(kCounterRegionBytes / sizeof(unsigned));
+
+// Partial-sum bytes one problem needs at `rows` <= 16 (0 when K is not split).
 size_t plan_bytes(const SkinnyPlan &plan) {
-  return plan.splits > 1 ? plan.counter_bytes + align256(plan.partial_bytes) : 0;
+  return plan.splits > 1 ? align256(plan.partial_bytes) : 0;
 }
 
 void fill_problem(SkinnyProblem &out, const sageb200_problem &in, const SkinnyPlan &plan,
-                  unsigned char *scratch, int cta_begin) {
+                  unsigned *counters, unsigned char *partials, int cta_begin) {
   out.x = static_cast<const __half *>(in.x);
   out.codes = static_cast<const uint32_t *>(in.codes);
   out.radii = static_cast<const uint32_t *>(in.radii);
@@ -95,8 +114,8 @@ void fill_problem(SkinnyProblem &out, const sageb200_problem &in, const SkinnyPl
   out.book = static_cast<const uint32_t *>(in.book);
   out.perm = in.perm;
   out.y = static_cast<__half *>(in.y);
-  out.counters = plan.splits > 1 ? reinterpret_cast<unsigned *>(scratch) : nullptr;
-  out.partial = plan.splits > 1 ? reinterpret_cast<float *>(scratch + plan.counter_bytes) : nullptr;
+  out.counters = plan.splits > 1 ? counters : nullptr;
+  out.partial = plan.splits > 1 ? reinterpret_cast<float *>(partials) : nullptr;
   out.rows = in.rows;
   out.n = in.n;
   out.k = in.k;
@@ -120,22 +139,32 @@ int run_skinny(const sageb200_problem *problems, int count, void *workspace,
   Tuning tuning = g_tuning;
   if (count > 1) tuning.tiles_per_cta = 1;  // grouped launches share one kernel variant
   SkinnyPlan launch{};
-  size_t offset = 0;
+  size_t offset = kCounterRegionBytes;
+  int counters_used = 0;
   int ctas = 0;
   int live = 0;
   for (int i = 0; i < count; ++i) {
     const sageb200_problem &in = problems[i];
     if (in.rows == 0) continue;
     plans[live] = plan_skinny(in.rows, in.n, in.k, in.entries, device.sm_count, tuning);
+    if (plans[live].splits > 1 && counters_used + plans[live].tile_blocks > kCounterCapacity) {
+      Tuning unsplit = tuning;  // more tile blocks than counters: plenty of CTAs without a split
+      unsplit.splits = 1;
+      plans[live] = plan_skinny(in.rows, in.n, in.k, in.entries, device.sm_count, unsplit);
+    }
     const SkinnyPlan &plan = plans[live];
     const size_t need = plan_bytes(plan);
     if (need) {
       if (!workspace || offset + need > workspace_bytes) return SAGEB200_ERR_WORKSPACE;
       if (reinterpret_cast<uintptr_t>(workspace) & 255) return SAGEB200_ERR_ALIGNMENT;
     }
-    fill_problem(params.problem[live], in, plan, static_cast<unsigned char *>(workspace) + offset,
-                 ctas);
-    offset += need;
+    fill_problem(params.problem[live], in, plan,
+                 static_cast<unsigned *>(workspace) + counters_used,
+                 static_cast<unsigned char *>(workspace) + offset, ctas);
+    if (need) {
+      offset += need;
+      counters_used += plan.tile_blocks;
+    }
     ctas += plan.tile_blocks * plan.splits;
     if (live == 0) {
       launch = plan;
@@ -208,9 +237,12 @@ int sageb200_gemm_splits(int rows, int n, int k, int sm_count) {
 
 size_t sageb200_workspace_bytes(int rows, int n, int k) {
   if (n <= 0 || k <= 0 || (k % 128) || rows <= 0) return 0;
+  if (rows >= kGemmMinRows)  // counter region (kept for layout uniformity) + gathered activations
+    return kCounterRegionBytes + align256(static_cast<size_t>(rows) * k * 2);
   const int planned_rows = rows > 16 ? 16 : rows;
   const SkinnyPlan plan = plan_skinny(planned_rows, n, k, 256, planning_sm_count(), g_tuning);
   size_t bytes = plan_bytes(plan);
+  if (plan.splits > 1 && plan.tile_blocks > kCounterCapacity) bytes = 0;
   if (rows > 16) {
     // the tail chunk (rows % 16) may plan differently; reserve for both
     const int tail = rows % 16;
@@ -219,7 +251,7 @@ size_t sageb200_workspace_bytes(int rows, int n, int k) {
       if (other > bytes) bytes = other;
     }
   }
-  return bytes;
+  return bytes ? kCounterRegionBytes + bytes : 0;
 }
 
 int sageb200_linear_grouped(const sageb200_problem *problems_host, int count, void *workspace,
@@ -250,7 +282,35 @@ int sageb200_linear(const void *x, const void *codes, const void *radii, const v
   status = device_state(&device);
   if (status) return status;
   cudaStream_t s = static_cast<cudaStream_t>(stream);
-  // Up to 16 rows go through in one pass; more rows run as 16-row passes over the
+  if (rows >= kGemmMinRows) {
+    // Prefill: tcgen05 GEMM over activations in quantised channel order.  The gather (or
+    // a re-alignment copy) lands in the workspace so the TMA loads see contiguous rows.
+    const __half *xq = static_cast<const __half *>(x);
+    if (perm || (reinterpret_cast<uintptr_t>(x) & 15)) {
+      const size_t need = kCounterRegionBytes + align256(static_cast<size_t>(rows) * k * 2);
+      if (!workspace || workspace_bytes < need) return SAGEB200_ERR_WORKSPACE;
+      if (reinterpret_cast<uintptr_t>(workspace) & 255) return SAGEB200_ERR_ALIGNMENT;
+      __half *gathered =
+          reinterpret_cast<__half *>(static_cast<unsigned char *>(workspace) + kCounterRegionBytes);
+      if (launch_gather(xq, perm, gathered, rows, k, s, device->sm_count) != cudaSuccess) {
+        cudaGetLastError();
+        return SAGEB200_ERR_CUDA;
+      }
+      g_launches.fetch_add(1, std::memory_order_relaxed);
+      xq = gathered;
+    }
+    const GemmPlan plan = plan_gemm_tc(rows, n, k, device->sm_count);
+    if (launch_gemm_tc(xq, static_cast<const uint32_t *>(codes), static_cast<const uint32_t *>(radii),
+                       static_cast<const uint32_t *>(grid), static_cast<const uint32_t *>(book),
+                       static_cast<__half *>(y), device->status, rows, n, k, entries, plan,
+                       s) != cudaSuccess) {
+      cudaGetLastError();
+      return SAGEB200_ERR_CUDA;
+    }
+    g_launches.fetch_add(1, std::memory_order_relaxed);
+    return SAGEB200_OK;
+  }
+  // Up to 16 rows go through in one pass; 17..32 rows run as 16-row passes over the
   // packed weights (each pass reuses the scratch, in stream order).
   for (int begin = 0; begin < rows; begin += 16) {
     sageb200_problem chunk = problem;

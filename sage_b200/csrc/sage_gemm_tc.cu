@@ -1,0 +1,494 @@
+// SAGE packed prefill GEMM for more than 16 activation rows: dequantise weight tiles
+// into shared memory, feed tcgen05 FP16 MMAs with FP32 accumulators in tensor memory.
+//
+// Replaces the reference's sage_gemm_kernel_base / _m64 (csrc/sage/sage_gemm_cuda.cu:35-197,
+// 272-445: 32x64 / 64x64 tiles on nvcuda::wmma, every activation tile re-decoding the
+// whole weight) and its separate split-K reduce kernel (:199-206).
+//
+// Orientation ("swap AB"): the MMA's M dimension is 128 OUTPUT rows (eight packed 16-row
+// tiles), its N dimension is up to 256 activation rows (tokens), so any token count that
+// is a multiple of 16 maps onto one instruction shape without padding waste:
+//     D[128 outputs][TN tokens] += Wtile[128][64] . Xq[TN][64]^T      per 64-channel stage
+// Both operands are K-major in shared memory with the 128-byte swizzle:
+//   A (weights)      written by 8 decode warps with 16-byte stores, bit-exact
+//                    w = fp16_rn(float(+-dir) * fmaf(code, step, min))
+//                    (reference csrc/sage/sage_gemm_cuda.cu:117-131)
+//   B (activations)  one TMA tile load per stage from the activations in quantised
+//                    channel order (no cluster multicast)
+// One elected thread issues tcgen05.mma (cta_group::1, kind::f16, M=128, N=TN, K=16, four per
+// stage) and releases stages with tcgen05.commit; the decode warps then read the
+// accumulator with tcgen05.ld and store FP16 outputs.
+//
+// Every wait is bounded: a wait that exceeds its time limit sets an abort flag in shared
+// memory (all later waits return at once), records SAGEB200_ERR_TIMEOUT in the status word
+// and the CTA still frees its tensor memory before returning.
+#include <cuda.h>
+
+#include "sage_common.cuh"
+#include "sage_kernels.h"
+
+namespace sageb200 {
+namespace {
+
+constexpr int kDecodeWarps = 8;
+constexpr int kDecodeThreads = kDecodeWarps * 32;
+constexpr int kTmaWarp = kDecodeWarps;
+constexpr int kMmaWarp = kDecodeWarps + 1;
+constexpr int kGemmThreads = (kDecodeWarps + 2) * 32;
+constexpr int kTileRows = 128;             // output rows per CTA = MMA M
+constexpr int kStageK = 64;                // channels per stage = one 128-byte swizzle row
+constexpr int kAStageBytes = kTileRows * kStageK * 2;
+constexpr int kMaxStages = 6;
+constexpr unsigned long long kWaitLimitNs = 2000000000ull;  // 2 s per wait
+
+struct GemmParams {
+  const uint32_t *codes;
+  const uint32_t *radii;
+  const uint32_t *grid;
+  const uint32_t *book;
+  __half *y;
+  int *status;          // device-visible status word (0 = ok)
+  int rows, n, k, groups, tiles;
+  int entries, dbits;
+  int tokens_per_cta;   // TN: multiple of 16, 16..256
+  int stages;
+  int tmem_columns;     // power of two >= max(32, TN)
+};
+
+// ---------------------------------------------------------------- PTX wrappers
+
+__device__ __forceinline__ void mbarrier_init(uint32_t bar, uint32_t count) {
+  asm volatile("mbarrier.init.shared::cta.b64 [%0], %1;" ::"r"(bar), "r"(count));
+}
+__device__ __forceinline__ void mbarrier_arrive(uint32_t bar) {
+  asm volatile("mbarrier.arrive.shared::cta.b64 _, [%0];" ::"r"(bar) : "memory");
+}
+__device__ __forceinline__ void mbarrier_arrive_expect_tx(uint32_t bar, uint32_t bytes) {
+  asm volatile("mbarrier.arrive.expect_tx.shared::cta.b64 _, [%0], %1;" ::"r"(bar), "r"(bytes)
+               : "memory");
+}
+__device__ __forceinline__ bool mbarrier_test(uint32_t bar, uint32_t parity) {
+  uint32_t done;
+  asm volatile(
+      "{\n .reg .pred p;\n mbarrier.test_wait.parity.shared::cta.b64 p, [%1], %2;\n"
+      " selp.u32 %0, 1, 0, p;\n}"
+      : "=r"(done)
+      : "r"(bar), "r"(parity)
+      : "memory");
+  return done != 0;
+}
+__device__ __forceinline__ unsigned long long global_timer() {
+  unsigned long long t;
+  asm volatile("mov.u64 %0, %globaltimer;" : "=l"(t));
+  return t;
+}
+
+// Bounded wait.  Returns false (and raises the CTA's abort flag) when the limit passes.
+__device__ __forceinline__ bool bounded_wait(uint32_t bar, uint32_t parity, volatile int *abort_flag,
+                                             int *status) {
+  if (mbarrier_test(bar, parity)) return true;
+  const unsigned long long begin = global_timer();
+  unsigned spins = 0;
+  while (true) {
+    if (mbarrier_test(bar, parity)) return true;
+    if (*abort_flag) return false;
+    if ((++spins & 63u) == 0) {
+      __nanosleep(64);
+      if (global_timer() - begin > kWaitLimitNs) {
+        *abort_flag = 1;
+        atomicExch(status, -7);  // SAGEB200_ERR_TIMEOUT
+        return false;
+      }
+    }
+  }
+}
+
+__device__ __forceinline__ void fence_proxy_async_shared() {
+  asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
+}
+__device__ __forceinline__ void tcgen05_fence_after() {
+  asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+}
+__device__ __forceinline__ void tcgen05_fence_before() {
+  asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
+}
+
+__device__ __forceinline__ void tma_load_2d(uint32_t dst, const CUtensorMap *map, int x, int y,
+                                            uint32_t bar) {
+  asm volatile(
+      "cp.async.bulk.tensor.2d.shared::cluster.global.mbarrier::complete_tx::bytes"
+      " [%0], [%1, {%2, %3}], [%4];" ::"r"(dst),
+      "l"(reinterpret_cast<uint64_t>(map)), "r"(x), "r"(y), "r"(bar)
+      : "memory");
+}
+
+// Shared-memory matrix descriptor: K-major, 128-byte swizzle, 8-row groups 1024 bytes apart.
+__device__ __forceinline__ uint64_t smem_descriptor(uint32_t address) {
+  uint64_t desc = 0;
+  desc |= static_cast<uint64_t>((address & 0x3ffffu) >> 4);  // start address
+  desc |= static_cast<uint64_t>(1) << 16;                    // leading byte offset (unused here)
+  desc |= static_cast<uint64_t>(1024 >> 4) << 32;            // stride byte offset
+  desc |= static_cast<uint64_t>(1) << 46;                    // descriptor version (sm_100)
+  desc |= static_cast<uint64_t>(2) << 61;                    // layout: 128-byte swizzle
+  return desc;
+}
+
+// kind::f16 instruction descriptor: FP16 A and B (both K-major), FP32 accumulator.
+__device__ __forceinline__ uint32_t instruction_descriptor(int m, int n) {
+  uint32_t d = 0;
+  d |= 1u << 4;                                  // D format FP32
+  d |= static_cast<uint32_t>(n >> 3) << 17;      // N
+  d |= static_cast<uint32_t>(m >> 4) << 24;      // M
+  return d;
+}
+
+__device__ __forceinline__ void umma_f16(uint32_t tmem_d, uint64_t a_desc, uint64_t b_desc,
+                                         uint32_t idesc, uint32_t accumulate) {
+  asm volatile(
+      "{\n .reg .pred p;\n setp.ne.b32 p, %4, 0;\n"
+      " tcgen05.mma.cta_group::1.kind::f16 [%0], %1, %2, %3, p;\n}" ::"r"(tmem_d),
+      "l"(a_desc), "l"(b_desc), "r"(idesc), "r"(accumulate)
+      : "memory");
+}
+__device__ __forceinline__ void umma_commit(uint32_t bar) {
+  asm volatile("tcgen05.commit.cta_group::1.mbarrier::arrive::one.shared::cluster.b64 [%0];" ::"r"(bar)
+               : "memory");
+}
+
+__device__ __forceinline__ void tmem_load_16(uint32_t taddr, uint32_t (&r)[16]) {
+  asm volatile(
+      "tcgen05.ld.sync.aligned.32x32b.x16.b32 "
+      "{%0,%1,%2,%3,%4,%5,%6,%7,%8,%9,%10,%11,%12,%13,%14,%15}, [%16];"
+      : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]), "=r"(r[4]), "=r"(r[5]), "=r"(r[6]),
+        "=r"(r[7]), "=r"(r[8]), "=r"(r[9]), "=r"(r[10]), "=r"(r[11]), "=r"(r[12]), "=r"(r[13]),
+        "=r"(r[14]), "=r"(r[15])
+      : "r"(taddr));
+}
+__device__ __forceinline__ void tmem_load_wait() {
+  asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory");
+}
+
+// ---------------------------------------------------------------- the kernel
+
+// Dynamic shared memory, 1024-byte aligned by hand:
+//   [A stages: stages x 16 KiB][B stages: stages x TN*128][codebook 4 KiB][barriers]
+__global__ void __launch_bounds__(kGemmThreads, 1)
+    sage_gemm_tc_kernel(const GemmParams p, const __grid_constant__ CUtensorMap x_map) {
+  extern __shared__ unsigned char raw_shared[];
+  __shared__ uint32_t tmem_base_holder;
+  __shared__ int abort_flag;
+
+  const uint32_t raw = smem_address(raw_shared);
+  const uint32_t base = (raw + 1023u) & ~1023u;
+  unsigned char *aligned = raw_shared + (base - raw);
+  const int tn = p.tokens_per_cta;
+  const int b_stage_bytes = tn * kStageK * 2;
+  const uint32_t a_base = base;
+  const uint32_t b_base = a_base + p.stages * kAStageBytes;
+  const uint32_t book_address = b_base + p.stages * b_stage_bytes;
+  uint4 *book_shared = reinterpret_cast<uint4 *>(aligned + (book_address - base));
+  const uint32_t bar_base = book_address + 256 * 16;
+  // barriers: full[stages], empty[stages], accumulator
+  auto full_bar = [&](int s) { return bar_base + 8u * s; };
+  auto empty_bar = [&](int s) { return bar_base + 8u * (kMaxStages + s); };
+  const uint32_t accum_bar = bar_base + 8u * (2 * kMaxStages);
+
+  const int tid = threadIdx.x;
+  const int warp = tid >> 5;
+  const int lane = tid & 31;
+  const int row_block = blockIdx.x;   // 128 output rows
+  const int token_block = blockIdx.y; // TN tokens
+  const int stages_k = p.k / kStageK;
+
+  if (tid == 0) {
+    abort_flag = 0;
+    for (int s = 0; s < p.stages; ++s) {
+      mbarrier_init(full_bar(s), kDecodeThreads + 1);
+      mbarrier_init(empty_bar(s), 1);
+    }
+    mbarrier_init(accum_bar, 1);
+    asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
+  }
+  if (warp == kTmaWarp) {
+    asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(
+                     smem_address(&tmem_base_holder)),
+                 "r"(static_cast<uint32_t>(p.tmem_columns))
+                 : "memory");
+    asm volatile("tcgen05.relinquish_alloc_permit.cta_group::1.sync.aligned;" ::: "memory");
+  }
+  // codebook, interleaved: entry e = 16 bytes (dims 0..7)
+  for (int e = tid; e < p.entries; e += kGemmThreads) {
+    uint4 entry;
+    entry.x = p.book[e];
+    entry.y = p.book[p.entries + e];
+    entry.z = p.book[2 * p.entries + e];
+    entry.w = p.book[3 * p.entries + e];
+    book_shared[e] = entry;
+  }
+  tcgen05_fence_before();
+  __syncthreads();
+  tcgen05_fence_after();
+  const uint32_t tmem_base = tmem_base_holder;
+  volatile int *abort_ptr = &abort_flag;
+
+  if (warp < kDecodeWarps) {
+    // ---------------- weight decode producers: thread = (row 0..127, half 0..1)
+    const int row = tid >> 1;
+    const int half_id = tid & 1;
+    const int out_row = row_block * kTileRows + row;
+    const int tile = out_row >> 4;
+    const bool row_valid = tile < p.tiles;  // rows past the last packed tile decode to zero
+    const size_t cell_base = (static_cast<size_t>(row_valid ? tile : 0) * p.groups) * 16 + (out_row & 15);
+    const uint32_t row_offset = static_cast<uint32_t>(row >> 3) * 1024u + static_cast<uint32_t>(row & 7) * 128u;
+    const uint32_t index_mask = static_cast<uint32_t>(p.entries - 1);
+    uint2 words[2] = {make_uint2(0, 0), make_uint2(0, 0)};
+    uint32_t radius_word = 0;
+    float minimum = 0.0f, step = 0.0f;
+    bool alive = true;
+    for (int ks = 0; ks < stages_k && alive; ++ks) {
+      const int s = ks % p.stages;
+      const uint32_t phase = static_cast<uint32_t>(ks / p.stages) & 1u;
+      if ((ks & 1) == 0 && row_valid) {
+        // one 128-channel group feeds two stages: this thread's words for both halves
+        const size_t cell = cell_base + static_cast<size_t>(ks >> 1) * 16;
+        words[0] = ldg_stream_u2(p.codes + cell * 8 + 2 * half_id);
+        words[1] = ldg_stream_u2(p.codes + cell * 8 + 4 + 2 * half_id);
+        radius_word = ldg_stream_u1(p.radii + cell);
+        const uint32_t endpoints = ldg_stream_u1(p.grid + cell);
+        const float2 e = __half22float2(*reinterpret_cast<const __half2 *>(&endpoints));
+        minimum = e.x;
+        step = e.y;
+      }
+      alive = bounded_wait(empty_bar(s), phase ^ 1u, abort_ptr, p.status);
+      if (!alive) break;
+      const uint2 w = words[ks & 1];
+      const uint32_t stage_address = a_base + s * kAStageBytes + row_offset;
+#pragma unroll
+      for (int j = 0; j < 4; ++j) {
+        const uint32_t word = (j < 2) ? w.x : w.y;
+        const uint32_t code = (word >> (16 * (j & 1))) & 0xffffu;
+        const int chunk = half_id * 4 + j;                 // 16-byte chunk within the 128-byte row
+        const int vector = (ks & 1) * 8 + chunk;           // vector index within the group
+        uint32_t out[4] = {0, 0, 0, 0};
+        if (row_valid) {
+          const uint4 dir = book_shared[(code >> 8) & index_mask];
+          const uint32_t rc = (code >> (8 + p.dbits)) |
+                              (((radius_word >> (2 * vector)) & 3u) << (8 - p.dbits));
+          const float radius = fmaf(static_cast<float>(rc), step, minimum);
+          const uint32_t planes[4] = {dir.x, dir.y, dir.z, dir.w};
+#pragma unroll
+          for (int q = 0; q < 4; ++q) {
+            uint32_t bits = planes[q];
+            bits ^= (((code >> (2 * q)) & 1u) << 15) | (((code >> (2 * q + 1)) & 1u) << 31);
+            const float2 d = __half22float2(*reinterpret_cast<const __half2 *>(&bits));
+            const __half2 v = __floats2half2_rn(d.x * radius, d.y * radius);
+            out[q] = *reinterpret_cast<const uint32_t *>(&v);
+          }
+        }
+        const uint32_t swizzled = static_cast<uint32_t>(chunk ^ (row & 7)) * 16u;
+        sts_u4(stage_address + swizzled, make_uint4(out[0], out[1], out[2], out[3]));
+      }
+      fence_proxy_async_shared();
+      mbarrier_arrive(full_bar(s));
+    }
+    // ---------------- epilogue: TMEM -> registers -> FP16 global
+    if (alive) alive = bounded_wait(accum_bar, 0, abort_ptr, p.status);
+    alive = __all_sync(0xffffffffu, alive);  // tcgen05.ld is warp-collective
+    tcgen05_fence_after();
+    if (alive) {
+      const int quarter = warp & 3;                 // TMEM lanes 32*quarter .. +31
+      const int column_half = warp >> 2;            // warps 0-3: first half of the tokens
+      const int columns_per_half = (tn / 16 + 1) / 2 * 16;
+      const int column_begin = column_half * columns_per_half;
+      const int column_end = min(tn, column_begin + columns_per_half);
+      const int out = row_block * kTileRows + quarter * 32 + lane;
+      for (int c = column_begin; c < column_end; c += 16) {
+        uint32_t r[16];
+        tmem_load_16(tmem_base + (static_cast<uint32_t>(quarter * 32) << 16) + c, r);
+        tmem_load_wait();
+        if (out < p.n) {
+#pragma unroll
+          for (int i = 0; i < 16; ++i) {
+            const int token = token_block * tn + c + i;
+            if (token < p.rows)
+              p.y[static_cast<size_t>(token) * p.n + out] = __float2half_rn(__uint_as_float(r[i]));
+          }
+        }
+      }
+    }
+  } else if (warp == kTmaWarp) {
+    // ---------------- activation tile loads
+    if (lane == 0) {
+      bool alive = true;
+      for (int ks = 0; ks < stages_k && alive; ++ks) {
+        const int s = ks % p.stages;
+        const uint32_t phase = static_cast<uint32_t>(ks / p.stages) & 1u;
+        alive = bounded_wait(empty_bar(s), phase ^ 1u, abort_ptr, p.status);
+        if (!alive) break;
+        mbarrier_arrive_expect_tx(full_bar(s), static_cast<uint32_t>(b_stage_bytes));
+        tma_load_2d(b_base + s * b_stage_bytes, &x_map, ks * kStageK, token_block * tn, full_bar(s));
+      }
+    }
+  } else {
+    // ---------------- MMA issue
+    if (lane == 0) {
+      const uint32_t idesc = instruction_descriptor(kTileRows, tn);
+      bool alive = true;
+      for (int ks = 0; ks < stages_k && alive; ++ks) {
+        const int s = ks % p.stages;
+        const uint32_t phase = static_cast<uint32_t>(ks / p.stages) & 1u;
+        alive = bounded_wait(full_bar(s), phase, abort_ptr, p.status);
+        if (!alive) break;
+        tcgen05_fence_after();
+        const uint64_t a_desc = smem_descriptor(a_base + s * kAStageBytes);
+        const uint64_t b_desc = smem_descriptor(b_base + s * b_stage_bytes);
+#pragma unroll
+        for (int j = 0; j < kStageK / 16; ++j) {
+          // advancing 16 channels = 32 bytes = 2 units of the descriptor's address field
+          umma_f16(tmem_base, a_desc + 2 * j, b_desc + 2 * j, idesc, (ks > 0 || j > 0) ? 1u : 0u);
+        }
+        umma_commit(empty_bar(s));
+      }
+      if (alive) umma_commit(accum_bar);
+    }
+  }
+
+  // Let in-flight TMA copies land before the CTA's shared memory goes away: every issued
+  // load targets a full barrier that the MMA thread has waited on unless we aborted; on
+  // abort, wait (bounded) for each stage's barrier once more.
+  tcgen05_fence_before();
+  __syncthreads();
+  if (warp == kTmaWarp) {
+    if (abort_flag && lane == 0) {
+      const unsigned long long begin = global_timer();
+      while (global_timer() - begin < 2000000ull) __nanosleep(1000);  // 2 ms grace for copies in flight
+    }
+    __syncwarp();
+    asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(tmem_base),
+                 "r"(static_cast<uint32_t>(p.tmem_columns))
+                 : "memory");
+  }
+}
+
+// x_q[m][j] = x[m][perm[j]]  (or a plain copy when perm is null): 2-byte loads, 16-byte stores.
+__global__ void __launch_bounds__(256) sage_gather_kernel(const __half *__restrict__ x,
+                                                          const int32_t *__restrict__ perm,
+                                                          __half *__restrict__ xq, int rows, int k) {
+  const int vectors = k >> 3;
+  const long long total = static_cast<long long>(rows) * vectors;
+  for (long long item = static_cast<long long>(blockIdx.x) * 256 + threadIdx.x; item < total;
+       item += static_cast<long long>(gridDim.x) * 256) {
+    const int m = static_cast<int>(item / vectors);
+    const int v = static_cast<int>(item - static_cast<long long>(m) * vectors);
+    const __half *source = x + static_cast<size_t>(m) * k;
+    __align__(16) __half values[8];
+#pragma unroll
+    for (int d = 0; d < 8; ++d) {
+      const int j = v * 8 + d;
+      values[d] = source[perm ? perm[j] : j];
+    }
+    *reinterpret_cast<uint4 *>(xq + static_cast<size_t>(m) * k + static_cast<size_t>(v) * 8) =
+        *reinterpret_cast<const uint4 *>(values);
+  }
+}
+
+typedef CUresult (*EncodeTiledFn)(CUtensorMap *, CUtensorMapDataType, cuuint32_t, void *,
+                                  const cuuint64_t *, const cuuint64_t *, const cuuint32_t *,
+                                  const cuuint32_t *, CUtensorMapInterleave, CUtensorMapSwizzle,
+                                  CUtensorMapL2promotion, CUtensorMapFloatOOBfill);
+
+EncodeTiledFn encode_tiled() {
+  static EncodeTiledFn fn = nullptr;
+  if (!fn) {
+    void *symbol = nullptr;
+    cudaDriverEntryPointQueryResult query;
+    if (cudaGetDriverEntryPoint("cuTensorMapEncodeTiled", &symbol, cudaEnableDefault, &query) ==
+            cudaSuccess &&
+        query == cudaDriverEntryPointSuccess)
+      fn = reinterpret_cast<EncodeTiledFn>(symbol);
+  }
+  return fn;
+}
+
+}  // namespace
+
+cudaError_t launch_gather(const __half *x, const int32_t *perm, __half *xq, int rows, int k,
+                          cudaStream_t stream, int sm_count) {
+  const long long total = static_cast<long long>(rows) * (k >> 3);
+  long long blocks = (total + 255) / 256;
+  if (blocks > static_cast<long long>(sm_count) * 8) blocks = static_cast<long long>(sm_count) * 8;
+  if (blocks < 1) blocks = 1;
+  sage_gather_kernel<<<static_cast<unsigned>(blocks), 256, 0, stream>>>(x, perm, xq, rows, k);
+  return cudaGetLastError();
+}
+
+GemmPlan plan_gemm_tc(int rows, int n, int k, int sm_count) {
+  (void)k;
+  GemmPlan plan{};
+  int tn = (rows + 15) / 16 * 16;
+  if (tn > 256) {
+    // split the tokens evenly into blocks of at most 256
+    const int blocks = (rows + 255) / 256;
+    tn = ((rows + blocks - 1) / blocks + 15) / 16 * 16;
+  }
+  plan.tokens_per_cta = tn;
+  plan.token_blocks = (rows + tn - 1) / tn;
+  plan.row_blocks = (n + kTileRows - 1) / kTileRows;
+  const int stage_bytes = kAStageBytes + tn * kStageK * 2;
+  int stages = (200 * 1024) / stage_bytes;
+  if (stages > kMaxStages) stages = kMaxStages;
+  if (stages < 2) stages = 2;
+  plan.stages = stages;
+  int columns = 32;
+  while (columns < tn) columns *= 2;
+  plan.tmem_columns = columns;
+  plan.shared_bytes = static_cast<size_t>(stages) * stage_bytes + 256 * 16 + (2 * kMaxStages + 1) * 8 + 1024;
+  (void)sm_count;
+  return plan;
+}
+
+cudaError_t configure_gemm_tc() {
+  return cudaFuncSetAttribute(sage_gemm_tc_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize,
+                              220 * 1024);
+}
+
+// xq: activations in quantised channel order, 16-byte aligned, [rows][k].
+cudaError_t launch_gemm_tc(const __half *xq, const uint32_t *codes, const uint32_t *radii,
+                           const uint32_t *grid, const uint32_t *book, __half *y, int *status,
+                           int rows, int n, int k, int entries, const GemmPlan &plan,
+                           cudaStream_t stream) {
+  EncodeTiledFn encode = encode_tiled();
+  if (!encode) return cudaErrorNotSupported;
+  CUtensorMap map;
+  const cuuint64_t dims[2] = {static_cast<cuuint64_t>(k), static_cast<cuuint64_t>(rows)};
+  const cuuint64_t strides[1] = {static_cast<cuuint64_t>(k) * 2};
+  const cuuint32_t box[2] = {kStageK, static_cast<cuuint32_t>(plan.tokens_per_cta)};
+  const cuuint32_t element_strides[2] = {1, 1};
+  const CUresult encoded = encode(
+      &map, CU_TENSOR_MAP_DATA_TYPE_FLOAT16, 2, const_cast<__half *>(xq), dims, strides, box,
+      element_strides, CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B,
+      CU_TENSOR_MAP_L2_PROMOTION_L2_256B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+  if (encoded != CUDA_SUCCESS) return cudaErrorInvalidValue;
+  GemmParams p{};
+  p.codes = codes;
+  p.radii = radii;
+  p.grid = grid;
+  p.book = book;
+  p.y = y;
+  p.status = status;
+  p.rows = rows;
+  p.n = n;
+  p.k = k;
+  p.groups = k / 128;
+  p.tiles = (n + 15) / 16;
+  p.entries = entries;
+  p.dbits = direction_bits_of(entries);
+  p.tokens_per_cta = plan.tokens_per_cta;
+  p.stages = plan.stages;
+  p.tmem_columns = plan.tmem_columns;
+  const dim3 blocks(plan.row_blocks, plan.token_blocks);
+  sage_gemm_tc_kernel<<<blocks, kGemmThreads, plan.shared_bytes, stream>>>(p, map);
+  return cudaGetLastError();
+}
+
+}  // namespace sageb200

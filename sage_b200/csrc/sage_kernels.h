@@ -33,7 +33,6 @@ struct SkinnyParams {
   SkinnyProblem problem[kMaxGrouped];
   int count;
   int replica_log2;     // codebook replicas in shared memory = 1 << replica_log2
-  int book_bytes;       // shared bytes reserved for the (largest) replicated codebook
   int x_bytes;          // shared bytes reserved for staged activations
 };
 
@@ -67,6 +66,25 @@ cudaError_t launch_skinny(SkinnyParams &params, const SkinnyPlan &plan, int tota
 cudaError_t launch_dequant(const uint32_t *codes, const uint32_t *radii, const uint32_t *grid,
                            const uint32_t *book, const int32_t *perm, __half *w, int n, int k,
                            int entries, cudaStream_t stream, int sm_count);
+
+// Launch plan of the tcgen05 prefill GEMM (host side).
+struct GemmPlan {
+  int tokens_per_cta;   // MMA N: multiple of 16, at most 256
+  int token_blocks;
+  int row_blocks;       // blocks of 128 output rows
+  int stages;
+  int tmem_columns;
+  size_t shared_bytes;
+};
+
+GemmPlan plan_gemm_tc(int rows, int n, int k, int sm_count);
+cudaError_t configure_gemm_tc();
+// xq: activations already in quantised channel order, 16-byte aligned.  `status` is a
+// device-visible word that receives SAGEB200_ERR_TIMEOUT if a bounded wait runs out.
+cudaError_t launch_gemm_tc(const __half *xq, const uint32_t *codes, const uint32_t *radii,
+                           const uint32_t *grid, const uint32_t *book, __half *y, int *status,
+                           int rows, int n, int k, int entries, const GemmPlan &plan,
+                           cudaStream_t stream);
 
 // x_q[m][j] = x[m][perm[j]] for the prefill path.
 cudaError_t launch_gather(const __half *x, const int32_t *perm, __half *xq, int rows, int k,

@@ -72,7 +72,8 @@ struct FieldConsts {
 
 template <int NB>
 __device__ __forceinline__ void compute_unit(const UnitRegs &r, float (&acc)[NB][4],
-                                             const FieldConsts &f, uint32_t book_lane_address,
+                                             const FieldConsts &f, uint32_t book_base,
+                                             uint32_t lane_offset,
                                              const uint32_t (&x_address)[NB], int t) {
   float step16[2], base[2];
   uint32_t high[2];
@@ -91,15 +92,17 @@ __device__ __forceinline__ void compute_unit(const UnitRegs &r, float (&acc)[NB]
       const uint32_t word = (s < 2) ? r.code[h].x : r.code[h].y;
       uint32_t address, signs, radius_bits;
       if (s & 1) {
-        address = ((word >> f.shift_hi) & f.index_mask) | book_lane_address;
+        address = ((word >> f.shift_hi) & f.index_mask) | lane_offset;
         signs = (word >> 16) & 0xffu;
         radius_bits = (word >> f.lo_right) & f.lo_mask;
       } else {
-        address = ((word >> f.shift_lo) & f.index_mask) | book_lane_address;
+        address = ((word >> f.shift_lo) & f.index_mask) | lane_offset;
         signs = word & 0xffu;
         radius_bits = (word << f.lo_left) & f.lo_mask;
       }
-      const uint4 dir = lds_u4(address);
+      // entry offset and replica offset never overlap, so OR; the base is a link-time
+      // constant of the static array and folds into the load's immediate
+      const uint4 dir = lds_u4(book_base + address);
       radius_bits |= ((high[h] >> (2 * s)) & f.hi_mask) | 0x3f800000u;
       const float radius = fmaf(__uint_as_float(radius_bits), step16[h], base[h]);
       const __half2 rr = __floats2half2_rn(radius, radius);
@@ -124,10 +127,15 @@ __device__ __forceinline__ void compute_unit(const UnitRegs &r, float (&acc)[NB]
   }
 }
 
-// Shared memory map (dynamic): [codebook replicas | staged x | warp partials].
+// The replicated codebook lives in STATIC shared memory (32 KiB: 256 entries x 8
+// replicas x 16 bytes) so that its base address is a compile-time immediate.
+constexpr int kBookBytes = 256 * 8 * 16;
+
+// Shared memory map (dynamic): [staged x | warp partials].
 template <int NB, int TB>
 __global__ void __launch_bounds__(256) sage_skinny_kernel(const __grid_constant__ SkinnyParams params) {
   extern __shared__ __align__(16) unsigned char shared[];
+  __shared__ __align__(128) unsigned char book_shared[kBookBytes];
   __shared__ int last_flag;
 
   int pi = 0;
@@ -166,9 +174,8 @@ __global__ void __launch_bounds__(256) sage_skinny_kernel(const __grid_constant_
 
   const int replica_log2 = params.replica_log2;
   const int line_log2 = 4 + replica_log2;
-  unsigned char *book_shared = shared;
-  __half *x_shared = reinterpret_cast<__half *>(shared + params.book_bytes);
-  float *partial_shared = reinterpret_cast<float *>(shared + params.book_bytes + params.x_bytes);
+  __half *x_shared = reinterpret_cast<__half *>(shared);
+  float *partial_shared = reinterpret_cast<float *>(shared + params.x_bytes);
 
   // Codebook: entry e, replica j at byte (e << line_log2) + 16*j, dims 0..7 contiguous.
   for (int e = tid; e < p.entries; e += threads) {
@@ -206,8 +213,8 @@ __global__ void __launch_bounds__(256) sage_skinny_kernel(const __grid_constant_
   f.lo_mask = ((1u << (8 - p.dbits)) - 1u) << 19;
   f.lo_left = 11 - p.dbits;
   f.lo_right = 5 + p.dbits;
-  const uint32_t book_lane_address =
-      smem_address(book_shared) + 16u * static_cast<uint32_t>(lane & ((1 << replica_log2) - 1));
+  const uint32_t book_base = smem_address(book_shared);
+  const uint32_t lane_offset = 16u * static_cast<uint32_t>(lane & ((1 << replica_log2) - 1));
   uint32_t x_row_address[NB];
 #pragma unroll
   for (int nb = 0; nb < NB; ++nb) {
@@ -247,7 +254,7 @@ __global__ void __launch_bounds__(256) sage_skinny_kernel(const __grid_constant_
       uint32_t x_address[NB];
 #pragma unroll
       for (int nb = 0; nb < NB; ++nb) x_address[nb] = x_row_address[nb] + 256u * gi;
-      compute_unit<NB>(current, acc, f, book_lane_address, x_address, t);
+      compute_unit<NB>(current, acc, f, book_base, lane_offset, x_address, t);
 
       if (!more || next_ti != ti) flush(ti);
       if (!more) break;
@@ -302,7 +309,7 @@ __global__ void __launch_bounds__(256) sage_skinny_kernel(const __grid_constant_
   if (tid == 0) p.counters[tile_block] = 0u;
 }
 
-constexpr int kMaxDynamicShared = 200 * 1024;
+constexpr int kMaxDynamicShared = 160 * 1024;
 
 template <int NB, int TB>
 cudaError_t launch_variant(const SkinnyParams &params, int ctas, int threads, size_t shared_bytes,
@@ -361,7 +368,7 @@ SkinnyPlan plan_skinny(int rows, int n, int k, int entries, int sm_count, const 
   if (plan.splits > 1) {
     plan.partial_bytes = static_cast<size_t>(plan.tile_blocks) * plan.splits * plan.tiles_per_cta *
                          plan.column_blocks * 128 * sizeof(float);
-    plan.counter_bytes = (static_cast<size_t>(plan.tile_blocks) * sizeof(unsigned) + 255) / 256 * 256;
+    plan.counter_bytes = static_cast<size_t>(plan.tile_blocks) * sizeof(unsigned);
   }
   return plan;
 }
@@ -388,11 +395,11 @@ cudaError_t launch_skinny(SkinnyParams &params, const SkinnyPlan &plan, int tota
     const size_t need = static_cast<size_t>(p.rows) * (p.groups_per_split * 256 + 64);
     if (need > x_bytes) x_bytes = need;
   }
-  params.book_bytes = max_entries * (16 << replica_log2);
+  (void)max_entries;
   params.x_bytes = static_cast<int>((x_bytes + 15) / 16 * 16);
   const size_t partial_bytes =
       static_cast<size_t>(plan.warps) * plan.tiles_per_cta * plan.column_blocks * 128 * sizeof(float);
-  const size_t shared_bytes = params.book_bytes + params.x_bytes + partial_bytes;
+  const size_t shared_bytes = params.x_bytes + partial_bytes;
   if (shared_bytes > static_cast<size_t>(kMaxDynamicShared)) return cudaErrorInvalidConfiguration;
   const int threads = plan.warps * 32;
 #define SAGEB200_LAUNCH(NB, TB) \
