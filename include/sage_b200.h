@@ -28,7 +28,7 @@ extern "C" {
 
 #define SAGEB200_OK 0
 #define SAGEB200_ERR_INVALID_ARGUMENT (-1) /* null pointer, bad shape, bad entries      */
-#define SAGEB200_ERR_ALIGNMENT (-2)        /* grid/book/codes/radii not 4-byte aligned   */
+#define SAGEB200_ERR_ALIGNMENT (-2)        /* book not 4-byte, codes/radii/grid not 16-byte aligned */
 #define SAGEB200_ERR_RANGE (-3)            /* rows > 65535 or a dimension overflows int  */
 #define SAGEB200_ERR_WORKSPACE (-4)        /* workspace missing or too small             */
 #define SAGEB200_ERR_CUDA (-5)             /* a CUDA call or launch failed               */
@@ -51,16 +51,17 @@ const char *sageb200_status_string(int status);
 int sageb200_gemv_fuses_permutation(int n, int k);
 
 /*
- * Number of K splits the matmul will use for this shape on a device with `sm_count`
- * SMs (informational; the workspace size already accounts for it).
+ * Number of K slices the decode kernel will use for this shape on a device with
+ * `sm_count` SMs (informational; the workspace size already accounts for it).
  * Replaces: int sage_gemm_splits(int rows, int n, int k, int sm_count)
  *           (reference csrc/sage/sage_gemv_cuda.h:21, csrc/sage/sage_gemm_cuda.cu:209-214,493-495).
  */
 int sageb200_gemm_splits(int rows, int n, int k, int sm_count);
 
 /*
- * Bytes of scratch sageb200_linear needs for this shape: split-K partial sums, their
- * arrival counters and (for rows > 16 with a permutation) the gathered activations.
+ * Bytes of scratch sageb200_linear needs for this shape: partial sums of output tiles
+ * that are shared between CTAs, their arrival counters and (for more than one row with a
+ * permutation) the gathered activations.
  * Returns 0 when the shape needs none.  The buffer must be 256-byte aligned and
  * ZERO-FILLED ONCE when it is allocated.  Its first 64 KiB hold the arrival counters and
  * nothing else; every call leaves them zero again, so one buffer (sized for the largest
@@ -138,13 +139,13 @@ int sageb200_linear_host(const void *x_host, const void *codes, const void *radi
                          int entries, void *stream);
 
 /*
- * Tuning knob for sweeps (debug): warps per CTA, K splits, codebook replicas and
- * tiles per CTA of the skinny kernel; 0 restores the built-in heuristic for a field.
- * Not thread safe, like its counterpart.
+ * Tuning knob for sweeps (debug): warps per CTA (<= 16), K slices (<= 8) and CTAs per SM
+ * of the decode kernel; 0 restores the built-in heuristic for a field; `reserved` must
+ * be 0.  Not thread safe, like its counterpart.
  * Replaces: _set_sage_tuning / sage_gemv_tuning (reference csrc/bindings.cpp:81-84,
  *           csrc/sage/sage_gemv_cuda.cu:3-4).
  */
-int sageb200_set_tuning(int warps, int splits, int replicas, int tiles_per_cta);
+int sageb200_set_tuning(int warps, int slices, int ctas_per_sm, int reserved);
 
 /* Number of kernels this library has launched in this process (all entry points). */
 unsigned long long sageb200_launch_count(void);

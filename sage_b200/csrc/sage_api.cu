@@ -88,8 +88,10 @@ int check_shape(int rows, int n, int k, int entries) {
 
 int check_buffers(const void *codes, const void *radii, const void *grid, const void *book) {
   if (!codes || !radii || !grid || !book) return SAGEB200_ERR_INVALID_ARGUMENT;
-  if ((reinterpret_cast<uintptr_t>(grid) & 3) || (reinterpret_cast<uintptr_t>(book) & 3) ||
-      (reinterpret_cast<uintptr_t>(radii) & 3) || (reinterpret_cast<uintptr_t>(codes) & 7))
+  // grid and codebook: 4 bytes as in the reference; codes/radii (and grid, for the bulk
+  // copies of the decode kernel) additionally 16 bytes, which any allocator provides
+  if ((reinterpret_cast<uintptr_t>(grid) & 15) || (reinterpret_cast<uintptr_t>(book) & 3) ||
+      (reinterpret_cast<uintptr_t>(radii) & 15) || (reinterpret_cast<uintptr_t>(codes) & 15))
     return SAGEB200_ERR_ALIGNMENT;
   return SAGEB200_OK;
 }
@@ -100,83 +102,83 @@ int check_buffers(const void *codes, const void *radii, const void *grid, const 
 constexpr size_t kCounterRegionBytes = 64 * 1024;
 constexpr int kCounterCapacity = static_cast<int>(kCounterRegionBytes / sizeof(unsigned));
 
-// Partial-sum bytes one problem needs at `rows` <= 16 (0 when K is not split).
-size_t plan_bytes(const SkinnyPlan &plan) {
-  return plan.splits > 1 ? align256(plan.partial_bytes) : 0;
+// Scratch one problem needs at `rows` <= 16: partial pieces, then (rows > 1 with a
+// permutation) the gathered activations.
+size_t gather_bytes(int rows, int k, bool permuted) {
+  return rows > 1 && permuted ? align256(static_cast<size_t>(rows) * k * 2) : 0;
 }
+size_t plan_bytes(const SkinnyPlan &plan) { return align256(plan.partial_bytes); }
 
-void fill_problem(SkinnyProblem &out, const sageb200_problem &in, const SkinnyPlan &plan,
-                  unsigned *counters, unsigned char *partials, int cta_begin) {
-  out.x = static_cast<const __half *>(in.x);
-  out.codes = static_cast<const uint32_t *>(in.codes);
-  out.radii = static_cast<const uint32_t *>(in.radii);
-  out.grid = static_cast<const uint32_t *>(in.grid);
-  out.book = static_cast<const uint32_t *>(in.book);
-  out.perm = in.perm;
-  out.y = static_cast<__half *>(in.y);
-  out.counters = plan.splits > 1 ? counters : nullptr;
-  out.partial = plan.splits > 1 ? reinterpret_cast<float *>(partials) : nullptr;
-  out.rows = in.rows;
-  out.n = in.n;
-  out.k = in.k;
-  out.groups = in.k / 128;
-  out.tiles = (in.n + 15) / 16;
-  out.entries = in.entries;
-  out.dbits = direction_bits_of(in.entries);
-  out.splits = plan.splits;
-  out.groups_per_split = plan.groups_per_split;
-  out.warps = plan.warps;
-  out.tile_blocks = plan.tile_blocks;
-  out.cta_begin = cta_begin;
-}
-
-// rows <= 16, one or more problems, one launch.
+// rows <= 16, one or more problems, one launch (plus one small gather launch for each
+// problem that has several rows and a permutation).
 int run_skinny(const sageb200_problem *problems, int count, void *workspace,
                size_t workspace_bytes, cudaStream_t stream, const DeviceState &device) {
   SkinnyParams params;
   std::memset(&params, 0, sizeof(params));
-  SkinnyPlan plans[kMaxGrouped];
-  Tuning tuning = g_tuning;
-  if (count > 1) tuning.tiles_per_cta = 1;  // grouped launches share one kernel variant
-  SkinnyPlan launch{};
+  params.status = device.status;
+  unsigned char *scratch = static_cast<unsigned char *>(workspace);
   size_t offset = kCounterRegionBytes;
   int counters_used = 0;
   int ctas = 0;
   int live = 0;
+  int warps = 0, column_blocks = 1;
   for (int i = 0; i < count; ++i) {
     const sageb200_problem &in = problems[i];
     if (in.rows == 0) continue;
-    plans[live] = plan_skinny(in.rows, in.n, in.k, in.entries, device.sm_count, tuning);
-    if (plans[live].splits > 1 && counters_used + plans[live].tile_blocks > kCounterCapacity) {
-      Tuning unsplit = tuning;  // more tile blocks than counters: plenty of CTAs without a split
-      unsplit.splits = 1;
-      plans[live] = plan_skinny(in.rows, in.n, in.k, in.entries, device.sm_count, unsplit);
-    }
-    const SkinnyPlan &plan = plans[live];
-    const size_t need = plan_bytes(plan);
-    if (need) {
-      if (!workspace || offset + need > workspace_bytes) return SAGEB200_ERR_WORKSPACE;
+    const SkinnyPlan plan = plan_skinny(in.rows, in.n, in.k, in.entries, device.sm_count, g_tuning);
+    const size_t partial = plan_bytes(plan);
+    const size_t gathered = gather_bytes(in.rows, in.k, in.perm != nullptr);
+    if (partial || gathered) {
+      if (!workspace || offset + partial + gathered > workspace_bytes) return SAGEB200_ERR_WORKSPACE;
       if (reinterpret_cast<uintptr_t>(workspace) & 255) return SAGEB200_ERR_ALIGNMENT;
     }
-    fill_problem(params.problem[live], in, plan,
-                 static_cast<unsigned *>(workspace) + counters_used,
-                 static_cast<unsigned char *>(workspace) + offset, ctas);
-    if (need) {
-      offset += need;
-      counters_used += plan.tile_blocks;
+    if (plan.needs_scratch && counters_used + plan.tiles > kCounterCapacity) return SAGEB200_ERR_RANGE;
+    SkinnyProblem &out = params.problem[live];
+    out.x = static_cast<const __half *>(in.x);
+    out.perm = in.perm;
+    if (gathered) {
+      // several activation rows: gather once here instead of once per CTA
+      __half *xq = reinterpret_cast<__half *>(scratch + offset + partial);
+      if (launch_gather(out.x, in.perm, xq, in.rows, in.k, stream, device.sm_count) != cudaSuccess) {
+        cudaGetLastError();
+        return SAGEB200_ERR_CUDA;
+      }
+      g_launches.fetch_add(1, std::memory_order_relaxed);
+      out.x = xq;
+      out.perm = nullptr;
     }
-    ctas += plan.tile_blocks * plan.splits;
-    if (live == 0) {
-      launch = plan;
-    } else {
-      if (plan.warps > launch.warps) launch.warps = plan.warps;
-      if (plan.column_blocks > launch.column_blocks) launch.column_blocks = plan.column_blocks;
-    }
+    out.codes = static_cast<const uint32_t *>(in.codes);
+    out.radii = static_cast<const uint32_t *>(in.radii);
+    out.grid = static_cast<const uint32_t *>(in.grid);
+    out.book = static_cast<const uint32_t *>(in.book);
+    out.y = static_cast<__half *>(in.y);
+    out.partial = plan.needs_scratch ? reinterpret_cast<float *>(scratch + offset) : nullptr;
+    out.counters = plan.needs_scratch ? static_cast<unsigned *>(workspace) + counters_used : nullptr;
+    out.rows = in.rows;
+    out.n = in.n;
+    out.k = in.k;
+    out.groups = in.k / 128;
+    out.tiles = plan.tiles;
+    out.entries = in.entries;
+    out.dbits = direction_bits_of(in.entries);
+    out.slices = plan.slices;
+    out.ctas_per_slice = plan.ctas_per_slice;
+    out.slots_per_tile = plan.slots_per_tile;
+    out.cta_begin = ctas;
+    ctas += plan.ctas;
+    offset += partial + gathered;
+    if (plan.needs_scratch) counters_used += plan.tiles;
+    if (static_cast<int>(plan.x_bytes) > params.x_bytes) params.x_bytes = static_cast<int>(plan.x_bytes);
+    if (plan.unit_capacity > params.unit_capacity) params.unit_capacity = plan.unit_capacity;
+    if (plan.warp_segments > params.warp_segments) params.warp_segments = plan.warp_segments;
+    if (static_cast<int>(plan.lin_bytes) > params.lin_bytes) params.lin_bytes = static_cast<int>(plan.lin_bytes);
+    if (plan.warps > warps) warps = plan.warps;
+    if (plan.column_blocks > column_blocks) column_blocks = plan.column_blocks;
     ++live;
   }
   if (live == 0) return SAGEB200_OK;
   params.count = live;
-  if (launch_skinny(params, launch, ctas, stream) != cudaSuccess) {
+  if (launch_skinny(params, warps, column_blocks, ctas, stream) != cudaSuccess) {
     cudaGetLastError();
     return SAGEB200_ERR_CUDA;
   }
@@ -232,24 +234,21 @@ int sageb200_gemv_fuses_permutation(int n, int k) {
 int sageb200_gemm_splits(int rows, int n, int k, int sm_count) {
   if (n <= 0 || k <= 0 || (k % 128) || rows <= 0) return 1;
   const int planned_rows = rows > 16 ? 16 : rows;
-  return plan_skinny(planned_rows, n, k, 256, sm_count > 0 ? sm_count : 148, g_tuning).splits;
+  return plan_skinny(planned_rows, n, k, 256, sm_count > 0 ? sm_count : 148, g_tuning).slices;
 }
 
 size_t sageb200_workspace_bytes(int rows, int n, int k) {
   if (n <= 0 || k <= 0 || (k % 128) || rows <= 0) return 0;
   if (rows >= kGemmMinRows)  // counter region (kept for layout uniformity) + gathered activations
     return kCounterRegionBytes + align256(static_cast<size_t>(rows) * k * 2);
-  const int planned_rows = rows > 16 ? 16 : rows;
-  const SkinnyPlan plan = plan_skinny(planned_rows, n, k, 256, planning_sm_count(), g_tuning);
-  size_t bytes = plan_bytes(plan);
-  if (plan.splits > 1 && plan.tile_blocks > kCounterCapacity) bytes = 0;
-  if (rows > 16) {
-    // the tail chunk (rows % 16) may plan differently; reserve for both
-    const int tail = rows % 16;
-    if (tail) {
-      const size_t other = plan_bytes(plan_skinny(tail, n, k, 256, planning_sm_count(), g_tuning));
-      if (other > bytes) bytes = other;
-    }
+  const int sms = planning_sm_count();
+  size_t bytes = 0;
+  // rows > 16 run as 16-row passes plus a tail pass; reserve for the larger of the two
+  const int passes[2] = {rows > 16 ? 16 : rows, rows > 16 ? rows % 16 : 0};
+  for (int pass : passes) {
+    if (pass == 0) continue;
+    const size_t need = plan_bytes(plan_skinny(pass, n, k, 256, sms, g_tuning)) + gather_bytes(pass, k, true);
+    if (need > bytes) bytes = need;
   }
   return bytes ? kCounterRegionBytes + bytes : 0;
 }
@@ -384,12 +383,11 @@ int sageb200_linear_host(const void *x_host, const void *codes, const void *radi
   return SAGEB200_OK;
 }
 
-int sageb200_set_tuning(int warps, int splits, int replicas, int tiles_per_cta) {
-  if (warps < 0 || warps > 8 || splits < 0 || tiles_per_cta < 0 || tiles_per_cta > 4)
+int sageb200_set_tuning(int warps, int slices, int ctas_per_sm, int reserved) {
+  if (warps < 0 || warps > 16 || slices < 0 || slices > 8 || ctas_per_sm < 0 || ctas_per_sm > 8 ||
+      reserved != 0)
     return SAGEB200_ERR_INVALID_ARGUMENT;
-  if (replicas != 0 && replicas != 1 && replicas != 2 && replicas != 4 && replicas != 8)
-    return SAGEB200_ERR_INVALID_ARGUMENT;
-  g_tuning = Tuning{warps, splits, replicas, tiles_per_cta};
+  g_tuning = Tuning{warps, slices, ctas_per_sm, 0};
   return SAGEB200_OK;
 }
 

@@ -19,38 +19,47 @@ struct SkinnyProblem {
   const uint32_t *book;
   const int32_t *perm;
   __half *y;
-  float *partial;       // [tile_blocks][splits][tiles_per_cta][column_blocks*128] when splits > 1
-  unsigned *counters;   // [tile_blocks], zero before and after every launch
+  float *partial;       // [tiles][slots_per_tile][16*rows] pieces of tiles shared between CTAs
+  unsigned *counters;   // [tiles] arrivals, zero before and after every launch
   int rows, n, k, groups, tiles;
   int entries, dbits;
-  int splits, groups_per_split;
-  int warps;            // warps of the CTA that take units (<= launched warps)
-  int tile_blocks;
+  int slices;           // K slices
+  int ctas_per_slice;   // CTAs that divide one slice's units evenly
+  int slots_per_tile;
   int cta_begin;        // first CTA of this problem in the grid
 };
 
 struct SkinnyParams {
   SkinnyProblem problem[kMaxGrouped];
   int count;
-  int replica_log2;     // codebook replicas in shared memory = 1 << replica_log2
   int x_bytes;          // shared bytes reserved for staged activations
+  int unit_capacity;    // most units any CTA holds (640 shared bytes each)
+  int warp_segments;    // most tiles any warp touches
+  int lin_bytes;        // shared bytes for activations in original order (0: none)
+  int *status;          // device-visible status word, may be null
 };
 
 // Launch plan for one problem (host side).
 struct SkinnyPlan {
   int warps;
-  int splits;
-  int groups_per_split;
-  int replicas;
-  int tiles_per_cta;
-  int tile_blocks;
+  int ctas_per_sm;
+  int slices;
+  int ctas_per_slice;
+  int ctas;
+  int unit_capacity;
+  int warp_segments;
+  int slots_per_tile;
   int column_blocks;    // 1 for rows <= 8, 2 for rows <= 16
+  int tiles;
+  bool needs_scratch;
+  size_t x_bytes;
+  size_t lin_bytes;
+  size_t shared_bytes;
   size_t partial_bytes;
-  size_t counter_bytes;
 };
 
 struct Tuning {
-  int warps, splits, replicas, tiles_per_cta;
+  int warps, slices, ctas_per_sm, reserved;
 };
 
 SkinnyPlan plan_skinny(int rows, int n, int k, int entries, int sm_count, const Tuning &tuning);
@@ -58,9 +67,8 @@ SkinnyPlan plan_skinny(int rows, int n, int k, int entries, int sm_count, const 
 // Opts every skinny-kernel variant into large dynamic shared memory on the CURRENT device.
 cudaError_t configure_skinny();
 
-// Launches `count` problems (all planned with the same warps/replicas/tiles_per_cta/
-// column_blocks) as one grid.  Returns the launch error.
-cudaError_t launch_skinny(SkinnyParams &params, const SkinnyPlan &plan, int total_ctas,
+// Launches the problems in `params` as one grid of `total_ctas` CTAs of `warps` warps.
+cudaError_t launch_skinny(const SkinnyParams &params, int warps, int column_blocks, int total_ctas,
                           cudaStream_t stream);
 
 cudaError_t launch_dequant(const uint32_t *codes, const uint32_t *radii, const uint32_t *grid,

@@ -7,11 +7,16 @@
 // 16) activation rows are the B operand, so weights are read and decoded once for any
 // row count and the FP16 products accumulate in FP32 inside the tensor core.
 //
-// Work split: CTA = (block of TB consecutive 16-row tiles) x (one of S splits of K).
-// The CTA's (tile, 128-channel group) units are dealt round-robin to its warps.  Warp
-// partials are combined through shared memory in a fixed order; with S > 1 the CTA's
-// partial goes to global scratch and the last CTA to arrive for that tile block (an
-// arrival counter, no spinning) adds the S partials in split order, so results do not
+// Work split ("stream-K"): the unit of work is (16-row tile, 128-channel group).  K may be
+// cut into a few slices so that the activations of one slice fit in shared memory; inside
+// a slice the units, in (tile, group) order, are divided EVENLY over the slice's CTAs, so
+// every CTA gets the same amount of packed data whatever the tile count.  A CTA's range
+// is contiguous in memory: each warp fetches its share with a handful of TMA bulk copies
+// (cp.async.bulk, 16-byte aligned, completion on an mbarrier) issued before anything
+// else, so the HBM stream is in flight while the CTA stages its codebook and activations.
+// Tiles that straddle CTAs are finished without spinning: every CTA that holds a piece
+// writes its partial sums to scratch and bumps the tile's arrival counter; whichever CTA
+// arrives last adds the pieces in a fixed (slice, position) order, so results do not
 // depend on scheduling.
 //
 // Per lane (g = lane / 4, t = lane % 4) and per unit: rows g and g+8 of the tile, code
@@ -28,115 +33,61 @@
 // bit-exact weight contract; this kernel is checked against an FP32 matmul.)
 #include "sage_common.cuh"
 #include "sage_kernels.h"
+#include "sage_skinny_core.cuh"
 
 namespace sageb200 {
 namespace {
 
-struct UnitRegs {
-  uint2 code[2];
-  uint32_t radius[2];
-  uint32_t grid[2];
-};
+constexpr int kBookBytes = 256 * 8 * 16;  // 256 entries x 8 replicas x 16 bytes, static
+constexpr unsigned long long kWaitLimitNs = 2000000000ull;
+constexpr int kMaxWarps = 16;
+constexpr int kMaxCtaTiles = 64;
+constexpr int kMaxSlices = 8;
+constexpr int kUnitBytes = 640;           // 512 codes + 64 radius words + 64 grid
+constexpr int kMaxDynamicShared = 184 * 1024;  // plus ~37 KiB static stays under the 227 KiB limit
 
-__device__ __forceinline__ void load_unit(UnitRegs &r, const SkinnyProblem &p, int tile,
-                                          int group, int g, int t) {
-  const size_t cell = (static_cast<size_t>(tile) * p.groups + group) * 16 + g;
-  r.code[0] = ldg_stream_u2(p.codes + cell * 8 + 2 * t);
-  r.code[1] = ldg_stream_u2(p.codes + (cell + 8) * 8 + 2 * t);
-  r.radius[0] = ldg_stream_u1(p.radii + cell);
-  r.radius[1] = ldg_stream_u1(p.radii + cell + 8);
-  r.grid[0] = ldg_stream_u1(p.grid + cell);
-  r.grid[1] = ldg_stream_u1(p.grid + cell + 8);
-}
-
-__device__ __forceinline__ void mma_16816(float (&c)[4], uint32_t a0, uint32_t a1, uint32_t a2,
-                                          uint32_t a3, uint32_t b0, uint32_t b1) {
+__device__ __forceinline__ void bulk_copy(uint32_t dst, const void *src, uint32_t bytes,
+                                          uint32_t bar) {
   asm volatile(
-      "mma.sync.aligned.m16n8k16.row.col.f32.f16.f16.f32 "
-      "{%0,%1,%2,%3}, {%4,%5,%6,%7}, {%8,%9}, {%0,%1,%2,%3};"
-      : "+f"(c[0]), "+f"(c[1]), "+f"(c[2]), "+f"(c[3])
-      : "r"(a0), "r"(a1), "r"(a2), "r"(a3), "r"(b0), "r"(b1));
+      "cp.async.bulk.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1], %2, [%3];" ::"r"(dst),
+      "l"(src), "r"(bytes), "r"(bar)
+      : "memory");
+}
+__device__ __forceinline__ bool barrier_done(uint32_t bar, uint32_t parity) {
+  uint32_t done;
+  asm volatile(
+      "{\n .reg .pred p;\n mbarrier.test_wait.parity.shared::cta.b64 p, [%1], %2;\n"
+      " selp.u32 %0, 1, 0, p;\n}"
+      : "=r"(done)
+      : "r"(bar), "r"(parity)
+      : "memory");
+  return done != 0;
+}
+__device__ __forceinline__ unsigned long long global_timer() {
+  unsigned long long t;
+  asm volatile("mov.u64 %0, %globaltimer;" : "=l"(t));
+  return t;
 }
 
-// Bit-field constants that depend on the direction-bit count D, hoisted per problem.
-struct FieldConsts {
-  uint32_t index_mask;   // (entries-1) << L, L = 4 + replica_log2
-  uint32_t shift_lo;     // 8 - L: moves the low code's index to bit L
-  uint32_t shift_hi;     // 24 - L: same for the high code
-  uint32_t hi_mask;      // 3 << (27 - D): the two high radius bits at mantissa position
-  uint32_t hi_shift;     // 27 - D
-  uint32_t lo_mask;      // ((1 << (8-D)) - 1) << 19: the low radius bits at mantissa position
-  uint32_t lo_left;      // 11 - D: low code's radius bits -> bit 19
-  uint32_t lo_right;     // 5 + D: high code's radius bits -> bit 19
-};
+// CTA that owns unit u when U units are divided evenly over J CTAs (CTA j owns
+// [j*U/J, (j+1)*U/J)).
+__device__ __forceinline__ int owner_of(long long u, long long U, int J) {
+  return static_cast<int>(((u + 1) * J - 1) / U);
+}
 
+// Dynamic shared memory: [x | codes | radii | grid | warp partials | x in original order].
 template <int NB>
-__device__ __forceinline__ void compute_unit(const UnitRegs &r, float (&acc)[NB][4],
-                                             const FieldConsts &f, uint32_t book_base,
-                                             uint32_t lane_offset,
-                                             const uint32_t (&x_address)[NB], int t) {
-  float step16[2], base[2];
-  uint32_t high[2];
-#pragma unroll
-  for (int h = 0; h < 2; ++h) {
-    const float2 e = __half22float2(*reinterpret_cast<const __half2 *>(&r.grid[h]));
-    step16[h] = e.y * 16.0f;
-    base[h] = fmaf(-16.0f, e.y, e.x);
-    high[h] = (r.radius[h] >> (8 * t)) << f.hi_shift;
-  }
-#pragma unroll
-  for (int s = 0; s < 4; ++s) {
-    uint32_t a[2][4];
-#pragma unroll
-    for (int h = 0; h < 2; ++h) {
-      const uint32_t word = (s < 2) ? r.code[h].x : r.code[h].y;
-      uint32_t address, signs, radius_bits;
-      if (s & 1) {
-        address = ((word >> f.shift_hi) & f.index_mask) | lane_offset;
-        signs = (word >> 16) & 0xffu;
-        radius_bits = (word >> f.lo_right) & f.lo_mask;
-      } else {
-        address = ((word >> f.shift_lo) & f.index_mask) | lane_offset;
-        signs = word & 0xffu;
-        radius_bits = (word << f.lo_left) & f.lo_mask;
-      }
-      // entry offset and replica offset never overlap, so OR; the base is a link-time
-      // constant of the static array and folds into the load's immediate
-      const uint4 dir = lds_u4(book_base + address);
-      radius_bits |= ((high[h] >> (2 * s)) & f.hi_mask) | 0x3f800000u;
-      const float radius = fmaf(__uint_as_float(radius_bits), step16[h], base[h]);
-      const __half2 rr = __floats2half2_rn(radius, radius);
-      // sign bit 2p -> bit 15 and sign bit 2p+1 -> bit 31 of half2 word p
-      const uint32_t spread = signs * 0x8001u;
-      const uint32_t d[4] = {dir.x ^ ((spread << 15) & 0x80008000u),
-                             dir.y ^ ((spread << 13) & 0x80008000u),
-                             dir.z ^ ((spread << 11) & 0x80008000u),
-                             dir.w ^ ((spread << 9) & 0x80008000u)};
-#pragma unroll
-      for (int p = 0; p < 4; ++p) {
-        const __half2 w = __hmul2(*reinterpret_cast<const __half2 *>(&d[p]), rr);
-        a[h][p] = *reinterpret_cast<const uint32_t *>(&w);
-      }
-    }
-#pragma unroll
-    for (int nb = 0; nb < NB; ++nb) {
-      const uint4 b = lds_u4(x_address[nb] + s * 64);
-      mma_16816(acc[nb], a[0][0], a[1][0], a[0][1], a[1][1], b.x, b.y);
-      mma_16816(acc[nb], a[0][2], a[1][2], a[0][3], a[1][3], b.z, b.w);
-    }
-  }
-}
-
-// The replicated codebook lives in STATIC shared memory (32 KiB: 256 entries x 8
-// replicas x 16 bytes) so that its base address is a compile-time immediate.
-constexpr int kBookBytes = 256 * 8 * 16;
-
-// Shared memory map (dynamic): [staged x | warp partials].
-template <int NB, int TB>
-__global__ void __launch_bounds__(256) sage_skinny_kernel(const __grid_constant__ SkinnyParams params) {
-  extern __shared__ __align__(16) unsigned char shared[];
+__global__ void __launch_bounds__(512, 1) sage_skinny_kernel(const __grid_constant__ SkinnyParams params) {
+  extern __shared__ __align__(128) unsigned char shared[];
   __shared__ __align__(128) unsigned char book_shared[kBookBytes];
-  __shared__ int last_flag;
+  __shared__ uint4 book_stage[256];  // codebook, one interleaved entry each, before replication
+  __shared__ __align__(8) unsigned long long barriers[kMaxWarps];
+  __shared__ int warp_first_tile[kMaxWarps];
+  __shared__ int warp_tile_count[kMaxWarps];
+  __shared__ int tile_parts[kMaxCtaTiles];  // CTAs contributing to the tile, all slices
+  __shared__ int tile_slot[kMaxCtaTiles];   // this CTA's position among them (slice-major)
+  __shared__ int tile_last[kMaxCtaTiles];   // this CTA arrived last
+  __shared__ int any_split;
 
   int pi = 0;
   while (pi + 1 < params.count && static_cast<int>(blockIdx.x) >= params.problem[pi + 1].cta_begin)
@@ -146,272 +97,447 @@ __global__ void __launch_bounds__(256) sage_skinny_kernel(const __grid_constant_
   const int tid = threadIdx.x;
   const int threads = blockDim.x;
   const int warp = tid >> 5;
-  const int launched_warps = threads >> 5;
-  const int warps = p.warps;  // warps that take units; a grouped launch may carry more
+  const int warps = threads >> 5;
   const int lane = tid & 31;
   const int g = lane >> 2;
   const int t = lane & 3;
 
   const int local = static_cast<int>(blockIdx.x) - p.cta_begin;
-  const int split = local % p.splits;
-  const int tile_block = local / p.splits;
-  const int group_begin = split * p.groups_per_split;
-  const int group_count = min(p.groups_per_split, p.groups - group_begin);
-  const int tile_begin = tile_block * TB;
-  const int tile_count = min(TB, p.tiles - tile_begin);
-  const int units = tile_count * group_count;
+  const int S = p.slices;
+  const int J = p.ctas_per_slice;
+  if (local >= S * J) return;  // spare CTA of a grouped launch
+  const int slice = local % S;
+  const int j = local / S;
+  const int group_begin = static_cast<int>(static_cast<long long>(p.groups) * slice / S);
+  const int group_count =
+      static_cast<int>(static_cast<long long>(p.groups) * (slice + 1) / S) - group_begin;
+  const long long U = static_cast<long long>(p.tiles) * group_count;
+  const int unit_begin = static_cast<int>(U * j / J);
+  const int unit_end = static_cast<int>(U * (j + 1) / J);
+  const int unit_count = unit_end - unit_begin;
 
-  // First unit of this warp: start its loads before anything else.
-  int unit = warp;
-  int ti = 0, gi = warp;
-  while (gi >= group_count && ti < tile_count) {
-    gi -= group_count;
-    ++ti;
-  }
-  UnitRegs current;
-  const bool has_work = warp < warps && unit < units;
-  if (has_work) load_unit(current, p, tile_begin + ti, group_begin + gi, g, t);
-
-  const int replica_log2 = params.replica_log2;
-  const int line_log2 = 4 + replica_log2;
   __half *x_shared = reinterpret_cast<__half *>(shared);
-  float *partial_shared = reinterpret_cast<float *>(shared + params.x_bytes);
+  unsigned char *codes_shared = shared + params.x_bytes;
+  unsigned char *radii_shared = codes_shared + static_cast<size_t>(params.unit_capacity) * 512;
+  unsigned char *grid_shared = radii_shared + static_cast<size_t>(params.unit_capacity) * 64;
+  float *partial_shared =
+      reinterpret_cast<float *>(grid_shared + static_cast<size_t>(params.unit_capacity) * 64);
+  __half *x_linear = reinterpret_cast<__half *>(
+      reinterpret_cast<unsigned char *>(partial_shared) +
+      static_cast<size_t>(warps) * params.warp_segments * NB * 512);
 
-  // Codebook: entry e, replica j at byte (e << line_log2) + 16*j, dims 0..7 contiguous.
+  // This warp's contiguous share of the CTA's units.
+  const int warp_begin =
+      unit_begin + static_cast<int>(static_cast<long long>(unit_count) * warp / warps);
+  const int warp_end =
+      unit_begin + static_cast<int>(static_cast<long long>(unit_count) * (warp + 1) / warps);
+  const uint32_t bar = smem_address(&barriers[warp]);
+
+  // ---- 1. start the weight stream: lane 0 of each warp copies the warp's units
+  if (lane == 0) {
+    asm volatile("mbarrier.init.shared::cta.b64 [%0], 1;" ::"r"(bar));
+    asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
+    if (warp_end > warp_begin) {
+      const uint32_t total = static_cast<uint32_t>(warp_end - warp_begin) * kUnitBytes;
+      asm volatile("mbarrier.arrive.expect_tx.shared::cta.b64 _, [%0], %1;" ::"r"(bar), "r"(total)
+                   : "memory");
+      int u = warp_begin;
+      while (u < warp_end) {
+        // a run of units inside one tile is contiguous in all three arrays; with a single
+        // K slice consecutive tiles are contiguous too
+        const int tile = u / group_count;
+        const int gi = u - tile * group_count;
+        const int run =
+            (group_count == p.groups) ? (warp_end - u) : min(warp_end - u, group_count - gi);
+        const size_t cell = (static_cast<size_t>(tile) * p.groups + group_begin + gi) * 16;
+        const uint32_t slot = static_cast<uint32_t>(u - unit_begin);
+        bulk_copy(smem_address(codes_shared) + slot * 512u, p.codes + cell * 8, run * 512u, bar);
+        bulk_copy(smem_address(radii_shared) + slot * 64u, p.radii + cell, run * 64u, bar);
+        bulk_copy(smem_address(grid_shared) + slot * 64u, p.grid + cell, run * 64u, bar);
+        u += run;
+      }
+    } else {
+      asm volatile("mbarrier.arrive.shared::cta.b64 _, [%0];" ::"r"(bar) : "memory");
+    }
+  }
+
+  // ---- 2. codebook, first half: one interleaved 16-byte entry per thread into a staging
+  //         copy (the eight replicas are written after the barrier below)
   for (int e = tid; e < p.entries; e += threads) {
     uint4 entry;
-    entry.x = p.book[e];
-    entry.y = p.book[p.entries + e];
-    entry.z = p.book[2 * p.entries + e];
-    entry.w = p.book[3 * p.entries + e];
-    const uint32_t base = smem_address(book_shared) + (static_cast<uint32_t>(e) << line_log2);
-    for (int j = 0; j < (1 << replica_log2); ++j) sts_u4(base + 16 * j, entry);
+    entry.x = __ldg(p.book + e);
+    entry.y = __ldg(p.book + p.entries + e);
+    entry.z = __ldg(p.book + 2 * p.entries + e);
+    entry.w = __ldg(p.book + 3 * p.entries + e);
+    book_stage[e] = entry;
   }
 
-  // Activations of this K range, gathered through the permutation and laid out so that
-  // lane (g,t), step s finds vector 4t+s of its row at [group][s][t][8 halves].
+  // ---- 3. activations of this K slice, laid out so that lane (g,t), step s finds vector
+  //         4t+s of its row at [group][s][t][8 halves]; rows are 64 bytes apart modulo 128.
+  //         Three ways in, all with their global loads issued back to back (no load waits
+  //         on another load):
+  //           a. no permutation, 16-byte aligned x: straight 16-byte copies
+  //           b. permutation and the rows fit the linear buffer: copy x linearly into
+  //              shared memory while the permutation indices load into registers, then
+  //              gather from shared memory after the barrier
+  //           c. otherwise: gather from global memory, four channels per item
   const int span = group_count * 128;
-  const int row_stride = span + 32;  // halves; +64 bytes staggers rows across banks
-  for (int i = tid; i < span; i += threads) {
-    const int j = group_begin * 128 + i;
-    const int source = p.perm ? p.perm[j] : j;
-    const int vector = (i >> 3) & 15;
-    const int target = (i & ~127) + (vector & 3) * 32 + (vector >> 2) * 8 + (i & 7);
-    for (int m = 0; m < p.rows; ++m)
-      x_shared[m * row_stride + target] = p.x[static_cast<size_t>(m) * p.k + source];
+  const int row_stride = span + 32;  // halves
+  const bool aligned_x = (reinterpret_cast<uintptr_t>(p.x) & 15) == 0;
+  const bool perm_aligned = (reinterpret_cast<uintptr_t>(p.perm) & 15) == 0;
+  const bool linear_gather = p.perm != nullptr && perm_aligned &&
+                             static_cast<size_t>(p.rows) * p.k * 2 <= static_cast<size_t>(params.lin_bytes);
+  constexpr int kItemBatch = 8;  // permutation items (4 channels each) a thread keeps in registers
+  int4 held[kItemBatch];
+  const int items = span >> 2;
+  if (p.perm == nullptr && aligned_x) {
+    const int vectors = span >> 3;
+    for (int i = tid; i < vectors * p.rows; i += threads) {
+      const int m = i / vectors;
+      const int v = i - m * vectors;  // vector index inside the slice
+      const uint4 value = __ldg(reinterpret_cast<const uint4 *>(
+          p.x + static_cast<size_t>(m) * p.k + group_begin * 128 + v * 8));
+      const int vg = v & 15;
+      const int target = (v >> 4) * 128 + (vg & 3) * 32 + (vg >> 2) * 8;
+      *reinterpret_cast<uint4 *>(x_shared + m * row_stride + target) = value;
+    }
+  } else if (linear_gather) {
+#pragma unroll
+    for (int it = 0; it < kItemBatch; ++it) {
+      const int q = tid + it * threads;
+      if (q < items)
+        held[it] = __ldg(reinterpret_cast<const int4 *>(p.perm + group_begin * 128) + q);
+    }
+    const int total = p.rows * p.k;
+    if (aligned_x) {
+      for (int i = tid; i < (total >> 3); i += threads)
+        reinterpret_cast<uint4 *>(x_linear)[i] = __ldg(reinterpret_cast<const uint4 *>(p.x) + i);
+    } else {
+#pragma unroll 8
+      for (int i = tid; i < total; i += threads) x_linear[i] = p.x[i];
+    }
+  } else {
+    for (int q = tid; q < items; q += threads) {
+      const int channel = group_begin * 128 + 4 * q;
+      int4 source = make_int4(channel, channel + 1, channel + 2, channel + 3);
+      if (p.perm) {
+        source.x = __ldg(p.perm + channel);
+        source.y = __ldg(p.perm + channel + 1);
+        source.z = __ldg(p.perm + channel + 2);
+        source.w = __ldg(p.perm + channel + 3);
+      }
+      const int i = 4 * q;
+      const int vector = (i >> 3) & 15;
+      const int target = (i & ~127) + (vector & 3) * 32 + (vector >> 2) * 8 + (i & 7);
+      for (int m = 0; m < p.rows; ++m) {
+        const __half *row = p.x + static_cast<size_t>(m) * p.k;
+        __align__(8) __half values[4] = {row[source.x], row[source.y], row[source.z], row[source.w]};
+        *reinterpret_cast<uint2 *>(x_shared + m * row_stride + target) =
+            *reinterpret_cast<const uint2 *>(values);
+      }
+    }
   }
-  const int partial_floats = launched_warps * TB * NB * 128;
-  for (int i = tid; i < partial_floats; i += threads) partial_shared[i] = 0.0f;
+  if (tid == 0) any_split = 0;
   __syncthreads();
 
+  // codebook, second half: item i = (entry i/8, replica i%8) -> byte 16*i, so the stores
+  // of a warp are contiguous
+  for (int i = tid; i < p.entries * 8; i += threads)
+    reinterpret_cast<uint4 *>(book_shared)[i] = book_stage[i >> 3];
+  if (linear_gather) {
+    for (int base = 0; base < items; base += kItemBatch * threads) {
+      if (base > 0) {
+#pragma unroll
+        for (int it = 0; it < kItemBatch; ++it) {
+          const int q = base + tid + it * threads;
+          if (q < items)
+            held[it] = __ldg(reinterpret_cast<const int4 *>(p.perm + group_begin * 128) + q);
+        }
+      }
+#pragma unroll
+      for (int it = 0; it < kItemBatch; ++it) {
+        const int q = base + tid + it * threads;
+        if (q >= items) continue;
+        const int4 source = held[it];
+        const int i = 4 * q;
+        const int vector = (i >> 3) & 15;
+        const int target = (i & ~127) + (vector & 3) * 32 + (vector >> 2) * 8 + (i & 7);
+        for (int m = 0; m < p.rows; ++m) {
+          const __half *row = x_linear + m * p.k;
+          __align__(8) __half values[4] = {row[source.x], row[source.y], row[source.z], row[source.w]};
+          *reinterpret_cast<uint2 *>(x_shared + m * row_stride + target) =
+              *reinterpret_cast<const uint2 *>(values);
+        }
+      }
+    }
+  }
+  __syncthreads();
+
+  // ---- 4. wait (bounded) for this warp's weights
+  bool ready = barrier_done(bar, 0);
+  if (!ready) {
+    const unsigned long long begin = global_timer();
+    unsigned spins = 0;
+    while (!(ready = barrier_done(bar, 0))) {
+      if ((++spins & 255u) == 0 && global_timer() - begin > kWaitLimitNs) break;
+    }
+  }
+  ready = __all_sync(0xffffffffu, ready);
+  if (!ready && lane == 0 && params.status) atomicExch(params.status, -7);
+
+  // ---- 5. main loop over this warp's units
   FieldConsts f;
-  f.index_mask = static_cast<uint32_t>(p.entries - 1) << line_log2;
-  f.shift_lo = 8 - line_log2;
-  f.shift_hi = 24 - line_log2;
+  f.index_mask = static_cast<uint32_t>(p.entries - 1) << 7;
   f.hi_shift = 27 - p.dbits;
   f.hi_mask = 3u << f.hi_shift;
   f.lo_mask = ((1u << (8 - p.dbits)) - 1u) << 19;
   f.lo_left = 11 - p.dbits;
   f.lo_right = 5 + p.dbits;
-  const uint32_t book_base = smem_address(book_shared);
-  const uint32_t lane_offset = 16u * static_cast<uint32_t>(lane & ((1 << replica_log2) - 1));
-  uint32_t x_row_address[NB];
+  const uint32_t lane_offset = 16u * static_cast<uint32_t>(lane & 7);
+  const unsigned char *x_row_base[NB];
 #pragma unroll
   for (int nb = 0; nb < NB; ++nb) {
     const int m = min(g + 8 * nb, p.rows - 1);
-    x_row_address[nb] = smem_address(x_shared) + 2u * static_cast<uint32_t>(m * row_stride) + 16u * t;
+    x_row_base[nb] = reinterpret_cast<const unsigned char *>(x_shared + m * row_stride) + 16 * t;
   }
-
+  const bool low_bits = p.dbits != 8;
   float acc[NB][4];
 #pragma unroll
   for (int nb = 0; nb < NB; ++nb)
 #pragma unroll
     for (int c = 0; c < 4; ++c) acc[nb][c] = 0.0f;
 
-  auto flush = [&](int tile_index) {
+  constexpr int kSegmentFloats = NB * 128;
+  float *my_partial =
+      partial_shared + static_cast<size_t>(warp) * params.warp_segments * kSegmentFloats;
+  int first_tile = 0, tile_count = 0;
+  if (ready && warp_end > warp_begin) {
+    const int tile0 = warp_begin / group_count;
+    int gi = warp_begin - tile0 * group_count;
+    first_tile = tile0;
+    const size_t first_slot = static_cast<size_t>(warp_begin - unit_begin);
+    const unsigned char *code_ptr = codes_shared + first_slot * 512 + g * 32 + t * 8;
+    const unsigned char *radius_ptr = radii_shared + first_slot * 64 + g * 4;
+    const unsigned char *grid_ptr = grid_shared + first_slot * 64 + g * 4;
+    for (int u = warp_begin; u < warp_end; ++u) {
+      uint2 code[2];
+      uint32_t radius_word[2], endpoints[2];
+      code[0] = *reinterpret_cast<const uint2 *>(code_ptr);
+      code[1] = *reinterpret_cast<const uint2 *>(code_ptr + 256);
+      radius_word[0] = *reinterpret_cast<const uint32_t *>(radius_ptr);
+      radius_word[1] = *reinterpret_cast<const uint32_t *>(radius_ptr + 32);
+      endpoints[0] = *reinterpret_cast<const uint32_t *>(grid_ptr);
+      endpoints[1] = *reinterpret_cast<const uint32_t *>(grid_ptr + 32);
+      const unsigned char *x_row[NB];
 #pragma unroll
-    for (int nb = 0; nb < NB; ++nb) {
-      float *dst = partial_shared + ((warp * TB + tile_index) * NB + nb) * 128;
-      *reinterpret_cast<float2 *>(dst + g * 8 + 2 * t) = make_float2(acc[nb][0], acc[nb][1]);
-      *reinterpret_cast<float2 *>(dst + (g + 8) * 8 + 2 * t) = make_float2(acc[nb][2], acc[nb][3]);
+      for (int nb = 0; nb < NB; ++nb) x_row[nb] = x_row_base[nb] + 256 * gi;
+      if (low_bits)
+        compute_unit<NB, true>(code, radius_word, endpoints, acc, f, book_shared, lane_offset, x_row, t);
+      else
+        compute_unit<NB, false>(code, radius_word, endpoints, acc, f, book_shared, lane_offset, x_row, t);
+      code_ptr += 512;
+      radius_ptr += 64;
+      grid_ptr += 64;
+      ++gi;
+      if (gi == group_count || u + 1 == warp_end) {
+        // this warp is done with the tile: park its partial sums
+        float *dst = my_partial + tile_count * kSegmentFloats;
 #pragma unroll
-      for (int c = 0; c < 4; ++c) acc[nb][c] = 0.0f;
-    }
-  };
-
-  if (has_work) {
-    while (true) {
-      // advance to the next unit of this warp and prefetch it
-      int next_ti = ti, next_gi = gi + warps;
-      while (next_gi >= group_count) {
-        next_gi -= group_count;
-        ++next_ti;
+        for (int nb = 0; nb < NB; ++nb) {
+          *reinterpret_cast<float2 *>(dst + nb * 128 + g * 8 + 2 * t) =
+              make_float2(acc[nb][0], acc[nb][1]);
+          *reinterpret_cast<float2 *>(dst + nb * 128 + (g + 8) * 8 + 2 * t) =
+              make_float2(acc[nb][2], acc[nb][3]);
+#pragma unroll
+          for (int c = 0; c < 4; ++c) acc[nb][c] = 0.0f;
+        }
+        ++tile_count;
+        gi = 0;
       }
-      const bool more = next_ti < tile_count;
-      UnitRegs next;
-      if (more) load_unit(next, p, tile_begin + next_ti, group_begin + next_gi, g, t);
-
-      uint32_t x_address[NB];
-#pragma unroll
-      for (int nb = 0; nb < NB; ++nb) x_address[nb] = x_row_address[nb] + 256u * gi;
-      compute_unit<NB>(current, acc, f, book_base, lane_offset, x_address, t);
-
-      if (!more || next_ti != ti) flush(ti);
-      if (!more) break;
-      current = next;
-      ti = next_ti;
-      gi = next_gi;
     }
+  }
+  if (lane == 0) {
+    warp_first_tile[warp] = first_tile;
+    warp_tile_count[warp] = tile_count;
+  }
+
+  // ---- 6. which tiles does this CTA touch, and who else touches them
+  const int cta_first_tile = unit_count > 0 ? unit_begin / group_count : 0;
+  const int cta_tiles = unit_count > 0 ? (unit_end - 1) / group_count - cta_first_tile + 1 : 0;
+  if (tid < cta_tiles) {
+    const int tile = cta_first_tile + tid;
+    int total = 0, slot = 0;
+    for (int s2 = 0; s2 < S; ++s2) {
+      const int gb = static_cast<int>(static_cast<long long>(p.groups) * s2 / S);
+      const int gc = static_cast<int>(static_cast<long long>(p.groups) * (s2 + 1) / S) - gb;
+      const long long U2 = static_cast<long long>(p.tiles) * gc;
+      const long long u0 = static_cast<long long>(tile) * gc;
+      const int first = owner_of(u0, U2, J);
+      const int last = owner_of(u0 + gc - 1, U2, J);
+      if (s2 == slice) slot = total + (j - first);
+      total += last - first + 1;
+    }
+    tile_parts[tid] = total;
+    tile_slot[tid] = slot;
+    tile_last[tid] = 0;
+    if (total > 1) any_split = 1;
   }
   __syncthreads();
 
-  // Combine warps in warp order.  Element index e = ((tile*NB + nb)*16 + row)*8 + column.
-  const int elements = tile_count * NB * 128;
-  const bool direct = p.splits == 1;
-  float *partial_global =
-      direct ? nullptr
-             : p.partial + (static_cast<size_t>(tile_block) * p.splits + split) * (TB * NB * 128);
-  for (int e = tid; e < elements; e += threads) {
+  // ---- 7. combine the warps (warp order = K order) and write y or the partial
+  const int columns = p.rows;              // valid MMA columns
+  const int tile_elements = 16 * columns;  // element r = row*columns + column
+  const int slots = p.slots_per_tile;
+  for (int e = tid; e < cta_tiles * tile_elements; e += threads) {
+    const int ti = e / tile_elements;
+    const int r = e - ti * tile_elements;
+    const int row = r / columns;
+    const int column = r - row * columns;
+    const int tile = cta_first_tile + ti;
+    const int source = (column >> 3) * 128 + row * 8 + (column & 7);
     float sum = 0.0f;
-    for (int w = 0; w < warps; ++w) sum += partial_shared[w * (TB * NB * 128) + e];
-    if (direct) {
-      const int column = e & 7, row = (e >> 3) & 15;
-      const int nb = (e >> 7) % NB, tile_index = (e >> 7) / NB;
-      const int m = nb * 8 + column;
-      const int out = (tile_begin + tile_index) * 16 + row;
-      if (m < p.rows && out < p.n) p.y[static_cast<size_t>(m) * p.n + out] = __float2half_rn(sum);
+    for (int w = 0; w < warps; ++w) {
+      const int k = tile - warp_first_tile[w];
+      if (k >= 0 && k < warp_tile_count[w])
+        sum += partial_shared[(static_cast<size_t>(w) * params.warp_segments + k) * kSegmentFloats + source];
+    }
+    if (tile_parts[ti] == 1) {
+      const int out = tile * 16 + row;
+      if (out < p.n) p.y[static_cast<size_t>(column) * p.n + out] = __float2half_rn(sum);
     } else {
-      __stcg(partial_global + e, sum);
+      __stcg(p.partial + (static_cast<size_t>(tile) * slots + tile_slot[ti]) * tile_elements + r, sum);
     }
   }
-  if (direct) return;
+  if (!any_split) return;
 
-  // Split-K: publish, count arrivals, the last CTA reduces in split order.
+  // ---- 8. tiles shared with other CTAs: publish, count arrivals, the last one finishes
   __threadfence();
   __syncthreads();
-  if (tid == 0) {
-    const unsigned arrived = atomicAdd(p.counters + tile_block, 1u);
-    last_flag = (arrived == static_cast<unsigned>(p.splits) - 1u);
+  if (tid < cta_tiles && tile_parts[tid] > 1) {
+    const unsigned arrived = atomicAdd(p.counters + cta_first_tile + tid, 1u);
+    tile_last[tid] = (arrived == static_cast<unsigned>(tile_parts[tid]) - 1u);
   }
   __syncthreads();
-  if (!last_flag) return;
   __threadfence();
-  const float *all = p.partial + static_cast<size_t>(tile_block) * p.splits * (TB * NB * 128);
-  for (int e = tid; e < elements; e += threads) {
+  for (int e = tid; e < cta_tiles * tile_elements; e += threads) {
+    const int ti = e / tile_elements;
+    if (!tile_last[ti]) continue;
+    const int r = e - ti * tile_elements;
+    const int row = r / columns;
+    const int column = r - row * columns;
+    const int tile = cta_first_tile + ti;
+    const float *pieces = p.partial + static_cast<size_t>(tile) * slots * tile_elements + r;
     float sum = 0.0f;
-    for (int s = 0; s < p.splits; ++s) sum += __ldcg(all + s * (TB * NB * 128) + e);
-    const int column = e & 7, row = (e >> 3) & 15;
-    const int nb = (e >> 7) % NB, tile_index = (e >> 7) / NB;
-    const int m = nb * 8 + column;
-    const int out = (tile_begin + tile_index) * 16 + row;
-    if (m < p.rows && out < p.n) p.y[static_cast<size_t>(m) * p.n + out] = __float2half_rn(sum);
+    for (int k = 0; k < tile_parts[ti]; ++k)
+      sum += __ldcg(pieces + static_cast<size_t>(k) * tile_elements);
+    const int out = tile * 16 + row;
+    if (out < p.n) p.y[static_cast<size_t>(column) * p.n + out] = __float2half_rn(sum);
   }
-  if (tid == 0) p.counters[tile_block] = 0u;
+  __syncthreads();
+  if (tid < cta_tiles && tile_last[tid]) p.counters[cta_first_tile + tid] = 0u;
 }
 
-constexpr int kMaxDynamicShared = 160 * 1024;
-
-template <int NB, int TB>
-cudaError_t launch_variant(const SkinnyParams &params, int ctas, int threads, size_t shared_bytes,
-                           cudaStream_t stream) {
-  sage_skinny_kernel<NB, TB><<<ctas, threads, shared_bytes, stream>>>(params);
-  return cudaGetLastError();
-}
-
-template <int NB, int TB>
+template <int NB>
 cudaError_t configure_variant() {
-  return cudaFuncSetAttribute(sage_skinny_kernel<NB, TB>,
-                              cudaFuncAttributeMaxDynamicSharedMemorySize, kMaxDynamicShared);
+  return cudaFuncSetAttribute(sage_skinny_kernel<NB>, cudaFuncAttributeMaxDynamicSharedMemorySize,
+                              kMaxDynamicShared);
 }
 
-int best_warps(int units, int limit) {
-  // fewest round-robin passes over the units, then the fewest warps that achieve it
-  const int most = units < limit ? units : limit;
-  const int passes = (units + most - 1) / most;
-  return (units + passes - 1) / passes;
+size_t x_bytes_for(int rows, int group_span) {
+  return (static_cast<size_t>(rows) * (static_cast<size_t>(group_span) * 256 + 64) + 127) / 128 * 128;
+}
+
+int slice_groups(int groups, int slices, int slice) {
+  return static_cast<int>(static_cast<long long>(groups) * (slice + 1) / slices) -
+         static_cast<int>(static_cast<long long>(groups) * slice / slices);
 }
 
 }  // namespace
 
 SkinnyPlan plan_skinny(int rows, int n, int k, int entries, int sm_count, const Tuning &tuning) {
+  (void)entries;
   SkinnyPlan plan{};
   const int tiles = (n + 15) / 16;
   const int groups = k / 128;
+  plan.tiles = tiles;
   plan.column_blocks = rows > 8 ? 2 : 1;
-  plan.replicas = tuning.replicas > 0 ? tuning.replicas : 8;
-  plan.tiles_per_cta = tuning.tiles_per_cta > 0 ? tuning.tiles_per_cta : 1;
-  if (plan.tiles_per_cta > 2 && plan.column_blocks == 2) plan.tiles_per_cta = 2;
-  if (plan.tiles_per_cta > 4) plan.tiles_per_cta = 4;
-  if (plan.tiles_per_cta == 3) plan.tiles_per_cta = 2;
-  plan.tile_blocks = (tiles + plan.tiles_per_cta - 1) / plan.tiles_per_cta;
+  plan.ctas_per_sm = tuning.ctas_per_sm > 0 ? tuning.ctas_per_sm : 2;
+  plan.warps = tuning.warps > 0 ? tuning.warps : 8;
+  if (plan.warps > kMaxWarps) plan.warps = kMaxWarps;
+  const int resident = sm_count * plan.ctas_per_sm;
 
-  int splits = tuning.splits;
-  if (splits <= 0) {
-    // enough CTAs for ~4 per SM, at least two groups per CTA
-    const int want = 4 * sm_count;
-    splits = (want + plan.tile_blocks - 1) / plan.tile_blocks;
-    const int most = groups >= 2 ? groups / 2 : 1;
-    if (splits > most) splits = most;
-    if (splits < 1) splits = 1;
+  // K slices: as few as keep one slice's activations within the shared-memory budget
+  const size_t x_budget = 72 * 1024;
+  int slices = tuning.slices > 0 ? tuning.slices : 1;
+  if (slices > kMaxSlices) slices = kMaxSlices;
+  if (slices > groups) slices = groups;
+  while (slices < kMaxSlices && slices < groups &&
+         x_bytes_for(rows, (groups + slices - 1) / slices) > x_budget)
+    ++slices;
+  plan.slices = slices;
+  int min_groups = groups, max_groups = 0;
+  for (int s = 0; s < slices; ++s) {
+    const int count = slice_groups(groups, slices, s);
+    if (count < min_groups) min_groups = count;
+    if (count > max_groups) max_groups = count;
   }
-  if (splits > groups) splits = groups;
-  // staged activations must fit: rows * (span*2 + 64) bytes <= 96 KiB
-  while (static_cast<size_t>(rows) * (((groups + splits - 1) / splits) * 256 + 64) > 96 * 1024 &&
-         splits < groups)
-    ++splits;
-  plan.groups_per_split = (groups + splits - 1) / splits;
-  plan.splits = (groups + plan.groups_per_split - 1) / plan.groups_per_split;
-  const int units = plan.groups_per_split * plan.tiles_per_cta;
-  plan.warps = tuning.warps > 0 ? tuning.warps : best_warps(units, 8);
-  if (plan.warps > 8) plan.warps = 8;
-  if (plan.warps > units) plan.warps = units;
-  if (plan.splits > 1) {
-    plan.partial_bytes = static_cast<size_t>(plan.tile_blocks) * plan.splits * plan.tiles_per_cta *
-                         plan.column_blocks * 128 * sizeof(float);
-    plan.counter_bytes = static_cast<size_t>(plan.tile_blocks) * sizeof(unsigned);
-  }
+
+  // CTAs per slice: the resident grid, but never more CTAs than units, and enough CTAs
+  // that one CTA's units and tiles fit its shared-memory tables
+  const long long min_units = static_cast<long long>(tiles) * min_groups;
+  const long long max_units = static_cast<long long>(tiles) * max_groups;
+  long long per_slice = resident / slices;
+  if (per_slice < 1) per_slice = 1;
+  const int unit_cap = 96;  // 96 * 640 B = 60 KiB of packed weights per CTA
+  if (per_slice * unit_cap < max_units) per_slice = (max_units + unit_cap - 1) / unit_cap;
+  const int tile_cap = kMaxCtaTiles - 2;
+  while ((max_units + per_slice - 1) / per_slice / min_groups + 2 > tile_cap) ++per_slice;
+  if (per_slice > min_units) per_slice = min_units;
+  plan.ctas_per_slice = static_cast<int>(per_slice);
+  plan.ctas = plan.ctas_per_slice * slices;
+  plan.unit_capacity = static_cast<int>((max_units + per_slice - 1) / per_slice);
+  const int warp_units = (plan.unit_capacity + plan.warps - 1) / plan.warps;
+  plan.warp_segments = warp_units / min_groups + 2;
+
+  // pieces per tile: in each slice a tile's units span at most `parts` CTAs
+  const long long least = min_units / per_slice;  // units in the smallest CTA range, >= 1
+  const int parts = static_cast<int>((max_groups + least - 1) / least) + 1;
+  plan.slots_per_tile = slices * parts;
+  plan.x_bytes = x_bytes_for(rows, max_groups);
+  // a single activation row with a permutation is gathered through a linear copy in
+  // shared memory (several rows arrive pre-gathered)
+  plan.lin_bytes = rows == 1 ? (static_cast<size_t>(k) * 2 + 127) / 128 * 128 : 0;
+  plan.shared_bytes = plan.x_bytes + static_cast<size_t>(plan.unit_capacity) * kUnitBytes +
+                      static_cast<size_t>(plan.warps) * plan.warp_segments * plan.column_blocks * 512 +
+                      plan.lin_bytes;
+  // every tile is whole inside one CTA only if K is unsliced and CTA ranges end on tile ends
+  const bool aligned = slices == 1 && max_units % per_slice == 0 &&
+                       (max_units / per_slice) % groups == 0;
+  plan.needs_scratch = !aligned;
+  plan.partial_bytes = plan.needs_scratch ? static_cast<size_t>(tiles) * plan.slots_per_tile * 16 *
+                                                rows * sizeof(float)
+                                          : 0;
   return plan;
 }
 
 cudaError_t configure_skinny() {
-  cudaError_t status;
-  if ((status = configure_variant<1, 1>()) != cudaSuccess) return status;
-  if ((status = configure_variant<1, 2>()) != cudaSuccess) return status;
-  if ((status = configure_variant<1, 4>()) != cudaSuccess) return status;
-  if ((status = configure_variant<2, 1>()) != cudaSuccess) return status;
-  return configure_variant<2, 2>();
+  cudaError_t status = configure_variant<1>();
+  if (status != cudaSuccess) return status;
+  return configure_variant<2>();
 }
 
-cudaError_t launch_skinny(SkinnyParams &params, const SkinnyPlan &plan, int total_ctas,
+cudaError_t launch_skinny(const SkinnyParams &params, int warps, int column_blocks, int total_ctas,
                           cudaStream_t stream) {
-  int replica_log2 = 0;
-  while ((1 << (replica_log2 + 1)) <= plan.replicas) ++replica_log2;
-  params.replica_log2 = replica_log2;
-  int max_entries = 0;
-  size_t x_bytes = 0;
-  for (int i = 0; i < params.count; ++i) {
-    const SkinnyProblem &p = params.problem[i];
-    if (p.entries > max_entries) max_entries = p.entries;
-    const size_t need = static_cast<size_t>(p.rows) * (p.groups_per_split * 256 + 64);
-    if (need > x_bytes) x_bytes = need;
-  }
-  (void)max_entries;
-  params.x_bytes = static_cast<int>((x_bytes + 15) / 16 * 16);
-  const size_t partial_bytes =
-      static_cast<size_t>(plan.warps) * plan.tiles_per_cta * plan.column_blocks * 128 * sizeof(float);
-  const size_t shared_bytes = params.x_bytes + partial_bytes;
+  const size_t shared_bytes = params.x_bytes + static_cast<size_t>(params.unit_capacity) * kUnitBytes +
+                              static_cast<size_t>(warps) * params.warp_segments * column_blocks * 512 +
+                              params.lin_bytes;
   if (shared_bytes > static_cast<size_t>(kMaxDynamicShared)) return cudaErrorInvalidConfiguration;
-  const int threads = plan.warps * 32;
-#define SAGEB200_LAUNCH(NB, TB) \
-  return launch_variant<NB, TB>(params, total_ctas, threads, shared_bytes, stream)
-  if (plan.column_blocks == 1) {
-    if (plan.tiles_per_cta == 1) SAGEB200_LAUNCH(1, 1);
-    if (plan.tiles_per_cta == 2) SAGEB200_LAUNCH(1, 2);
-    SAGEB200_LAUNCH(1, 4);
-  }
-  if (plan.tiles_per_cta == 1) SAGEB200_LAUNCH(2, 1);
-  SAGEB200_LAUNCH(2, 2);
-#undef SAGEB200_LAUNCH
+  const int threads = warps * 32;
+  if (column_blocks == 1)
+    sage_skinny_kernel<1><<<total_ctas, threads, shared_bytes, stream>>>(params);
+  else
+    sage_skinny_kernel<2><<<total_ctas, threads, shared_bytes, stream>>>(params);
+  return cudaGetLastError();
 }
 
 }  // namespace sageb200

@@ -349,10 +349,10 @@ def test_tuning_knob_sweep_stays_within_tolerance():
         for rows in (1, 12):
             x = torch.randn(rows, k, generator=torch.Generator().manual_seed(3), dtype=torch.float16).cuda()
             want = expected_output(x, cpu, n)
-            for warps, splits, replicas, tiles in [
-                (1, 1, 1, 1), (8, 1, 8, 1), (4, 4, 2, 2), (3, 5, 4, 4), (8, 32, 8, 1), (2, 2, 8, 2), (5, 3, 1, 4),
+            for warps, slices, ctas_per_sm in [
+                (1, 1, 1), (8, 1, 2), (4, 4, 2), (3, 5, 4), (16, 8, 1), (2, 2, 8), (5, 3, 1), (16, 1, 1),
             ]:
-                assert lib.sageb200_set_tuning(warps, splits, replicas, tiles) == 0
+                assert lib.sageb200_set_tuning(warps, slices, ctas_per_sm, 0) == 0
                 assert_output(layer(x), want)
     finally:
         lib.sageb200_set_tuning(0, 0, 0, 0)
