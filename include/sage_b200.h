@@ -140,12 +140,22 @@ int sageb200_linear_host(const void *x_host, const void *codes, const void *radi
 
 /*
  * Tuning knob for sweeps (debug): warps per CTA (<= 16), K slices (<= 8) and CTAs per SM
- * of the decode kernel; 0 restores the built-in heuristic for a field; `reserved` must
- * be 0.  Not thread safe, like its counterpart.
+ * of the decode kernel, and how output tiles are shared out (`mode` 1: every CTA gets an
+ * even share of the (tile, group) units and shared tiles are finished through scratch;
+ * 2: whole tiles per CTA); 0 restores the built-in heuristic for a field.  Not thread
+ * safe, like its counterpart.
  * Replaces: _set_sage_tuning / sage_gemv_tuning (reference csrc/bindings.cpp:81-84,
  *           csrc/sage/sage_gemv_cuda.cu:3-4).
  */
-int sageb200_set_tuning(int warps, int slices, int ctas_per_sm, int reserved);
+int sageb200_set_tuning(int warps, int slices, int ctas_per_sm, int mode);
+
+/*
+ * Profiling aid (debug): while `device_buffer` is non-NULL every CTA of the decode kernel
+ * writes 16 SM-clock readings (one per phase of its work) at device_buffer[16*cta ...];
+ * the buffer must hold 16 * 8 bytes per CTA of the largest launch.  NULL switches it off.
+ * No counterpart in the reference.
+ */
+int sageb200_debug_trace(void *device_buffer);
 
 /* Number of kernels this library has launched in this process (all entry points). */
 unsigned long long sageb200_launch_count(void);

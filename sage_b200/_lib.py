@@ -27,6 +27,7 @@ EXPORTED = (
     "sageb200_host_staging_bytes",
     "sageb200_linear_host",
     "sageb200_set_tuning",
+    "sageb200_debug_trace",
     "sageb200_launch_count",
 )
 
@@ -86,6 +87,8 @@ def load() -> ctypes.CDLL:
     lib.sageb200_linear_host.argtypes = [vp, vp, vp, vp, vp, vp, vp, vp, sz, ci, ci, ci, ci, vp]
     lib.sageb200_set_tuning.restype = ci
     lib.sageb200_set_tuning.argtypes = [ci, ci, ci, ci]
+    lib.sageb200_debug_trace.restype = ci
+    lib.sageb200_debug_trace.argtypes = [vp]
     lib.sageb200_launch_count.restype = ctypes.c_ulonglong
     lib.sageb200_launch_count.argtypes = []
     _handle = lib

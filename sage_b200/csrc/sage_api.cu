@@ -31,6 +31,7 @@ constexpr int kGemmMinRows = 33;
 DeviceState g_devices[kMaxDevices];
 Tuning g_tuning{0, 0, 0, 0};
 std::atomic<unsigned long long> g_launches{0};
+long long *g_trace = nullptr;  // profiling aid, see sageb200_debug_trace
 
 size_t align256(size_t bytes) { return (bytes + 255) / 256 * 256; }
 
@@ -116,6 +117,7 @@ int run_skinny(const sageb200_problem *problems, int count, void *workspace,
   SkinnyParams params;
   std::memset(&params, 0, sizeof(params));
   params.status = device.status;
+  params.trace = g_trace;
   unsigned char *scratch = static_cast<unsigned char *>(workspace);
   size_t offset = kCounterRegionBytes;
   int counters_used = 0;
@@ -164,6 +166,7 @@ int run_skinny(const sageb200_problem *problems, int count, void *workspace,
     out.slices = plan.slices;
     out.ctas_per_slice = plan.ctas_per_slice;
     out.slots_per_tile = plan.slots_per_tile;
+    out.whole_tiles = plan.whole_tiles;
     out.cta_begin = ctas;
     ctas += plan.ctas;
     offset += partial + gathered;
@@ -383,11 +386,16 @@ int sageb200_linear_host(const void *x_host, const void *codes, const void *radi
   return SAGEB200_OK;
 }
 
-int sageb200_set_tuning(int warps, int slices, int ctas_per_sm, int reserved) {
+int sageb200_debug_trace(void *device_buffer) {
+  g_trace = static_cast<long long *>(device_buffer);
+  return SAGEB200_OK;
+}
+
+int sageb200_set_tuning(int warps, int slices, int ctas_per_sm, int mode) {
   if (warps < 0 || warps > 16 || slices < 0 || slices > 8 || ctas_per_sm < 0 || ctas_per_sm > 8 ||
-      reserved != 0)
+      mode < 0 || mode > 2)
     return SAGEB200_ERR_INVALID_ARGUMENT;
-  g_tuning = Tuning{warps, slices, ctas_per_sm, 0};
+  g_tuning = Tuning{warps, slices, ctas_per_sm, mode};
   return SAGEB200_OK;
 }
 

@@ -26,6 +26,7 @@ struct SkinnyProblem {
   int slices;           // K slices
   int ctas_per_slice;   // CTAs that divide one slice's units evenly
   int slots_per_tile;
+  int whole_tiles;      // 1: CTAs own whole tiles (no sharing); 0: even share of units
   int cta_begin;        // first CTA of this problem in the grid
 };
 
@@ -37,6 +38,7 @@ struct SkinnyParams {
   int warp_segments;    // most tiles any warp touches
   int lin_bytes;        // shared bytes for activations in original order (0: none)
   int *status;          // device-visible status word, may be null
+  long long *trace;     // optional: per-CTA phase clocks (16 per CTA), null in normal use
 };
 
 // Launch plan for one problem (host side).
@@ -49,6 +51,7 @@ struct SkinnyPlan {
   int unit_capacity;
   int warp_segments;
   int slots_per_tile;
+  int whole_tiles;
   int column_blocks;    // 1 for rows <= 8, 2 for rows <= 16
   int tiles;
   bool needs_scratch;
@@ -59,7 +62,7 @@ struct SkinnyPlan {
 };
 
 struct Tuning {
-  int warps, slices, ctas_per_sm, reserved;
+  int warps, slices, ctas_per_sm, mode;  // mode: 0 auto, 1 even units, 2 whole tiles
 };
 
 SkinnyPlan plan_skinny(int rows, int n, int k, int entries, int sm_count, const Tuning &tuning);

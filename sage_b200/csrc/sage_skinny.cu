@@ -69,10 +69,12 @@ __device__ __forceinline__ unsigned long long global_timer() {
   return t;
 }
 
-// CTA that owns unit u when U units are divided evenly over J CTAs (CTA j owns
-// [j*U/J, (j+1)*U/J)).
-__device__ __forceinline__ int owner_of(long long u, long long U, int J) {
-  return static_cast<int>(((u + 1) * J - 1) / U);
+// Even split of n items over `parts` (n >= parts >= 1): with q = n / parts and
+// r = n % parts, part i holds q + (i < r) items starting at i*q + min(i, r).  32-bit only.
+__device__ __forceinline__ int split_begin(int i, int q, int r) { return i * q + min(i, r); }
+__device__ __forceinline__ int split_owner(int u, int q, int r) {
+  const int big = r * (q + 1);
+  return u < big ? u / (q + 1) : r + (u - big) / q;
 }
 
 // Dynamic shared memory: [x | codes | radii | grid | warp partials | x in original order].
@@ -80,15 +82,16 @@ template <int NB>
 __global__ void __launch_bounds__(512, 1) sage_skinny_kernel(const __grid_constant__ SkinnyParams params) {
   extern __shared__ __align__(128) unsigned char shared[];
   __shared__ __align__(128) unsigned char book_shared[kBookBytes];
-  __shared__ uint4 book_stage[256];  // codebook, one interleaved entry each, before replication
   __shared__ __align__(8) unsigned long long barriers[kMaxWarps];
   __shared__ int warp_first_tile[kMaxWarps];
   __shared__ int warp_tile_count[kMaxWarps];
   __shared__ int tile_parts[kMaxCtaTiles];  // CTAs contributing to the tile, all slices
   __shared__ int tile_slot[kMaxCtaTiles];   // this CTA's position among them (slice-major)
   __shared__ int tile_last[kMaxCtaTiles];   // this CTA arrived last
-  __shared__ int any_split;
 
+  long long *trace = params.trace ? params.trace + 16 * static_cast<size_t>(blockIdx.x) : nullptr;
+#define SAGE_STAMP(i) do { if (trace && threadIdx.x == 0) trace[i] = clock64(); } while (0)
+  SAGE_STAMP(0);
   int pi = 0;
   while (pi + 1 < params.count && static_cast<int>(blockIdx.x) >= params.problem[pi + 1].cta_begin)
     ++pi;
@@ -108,12 +111,17 @@ __global__ void __launch_bounds__(512, 1) sage_skinny_kernel(const __grid_consta
   if (local >= S * J) return;  // spare CTA of a grouped launch
   const int slice = local % S;
   const int j = local / S;
-  const int group_begin = static_cast<int>(static_cast<long long>(p.groups) * slice / S);
-  const int group_count =
-      static_cast<int>(static_cast<long long>(p.groups) * (slice + 1) / S) - group_begin;
-  const long long U = static_cast<long long>(p.tiles) * group_count;
-  const int unit_begin = static_cast<int>(U * j / J);
-  const int unit_end = static_cast<int>(U * (j + 1) / J);
+  const int group_begin = p.groups * slice / S;
+  const int group_count = p.groups * (slice + 1) / S - group_begin;
+  // Two ways to share the units out.  Whole tiles (S == 1): CTA j gets an even share of the
+  // tiles, so no tile is shared and nothing needs finishing afterwards.  Even units: CTA j
+  // gets an even share of the slice's units; tiles that straddle CTAs are finished in step 8.
+  const bool whole = p.whole_tiles != 0;
+  const int share = whole ? p.tiles : p.tiles * group_count;  // >= J
+  const int unit_q = share / J, unit_r = share - unit_q * J;
+  const int scale = whole ? group_count : 1;
+  const int unit_begin = split_begin(j, unit_q, unit_r) * scale;
+  const int unit_end = split_begin(j + 1, unit_q, unit_r) * scale;
   const int unit_count = unit_end - unit_begin;
 
   __half *x_shared = reinterpret_cast<__half *>(shared);
@@ -127,10 +135,9 @@ __global__ void __launch_bounds__(512, 1) sage_skinny_kernel(const __grid_consta
       static_cast<size_t>(warps) * params.warp_segments * NB * 512);
 
   // This warp's contiguous share of the CTA's units.
-  const int warp_begin =
-      unit_begin + static_cast<int>(static_cast<long long>(unit_count) * warp / warps);
-  const int warp_end =
-      unit_begin + static_cast<int>(static_cast<long long>(unit_count) * (warp + 1) / warps);
+  const int warp_q = unit_count / warps, warp_r = unit_count - warp_q * warps;
+  const int warp_begin = unit_begin + split_begin(warp, warp_q, warp_r);
+  const int warp_end = unit_begin + split_begin(warp + 1, warp_q, warp_r);
   const uint32_t bar = smem_address(&barriers[warp]);
 
   // ---- 1. start the weight stream: lane 0 of each warp copies the warp's units
@@ -161,62 +168,139 @@ __global__ void __launch_bounds__(512, 1) sage_skinny_kernel(const __grid_consta
     }
   }
 
-  // ---- 2. codebook, first half: one interleaved 16-byte entry per thread into a staging
-  //         copy (the eight replicas are written after the barrier below)
-  for (int e = tid; e < p.entries; e += threads) {
-    uint4 entry;
-    entry.x = __ldg(p.book + e);
-    entry.y = __ldg(p.book + p.entries + e);
-    entry.z = __ldg(p.book + 2 * p.entries + e);
-    entry.w = __ldg(p.book + 3 * p.entries + e);
-    book_stage[e] = entry;
+  // ---- 1b. which tiles does this CTA touch, and who else touches them (static
+  //          arithmetic, done while the copies fly)
+  const int cta_first_tile = unit_count > 0 ? unit_begin / group_count : 0;
+  const int cta_tiles = unit_count > 0 ? (unit_end - 1) / group_count - cta_first_tile + 1 : 0;
+  int shared_tile = 0;
+  if (!whole && tid < cta_tiles) {
+    const int tile = cta_first_tile + tid;
+    int total = 0, slot = 0;
+    for (int s2 = 0; s2 < S; ++s2) {
+      const int gc = p.groups * (s2 + 1) / S - p.groups * s2 / S;
+      const int U2 = p.tiles * gc;
+      const int q2 = U2 / J, r2 = U2 - q2 * J;
+      const int u0 = tile * gc;
+      const int first = split_owner(u0, q2, r2);
+      const int last = split_owner(u0 + gc - 1, q2, r2);
+      if (s2 == slice) slot = total + (j - first);
+      total += last - first + 1;
+    }
+    tile_parts[tid] = total;
+    tile_slot[tid] = slot;
+    tile_last[tid] = 0;
+    shared_tile = total > 1;
   }
 
-  // ---- 3. activations of this K slice, laid out so that lane (g,t), step s finds vector
-  //         4t+s of its row at [group][s][t][8 halves]; rows are 64 bytes apart modulo 128.
-  //         Three ways in, all with their global loads issued back to back (no load waits
-  //         on another load):
-  //           a. no permutation, 16-byte aligned x: straight 16-byte copies
-  //           b. permutation and the rows fit the linear buffer: copy x linearly into
-  //              shared memory while the permutation indices load into registers, then
-  //              gather from shared memory after the barrier
-  //           c. otherwise: gather from global memory, four channels per item
+  SAGE_STAMP(1);
+  // ---- 2. staging.  Every global load of this phase is issued before the first value
+  //         is used, so the phase costs one trip to L2, not one per item.
+  //   codebook    thread e holds entry e (16 bytes, dims interleaved) and writes its eight
+  //               replicas, starting at replica (lane % 8) so a warp's stores spread over
+  //               all banks
+  //   activations laid out so that lane (g,t), step s finds vector 4t+s of its row at
+  //               [group][s][t][8 halves]; rows are 64 bytes apart modulo 128.  Ways in:
+  //     a. no permutation, 16-byte aligned x: 16-byte copies
+  //     b. permutation and the rows fit the linear buffer: x is copied linearly into shared
+  //        memory while the permutation indices load into registers; the gather then reads
+  //        shared memory (after the barrier)
+  //     c. otherwise: gather from global memory, four channels per item
   const int span = group_count * 128;
   const int row_stride = span + 32;  // halves
   const bool aligned_x = (reinterpret_cast<uintptr_t>(p.x) & 15) == 0;
   const bool perm_aligned = (reinterpret_cast<uintptr_t>(p.perm) & 15) == 0;
   const bool linear_gather = p.perm != nullptr && perm_aligned &&
                              static_cast<size_t>(p.rows) * p.k * 2 <= static_cast<size_t>(params.lin_bytes);
-  constexpr int kItemBatch = 8;  // permutation items (4 channels each) a thread keeps in registers
+  const bool direct_copy = p.perm == nullptr && aligned_x;
+  constexpr int kItemBatch = 8;  // permutation items (4 channels each) held in registers
+  constexpr int kCopyBatch = 4;  // 16-byte activation pieces held in registers
   int4 held[kItemBatch];
+  uint4 piece[kCopyBatch];
   const int items = span >> 2;
-  if (p.perm == nullptr && aligned_x) {
-    const int vectors = span >> 3;
-    for (int i = tid; i < vectors * p.rows; i += threads) {
-      const int m = i / vectors;
-      const int v = i - m * vectors;  // vector index inside the slice
-      const uint4 value = __ldg(reinterpret_cast<const uint4 *>(
-          p.x + static_cast<size_t>(m) * p.k + group_begin * 128 + v * 8));
-      const int vg = v & 15;
-      const int target = (v >> 4) * 128 + (vg & 3) * 32 + (vg >> 2) * 8;
-      *reinterpret_cast<uint4 *>(x_shared + m * row_stride + target) = value;
-    }
-  } else if (linear_gather) {
+  const int vectors = span >> 3;
+  // what the first batch of 16-byte pieces copies: the slice of every row (a) or all of x (b)
+  const int pieces = direct_copy ? vectors * p.rows : (linear_gather && aligned_x ? (p.rows * p.k) >> 3 : 0);
+
+  uint4 entry = make_uint4(0, 0, 0, 0);
+  if (tid < p.entries) {
+    entry.x = __ldg(p.book + tid);
+    entry.y = __ldg(p.book + p.entries + tid);
+    entry.z = __ldg(p.book + 2 * p.entries + tid);
+    entry.w = __ldg(p.book + 3 * p.entries + tid);
+  }
+  if (linear_gather) {
 #pragma unroll
     for (int it = 0; it < kItemBatch; ++it) {
       const int q = tid + it * threads;
-      if (q < items)
-        held[it] = __ldg(reinterpret_cast<const int4 *>(p.perm + group_begin * 128) + q);
+      if (q < items) held[it] = __ldg(reinterpret_cast<const int4 *>(p.perm + group_begin * 128) + q);
     }
+  }
+  auto load_piece = [&](int i) {
+    if (direct_copy) {
+      const int m = i / vectors;
+      const int v = i - m * vectors;
+      return __ldg(reinterpret_cast<const uint4 *>(p.x + static_cast<size_t>(m) * p.k +
+                                                    group_begin * 128 + v * 8));
+    }
+    return __ldg(reinterpret_cast<const uint4 *>(p.x) + i);
+  };
+#pragma unroll
+  for (int it = 0; it < kCopyBatch; ++it) {
+    const int i = tid + it * threads;
+    if (i < pieces) piece[it] = load_piece(i);
+  }
+  // ... and now the stores
+  auto store_entry = [&](int e, const uint4 &value) {
+    uint4 *line = reinterpret_cast<uint4 *>(book_shared) + e * 8;
+#pragma unroll
+    for (int r = 0; r < 8; ++r) line[(r + lane) & 7] = value;
+  };
+  if (tid < p.entries) store_entry(tid, entry);
+  for (int e = tid + threads; e < p.entries; e += threads) {  // CTAs with fewer threads than entries
+    uint4 value;
+    value.x = __ldg(p.book + e);
+    value.y = __ldg(p.book + p.entries + e);
+    value.z = __ldg(p.book + 2 * p.entries + e);
+    value.w = __ldg(p.book + 3 * p.entries + e);
+    store_entry(e, value);
+  }
+  auto store_direct = [&](int i, const uint4 &value) {
+    const int m = i / vectors;
+    const int v = i - m * vectors;
+    const int vg = v & 15;
+    const int target = (v >> 4) * 128 + (vg & 3) * 32 + (vg >> 2) * 8;
+    *reinterpret_cast<uint4 *>(x_shared + m * row_stride + target) = value;
+  };
+#pragma unroll
+  for (int it = 0; it < kCopyBatch; ++it) {
+    const int i = tid + it * threads;
+    if (i < pieces) {
+      if (direct_copy) store_direct(i, piece[it]);
+      else reinterpret_cast<uint4 *>(x_linear)[i] = piece[it];
+    }
+  }
+  for (int base = kCopyBatch * threads; base < pieces; base += kCopyBatch * threads) {
+    // long rows / many rows: further batches, loads before stores again
+#pragma unroll
+    for (int it = 0; it < kCopyBatch; ++it) {
+      const int i = base + tid + it * threads;
+      if (i < pieces) piece[it] = load_piece(i);
+    }
+#pragma unroll
+    for (int it = 0; it < kCopyBatch; ++it) {
+      const int i = base + tid + it * threads;
+      if (i < pieces) {
+        if (direct_copy) store_direct(i, piece[it]);
+        else reinterpret_cast<uint4 *>(x_linear)[i] = piece[it];
+      }
+    }
+  }
+  if (linear_gather && !aligned_x) {
     const int total = p.rows * p.k;
-    if (aligned_x) {
-      for (int i = tid; i < (total >> 3); i += threads)
-        reinterpret_cast<uint4 *>(x_linear)[i] = __ldg(reinterpret_cast<const uint4 *>(p.x) + i);
-    } else {
 #pragma unroll 8
-      for (int i = tid; i < total; i += threads) x_linear[i] = p.x[i];
-    }
-  } else {
+    for (int i = tid; i < total; i += threads) x_linear[i] = p.x[i];
+  }
+  if (!direct_copy && !linear_gather) {
     for (int q = tid; q < items; q += threads) {
       const int channel = group_begin * 128 + 4 * q;
       int4 source = make_int4(channel, channel + 1, channel + 2, channel + 3);
@@ -237,14 +321,11 @@ __global__ void __launch_bounds__(512, 1) sage_skinny_kernel(const __grid_consta
       }
     }
   }
-  if (tid == 0) any_split = 0;
-  __syncthreads();
+  SAGE_STAMP(2);
+  const bool any_split = __syncthreads_or(shared_tile) != 0;
+  SAGE_STAMP(3);
 
-  // codebook, second half: item i = (entry i/8, replica i%8) -> byte 16*i, so the stores
-  // of a warp are contiguous
-  for (int i = tid; i < p.entries * 8; i += threads)
-    reinterpret_cast<uint4 *>(book_shared)[i] = book_stage[i >> 3];
-  if (linear_gather) {
+  if (linear_gather) {  // warp-uniform: the gather out of shared memory, then a second barrier
     for (int base = 0; base < items; base += kItemBatch * threads) {
       if (base > 0) {
 #pragma unroll
@@ -270,9 +351,10 @@ __global__ void __launch_bounds__(512, 1) sage_skinny_kernel(const __grid_consta
         }
       }
     }
+    __syncthreads();
   }
-  __syncthreads();
 
+  SAGE_STAMP(4);
   // ---- 4. wait (bounded) for this warp's weights
   bool ready = barrier_done(bar, 0);
   if (!ready) {
@@ -285,6 +367,7 @@ __global__ void __launch_bounds__(512, 1) sage_skinny_kernel(const __grid_consta
   ready = __all_sync(0xffffffffu, ready);
   if (!ready && lane == 0 && params.status) atomicExch(params.status, -7);
 
+  SAGE_STAMP(5);
   // ---- 5. main loop over this warp's units
   FieldConsts f;
   f.index_mask = static_cast<uint32_t>(p.entries - 1) << 7;
@@ -361,29 +444,10 @@ __global__ void __launch_bounds__(512, 1) sage_skinny_kernel(const __grid_consta
     warp_tile_count[warp] = tile_count;
   }
 
-  // ---- 6. which tiles does this CTA touch, and who else touches them
-  const int cta_first_tile = unit_count > 0 ? unit_begin / group_count : 0;
-  const int cta_tiles = unit_count > 0 ? (unit_end - 1) / group_count - cta_first_tile + 1 : 0;
-  if (tid < cta_tiles) {
-    const int tile = cta_first_tile + tid;
-    int total = 0, slot = 0;
-    for (int s2 = 0; s2 < S; ++s2) {
-      const int gb = static_cast<int>(static_cast<long long>(p.groups) * s2 / S);
-      const int gc = static_cast<int>(static_cast<long long>(p.groups) * (s2 + 1) / S) - gb;
-      const long long U2 = static_cast<long long>(p.tiles) * gc;
-      const long long u0 = static_cast<long long>(tile) * gc;
-      const int first = owner_of(u0, U2, J);
-      const int last = owner_of(u0 + gc - 1, U2, J);
-      if (s2 == slice) slot = total + (j - first);
-      total += last - first + 1;
-    }
-    tile_parts[tid] = total;
-    tile_slot[tid] = slot;
-    tile_last[tid] = 0;
-    if (total > 1) any_split = 1;
-  }
+  SAGE_STAMP(6);
   __syncthreads();
 
+  SAGE_STAMP(7);
   // ---- 7. combine the warps (warp order = K order) and write y or the partial
   const int columns = p.rows;              // valid MMA columns
   const int tile_elements = 16 * columns;  // element r = row*columns + column
@@ -394,31 +458,40 @@ __global__ void __launch_bounds__(512, 1) sage_skinny_kernel(const __grid_consta
     const int row = r / columns;
     const int column = r - row * columns;
     const int tile = cta_first_tile + ti;
-    const int source = (column >> 3) * 128 + row * 8 + (column & 7);
-    float sum = 0.0f;
-    for (int w = 0; w < warps; ++w) {
-      const int k = tile - warp_first_tile[w];
-      if (k >= 0 && k < warp_tile_count[w])
-        sum += partial_shared[(static_cast<size_t>(w) * params.warp_segments + k) * kSegmentFloats + source];
+    const float *source = partial_shared + (column >> 3) * 128 + row * 8 + (column & 7);
+    float part[kMaxWarps];
+#pragma unroll
+    for (int w = 0; w < kMaxWarps; ++w) {  // independent loads first, ordered sum after
+      const int k = w < warps ? tile - warp_first_tile[w] : -1;
+      const bool valid = k >= 0 && k < (w < warps ? warp_tile_count[w] : 0);
+      part[w] = valid ? source[(static_cast<size_t>(w) * params.warp_segments + k) * kSegmentFloats] : 0.0f;
     }
-    if (tile_parts[ti] == 1) {
+    float sum = 0.0f;
+#pragma unroll
+    for (int w = 0; w < kMaxWarps; ++w) sum += part[w];
+    if (whole || tile_parts[ti] == 1) {
       const int out = tile * 16 + row;
       if (out < p.n) p.y[static_cast<size_t>(column) * p.n + out] = __float2half_rn(sum);
     } else {
       __stcg(p.partial + (static_cast<size_t>(tile) * slots + tile_slot[ti]) * tile_elements + r, sum);
     }
   }
+  SAGE_STAMP(8);
   if (!any_split) return;
 
-  // ---- 8. tiles shared with other CTAs: publish, count arrivals, the last one finishes
-  __threadfence();
+  // ---- 8. tiles shared with other CTAs: publish, count arrivals, the last one finishes.
+  //         The barrier orders the CTA's partial stores before the counting thread's
+  //         fence + atomic (release); the same thread's fence after the atomic and the
+  //         next barrier order the other CTAs' partials before this CTA's reads (acquire).
   __syncthreads();
   if (tid < cta_tiles && tile_parts[tid] > 1) {
+    __threadfence();
     const unsigned arrived = atomicAdd(p.counters + cta_first_tile + tid, 1u);
+    __threadfence();
     tile_last[tid] = (arrived == static_cast<unsigned>(tile_parts[tid]) - 1u);
   }
   __syncthreads();
-  __threadfence();
+  SAGE_STAMP(9);
   for (int e = tid; e < cta_tiles * tile_elements; e += threads) {
     const int ti = e / tile_elements;
     if (!tile_last[ti]) continue;
@@ -435,6 +508,8 @@ __global__ void __launch_bounds__(512, 1) sage_skinny_kernel(const __grid_consta
   }
   __syncthreads();
   if (tid < cta_tiles && tile_last[tid]) p.counters[cta_first_tile + tid] = 0u;
+  SAGE_STAMP(10);
+#undef SAGE_STAMP
 }
 
 template <int NB>
@@ -461,62 +536,93 @@ SkinnyPlan plan_skinny(int rows, int n, int k, int entries, int sm_count, const 
   const int groups = k / 128;
   plan.tiles = tiles;
   plan.column_blocks = rows > 8 ? 2 : 1;
-  plan.ctas_per_sm = tuning.ctas_per_sm > 0 ? tuning.ctas_per_sm : 2;
-  plan.warps = tuning.warps > 0 ? tuning.warps : 8;
+  plan.ctas_per_sm = tuning.ctas_per_sm > 0 ? tuning.ctas_per_sm : 1;
+  plan.warps = tuning.warps > 0 ? tuning.warps : 16;
   if (plan.warps > kMaxWarps) plan.warps = kMaxWarps;
   const int resident = sm_count * plan.ctas_per_sm;
+  const int unit_cap = 160;  // 160 * 640 B = 100 KiB of packed weights per CTA
 
   // K slices: as few as keep one slice's activations within the shared-memory budget
-  const size_t x_budget = 72 * 1024;
+  const size_t x_budget = 40 * 1024;
   int slices = tuning.slices > 0 ? tuning.slices : 1;
   if (slices > kMaxSlices) slices = kMaxSlices;
   if (slices > groups) slices = groups;
   while (slices < kMaxSlices && slices < groups &&
          x_bytes_for(rows, (groups + slices - 1) / slices) > x_budget)
     ++slices;
-  plan.slices = slices;
-  int min_groups = groups, max_groups = 0;
-  for (int s = 0; s < slices; ++s) {
-    const int count = slice_groups(groups, slices, s);
-    if (count < min_groups) min_groups = count;
-    if (count > max_groups) max_groups = count;
+
+  // Whole tiles per CTA or an even share of units?  Sharing a tile between CTAs costs a
+  // trip through scratch memory and an arrival counter, about as long as decoding
+  // kFinishUnits units; whole tiles cost imbalance when tiles are few.  Compare per SM.
+  constexpr int kFinishUnits = 50;
+  const long long even_cost =
+      (static_cast<long long>(tiles) * groups + sm_count - 1) / sm_count + kFinishUnits;
+  const long long whole_cost = static_cast<long long>((tiles + sm_count - 1) / sm_count) * groups;
+  bool whole = slices == 1 && whole_cost <= even_cost;
+  if (tuning.mode == 1) whole = false;
+  if (tuning.mode == 2 && slices == 1) whole = true;
+  if (whole) {
+    long long ctas = resident < tiles ? resident : tiles;
+    // a CTA's tiles must fit its shared-memory budget
+    while (((tiles + ctas - 1) / ctas) * groups > unit_cap && ctas < tiles) ++ctas;
+    if (((tiles + ctas - 1) / ctas) * groups > unit_cap) whole = false;  // one tile is too long
+    if (whole) {
+      plan.whole_tiles = 1;
+      plan.slices = 1;
+      plan.ctas_per_slice = static_cast<int>(ctas);
+      plan.ctas = plan.ctas_per_slice;
+      plan.unit_capacity = static_cast<int>((tiles + ctas - 1) / ctas) * groups;
+      const int warp_units = (plan.unit_capacity + plan.warps - 1) / plan.warps;
+      plan.warp_segments = warp_units / groups + 2;
+      plan.slots_per_tile = 1;
+      plan.x_bytes = x_bytes_for(rows, groups);
+      plan.needs_scratch = false;
+      plan.partial_bytes = 0;
+    }
   }
-
-  // CTAs per slice: the resident grid, but never more CTAs than units, and enough CTAs
-  // that one CTA's units and tiles fit its shared-memory tables
-  const long long min_units = static_cast<long long>(tiles) * min_groups;
-  const long long max_units = static_cast<long long>(tiles) * max_groups;
-  long long per_slice = resident / slices;
-  if (per_slice < 1) per_slice = 1;
-  const int unit_cap = 96;  // 96 * 640 B = 60 KiB of packed weights per CTA
-  if (per_slice * unit_cap < max_units) per_slice = (max_units + unit_cap - 1) / unit_cap;
-  const int tile_cap = kMaxCtaTiles - 2;
-  while ((max_units + per_slice - 1) / per_slice / min_groups + 2 > tile_cap) ++per_slice;
-  if (per_slice > min_units) per_slice = min_units;
-  plan.ctas_per_slice = static_cast<int>(per_slice);
-  plan.ctas = plan.ctas_per_slice * slices;
-  plan.unit_capacity = static_cast<int>((max_units + per_slice - 1) / per_slice);
-  const int warp_units = (plan.unit_capacity + plan.warps - 1) / plan.warps;
-  plan.warp_segments = warp_units / min_groups + 2;
-
-  // pieces per tile: in each slice a tile's units span at most `parts` CTAs
-  const long long least = min_units / per_slice;  // units in the smallest CTA range, >= 1
-  const int parts = static_cast<int>((max_groups + least - 1) / least) + 1;
-  plan.slots_per_tile = slices * parts;
-  plan.x_bytes = x_bytes_for(rows, max_groups);
+  if (!whole) {
+    plan.whole_tiles = 0;
+    plan.slices = slices;
+    int min_groups = groups, max_groups = 0;
+    for (int s = 0; s < slices; ++s) {
+      const int count = slice_groups(groups, slices, s);
+      if (count < min_groups) min_groups = count;
+      if (count > max_groups) max_groups = count;
+    }
+    // CTAs per slice: the resident grid, but never more CTAs than units, and enough CTAs
+    // that one CTA's units and tiles fit its shared-memory tables
+    const long long min_units = static_cast<long long>(tiles) * min_groups;
+    const long long max_units = static_cast<long long>(tiles) * max_groups;
+    long long per_slice = resident / slices;
+    if (per_slice < 1) per_slice = 1;
+    if (per_slice * unit_cap < max_units) per_slice = (max_units + unit_cap - 1) / unit_cap;
+    const int tile_cap = kMaxCtaTiles - 2;
+    while ((max_units + per_slice - 1) / per_slice / min_groups + 2 > tile_cap) ++per_slice;
+    if (per_slice > min_units) per_slice = min_units;
+    plan.ctas_per_slice = static_cast<int>(per_slice);
+    plan.ctas = plan.ctas_per_slice * slices;
+    plan.unit_capacity = static_cast<int>((max_units + per_slice - 1) / per_slice);
+    const int warp_units = (plan.unit_capacity + plan.warps - 1) / plan.warps;
+    plan.warp_segments = warp_units / min_groups + 2;
+    // pieces per tile: in each slice a tile's units span at most `parts` CTAs
+    const long long least = min_units / per_slice;  // units in the smallest CTA range, >= 1
+    const int parts = static_cast<int>((max_groups + least - 1) / least) + 1;
+    plan.slots_per_tile = slices * parts;
+    plan.x_bytes = x_bytes_for(rows, max_groups);
+    // every tile is whole inside one CTA only if K is unsliced and CTA ranges end on tile ends
+    const bool aligned = slices == 1 && max_units % per_slice == 0 &&
+                         (max_units / per_slice) % groups == 0;
+    plan.needs_scratch = !aligned;
+    plan.partial_bytes = plan.needs_scratch ? static_cast<size_t>(tiles) * plan.slots_per_tile *
+                                                  16 * rows * sizeof(float)
+                                            : 0;
+  }
   // a single activation row with a permutation is gathered through a linear copy in
   // shared memory (several rows arrive pre-gathered)
   plan.lin_bytes = rows == 1 ? (static_cast<size_t>(k) * 2 + 127) / 128 * 128 : 0;
   plan.shared_bytes = plan.x_bytes + static_cast<size_t>(plan.unit_capacity) * kUnitBytes +
                       static_cast<size_t>(plan.warps) * plan.warp_segments * plan.column_blocks * 512 +
                       plan.lin_bytes;
-  // every tile is whole inside one CTA only if K is unsliced and CTA ranges end on tile ends
-  const bool aligned = slices == 1 && max_units % per_slice == 0 &&
-                       (max_units / per_slice) % groups == 0;
-  plan.needs_scratch = !aligned;
-  plan.partial_bytes = plan.needs_scratch ? static_cast<size_t>(tiles) * plan.slots_per_tile * 16 *
-                                                rows * sizeof(float)
-                                          : 0;
   return plan;
 }
 

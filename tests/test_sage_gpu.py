@@ -349,10 +349,11 @@ def test_tuning_knob_sweep_stays_within_tolerance():
         for rows in (1, 12):
             x = torch.randn(rows, k, generator=torch.Generator().manual_seed(3), dtype=torch.float16).cuda()
             want = expected_output(x, cpu, n)
-            for warps, slices, ctas_per_sm in [
-                (1, 1, 1), (8, 1, 2), (4, 4, 2), (3, 5, 4), (16, 8, 1), (2, 2, 8), (5, 3, 1), (16, 1, 1),
+            for warps, slices, ctas_per_sm, mode in [
+                (1, 1, 1, 1), (8, 1, 2, 2), (4, 4, 2, 0), (3, 5, 4, 1), (16, 8, 1, 0), (2, 2, 8, 2),
+                (5, 3, 1, 1), (16, 1, 1, 1), (16, 1, 1, 2), (7, 1, 3, 2),
             ]:
-                assert lib.sageb200_set_tuning(warps, slices, ctas_per_sm, 0) == 0
+                assert lib.sageb200_set_tuning(warps, slices, ctas_per_sm, mode) == 0
                 assert_output(layer(x), want)
     finally:
         lib.sageb200_set_tuning(0, 0, 0, 0)
