@@ -34,6 +34,7 @@ extern "C" {
 #define SAGEB200_ERR_CUDA (-5)             /* a CUDA call or launch failed               */
 #define SAGEB200_ERR_NO_DEVICE (-6)        /* no sm_100 device is current                */
 #define SAGEB200_ERR_TIMEOUT (-7)          /* a bounded device-side wait ran out         */
+#define SAGEB200_ERR_STATIC_SCRATCH (-8)   /* shape too large for sageb200_linear_static */
 
 /* Library version, major*10000 + minor*100 + patch. */
 int sageb200_version(void);
@@ -156,6 +157,35 @@ int sageb200_set_tuning(int warps, int slices, int ctas_per_sm, int mode);
  * No counterpart in the reference.
  */
 int sageb200_debug_trace(void *device_buffer);
+
+/*
+ * Allocation-free form of sageb200_linear for the decode range (rows <= 16).
+ *
+ * For callers that cannot provide a workspace because they are not in a position to
+ * allocate device memory: engines that fixed their whole memory plan at start-up, plugins
+ * that only ever receive a stream and tensor pointers from the runtime hosting them, and
+ * serving loops that cannot risk the device-wide stall (or the failure) of an allocator
+ * call between two tokens.  The scratch the decode kernel needs sits in a static device
+ * array inside the library instead: SAGEB200_STATIC_SCRATCH_BYTES bytes on every GPU that
+ * loads the library, held until the process exits.
+ *
+ *   - Shapes whose sageb200_workspace_bytes(rows, n, k) exceeds that size, and rows > 16,
+ *     are refused with SAGEB200_ERR_STATIC_SCRATCH; nothing is launched.
+ *   - It calls no cudaMalloc, cudaFree or any other allocating routine.  The first call on
+ *     each device looks up the array's device address (a one-off set-up step that may load
+ *     the library's device code): make that first call outside any stream capture.
+ *   - All calls on a device share the one array.  Each call re-zeroes the arrival counters
+ *     on `stream` before it launches, so calls ordered on one stream are safe; calls that
+ *     can overlap on the GPU (different streams, different threads) race on the array and
+ *     must be serialised by the caller or use sageb200_linear with separate workspaces.
+ * Arguments and results are those of sageb200_linear.
+ * No counterpart in the reference, which allocates its workspace with torch::empty on
+ * every call.
+ */
+#define SAGEB200_STATIC_SCRATCH_BYTES (8 * 1024 * 1024)
+int sageb200_linear_static(const void *x, const void *codes, const void *radii, const void *grid,
+                           const void *book, const int32_t *perm, void *y, int rows, int n, int k,
+                           int entries, void *stream);
 
 /* Number of kernels this library has launched in this process (all entry points). */
 unsigned long long sageb200_launch_count(void);

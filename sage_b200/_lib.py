@@ -28,6 +28,7 @@ EXPORTED = (
     "sageb200_linear_host",
     "sageb200_set_tuning",
     "sageb200_debug_trace",
+    "sageb200_linear_static",
     "sageb200_launch_count",
 )
 
@@ -87,6 +88,8 @@ def load() -> ctypes.CDLL:
     lib.sageb200_linear_host.argtypes = [vp, vp, vp, vp, vp, vp, vp, vp, sz, ci, ci, ci, ci, vp]
     lib.sageb200_set_tuning.restype = ci
     lib.sageb200_set_tuning.argtypes = [ci, ci, ci, ci]
+    lib.sageb200_linear_static.restype = ci
+    lib.sageb200_linear_static.argtypes = [vp, vp, vp, vp, vp, vp, vp, ci, ci, ci, ci, vp]
     lib.sageb200_debug_trace.restype = ci
     lib.sageb200_debug_trace.argtypes = [vp]
     lib.sageb200_launch_count.restype = ctypes.c_ulonglong

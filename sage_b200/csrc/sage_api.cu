@@ -224,6 +224,10 @@ const char *sageb200_status_string(int status) {
     case SAGEB200_ERR_CUDA: return "a CUDA call or kernel launch failed";
     case SAGEB200_ERR_NO_DEVICE: return "no current CUDA device of compute capability 10.x";
     case SAGEB200_ERR_TIMEOUT: return "a bounded device-side wait ran out";
+    case SAGEB200_ERR_STATIC_SCRATCH:
+      return "this shape needs more scratch than the library's built-in static buffer holds "
+             "(SAGEB200_STATIC_SCRATCH_BYTES) or more than 16 rows; use sageb200_linear with "
+             "caller-provided scratch";
     default: return "unknown status";
   }
 }
@@ -400,5 +404,79 @@ int sageb200_set_tuning(int warps, int slices, int ctas_per_sm, int mode) {
 }
 
 unsigned long long sageb200_launch_count(void) { return g_launches.load(std::memory_order_relaxed); }
+
+/* ---------------------------------------------------------------------------------------
+ * sageb200_linear_static: the decode matmul for callers that cannot hand over scratch.
+ *
+ * Some hosts of this library may not allocate device memory at all once serving has begun:
+ * an engine whose whole memory budget was carved up at start-up, a plugin that is only ever
+ * given a stream and tensor pointers by the runtime that loaded it, a request handler that
+ * must not hit the device-wide synchronisation and possible out-of-memory failure of an
+ * allocator call in the middle of a token.  sageb200_linear asks such callers for a
+ * workspace they have no way to produce.  This entry point takes none: the partial sums,
+ * arrival counters and gathered activations of the decode kernel live in the file-scope
+ * device array below, which is part of the loaded library image on every GPU that uses
+ * the library and stays there until the process exits.
+ *
+ * The array's name is only a handle on the host side; the device address is looked up
+ * once per device with cudaGetSymbolAddress (with that device current) and that address
+ * is what the kernels receive.
+ * ------------------------------------------------------------------------------------- */
+static __device__ __align__(256) unsigned char g_static_scratch[SAGEB200_STATIC_SCRATCH_BYTES];
+
+namespace {
+struct StaticScratch {
+  std::atomic<int> ready{0};
+  void *address = nullptr;
+};
+StaticScratch g_static_scratch_state[kMaxDevices];
+
+// Device address of g_static_scratch on the current device; looked up on first use.
+int static_scratch_address(void **out) {
+  int device = 0;
+  if (cudaGetDevice(&device) != cudaSuccess || device < 0 || device >= kMaxDevices) {
+    cudaGetLastError();
+    return SAGEB200_ERR_NO_DEVICE;
+  }
+  StaticScratch &state = g_static_scratch_state[device];
+  if (!state.ready.load(std::memory_order_acquire)) {
+    void *address = nullptr;
+    if (cudaGetSymbolAddress(&address, g_static_scratch) != cudaSuccess || address == nullptr) {
+      cudaGetLastError();
+      return SAGEB200_ERR_CUDA;
+    }
+    state.address = address;
+    state.ready.store(1, std::memory_order_release);
+  }
+  *out = state.address;
+  return SAGEB200_OK;
+}
+}  // namespace
+
+int sageb200_linear_static(const void *x, const void *codes, const void *radii, const void *grid,
+                           const void *book, const int32_t *perm, void *y, int rows, int n, int k,
+                           int entries, void *stream) {
+  sageb200_problem problem{x, codes, radii, grid, book, perm, y, rows, n, k, entries};
+  int status = validate_problem(problem);
+  if (status) return status;
+  if (rows == 0) return SAGEB200_OK;
+  if (rows > 16) return SAGEB200_ERR_STATIC_SCRATCH;
+  DeviceState *device = nullptr;
+  status = device_state(&device);
+  if (status) return status;
+  if (sageb200_workspace_bytes(rows, n, k) > static_cast<size_t>(SAGEB200_STATIC_SCRATCH_BYTES))
+    return SAGEB200_ERR_STATIC_SCRATCH;
+  void *scratch = nullptr;
+  status = static_scratch_address(&scratch);
+  if (status) return status;
+  cudaStream_t s = static_cast<cudaStream_t>(stream);
+  // The array keeps whatever the previous call left.  Only the arrival counters have to
+  // start at zero; partial sums and gathered activations are fully rewritten before use.
+  if (cudaMemsetAsync(scratch, 0, kCounterRegionBytes, s) != cudaSuccess) {
+    cudaGetLastError();
+    return SAGEB200_ERR_CUDA;
+  }
+  return run_skinny(&problem, 1, scratch, SAGEB200_STATIC_SCRATCH_BYTES, s, *device);
+}
 
 }  // extern "C"
