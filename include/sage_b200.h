@@ -108,10 +108,13 @@ typedef struct sageb200_problem {
  * Several independent packed linears with rows <= 16 in ONE kernel launch (q/k/v,
  * gate/up, the experts a token routes to).  `problems_host` is a HOST array of
  * `count` <= SAGEB200_MAX_GROUPED descriptors whose pointers are device pointers.
- * Workspace: the sum of sageb200_workspace_bytes over the problems, same zero-fill rule.
+ * The launch is planned as one resident wave: each problem gets CTAs in proportion to its
+ * packed size.  Workspace: sageb200_grouped_workspace_bytes for the same descriptors (only
+ * rows, n, k, entries and whether perm is NULL are read), same zero-fill rule.
  * No counterpart in the reference, which launches one kernel per linear
  * (csrc/bindings.cpp:52-61).
  */
+size_t sageb200_grouped_workspace_bytes(const sageb200_problem *problems_host, int count);
 int sageb200_linear_grouped(const sageb200_problem *problems_host, int count, void *workspace,
                             size_t workspace_bytes, void *stream);
 

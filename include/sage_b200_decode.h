@@ -1,0 +1,74 @@
+/*
+ * sage_b200 — C ABI of the non-matmul steps of a Qwen3 decode step (one new token for each
+ * of 1..16 sequences): embedding lookup, residual add + RMSNorm, per-head q/k RMSNorm +
+ * rotate-half RoPE + KV-cache append, split-context attention, SwiGLU, FP16 lm_head and
+ * argmax.  They let a whole decode step run as one CUDA graph with token ids and positions
+ * kept in device memory.
+ *
+ * None of these has a counterpart in the reference's native code: there the same steps are
+ * Hugging Face `transformers` Qwen3 modules and torch SDPA, driven by
+ * benchmarks/model.py:43-133 (prefill, then one model call per token with a StaticCache).
+ *
+ * All pointers are device pointers, all tensors FP16 and contiguous unless noted; `stream`
+ * is a cudaStream_t; every function returns 0, -1 (unsupported shape) or -5 (launch failed).
+ * head_dim must be 128.
+ */
+#ifndef SAGE_B200_DECODE_H_
+#define SAGE_B200_DECODE_H_
+
+#include <stddef.h>
+
+#ifdef __cplusplus
+extern "C" {
+#endif
+
+/* h[rows][hidden] = table[tokens[row]][:]; tokens are int64. */
+int sageb200_glue_embed(const void *table, const void *tokens, void *h, int rows, int hidden,
+                        void *stream);
+
+/* residual += delta (skipped when delta is NULL); x = weight * rmsnorm(residual, eps). */
+int sageb200_glue_add_rmsnorm(void *residual, const void *delta, const void *weight, void *x,
+                              int rows, int hidden, float eps, void *stream);
+
+/*
+ * q[rows][q_heads][128] is normalised and rotated in place; k is normalised, rotated and
+ * written to k_cache[row][kv_head][positions[row]][:]; v is copied to v_cache likewise.
+ * cos/sin tables are FP16 [max_seq][64]; positions are int32 [rows].
+ */
+int sageb200_glue_qk_norm_rope_cache(void *q, const void *k, const void *v, const void *q_weight,
+                                     const void *k_weight, const void *cos_table,
+                                     const void *sin_table, const void *positions, void *k_cache,
+                                     void *v_cache, int rows, int q_heads, int kv_heads, int head_dim,
+                                     int max_seq, float eps, void *stream);
+
+/* FP32 scratch for sageb200_glue_attention_decode. */
+size_t sageb200_glue_attention_scratch_bytes(int rows, int q_heads, int splits);
+
+/*
+ * out[rows][q_heads][128] = softmax(q . K^T / sqrt(128)) . V over cache positions
+ * 0..positions[row] (the new token included), grouped-query heads, the context split over
+ * `splits` CTAs per (row, kv head).
+ */
+int sageb200_glue_attention_decode(const void *q, const void *k_cache, const void *v_cache,
+                                   const void *positions, void *out, void *scratch, int rows,
+                                   int q_heads, int kv_heads, int head_dim, int max_seq, int splits,
+                                   void *stream);
+
+/* act[i] = fp16(silu(gate[i])) * up[i]. */
+int sageb200_glue_swiglu(const void *gate, const void *up, void *act, long long count, void *stream);
+
+/* logits[rows][vocab] = x[rows][hidden] . head[vocab][hidden]^T, FP32 accumulation. */
+int sageb200_glue_lm_head(const void *head, const void *x, void *logits, int rows, int vocab,
+                          int hidden, int sm_count, void *stream);
+
+/*
+ * tokens[row] = argmax(logits[row]) (int64, lowest index on ties); positions[row] += 1;
+ * if log != NULL, log[row*log_stride + step[0]] = token and step[0] += 1 (int32).
+ */
+int sageb200_glue_argmax_advance(const void *logits, void *tokens, void *positions, void *log,
+                                 void *step, int rows, int vocab, int log_stride, void *stream);
+
+#ifdef __cplusplus
+}
+#endif
+#endif /* SAGE_B200_DECODE_H_ */

@@ -23,6 +23,7 @@ EXPORTED = (
     "sageb200_workspace_bytes",
     "sageb200_linear",
     "sageb200_linear_grouped",
+    "sageb200_grouped_workspace_bytes",
     "sageb200_dequant",
     "sageb200_host_staging_bytes",
     "sageb200_linear_host",
@@ -30,6 +31,19 @@ EXPORTED = (
     "sageb200_debug_trace",
     "sageb200_linear_static",
     "sageb200_launch_count",
+)
+
+
+# every symbol include/sage_b200_decode.h declares
+EXPORTED_DECODE = (
+    "sageb200_glue_embed",
+    "sageb200_glue_add_rmsnorm",
+    "sageb200_glue_qk_norm_rope_cache",
+    "sageb200_glue_attention_scratch_bytes",
+    "sageb200_glue_attention_decode",
+    "sageb200_glue_swiglu",
+    "sageb200_glue_lm_head",
+    "sageb200_glue_argmax_advance",
 )
 
 
@@ -78,6 +92,8 @@ def load() -> ctypes.CDLL:
     lib.sageb200_workspace_bytes.argtypes = [ci, ci, ci]
     lib.sageb200_linear.restype = ci
     lib.sageb200_linear.argtypes = [vp, vp, vp, vp, vp, vp, vp, vp, sz, ci, ci, ci, ci, vp]
+    lib.sageb200_grouped_workspace_bytes.restype = sz
+    lib.sageb200_grouped_workspace_bytes.argtypes = [ctypes.POINTER(Problem), ci]
     lib.sageb200_linear_grouped.restype = ci
     lib.sageb200_linear_grouped.argtypes = [ctypes.POINTER(Problem), ci, vp, sz, vp]
     lib.sageb200_dequant.restype = ci
@@ -94,6 +110,24 @@ def load() -> ctypes.CDLL:
     lib.sageb200_debug_trace.argtypes = [vp]
     lib.sageb200_launch_count.restype = ctypes.c_ulonglong
     lib.sageb200_launch_count.argtypes = []
+    # decode glue (include/sage_b200_decode.h)
+    fl, ll = ctypes.c_float, ctypes.c_longlong
+    lib.sageb200_glue_embed.restype = ci
+    lib.sageb200_glue_embed.argtypes = [vp, vp, vp, ci, ci, vp]
+    lib.sageb200_glue_add_rmsnorm.restype = ci
+    lib.sageb200_glue_add_rmsnorm.argtypes = [vp, vp, vp, vp, ci, ci, fl, vp]
+    lib.sageb200_glue_qk_norm_rope_cache.restype = ci
+    lib.sageb200_glue_qk_norm_rope_cache.argtypes = [vp] * 10 + [ci] * 5 + [fl, vp]
+    lib.sageb200_glue_attention_scratch_bytes.restype = sz
+    lib.sageb200_glue_attention_scratch_bytes.argtypes = [ci, ci, ci]
+    lib.sageb200_glue_attention_decode.restype = ci
+    lib.sageb200_glue_attention_decode.argtypes = [vp] * 6 + [ci] * 6 + [vp]
+    lib.sageb200_glue_swiglu.restype = ci
+    lib.sageb200_glue_swiglu.argtypes = [vp, vp, vp, ll, vp]
+    lib.sageb200_glue_lm_head.restype = ci
+    lib.sageb200_glue_lm_head.argtypes = [vp, vp, vp, ci, ci, ci, ci, vp]
+    lib.sageb200_glue_argmax_advance.restype = ci
+    lib.sageb200_glue_argmax_advance.argtypes = [vp] * 5 + [ci, ci, ci, vp]
     _handle = lib
     return lib
 

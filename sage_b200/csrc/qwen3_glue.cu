@@ -1,0 +1,439 @@
+// Everything in a Qwen3 decode step that is not a packed linear, as small fused kernels for
+// 1..16 sequences decoding one token each.  In the reference these steps are Hugging Face
+// `transformers` modules driven by benchmarks/model.py:43-133 (RMSNorm eps 1e-6, per-head
+// q/k RMSNorm, rotate-half RoPE, static KV cache, SDPA, SwiGLU, FP16 lm_head, argmax); here
+// they exist so that a whole decode step can be captured in one CUDA graph with no host
+// round trip: token ids and positions live in device memory.
+//
+// Numerics follow the Hugging Face modules: norms and softmax in FP32, one rounding to FP16
+// where the module returns FP16, RoPE products in FP16 with FP16 cos/sin tables.
+#include "../../include/sage_b200_decode.h"
+
+#include <cuda_fp16.h>
+#include <cuda_runtime.h>
+#include <stdint.h>
+
+namespace {
+
+constexpr int kNormThreads = 256;
+
+__device__ __forceinline__ float warp_sum(float v) {
+#pragma unroll
+  for (int o = 16; o; o >>= 1) v += __shfl_xor_sync(0xffffffffu, v, o);
+  return v;
+}
+__device__ __forceinline__ float warp_max(float v) {
+#pragma unroll
+  for (int o = 16; o; o >>= 1) v = fmaxf(v, __shfl_xor_sync(0xffffffffu, v, o));
+  return v;
+}
+
+// Block-wide sum for blockDim.x <= 1024 (result in every thread).
+__device__ float block_sum(float v, float *scratch) {
+  const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
+  v = warp_sum(v);
+  __syncthreads();
+  if (lane == 0) scratch[warp] = v;
+  __syncthreads();
+  float total = 0.0f;
+  const int warps = (blockDim.x + 31) >> 5;
+  for (int w = 0; w < warps; ++w) total += scratch[w];
+  return total;
+}
+
+// h[m][:] = embedding[token[m]][:]
+__global__ void embed_kernel(const __half *__restrict__ table, const long long *__restrict__ tokens,
+                             __half *__restrict__ h, int hidden) {
+  const int m = blockIdx.x;
+  const __half *row = table + static_cast<size_t>(tokens[m]) * hidden;
+  for (int i = threadIdx.x; i < hidden / 8; i += blockDim.x)
+    reinterpret_cast<uint4 *>(h + static_cast<size_t>(m) * hidden)[i] =
+        reinterpret_cast<const uint4 *>(row)[i];
+}
+
+// residual[m] += delta[m] (FP16 add, skipped when delta is null);
+// x[m] = weight * fp16(residual[m] * rsqrt(mean(residual[m]^2) + eps))
+__global__ void __launch_bounds__(kNormThreads)
+    add_rmsnorm_kernel(__half *__restrict__ residual, const __half *__restrict__ delta,
+                       const __half *__restrict__ weight, __half *__restrict__ x, int hidden,
+                       float eps) {
+  __shared__ float scratch[32];
+  extern __shared__ __half row_shared[];
+  const int m = blockIdx.x;
+  __half *r = residual + static_cast<size_t>(m) * hidden;
+  const __half *d = delta ? delta + static_cast<size_t>(m) * hidden : nullptr;
+  float square = 0.0f;
+  for (int i = threadIdx.x; i < hidden; i += kNormThreads) {
+    __half v = r[i];
+    if (d) {
+      v = __hadd(v, d[i]);
+      r[i] = v;
+    }
+    row_shared[i] = v;
+    const float f = __half2float(v);
+    square += f * f;
+  }
+  const float total = block_sum(square, scratch);
+  const float scale = rsqrtf(total / hidden + eps);
+  for (int i = threadIdx.x; i < hidden; i += kNormThreads) {
+    const __half normed = __float2half_rn(__half2float(row_shared[i]) * scale);
+    x[static_cast<size_t>(m) * hidden + i] = __hmul(weight[i], normed);
+  }
+}
+
+// One warp per (sequence, head): per-head RMSNorm of q or k (head_dim 128), rotate-half
+// RoPE at the sequence's position, q written in place, k and v written into the cache.
+// Heads 0..q_heads-1 are query heads, then kv_heads key heads, then kv_heads value heads.
+__global__ void qk_norm_rope_cache_kernel(__half *__restrict__ q, const __half *__restrict__ k,
+                                          const __half *__restrict__ v,
+                                          const __half *__restrict__ q_weight,
+                                          const __half *__restrict__ k_weight,
+                                          const __half *__restrict__ cos_table,
+                                          const __half *__restrict__ sin_table,
+                                          const int *__restrict__ positions,
+                                          __half *__restrict__ k_cache, __half *__restrict__ v_cache,
+                                          int q_heads, int kv_heads, int max_seq, float eps) {
+  const int lane = threadIdx.x & 31;
+  const int head = blockIdx.x * (blockDim.x >> 5) + (threadIdx.x >> 5);
+  const int m = blockIdx.y;
+  const int heads = q_heads + 2 * kv_heads;
+  if (head >= heads) return;
+  const int position = positions[m];
+  if (head >= q_heads + kv_heads) {  // value head: plain copy into the cache
+    const int j = head - q_heads - kv_heads;
+    const uint2 value = reinterpret_cast<const uint2 *>(v + (static_cast<size_t>(m) * kv_heads + j) * 128)[lane];
+    reinterpret_cast<uint2 *>(v_cache + ((static_cast<size_t>(m) * kv_heads + j) * max_seq + position) * 128)[lane] = value;
+    return;
+  }
+  const bool is_query = head < q_heads;
+  const int j = is_query ? head : head - q_heads;
+  const __half *source = is_query ? q + (static_cast<size_t>(m) * q_heads + j) * 128
+                                  : k + (static_cast<size_t>(m) * kv_heads + j) * 128;
+  const __half *weight = is_query ? q_weight : k_weight;
+  // lane holds dims lane*2, lane*2+1 of the first half and the same of the second half
+  const __half2 lo = reinterpret_cast<const __half2 *>(source)[lane];
+  const __half2 hi = reinterpret_cast<const __half2 *>(source + 64)[lane];
+  const float2 lof = __half22float2(lo), hif = __half22float2(hi);
+  const float square = warp_sum(lof.x * lof.x + lof.y * lof.y + hif.x * hif.x + hif.y * hif.y);
+  const float scale = rsqrtf(square / 128.0f + eps);
+  const __half2 wl = reinterpret_cast<const __half2 *>(weight)[lane];
+  const __half2 wh = reinterpret_cast<const __half2 *>(weight + 64)[lane];
+  const __half2 nl = __hmul2(wl, __floats2half2_rn(lof.x * scale, lof.y * scale));
+  const __half2 nh = __hmul2(wh, __floats2half2_rn(hif.x * scale, hif.y * scale));
+  const __half2 c = reinterpret_cast<const __half2 *>(cos_table + static_cast<size_t>(position) * 64)[lane];
+  const __half2 s = reinterpret_cast<const __half2 *>(sin_table + static_cast<size_t>(position) * 64)[lane];
+  // out_lo = x_lo*cos - x_hi*sin ; out_hi = x_hi*cos + x_lo*sin  (FP16 products and sums)
+  const __half2 out_lo = __hadd2(__hmul2(nl, c), __hmul2(__hneg2(nh), s));
+  const __half2 out_hi = __hadd2(__hmul2(nh, c), __hmul2(nl, s));
+  __half *target = is_query ? q + (static_cast<size_t>(m) * q_heads + j) * 128
+                            : k_cache + ((static_cast<size_t>(m) * kv_heads + j) * max_seq + position) * 128;
+  reinterpret_cast<__half2 *>(target)[lane] = out_lo;
+  reinterpret_cast<__half2 *>(target + 64)[lane] = out_hi;
+}
+
+// Attention for one new token per sequence, split over the context ("flash decoding").
+// CTA = (split, kv head, sequence); its `group` query heads share the K/V chunk.  Each warp
+// walks positions of the chunk; partial (max, sum, weighted V) per query head go to scratch.
+constexpr int kAttnWarps = 8;
+constexpr int kMaxGroup = 8;
+
+__global__ void __launch_bounds__(kAttnWarps * 32)
+    attention_partial_kernel(const __half *__restrict__ q, const __half *__restrict__ k_cache,
+                             const __half *__restrict__ v_cache, const int *__restrict__ positions,
+                             float *__restrict__ partial, int q_heads, int kv_heads, int max_seq,
+                             int splits, float scale) {
+  __shared__ float shared_max[kAttnWarps][kMaxGroup];
+  __shared__ float shared_sum[kAttnWarps][kMaxGroup];
+  __shared__ float shared_acc[kAttnWarps][kMaxGroup][128];
+  const int split = blockIdx.x, kv = blockIdx.y, m = blockIdx.z;
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  const int group = q_heads / kv_heads;
+  const int context = positions[m] + 1;
+  const int chunk = (context + splits - 1) / splits;
+  const int begin = split * chunk;
+  const int end = min(context, begin + chunk);
+  // lane holds dims 4*lane .. 4*lane+3
+  float2 qa[kMaxGroup], qb[kMaxGroup];
+  for (int g = 0; g < group; ++g) {
+    const __half *qh = q + (static_cast<size_t>(m) * q_heads + kv * group + g) * 128 + 4 * lane;
+    qa[g] = __half22float2(reinterpret_cast<const __half2 *>(qh)[0]);
+    qb[g] = __half22float2(reinterpret_cast<const __half2 *>(qh)[1]);
+  }
+  float running_max[kMaxGroup], running_sum[kMaxGroup], acc[kMaxGroup][4];
+  for (int g = 0; g < kMaxGroup; ++g) {
+    running_max[g] = -INFINITY;
+    running_sum[g] = 0.0f;
+    acc[g][0] = acc[g][1] = acc[g][2] = acc[g][3] = 0.0f;
+  }
+  const __half *k_base = k_cache + (static_cast<size_t>(m) * kv_heads + kv) * max_seq * 128;
+  const __half *v_base = v_cache + (static_cast<size_t>(m) * kv_heads + kv) * max_seq * 128;
+  for (int p = begin + warp; p < end; p += kAttnWarps) {
+    const uint2 kw = reinterpret_cast<const uint2 *>(k_base + static_cast<size_t>(p) * 128)[lane];
+    const uint2 vw = reinterpret_cast<const uint2 *>(v_base + static_cast<size_t>(p) * 128)[lane];
+    const float2 ka = __half22float2(*reinterpret_cast<const __half2 *>(&kw.x));
+    const float2 kb = __half22float2(*reinterpret_cast<const __half2 *>(&kw.y));
+    const float2 va = __half22float2(*reinterpret_cast<const __half2 *>(&vw.x));
+    const float2 vb = __half22float2(*reinterpret_cast<const __half2 *>(&vw.y));
+    for (int g = 0; g < group; ++g) {
+      float dot = qa[g].x * ka.x + qa[g].y * ka.y + qb[g].x * kb.x + qb[g].y * kb.y;
+      dot = warp_sum(dot) * scale;
+      const float new_max = fmaxf(running_max[g], dot);
+      const float rescale = __expf(running_max[g] - new_max);
+      const float weight = __expf(dot - new_max);
+      running_sum[g] = running_sum[g] * rescale + weight;
+      acc[g][0] = acc[g][0] * rescale + weight * va.x;
+      acc[g][1] = acc[g][1] * rescale + weight * va.y;
+      acc[g][2] = acc[g][2] * rescale + weight * vb.x;
+      acc[g][3] = acc[g][3] * rescale + weight * vb.y;
+      running_max[g] = new_max;
+    }
+  }
+  for (int g = 0; g < group; ++g) {
+    if (lane == 0) {
+      shared_max[warp][g] = running_max[g];
+      shared_sum[warp][g] = running_sum[g];
+    }
+    for (int c = 0; c < 4; ++c) shared_acc[warp][g][4 * lane + c] = acc[g][c];
+  }
+  __syncthreads();
+  // combine the warps: thread = (query head of the group, dim)
+  for (int item = threadIdx.x; item < group * 128; item += blockDim.x) {
+    const int g = item >> 7, dim = item & 127;
+    float top = -INFINITY;
+    for (int w = 0; w < kAttnWarps; ++w) top = fmaxf(top, shared_max[w][g]);
+    float sum = 0.0f, value = 0.0f;
+    for (int w = 0; w < kAttnWarps; ++w) {
+      const float f = shared_max[w][g] == -INFINITY ? 0.0f : __expf(shared_max[w][g] - top);
+      sum += shared_sum[w][g] * f;
+      value += shared_acc[w][g][dim] * f;
+    }
+    // partial layout: [sequence][query head][split][130] = (max, sum, 128 values)
+    float *out = partial + ((static_cast<size_t>(m) * q_heads + kv * group + g) * splits + split) * 130;
+    if (dim == 0) {
+      out[0] = top;
+      out[1] = sum;
+    }
+    out[2 + dim] = value;
+  }
+}
+
+// out[m][head][:] = sum over splits, softmax-normalised; one warp-quad (128 threads) per head.
+__global__ void attention_combine_kernel(const float *__restrict__ partial, __half *__restrict__ out,
+                                         int q_heads, int splits) {
+  const int head = blockIdx.x, m = blockIdx.y, dim = threadIdx.x;
+  const float *base = partial + (static_cast<size_t>(m) * q_heads + head) * splits * 130;
+  float top = -INFINITY;
+  for (int s = 0; s < splits; ++s) top = fmaxf(top, base[s * 130]);
+  float sum = 0.0f, value = 0.0f;
+  for (int s = 0; s < splits; ++s) {
+    const float mx = base[s * 130];
+    const float f = mx == -INFINITY ? 0.0f : __expf(mx - top);
+    sum += base[s * 130 + 1] * f;
+    value += base[s * 130 + 2 + dim] * f;
+  }
+  out[(static_cast<size_t>(m) * q_heads + head) * 128 + dim] = __float2half_rn(value / sum);
+}
+
+// act = silu(gate) * up, FP32 math on FP16 inputs, rounded as the FP16 modules round:
+// silu(gate) to FP16, then the FP16 product.
+__global__ void swiglu_kernel(const __half *__restrict__ gate, const __half *__restrict__ up,
+                              __half *__restrict__ act, long long count) {
+  const long long i = static_cast<long long>(blockIdx.x) * blockDim.x + threadIdx.x;
+  if (i >= count) return;
+  const float g = __half2float(gate[i]);
+  const __half silu = __float2half_rn(g / (1.0f + __expf(-g)));
+  act[i] = __hmul(silu, up[i]);
+}
+
+// logits[m][v] = dot(head[v][:], x[m][:]) in FP32, rounded to FP16.  One warp per vocabulary
+// row; the (up to 16) activation rows sit in shared memory.  HBM-bound on the head matrix.
+constexpr int kHeadWarps = 8;
+
+__global__ void __launch_bounds__(kHeadWarps * 32)
+    lm_head_kernel(const __half *__restrict__ head, const __half *__restrict__ x,
+                   __half *__restrict__ logits, int vocab, int hidden, int rows) {
+  extern __shared__ __half x_shared[];
+  for (int i = threadIdx.x; i < rows * hidden / 8; i += blockDim.x)
+    reinterpret_cast<uint4 *>(x_shared)[i] = reinterpret_cast<const uint4 *>(x)[i];
+  __syncthreads();
+  const int lane = threadIdx.x & 31;
+  const int pieces = hidden / 8;
+  for (int v = blockIdx.x * kHeadWarps + (threadIdx.x >> 5); v < vocab; v += gridDim.x * kHeadWarps) {
+    const uint4 *row = reinterpret_cast<const uint4 *>(head + static_cast<size_t>(v) * hidden);
+    float sums[16];
+    for (int m = 0; m < rows; ++m) sums[m] = 0.0f;
+    for (int i = lane; i < pieces; i += 32) {
+      uint4 w;
+      asm volatile("ld.global.nc.L1::no_allocate.v4.u32 {%0,%1,%2,%3}, [%4];"
+                   : "=r"(w.x), "=r"(w.y), "=r"(w.z), "=r"(w.w)
+                   : "l"(row + i));
+      const __half2 *wh = reinterpret_cast<const __half2 *>(&w);
+      for (int m = 0; m < rows; ++m) {
+        const uint4 a = reinterpret_cast<const uint4 *>(x_shared + static_cast<size_t>(m) * hidden)[i];
+        const __half2 *ah = reinterpret_cast<const __half2 *>(&a);
+        float s = sums[m];
+#pragma unroll
+        for (int c = 0; c < 4; ++c) {
+          const float2 wf = __half22float2(wh[c]), af = __half22float2(ah[c]);
+          s = fmaf(wf.x, af.x, s);
+          s = fmaf(wf.y, af.y, s);
+        }
+        sums[m] = s;
+      }
+    }
+    for (int m = 0; m < rows; ++m) {
+      const float total = warp_sum(sums[m]);
+      if (lane == 0) logits[static_cast<size_t>(m) * vocab + v] = __float2half_rn(total);
+    }
+  }
+}
+
+// next[m] = argmax(logits[m]), lowest index on ties; also appends the token to the output
+// log at column step[0] and advances the sequence's position.
+__global__ void __launch_bounds__(1024)
+    argmax_advance_kernel(const __half *__restrict__ logits, long long *__restrict__ tokens,
+                          int *__restrict__ positions, long long *__restrict__ log,
+                          int *__restrict__ step, int vocab, int log_stride) {
+  __shared__ float best_value[32];
+  __shared__ int best_index[32];
+  const int m = blockIdx.x;
+  const __half *row = logits + static_cast<size_t>(m) * vocab;
+  float value = -INFINITY;
+  int index = 0x7fffffff;
+  for (int i = threadIdx.x; i < vocab; i += blockDim.x) {
+    const float f = __half2float(row[i]);
+    if (f > value || (f == value && i < index)) {
+      value = f;
+      index = i;
+    }
+  }
+  for (int o = 16; o; o >>= 1) {
+    const float other = __shfl_xor_sync(0xffffffffu, value, o);
+    const int other_index = __shfl_xor_sync(0xffffffffu, index, o);
+    if (other > value || (other == value && other_index < index)) {
+      value = other;
+      index = other_index;
+    }
+  }
+  const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
+  if (lane == 0) {
+    best_value[warp] = value;
+    best_index[warp] = index;
+  }
+  __syncthreads();
+  if (threadIdx.x == 0) {
+    for (int w = 1; w < (blockDim.x >> 5); ++w)
+      if (best_value[w] > value || (best_value[w] == value && best_index[w] < index)) {
+        value = best_value[w];
+        index = best_index[w];
+      }
+    tokens[m] = index;
+    if (log && step[0] < log_stride) log[static_cast<size_t>(m) * log_stride + step[0]] = index;
+    positions[m] += 1;
+  }
+}
+
+// The step counter advances once per decode step, after every row's argmax has used it.
+__global__ void advance_step_kernel(int *step) { step[0] += 1; }
+
+int launch_status() { return cudaGetLastError() == cudaSuccess ? 0 : -5; }
+
+}  // namespace
+
+extern "C" {
+
+int sageb200_glue_embed(const void *table, const void *tokens, void *h, int rows, int hidden,
+                        void *stream) {
+  if (hidden % 8) return -1;
+  embed_kernel<<<rows, 128, 0, static_cast<cudaStream_t>(stream)>>>(
+      static_cast<const __half *>(table), static_cast<const long long *>(tokens),
+      static_cast<__half *>(h), hidden);
+  return launch_status();
+}
+
+int sageb200_glue_add_rmsnorm(void *residual, const void *delta, const void *weight, void *x,
+                              int rows, int hidden, float eps, void *stream) {
+  if (hidden > 24576) return -1;
+  add_rmsnorm_kernel<<<rows, kNormThreads, hidden * sizeof(__half), static_cast<cudaStream_t>(stream)>>>(
+      static_cast<__half *>(residual), static_cast<const __half *>(delta),
+      static_cast<const __half *>(weight), static_cast<__half *>(x), hidden, eps);
+  return launch_status();
+}
+
+int sageb200_glue_qk_norm_rope_cache(void *q, const void *k, const void *v, const void *q_weight,
+                                     const void *k_weight, const void *cos_table,
+                                     const void *sin_table, const void *positions, void *k_cache,
+                                     void *v_cache, int rows, int q_heads, int kv_heads, int head_dim,
+                                     int max_seq, float eps, void *stream) {
+  if (head_dim != 128) return -1;
+  const int heads = q_heads + 2 * kv_heads;
+  const dim3 grid((heads + 3) / 4, rows);
+  qk_norm_rope_cache_kernel<<<grid, 128, 0, static_cast<cudaStream_t>(stream)>>>(
+      static_cast<__half *>(q), static_cast<const __half *>(k), static_cast<const __half *>(v),
+      static_cast<const __half *>(q_weight), static_cast<const __half *>(k_weight),
+      static_cast<const __half *>(cos_table), static_cast<const __half *>(sin_table),
+      static_cast<const int *>(positions), static_cast<__half *>(k_cache),
+      static_cast<__half *>(v_cache), q_heads, kv_heads, max_seq, eps);
+  return launch_status();
+}
+
+size_t sageb200_glue_attention_scratch_bytes(int rows, int q_heads, int splits) {
+  return static_cast<size_t>(rows) * q_heads * splits * 130 * sizeof(float);
+}
+
+int sageb200_glue_attention_decode(const void *q, const void *k_cache, const void *v_cache,
+                                   const void *positions, void *out, void *scratch, int rows,
+                                   int q_heads, int kv_heads, int head_dim, int max_seq, int splits,
+                                   void *stream) {
+  if (head_dim != 128 || q_heads % kv_heads || q_heads / kv_heads > kMaxGroup || splits < 1) return -1;
+  cudaStream_t s = static_cast<cudaStream_t>(stream);
+  const dim3 grid(splits, kv_heads, rows);
+  attention_partial_kernel<<<grid, kAttnWarps * 32, 0, s>>>(
+      static_cast<const __half *>(q), static_cast<const __half *>(k_cache),
+      static_cast<const __half *>(v_cache), static_cast<const int *>(positions),
+      static_cast<float *>(scratch), q_heads, kv_heads, max_seq, splits, rsqrtf(128.0f));
+  attention_combine_kernel<<<dim3(q_heads, rows), 128, 0, s>>>(static_cast<const float *>(scratch),
+                                                              static_cast<__half *>(out), q_heads,
+                                                              splits);
+  return launch_status();
+}
+
+int sageb200_glue_swiglu(const void *gate, const void *up, void *act, long long count, void *stream) {
+  const unsigned blocks = static_cast<unsigned>((count + 255) / 256);
+  swiglu_kernel<<<blocks, 256, 0, static_cast<cudaStream_t>(stream)>>>(
+      static_cast<const __half *>(gate), static_cast<const __half *>(up), static_cast<__half *>(act),
+      count);
+  return launch_status();
+}
+
+int sageb200_glue_lm_head(const void *head, const void *x, void *logits, int rows, int vocab,
+                          int hidden, int sm_count, void *stream) {
+  if (rows > 16 || hidden % 8) return -1;
+  const size_t shared = static_cast<size_t>(rows) * hidden * sizeof(__half);
+  static bool configured = false;
+  if (shared > 48 * 1024 && !configured) {
+    if (cudaFuncSetAttribute(lm_head_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, 200 * 1024) !=
+        cudaSuccess)
+      return -5;
+    configured = true;
+  }
+  const int blocks = (sm_count > 0 ? sm_count : 148) * 4;
+  lm_head_kernel<<<blocks, kHeadWarps * 32, shared, static_cast<cudaStream_t>(stream)>>>(
+      static_cast<const __half *>(head), static_cast<const __half *>(x), static_cast<__half *>(logits),
+      vocab, hidden, rows);
+  return launch_status();
+}
+
+int sageb200_glue_argmax_advance(const void *logits, void *tokens, void *positions, void *log,
+                                 void *step, int rows, int vocab, int log_stride, void *stream) {
+  cudaStream_t s = static_cast<cudaStream_t>(stream);
+  argmax_advance_kernel<<<rows, 1024, 0, s>>>(static_cast<const __half *>(logits),
+                                               static_cast<long long *>(tokens),
+                                               static_cast<int *>(positions),
+                                               static_cast<long long *>(log), static_cast<int *>(step),
+                                               vocab, log_stride);
+  if (step) advance_step_kernel<<<1, 1, 0, s>>>(static_cast<int *>(step));
+  return launch_status();
+}
+
+}  // extern "C"

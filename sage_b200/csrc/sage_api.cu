@@ -110,6 +110,42 @@ size_t gather_bytes(int rows, int k, bool permuted) {
 }
 size_t plan_bytes(const SkinnyPlan &plan) { return align256(plan.partial_bytes); }
 
+// Shares of the device for the problems of a grouped launch: CTAs in proportion to the
+// (tile, group) units of each problem, so the launch is one resident wave.
+void cta_budgets(const sageb200_problem *problems, int count, const DeviceState &device, int *budgets) {
+  for (int i = 0; i < count; ++i) budgets[i] = 0;
+  int live = 0;
+  double total = 0;
+  for (int i = 0; i < count; ++i)
+    if (problems[i].rows > 0) {
+      ++live;
+      total += static_cast<double>((problems[i].n + 15) / 16) * (problems[i].k / 128);
+    }
+  if (live <= 1) return;  // a single problem plans for the whole device
+  const int per_sm = g_tuning.ctas_per_sm > 0 ? g_tuning.ctas_per_sm : 1;
+  const int resident = device.sm_count * per_sm;
+  for (int i = 0; i < count; ++i) {
+    if (problems[i].rows == 0) continue;
+    const double units = static_cast<double>((problems[i].n + 15) / 16) * (problems[i].k / 128);
+    int share = static_cast<int>(resident * units / total);
+    budgets[i] = share < 1 ? 1 : share;
+  }
+}
+
+// Scratch bytes (after the counter region) the problems need together.
+size_t grouped_scratch_bytes(const sageb200_problem *problems, int count, const DeviceState &device) {
+  int budgets[kMaxGrouped];
+  cta_budgets(problems, count, device, budgets);
+  size_t bytes = 0;
+  for (int i = 0; i < count; ++i) {
+    const sageb200_problem &in = problems[i];
+    if (in.rows == 0) continue;
+    const SkinnyPlan plan = plan_skinny(in.rows, in.n, in.k, in.entries, device.sm_count, g_tuning, budgets[i]);
+    bytes += align256(plan.partial_bytes) + (in.rows > 1 && in.perm ? align256(static_cast<size_t>(in.rows) * in.k * 2) : 0);
+  }
+  return bytes;
+}
+
 // rows <= 16, one or more problems, one launch (plus one small gather launch for each
 // problem that has several rows and a permutation).
 int run_skinny(const sageb200_problem *problems, int count, void *workspace,
@@ -124,10 +160,13 @@ int run_skinny(const sageb200_problem *problems, int count, void *workspace,
   int ctas = 0;
   int live = 0;
   int warps = 0, column_blocks = 1;
+  int budgets[kMaxGrouped];
+  cta_budgets(problems, count, device, budgets);
   for (int i = 0; i < count; ++i) {
     const sageb200_problem &in = problems[i];
     if (in.rows == 0) continue;
-    const SkinnyPlan plan = plan_skinny(in.rows, in.n, in.k, in.entries, device.sm_count, g_tuning);
+    const SkinnyPlan plan =
+        plan_skinny(in.rows, in.n, in.k, in.entries, device.sm_count, g_tuning, budgets[i]);
     const size_t partial = plan_bytes(plan);
     const size_t gathered = gather_bytes(in.rows, in.k, in.perm != nullptr);
     if (partial || gathered) {
@@ -167,6 +206,11 @@ int run_skinny(const sageb200_problem *problems, int count, void *workspace,
     out.ctas_per_slice = plan.ctas_per_slice;
     out.slots_per_tile = plan.slots_per_tile;
     out.whole_tiles = plan.whole_tiles;
+    {
+      const long long share = plan.whole_tiles ? plan.tiles : static_cast<long long>(plan.tiles) * (in.k / 128);
+      out.share_q = static_cast<int>(share / plan.ctas_per_slice);
+      out.share_r = static_cast<int>(share % plan.ctas_per_slice);
+    }
     out.cta_begin = ctas;
     ctas += plan.ctas;
     offset += partial + gathered;
@@ -181,6 +225,8 @@ int run_skinny(const sageb200_problem *problems, int count, void *workspace,
   }
   if (live == 0) return SAGEB200_OK;
   params.count = live;
+  // floor(2^32 / warps) + 1; unused (and not representable) for a single warp
+  params.warps_reciprocal = warps > 1 ? static_cast<unsigned>((1ull << 32) / static_cast<unsigned>(warps)) + 1u : 0u;
   if (launch_skinny(params, warps, column_blocks, ctas, stream) != cudaSuccess) {
     cudaGetLastError();
     return SAGEB200_ERR_CUDA;
@@ -257,6 +303,20 @@ size_t sageb200_workspace_bytes(int rows, int n, int k) {
     const size_t need = plan_bytes(plan_skinny(pass, n, k, 256, sms, g_tuning)) + gather_bytes(pass, k, true);
     if (need > bytes) bytes = need;
   }
+  return bytes ? kCounterRegionBytes + bytes : 0;
+}
+
+size_t sageb200_grouped_workspace_bytes(const sageb200_problem *problems_host, int count) {
+  if (!problems_host || count <= 0 || count > SAGEB200_MAX_GROUPED) return 0;
+  for (int i = 0; i < count; ++i)
+    if (check_shape(problems_host[i].rows, problems_host[i].n, problems_host[i].k, problems_host[i].entries) ||
+        problems_host[i].rows > 16)
+      return 0;
+  DeviceState fallback;
+  fallback.sm_count = 148;
+  DeviceState *device = nullptr;
+  if (device_state(&device) != SAGEB200_OK) device = &fallback;
+  const size_t bytes = grouped_scratch_bytes(problems_host, count, *device);
   return bytes ? kCounterRegionBytes + bytes : 0;
 }
 

@@ -27,6 +27,7 @@ struct SkinnyProblem {
   int ctas_per_slice;   // CTAs that divide one slice's units evenly
   int slots_per_tile;
   int whole_tiles;      // 1: CTAs own whole tiles (no sharing); 0: even share of units
+  int share_q, share_r; // (tiles or units) / ctas_per_slice and remainder, for slices == 1
   int cta_begin;        // first CTA of this problem in the grid
 };
 
@@ -37,6 +38,7 @@ struct SkinnyParams {
   int unit_capacity;    // most units any CTA holds (640 shared bytes each)
   int warp_segments;    // most tiles any warp touches
   int lin_bytes;        // shared bytes for activations in original order (0: none)
+  unsigned warps_reciprocal;  // floor(2^32 / warps) + 1
   int *status;          // device-visible status word, may be null
   long long *trace;     // optional: per-CTA phase clocks (16 per CTA), null in normal use
 };
@@ -65,7 +67,9 @@ struct Tuning {
   int warps, slices, ctas_per_sm, mode;  // mode: 0 auto, 1 even units, 2 whole tiles
 };
 
-SkinnyPlan plan_skinny(int rows, int n, int k, int entries, int sm_count, const Tuning &tuning);
+// cta_budget: CTAs the problem may occupy at once (0: the whole device).
+SkinnyPlan plan_skinny(int rows, int n, int k, int entries, int sm_count, const Tuning &tuning,
+                       int cta_budget = 0);
 
 // Opts every skinny-kernel variant into large dynamic shared memory on the CURRENT device.
 cudaError_t configure_skinny();

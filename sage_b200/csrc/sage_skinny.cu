@@ -41,7 +41,8 @@ namespace {
 constexpr int kBookBytes = 256 * 8 * 16;  // 256 entries x 8 replicas x 16 bytes, static
 constexpr unsigned long long kWaitLimitNs = 2000000000ull;
 constexpr int kMaxWarps = 16;
-constexpr int kMaxCtaTiles = 64;
+constexpr int kMaxCtaTiles = 64;      // tiles of one CTA when tiles are shared between CTAs
+constexpr int kMaxWholeTiles = 192;   // tiles of one CTA in any mode (unit capacity / 1 group)
 constexpr int kMaxSlices = 8;
 constexpr int kUnitBytes = 640;           // 512 codes + 64 radius words + 64 grid
 constexpr int kMaxDynamicShared = 184 * 1024;  // plus ~37 KiB static stays under the 227 KiB limit
@@ -78,23 +79,28 @@ __device__ __forceinline__ int split_owner(int u, int q, int r) {
 }
 
 // Dynamic shared memory: [x | codes | radii | grid | warp partials | x in original order].
-template <int NB>
+// kLowBits: some problem of the launch has 64 or 128 codebook entries (codes carry low
+// radius bits); a launch whose codebooks all have 256 entries uses the shorter variant.
+template <int NB, bool kLowBits>
 __global__ void __launch_bounds__(512, 1) sage_skinny_kernel(const __grid_constant__ SkinnyParams params) {
   extern __shared__ __align__(128) unsigned char shared[];
   __shared__ __align__(128) unsigned char book_shared[kBookBytes];
   __shared__ __align__(8) unsigned long long barriers[kMaxWarps];
   __shared__ int warp_first_tile[kMaxWarps];
-  __shared__ int warp_tile_count[kMaxWarps];
   __shared__ int tile_parts[kMaxCtaTiles];  // CTAs contributing to the tile, all slices
   __shared__ int tile_slot[kMaxCtaTiles];   // this CTA's position among them (slice-major)
   __shared__ int tile_last[kMaxCtaTiles];   // this CTA arrived last
+  __shared__ unsigned char tile_warp_lo[kMaxWholeTiles];  // first and last warp holding a
+  __shared__ unsigned char tile_warp_hi[kMaxWholeTiles];  // piece of the CTA's tile
 
   long long *trace = params.trace ? params.trace + 16 * static_cast<size_t>(blockIdx.x) : nullptr;
 #define SAGE_STAMP(i) do { if (trace && threadIdx.x == 0) trace[i] = clock64(); } while (0)
   SAGE_STAMP(0);
   int pi = 0;
-  while (pi + 1 < params.count && static_cast<int>(blockIdx.x) >= params.problem[pi + 1].cta_begin)
-    ++pi;
+  if (params.count > 1) {
+    while (pi + 1 < params.count && static_cast<int>(blockIdx.x) >= params.problem[pi + 1].cta_begin)
+      ++pi;
+  }
   const SkinnyProblem &p = params.problem[pi];
 
   const int tid = threadIdx.x;
@@ -109,16 +115,23 @@ __global__ void __launch_bounds__(512, 1) sage_skinny_kernel(const __grid_consta
   const int S = p.slices;
   const int J = p.ctas_per_slice;
   if (local >= S * J) return;  // spare CTA of a grouped launch
-  const int slice = local % S;
-  const int j = local / S;
-  const int group_begin = p.groups * slice / S;
-  const int group_count = p.groups * (slice + 1) / S - group_begin;
+  int slice = 0, j = local, group_begin = 0, group_count = p.groups;
+  if (S > 1) {
+    slice = local % S;
+    j = local / S;
+    group_begin = p.groups * slice / S;
+    group_count = p.groups * (slice + 1) / S - group_begin;
+  }
   // Two ways to share the units out.  Whole tiles (S == 1): CTA j gets an even share of the
   // tiles, so no tile is shared and nothing needs finishing afterwards.  Even units: CTA j
   // gets an even share of the slice's units; tiles that straddle CTAs are finished in step 8.
   const bool whole = p.whole_tiles != 0;
-  const int share = whole ? p.tiles : p.tiles * group_count;  // >= J
-  const int unit_q = share / J, unit_r = share - unit_q * J;
+  int unit_q = p.share_q, unit_r = p.share_r;  // host-computed for an unsliced K
+  if (S > 1) {
+    const int share = p.tiles * group_count;  // >= J
+    unit_q = share / J;
+    unit_r = share - unit_q * J;
+  }
   const int scale = whole ? group_count : 1;
   const int unit_begin = split_begin(j, unit_q, unit_r) * scale;
   const int unit_end = split_begin(j + 1, unit_q, unit_r) * scale;
@@ -135,11 +148,16 @@ __global__ void __launch_bounds__(512, 1) sage_skinny_kernel(const __grid_consta
       static_cast<size_t>(warps) * params.warp_segments * NB * 512);
 
   // This warp's contiguous share of the CTA's units.
-  const int warp_q = unit_count / warps, warp_r = unit_count - warp_q * warps;
+  // unit_count / warps by multiplication (exact: unit_count * warps < 2^32)
+  const int warp_q = warps == 1 ? unit_count  // (2^32 / 1 + 1 does not fit the reciprocal)
+                                : static_cast<int>(__umulhi(static_cast<unsigned>(unit_count),
+                                                            params.warps_reciprocal));
+  const int warp_r = unit_count - warp_q * warps;
   const int warp_begin = unit_begin + split_begin(warp, warp_q, warp_r);
   const int warp_end = unit_begin + split_begin(warp + 1, warp_q, warp_r);
   const uint32_t bar = smem_address(&barriers[warp]);
 
+  SAGE_STAMP(11);
   // ---- 1. start the weight stream: lane 0 of each warp copies the warp's units
   if (lane == 0) {
     asm volatile("mbarrier.init.shared::cta.b64 [%0], 1;" ::"r"(bar));
@@ -151,12 +169,15 @@ __global__ void __launch_bounds__(512, 1) sage_skinny_kernel(const __grid_consta
       int u = warp_begin;
       while (u < warp_end) {
         // a run of units inside one tile is contiguous in all three arrays; with a single
-        // K slice consecutive tiles are contiguous too
-        const int tile = u / group_count;
-        const int gi = u - tile * group_count;
-        const int run =
-            (group_count == p.groups) ? (warp_end - u) : min(warp_end - u, group_count - gi);
-        const size_t cell = (static_cast<size_t>(tile) * p.groups + group_begin + gi) * 16;
+        // K slice the unit index is the memory order and the whole share is one run
+        int run = warp_end - u;
+        size_t cell = static_cast<size_t>(u) * 16;
+        if (S > 1) {
+          const int tile = u / group_count;
+          const int gi = u - tile * group_count;
+          run = min(run, group_count - gi);
+          cell = (static_cast<size_t>(tile) * p.groups + group_begin + gi) * 16;
+        }
         const uint32_t slot = static_cast<uint32_t>(u - unit_begin);
         bulk_copy(smem_address(codes_shared) + slot * 512u, p.codes + cell * 8, run * 512u, bar);
         bulk_copy(smem_address(radii_shared) + slot * 64u, p.radii + cell, run * 64u, bar);
@@ -168,13 +189,22 @@ __global__ void __launch_bounds__(512, 1) sage_skinny_kernel(const __grid_consta
     }
   }
 
+  SAGE_STAMP(12);
   // ---- 1b. which tiles does this CTA touch, and who else touches them (static
   //          arithmetic, done while the copies fly)
   const int cta_first_tile = unit_count > 0 ? unit_begin / group_count : 0;
   const int cta_tiles = unit_count > 0 ? (unit_end - 1) / group_count - cta_first_tile + 1 : 0;
+  for (int ti = tid; ti < cta_tiles; ti += threads) {
+    // warps whose contiguous shares overlap this tile's units inside the CTA
+    const int tile = cta_first_tile + ti;
+    const int u0 = max(tile * group_count, unit_begin) - unit_begin;
+    const int u1 = min((tile + 1) * group_count, unit_end) - 1 - unit_begin;
+    tile_warp_lo[ti] = static_cast<unsigned char>(split_owner(u0, warp_q, warp_r));
+    tile_warp_hi[ti] = static_cast<unsigned char>(split_owner(u1, warp_q, warp_r));
+  }
   int shared_tile = 0;
-  if (!whole && tid < cta_tiles) {
-    const int tile = cta_first_tile + tid;
+  for (int ti = tid; !whole && ti < cta_tiles; ti += threads) {
+    const int tile = cta_first_tile + ti;
     int total = 0, slot = 0;
     for (int s2 = 0; s2 < S; ++s2) {
       const int gc = p.groups * (s2 + 1) / S - p.groups * s2 / S;
@@ -186,10 +216,10 @@ __global__ void __launch_bounds__(512, 1) sage_skinny_kernel(const __grid_consta
       if (s2 == slice) slot = total + (j - first);
       total += last - first + 1;
     }
-    tile_parts[tid] = total;
-    tile_slot[tid] = slot;
-    tile_last[tid] = 0;
-    shared_tile = total > 1;
+    tile_parts[ti] = total;
+    tile_slot[ti] = slot;
+    tile_last[ti] = 0;
+    shared_tile |= total > 1;
   }
 
   SAGE_STAMP(1);
@@ -212,7 +242,7 @@ __global__ void __launch_bounds__(512, 1) sage_skinny_kernel(const __grid_consta
   const bool linear_gather = p.perm != nullptr && perm_aligned &&
                              static_cast<size_t>(p.rows) * p.k * 2 <= static_cast<size_t>(params.lin_bytes);
   const bool direct_copy = p.perm == nullptr && aligned_x;
-  constexpr int kItemBatch = 8;  // permutation items (4 channels each) held in registers
+  constexpr int kItemBatch = 4;  // permutation items (4 channels each) held in registers
   constexpr int kCopyBatch = 4;  // 16-byte activation pieces held in registers
   int4 held[kItemBatch];
   uint4 piece[kCopyBatch];
@@ -383,7 +413,6 @@ __global__ void __launch_bounds__(512, 1) sage_skinny_kernel(const __grid_consta
     const int m = min(g + 8 * nb, p.rows - 1);
     x_row_base[nb] = reinterpret_cast<const unsigned char *>(x_shared + m * row_stride) + 16 * t;
   }
-  const bool low_bits = p.dbits != 8;
   float acc[NB][4];
 #pragma unroll
   for (int nb = 0; nb < NB; ++nb)
@@ -414,10 +443,7 @@ __global__ void __launch_bounds__(512, 1) sage_skinny_kernel(const __grid_consta
       const unsigned char *x_row[NB];
 #pragma unroll
       for (int nb = 0; nb < NB; ++nb) x_row[nb] = x_row_base[nb] + 256 * gi;
-      if (low_bits)
-        compute_unit<NB, true>(code, radius_word, endpoints, acc, f, book_shared, lane_offset, x_row, t);
-      else
-        compute_unit<NB, false>(code, radius_word, endpoints, acc, f, book_shared, lane_offset, x_row, t);
+      compute_unit<NB, kLowBits>(code, radius_word, endpoints, acc, f, book_shared, lane_offset, x_row, t);
       code_ptr += 512;
       radius_ptr += 64;
       grid_ptr += 64;
@@ -441,39 +467,34 @@ __global__ void __launch_bounds__(512, 1) sage_skinny_kernel(const __grid_consta
   }
   if (lane == 0) {
     warp_first_tile[warp] = first_tile;
-    warp_tile_count[warp] = tile_count;
   }
 
   SAGE_STAMP(6);
   __syncthreads();
 
   SAGE_STAMP(7);
-  // ---- 7. combine the warps (warp order = K order) and write y or the partial
+  // ---- 7. combine the warps (warp order = K order) and write y or the partial.
+  //         Item e = tile * (NB*128) + the accumulator's position [nb][row][column % 8].
   const int columns = p.rows;              // valid MMA columns
-  const int tile_elements = 16 * columns;  // element r = row*columns + column
+  const int tile_elements = 16 * columns;  // scratch element r = row*columns + column
   const int slots = p.slots_per_tile;
-  for (int e = tid; e < cta_tiles * tile_elements; e += threads) {
-    const int ti = e / tile_elements;
-    const int r = e - ti * tile_elements;
-    const int row = r / columns;
-    const int column = r - row * columns;
+  for (int e = tid; e < cta_tiles * kSegmentFloats; e += threads) {
+    const int ti = e / kSegmentFloats;
+    const int position = e - ti * kSegmentFloats;
+    const int row = (position >> 3) & 15;
+    const int column = (position >> 7) * 8 + (position & 7);
+    if (column >= columns) continue;
     const int tile = cta_first_tile + ti;
-    const float *source = partial_shared + (column >> 3) * 128 + row * 8 + (column & 7);
-    float part[kMaxWarps];
-#pragma unroll
-    for (int w = 0; w < kMaxWarps; ++w) {  // independent loads first, ordered sum after
-      const int k = w < warps ? tile - warp_first_tile[w] : -1;
-      const bool valid = k >= 0 && k < (w < warps ? warp_tile_count[w] : 0);
-      part[w] = valid ? source[(static_cast<size_t>(w) * params.warp_segments + k) * kSegmentFloats] : 0.0f;
-    }
     float sum = 0.0f;
-#pragma unroll
-    for (int w = 0; w < kMaxWarps; ++w) sum += part[w];
+    for (int w = tile_warp_lo[ti]; w <= tile_warp_hi[ti]; ++w)
+      sum += partial_shared[(static_cast<size_t>(w) * params.warp_segments + (tile - warp_first_tile[w])) *
+                                kSegmentFloats + position];
     if (whole || tile_parts[ti] == 1) {
       const int out = tile * 16 + row;
       if (out < p.n) p.y[static_cast<size_t>(column) * p.n + out] = __float2half_rn(sum);
     } else {
-      __stcg(p.partial + (static_cast<size_t>(tile) * slots + tile_slot[ti]) * tile_elements + r, sum);
+      __stcg(p.partial + (static_cast<size_t>(tile) * slots + tile_slot[ti]) * tile_elements +
+                 row * columns + column, sum);
     }
   }
   SAGE_STAMP(8);
@@ -484,11 +505,12 @@ __global__ void __launch_bounds__(512, 1) sage_skinny_kernel(const __grid_consta
   //         fence + atomic (release); the same thread's fence after the atomic and the
   //         next barrier order the other CTAs' partials before this CTA's reads (acquire).
   __syncthreads();
-  if (tid < cta_tiles && tile_parts[tid] > 1) {
+  for (int ti = tid; ti < cta_tiles; ti += threads) {
+    if (tile_parts[ti] <= 1) continue;
     __threadfence();
-    const unsigned arrived = atomicAdd(p.counters + cta_first_tile + tid, 1u);
+    const unsigned arrived = atomicAdd(p.counters + cta_first_tile + ti, 1u);
     __threadfence();
-    tile_last[tid] = (arrived == static_cast<unsigned>(tile_parts[tid]) - 1u);
+    tile_last[ti] = (arrived == static_cast<unsigned>(tile_parts[ti]) - 1u);
   }
   __syncthreads();
   SAGE_STAMP(9);
@@ -507,15 +529,16 @@ __global__ void __launch_bounds__(512, 1) sage_skinny_kernel(const __grid_consta
     if (out < p.n) p.y[static_cast<size_t>(column) * p.n + out] = __float2half_rn(sum);
   }
   __syncthreads();
-  if (tid < cta_tiles && tile_last[tid]) p.counters[cta_first_tile + tid] = 0u;
+  for (int ti = tid; ti < cta_tiles; ti += threads)
+    if (tile_last[ti]) p.counters[cta_first_tile + ti] = 0u;
   SAGE_STAMP(10);
 #undef SAGE_STAMP
 }
 
-template <int NB>
+template <int NB, bool kLowBits>
 cudaError_t configure_variant() {
-  return cudaFuncSetAttribute(sage_skinny_kernel<NB>, cudaFuncAttributeMaxDynamicSharedMemorySize,
-                              kMaxDynamicShared);
+  return cudaFuncSetAttribute(sage_skinny_kernel<NB, kLowBits>,
+                              cudaFuncAttributeMaxDynamicSharedMemorySize, kMaxDynamicShared);
 }
 
 size_t x_bytes_for(int rows, int group_span) {
@@ -529,7 +552,8 @@ int slice_groups(int groups, int slices, int slice) {
 
 }  // namespace
 
-SkinnyPlan plan_skinny(int rows, int n, int k, int entries, int sm_count, const Tuning &tuning) {
+SkinnyPlan plan_skinny(int rows, int n, int k, int entries, int sm_count, const Tuning &tuning,
+                       int cta_budget) {
   (void)entries;
   SkinnyPlan plan{};
   const int tiles = (n + 15) / 16;
@@ -539,7 +563,8 @@ SkinnyPlan plan_skinny(int rows, int n, int k, int entries, int sm_count, const 
   plan.ctas_per_sm = tuning.ctas_per_sm > 0 ? tuning.ctas_per_sm : 1;
   plan.warps = tuning.warps > 0 ? tuning.warps : 16;
   if (plan.warps > kMaxWarps) plan.warps = kMaxWarps;
-  const int resident = sm_count * plan.ctas_per_sm;
+  // CTAs this problem may occupy at once: the whole device, or its share of a grouped launch
+  const int resident = cta_budget > 0 ? cta_budget : sm_count * plan.ctas_per_sm;
   const int unit_cap = 160;  // 160 * 640 B = 100 KiB of packed weights per CTA
 
   // K slices: as few as keep one slice's activations within the shared-memory budget
@@ -556,8 +581,8 @@ SkinnyPlan plan_skinny(int rows, int n, int k, int entries, int sm_count, const 
   // kFinishUnits units; whole tiles cost imbalance when tiles are few.  Compare per SM.
   constexpr int kFinishUnits = 50;
   const long long even_cost =
-      (static_cast<long long>(tiles) * groups + sm_count - 1) / sm_count + kFinishUnits;
-  const long long whole_cost = static_cast<long long>((tiles + sm_count - 1) / sm_count) * groups;
+      (static_cast<long long>(tiles) * groups + resident - 1) / resident + kFinishUnits;
+  const long long whole_cost = static_cast<long long>((tiles + resident - 1) / resident) * groups;
   bool whole = slices == 1 && whole_cost <= even_cost;
   if (tuning.mode == 1) whole = false;
   if (tuning.mode == 2 && slices == 1) whole = true;
@@ -627,9 +652,11 @@ SkinnyPlan plan_skinny(int rows, int n, int k, int entries, int sm_count, const 
 }
 
 cudaError_t configure_skinny() {
-  cudaError_t status = configure_variant<1>();
-  if (status != cudaSuccess) return status;
-  return configure_variant<2>();
+  cudaError_t status = configure_variant<1, false>();
+  if (status == cudaSuccess) status = configure_variant<1, true>();
+  if (status == cudaSuccess) status = configure_variant<2, false>();
+  if (status == cudaSuccess) status = configure_variant<2, true>();
+  return status;
 }
 
 cudaError_t launch_skinny(const SkinnyParams &params, int warps, int column_blocks, int total_ctas,
@@ -639,10 +666,15 @@ cudaError_t launch_skinny(const SkinnyParams &params, int warps, int column_bloc
                               params.lin_bytes;
   if (shared_bytes > static_cast<size_t>(kMaxDynamicShared)) return cudaErrorInvalidConfiguration;
   const int threads = warps * 32;
-  if (column_blocks == 1)
-    sage_skinny_kernel<1><<<total_ctas, threads, shared_bytes, stream>>>(params);
-  else
-    sage_skinny_kernel<2><<<total_ctas, threads, shared_bytes, stream>>>(params);
+  bool low_bits = false;
+  for (int i = 0; i < params.count; ++i) low_bits = low_bits || params.problem[i].dbits != 8;
+  if (column_blocks == 1) {
+    if (low_bits) sage_skinny_kernel<1, true><<<total_ctas, threads, shared_bytes, stream>>>(params);
+    else sage_skinny_kernel<1, false><<<total_ctas, threads, shared_bytes, stream>>>(params);
+  } else {
+    if (low_bits) sage_skinny_kernel<2, true><<<total_ctas, threads, shared_bytes, stream>>>(params);
+    else sage_skinny_kernel<2, false><<<total_ctas, threads, shared_bytes, stream>>>(params);
+  }
   return cudaGetLastError();
 }
 

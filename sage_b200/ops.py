@@ -171,7 +171,6 @@ def sage_grouped(problems: list[tuple], out_features: list[int]) -> list[torch.T
     lib = _lib.load()
     array = (_lib.Problem * len(problems))()
     outputs = []
-    total = 0
     device = problems[0][0].device
     for i, ((x, codes, radii, grid, book, perm), n) in enumerate(zip(problems, out_features)):
         k = _check_layout(x, codes, radii, grid, book, perm, n)
@@ -182,9 +181,9 @@ def sage_grouped(problems: list[tuple], out_features: list[int]) -> list[torch.T
             x.data_ptr(), codes.data_ptr(), radii.data_ptr(), grid.data_ptr(), book.data_ptr(),
             perm.data_ptr() if perm.numel() else None, y.data_ptr(), rows, n, k, book.shape[1],
         )
-        total += lib.sageb200_workspace_bytes(rows, n, k) if rows else 0
     with torch.cuda.device(device):
         stream = torch.cuda.current_stream(device).cuda_stream
+        total = lib.sageb200_grouped_workspace_bytes(array, len(problems))
         workspace = _workspace(device, stream, total) if total else None
         _lib.check(
             lib.sageb200_linear_grouped(

@@ -1,0 +1,265 @@
+"""Random-initialised Qwen3 decoder whose linears are SAGE-packed, for decode benchmarks
+and greedy-token parity.
+
+The reference runs packed checkpoints inside Hugging Face `transformers` Qwen3
+(weight_vq/integrations/transformers.py:83-164) and measures them with
+benchmarks/model.py:43-133: StaticCache, one model call per generated token, the token kept
+on the GPU.  This module is the same computation with the model glue written against the
+decode kernels of libsage_b200 (include/sage_b200_decode.h): every step of a decode iteration
+is enqueued on one stream without host synchronisation, so the iteration is captured once in
+a CUDA graph and replayed per token.
+
+`linear="sage"` runs the packed kernels; `linear="dense"` replaces every packed linear by an
+FP16 `torch.nn.functional.linear` on the kernel-dequantised weight (the greedy-token oracle
+the reference uses at tests/inference/test_hf_cuda.py:30-42), everything else identical.
+"""
+
+from __future__ import annotations
+
+import ctypes
+import dataclasses
+import math
+
+import torch
+
+from . import _lib
+from .ops import sage_dequantize, sage_grouped
+from .synthetic import linear_algorithmic_bytes, synthetic_sage_device
+
+
+@dataclasses.dataclass(frozen=True)
+class Qwen3Config:
+    layers: int
+    hidden: int
+    heads: int
+    kv_heads: int
+    intermediate: int
+    vocab: int = 151936
+    head_dim: int = 128
+    eps: float = 1e-6
+    rope_theta: float = 1e6
+    name: str = "qwen3"
+
+
+QWEN3_4B = Qwen3Config(layers=36, hidden=2560, heads=32, kv_heads=8, intermediate=9728, name="Qwen3-4B")
+QWEN3_32B = Qwen3Config(layers=64, hidden=5120, heads=64, kv_heads=8, intermediate=25600, name="Qwen3-32B")
+
+
+def _vp(tensor: torch.Tensor | None):
+    return ctypes.c_void_p(tensor.data_ptr()) if tensor is not None else None
+
+
+class PackedLinear:
+    """One packed linear's buffers (and, for the oracle, its dense FP16 weight)."""
+
+    def __init__(self, k: int, n: int, seed: int, device, dense: bool):
+        self.k, self.n = k, n
+        packed = synthetic_sage_device(k, n, seed, device, permuted=True)
+        self.entries = packed["codebook"].shape[1]
+        self.bytes = linear_algorithmic_bytes(1, n, k, self.entries, True)
+        if dense:
+            self.weight = sage_dequantize(
+                packed["packed_codes"], packed["radius_codes"], packed["radius_grid"],
+                packed["codebook"], packed["permutation"], n,
+            )
+            self.packed = None
+        else:
+            self.weight = None
+            self.packed = packed
+
+    def problem(self, x: torch.Tensor):
+        p = self.packed
+        return (x, p["packed_codes"], p["radius_codes"], p["radius_grid"], p["codebook"], p["permutation"])
+
+
+class PackedQwen3:
+    """Batch-`batch` greedy decoder with a static KV cache of `max_seq` positions."""
+
+    def __init__(self, config: Qwen3Config, device, *, seed: int = 0, max_seq: int = 2560,
+                 batch: int = 1, linear: str = "sage", max_new: int = 512):
+        if linear not in ("sage", "dense"):
+            raise ValueError("linear must be 'sage' or 'dense'")
+        if batch < 1 or batch > 16:
+            raise ValueError("batch must be 1..16")
+        self.config, self.device, self.batch, self.max_seq = config, torch.device(device), batch, max_seq
+        self.dense = linear == "dense"
+        self.lib = _lib.load()
+        self.sm_count = torch.cuda.get_device_properties(self.device).multi_processor_count
+        c = config
+        gen = torch.Generator(device=self.device).manual_seed(seed)
+        half = dict(device=self.device, dtype=torch.float16)
+        self.embed = (torch.randn(c.vocab, c.hidden, generator=gen, device=self.device) * 0.02).half()
+        self.lm_head = self.embed  # tied, as in Qwen3-4B
+        def norm_weight(width):  # random-init norms (around one) so the tests exercise them
+            return (1.0 + 0.1 * torch.randn(width, generator=gen, device=self.device)).half()
+
+        self.final_norm = norm_weight(c.hidden)
+        self.layers = []
+        q_out, kv_out = c.heads * c.head_dim, c.kv_heads * c.head_dim
+        shapes = [("q", c.hidden, q_out), ("k", c.hidden, kv_out), ("v", c.hidden, kv_out),
+                  ("o", q_out, c.hidden), ("gate", c.hidden, c.intermediate),
+                  ("up", c.hidden, c.intermediate), ("down", c.intermediate, c.hidden)]
+        index = 0
+        self.packed_bytes = 0
+        for _ in range(c.layers):
+            layer = {}
+            for name, k, n in shapes:
+                layer[name] = PackedLinear(k, n, seed * 100003 + index, self.device, self.dense)
+                self.packed_bytes += layer[name].bytes
+                index += 1
+            layer["input_norm"] = norm_weight(c.hidden)
+            layer["post_norm"] = norm_weight(c.hidden)
+            layer["q_norm"] = norm_weight(c.head_dim)
+            layer["k_norm"] = norm_weight(c.head_dim)
+            layer["k_cache"] = torch.zeros(batch, c.kv_heads, max_seq, c.head_dim, **half)
+            layer["v_cache"] = torch.zeros(batch, c.kv_heads, max_seq, c.head_dim, **half)
+            self.layers.append(layer)
+        # rotary tables, computed in FP32 and rounded to FP16 as the HF module does
+        inv_freq = 1.0 / (c.rope_theta ** (torch.arange(0, c.head_dim, 2, device=self.device).float() / c.head_dim))
+        angles = torch.arange(max_seq, device=self.device).float()[:, None] * inv_freq[None, :]
+        self.cos, self.sin = angles.cos().half().contiguous(), angles.sin().half().contiguous()
+        # state
+        self.tokens = torch.zeros(batch, dtype=torch.int64, device=self.device)
+        self.positions = torch.zeros(batch, dtype=torch.int32, device=self.device)
+        self.step_counter = torch.zeros(1, dtype=torch.int32, device=self.device)
+        self.log = torch.zeros(batch, max_new, dtype=torch.int64, device=self.device)
+        self.max_new = max_new
+        self.h = torch.zeros(batch, c.hidden, **half)
+        self.x = torch.zeros(batch, c.hidden, **half)
+        self.attn = torch.zeros(batch, q_out, **half)
+        self.act = torch.zeros(batch, c.intermediate, **half)
+        self.logits = torch.zeros(batch, c.vocab, **half)
+        self.splits = 16
+        scratch = self.lib.sageb200_glue_attention_scratch_bytes(batch, c.heads, self.splits)
+        self.attn_scratch = torch.zeros(scratch // 4, dtype=torch.float32, device=self.device)
+        self.graph = None
+        self.graph_no_head = None
+
+    # ------------------------------------------------------------------ pieces
+
+    def _stream(self):
+        return ctypes.c_void_p(torch.cuda.current_stream(self.device).cuda_stream)
+
+    def _check(self, status: int, what: str):
+        if status:
+            raise RuntimeError(f"sage_b200 decode glue: {what} failed with status {status}")
+
+    def _linears(self, layer, names, x):
+        if self.dense:
+            return [torch.nn.functional.linear(x, layer[name].weight) for name in names]
+        return sage_grouped([layer[name].problem(x) for name in names], [layer[name].n for name in names])
+
+    def _layer(self, layer, delta):
+        """One decoder layer; `delta` is the previous layer's MLP output still to be added to
+        the residual stream (None for the first layer).  Returns this layer's MLP output."""
+        c, lib, b = self.config, self.lib, self.batch
+        s = self._stream()
+        self._check(lib.sageb200_glue_add_rmsnorm(_vp(self.h), _vp(delta), _vp(layer["input_norm"]),
+                                                  _vp(self.x), b, c.hidden, c.eps, s), "add_rmsnorm")
+        q, k, v = self._linears(layer, ("q", "k", "v"), self.x)
+        self._check(lib.sageb200_glue_qk_norm_rope_cache(
+            _vp(q), _vp(k), _vp(v), _vp(layer["q_norm"]), _vp(layer["k_norm"]), _vp(self.cos),
+            _vp(self.sin), _vp(self.positions), _vp(layer["k_cache"]), _vp(layer["v_cache"]), b,
+            c.heads, c.kv_heads, c.head_dim, self.max_seq, c.eps, s), "qk_norm_rope_cache")
+        self._check(lib.sageb200_glue_attention_decode(
+            _vp(q), _vp(layer["k_cache"]), _vp(layer["v_cache"]), _vp(self.positions), _vp(self.attn),
+            _vp(self.attn_scratch), b, c.heads, c.kv_heads, c.head_dim, self.max_seq, self.splits, s),
+            "attention_decode")
+        (o,) = self._linears(layer, ("o",), self.attn)
+        self._check(lib.sageb200_glue_add_rmsnorm(_vp(self.h), _vp(o), _vp(layer["post_norm"]),
+                                                  _vp(self.x), b, c.hidden, c.eps, s), "add_rmsnorm")
+        gate, up = self._linears(layer, ("gate", "up"), self.x)
+        self._check(lib.sageb200_glue_swiglu(_vp(gate), _vp(up), _vp(self.act), gate.numel(), s), "swiglu")
+        (down,) = self._linears(layer, ("down",), self.act)
+        return down
+
+    def _body(self):
+        c, lib, b = self.config, self.lib, self.batch
+        s = self._stream()
+        self._check(lib.sageb200_glue_embed(_vp(self.embed), _vp(self.tokens), _vp(self.h), b, c.hidden, s), "embed")
+        delta = None
+        for layer in self.layers:
+            delta = self._layer(layer, delta)
+        return delta
+
+    def step(self, head: bool = True):
+        """Enqueue one decode iteration for the tokens in `self.tokens` at `self.positions`."""
+        c, lib, b = self.config, self.lib, self.batch
+        delta = self._body()
+        s = self._stream()
+        if not head:
+            self.positions.add_(1)
+            return
+        self._check(lib.sageb200_glue_add_rmsnorm(_vp(self.h), _vp(delta), _vp(self.final_norm),
+                                                  _vp(self.x), b, c.hidden, c.eps, s), "final norm")
+        if self.dense:
+            torch.matmul(self.x, self.lm_head.T, out=self.logits)
+        else:
+            self._check(lib.sageb200_glue_lm_head(_vp(self.lm_head), _vp(self.x), _vp(self.logits), b,
+                                                  c.vocab, c.hidden, self.sm_count, s), "lm_head")
+        self._check(lib.sageb200_glue_argmax_advance(_vp(self.logits), _vp(self.tokens), _vp(self.positions),
+                                                     _vp(self.log), _vp(self.step_counter), b, c.vocab,
+                                                     self.max_new, s), "argmax")
+
+    # ------------------------------------------------------------------ graphs and drivers
+
+    def capture(self):
+        """Capture the decode iteration (with and without the lm_head) in CUDA graphs.
+
+        Warm-up and capture run on one stream owned by the model, so everything that is
+        cached per stream (this library's scratch, cuBLAS workspaces of the dense oracle) is
+        allocated by the eager warm-up and not inside a graph's private memory pool, which
+        would go away with the graph while the cache still points at it."""
+        saved = (self.tokens.clone(), self.positions.clone(), self.step_counter.clone(), self.log.clone())
+        stream = torch.cuda.Stream(device=self.device)
+        stream.wait_stream(torch.cuda.current_stream(self.device))
+        with torch.cuda.stream(stream):
+            self.step(head=True)
+            self.step(head=False)
+        torch.cuda.current_stream(self.device).wait_stream(stream)
+        torch.cuda.synchronize(self.device)
+        self.graph, self.graph_no_head = torch.cuda.CUDAGraph(), torch.cuda.CUDAGraph()
+        launches = self.lib.sageb200_launch_count()
+        with torch.cuda.graph(self.graph, stream=stream):
+            self.step(head=True)
+        self.sage_launches_per_step = self.lib.sageb200_launch_count() - launches
+        with torch.cuda.graph(self.graph_no_head, stream=stream):
+            self.step(head=False)
+        self.tokens.copy_(saved[0])
+        self.positions.copy_(saved[1])
+        self.step_counter.copy_(saved[2])
+        self.log.copy_(saved[3])
+        torch.cuda.synchronize(self.device)
+
+    def reset(self):
+        self.positions.zero_()
+        self.step_counter.zero_()
+        self.log.zero_()
+
+    def prefill(self, prompt: torch.Tensor):
+        """Feed `prompt` [batch, length] through the cache one position at a time (the same
+        kernels as decoding); after it, `self.tokens` holds the first generated token."""
+        if self.graph is None:
+            self.capture()
+        self.reset()
+        prompt = prompt.to(self.device)
+        length = prompt.shape[1]
+        for i in range(length):
+            self.tokens.copy_(prompt[:, i])
+            (self.graph if i == length - 1 else self.graph_no_head).replay()
+
+    def generate(self, prompt: torch.Tensor, new_tokens: int) -> torch.Tensor:
+        """Greedy generation; returns [batch, new_tokens] token ids (device tensor)."""
+        if new_tokens > self.max_new:
+            raise ValueError("new_tokens exceeds max_new")
+        self.prefill(prompt)  # logs token 0
+        for _ in range(new_tokens - 1):
+            self.graph.replay()
+        return self.log[:, :new_tokens].clone()
+
+    def bytes_per_token(self, context: int) -> int:
+        """Algorithmic HBM bytes of one decode iteration at batch 1: packed linears, FP16
+        lm_head, KV cache read for `context` positions."""
+        c = self.config
+        kv = 2 * c.layers * c.kv_heads * c.head_dim * 2 * context
+        return self.packed_bytes + c.vocab * c.hidden * 2 + kv

@@ -18,8 +18,8 @@ def lib():
     return _lib.load()
 
 
-def declared_symbols():
-    text = (ROOT / "include" / "sage_b200.h").read_text()
+def declared_symbols(header="sage_b200.h"):
+    text = (ROOT / "include" / header).read_text()
     text = re.sub(r"/\*.*?\*/", "", text, flags=re.S)
     return sorted(set(re.findall(r"\b(sageb200_[a-z0-9_]+)\s*\(", text)))
 
@@ -32,6 +32,13 @@ def test_every_declared_symbol_is_exported(lib):
     assert set(names) == set(_lib.EXPORTED) | {n for n in names if n not in _lib.EXPORTED}
     for name in _lib.EXPORTED:
         assert name in names, f"{name} bound in Python but not declared in the header"
+
+
+def test_decode_header_symbols_are_exported(lib):
+    names = declared_symbols("sage_b200_decode.h")
+    assert set(names) == set(_lib.EXPORTED_DECODE)
+    for name in names:
+        assert hasattr(lib, name), name
 
 
 def test_version_and_status_strings(lib):
