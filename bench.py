@@ -308,8 +308,11 @@ def run_model(args) -> None:
         barrier()
         elapsed_ms = start.elapsed_time(stop)
         if elapsed_ms < 500:  # keep the GPU busy long enough for a few clock samples
+            hold = model.positions.clone()
             for _ in range(int(500 / max(elapsed_ms / args.steps, 1e-3))):
+                model.positions.copy_(hold)  # stay inside the KV cache
                 model.graph_no_head.replay()
+            model.positions.copy_(hold)
             torch.cuda.synchronize()
     clocks = sampler.summary()
     context = prompt_length + warmup + args.steps // 2

@@ -99,6 +99,7 @@ __global__ void qk_norm_rope_cache_kernel(__half *__restrict__ q, const __half *
   const int heads = q_heads + 2 * kv_heads;
   if (head >= heads) return;
   const int position = positions[m];
+  if (position < 0 || position >= max_seq) return;  // a full cache: write nothing out of range
   if (head >= q_heads + kv_heads) {  // value head: plain copy into the cache
     const int j = head - q_heads - kv_heads;
     const uint2 value = reinterpret_cast<const uint2 *>(v + (static_cast<size_t>(m) * kv_heads + j) * 128)[lane];
@@ -148,7 +149,7 @@ __global__ void __launch_bounds__(kAttnWarps * 32)
   const int split = blockIdx.x, kv = blockIdx.y, m = blockIdx.z;
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
   const int group = q_heads / kv_heads;
-  const int context = positions[m] + 1;
+  const int context = min(positions[m] + 1, max_seq);
   const int chunk = (context + splits - 1) / splits;
   const int begin = split * chunk;
   const int end = min(context, begin + chunk);
