@@ -1,7 +1,7 @@
 """Benchmark of the SAGE packed-weight decode path on B200.
 
     python bench.py [--gpus N] [--steps K] [--warmup W] [--impl ours|reference]
-                    [--workload decode_model|decode_linears|linear:K:N:M] [--prompt P]
+                    [--workload decode_model|decode_linears|tp32b|linear:K:N:M] [--prompt P]
 
 A step is one decoded token of the full Qwen3-4B architecture at batch 1 (synthetic seeded
 packed weights, ABS split cycling 6/7/8 direction bits per matrix; `decode_linears` times the
@@ -441,6 +441,88 @@ def run_model(args) -> None:
         dist.destroy_process_group()
 
 
+def run_tp(args) -> None:
+    """`--workload tp32b`: Qwen3-32B shape, SAGE-packed, batch-1 decode with the linears
+    tensor-parallel over all ranks (q/k/v/gate/up column-parallel, o/down row-parallel +
+    NCCL all-reduce, vocabulary-parallel lm_head + all-gather).  One sequence for the whole
+    job, so `scaling` is "strong"."""
+    import torch
+    import torch.distributed as dist
+
+    from sage_b200.qwen3 import QWEN3_32B, PackedQwen3
+
+    rank = int(os.environ.get("RANK", "0"))
+    world = int(os.environ.get("WORLD_SIZE", "1"))
+    local = int(os.environ.get("LOCAL_RANK", "0"))
+    torch.cuda.set_device(local)
+    device = torch.device("cuda", local)
+    group = None
+    if world > 1:
+        dist.init_process_group("nccl", device_id=device)
+        group = dist.group.WORLD
+    warmup = max(args.warmup, 3)
+    prompt_length = min(args.prompt, 64)
+    model = PackedQwen3(QWEN3_32B, device, seed=0, max_seq=prompt_length + 2 * (args.steps + warmup) + 16,
+                        batch=1, max_new=2 * (args.steps + warmup) + 16, tp_group=group, perm_blocks=8)
+    model.capture()
+    prompt = torch.randint(3, QWEN3_32B.vocab, (1, prompt_length), generator=torch.Generator().manual_seed(7))
+    model.prefill(prompt)
+
+    def barrier():
+        if world > 1:
+            dist.barrier()
+        torch.cuda.synchronize()
+
+    for _ in range(warmup):
+        model.graph.replay()
+    start, stop = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    barrier()
+    with ClockSampler(local) as sampler:
+        start.record()
+        for _ in range(args.steps):
+            model.graph.replay()
+        stop.record()
+        barrier()
+    clocks = sampler.summary()
+    times = torch.tensor([start.elapsed_time(stop)], dtype=torch.float64, device=device)
+    if world > 1:
+        dist.all_reduce(times, op=dist.ReduceOp.MAX)
+    tokens = model.log[0, : warmup + args.steps + 1].tolist()
+    if rank == 0:
+        ms_per_step = float(times[0]) / args.steps
+        peak, peak_kind = measured_peaks()
+        step_bytes = model.bytes_per_token(prompt_length + warmup + args.steps // 2)
+        line = {
+            "metric": "qwen3_32b_sage_2.25bpw_batch1_decode_tok_s",
+            "value": 1000.0 / ms_per_step,
+            "unit": UNIT,
+            "n_gpus": world,
+            "steps": args.steps,
+            "warmup": warmup,
+            "ms_per_step": ms_per_step,
+            "higher_is_better": True,
+            "scaling": "strong",
+            "vs_baseline": None,
+            "dtype": "f16 products, f32 accumulate",
+            "data": "synthetic",
+            "config": {
+                "workload": "Qwen3-32B shape (64 layers, hidden 5120, 64/8 heads, inter 25600), random-init, "
+                            "SAGE-packed, batch 1 greedy decode, tensor parallel",
+                "parallelism": f"tp{world}",
+                "row_parallel_permutation": "block permutation, 8 blocks (each rank gathers inside its slice)",
+                "per_rank_hbm_bytes_per_step": step_bytes,
+                "per_rank_hbm_gbs": step_bytes / (ms_per_step / 1000.0) / 1e9,
+                "hbm_frac": step_bytes / (ms_per_step / 1000.0) / 1e9 / peak,
+                "peak_kind": f"of {peak_kind}",
+                "first_tokens": tokens[:8],
+            },
+            "clocks": clocks,
+        }
+        print(json.dumps(line), flush=True)
+    if world > 1:
+        dist.destroy_process_group()
+
+
 def run_ours(args) -> None:
     import torch
     import torch.distributed as dist
@@ -614,6 +696,8 @@ def main() -> None:
         run_single_linear(args)
     elif args.workload == "decode_model":
         run_model(args)
+    elif args.workload == "tp32b":
+        run_tp(args)
     else:
         run_ours(args)
 

@@ -42,7 +42,7 @@ constexpr int kBookBytes = 256 * 8 * 16;  // 256 entries x 8 replicas x 16 bytes
 constexpr unsigned long long kWaitLimitNs = 2000000000ull;
 constexpr int kMaxWarps = 16;
 constexpr int kMaxCtaTiles = 64;      // tiles of one CTA when tiles are shared between CTAs
-constexpr int kMaxWholeTiles = 192;   // tiles of one CTA in any mode (unit capacity / 1 group)
+constexpr int kMaxWholeTiles = 192;   // tiles of one CTA in any mode (unit capacity 192 / 1 group)
 constexpr int kMaxSlices = 8;
 constexpr int kUnitBytes = 640;           // 512 codes + 64 radius words + 64 grid
 constexpr int kMaxDynamicShared = 184 * 1024;  // plus ~37 KiB static stays under the 227 KiB limit
@@ -565,7 +565,7 @@ SkinnyPlan plan_skinny(int rows, int n, int k, int entries, int sm_count, const 
   if (plan.warps > kMaxWarps) plan.warps = kMaxWarps;
   // CTAs this problem may occupy at once: the whole device, or its share of a grouped launch
   const int resident = cta_budget > 0 ? cta_budget : sm_count * plan.ctas_per_sm;
-  const int unit_cap = 160;  // 160 * 640 B = 100 KiB of packed weights per CTA
+  const int unit_cap = 192;  // 192 * 640 B = 120 KiB of packed weights per CTA
 
   // K slices: as few as keep one slice's activations within the shared-memory budget
   const size_t x_budget = 40 * 1024;
@@ -588,9 +588,8 @@ SkinnyPlan plan_skinny(int rows, int n, int k, int entries, int sm_count, const 
   if (tuning.mode == 2 && slices == 1) whole = true;
   if (whole) {
     long long ctas = resident < tiles ? resident : tiles;
-    // a CTA's tiles must fit its shared-memory budget
-    while (((tiles + ctas - 1) / ctas) * groups > unit_cap && ctas < tiles) ++ctas;
-    if (((tiles + ctas - 1) / ctas) * groups > unit_cap) whole = false;  // one tile is too long
+    // a CTA's tiles must fit its shared-memory budget without going past one resident wave
+    if (((tiles + ctas - 1) / ctas) * groups > unit_cap) whole = false;
     if (whole) {
       plan.whole_tiles = 1;
       plan.slices = 1;
@@ -603,6 +602,10 @@ SkinnyPlan plan_skinny(int rows, int n, int k, int entries, int sm_count, const 
       plan.x_bytes = x_bytes_for(rows, groups);
       plan.needs_scratch = false;
       plan.partial_bytes = 0;
+      const size_t lin = rows == 1 ? (static_cast<size_t>(k) * 2 + 127) / 128 * 128 : 0;
+      const size_t shared = plan.x_bytes + static_cast<size_t>(plan.unit_capacity) * kUnitBytes +
+                            static_cast<size_t>(plan.warps) * plan.warp_segments * plan.column_blocks * 512 + lin;
+      if (shared > static_cast<size_t>(kMaxDynamicShared)) whole = false;
     }
   }
   if (!whole) {
@@ -624,11 +627,20 @@ SkinnyPlan plan_skinny(int rows, int n, int k, int entries, int sm_count, const 
     const int tile_cap = kMaxCtaTiles - 2;
     while ((max_units + per_slice - 1) / per_slice / min_groups + 2 > tile_cap) ++per_slice;
     if (per_slice > min_units) per_slice = min_units;
+    const size_t fixed = x_bytes_for(rows, max_groups) +
+                         (rows == 1 ? (static_cast<size_t>(k) * 2 + 127) / 128 * 128 : 0);
+    while (true) {  // more (smaller) CTAs until one CTA's units fit shared memory
+      plan.unit_capacity = static_cast<int>((max_units + per_slice - 1) / per_slice);
+      const int warp_units = (plan.unit_capacity + plan.warps - 1) / plan.warps;
+      plan.warp_segments = warp_units / min_groups + 2;
+      const size_t shared = fixed + static_cast<size_t>(plan.unit_capacity) * kUnitBytes +
+                            static_cast<size_t>(plan.warps) * plan.warp_segments * plan.column_blocks * 512;
+      if (shared <= static_cast<size_t>(kMaxDynamicShared) || per_slice >= min_units) break;
+      per_slice += (per_slice + 3) / 4;
+      if (per_slice > min_units) per_slice = min_units;
+    }
     plan.ctas_per_slice = static_cast<int>(per_slice);
     plan.ctas = plan.ctas_per_slice * slices;
-    plan.unit_capacity = static_cast<int>((max_units + per_slice - 1) / per_slice);
-    const int warp_units = (plan.unit_capacity + plan.warps - 1) / plan.warps;
-    plan.warp_segments = warp_units / min_groups + 2;
     // pieces per tile: in each slice a tile's units span at most `parts` CTAs
     const long long least = min_units / per_slice;  // units in the smallest CTA range, >= 1
     const int parts = static_cast<int>((max_groups + least - 1) / least) + 1;

@@ -24,6 +24,7 @@ import torch
 
 from . import _lib
 from .ops import sage_dequantize, sage_grouped
+from .parallel import block_permutation, shard_columns, shard_rows, shard_vocab
 from .synthetic import linear_algorithmic_bytes, synthetic_sage_device
 
 
@@ -50,11 +51,21 @@ def _vp(tensor: torch.Tensor | None):
 
 
 class PackedLinear:
-    """One packed linear's buffers (and, for the oracle, its dense FP16 weight)."""
+    """One packed linear's buffers (and, for the oracle, its dense FP16 weight), optionally
+    this rank's column- or row-parallel shard of it."""
 
-    def __init__(self, k: int, n: int, seed: int, device, dense: bool):
-        self.k, self.n = k, n
+    def __init__(self, k: int, n: int, seed: int, device, dense: bool, *, kind: str | None = None,
+                 rank: int = 0, world: int = 1, perm_blocks: int = 1):
         packed = synthetic_sage_device(k, n, seed, device, permuted=True)
+        if kind == "row" and perm_blocks > 1:
+            # row-parallel linears gather inside each rank's slice of the activations
+            packed["permutation"] = block_permutation(k, perm_blocks, seed, device)
+        if world > 1 and kind == "col":
+            packed, n = shard_columns(packed, n, rank, world)
+        elif world > 1 and kind == "row":
+            packed = shard_rows(packed, rank, world)
+            k //= world
+        self.k, self.n = k, n
         self.entries = packed["codebook"].shape[1]
         self.bytes = linear_algorithmic_bytes(1, n, k, self.entries, True)
         if dense:
@@ -76,43 +87,63 @@ class PackedQwen3:
     """Batch-`batch` greedy decoder with a static KV cache of `max_seq` positions."""
 
     def __init__(self, config: Qwen3Config, device, *, seed: int = 0, max_seq: int = 2560,
-                 batch: int = 1, linear: str = "sage", max_new: int = 512):
+                 batch: int = 1, linear: str = "sage", max_new: int = 512, tp_group=None,
+                 perm_blocks: int = 1):
+        """`tp_group`: a torch.distributed process group for tensor parallelism (q/k/v/gate/up
+        column-parallel, o/down row-parallel with an all-reduce, vocabulary-parallel lm_head
+        with an all-gather); every rank must pass the same seed.  `perm_blocks`: o/down use
+        a block permutation with this many blocks (a multiple of the group size)."""
         if linear not in ("sage", "dense"):
             raise ValueError("linear must be 'sage' or 'dense'")
         if batch < 1 or batch > 16:
             raise ValueError("batch must be 1..16")
         self.config, self.device, self.batch, self.max_seq = config, torch.device(device), batch, max_seq
         self.dense = linear == "dense"
+        self.tp_group = tp_group
+        if tp_group is not None:
+            import torch.distributed as dist
+
+            self.tp_world, self.tp_rank = dist.get_world_size(tp_group), dist.get_rank(tp_group)
+        else:
+            self.tp_world, self.tp_rank = 1, 0
+        world, rank = self.tp_world, self.tp_rank
+        if config.heads % world or config.kv_heads % world or config.intermediate % (128 * world) or config.vocab % world:
+            raise ValueError("heads, kv heads, intermediate/128 and vocabulary must divide by the TP size")
+        if world > 1 and perm_blocks % world:
+            raise ValueError("perm_blocks must be a multiple of the TP size")
+        self.heads, self.kv_heads = config.heads // world, config.kv_heads // world
         self.lib = _lib.load()
         self.sm_count = torch.cuda.get_device_properties(self.device).multi_processor_count
         c = config
         gen = torch.Generator(device=self.device).manual_seed(seed)
         half = dict(device=self.device, dtype=torch.float16)
         self.embed = (torch.randn(c.vocab, c.hidden, generator=gen, device=self.device) * 0.02).half()
-        self.lm_head = self.embed  # tied, as in Qwen3-4B
+        # tied head, as in Qwen3-4B; under TP each rank keeps V/world rows of it
+        self.lm_head = self.embed if world == 1 else shard_vocab(self.embed, rank, world)
         def norm_weight(width):  # random-init norms (around one) so the tests exercise them
             return (1.0 + 0.1 * torch.randn(width, generator=gen, device=self.device)).half()
 
         self.final_norm = norm_weight(c.hidden)
         self.layers = []
         q_out, kv_out = c.heads * c.head_dim, c.kv_heads * c.head_dim
-        shapes = [("q", c.hidden, q_out), ("k", c.hidden, kv_out), ("v", c.hidden, kv_out),
-                  ("o", q_out, c.hidden), ("gate", c.hidden, c.intermediate),
-                  ("up", c.hidden, c.intermediate), ("down", c.intermediate, c.hidden)]
+        shapes = [("q", c.hidden, q_out, "col"), ("k", c.hidden, kv_out, "col"), ("v", c.hidden, kv_out, "col"),
+                  ("o", q_out, c.hidden, "row"), ("gate", c.hidden, c.intermediate, "col"),
+                  ("up", c.hidden, c.intermediate, "col"), ("down", c.intermediate, c.hidden, "row")]
         index = 0
         self.packed_bytes = 0
         for _ in range(c.layers):
             layer = {}
-            for name, k, n in shapes:
-                layer[name] = PackedLinear(k, n, seed * 100003 + index, self.device, self.dense)
+            for name, k, n, kind in shapes:
+                layer[name] = PackedLinear(k, n, seed * 100003 + index, self.device, self.dense, kind=kind,
+                                           rank=rank, world=world, perm_blocks=perm_blocks)
                 self.packed_bytes += layer[name].bytes
                 index += 1
             layer["input_norm"] = norm_weight(c.hidden)
             layer["post_norm"] = norm_weight(c.hidden)
             layer["q_norm"] = norm_weight(c.head_dim)
             layer["k_norm"] = norm_weight(c.head_dim)
-            layer["k_cache"] = torch.zeros(batch, c.kv_heads, max_seq, c.head_dim, **half)
-            layer["v_cache"] = torch.zeros(batch, c.kv_heads, max_seq, c.head_dim, **half)
+            layer["k_cache"] = torch.zeros(batch, self.kv_heads, max_seq, c.head_dim, **half)
+            layer["v_cache"] = torch.zeros(batch, self.kv_heads, max_seq, c.head_dim, **half)
             self.layers.append(layer)
         # rotary tables, computed in FP32 and rounded to FP16 as the HF module does
         inv_freq = 1.0 / (c.rope_theta ** (torch.arange(0, c.head_dim, 2, device=self.device).float() / c.head_dim))
@@ -126,11 +157,13 @@ class PackedQwen3:
         self.max_new = max_new
         self.h = torch.zeros(batch, c.hidden, **half)
         self.x = torch.zeros(batch, c.hidden, **half)
-        self.attn = torch.zeros(batch, q_out, **half)
-        self.act = torch.zeros(batch, c.intermediate, **half)
+        self.attn = torch.zeros(batch, q_out // world, **half)
+        self.act = torch.zeros(batch, c.intermediate // world, **half)
         self.logits = torch.zeros(batch, c.vocab, **half)
+        self.local_logits = torch.zeros(batch, c.vocab // world, **half) if world > 1 else self.logits
+        self.gathered_logits = torch.zeros(world, batch, c.vocab // world, **half) if world > 1 else None
         self.splits = 16
-        scratch = self.lib.sageb200_glue_attention_scratch_bytes(batch, c.heads, self.splits)
+        scratch = self.lib.sageb200_glue_attention_scratch_bytes(batch, self.heads, self.splits)
         self.attn_scratch = torch.zeros(scratch // 4, dtype=torch.float32, device=self.device)
         self.graph = None
         self.graph_no_head = None
@@ -149,6 +182,13 @@ class PackedQwen3:
             return [torch.nn.functional.linear(x, layer[name].weight) for name in names]
         return sage_grouped([layer[name].problem(x) for name in names], [layer[name].n for name in names])
 
+    def _all_reduce(self, tensor):
+        """Sum the row-parallel partial outputs over the tensor-parallel group (NCCL)."""
+        if self.tp_world > 1:
+            import torch.distributed as dist
+
+            dist.all_reduce(tensor, group=self.tp_group)
+
     def _layer(self, layer, delta):
         """One decoder layer; `delta` is the previous layer's MLP output still to be added to
         the residual stream (None for the first layer).  Returns this layer's MLP output."""
@@ -160,17 +200,19 @@ class PackedQwen3:
         self._check(lib.sageb200_glue_qk_norm_rope_cache(
             _vp(q), _vp(k), _vp(v), _vp(layer["q_norm"]), _vp(layer["k_norm"]), _vp(self.cos),
             _vp(self.sin), _vp(self.positions), _vp(layer["k_cache"]), _vp(layer["v_cache"]), b,
-            c.heads, c.kv_heads, c.head_dim, self.max_seq, c.eps, s), "qk_norm_rope_cache")
+            self.heads, self.kv_heads, c.head_dim, self.max_seq, c.eps, s), "qk_norm_rope_cache")
         self._check(lib.sageb200_glue_attention_decode(
             _vp(q), _vp(layer["k_cache"]), _vp(layer["v_cache"]), _vp(self.positions), _vp(self.attn),
-            _vp(self.attn_scratch), b, c.heads, c.kv_heads, c.head_dim, self.max_seq, self.splits, s),
+            _vp(self.attn_scratch), b, self.heads, self.kv_heads, c.head_dim, self.max_seq, self.splits, s),
             "attention_decode")
         (o,) = self._linears(layer, ("o",), self.attn)
+        self._all_reduce(o)
         self._check(lib.sageb200_glue_add_rmsnorm(_vp(self.h), _vp(o), _vp(layer["post_norm"]),
                                                   _vp(self.x), b, c.hidden, c.eps, s), "add_rmsnorm")
         gate, up = self._linears(layer, ("gate", "up"), self.x)
         self._check(lib.sageb200_glue_swiglu(_vp(gate), _vp(up), _vp(self.act), gate.numel(), s), "swiglu")
         (down,) = self._linears(layer, ("down",), self.act)
+        self._all_reduce(down)
         return down
 
     def _body(self):
@@ -192,11 +234,17 @@ class PackedQwen3:
             return
         self._check(lib.sageb200_glue_add_rmsnorm(_vp(self.h), _vp(delta), _vp(self.final_norm),
                                                   _vp(self.x), b, c.hidden, c.eps, s), "final norm")
+        local_vocab = c.vocab // self.tp_world
         if self.dense:
-            torch.matmul(self.x, self.lm_head.T, out=self.logits)
+            torch.matmul(self.x, self.lm_head.T, out=self.local_logits)
         else:
-            self._check(lib.sageb200_glue_lm_head(_vp(self.lm_head), _vp(self.x), _vp(self.logits), b,
-                                                  c.vocab, c.hidden, self.sm_count, s), "lm_head")
+            self._check(lib.sageb200_glue_lm_head(_vp(self.lm_head), _vp(self.x), _vp(self.local_logits), b,
+                                                  local_vocab, c.hidden, self.sm_count, s), "lm_head")
+        if self.tp_world > 1:
+            import torch.distributed as dist
+
+            dist.all_gather_into_tensor(self.gathered_logits, self.local_logits, group=self.tp_group)
+            self.logits.view(b, self.tp_world, local_vocab).copy_(self.gathered_logits.permute(1, 0, 2))
         self._check(lib.sageb200_glue_argmax_advance(_vp(self.logits), _vp(self.tokens), _vp(self.positions),
                                                      _vp(self.log), _vp(self.step_counter), b, c.vocab,
                                                      self.max_new, s), "argmax")
@@ -261,5 +309,5 @@ class PackedQwen3:
         """Algorithmic HBM bytes of one decode iteration at batch 1: packed linears, FP16
         lm_head, KV cache read for `context` positions."""
         c = self.config
-        kv = 2 * c.layers * c.kv_heads * c.head_dim * 2 * context
-        return self.packed_bytes + c.vocab * c.hidden * 2 + kv
+        kv = 2 * c.layers * self.kv_heads * c.head_dim * 2 * context
+        return self.packed_bytes + (c.vocab // self.tp_world) * c.hidden * 2 + kv
