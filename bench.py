@@ -456,10 +456,14 @@ def run_tp(args) -> None:
     local = int(os.environ.get("LOCAL_RANK", "0"))
     torch.cuda.set_device(local)
     device = torch.device("cuda", local)
-    group = None
+    group = cpu_group = None
     if world > 1:
         dist.init_process_group("nccl", device_id=device)
         group = dist.group.WORLD
+        # Host-side barriers and the max-over-ranks reduction go through a gloo group: an eager
+        # NCCL collective issued after NCCL collectives were captured into CUDA graphs did not
+        # return on this software stack (seen with a 2-GPU run), a CPU group does.
+        cpu_group = dist.new_group(backend="gloo")
     warmup = max(args.warmup, 3)
     prompt_length = min(args.prompt, 64)
     model = PackedQwen3(QWEN3_32B, device, seed=0, max_seq=prompt_length + 2 * (args.steps + warmup) + 16,
@@ -469,8 +473,9 @@ def run_tp(args) -> None:
     model.prefill(prompt)
 
     def barrier():
+        torch.cuda.synchronize()
         if world > 1:
-            dist.barrier()
+            dist.barrier(group=cpu_group)
         torch.cuda.synchronize()
 
     for _ in range(warmup):
@@ -484,9 +489,9 @@ def run_tp(args) -> None:
         stop.record()
         barrier()
     clocks = sampler.summary()
-    times = torch.tensor([start.elapsed_time(stop)], dtype=torch.float64, device=device)
+    times = torch.tensor([start.elapsed_time(stop)], dtype=torch.float64)
     if world > 1:
-        dist.all_reduce(times, op=dist.ReduceOp.MAX)
+        dist.all_reduce(times, op=dist.ReduceOp.MAX, group=cpu_group)
     tokens = model.log[0, : warmup + args.steps + 1].tolist()
     if rank == 0:
         ms_per_step = float(times[0]) / args.steps
@@ -520,7 +525,10 @@ def run_tp(args) -> None:
         }
         print(json.dumps(line), flush=True)
     if world > 1:
-        dist.destroy_process_group()
+        # leave without tearing the NCCL communicator down under live graphs (see above)
+        dist.barrier(group=cpu_group)
+        sys.stdout.flush()
+        os._exit(0)
 
 
 def run_ours(args) -> None:

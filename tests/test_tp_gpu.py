@@ -17,6 +17,7 @@ def _worker(rank, world, path, results):
     torch.cuda.set_device(rank)
     dist.init_process_group("nccl", init_method=f"file://{path}", rank=rank, world_size=world,
                             device_id=torch.device("cuda", rank))
+    cpu_group = dist.new_group(backend="gloo")  # host-side barrier, see bench.py run_tp
     try:
         from sage_b200.qwen3 import PackedQwen3, Qwen3Config
 
@@ -33,9 +34,12 @@ def _worker(rank, world, path, results):
             same = (tokens[0] == want[0]).long().cumprod(0).sum().item()
             results.put(("tokens", same, tokens.tolist(), want.tolist(),
                          ((logits - want_logits).norm() / want_logits.norm()).item()))
-        dist.barrier()
+        torch.cuda.synchronize()
+        dist.barrier(group=cpu_group)
+        results.close()
+        results.join_thread()
     finally:
-        dist.destroy_process_group()
+        os._exit(0)  # no NCCL teardown under live CUDA graphs
 
 
 def test_tp2_matches_single_gpu():
