@@ -119,6 +119,37 @@ int sageb200_linear_grouped(const sageb200_problem *problems_host, int count, vo
                             size_t workspace_bytes, void *stream);
 
 /*
+ * The producer of the activations, fused into a grouped decode launch: instead of reading
+ * problem.x, the kernels compute the shared input row(s) of all problems themselves.
+ *   kind 0  none (problem.x is read)
+ *   kind 1  x = weight * fp16((a + b) * rsqrt(mean((a + b)^2) + eps)): residual add and
+ *           RMSNorm as the Hugging Face Qwen3 modules round them; a + b is also written to
+ *           residual_out (must not alias a); b may be NULL
+ *   kind 2  x = fp16(silu(a)) * b: SwiGLU
+ * a, b, residual_out are FP16 [rows][k], weight FP16 [k], all 16-byte aligned.
+ */
+typedef struct sageb200_activation {
+  int kind;
+  float eps;
+  const void *a;
+  const void *b;
+  const void *weight;
+  void *residual_out;
+} sageb200_activation;
+
+/*
+ * sageb200_linear_grouped with the activations' producer fused in (all problems share rows
+ * and k; problem.x is ignored).  With one row the producer runs inside the decode kernel's
+ * activation staging, saving a kernel launch per norm / SwiGLU; with more rows one small
+ * kernel materialises the activations first.  Workspace: sageb200_fused_workspace_bytes.
+ * No counterpart in the reference, where these are separate Hugging Face modules.
+ */
+size_t sageb200_fused_workspace_bytes(const sageb200_problem *problems_host, int count);
+int sageb200_linear_grouped_fused(const sageb200_problem *problems_host, int count,
+                                  const sageb200_activation *activation, void *workspace,
+                                  size_t workspace_bytes, void *stream);
+
+/*
  * Dequantise to a dense fp16 matrix w[n][k]: bit-exact
  *   w = fp16_rn(float(+-dir) * fmaf(float(radius_code), step, min))
  * (reference csrc/sage/sage_gemm_cuda.cu:117-131 and tests/inference/reference.py:39-49).

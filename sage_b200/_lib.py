@@ -24,6 +24,8 @@ EXPORTED = (
     "sageb200_linear",
     "sageb200_linear_grouped",
     "sageb200_grouped_workspace_bytes",
+    "sageb200_fused_workspace_bytes",
+    "sageb200_linear_grouped_fused",
     "sageb200_dequant",
     "sageb200_host_staging_bytes",
     "sageb200_linear_host",
@@ -45,6 +47,19 @@ EXPORTED_DECODE = (
     "sageb200_glue_lm_head",
     "sageb200_glue_argmax_advance",
 )
+
+
+class Activation(ctypes.Structure):
+    """struct sageb200_activation."""
+
+    _fields_ = [
+        ("kind", ctypes.c_int),
+        ("eps", ctypes.c_float),
+        ("a", ctypes.c_void_p),
+        ("b", ctypes.c_void_p),
+        ("weight", ctypes.c_void_p),
+        ("residual_out", ctypes.c_void_p),
+    ]
 
 
 class Problem(ctypes.Structure):
@@ -94,6 +109,10 @@ def load() -> ctypes.CDLL:
     lib.sageb200_linear.argtypes = [vp, vp, vp, vp, vp, vp, vp, vp, sz, ci, ci, ci, ci, vp]
     lib.sageb200_grouped_workspace_bytes.restype = sz
     lib.sageb200_grouped_workspace_bytes.argtypes = [ctypes.POINTER(Problem), ci]
+    lib.sageb200_fused_workspace_bytes.restype = sz
+    lib.sageb200_fused_workspace_bytes.argtypes = [ctypes.POINTER(Problem), ci]
+    lib.sageb200_linear_grouped_fused.restype = ci
+    lib.sageb200_linear_grouped_fused.argtypes = [ctypes.POINTER(Problem), ci, ctypes.POINTER(Activation), vp, sz, vp]
     lib.sageb200_linear_grouped.restype = ci
     lib.sageb200_linear_grouped.argtypes = [ctypes.POINTER(Problem), ci, vp, sz, vp]
     lib.sageb200_dequant.restype = ci

@@ -149,10 +149,19 @@ size_t grouped_scratch_bytes(const sageb200_problem *problems, int count, const 
 // rows <= 16, one or more problems, one launch (plus one small gather launch for each
 // problem that has several rows and a permutation).
 int run_skinny(const sageb200_problem *problems, int count, void *workspace,
-               size_t workspace_bytes, cudaStream_t stream, const DeviceState &device) {
+               size_t workspace_bytes, cudaStream_t stream, const DeviceState &device,
+               const sageb200_activation *activation = nullptr) {
   SkinnyParams params;
   std::memset(&params, 0, sizeof(params));
   params.status = device.status;
+  if (activation && activation->kind != 0) {  // single-row launches only (checked by the caller)
+    params.act_kind = activation->kind;
+    params.act_eps = activation->eps;
+    params.act_a = activation->a;
+    params.act_b = activation->b;
+    params.act_weight = activation->weight;
+    params.act_residual_out = activation->residual_out;
+  }
   params.trace = g_trace;
   unsigned char *scratch = static_cast<unsigned char *>(workspace);
   size_t offset = kCounterRegionBytes;
@@ -233,6 +242,40 @@ int run_skinny(const sageb200_problem *problems, int count, void *workspace,
   }
   g_launches.fetch_add(1, std::memory_order_relaxed);
   return SAGEB200_OK;
+}
+
+// Activations of several rows for the fused entry point: kind 1 residual add + RMSNorm
+// (also writes the new residual), kind 2 SwiGLU.  One CTA per row.
+__global__ void __launch_bounds__(256)
+    activation_rows_kernel(int kind, const __half *__restrict__ a, const __half *__restrict__ b,
+                           const __half *__restrict__ weight, __half *__restrict__ residual_out,
+                           __half *__restrict__ x, int k, float eps) {
+  extern __shared__ __half row_shared[];
+  __shared__ float sums[8];
+  const size_t offset = static_cast<size_t>(blockIdx.x) * k;
+  if (kind == 2) {
+    for (int i = threadIdx.x; i < k; i += 256) {
+      const float g = __half2float(a[offset + i]);
+      x[offset + i] = __hmul(__float2half_rn(g / (1.0f + __expf(-g))), b[offset + i]);
+    }
+    return;
+  }
+  float square = 0.0f;
+  for (int i = threadIdx.x; i < k; i += 256) {
+    const __half v = b ? __hadd(a[offset + i], b[offset + i]) : a[offset + i];
+    row_shared[i] = v;
+    residual_out[offset + i] = v;
+    const float f = __half2float(v);
+    square = fmaf(f, f, square);
+  }
+  for (int o = 16; o; o >>= 1) square += __shfl_xor_sync(0xffffffffu, square, o);
+  if ((threadIdx.x & 31) == 0) sums[threadIdx.x >> 5] = square;
+  __syncthreads();
+  float total = 0.0f;
+  for (int w = 0; w < 8; ++w) total += sums[w];
+  const float scale = rsqrtf(total / k + eps);
+  for (int i = threadIdx.x; i < k; i += 256)
+    x[offset + i] = __hmul(weight[i], __float2half_rn(__half2float(row_shared[i]) * scale));
 }
 
 int validate_problem(const sageb200_problem &p) {
@@ -464,6 +507,61 @@ int sageb200_set_tuning(int warps, int slices, int ctas_per_sm, int mode) {
 }
 
 unsigned long long sageb200_launch_count(void) { return g_launches.load(std::memory_order_relaxed); }
+
+size_t sageb200_fused_workspace_bytes(const sageb200_problem *problems_host, int count) {
+  const size_t grouped = sageb200_grouped_workspace_bytes(problems_host, count);
+  if (!problems_host || count <= 0) return 0;
+  const int rows = problems_host[0].rows, k = problems_host[0].k;
+  const size_t staged = rows > 1 ? align256(static_cast<size_t>(rows) * k * 2) : 0;
+  if (!staged) return grouped;
+  return (grouped ? grouped : kCounterRegionBytes) + staged;
+}
+
+int sageb200_linear_grouped_fused(const sageb200_problem *problems_host, int count,
+                                  const sageb200_activation *activation, void *workspace,
+                                  size_t workspace_bytes, void *stream) {
+  if (!activation || activation->kind == 0)
+    return sageb200_linear_grouped(problems_host, count, workspace, workspace_bytes, stream);
+  if (!problems_host || count <= 0 || count > SAGEB200_MAX_GROUPED) return SAGEB200_ERR_INVALID_ARGUMENT;
+  if ((activation->kind != 1 && activation->kind != 2) || !activation->a ||
+      (activation->kind == 1 && (!activation->weight || !activation->residual_out)) ||
+      (activation->kind == 2 && !activation->b))
+    return SAGEB200_ERR_INVALID_ARGUMENT;
+  if ((reinterpret_cast<uintptr_t>(activation->a) & 15) || (reinterpret_cast<uintptr_t>(activation->b) & 15) ||
+      (reinterpret_cast<uintptr_t>(activation->weight) & 15) ||
+      (reinterpret_cast<uintptr_t>(activation->residual_out) & 15))
+    return SAGEB200_ERR_ALIGNMENT;
+  sageb200_problem local[SAGEB200_MAX_GROUPED];
+  const int rows = problems_host[0].rows, k = problems_host[0].k;
+  for (int i = 0; i < count; ++i) {
+    local[i] = problems_host[i];
+    local[i].x = activation->a;  // placeholder for validation; the kernels compute the row
+    if (local[i].rows != rows || local[i].k != k) return SAGEB200_ERR_INVALID_ARGUMENT;
+    const int status = validate_problem(local[i]);
+    if (status) return status;
+    if (rows > 16) return SAGEB200_ERR_RANGE;
+  }
+  if (rows == 0) return SAGEB200_OK;
+  DeviceState *device = nullptr;
+  const int status = device_state(&device);
+  if (status) return status;
+  cudaStream_t s = static_cast<cudaStream_t>(stream);
+  if (rows == 1) return run_skinny(local, count, workspace, workspace_bytes, s, *device, activation);
+  // several rows: one small kernel materialises the activations, then the plain path
+  const size_t staged = align256(static_cast<size_t>(rows) * k * 2);
+  const size_t need = sageb200_fused_workspace_bytes(problems_host, count);
+  if (!workspace || workspace_bytes < need) return SAGEB200_ERR_WORKSPACE;
+  if (reinterpret_cast<uintptr_t>(workspace) & 255) return SAGEB200_ERR_ALIGNMENT;
+  __half *x = reinterpret_cast<__half *>(static_cast<unsigned char *>(workspace) + need - staged);
+  activation_rows_kernel<<<rows, 256, static_cast<size_t>(k) * sizeof(__half), s>>>(
+      activation->kind, static_cast<const __half *>(activation->a), static_cast<const __half *>(activation->b),
+      static_cast<const __half *>(activation->weight), static_cast<__half *>(activation->residual_out), x, k,
+      activation->eps);
+  if (cudaGetLastError() != cudaSuccess) return SAGEB200_ERR_CUDA;
+  g_launches.fetch_add(1, std::memory_order_relaxed);
+  for (int i = 0; i < count; ++i) local[i].x = x;
+  return run_skinny(local, count, workspace, need - staged, s, *device);
+}
 
 /* ---------------------------------------------------------------------------------------
  * sageb200_linear_static: the decode matmul for callers that cannot hand over scratch.

@@ -39,6 +39,11 @@ struct SkinnyParams {
   int warp_segments;    // most tiles any warp touches
   int lin_bytes;        // shared bytes for activations in original order (0: none)
   unsigned warps_reciprocal;  // floor(2^32 / warps) + 1
+  // producer fused into the activation staging (single row only); 0 = none
+  int act_kind;
+  float act_eps;
+  const void *act_a, *act_b, *act_weight;
+  void *act_residual_out;
   int *status;          // device-visible status word, may be null
   long long *trace;     // optional: per-CTA phase clocks (16 per CTA), null in normal use
 };

@@ -87,6 +87,7 @@ __global__ void __launch_bounds__(512, 1) sage_skinny_kernel(const __grid_consta
   __shared__ __align__(128) unsigned char book_shared[kBookBytes];
   __shared__ __align__(8) unsigned long long barriers[kMaxWarps];
   __shared__ int warp_first_tile[kMaxWarps];
+  __shared__ float norm_sums[kMaxWarps];
   __shared__ int tile_parts[kMaxCtaTiles];  // CTAs contributing to the tile, all slices
   __shared__ int tile_slot[kMaxCtaTiles];   // this CTA's position among them (slice-major)
   __shared__ int tile_last[kMaxCtaTiles];   // this CTA arrived last
@@ -241,7 +242,14 @@ __global__ void __launch_bounds__(512, 1) sage_skinny_kernel(const __grid_consta
   const bool perm_aligned = (reinterpret_cast<uintptr_t>(p.perm) & 15) == 0;
   const bool linear_gather = p.perm != nullptr && perm_aligned &&
                              static_cast<size_t>(p.rows) * p.k * 2 <= static_cast<size_t>(params.lin_bytes);
-  const bool direct_copy = p.perm == nullptr && aligned_x;
+  // Fused producer (single activation row only): the row is computed here from the
+  // producer's inputs instead of being read from p.x:
+  //   1  x = weight * fp16((a + b) * rsqrt(mean((a + b)^2) + eps)),  a + b also stored as the
+  //      new residual by the launch's first CTA                      (residual add + RMSNorm)
+  //   2  x = fp16(silu(a)) * b                                        (SwiGLU)
+  const int fused = params.act_kind;
+  const bool gather_from_linear = linear_gather || fused != 0;
+  const bool direct_copy = p.perm == nullptr && aligned_x && fused == 0;
   constexpr int kItemBatch = 4;  // permutation items (4 channels each) held in registers
   constexpr int kCopyBatch = 4;  // 16-byte activation pieces held in registers
   int4 held[kItemBatch];
@@ -249,7 +257,9 @@ __global__ void __launch_bounds__(512, 1) sage_skinny_kernel(const __grid_consta
   const int items = span >> 2;
   const int vectors = span >> 3;
   // what the first batch of 16-byte pieces copies: the slice of every row (a) or all of x (b)
-  const int pieces = direct_copy ? vectors * p.rows : (linear_gather && aligned_x ? (p.rows * p.k) >> 3 : 0);
+  const int pieces = fused ? 0
+                     : direct_copy ? vectors * p.rows
+                                   : (linear_gather && aligned_x ? (p.rows * p.k) >> 3 : 0);
 
   uint4 entry = make_uint4(0, 0, 0, 0);
   if (tid < p.entries) {
@@ -258,11 +268,71 @@ __global__ void __launch_bounds__(512, 1) sage_skinny_kernel(const __grid_consta
     entry.z = __ldg(p.book + 2 * p.entries + tid);
     entry.w = __ldg(p.book + 3 * p.entries + tid);
   }
-  if (linear_gather) {
+  auto load_item = [&](int q) {  // source channels of quantised channels 4q .. 4q+3
+    const int channel = group_begin * 128 + 4 * q;
+    if (p.perm == nullptr) return make_int4(channel, channel + 1, channel + 2, channel + 3);
+    if (perm_aligned) return __ldg(reinterpret_cast<const int4 *>(p.perm) + (channel >> 2));
+    return make_int4(__ldg(p.perm + channel), __ldg(p.perm + channel + 1), __ldg(p.perm + channel + 2),
+                     __ldg(p.perm + channel + 3));
+  };
+  if (gather_from_linear) {
 #pragma unroll
     for (int it = 0; it < kItemBatch; ++it) {
       const int q = tid + it * threads;
-      if (q < items) held[it] = __ldg(reinterpret_cast<const int4 *>(p.perm + group_begin * 128) + q);
+      if (q < items) held[it] = load_item(q);
+    }
+  }
+  float square_sum = 0.0f;
+  if (fused) {
+    // the whole row, in original channel order, into the linear buffer (and the norm
+    // weights behind it); loads of a batch first, arithmetic and stores after
+    const uint4 *a4 = reinterpret_cast<const uint4 *>(params.act_a);
+    const uint4 *b4 = reinterpret_cast<const uint4 *>(params.act_b);
+    const uint4 *w4 = reinterpret_cast<const uint4 *>(params.act_weight);
+    uint4 *out4 = reinterpret_cast<uint4 *>(x_linear);
+    uint4 *weight4 = reinterpret_cast<uint4 *>(x_linear + p.k);
+    uint4 *residual4 = (fused == 1 && blockIdx.x == 0) ? reinterpret_cast<uint4 *>(params.act_residual_out) : nullptr;
+    const int row_pieces = p.k >> 3;
+    for (int base = 0; base < row_pieces; base += kCopyBatch * threads) {
+      uint4 pa[kCopyBatch], pb[kCopyBatch], pw[kCopyBatch];
+#pragma unroll
+      for (int it = 0; it < kCopyBatch; ++it) {
+        const int i = base + tid + it * threads;
+        if (i < row_pieces) {
+          pa[it] = __ldg(a4 + i);
+          pb[it] = b4 ? __ldg(b4 + i) : make_uint4(0, 0, 0, 0);
+          if (fused == 1) pw[it] = __ldg(w4 + i);
+        }
+      }
+#pragma unroll
+      for (int it = 0; it < kCopyBatch; ++it) {
+        const int i = base + tid + it * threads;
+        if (i >= row_pieces) continue;
+        uint4 value;
+        const __half2 *ah = reinterpret_cast<const __half2 *>(&pa[it]);
+        const __half2 *bh = reinterpret_cast<const __half2 *>(&pb[it]);
+        __half2 *vh = reinterpret_cast<__half2 *>(&value);
+#pragma unroll
+        for (int c = 0; c < 4; ++c) {
+          if (fused == 1) {
+            vh[c] = b4 ? __hadd2(ah[c], bh[c]) : ah[c];
+            const float2 f = __half22float2(vh[c]);
+            square_sum = fmaf(f.x, f.x, fmaf(f.y, f.y, square_sum));
+          } else {
+            const float2 g2 = __half22float2(ah[c]);
+            const __half2 silu = __floats2half2_rn(g2.x / (1.0f + __expf(-g2.x)), g2.y / (1.0f + __expf(-g2.y)));
+            vh[c] = __hmul2(silu, bh[c]);
+          }
+        }
+        out4[i] = value;
+        if (fused == 1) weight4[i] = pw[it];
+        if (residual4) residual4[i] = value;
+      }
+    }
+    if (fused == 1) {
+#pragma unroll
+      for (int o = 16; o; o >>= 1) square_sum += __shfl_xor_sync(0xffffffffu, square_sum, o);
+      if (lane == 0) norm_sums[warp] = square_sum;
     }
   }
   auto load_piece = [&](int i) {
@@ -325,12 +395,12 @@ __global__ void __launch_bounds__(512, 1) sage_skinny_kernel(const __grid_consta
       }
     }
   }
-  if (linear_gather && !aligned_x) {
+  if (linear_gather && !aligned_x && !fused) {
     const int total = p.rows * p.k;
 #pragma unroll 8
     for (int i = tid; i < total; i += threads) x_linear[i] = p.x[i];
   }
-  if (!direct_copy && !linear_gather) {
+  if (!direct_copy && !gather_from_linear) {
     for (int q = tid; q < items; q += threads) {
       const int channel = group_begin * 128 + 4 * q;
       int4 source = make_int4(channel, channel + 1, channel + 2, channel + 3);
@@ -355,14 +425,20 @@ __global__ void __launch_bounds__(512, 1) sage_skinny_kernel(const __grid_consta
   const bool any_split = __syncthreads_or(shared_tile) != 0;
   SAGE_STAMP(3);
 
-  if (linear_gather) {  // warp-uniform: the gather out of shared memory, then a second barrier
+  if (gather_from_linear) {  // warp-uniform: the gather out of shared memory, then a second barrier
+    float norm_scale = 1.0f;
+    if (fused == 1) {
+      float total = 0.0f;
+      for (int w = 0; w < warps; ++w) total += norm_sums[w];
+      norm_scale = rsqrtf(total / static_cast<float>(p.k) + params.act_eps);
+    }
+    const __half *weight_linear = x_linear + p.k;
     for (int base = 0; base < items; base += kItemBatch * threads) {
       if (base > 0) {
 #pragma unroll
         for (int it = 0; it < kItemBatch; ++it) {
           const int q = base + tid + it * threads;
-          if (q < items)
-            held[it] = __ldg(reinterpret_cast<const int4 *>(p.perm + group_begin * 128) + q);
+          if (q < items) held[it] = load_item(q);
         }
       }
 #pragma unroll
@@ -376,6 +452,13 @@ __global__ void __launch_bounds__(512, 1) sage_skinny_kernel(const __grid_consta
         for (int m = 0; m < p.rows; ++m) {
           const __half *row = x_linear + m * p.k;
           __align__(8) __half values[4] = {row[source.x], row[source.y], row[source.z], row[source.w]};
+          if (fused == 1) {  // RMSNorm: weight * fp16(value * scale), as the unfused kernel rounds
+            const int sources[4] = {source.x, source.y, source.z, source.w};
+#pragma unroll
+            for (int c = 0; c < 4; ++c)
+              values[c] = __hmul(weight_linear[sources[c]],
+                                 __float2half_rn(__half2float(values[c]) * norm_scale));
+          }
           *reinterpret_cast<uint2 *>(x_shared + m * row_stride + target) =
               *reinterpret_cast<const uint2 *>(values);
         }
@@ -602,7 +685,7 @@ SkinnyPlan plan_skinny(int rows, int n, int k, int entries, int sm_count, const 
       plan.x_bytes = x_bytes_for(rows, groups);
       plan.needs_scratch = false;
       plan.partial_bytes = 0;
-      const size_t lin = rows == 1 ? (static_cast<size_t>(k) * 2 + 127) / 128 * 128 : 0;
+      const size_t lin = rows == 1 ? (static_cast<size_t>(k) * 4 + 127) / 128 * 128 : 0;
       const size_t shared = plan.x_bytes + static_cast<size_t>(plan.unit_capacity) * kUnitBytes +
                             static_cast<size_t>(plan.warps) * plan.warp_segments * plan.column_blocks * 512 + lin;
       if (shared > static_cast<size_t>(kMaxDynamicShared)) whole = false;
@@ -628,7 +711,7 @@ SkinnyPlan plan_skinny(int rows, int n, int k, int entries, int sm_count, const 
     while ((max_units + per_slice - 1) / per_slice / min_groups + 2 > tile_cap) ++per_slice;
     if (per_slice > min_units) per_slice = min_units;
     const size_t fixed = x_bytes_for(rows, max_groups) +
-                         (rows == 1 ? (static_cast<size_t>(k) * 2 + 127) / 128 * 128 : 0);
+                         (rows == 1 ? (static_cast<size_t>(k) * 4 + 127) / 128 * 128 : 0);
     while (true) {  // more (smaller) CTAs until one CTA's units fit shared memory
       plan.unit_capacity = static_cast<int>((max_units + per_slice - 1) / per_slice);
       const int warp_units = (plan.unit_capacity + plan.warps - 1) / plan.warps;
@@ -656,7 +739,7 @@ SkinnyPlan plan_skinny(int rows, int n, int k, int entries, int sm_count, const 
   }
   // a single activation row with a permutation is gathered through a linear copy in
   // shared memory (several rows arrive pre-gathered)
-  plan.lin_bytes = rows == 1 ? (static_cast<size_t>(k) * 2 + 127) / 128 * 128 : 0;
+  plan.lin_bytes = rows == 1 ? (static_cast<size_t>(k) * 4 + 127) / 128 * 128 : 0;  // row + norm weights
   plan.shared_bytes = plan.x_bytes + static_cast<size_t>(plan.unit_capacity) * kUnitBytes +
                       static_cast<size_t>(plan.warps) * plan.warp_segments * plan.column_blocks * 512 +
                       plan.lin_bytes;

@@ -13,6 +13,8 @@ Argument checks and their messages follow the reference's native entry point
 
 from __future__ import annotations
 
+import ctypes
+
 import torch
 
 from . import _lib
@@ -161,10 +163,13 @@ def sage_dequantize(
     return weight
 
 
-def sage_grouped(problems: list[tuple], out_features: list[int]) -> list[torch.Tensor]:
+def sage_grouped(problems: list[tuple], out_features: list[int], activation: tuple | None = None) -> list[torch.Tensor]:
     """Several packed linears (rows <= 16 each) in one launch.
 
     `problems[i]` = (x, packed_codes, radius_codes, radius_grid, codebook, permutation).
+    `activation` = (kind, eps, a, b, weight, residual_out) fuses the producer of the shared
+    input into the launch (kind 1: residual add + RMSNorm, kind 2: SwiGLU; see
+    `sageb200_activation` in include/sage_b200.h); `x` then only supplies shape and dtype.
     """
     if len(problems) > _lib.MAX_GROUPED:
         raise RuntimeError("too many problems for one grouped launch")
@@ -183,15 +188,32 @@ def sage_grouped(problems: list[tuple], out_features: list[int]) -> list[torch.T
         )
     with torch.cuda.device(device):
         stream = torch.cuda.current_stream(device).cuda_stream
-        total = lib.sageb200_grouped_workspace_bytes(array, len(problems))
-        workspace = _workspace(device, stream, total) if total else None
-        _lib.check(
-            lib.sageb200_linear_grouped(
-                array,
-                len(problems),
-                workspace.data_ptr() if workspace is not None else None,
-                workspace.numel() if workspace is not None else 0,
-                stream,
+        if activation is None:
+            total = lib.sageb200_grouped_workspace_bytes(array, len(problems))
+            workspace = _workspace(device, stream, total) if total else None
+            _lib.check(
+                lib.sageb200_linear_grouped(
+                    array,
+                    len(problems),
+                    workspace.data_ptr() if workspace is not None else None,
+                    workspace.numel() if workspace is not None else 0,
+                    stream,
+                )
             )
-        )
+        else:
+            kind, eps, a, b, weight, residual_out = activation
+            pointer = lambda t: t.data_ptr() if t is not None else None  # noqa: E731
+            act = _lib.Activation(kind, eps, pointer(a), pointer(b), pointer(weight), pointer(residual_out))
+            total = lib.sageb200_fused_workspace_bytes(array, len(problems))
+            workspace = _workspace(device, stream, total) if total else None
+            _lib.check(
+                lib.sageb200_linear_grouped_fused(
+                    array,
+                    len(problems),
+                    ctypes.byref(act),
+                    workspace.data_ptr() if workspace is not None else None,
+                    workspace.numel() if workspace is not None else 0,
+                    stream,
+                )
+            )
     return outputs

@@ -156,6 +156,8 @@ class PackedQwen3:
         self.log = torch.zeros(batch, max_new, dtype=torch.int64, device=self.device)
         self.max_new = max_new
         self.h = torch.zeros(batch, c.hidden, **half)
+        self.h_other = torch.zeros(batch, c.hidden, **half)  # residual ping-pong for fused norms
+        self.fuse = True
         self.x = torch.zeros(batch, c.hidden, **half)
         self.attn = torch.zeros(batch, q_out // world, **half)
         self.act = torch.zeros(batch, c.intermediate // world, **half)
@@ -177,10 +179,25 @@ class PackedQwen3:
         if status:
             raise RuntimeError(f"sage_b200 decode glue: {what} failed with status {status}")
 
-    def _linears(self, layer, names, x):
+    def _linears(self, layer, names, x, activation=None):
         if self.dense:
             return [torch.nn.functional.linear(x, layer[name].weight) for name in names]
-        return sage_grouped([layer[name].problem(x) for name in names], [layer[name].n for name in names])
+        return sage_grouped([layer[name].problem(x) for name in names], [layer[name].n for name in names],
+                            activation)
+
+    def _norm_linears(self, layer, names, delta, weight):
+        """x = rmsnorm(h + delta) * weight, h += delta, then the packed linears `names` on x.
+        Packed path: one launch (the norm runs inside the decode kernel's activation staging
+        and the new residual goes to the other of two residual buffers).  Dense oracle: the
+        stand-alone norm kernel, then torch matmuls."""
+        c, lib, b = self.config, self.lib, self.batch
+        if self.dense or not self.fuse:
+            self._check(lib.sageb200_glue_add_rmsnorm(_vp(self.h), _vp(delta), _vp(weight), _vp(self.x), b,
+                                                      c.hidden, c.eps, self._stream()), "add_rmsnorm")
+            return self._linears(layer, names, self.x)
+        out = self._linears(layer, names, self.h, (1, c.eps, self.h, delta, weight, self.h_other))
+        self.h, self.h_other = self.h_other, self.h
+        return out
 
     def _all_reduce(self, tensor):
         """Sum the row-parallel partial outputs over the tensor-parallel group (NCCL)."""
@@ -194,9 +211,7 @@ class PackedQwen3:
         the residual stream (None for the first layer).  Returns this layer's MLP output."""
         c, lib, b = self.config, self.lib, self.batch
         s = self._stream()
-        self._check(lib.sageb200_glue_add_rmsnorm(_vp(self.h), _vp(delta), _vp(layer["input_norm"]),
-                                                  _vp(self.x), b, c.hidden, c.eps, s), "add_rmsnorm")
-        q, k, v = self._linears(layer, ("q", "k", "v"), self.x)
+        q, k, v = self._norm_linears(layer, ("q", "k", "v"), delta, layer["input_norm"])
         self._check(lib.sageb200_glue_qk_norm_rope_cache(
             _vp(q), _vp(k), _vp(v), _vp(layer["q_norm"]), _vp(layer["k_norm"]), _vp(self.cos),
             _vp(self.sin), _vp(self.positions), _vp(layer["k_cache"]), _vp(layer["v_cache"]), b,
@@ -207,11 +222,12 @@ class PackedQwen3:
             "attention_decode")
         (o,) = self._linears(layer, ("o",), self.attn)
         self._all_reduce(o)
-        self._check(lib.sageb200_glue_add_rmsnorm(_vp(self.h), _vp(o), _vp(layer["post_norm"]),
-                                                  _vp(self.x), b, c.hidden, c.eps, s), "add_rmsnorm")
-        gate, up = self._linears(layer, ("gate", "up"), self.x)
-        self._check(lib.sageb200_glue_swiglu(_vp(gate), _vp(up), _vp(self.act), gate.numel(), s), "swiglu")
-        (down,) = self._linears(layer, ("down",), self.act)
+        gate, up = self._norm_linears(layer, ("gate", "up"), o, layer["post_norm"])
+        if self.dense or not self.fuse:
+            self._check(lib.sageb200_glue_swiglu(_vp(gate), _vp(up), _vp(self.act), gate.numel(), s), "swiglu")
+            (down,) = self._linears(layer, ("down",), self.act)
+        else:  # SwiGLU inside the down projection's activation staging
+            (down,) = self._linears(layer, ("down",), self.act, (2, 0.0, gate, up, None, None))
         self._all_reduce(down)
         return down
 

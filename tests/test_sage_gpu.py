@@ -390,3 +390,46 @@ def test_reference_cuda_kernels_agree_when_built():
         want = expected_output(x, cpu, n)
         assert_output(theirs, want)
         assert_output(ours, want)
+
+
+@pytest.mark.parametrize("rows", [1, 5])
+@pytest.mark.parametrize("permuted", [True, False])
+def test_fused_producers_match_separate_kernels(rows, permuted):
+    """Residual add + RMSNorm and SwiGLU fused into the grouped launch against the
+    stand-alone glue kernels followed by the plain grouped launch."""
+    lib = _lib.load()
+    vp = ctypes.c_void_p
+    stream = vp(torch.cuda.current_stream().cuda_stream)
+    k = 2560
+    gen = torch.Generator(device="cuda").manual_seed(rows)
+    residual = torch.randn(rows, k, generator=gen, device="cuda").half()
+    delta = torch.randn(rows, k, generator=gen, device="cuda").half()
+    weight = (1 + 0.1 * torch.randn(k, generator=gen, device="cuda")).half()
+    cpus = [synthetic_sage(k, n, seed=s, permuted=permuted) for n, s in [(1024, 0), (4096, 1)]]
+    layers = [SAGELinear(to_cuda(cpu), n) for cpu, n in zip(cpus, (1024, 4096))]
+    problem = lambda x: [(x, l.packed_codes, l.radius_codes, l.radius_grid, l.codebook, l.permutation) for l in layers]  # noqa: E731
+    outs = [1024, 4096]
+    # separate kernels
+    h = residual.clone()
+    x = torch.empty_like(h)
+    assert lib.sageb200_glue_add_rmsnorm(vp(h.data_ptr()), vp(delta.data_ptr()), vp(weight.data_ptr()),
+                                         vp(x.data_ptr()), rows, k, 1e-6, stream) == 0
+    want = sage_grouped(problem(x), outs)
+    # fused
+    new_residual = torch.zeros_like(residual)
+    got = sage_grouped(problem(residual), outs, (1, 1e-6, residual, delta, weight, new_residual))
+    assert torch.equal(new_residual, h)
+    for a, b in zip(got, want):
+        assert ((a.float() - b.float()).norm() / b.float().norm()).item() < 1e-3
+    got_none = sage_grouped(problem(residual), outs, (1, 1e-6, residual, None, weight, new_residual))
+    assert torch.equal(new_residual, residual)
+    assert all(torch.isfinite(t).all() for t in got_none)
+    # SwiGLU
+    gate = torch.randn(rows, k, generator=gen, device="cuda").half()
+    up = torch.randn(rows, k, generator=gen, device="cuda").half()
+    act = torch.empty_like(gate)
+    assert lib.sageb200_glue_swiglu(vp(gate.data_ptr()), vp(up.data_ptr()), vp(act.data_ptr()), gate.numel(), stream) == 0
+    want = sage_grouped(problem(act), outs)
+    got = sage_grouped(problem(gate), outs, (2, 0.0, gate, up, None, None))
+    for a, b in zip(got, want):
+        assert ((a.float() - b.float()).norm() / b.float().norm()).item() < 1e-3
