@@ -1,7 +1,7 @@
 """Benchmark of the SAGE packed-weight decode path on B200.
 
     python bench.py [--gpus N] [--steps K] [--warmup W] [--impl ours|reference]
-                    [--workload decode_model|decode_linears|tp32b|linear:K:N:M] [--prompt P]
+                    [--workload decode_model|decode_linears|tp32b|ep30b|linear:K:N:M] [--prompt P]
 
 A step is one decoded token of the full Qwen3-4B architecture at batch 1 (synthetic seeded
 packed weights, ABS split cycling 6/7/8 direction bits per matrix; `decode_linears` times the
@@ -449,7 +449,10 @@ def run_tp(args) -> None:
     import torch
     import torch.distributed as dist
 
-    from sage_b200.qwen3 import QWEN3_32B, PackedQwen3
+    from sage_b200.qwen3 import QWEN3_30B_A3B, QWEN3_32B, PackedQwen3
+
+    expert_parallel = args.workload == "ep30b"
+    config = QWEN3_30B_A3B if expert_parallel else QWEN3_32B
 
     rank = int(os.environ.get("RANK", "0"))
     world = int(os.environ.get("WORLD_SIZE", "1"))
@@ -466,10 +469,12 @@ def run_tp(args) -> None:
         cpu_group = dist.new_group(backend="gloo")
     warmup = max(args.warmup, 3)
     prompt_length = min(args.prompt, 64)
-    model = PackedQwen3(QWEN3_32B, device, seed=0, max_seq=prompt_length + 2 * (args.steps + warmup) + 16,
-                        batch=1, max_new=2 * (args.steps + warmup) + 16, tp_group=group, perm_blocks=8)
+    model = PackedQwen3(config, device, seed=0, max_seq=prompt_length + 2 * (args.steps + warmup) + 16,
+                        batch=1, max_new=2 * (args.steps + warmup) + 16,
+                        tp_group=None if expert_parallel else group, perm_blocks=1 if expert_parallel else 8,
+                        ep_group=group if expert_parallel else None)
     model.capture()
-    prompt = torch.randint(3, QWEN3_32B.vocab, (1, prompt_length), generator=torch.Generator().manual_seed(7))
+    prompt = torch.randint(3, config.vocab, (1, prompt_length), generator=torch.Generator().manual_seed(7))
     model.prefill(prompt)
 
     def barrier():
@@ -498,7 +503,7 @@ def run_tp(args) -> None:
         peak, peak_kind = measured_peaks()
         step_bytes = model.bytes_per_token(prompt_length + warmup + args.steps // 2)
         line = {
-            "metric": "qwen3_32b_sage_2.25bpw_batch1_decode_tok_s",
+            "metric": ("qwen3_30b_a3b" if expert_parallel else "qwen3_32b") + "_sage_2.25bpw_batch1_decode_tok_s",
             "value": 1000.0 / ms_per_step,
             "unit": UNIT,
             "n_gpus": world,
@@ -511,9 +516,14 @@ def run_tp(args) -> None:
             "dtype": "f16 products, f32 accumulate",
             "data": "synthetic",
             "config": {
-                "workload": "Qwen3-32B shape (64 layers, hidden 5120, 64/8 heads, inter 25600), random-init, "
-                            "SAGE-packed, batch 1 greedy decode, tensor parallel",
-                "parallelism": f"tp{world}",
+                "workload": ("Qwen3-30B-A3B shape (48 layers, hidden 2048, 32/4 heads, 128 experts top-8, "
+                             "moe_inter 768), random-init, attention and expert linears SAGE-packed, FP16 router, "
+                             "batch 1 greedy decode, expert parallel (attention and router replicated, each "
+                             "rank runs its block of experts, outputs summed with an all-reduce)"
+                             if expert_parallel else
+                             "Qwen3-32B shape (64 layers, hidden 5120, 64/8 heads, inter 25600), random-init, "
+                             "SAGE-packed, batch 1 greedy decode, tensor parallel"),
+                "parallelism": f"ep{world}" if expert_parallel else f"tp{world}",
                 "row_parallel_permutation": "block permutation, 8 blocks (each rank gathers inside its slice)",
                 "per_rank_hbm_bytes_per_step": step_bytes,
                 "per_rank_hbm_gbs": step_bytes / (ms_per_step / 1000.0) / 1e9,
@@ -704,7 +714,7 @@ def main() -> None:
         run_single_linear(args)
     elif args.workload == "decode_model":
         run_model(args)
-    elif args.workload == "tp32b":
+    elif args.workload in ("tp32b", "ep30b"):
         run_tp(args)
     else:
         run_ours(args)

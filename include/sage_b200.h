@@ -150,6 +150,44 @@ int sageb200_linear_grouped_fused(const sageb200_problem *problems_host, int cou
                                   size_t workspace_bytes, void *stream);
 
 /*
+ * A stack of `experts` packed linears of one shape (the experts of one MoE projection that
+ * live on this GPU), every buffer with a leading expert dimension:
+ *   codes [experts][tiles][groups][16][8], radii and grid likewise, book [experts][4][entries][2],
+ *   perm [experts][k] or NULL.  `first_expert` is the global index of the stack's first expert.
+ */
+typedef struct sageb200_expert_stack {
+  const void *codes;
+  const void *radii;
+  const void *grid;
+  const void *book;
+  const int32_t *perm;
+  int experts;
+  int first_expert;
+  int n;
+  int k;
+  int entries;
+} sageb200_expert_stack;
+
+/*
+ * Routed experts, one activation row per slot: for every slot s and stack t
+ *   ys[t][s][:] = W(stack t, expert expert_ids[s]) . x[s * x_slot_stride ...]
+ * `expert_ids` is a DEVICE array of `slots` global expert indices (the router's top-k, still on
+ * the GPU: no host round trip); slots whose expert is outside [first_expert, first_expert +
+ * experts) are skipped, so the caller zero-fills ys and, under expert parallelism, sums the
+ * ranks' outputs.  x_slot_stride = 0 shares one activation row between all slots (gate/up of
+ * one token), x_slot_stride = k gives each slot its own row (down).  Launches
+ * SAGEB200_MAX_GROUPED problems at a time.  Workspace as for a grouped launch of the same
+ * shapes (sageb200_experts_workspace_bytes).
+ * No counterpart in the reference, which has no packed MoE module (its loader rejects every
+ * model type but dense qwen3, weight_vq/integrations/transformers.py:88-89).
+ */
+size_t sageb200_experts_workspace_bytes(const sageb200_expert_stack *stacks_host, int stack_count,
+                                        int slots);
+int sageb200_experts(const void *x, long long x_slot_stride, const sageb200_expert_stack *stacks_host,
+                     void *const *ys_host, int stack_count, const int32_t *expert_ids, int slots,
+                     void *workspace, size_t workspace_bytes, void *stream);
+
+/*
  * Dequantise to a dense fp16 matrix w[n][k]: bit-exact
  *   w = fp16_rn(float(+-dir) * fmaf(float(radius_code), step, min))
  * (reference csrc/sage/sage_gemm_cuda.cu:117-131 and tests/inference/reference.py:39-49).

@@ -26,6 +26,8 @@ EXPORTED = (
     "sageb200_grouped_workspace_bytes",
     "sageb200_fused_workspace_bytes",
     "sageb200_linear_grouped_fused",
+    "sageb200_experts_workspace_bytes",
+    "sageb200_experts",
     "sageb200_dequant",
     "sageb200_host_staging_bytes",
     "sageb200_linear_host",
@@ -59,6 +61,23 @@ class Activation(ctypes.Structure):
         ("b", ctypes.c_void_p),
         ("weight", ctypes.c_void_p),
         ("residual_out", ctypes.c_void_p),
+    ]
+
+
+class ExpertStack(ctypes.Structure):
+    """struct sageb200_expert_stack."""
+
+    _fields_ = [
+        ("codes", ctypes.c_void_p),
+        ("radii", ctypes.c_void_p),
+        ("grid", ctypes.c_void_p),
+        ("book", ctypes.c_void_p),
+        ("perm", ctypes.c_void_p),
+        ("experts", ctypes.c_int),
+        ("first_expert", ctypes.c_int),
+        ("n", ctypes.c_int),
+        ("k", ctypes.c_int),
+        ("entries", ctypes.c_int),
     ]
 
 
@@ -113,6 +132,10 @@ def load() -> ctypes.CDLL:
     lib.sageb200_fused_workspace_bytes.argtypes = [ctypes.POINTER(Problem), ci]
     lib.sageb200_linear_grouped_fused.restype = ci
     lib.sageb200_linear_grouped_fused.argtypes = [ctypes.POINTER(Problem), ci, ctypes.POINTER(Activation), vp, sz, vp]
+    lib.sageb200_experts_workspace_bytes.restype = sz
+    lib.sageb200_experts_workspace_bytes.argtypes = [ctypes.POINTER(ExpertStack), ci, ci]
+    lib.sageb200_experts.restype = ci
+    lib.sageb200_experts.argtypes = [vp, ctypes.c_longlong, ctypes.POINTER(ExpertStack), ctypes.POINTER(vp), ci, vp, ci, vp, sz, vp]
     lib.sageb200_linear_grouped.restype = ci
     lib.sageb200_linear_grouped.argtypes = [ctypes.POINTER(Problem), ci, vp, sz, vp]
     lib.sageb200_dequant.restype = ci

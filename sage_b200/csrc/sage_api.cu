@@ -148,9 +148,16 @@ size_t grouped_scratch_bytes(const sageb200_problem *problems, int count, const 
 
 // rows <= 16, one or more problems, one launch (plus one small gather launch for each
 // problem that has several rows and a permutation).
+// Expert indirection of one problem of a launch (see SkinnyProblem).
+struct ExpertRef {
+  const int *ids;
+  int slot, first, count;
+  long long codes_stride, cell_stride, book_stride;
+};
+
 int run_skinny(const sageb200_problem *problems, int count, void *workspace,
                size_t workspace_bytes, cudaStream_t stream, const DeviceState &device,
-               const sageb200_activation *activation = nullptr) {
+               const sageb200_activation *activation = nullptr, const ExpertRef *experts = nullptr) {
   SkinnyParams params;
   std::memset(&params, 0, sizeof(params));
   params.status = device.status;
@@ -221,6 +228,15 @@ int run_skinny(const sageb200_problem *problems, int count, void *workspace,
       out.share_r = static_cast<int>(share % plan.ctas_per_slice);
     }
     out.cta_begin = ctas;
+    if (experts) {
+      out.expert_ids = experts[i].ids;
+      out.expert_slot = experts[i].slot;
+      out.expert_first = experts[i].first;
+      out.expert_count = experts[i].count;
+      out.codes_stride = experts[i].codes_stride;
+      out.cell_stride = experts[i].cell_stride;
+      out.book_stride = experts[i].book_stride;
+    }
     ctas += plan.ctas;
     offset += partial + gathered;
     if (plan.needs_scratch) counters_used += plan.tiles;
@@ -561,6 +577,59 @@ int sageb200_linear_grouped_fused(const sageb200_problem *problems_host, int cou
   g_launches.fetch_add(1, std::memory_order_relaxed);
   for (int i = 0; i < count; ++i) local[i].x = x;
   return run_skinny(local, count, workspace, need - staged, s, *device);
+}
+
+size_t sageb200_experts_workspace_bytes(const sageb200_expert_stack *stacks_host, int stack_count,
+                                        int slots) {
+  if (!stacks_host || stack_count <= 0 || slots <= 0) return 0;
+  sageb200_problem problems[SAGEB200_MAX_GROUPED];
+  int count = 0;
+  for (int s = 0; s < slots && count < SAGEB200_MAX_GROUPED; ++s)
+    for (int t = 0; t < stack_count && count < SAGEB200_MAX_GROUPED; ++t) {
+      problems[count] = sageb200_problem{nullptr, nullptr, nullptr, nullptr, nullptr, stacks_host[t].perm,
+                                         nullptr, 1, stacks_host[t].n, stacks_host[t].k,
+                                         stacks_host[t].entries};
+      ++count;
+    }
+  return sageb200_grouped_workspace_bytes(problems, count);
+}
+
+int sageb200_experts(const void *x, long long x_slot_stride, const sageb200_expert_stack *stacks_host,
+                     void *const *ys_host, int stack_count, const int32_t *expert_ids, int slots,
+                     void *workspace, size_t workspace_bytes, void *stream) {
+  if (!x || !stacks_host || !ys_host || !expert_ids || stack_count <= 0 || stack_count > SAGEB200_MAX_GROUPED ||
+      slots < 0 || x_slot_stride < 0)
+    return SAGEB200_ERR_INVALID_ARGUMENT;
+  if (slots == 0) return SAGEB200_OK;
+  DeviceState *device = nullptr;
+  int status = device_state(&device);
+  if (status) return status;
+  cudaStream_t s = static_cast<cudaStream_t>(stream);
+  const int slots_per_launch = SAGEB200_MAX_GROUPED / stack_count;
+  for (int begin = 0; begin < slots; begin += slots_per_launch) {
+    sageb200_problem problems[SAGEB200_MAX_GROUPED];
+    ExpertRef refs[SAGEB200_MAX_GROUPED];
+    int count = 0;
+    for (int slot = begin; slot < slots && slot < begin + slots_per_launch; ++slot)
+      for (int t = 0; t < stack_count; ++t) {
+        const sageb200_expert_stack &stack = stacks_host[t];
+        if (stack.experts <= 0 || !ys_host[t]) return SAGEB200_ERR_INVALID_ARGUMENT;
+        sageb200_problem &p = problems[count];
+        p = sageb200_problem{static_cast<const __half *>(x) + slot * x_slot_stride, stack.codes, stack.radii,
+                             stack.grid, stack.book, stack.perm,
+                             static_cast<__half *>(ys_host[t]) + static_cast<size_t>(slot) * stack.n, 1,
+                             stack.n, stack.k, stack.entries};
+        status = validate_problem(p);
+        if (status) return status;
+        const long long tiles = (stack.n + 15) / 16, groups = stack.k / 128;
+        refs[count] = ExpertRef{expert_ids, slot, stack.first_expert, stack.experts,
+                                tiles * groups * 128, tiles * groups * 16, 4ll * stack.entries};
+        ++count;
+      }
+    status = run_skinny(problems, count, workspace, workspace_bytes, s, *device, nullptr, refs);
+    if (status) return status;
+  }
+  return SAGEB200_OK;
 }
 
 /* ---------------------------------------------------------------------------------------

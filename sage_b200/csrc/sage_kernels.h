@@ -29,6 +29,11 @@ struct SkinnyProblem {
   int whole_tiles;      // 1: CTAs own whole tiles (no sharing); 0: even share of units
   int share_q, share_r; // (tiles or units) / ctas_per_slice and remainder, for slices == 1
   int cta_begin;        // first CTA of this problem in the grid
+  // expert indirection (null: none): the weights are those of expert expert_ids[expert_slot]
+  // inside a stack of expert_count experts starting at global expert expert_first
+  const int *expert_ids;
+  int expert_slot, expert_first, expert_count;
+  long long codes_stride, cell_stride, book_stride;  // per-expert strides in 32-bit words
 };
 
 struct SkinnyParams {

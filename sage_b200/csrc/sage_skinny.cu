@@ -102,7 +102,18 @@ __global__ void __launch_bounds__(512, 1) sage_skinny_kernel(const __grid_consta
     while (pi + 1 < params.count && static_cast<int>(blockIdx.x) >= params.problem[pi + 1].cta_begin)
       ++pi;
   }
-  const SkinnyProblem &p = params.problem[pi];
+  SkinnyProblem p = params.problem[pi];
+  if (p.expert_ids) {
+    // routed expert: pick this slot's expert out of the stack; an expert that lives on
+    // another rank leaves y as the caller zeroed it
+    const int expert = __ldg(p.expert_ids + p.expert_slot) - p.expert_first;
+    if (expert < 0 || expert >= p.expert_count) return;
+    p.codes += expert * p.codes_stride;
+    p.radii += expert * p.cell_stride;
+    p.grid += expert * p.cell_stride;
+    p.book += expert * p.book_stride;
+    if (p.perm) p.perm += static_cast<long long>(expert) * p.k;
+  }
 
   const int tid = threadIdx.x;
   const int threads = blockDim.x;

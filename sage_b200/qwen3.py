@@ -24,6 +24,7 @@ import torch
 
 from . import _lib
 from .ops import sage_dequantize, sage_grouped
+from .experts import SAGEExperts, expert_slice, route, synthetic_expert_stack
 from .parallel import block_permutation, shard_columns, shard_rows, shard_vocab
 from .synthetic import linear_algorithmic_bytes, synthetic_sage_device
 
@@ -40,9 +41,14 @@ class Qwen3Config:
     eps: float = 1e-6
     rope_theta: float = 1e6
     name: str = "qwen3"
+    experts: int = 0           # > 0: mixture-of-experts MLP (Qwen3-MoE)
+    top_k: int = 0
+    moe_intermediate: int = 0
 
 
 QWEN3_4B = Qwen3Config(layers=36, hidden=2560, heads=32, kv_heads=8, intermediate=9728, name="Qwen3-4B")
+QWEN3_30B_A3B = Qwen3Config(layers=48, hidden=2048, heads=32, kv_heads=4, intermediate=6144, experts=128,
+                            top_k=8, moe_intermediate=768, name="Qwen3-30B-A3B")
 QWEN3_32B = Qwen3Config(layers=64, hidden=5120, heads=64, kv_heads=8, intermediate=25600, name="Qwen3-32B")
 
 
@@ -88,11 +94,14 @@ class PackedQwen3:
 
     def __init__(self, config: Qwen3Config, device, *, seed: int = 0, max_seq: int = 2560,
                  batch: int = 1, linear: str = "sage", max_new: int = 512, tp_group=None,
-                 perm_blocks: int = 1):
+                 perm_blocks: int = 1, ep_group=None):
         """`tp_group`: a torch.distributed process group for tensor parallelism (q/k/v/gate/up
         column-parallel, o/down row-parallel with an all-reduce, vocabulary-parallel lm_head
         with an all-gather); every rank must pass the same seed.  `perm_blocks`: o/down use
-        a block permutation with this many blocks (a multiple of the group size)."""
+        a block permutation with this many blocks (a multiple of the group size).
+        `ep_group`: process group for expert parallelism of a mixture-of-experts config: each
+        rank keeps experts/world contiguous experts, attention and router are replicated, the
+        ranks' expert outputs are summed with an all-reduce."""
         if linear not in ("sage", "dense"):
             raise ValueError("linear must be 'sage' or 'dense'")
         if batch < 1 or batch > 16:
@@ -107,6 +116,15 @@ class PackedQwen3:
         else:
             self.tp_world, self.tp_rank = 1, 0
         world, rank = self.tp_world, self.tp_rank
+        self.ep_group = ep_group
+        if ep_group is not None:
+            import torch.distributed as dist
+
+            self.ep_world, self.ep_rank = dist.get_world_size(ep_group), dist.get_rank(ep_group)
+        else:
+            self.ep_world, self.ep_rank = 1, 0
+        if config.experts and (config.experts % self.ep_world or world != 1):
+            raise ValueError("experts must divide by the EP size; MoE configs do not combine with TP here")
         if config.heads % world or config.kv_heads % world or config.intermediate % (128 * world) or config.vocab % world:
             raise ValueError("heads, kv heads, intermediate/128 and vocabulary must divide by the TP size")
         if world > 1 and perm_blocks % world:
@@ -134,10 +152,36 @@ class PackedQwen3:
         for _ in range(c.layers):
             layer = {}
             for name, k, n, kind in shapes:
+                if c.experts and name in ("gate", "up", "down"):
+                    continue
                 layer[name] = PackedLinear(k, n, seed * 100003 + index, self.device, self.dense, kind=kind,
                                            rank=rank, world=world, perm_blocks=perm_blocks)
                 self.packed_bytes += layer[name].bytes
                 index += 1
+            if c.experts:
+                local = c.experts // self.ep_world
+                first = self.ep_rank * local
+                base = (seed * 100003 + index) * 7919
+                stacks = []
+                for j, (k, n) in enumerate(((c.hidden, c.moe_intermediate), (c.hidden, c.moe_intermediate),
+                                            (c.moe_intermediate, c.hidden))):
+                    # every rank draws its own block of the same global experts
+                    stacks.append(synthetic_expert_stack(k, n, local, base + j, self.device,
+                                                         direction_bits=6 + (index + j) % 3, first=first))
+                    self.packed_bytes += c.top_k * linear_algorithmic_bytes(1, n, k, 1 << (6 + (index + j) % 3), True)
+                if self.dense:
+                    from .ops import sage_dequantize as dq
+
+                    layer["expert_weights"] = [
+                        torch.stack([dq(*[expert_slice(stack, e)[key] for key in ("packed_codes", "radius_codes", "radius_grid", "codebook", "permutation")], n)
+                                     for e in range(local)])
+                        for stack, n in zip(stacks, (c.moe_intermediate, c.moe_intermediate, c.hidden))
+                    ]
+                else:
+                    layer["experts"] = SAGEExperts(*stacks, first_expert=first)
+                layer["first_expert"], layer["local_experts"] = first, local
+                layer["router"] = (torch.randn(c.experts, c.hidden, generator=gen, device=self.device) * 0.5).half()
+                index += 3
             layer["input_norm"] = norm_weight(c.hidden)
             layer["post_norm"] = norm_weight(c.hidden)
             layer["q_norm"] = norm_weight(c.head_dim)
@@ -222,6 +266,8 @@ class PackedQwen3:
             "attention_decode")
         (o,) = self._linears(layer, ("o",), self.attn)
         self._all_reduce(o)
+        if c.experts:
+            return self._moe(layer, o)
         gate, up = self._norm_linears(layer, ("gate", "up"), o, layer["post_norm"])
         if self.dense or not self.fuse:
             self._check(lib.sageb200_glue_swiglu(_vp(gate), _vp(up), _vp(self.act), gate.numel(), s), "swiglu")
@@ -230,6 +276,32 @@ class PackedQwen3:
             (down,) = self._linears(layer, ("down",), self.act, (2, 0.0, gate, up, None, None))
         self._all_reduce(down)
         return down
+
+    def _moe(self, layer, o):
+        """Mixture-of-experts MLP: norm, FP16 router, top-k routing on the GPU, routed packed
+        experts (this rank's block), all-reduce over the expert-parallel group."""
+        c, lib, b = self.config, self.lib, self.batch
+        self._check(lib.sageb200_glue_add_rmsnorm(_vp(self.h), _vp(o), _vp(layer["post_norm"]), _vp(self.x), b,
+                                                  c.hidden, c.eps, self._stream()), "add_rmsnorm")
+        ids, weights = route(torch.nn.functional.linear(self.x, layer["router"]), c.top_k)
+        if self.dense:
+            gate_w, up_w, down_w = layer["expert_weights"]
+            local = ids.long() - layer["first_expert"]
+            mine = (local >= 0) & (local < layer["local_experts"])
+            index = local.clamp(0, layer["local_experts"] - 1)
+            x = self.x[:, None, :, None]                                        # [b, 1, hidden, 1]
+            g = torch.matmul(gate_w[index], x).squeeze(-1)                       # [b, top_k, inter]
+            u = torch.matmul(up_w[index], x).squeeze(-1)
+            act = torch.nn.functional.silu(g.float()).half() * u
+            d = torch.matmul(down_w[index], act[..., None]).squeeze(-1)          # [b, top_k, hidden]
+            out = (d.float() * (weights * mine)[..., None]).sum(dim=1).half()
+        else:
+            out = layer["experts"](self.x, ids, weights)
+        if self.ep_world > 1:
+            import torch.distributed as dist
+
+            dist.all_reduce(out, group=self.ep_group)
+        return out
 
     def _body(self):
         c, lib, b = self.config, self.lib, self.batch

@@ -119,3 +119,45 @@ def test_generate_is_repeatable_and_batched():
         # batch sizes, so allow a late near-tie flip but require a long common prefix
         same = (alone[0] == first[row]).long().cumprod(0).sum().item()
         assert same >= 8, (row, same)
+
+
+def test_routed_experts_match_per_expert_linears():
+    """`SAGEExperts` (device-side expert selection, stacked buffers) against one `SAGELinear`
+    per routed expert, for one token and for several; and the expert-parallel split: two
+    half-stacks sum to the full stack's output."""
+    from sage_b200 import SAGELinear
+    from sage_b200.experts import SAGEExperts, expert_slice, route, synthetic_expert_stack
+
+    hidden, inter, experts, top_k = 512, 256, 8, 3
+    gate = synthetic_expert_stack(hidden, inter, experts, 1, "cuda")
+    up = synthetic_expert_stack(hidden, inter, experts, 2, "cuda")
+    down = synthetic_expert_stack(inter, hidden, experts, 3, "cuda")
+    module = SAGEExperts(gate, up, down)
+    for tokens in (1, 4):
+        gen = torch.Generator(device="cuda").manual_seed(tokens)
+        x = torch.randn(tokens, hidden, generator=gen, device="cuda").half()
+        ids, weights = route(torch.randn(tokens, experts, generator=gen, device="cuda"), top_k)
+        got = module(x, ids, weights)
+        want = torch.zeros(tokens, hidden, device="cuda")
+        for t in range(tokens):
+            for j in range(top_k):
+                e = int(ids[t, j])
+                g = SAGELinear(expert_slice(gate, e), inter)(x[t : t + 1])
+                u = SAGELinear(expert_slice(up, e), inter)(x[t : t + 1])
+                act = torch.nn.functional.silu(g.float()).half() * u
+                want[t] += weights[t, j] * SAGELinear(expert_slice(down, e), hidden)(act)[0].float()
+        assert ((got.float() - want).norm() / want.norm()).item() < 2e-3
+        halves = [
+            SAGEExperts(*[{k: v[lo : lo + 4].contiguous() for k, v in stack.items()} for stack in (gate, up, down)],
+                        first_expert=lo)(x, ids, weights)
+            for lo in (0, 4)
+        ]
+        both = halves[0].float() + halves[1].float()
+        assert ((both - got.float()).norm() / got.float().norm()).item() < 2e-3
+
+
+def test_greedy_tokens_small_moe_model():
+    config = Qwen3Config(layers=2, hidden=512, heads=4, kv_heads=2, intermediate=1024, vocab=4096,
+                         experts=8, top_k=2, moe_intermediate=256)
+    mismatches, error = lockstep(config, steps=32, prompt_length=8, seed=3, max_seq=64)
+    check_lockstep(mismatches, error, 32)
