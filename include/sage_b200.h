@@ -223,6 +223,15 @@ int sageb200_linear_host(const void *x_host, const void *codes, const void *radi
 int sageb200_set_tuning(int warps, int slices, int ctas_per_sm, int mode);
 
 /*
+ * Programmatic dependent launch (on by default): the decode kernel and the decode glue are
+ * launched so that they may be scheduled before the previous kernel of the stream has
+ * finished; they prefetch packed weights and codebooks, then wait for the previous kernel
+ * before reading activations or writing anything.  0 switches to plain launches (debug).
+ * No counterpart in the reference.
+ */
+int sageb200_set_pdl(int enabled);
+
+/*
  * Profiling aid (debug): while `device_buffer` is non-NULL every CTA of the decode kernel
  * writes 16 SM-clock readings (one per phase of its work) at device_buffer[16*cta ...];
  * the buffer must hold 16 * 8 bytes per CTA of the largest launch.  NULL switches it off.

@@ -6,6 +6,7 @@ There is no fallback: if the library is missing or a call fails, an exception is
 from __future__ import annotations
 
 import ctypes
+import os
 import pathlib
 
 PACKAGE = pathlib.Path(__file__).resolve().parent
@@ -33,6 +34,7 @@ EXPORTED = (
     "sageb200_linear_host",
     "sageb200_set_tuning",
     "sageb200_debug_trace",
+    "sageb200_set_pdl",
     "sageb200_linear_static",
     "sageb200_launch_count",
 )
@@ -148,6 +150,8 @@ def load() -> ctypes.CDLL:
     lib.sageb200_set_tuning.argtypes = [ci, ci, ci, ci]
     lib.sageb200_linear_static.restype = ci
     lib.sageb200_linear_static.argtypes = [vp, vp, vp, vp, vp, vp, vp, ci, ci, ci, ci, vp]
+    lib.sageb200_set_pdl.restype = ci
+    lib.sageb200_set_pdl.argtypes = [ci]
     lib.sageb200_debug_trace.restype = ci
     lib.sageb200_debug_trace.argtypes = [vp]
     lib.sageb200_launch_count.restype = ctypes.c_ulonglong
@@ -170,6 +174,8 @@ def load() -> ctypes.CDLL:
     lib.sageb200_glue_lm_head.argtypes = [vp, vp, vp, ci, ci, ci, ci, vp]
     lib.sageb200_glue_argmax_advance.restype = ci
     lib.sageb200_glue_argmax_advance.argtypes = [vp] * 5 + [ci, ci, ci, vp]
+    if "SAGEB200_PDL" in os.environ:  # debug switch: which kernel families launch dependently
+        lib.sageb200_set_pdl(int(os.environ["SAGEB200_PDL"]))
     _handle = lib
     return lib
 

@@ -13,6 +13,8 @@
 #include <cuda_runtime.h>
 #include <stdint.h>
 
+#include "sage_common.cuh"
+
 namespace {
 
 constexpr int kNormThreads = 256;
@@ -44,6 +46,11 @@ __device__ float block_sum(float v, float *scratch) {
 // h[m][:] = embedding[token[m]][:]
 __global__ void embed_kernel(const __half *__restrict__ table, const long long *__restrict__ tokens,
                              __half *__restrict__ h, int hidden) {
+  // programmatic dependent launch: let the next kernel be scheduled, then wait for the
+  // previous one before touching memory
+  sageb200::pdl_launch_dependents();
+  sageb200::pdl_wait();
+
   const int m = blockIdx.x;
   const __half *row = table + static_cast<size_t>(tokens[m]) * hidden;
   for (int i = threadIdx.x; i < hidden / 8; i += blockDim.x)
@@ -57,6 +64,11 @@ __global__ void __launch_bounds__(kNormThreads)
     add_rmsnorm_kernel(__half *__restrict__ residual, const __half *__restrict__ delta,
                        const __half *__restrict__ weight, __half *__restrict__ x, int hidden,
                        float eps) {
+  // programmatic dependent launch: let the next kernel be scheduled, then wait for the
+  // previous one before touching memory
+  sageb200::pdl_launch_dependents();
+  sageb200::pdl_wait();
+
   __shared__ float scratch[32];
   extern __shared__ __half row_shared[];
   const int m = blockIdx.x;
@@ -93,6 +105,11 @@ __global__ void qk_norm_rope_cache_kernel(__half *__restrict__ q, const __half *
                                           const int *__restrict__ positions,
                                           __half *__restrict__ k_cache, __half *__restrict__ v_cache,
                                           int q_heads, int kv_heads, int max_seq, float eps) {
+  // programmatic dependent launch: let the next kernel be scheduled, then wait for the
+  // previous one before touching memory
+  sageb200::pdl_launch_dependents();
+  sageb200::pdl_wait();
+
   const int lane = threadIdx.x & 31;
   const int head = blockIdx.x * (blockDim.x >> 5) + (threadIdx.x >> 5);
   const int m = blockIdx.y;
@@ -143,6 +160,11 @@ __global__ void __launch_bounds__(kAttnWarps * 32)
                              const __half *__restrict__ v_cache, const int *__restrict__ positions,
                              float *__restrict__ partial, int q_heads, int kv_heads, int max_seq,
                              int splits, float scale) {
+  // programmatic dependent launch: let the next kernel be scheduled, then wait for the
+  // previous one before touching memory
+  sageb200::pdl_launch_dependents();
+  sageb200::pdl_wait();
+
   __shared__ float shared_max[kAttnWarps][kMaxGroup];
   __shared__ float shared_sum[kAttnWarps][kMaxGroup];
   __shared__ float shared_acc[kAttnWarps][kMaxGroup][128];
@@ -221,6 +243,11 @@ __global__ void __launch_bounds__(kAttnWarps * 32)
 // out[m][head][:] = sum over splits, softmax-normalised; one warp-quad (128 threads) per head.
 __global__ void attention_combine_kernel(const float *__restrict__ partial, __half *__restrict__ out,
                                          int q_heads, int splits) {
+  // programmatic dependent launch: let the next kernel be scheduled, then wait for the
+  // previous one before touching memory
+  sageb200::pdl_launch_dependents();
+  sageb200::pdl_wait();
+
   const int head = blockIdx.x, m = blockIdx.y, dim = threadIdx.x;
   const float *base = partial + (static_cast<size_t>(m) * q_heads + head) * splits * 130;
   float top = -INFINITY;
@@ -239,6 +266,11 @@ __global__ void attention_combine_kernel(const float *__restrict__ partial, __ha
 // silu(gate) to FP16, then the FP16 product.
 __global__ void swiglu_kernel(const __half *__restrict__ gate, const __half *__restrict__ up,
                               __half *__restrict__ act, long long count) {
+  // programmatic dependent launch: let the next kernel be scheduled, then wait for the
+  // previous one before touching memory
+  sageb200::pdl_launch_dependents();
+  sageb200::pdl_wait();
+
   const long long i = static_cast<long long>(blockIdx.x) * blockDim.x + threadIdx.x;
   if (i >= count) return;
   const float g = __half2float(gate[i]);
@@ -253,6 +285,11 @@ constexpr int kHeadWarps = 8;
 __global__ void __launch_bounds__(kHeadWarps * 32)
     lm_head_kernel(const __half *__restrict__ head, const __half *__restrict__ x,
                    __half *__restrict__ logits, int vocab, int hidden, int rows) {
+  // programmatic dependent launch: let the next kernel be scheduled, then wait for the
+  // previous one before touching memory
+  sageb200::pdl_launch_dependents();
+  sageb200::pdl_wait();
+
   extern __shared__ __half x_shared[];
   for (int i = threadIdx.x; i < rows * hidden / 8; i += blockDim.x)
     reinterpret_cast<uint4 *>(x_shared)[i] = reinterpret_cast<const uint4 *>(x)[i];
@@ -295,6 +332,11 @@ __global__ void __launch_bounds__(1024)
     argmax_advance_kernel(const __half *__restrict__ logits, long long *__restrict__ tokens,
                           int *__restrict__ positions, long long *__restrict__ log,
                           int *__restrict__ step, int vocab, int log_stride) {
+  // programmatic dependent launch: let the next kernel be scheduled, then wait for the
+  // previous one before touching memory
+  sageb200::pdl_launch_dependents();
+  sageb200::pdl_wait();
+
   __shared__ float best_value[32];
   __shared__ int best_index[32];
   const int m = blockIdx.x;
@@ -335,7 +377,11 @@ __global__ void __launch_bounds__(1024)
 }
 
 // The step counter advances once per decode step, after every row's argmax has used it.
-__global__ void advance_step_kernel(int *step) { step[0] += 1; }
+__global__ void advance_step_kernel(int *step) {
+  sageb200::pdl_launch_dependents();
+  sageb200::pdl_wait();
+  step[0] += 1;
+}
 
 int launch_status() { return cudaGetLastError() == cudaSuccess ? 0 : -5; }
 
@@ -346,7 +392,7 @@ extern "C" {
 int sageb200_glue_embed(const void *table, const void *tokens, void *h, int rows, int hidden,
                         void *stream) {
   if (hidden % 8) return -1;
-  embed_kernel<<<rows, 128, 0, static_cast<cudaStream_t>(stream)>>>(
+  sageb200::launch_dependent<2>(embed_kernel, rows, 128, 0, static_cast<cudaStream_t>(stream),
       static_cast<const __half *>(table), static_cast<const long long *>(tokens),
       static_cast<__half *>(h), hidden);
   return launch_status();
@@ -355,7 +401,7 @@ int sageb200_glue_embed(const void *table, const void *tokens, void *h, int rows
 int sageb200_glue_add_rmsnorm(void *residual, const void *delta, const void *weight, void *x,
                               int rows, int hidden, float eps, void *stream) {
   if (hidden > 24576) return -1;
-  add_rmsnorm_kernel<<<rows, kNormThreads, hidden * sizeof(__half), static_cast<cudaStream_t>(stream)>>>(
+  sageb200::launch_dependent<2>(add_rmsnorm_kernel, rows, kNormThreads, hidden * sizeof(__half), static_cast<cudaStream_t>(stream),
       static_cast<__half *>(residual), static_cast<const __half *>(delta),
       static_cast<const __half *>(weight), static_cast<__half *>(x), hidden, eps);
   return launch_status();
@@ -369,7 +415,7 @@ int sageb200_glue_qk_norm_rope_cache(void *q, const void *k, const void *v, cons
   if (head_dim != 128) return -1;
   const int heads = q_heads + 2 * kv_heads;
   const dim3 grid((heads + 3) / 4, rows);
-  qk_norm_rope_cache_kernel<<<grid, 128, 0, static_cast<cudaStream_t>(stream)>>>(
+  sageb200::launch_dependent<2>(qk_norm_rope_cache_kernel, grid, 128, 0, static_cast<cudaStream_t>(stream),
       static_cast<__half *>(q), static_cast<const __half *>(k), static_cast<const __half *>(v),
       static_cast<const __half *>(q_weight), static_cast<const __half *>(k_weight),
       static_cast<const __half *>(cos_table), static_cast<const __half *>(sin_table),
@@ -389,11 +435,11 @@ int sageb200_glue_attention_decode(const void *q, const void *k_cache, const voi
   if (head_dim != 128 || q_heads % kv_heads || q_heads / kv_heads > kMaxGroup || splits < 1) return -1;
   cudaStream_t s = static_cast<cudaStream_t>(stream);
   const dim3 grid(splits, kv_heads, rows);
-  attention_partial_kernel<<<grid, kAttnWarps * 32, 0, s>>>(
+  sageb200::launch_dependent<2>(attention_partial_kernel, grid, kAttnWarps * 32, 0, s,
       static_cast<const __half *>(q), static_cast<const __half *>(k_cache),
       static_cast<const __half *>(v_cache), static_cast<const int *>(positions),
       static_cast<float *>(scratch), q_heads, kv_heads, max_seq, splits, rsqrtf(128.0f));
-  attention_combine_kernel<<<dim3(q_heads, rows), 128, 0, s>>>(static_cast<const float *>(scratch),
+  sageb200::launch_dependent<2>(attention_combine_kernel, dim3(q_heads, rows), 128, 0, s, static_cast<const float *>(scratch),
                                                               static_cast<__half *>(out), q_heads,
                                                               splits);
   return launch_status();
@@ -401,7 +447,7 @@ int sageb200_glue_attention_decode(const void *q, const void *k_cache, const voi
 
 int sageb200_glue_swiglu(const void *gate, const void *up, void *act, long long count, void *stream) {
   const unsigned blocks = static_cast<unsigned>((count + 255) / 256);
-  swiglu_kernel<<<blocks, 256, 0, static_cast<cudaStream_t>(stream)>>>(
+  sageb200::launch_dependent<2>(swiglu_kernel, blocks, 256, 0, static_cast<cudaStream_t>(stream),
       static_cast<const __half *>(gate), static_cast<const __half *>(up), static_cast<__half *>(act),
       count);
   return launch_status();
@@ -419,7 +465,7 @@ int sageb200_glue_lm_head(const void *head, const void *x, void *logits, int row
     configured = true;
   }
   const int blocks = (sm_count > 0 ? sm_count : 148) * 4;
-  lm_head_kernel<<<blocks, kHeadWarps * 32, shared, static_cast<cudaStream_t>(stream)>>>(
+  sageb200::launch_dependent<2>(lm_head_kernel, blocks, kHeadWarps * 32, shared, static_cast<cudaStream_t>(stream),
       static_cast<const __half *>(head), static_cast<const __half *>(x), static_cast<__half *>(logits),
       vocab, hidden, rows);
   return launch_status();
@@ -428,12 +474,12 @@ int sageb200_glue_lm_head(const void *head, const void *x, void *logits, int row
 int sageb200_glue_argmax_advance(const void *logits, void *tokens, void *positions, void *log,
                                  void *step, int rows, int vocab, int log_stride, void *stream) {
   cudaStream_t s = static_cast<cudaStream_t>(stream);
-  argmax_advance_kernel<<<rows, 1024, 0, s>>>(static_cast<const __half *>(logits),
+  sageb200::launch_dependent<2>(argmax_advance_kernel, rows, 1024, 0, s, static_cast<const __half *>(logits),
                                                static_cast<long long *>(tokens),
                                                static_cast<int *>(positions),
                                                static_cast<long long *>(log), static_cast<int *>(step),
                                                vocab, log_stride);
-  if (step) advance_step_kernel<<<1, 1, 0, s>>>(static_cast<int *>(step));
+  if (step) sageb200::launch_dependent<2>(advance_step_kernel, 1, 1, 0, s, static_cast<int *>(step));
   return launch_status();
 }
 

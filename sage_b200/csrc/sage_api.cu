@@ -14,6 +14,7 @@
 #include "sage_kernels.h"
 
 namespace sageb200 {
+int g_sageb200_pdl = 3;
 namespace {
 
 constexpr int kMaxDevices = 64;
@@ -506,6 +507,11 @@ int sageb200_linear_host(const void *x_host, const void *codes, const void *radi
     cudaGetLastError();
     return SAGEB200_ERR_CUDA;
   }
+  return SAGEB200_OK;
+}
+
+int sageb200_set_pdl(int enabled) {
+  g_sageb200_pdl = enabled & 3;
   return SAGEB200_OK;
 }
 

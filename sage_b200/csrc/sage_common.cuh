@@ -52,6 +52,36 @@ __device__ __forceinline__ void sts_u4(uint32_t shared_address, uint4 v) {
                "r"(v.y), "r"(v.z), "r"(v.w));
 }
 
+// Programmatic dependent launch.  A kernel calls pdl_launch_dependents() as early as it
+// likes (the next kernel in the stream may then be scheduled while this one still runs) and
+// pdl_wait() before its first read of anything an earlier kernel wrote and before its first
+// global write; pdl_wait() returns once all earlier kernels have completed and flushed.
+// Both are no-ops for kernels launched without the attribute.
+__device__ __forceinline__ void pdl_launch_dependents() {
+  asm volatile("griddepcontrol.launch_dependents;" ::: "memory");
+}
+__device__ __forceinline__ void pdl_wait() { asm volatile("griddepcontrol.wait;" ::: "memory"); }
+
+// Host side: launch `kernel` allowing it to start before the previous kernel of `stream`
+// has finished (the kernel must follow the protocol above).
+// `kBit` names the kernel family: 1 = packed-linear kernels, 2 = decode glue.
+extern int g_sageb200_pdl;  // bit mask of families launched this way; 0: plain launches
+template <int kBit = 1, typename... KernelArgs, typename... Args>
+inline cudaError_t launch_dependent(void (*kernel)(KernelArgs...), dim3 grid, dim3 block, size_t shared,
+                                    cudaStream_t stream, Args &&...args) {
+  cudaLaunchConfig_t config = {};
+  config.gridDim = grid;
+  config.blockDim = block;
+  config.dynamicSmemBytes = shared;
+  config.stream = stream;
+  cudaLaunchAttribute attribute[1];
+  attribute[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+  attribute[0].val.programmaticStreamSerializationAllowed = 1;
+  config.attrs = attribute;
+  config.numAttrs = (g_sageb200_pdl & kBit) ? 1 : 0;
+  return cudaLaunchKernelEx(&config, kernel, static_cast<KernelArgs>(args)...);
+}
+
 __device__ __forceinline__ uint32_t smem_address(const void *p) {
   return static_cast<uint32_t>(__cvta_generic_to_shared(p));
 }

@@ -97,6 +97,7 @@ __global__ void __launch_bounds__(512, 1) sage_skinny_kernel(const __grid_consta
   long long *trace = params.trace ? params.trace + 16 * static_cast<size_t>(blockIdx.x) : nullptr;
 #define SAGE_STAMP(i) do { if (trace && threadIdx.x == 0) trace[i] = clock64(); } while (0)
   SAGE_STAMP(0);
+  pdl_launch_dependents();  // the next kernel may be scheduled as SM resources free up
   int pi = 0;
   if (params.count > 1) {
     while (pi + 1 < params.count && static_cast<int>(blockIdx.x) >= params.problem[pi + 1].cta_begin)
@@ -293,6 +294,9 @@ __global__ void __launch_bounds__(512, 1) sage_skinny_kernel(const __grid_consta
       if (q < items) held[it] = load_item(q);
     }
   }
+  // Everything above read only weights, codebook and permutation (never written by a kernel);
+  // from here on the activations of the previous kernel are read and global memory is written.
+  pdl_wait();
   float square_sum = 0.0f;
   if (fused) {
     // the whole row, in original channel order, into the linear buffer (and the norm
@@ -775,11 +779,11 @@ cudaError_t launch_skinny(const SkinnyParams &params, int warps, int column_bloc
   bool low_bits = false;
   for (int i = 0; i < params.count; ++i) low_bits = low_bits || params.problem[i].dbits != 8;
   if (column_blocks == 1) {
-    if (low_bits) sage_skinny_kernel<1, true><<<total_ctas, threads, shared_bytes, stream>>>(params);
-    else sage_skinny_kernel<1, false><<<total_ctas, threads, shared_bytes, stream>>>(params);
+    if (low_bits) return launch_dependent(sage_skinny_kernel<1, true>, total_ctas, threads, shared_bytes, stream, params);
+    return launch_dependent(sage_skinny_kernel<1, false>, total_ctas, threads, shared_bytes, stream, params);
   } else {
-    if (low_bits) sage_skinny_kernel<2, true><<<total_ctas, threads, shared_bytes, stream>>>(params);
-    else sage_skinny_kernel<2, false><<<total_ctas, threads, shared_bytes, stream>>>(params);
+    if (low_bits) return launch_dependent(sage_skinny_kernel<2, true>, total_ctas, threads, shared_bytes, stream, params);
+    return launch_dependent(sage_skinny_kernel<2, false>, total_ctas, threads, shared_bytes, stream, params);
   }
   return cudaGetLastError();
 }
