@@ -402,7 +402,8 @@ def run_model(args) -> None:
                 "context_at_midpoint": context,
                 "step_hbm_bytes": step_bytes,
                 "step_hbm_gbs": step_bytes / (ms_per_step / 1000.0) / 1e9,
-                "kernels_per_step": {"sage_linear": int(model.sage_launches_per_step)},
+                "kernels_per_step": {"sage_linear": int(model.sage_launches_per_step),
+                                     "glue": int(model.glue_launches_per_step)},
                 "l2_policy": "inputs larger than L2: 1.92 GB of weights stream per step",
                 "parallelism": f"replicas x{world}" if world > 1 else "single GPU",
             },
@@ -433,7 +434,7 @@ def run_model(args) -> None:
                 "h2d_bytes_per_step": 8,
                 "d2h_bytes_per_step": 8,
             },
-            "gpu_launches": int(model.sage_launches_per_step * args.steps),
+            "gpu_launches": int((model.sage_launches_per_step + model.glue_launches_per_step) * args.steps),
             "clocks": clocks,
         }
         print(json.dumps(line), flush=True)

@@ -271,6 +271,9 @@ int sageb200_linear_static(const void *x, const void *codes, const void *radii, 
 /* Number of kernels this library has launched in this process (all entry points). */
 unsigned long long sageb200_launch_count(void);
 
+/* Kernels launched so far by the decode glue of sage_b200_decode.h (same purpose). */
+unsigned long long sageb200_glue_launch_count(void);
+
 #ifdef __cplusplus
 }
 #endif

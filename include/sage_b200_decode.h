@@ -54,6 +54,21 @@ int sageb200_glue_attention_decode(const void *q, const void *k_cache, const voi
                                    int q_heads, int kv_heads, int head_dim, int max_seq, int splits,
                                    void *stream);
 
+/*
+ * The three calls above in ONE launch, bit-identical to them: q and the new k are normalised
+ * and rotated (q is left untouched in memory), the new k/v go into the cache at
+ * positions[row], each (row, kv head) is attended in `splits` CTAs and the last CTA to finish
+ * combines the splits.  `scratch` holds sageb200_glue_attention_step_scratch_bytes() bytes
+ * whose first 256*ceil(rows*kv_heads*4/256) bytes (arrival counters) must be zero before the
+ * first call; every call leaves them zero.  Calls sharing one scratch must be stream-ordered.
+ */
+size_t sageb200_glue_attention_step_scratch_bytes(int rows, int q_heads, int kv_heads, int splits);
+int sageb200_glue_attention_step(const void *q, const void *k, const void *v, const void *q_weight,
+                                 const void *k_weight, const void *cos_table, const void *sin_table,
+                                 const void *positions, void *k_cache, void *v_cache, void *out,
+                                 void *scratch, int rows, int q_heads, int kv_heads, int head_dim,
+                                 int max_seq, int splits, float eps, void *stream);
+
 /* act[i] = fp16(silu(gate[i])) * up[i]. */
 int sageb200_glue_swiglu(const void *gate, const void *up, void *act, long long count, void *stream);
 
@@ -67,6 +82,19 @@ int sageb200_glue_lm_head(const void *head, const void *x, void *logits, int row
  */
 int sageb200_glue_argmax_advance(const void *logits, void *tokens, void *positions, void *log,
                                  void *step, int rows, int vocab, int log_stride, void *stream);
+
+/*
+ * The tail of a decode step in ONE launch: x = rmsnorm(residual + delta) * norm_weight (the
+ * arithmetic of sageb200_glue_add_rmsnorm; `residual` itself is not updated, `delta` may be
+ * NULL), logits = x . head^T, then what sageb200_glue_argmax_advance does.  `scratch` holds
+ * sageb200_glue_lm_head_step_scratch_bytes() bytes whose first 256 (an arrival counter) must
+ * be zero before the first call; every call leaves them zero.
+ */
+size_t sageb200_glue_lm_head_step_scratch_bytes(int rows, int sm_count);
+int sageb200_glue_lm_head_step(const void *head, const void *residual, const void *delta,
+                               const void *norm_weight, void *x, void *logits, void *tokens,
+                               void *positions, void *log, void *step, void *scratch, int rows, int vocab,
+                               int hidden, float eps, int log_stride, int sm_count, void *stream);
 
 #ifdef __cplusplus
 }

@@ -37,6 +37,7 @@ EXPORTED = (
     "sageb200_set_pdl",
     "sageb200_linear_static",
     "sageb200_launch_count",
+    "sageb200_glue_launch_count",
 )
 
 
@@ -47,6 +48,10 @@ EXPORTED_DECODE = (
     "sageb200_glue_qk_norm_rope_cache",
     "sageb200_glue_attention_scratch_bytes",
     "sageb200_glue_attention_decode",
+    "sageb200_glue_attention_step_scratch_bytes",
+    "sageb200_glue_attention_step",
+    "sageb200_glue_lm_head_step_scratch_bytes",
+    "sageb200_glue_lm_head_step",
     "sageb200_glue_swiglu",
     "sageb200_glue_lm_head",
     "sageb200_glue_argmax_advance",
@@ -156,6 +161,8 @@ def load() -> ctypes.CDLL:
     lib.sageb200_debug_trace.argtypes = [vp]
     lib.sageb200_launch_count.restype = ctypes.c_ulonglong
     lib.sageb200_launch_count.argtypes = []
+    lib.sageb200_glue_launch_count.restype = ctypes.c_ulonglong
+    lib.sageb200_glue_launch_count.argtypes = []
     # decode glue (include/sage_b200_decode.h)
     fl, ll = ctypes.c_float, ctypes.c_longlong
     lib.sageb200_glue_embed.restype = ci
@@ -166,6 +173,14 @@ def load() -> ctypes.CDLL:
     lib.sageb200_glue_qk_norm_rope_cache.argtypes = [vp] * 10 + [ci] * 5 + [fl, vp]
     lib.sageb200_glue_attention_scratch_bytes.restype = sz
     lib.sageb200_glue_attention_scratch_bytes.argtypes = [ci, ci, ci]
+    lib.sageb200_glue_attention_step_scratch_bytes.restype = sz
+    lib.sageb200_glue_attention_step_scratch_bytes.argtypes = [ci] * 4
+    lib.sageb200_glue_attention_step.restype = ci
+    lib.sageb200_glue_attention_step.argtypes = [vp] * 12 + [ci] * 6 + [ctypes.c_float, vp]
+    lib.sageb200_glue_lm_head_step_scratch_bytes.restype = sz
+    lib.sageb200_glue_lm_head_step_scratch_bytes.argtypes = [ci, ci]
+    lib.sageb200_glue_lm_head_step.restype = ci
+    lib.sageb200_glue_lm_head_step.argtypes = [vp] * 11 + [ci] * 3 + [ctypes.c_float, ci, ci, vp]
     lib.sageb200_glue_attention_decode.restype = ci
     lib.sageb200_glue_attention_decode.argtypes = [vp] * 6 + [ci] * 6 + [vp]
     lib.sageb200_glue_swiglu.restype = ci

@@ -262,6 +262,188 @@ __global__ void attention_combine_kernel(const float *__restrict__ partial, __ha
   out[(static_cast<size_t>(m) * q_heads + head) * 128 + dim] = __float2half_rn(value / sum);
 }
 
+// The whole attention step of one new token per sequence in ONE launch: per-head RMSNorm +
+// RoPE of q and of the new k, the new k/v written into the cache, attention over the context
+// split across CTAs, and the combination of the splits by the last CTA of each (sequence,
+// kv head) to arrive (a counter in `counters`, zero before the launch and zero again after).
+// CTA = (split, kv head, sequence).  Arithmetic and rounding are those of the three kernels
+// above, so the result is bit-identical to running them one after the other.
+__device__ __forceinline__ void norm_rope_head(const __half *source, const __half *weight,
+                                               const __half *cos_row, const __half *sin_row,
+                                               float eps, int lane, __half2 &out_lo, __half2 &out_hi) {
+  const __half2 lo = reinterpret_cast<const __half2 *>(source)[lane];
+  const __half2 hi = reinterpret_cast<const __half2 *>(source + 64)[lane];
+  const float2 lof = __half22float2(lo), hif = __half22float2(hi);
+  const float square = warp_sum(lof.x * lof.x + lof.y * lof.y + hif.x * hif.x + hif.y * hif.y);
+  const float scale = rsqrtf(square / 128.0f + eps);
+  const __half2 wl = reinterpret_cast<const __half2 *>(weight)[lane];
+  const __half2 wh = reinterpret_cast<const __half2 *>(weight + 64)[lane];
+  const __half2 nl = __hmul2(wl, __floats2half2_rn(lof.x * scale, lof.y * scale));
+  const __half2 nh = __hmul2(wh, __floats2half2_rn(hif.x * scale, hif.y * scale));
+  const __half2 c = reinterpret_cast<const __half2 *>(cos_row)[lane];
+  const __half2 s = reinterpret_cast<const __half2 *>(sin_row)[lane];
+  out_lo = __hadd2(__hmul2(nl, c), __hmul2(__hneg2(nh), s));
+  out_hi = __hadd2(__hmul2(nh, c), __hmul2(nl, s));
+}
+
+// kGroup = query heads per kv head when it is 1, 2, 4 or 8 (arrays stay in registers), 0 = any.
+template <int kGroup>
+__global__ void __launch_bounds__(kAttnWarps * 32)
+    attention_step_kernel(const __half *__restrict__ q, const __half *__restrict__ k,
+                          const __half *__restrict__ v, const __half *__restrict__ q_weight,
+                          const __half *__restrict__ k_weight, const __half *__restrict__ cos_table,
+                          const __half *__restrict__ sin_table, const int *__restrict__ positions,
+                          __half *k_cache, __half *v_cache, float *partial, unsigned *counters,
+                          __half *__restrict__ out, int q_heads, int kv_heads, int max_seq, int splits,
+                          float eps, float scale) {
+  sageb200::pdl_launch_dependents();
+  sageb200::pdl_wait();
+
+  __shared__ float shared_max[kAttnWarps][kMaxGroup];
+  __shared__ float shared_sum[kAttnWarps][kMaxGroup];
+  __shared__ float shared_acc[kAttnWarps][kMaxGroup][128];
+  __shared__ __align__(16) __half q_shared[kMaxGroup][128];
+  __shared__ __align__(16) __half new_k[128], new_v[128];
+  __shared__ int is_last;
+  const int split = blockIdx.x, kv = blockIdx.y, m = blockIdx.z;
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  const int group = kGroup ? kGroup : q_heads / kv_heads;
+  constexpr int kUnroll = kGroup ? kGroup : kMaxGroup;
+  const int position = positions[m];
+  const bool in_range = position >= 0 && position < max_seq;  // a full cache takes no new token
+  const int table_row = min(max(position, 0), max_seq - 1);
+  const int context = min(position + 1, max_seq);
+  const int chunk = (context + splits - 1) / splits;
+  const int begin = split * chunk;
+  const int end = min(context, begin + chunk);
+  const bool owns_new = in_range && begin <= position && position < end;
+  const __half *cos_row = cos_table + static_cast<size_t>(table_row) * 64;
+  const __half *sin_row = sin_table + static_cast<size_t>(table_row) * 64;
+  __half *k_base = k_cache + (static_cast<size_t>(m) * kv_heads + kv) * max_seq * 128;
+  __half *v_base = v_cache + (static_cast<size_t>(m) * kv_heads + kv) * max_seq * 128;
+
+  // items 0..group-1: the group's query heads; item `group`: the new token's key and value
+  for (int item = warp; item < group + (owns_new ? 1 : 0); item += kAttnWarps) {
+    __half2 lo, hi;
+    if (item < group) {
+      norm_rope_head(q + (static_cast<size_t>(m) * q_heads + kv * group + item) * 128, q_weight, cos_row,
+                     sin_row, eps, lane, lo, hi);
+      reinterpret_cast<__half2 *>(q_shared[item])[lane] = lo;
+      reinterpret_cast<__half2 *>(q_shared[item] + 64)[lane] = hi;
+    } else {
+      norm_rope_head(k + (static_cast<size_t>(m) * kv_heads + kv) * 128, k_weight, cos_row, sin_row, eps,
+                     lane, lo, hi);
+      reinterpret_cast<__half2 *>(new_k)[lane] = lo;
+      reinterpret_cast<__half2 *>(new_k + 64)[lane] = hi;
+      reinterpret_cast<__half2 *>(k_base + static_cast<size_t>(position) * 128)[lane] = lo;
+      reinterpret_cast<__half2 *>(k_base + static_cast<size_t>(position) * 128 + 64)[lane] = hi;
+      const uint2 value = reinterpret_cast<const uint2 *>(v + (static_cast<size_t>(m) * kv_heads + kv) * 128)[lane];
+      reinterpret_cast<uint2 *>(new_v)[lane] = value;
+      reinterpret_cast<uint2 *>(v_base + static_cast<size_t>(position) * 128)[lane] = value;
+    }
+  }
+  __syncthreads();
+
+  // lane holds dims 4*lane .. 4*lane+3
+  float2 qa[kUnroll], qb[kUnroll];
+#pragma unroll
+  for (int g = 0; g < kUnroll; ++g) {
+    const __half2 *qh = reinterpret_cast<const __half2 *>(q_shared[g < group ? g : 0] + 4 * lane);
+    qa[g] = __half22float2(qh[0]);
+    qb[g] = __half22float2(qh[1]);
+  }
+  float running_max[kUnroll], running_sum[kUnroll], acc[kUnroll][4];
+#pragma unroll
+  for (int g = 0; g < kUnroll; ++g) {
+    running_max[g] = -INFINITY;
+    running_sum[g] = 0.0f;
+    acc[g][0] = acc[g][1] = acc[g][2] = acc[g][3] = 0.0f;
+  }
+  for (int p = begin + warp; p < end; p += kAttnWarps) {
+    uint2 kw, vw;
+    if (owns_new && p == position) {
+      kw = reinterpret_cast<const uint2 *>(new_k)[lane];
+      vw = reinterpret_cast<const uint2 *>(new_v)[lane];
+    } else {
+      kw = __ldcg(reinterpret_cast<const uint2 *>(k_base + static_cast<size_t>(p) * 128) + lane);
+      vw = __ldcg(reinterpret_cast<const uint2 *>(v_base + static_cast<size_t>(p) * 128) + lane);
+    }
+    const float2 ka = __half22float2(*reinterpret_cast<const __half2 *>(&kw.x));
+    const float2 kb = __half22float2(*reinterpret_cast<const __half2 *>(&kw.y));
+    const float2 va = __half22float2(*reinterpret_cast<const __half2 *>(&vw.x));
+    const float2 vb = __half22float2(*reinterpret_cast<const __half2 *>(&vw.y));
+#pragma unroll
+    for (int g = 0; g < kUnroll; ++g) {
+      if (g >= group) break;
+      float dot = qa[g].x * ka.x + qa[g].y * ka.y + qb[g].x * kb.x + qb[g].y * kb.y;
+      dot = warp_sum(dot) * scale;
+      const float new_max = fmaxf(running_max[g], dot);
+      const float rescale = __expf(running_max[g] - new_max);
+      const float weight = __expf(dot - new_max);
+      running_sum[g] = running_sum[g] * rescale + weight;
+      acc[g][0] = acc[g][0] * rescale + weight * va.x;
+      acc[g][1] = acc[g][1] * rescale + weight * va.y;
+      acc[g][2] = acc[g][2] * rescale + weight * vb.x;
+      acc[g][3] = acc[g][3] * rescale + weight * vb.y;
+      running_max[g] = new_max;
+    }
+  }
+#pragma unroll
+  for (int g = 0; g < kUnroll; ++g) {
+    if (g >= group) break;
+    if (lane == 0) {
+      shared_max[warp][g] = running_max[g];
+      shared_sum[warp][g] = running_sum[g];
+    }
+    for (int c = 0; c < 4; ++c) shared_acc[warp][g][4 * lane + c] = acc[g][c];
+  }
+  __syncthreads();
+  // combine the warps: thread = (query head of the group, dim); partial layout
+  // [sequence][query head][split][130] = (max, sum, 128 values)
+  for (int item = threadIdx.x; item < group * 128; item += blockDim.x) {
+    const int g = item >> 7, dim = item & 127;
+    float top = -INFINITY;
+    for (int w = 0; w < kAttnWarps; ++w) top = fmaxf(top, shared_max[w][g]);
+    float sum = 0.0f, value = 0.0f;
+    for (int w = 0; w < kAttnWarps; ++w) {
+      const float f = shared_max[w][g] == -INFINITY ? 0.0f : __expf(shared_max[w][g] - top);
+      sum += shared_sum[w][g] * f;
+      value += shared_acc[w][g][dim] * f;
+    }
+    float *slot = partial + ((static_cast<size_t>(m) * q_heads + kv * group + g) * splits + split) * 130;
+    if (dim == 0) {
+      slot[0] = top;
+      slot[1] = sum;
+    }
+    slot[2 + dim] = value;
+  }
+  // the last CTA of this (sequence, kv head) to get here combines the splits
+  __threadfence();
+  __syncthreads();
+  if (threadIdx.x == 0) {
+    const unsigned ticket = atomicAdd(&counters[m * kv_heads + kv], 1u);
+    is_last = ticket == static_cast<unsigned>(splits - 1);
+    if (is_last) counters[m * kv_heads + kv] = 0u;  // zero again for the next launch
+  }
+  __syncthreads();
+  if (!is_last) return;
+  __threadfence();
+  for (int item = threadIdx.x; item < group * 128; item += blockDim.x) {
+    const int g = item >> 7, dim = item & 127;
+    const float *base = partial + (static_cast<size_t>(m) * q_heads + kv * group + g) * splits * 130;
+    float top = -INFINITY;
+    for (int s = 0; s < splits; ++s) top = fmaxf(top, __ldcg(base + s * 130));
+    float sum = 0.0f, value = 0.0f;
+    for (int s = 0; s < splits; ++s) {
+      const float mx = __ldcg(base + s * 130);
+      const float f = mx == -INFINITY ? 0.0f : __expf(mx - top);
+      sum += __ldcg(base + s * 130 + 1) * f;
+      value += __ldcg(base + s * 130 + 2 + dim) * f;
+    }
+    out[(static_cast<size_t>(m) * q_heads + kv * group + g) * 128 + dim] = __float2half_rn(value / sum);
+  }
+}
+
 // act = silu(gate) * up, FP32 math on FP16 inputs, rounded as the FP16 modules round:
 // silu(gate) to FP16, then the FP16 product.
 __global__ void swiglu_kernel(const __half *__restrict__ gate, const __half *__restrict__ up,
@@ -323,6 +505,174 @@ __global__ void __launch_bounds__(kHeadWarps * 32)
       const float total = warp_sum(sums[m]);
       if (lane == 0) logits[static_cast<size_t>(m) * vocab + v] = __float2half_rn(total);
     }
+  }
+}
+
+// The tail of a decode step in ONE launch: final residual add + RMSNorm (recomputed by every
+// CTA, same arithmetic and summation order as add_rmsnorm_kernel), the lm_head rows of this
+// CTA, and the greedy argmax: every CTA leaves its best (value, index) per sequence in
+// `block_best`, and the last CTA to arrive (a counter, zero before and after the launch) picks
+// the overall best (lowest index on ties), appends it to the log and advances positions and
+// the step counter.  The residual stream itself is left as it was.
+__device__ __forceinline__ bool better(float value, int index, float than_value, int than_index) {
+  return value > than_value || (value == than_value && index < than_index);
+}
+
+// kRows bounds `rows` (1, 4 or 16) so that the per-row sums stay in registers.
+template <int kRows>
+__global__ void __launch_bounds__(kHeadWarps * 32)
+    lm_head_step_kernel(const __half *__restrict__ head, const __half *__restrict__ residual,
+                        const __half *__restrict__ delta, const __half *__restrict__ norm_weight,
+                        __half *__restrict__ x_out, __half *__restrict__ logits,
+                        long long *__restrict__ tokens, int *__restrict__ positions,
+                        long long *__restrict__ log, int *__restrict__ step, float2 *block_best,
+                        unsigned *counter, int vocab, int hidden, int rows, float eps, int log_stride) {
+  sageb200::pdl_launch_dependents();
+  sageb200::pdl_wait();
+
+  extern __shared__ __half x_shared[];
+  __shared__ float scratch[32];
+  __shared__ float best_value[kHeadWarps][16];
+  __shared__ int best_index[kHeadWarps][16];
+  __shared__ int is_last;
+  static_assert(kHeadWarps * 32 == kNormThreads, "the norm must sum in add_rmsnorm_kernel's order");
+  for (int m = 0; m < rows; ++m) {
+    const __half *r = residual + static_cast<size_t>(m) * hidden;
+    const __half *d = delta ? delta + static_cast<size_t>(m) * hidden : nullptr;
+    __half *row_shared = x_shared + static_cast<size_t>(m) * hidden;
+    float square = 0.0f;
+    for (int i = threadIdx.x; i < hidden; i += kNormThreads) {
+      __half v = r[i];
+      if (d) v = __hadd(v, d[i]);
+      row_shared[i] = v;
+      const float f = __half2float(v);
+      square += f * f;
+    }
+    const float total = block_sum(square, scratch);
+    const float scale = rsqrtf(total / hidden + eps);
+    for (int i = threadIdx.x; i < hidden; i += kNormThreads) {
+      const __half normed = __float2half_rn(__half2float(row_shared[i]) * scale);
+      const __half value = __hmul(norm_weight[i], normed);
+      row_shared[i] = value;
+      if (blockIdx.x == 0) x_out[static_cast<size_t>(m) * hidden + i] = value;
+    }
+  }
+  __syncthreads();
+  const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
+  const int pieces = hidden / 8;
+  float top_value[kRows];
+  int top_index[kRows];
+#pragma unroll
+  for (int m = 0; m < kRows; ++m) {
+    top_value[m] = -INFINITY;
+    top_index[m] = 0x7fffffff;
+  }
+  for (int v = blockIdx.x * kHeadWarps + warp; v < vocab; v += gridDim.x * kHeadWarps) {
+    const uint4 *row = reinterpret_cast<const uint4 *>(head + static_cast<size_t>(v) * hidden);
+    float sums[kRows];
+#pragma unroll
+    for (int m = 0; m < kRows; ++m) sums[m] = 0.0f;
+    for (int first = lane; first < pieces; first += 128) {  // four 16-byte loads in flight per lane
+      uint4 w4[4];
+#pragma unroll
+      for (int j = 0; j < 4; ++j)
+        if (first + 32 * j < pieces) w4[j] = sageb200::ldg_stream_u4(row + first + 32 * j);
+#pragma unroll
+      for (int j = 0; j < 4; ++j) {
+        const int i = first + 32 * j;
+        if (i >= pieces) break;
+        const __half2 *wh = reinterpret_cast<const __half2 *>(&w4[j]);
+#pragma unroll
+        for (int m = 0; m < kRows; ++m) {
+          if (m >= rows) break;
+          const uint4 a = reinterpret_cast<const uint4 *>(x_shared + static_cast<size_t>(m) * hidden)[i];
+          const __half2 *ah = reinterpret_cast<const __half2 *>(&a);
+          float s = sums[m];
+#pragma unroll
+          for (int c = 0; c < 4; ++c) {
+            const float2 wf = __half22float2(wh[c]), af = __half22float2(ah[c]);
+            s = fmaf(wf.x, af.x, s);
+            s = fmaf(wf.y, af.y, s);
+          }
+          sums[m] = s;
+        }
+      }
+    }
+#pragma unroll
+    for (int m = 0; m < kRows; ++m) {
+      if (m < rows) {
+        const __half rounded = __float2half_rn(warp_sum(sums[m]));
+        if (lane == 0) logits[static_cast<size_t>(m) * vocab + v] = rounded;
+        const float f = __half2float(rounded);
+        if (better(f, v, top_value[m], top_index[m])) {
+          top_value[m] = f;
+          top_index[m] = v;
+        }
+      }
+    }
+  }
+#pragma unroll
+  for (int m = 0; m < kRows; ++m)
+    if (m < rows && lane == 0) {
+      best_value[warp][m] = top_value[m];
+      best_index[warp][m] = top_index[m];
+    }
+  __syncthreads();
+  if (threadIdx.x < rows) {
+    const int m = threadIdx.x;
+    float value = best_value[0][m];
+    int index = best_index[0][m];
+    for (int w = 1; w < kHeadWarps; ++w)
+      if (better(best_value[w][m], best_index[w][m], value, index)) {
+        value = best_value[w][m];
+        index = best_index[w][m];
+      }
+    block_best[static_cast<size_t>(blockIdx.x) * rows + m] = make_float2(value, __int_as_float(index));
+  }
+  __threadfence();
+  __syncthreads();
+  if (threadIdx.x == 0) is_last = atomicAdd(counter, 1u) == gridDim.x - 1;
+  __syncthreads();
+  if (!is_last) return;
+  __threadfence();
+  for (int m = 0; m < rows; ++m) {
+    float value = -INFINITY;
+    int index = 0x7fffffff;
+    for (int b = threadIdx.x; b < static_cast<int>(gridDim.x); b += blockDim.x) {
+      const float2 candidate = __ldcg(block_best + static_cast<size_t>(b) * rows + m);
+      if (better(candidate.x, __float_as_int(candidate.y), value, index)) {
+        value = candidate.x;
+        index = __float_as_int(candidate.y);
+      }
+    }
+    for (int o = 16; o; o >>= 1) {
+      const float other = __shfl_xor_sync(0xffffffffu, value, o);
+      const int other_index = __shfl_xor_sync(0xffffffffu, index, o);
+      if (better(other, other_index, value, index)) {
+        value = other;
+        index = other_index;
+      }
+    }
+    __syncthreads();
+    if (lane == 0) {
+      best_value[warp][0] = value;
+      best_index[warp][0] = index;
+    }
+    __syncthreads();
+    if (threadIdx.x == 0) {
+      for (int w = 1; w < kHeadWarps; ++w)
+        if (better(best_value[w][0], best_index[w][0], value, index)) {
+          value = best_value[w][0];
+          index = best_index[w][0];
+        }
+      tokens[m] = index;
+      if (log && step && step[0] < log_stride) log[static_cast<size_t>(m) * log_stride + step[0]] = index;
+      positions[m] += 1;
+    }
+  }
+  if (threadIdx.x == 0) {
+    if (step) step[0] += 1;
+    *counter = 0u;  // zero again for the next launch
   }
 }
 
@@ -445,6 +795,38 @@ int sageb200_glue_attention_decode(const void *q, const void *k_cache, const voi
   return launch_status();
 }
 
+size_t sageb200_glue_attention_step_scratch_bytes(int rows, int q_heads, int kv_heads, int splits) {
+  const size_t counters = (static_cast<size_t>(rows) * kv_heads * sizeof(unsigned) + 255) / 256 * 256;
+  return counters + static_cast<size_t>(rows) * q_heads * splits * 130 * sizeof(float);
+}
+
+int sageb200_glue_attention_step(const void *q, const void *k, const void *v, const void *q_weight,
+                                 const void *k_weight, const void *cos_table, const void *sin_table,
+                                 const void *positions, void *k_cache, void *v_cache, void *out,
+                                 void *scratch, int rows, int q_heads, int kv_heads, int head_dim,
+                                 int max_seq, int splits, float eps, void *stream) {
+  if (head_dim != 128 || kv_heads < 1 || q_heads % kv_heads || q_heads / kv_heads > kMaxGroup || splits < 1 ||
+      max_seq < 1)
+    return -1;
+  const size_t counters = (static_cast<size_t>(rows) * kv_heads * sizeof(unsigned) + 255) / 256 * 256;
+  const dim3 grid(splits, kv_heads, rows);
+  const int group = q_heads / kv_heads;
+  auto kernel = group == 1   ? attention_step_kernel<1>
+                : group == 2 ? attention_step_kernel<2>
+                : group == 4 ? attention_step_kernel<4>
+                : group == 8 ? attention_step_kernel<8>
+                             : attention_step_kernel<0>;
+  sageb200::launch_dependent<2>(
+      kernel, grid, kAttnWarps * 32, 0, static_cast<cudaStream_t>(stream),
+      static_cast<const __half *>(q), static_cast<const __half *>(k), static_cast<const __half *>(v),
+      static_cast<const __half *>(q_weight), static_cast<const __half *>(k_weight),
+      static_cast<const __half *>(cos_table), static_cast<const __half *>(sin_table),
+      static_cast<const int *>(positions), static_cast<__half *>(k_cache), static_cast<__half *>(v_cache),
+      reinterpret_cast<float *>(static_cast<char *>(scratch) + counters), static_cast<unsigned *>(scratch),
+      static_cast<__half *>(out), q_heads, kv_heads, max_seq, splits, eps, rsqrtf(128.0f));
+  return launch_status();
+}
+
 int sageb200_glue_swiglu(const void *gate, const void *up, void *act, long long count, void *stream) {
   const unsigned blocks = static_cast<unsigned>((count + 255) / 256);
   sageb200::launch_dependent<2>(swiglu_kernel, blocks, 256, 0, static_cast<cudaStream_t>(stream),
@@ -468,6 +850,34 @@ int sageb200_glue_lm_head(const void *head, const void *x, void *logits, int row
   sageb200::launch_dependent<2>(lm_head_kernel, blocks, kHeadWarps * 32, shared, static_cast<cudaStream_t>(stream),
       static_cast<const __half *>(head), static_cast<const __half *>(x), static_cast<__half *>(logits),
       vocab, hidden, rows);
+  return launch_status();
+}
+
+size_t sageb200_glue_lm_head_step_scratch_bytes(int rows, int sm_count) {
+  const int blocks = (sm_count > 0 ? sm_count : 148) * 4;
+  return 256 + static_cast<size_t>(blocks) * rows * sizeof(float2);
+}
+
+int sageb200_glue_lm_head_step(const void *head, const void *residual, const void *delta,
+                               const void *norm_weight, void *x, void *logits, void *tokens,
+                               void *positions, void *log, void *step, void *scratch, int rows, int vocab,
+                               int hidden, float eps, int log_stride, int sm_count, void *stream) {
+  if (rows < 1 || rows > 16 || hidden % 8 || vocab < 1) return -1;
+  const size_t shared = static_cast<size_t>(rows) * hidden * sizeof(__half);
+  if (shared > 200 * 1024) return -1;
+  auto kernel = rows == 1 ? lm_head_step_kernel<1> : rows <= 4 ? lm_head_step_kernel<4> : lm_head_step_kernel<16>;
+  if (shared > 40 * 1024 &&
+      cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, 200 * 1024) != cudaSuccess)
+    return -5;
+  const int blocks = (sm_count > 0 ? sm_count : 148) * 4;
+  sageb200::launch_dependent<2>(
+      kernel, blocks, kHeadWarps * 32, shared, static_cast<cudaStream_t>(stream),
+      static_cast<const __half *>(head), static_cast<const __half *>(residual),
+      static_cast<const __half *>(delta), static_cast<const __half *>(norm_weight), static_cast<__half *>(x),
+      static_cast<__half *>(logits), static_cast<long long *>(tokens), static_cast<int *>(positions),
+      static_cast<long long *>(log), static_cast<int *>(step),
+      reinterpret_cast<float2 *>(static_cast<char *>(scratch) + 256), static_cast<unsigned *>(scratch), vocab,
+      hidden, rows, eps, log_stride);
   return launch_status();
 }
 

@@ -14,7 +14,8 @@
 #include "sage_kernels.h"
 
 namespace sageb200 {
-int g_sageb200_pdl = 3;
+int g_sageb200_pdl = 1;  // packed-linear kernels only: measured slower with the glue included
+unsigned long long g_sageb200_glue_launches = 0;
 namespace {
 
 constexpr int kMaxDevices = 64;
@@ -529,6 +530,10 @@ int sageb200_set_tuning(int warps, int slices, int ctas_per_sm, int mode) {
 }
 
 unsigned long long sageb200_launch_count(void) { return g_launches.load(std::memory_order_relaxed); }
+
+unsigned long long sageb200_glue_launch_count(void) {
+  return __atomic_load_n(&sageb200::g_sageb200_glue_launches, __ATOMIC_RELAXED);
+}
 
 size_t sageb200_fused_workspace_bytes(const sageb200_problem *problems_host, int count) {
   const size_t grouped = sageb200_grouped_workspace_bytes(problems_host, count);

@@ -66,6 +66,7 @@ __device__ __forceinline__ void pdl_wait() { asm volatile("griddepcontrol.wait;"
 // has finished (the kernel must follow the protocol above).
 // `kBit` names the kernel family: 1 = packed-linear kernels, 2 = decode glue.
 extern int g_sageb200_pdl;  // bit mask of families launched this way; 0: plain launches
+extern unsigned long long g_sageb200_glue_launches;  // decode-glue kernels launched (bench bookkeeping)
 template <int kBit = 1, typename... KernelArgs, typename... Args>
 inline cudaError_t launch_dependent(void (*kernel)(KernelArgs...), dim3 grid, dim3 block, size_t shared,
                                     cudaStream_t stream, Args &&...args) {
@@ -79,6 +80,7 @@ inline cudaError_t launch_dependent(void (*kernel)(KernelArgs...), dim3 grid, di
   attribute[0].val.programmaticStreamSerializationAllowed = 1;
   config.attrs = attribute;
   config.numAttrs = (g_sageb200_pdl & kBit) ? 1 : 0;
+  if (kBit == 2) __atomic_fetch_add(&g_sageb200_glue_launches, 1ull, __ATOMIC_RELAXED);
   return cudaLaunchKernelEx(&config, kernel, static_cast<KernelArgs>(args)...);
 }
 

@@ -211,6 +211,12 @@ class PackedQwen3:
         self.splits = 16
         scratch = self.lib.sageb200_glue_attention_scratch_bytes(batch, self.heads, self.splits)
         self.attn_scratch = torch.zeros(scratch // 4, dtype=torch.float32, device=self.device)
+        # single-launch attention and step tail (`fuse_glue`); their arrival counters start at zero
+        self.fuse_glue = True
+        scratch = self.lib.sageb200_glue_attention_step_scratch_bytes(batch, self.heads, self.kv_heads, self.splits)
+        self.attn_step_scratch = torch.zeros(scratch // 4, dtype=torch.float32, device=self.device)
+        scratch = self.lib.sageb200_glue_lm_head_step_scratch_bytes(batch, self.sm_count)
+        self.head_scratch = torch.zeros(scratch // 4, dtype=torch.float32, device=self.device)
         self.graph = None
         self.graph_no_head = None
 
@@ -256,6 +262,13 @@ class PackedQwen3:
         c, lib, b = self.config, self.lib, self.batch
         s = self._stream()
         q, k, v = self._norm_linears(layer, ("q", "k", "v"), delta, layer["input_norm"])
+        if self.fuse_glue:
+            self._check(lib.sageb200_glue_attention_step(
+                _vp(q), _vp(k), _vp(v), _vp(layer["q_norm"]), _vp(layer["k_norm"]), _vp(self.cos), _vp(self.sin),
+                _vp(self.positions), _vp(layer["k_cache"]), _vp(layer["v_cache"]), _vp(self.attn),
+                _vp(self.attn_step_scratch), b, self.heads, self.kv_heads, c.head_dim, self.max_seq, self.splits,
+                c.eps, s), "attention_step")
+            return self._after_attention(layer)
         self._check(lib.sageb200_glue_qk_norm_rope_cache(
             _vp(q), _vp(k), _vp(v), _vp(layer["q_norm"]), _vp(layer["k_norm"]), _vp(self.cos),
             _vp(self.sin), _vp(self.positions), _vp(layer["k_cache"]), _vp(layer["v_cache"]), b,
@@ -264,6 +277,11 @@ class PackedQwen3:
             _vp(q), _vp(layer["k_cache"]), _vp(layer["v_cache"]), _vp(self.positions), _vp(self.attn),
             _vp(self.attn_scratch), b, self.heads, self.kv_heads, c.head_dim, self.max_seq, self.splits, s),
             "attention_decode")
+        return self._after_attention(layer)
+
+    def _after_attention(self, layer):
+        c, lib, b = self.config, self.lib, self.batch
+        s = self._stream()
         (o,) = self._linears(layer, ("o",), self.attn)
         self._all_reduce(o)
         if c.experts:
@@ -320,6 +338,13 @@ class PackedQwen3:
         if not head:
             self.positions.add_(1)
             return
+        if self.fuse_glue and not self.dense and self.tp_world == 1:
+            self._check(lib.sageb200_glue_lm_head_step(
+                _vp(self.lm_head), _vp(self.h), _vp(delta), _vp(self.final_norm), _vp(self.x), _vp(self.logits),
+                _vp(self.tokens), _vp(self.positions), _vp(self.log), _vp(self.step_counter),
+                _vp(self.head_scratch), b, c.vocab, c.hidden, c.eps, self.max_new, self.sm_count, s),
+                "lm_head_step")
+            return
         self._check(lib.sageb200_glue_add_rmsnorm(_vp(self.h), _vp(delta), _vp(self.final_norm),
                                                   _vp(self.x), b, c.hidden, c.eps, s), "final norm")
         local_vocab = c.vocab // self.tp_world
@@ -355,10 +380,11 @@ class PackedQwen3:
         torch.cuda.current_stream(self.device).wait_stream(stream)
         torch.cuda.synchronize(self.device)
         self.graph, self.graph_no_head = torch.cuda.CUDAGraph(), torch.cuda.CUDAGraph()
-        launches = self.lib.sageb200_launch_count()
+        launches, glue = self.lib.sageb200_launch_count(), self.lib.sageb200_glue_launch_count()
         with torch.cuda.graph(self.graph, stream=stream):
             self.step(head=True)
         self.sage_launches_per_step = self.lib.sageb200_launch_count() - launches
+        self.glue_launches_per_step = self.lib.sageb200_glue_launch_count() - glue
         with torch.cuda.graph(self.graph_no_head, stream=stream):
             self.step(head=False)
         self.tokens.copy_(saved[0])

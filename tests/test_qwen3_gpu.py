@@ -2,6 +2,8 @@
 tokens of the packed model against the same model with dense FP16 dequantised linears
 (the oracle the reference uses at tests/inference/test_hf_cuda.py:30-42)."""
 
+import ctypes
+
 import pytest
 import torch
 
@@ -161,3 +163,114 @@ def test_greedy_tokens_small_moe_model():
                          experts=8, top_k=2, moe_intermediate=256)
     mismatches, error = lockstep(config, steps=32, prompt_length=8, seed=3, max_seq=64)
     check_lockstep(mismatches, error, 32)
+
+
+def _vp(tensor):
+    return ctypes.c_void_p(tensor.data_ptr()) if tensor is not None else None
+
+
+@pytest.mark.parametrize("q_heads,kv_heads", [(8, 8), (8, 4), (32, 8), (16, 2), (6, 2)])
+@pytest.mark.parametrize("splits", [1, 5, 16])
+def test_single_launch_attention_is_bit_identical_to_the_three_kernels(q_heads, kv_heads, splits):
+    """norm + RoPE + cache write + split attention + combine in one launch against the same
+    steps as three launches: same cache contents and same attention output, bit for bit, for
+    positions at the start, in the middle, at the end of the cache and beyond it (full cache)."""
+    from sage_b200 import _lib
+
+    lib = _lib.load()
+    device = torch.device("cuda:0")
+    gen = torch.Generator(device="cpu").manual_seed(q_heads * 100 + kv_heads * 10 + splits)
+    max_seq = 96
+    positions = torch.tensor([0, 1, 37, max_seq - 1, max_seq, 64], dtype=torch.int32, device=device)
+    rows = positions.numel()
+    half = dict(dtype=torch.float16, device=device)
+    rand = lambda *shape: torch.randn(*shape, generator=gen).to(**half)  # noqa: E731
+    q, k, v = rand(rows, q_heads * 128), rand(rows, kv_heads * 128), rand(rows, kv_heads * 128)
+    q_weight, k_weight = 1 + 0.1 * rand(128), 1 + 0.1 * rand(128)
+    angles = torch.outer(torch.arange(max_seq).float(), 1e6 ** (-torch.arange(64).float() / 64))
+    cos, sin = angles.cos().to(**half).contiguous(), angles.sin().to(**half).contiguous()
+    cache = lambda: (0.5 * torch.randn(rows, kv_heads, max_seq, 128, generator=gen)).to(**half)  # noqa: E731
+    k_cache, v_cache = cache(), cache()
+    stream = ctypes.c_void_p(torch.cuda.current_stream(device).cuda_stream)
+
+    q_a, k_cache_a, v_cache_a = q.clone(), k_cache.clone(), v_cache.clone()
+    out_a = torch.zeros(rows, q_heads * 128, **half)
+    scratch_a = torch.zeros(lib.sageb200_glue_attention_scratch_bytes(rows, q_heads, splits) // 4,
+                            dtype=torch.float32, device=device)
+    assert lib.sageb200_glue_qk_norm_rope_cache(
+        _vp(q_a), _vp(k), _vp(v), _vp(q_weight), _vp(k_weight), _vp(cos), _vp(sin), _vp(positions),
+        _vp(k_cache_a), _vp(v_cache_a), rows, q_heads, kv_heads, 128, max_seq, 1e-6, stream) == 0
+    assert lib.sageb200_glue_attention_decode(
+        _vp(q_a), _vp(k_cache_a), _vp(v_cache_a), _vp(positions), _vp(out_a), _vp(scratch_a), rows, q_heads,
+        kv_heads, 128, max_seq, splits, stream) == 0
+
+    k_cache_b, v_cache_b = k_cache.clone(), v_cache.clone()
+    out_b = torch.zeros_like(out_a)
+    scratch_b = torch.zeros(lib.sageb200_glue_attention_step_scratch_bytes(rows, q_heads, kv_heads, splits) // 4,
+                            dtype=torch.float32, device=device)
+    for _ in range(2):  # the second call runs on the counters the first one left behind
+        out_b.zero_()
+        assert lib.sageb200_glue_attention_step(
+            _vp(q), _vp(k), _vp(v), _vp(q_weight), _vp(k_weight), _vp(cos), _vp(sin), _vp(positions),
+            _vp(k_cache_b), _vp(v_cache_b), _vp(out_b), _vp(scratch_b), rows, q_heads, kv_heads, 128, max_seq,
+            splits, 1e-6, stream) == 0
+        torch.cuda.synchronize()
+        assert torch.equal(k_cache_a, k_cache_b) and torch.equal(v_cache_a, v_cache_b)
+        valid = (positions < max_seq).cpu()  # beyond the cache q is not normalised by the old kernels
+        assert torch.equal(out_a[valid], out_b[valid])
+        assert torch.isfinite(out_b.float()).all()
+    counters = rows * kv_heads
+    assert int(scratch_b[:counters].view(torch.int32).abs().sum()) == 0
+
+
+@pytest.mark.parametrize("rows", [1, 3, 16])
+def test_single_launch_step_tail_matches_norm_head_argmax(rows):
+    """final norm + lm_head + greedy argmax + bookkeeping in one launch against the separate
+    kernels: same normalised activations, same logits (bit for bit), same tokens (ties included:
+    duplicated head rows), same positions, log and step counter."""
+    from sage_b200 import _lib
+
+    lib = _lib.load()
+    device = torch.device("cuda:0")
+    gen = torch.Generator(device="cpu").manual_seed(rows)
+    hidden, vocab, max_new = 640, 5003, 4
+    half = dict(dtype=torch.float16, device=device)
+    rand = lambda *shape: torch.randn(*shape, generator=gen).to(**half)  # noqa: E731
+    head = (0.05 * torch.randn(vocab, hidden, generator=gen)).to(**half)
+    head[4000:4500] = head[1000:1500]  # exact ties: the lower index must win
+    residual, delta, weight = rand(rows, hidden), rand(rows, hidden), 1 + 0.1 * rand(hidden)
+    sm_count = torch.cuda.get_device_properties(device).multi_processor_count
+    stream = ctypes.c_void_p(torch.cuda.current_stream(device).cuda_stream)
+
+    def state():
+        return (torch.zeros(rows, dtype=torch.int64, device=device),
+                torch.arange(rows, dtype=torch.int32, device=device),
+                torch.full((rows, max_new), -1, dtype=torch.int64, device=device),
+                torch.zeros(1, dtype=torch.int32, device=device))
+
+    tokens_a, positions_a, log_a, step_a = state()
+    tokens_b, positions_b, log_b, step_b = state()
+    x_a, x_b = torch.zeros(rows, hidden, **half), torch.zeros(rows, hidden, **half)
+    logits_a, logits_b = torch.zeros(rows, vocab, **half), torch.zeros(rows, vocab, **half)
+    scratch = torch.zeros(lib.sageb200_glue_lm_head_step_scratch_bytes(rows, sm_count) // 4,
+                          dtype=torch.float32, device=device)
+    for call in range(3):
+        residual_a = residual.clone()
+        assert lib.sageb200_glue_add_rmsnorm(_vp(residual_a), _vp(delta), _vp(weight), _vp(x_a), rows, hidden,
+                                             1e-6, stream) == 0
+        assert lib.sageb200_glue_lm_head(_vp(head), _vp(x_a), _vp(logits_a), rows, vocab, hidden, sm_count,
+                                         stream) == 0
+        assert lib.sageb200_glue_argmax_advance(_vp(logits_a), _vp(tokens_a), _vp(positions_a), _vp(log_a),
+                                                _vp(step_a), rows, vocab, max_new, stream) == 0
+        assert lib.sageb200_glue_lm_head_step(
+            _vp(head), _vp(residual), _vp(delta), _vp(weight), _vp(x_b), _vp(logits_b), _vp(tokens_b),
+            _vp(positions_b), _vp(log_b), _vp(step_b), _vp(scratch), rows, vocab, hidden, 1e-6, max_new,
+            sm_count, stream) == 0
+        torch.cuda.synchronize()
+        assert torch.equal(x_a, x_b) and torch.equal(logits_a, logits_b)
+        assert torch.equal(tokens_a, tokens_b) and torch.equal(positions_a, positions_b)
+        assert torch.equal(log_a, log_b) and int(step_b) == call + 1 == int(step_a)
+        assert torch.equal(tokens_b.cpu(), logits_b.float().argmax(dim=-1).cpu()) or bool(
+            (logits_b.float().gather(1, tokens_b[:, None]) == logits_b.float().max(dim=-1, keepdim=True).values).all())
+        assert int(scratch[:64].view(torch.int32).abs().sum()) == 0
+        delta = rand(rows, hidden)  # another input for the next call
