@@ -233,8 +233,11 @@ int sageb200_set_pdl(int enabled);
 
 /*
  * Profiling aid (debug): while `device_buffer` is non-NULL every CTA of the decode kernel
- * writes 16 SM-clock readings (one per phase of its work) at device_buffer[16*cta ...];
- * the buffer must hold 16 * 8 bytes per CTA of the largest launch.  NULL switches it off.
+ * writes 16 readings at device_buffer[(512*launch + cta)*16 ...]: SM clocks at the phases of
+ * its work ([0..12], [14] = after the wait for the previous kernel) and the global
+ * nanosecond timer at its start [13] and end [15].  `launch` counts the decode-kernel launches
+ * since this call and stops at 63; the buffer holds 64*512*16*8 bytes (one launch only:
+ * 512*16*8).  NULL switches it off.
  * No counterpart in the reference.
  */
 int sageb200_debug_trace(void *device_buffer);

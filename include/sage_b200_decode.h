@@ -55,19 +55,18 @@ int sageb200_glue_attention_decode(const void *q, const void *k_cache, const voi
                                    void *stream);
 
 /*
- * The three calls above in ONE launch, bit-identical to them: q and the new k are normalised
- * and rotated (q is left untouched in memory), the new k/v go into the cache at
- * positions[row], each (row, kv head) is attended in `splits` CTAs and the last CTA to finish
- * combines the splits.  `scratch` holds sageb200_glue_attention_step_scratch_bytes() bytes
- * whose first 256*ceil(rows*kv_heads*4/256) bytes (arrival counters) must be zero before the
- * first call; every call leaves them zero.  Calls sharing one scratch must be stream-ordered.
+ * The three calls above in ONE launch: q and the new k are normalised and rotated (q is left
+ * untouched in memory), the new k/v go into the cache at positions[row] (bit-identical to
+ * sageb200_glue_qk_norm_rope_cache), and each (row, kv head, block of four query heads) is
+ * attended by a thread-block cluster of `splits` CTAs (1, 2, 4 or 8) that combine their
+ * partial results through distributed shared memory: no scratch.  Same FP32 arithmetic as
+ * sageb200_glue_attention_decode, summed in another order.
  */
-size_t sageb200_glue_attention_step_scratch_bytes(int rows, int q_heads, int kv_heads, int splits);
 int sageb200_glue_attention_step(const void *q, const void *k, const void *v, const void *q_weight,
                                  const void *k_weight, const void *cos_table, const void *sin_table,
-                                 const void *positions, void *k_cache, void *v_cache, void *out,
-                                 void *scratch, int rows, int q_heads, int kv_heads, int head_dim,
-                                 int max_seq, int splits, float eps, void *stream);
+                                 const void *positions, void *k_cache, void *v_cache, void *out, int rows,
+                                 int q_heads, int kv_heads, int head_dim, int max_seq, int splits, float eps,
+                                 void *stream);
 
 /* act[i] = fp16(silu(gate[i])) * up[i]. */
 int sageb200_glue_swiglu(const void *gate, const void *up, void *act, long long count, void *stream);

@@ -48,7 +48,6 @@ EXPORTED_DECODE = (
     "sageb200_glue_qk_norm_rope_cache",
     "sageb200_glue_attention_scratch_bytes",
     "sageb200_glue_attention_decode",
-    "sageb200_glue_attention_step_scratch_bytes",
     "sageb200_glue_attention_step",
     "sageb200_glue_lm_head_step_scratch_bytes",
     "sageb200_glue_lm_head_step",
@@ -173,10 +172,8 @@ def load() -> ctypes.CDLL:
     lib.sageb200_glue_qk_norm_rope_cache.argtypes = [vp] * 10 + [ci] * 5 + [fl, vp]
     lib.sageb200_glue_attention_scratch_bytes.restype = sz
     lib.sageb200_glue_attention_scratch_bytes.argtypes = [ci, ci, ci]
-    lib.sageb200_glue_attention_step_scratch_bytes.restype = sz
-    lib.sageb200_glue_attention_step_scratch_bytes.argtypes = [ci] * 4
     lib.sageb200_glue_attention_step.restype = ci
-    lib.sageb200_glue_attention_step.argtypes = [vp] * 12 + [ci] * 6 + [ctypes.c_float, vp]
+    lib.sageb200_glue_attention_step.argtypes = [vp] * 11 + [ci] * 6 + [ctypes.c_float, vp]
     lib.sageb200_glue_lm_head_step_scratch_bytes.restype = sz
     lib.sageb200_glue_lm_head_step_scratch_bytes.argtypes = [ci, ci]
     lib.sageb200_glue_lm_head_step.restype = ci

@@ -13,6 +13,8 @@
 #include <cuda_runtime.h>
 #include <stdint.h>
 
+#include <cooperative_groups.h>
+
 #include "sage_common.cuh"
 
 namespace {
@@ -263,11 +265,14 @@ __global__ void attention_combine_kernel(const float *__restrict__ partial, __ha
 }
 
 // The whole attention step of one new token per sequence in ONE launch: per-head RMSNorm +
-// RoPE of q and of the new k, the new k/v written into the cache, attention over the context
-// split across CTAs, and the combination of the splits by the last CTA of each (sequence,
-// kv head) to arrive (a counter in `counters`, zero before the launch and zero again after).
-// CTA = (split, kv head, sequence).  Arithmetic and rounding are those of the three kernels
-// above, so the result is bit-identical to running them one after the other.
+// RoPE of q and of the new k, the new k/v written into the cache, attention over the context.
+// A thread-block cluster of `splits` CTAs shares one (sequence, kv head, block of up to four
+// query heads): CTA r attends to the r-th chunk of the context, leaves its (max, sum, weighted
+// V) in its own shared memory, and after a cluster barrier every CTA combines a slice of the
+// output dims by reading all CTAs' partials through distributed shared memory - no scratch in
+// global memory, no second launch.  q/k arithmetic and the cache contents are those of
+// qk_norm_rope_cache_kernel, bit for bit; the attention sums run in another order than
+// attention_partial_kernel's (same FP32 math).
 __device__ __forceinline__ void norm_rope_head(const __half *source, const __half *weight,
                                                const __half *cos_row, const __half *sin_row,
                                                float eps, int lane, __half2 &out_lo, __half2 &out_hi) {
@@ -286,29 +291,47 @@ __device__ __forceinline__ void norm_rope_head(const __half *source, const __hal
   out_hi = __hadd2(__hmul2(nh, c), __hmul2(nl, s));
 }
 
-// kGroup = query heads per kv head when it is 1, 2, 4 or 8 (arrays stay in registers), 0 = any.
-template <int kGroup>
+constexpr int kStepHeads = 4;  // query heads per CTA (of one kv head)
+
+__device__ __forceinline__ void unpack16(const uint4 &a, const uint4 &b, float out[16]) {
+  const __half2 *ha = reinterpret_cast<const __half2 *>(&a);
+  const __half2 *hb = reinterpret_cast<const __half2 *>(&b);
+#pragma unroll
+  for (int i = 0; i < 4; ++i) {
+    const float2 fa = __half22float2(ha[i]), fb = __half22float2(hb[i]);
+    out[2 * i] = fa.x;
+    out[2 * i + 1] = fa.y;
+    out[8 + 2 * i] = fb.x;
+    out[8 + 2 * i + 1] = fb.y;
+  }
+}
+
 __global__ void __launch_bounds__(kAttnWarps * 32)
     attention_step_kernel(const __half *__restrict__ q, const __half *__restrict__ k,
                           const __half *__restrict__ v, const __half *__restrict__ q_weight,
                           const __half *__restrict__ k_weight, const __half *__restrict__ cos_table,
                           const __half *__restrict__ sin_table, const int *__restrict__ positions,
-                          __half *k_cache, __half *v_cache, float *partial, unsigned *counters,
-                          __half *__restrict__ out, int q_heads, int kv_heads, int max_seq, int splits,
-                          float eps, float scale) {
+                          __half *k_cache, __half *v_cache, __half *__restrict__ out, int q_heads,
+                          int kv_heads, int max_seq, float eps, float scale) {
   sageb200::pdl_launch_dependents();
   sageb200::pdl_wait();
 
-  __shared__ float shared_max[kAttnWarps][kMaxGroup];
-  __shared__ float shared_sum[kAttnWarps][kMaxGroup];
-  __shared__ float shared_acc[kAttnWarps][kMaxGroup][128];
-  __shared__ __align__(16) __half q_shared[kMaxGroup][128];
+  namespace cg = cooperative_groups;
+  cg::cluster_group cluster = cg::this_cluster();
+  __shared__ float warp_max[kAttnWarps][kStepHeads];
+  __shared__ float warp_total[kAttnWarps][kStepHeads];
+  __shared__ __align__(16) float warp_acc[kAttnWarps][kStepHeads][128];
+  __shared__ float cta_max[kStepHeads], cta_total[kStepHeads];
+  __shared__ __align__(16) float cta_acc[kStepHeads][128];
+  __shared__ __align__(16) __half q_shared[kStepHeads][128];
   __shared__ __align__(16) __half new_k[128], new_v[128];
-  __shared__ int is_last;
-  const int split = blockIdx.x, kv = blockIdx.y, m = blockIdx.z;
+  const int splits = gridDim.x, split = blockIdx.x, m = blockIdx.z;
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
-  const int group = kGroup ? kGroup : q_heads / kv_heads;
-  constexpr int kUnroll = kGroup ? kGroup : kMaxGroup;
+  const int group = q_heads / kv_heads;
+  const int parts = (group + kStepHeads - 1) / kStepHeads;
+  const int kv = blockIdx.y / parts, part = blockIdx.y - kv * parts;
+  const int heads = min(kStepHeads, group - part * kStepHeads);
+  const int first_head = kv * group + part * kStepHeads;
   const int position = positions[m];
   const bool in_range = position >= 0 && position < max_seq;  // a full cache takes no new token
   const int table_row = min(max(position, 0), max_seq - 1);
@@ -322,11 +345,12 @@ __global__ void __launch_bounds__(kAttnWarps * 32)
   __half *k_base = k_cache + (static_cast<size_t>(m) * kv_heads + kv) * max_seq * 128;
   __half *v_base = v_cache + (static_cast<size_t>(m) * kv_heads + kv) * max_seq * 128;
 
-  // items 0..group-1: the group's query heads; item `group`: the new token's key and value
-  for (int item = warp; item < group + (owns_new ? 1 : 0); item += kAttnWarps) {
+  // items 0..heads-1: this CTA's query heads; item `heads`: the new token's key and value
+  // (every part needs them, part 0 stores them)
+  for (int item = warp; item < heads + (owns_new ? 1 : 0); item += kAttnWarps) {
     __half2 lo, hi;
-    if (item < group) {
-      norm_rope_head(q + (static_cast<size_t>(m) * q_heads + kv * group + item) * 128, q_weight, cos_row,
+    if (item < heads) {
+      norm_rope_head(q + (static_cast<size_t>(m) * q_heads + first_head + item) * 128, q_weight, cos_row,
                      sin_row, eps, lane, lo, hi);
       reinterpret_cast<__half2 *>(q_shared[item])[lane] = lo;
       reinterpret_cast<__half2 *>(q_shared[item] + 64)[lane] = hi;
@@ -335,113 +359,139 @@ __global__ void __launch_bounds__(kAttnWarps * 32)
                      lane, lo, hi);
       reinterpret_cast<__half2 *>(new_k)[lane] = lo;
       reinterpret_cast<__half2 *>(new_k + 64)[lane] = hi;
-      reinterpret_cast<__half2 *>(k_base + static_cast<size_t>(position) * 128)[lane] = lo;
-      reinterpret_cast<__half2 *>(k_base + static_cast<size_t>(position) * 128 + 64)[lane] = hi;
       const uint2 value = reinterpret_cast<const uint2 *>(v + (static_cast<size_t>(m) * kv_heads + kv) * 128)[lane];
       reinterpret_cast<uint2 *>(new_v)[lane] = value;
-      reinterpret_cast<uint2 *>(v_base + static_cast<size_t>(position) * 128)[lane] = value;
+      if (part == 0) {
+        reinterpret_cast<__half2 *>(k_base + static_cast<size_t>(position) * 128)[lane] = lo;
+        reinterpret_cast<__half2 *>(k_base + static_cast<size_t>(position) * 128 + 64)[lane] = hi;
+        reinterpret_cast<uint2 *>(v_base + static_cast<size_t>(position) * 128)[lane] = value;
+      }
     }
   }
   __syncthreads();
 
-  // lane holds dims 4*lane .. 4*lane+3
-  float2 qa[kUnroll], qb[kUnroll];
+  // A warp takes four consecutive positions at a time: lanes 8s..8s+7 share position s and hold
+  // 16 dims each (dims 16*piece .. 16*piece+15), so a dot product needs three shuffles.
+  const int sub = lane >> 3, piece = lane & 7;
+  float qf[kStepHeads][16];
 #pragma unroll
-  for (int g = 0; g < kUnroll; ++g) {
-    const __half2 *qh = reinterpret_cast<const __half2 *>(q_shared[g < group ? g : 0] + 4 * lane);
-    qa[g] = __half22float2(qh[0]);
-    qb[g] = __half22float2(qh[1]);
+  for (int g = 0; g < kStepHeads; ++g) {
+    const uint4 *source = reinterpret_cast<const uint4 *>(q_shared[g < heads ? g : 0] + 16 * piece);
+    unpack16(source[0], source[1], qf[g]);
   }
-  float running_max[kUnroll], running_sum[kUnroll], acc[kUnroll][4];
+  float running_max[kStepHeads], running_sum[kStepHeads], acc[kStepHeads][16];
 #pragma unroll
-  for (int g = 0; g < kUnroll; ++g) {
+  for (int g = 0; g < kStepHeads; ++g) {
     running_max[g] = -INFINITY;
     running_sum[g] = 0.0f;
-    acc[g][0] = acc[g][1] = acc[g][2] = acc[g][3] = 0.0f;
-  }
-  for (int p = begin + warp; p < end; p += kAttnWarps) {
-    uint2 kw, vw;
-    if (owns_new && p == position) {
-      kw = reinterpret_cast<const uint2 *>(new_k)[lane];
-      vw = reinterpret_cast<const uint2 *>(new_v)[lane];
-    } else {
-      kw = __ldcg(reinterpret_cast<const uint2 *>(k_base + static_cast<size_t>(p) * 128) + lane);
-      vw = __ldcg(reinterpret_cast<const uint2 *>(v_base + static_cast<size_t>(p) * 128) + lane);
-    }
-    const float2 ka = __half22float2(*reinterpret_cast<const __half2 *>(&kw.x));
-    const float2 kb = __half22float2(*reinterpret_cast<const __half2 *>(&kw.y));
-    const float2 va = __half22float2(*reinterpret_cast<const __half2 *>(&vw.x));
-    const float2 vb = __half22float2(*reinterpret_cast<const __half2 *>(&vw.y));
 #pragma unroll
-    for (int g = 0; g < kUnroll; ++g) {
-      if (g >= group) break;
-      float dot = qa[g].x * ka.x + qa[g].y * ka.y + qb[g].x * kb.x + qb[g].y * kb.y;
-      dot = warp_sum(dot) * scale;
-      const float new_max = fmaxf(running_max[g], dot);
-      const float rescale = __expf(running_max[g] - new_max);
-      const float weight = __expf(dot - new_max);
-      running_sum[g] = running_sum[g] * rescale + weight;
-      acc[g][0] = acc[g][0] * rescale + weight * va.x;
-      acc[g][1] = acc[g][1] * rescale + weight * va.y;
-      acc[g][2] = acc[g][2] * rescale + weight * vb.x;
-      acc[g][3] = acc[g][3] * rescale + weight * vb.y;
-      running_max[g] = new_max;
+    for (int i = 0; i < 16; ++i) acc[g][i] = 0.0f;
+  }
+  for (int base = begin + warp * 4; base < end; base += kAttnWarps * 4) {
+    const int p = base + sub;
+    const bool valid = p < end;
+    uint4 k0 = make_uint4(0, 0, 0, 0), k1 = k0, v0 = k0, v1 = k0;
+    if (valid) {
+      const bool fresh = owns_new && p == position;
+      const uint4 *k_row = fresh ? reinterpret_cast<const uint4 *>(new_k)
+                                 : reinterpret_cast<const uint4 *>(k_base + static_cast<size_t>(p) * 128);
+      const uint4 *v_row = fresh ? reinterpret_cast<const uint4 *>(new_v)
+                                 : reinterpret_cast<const uint4 *>(v_base + static_cast<size_t>(p) * 128);
+      k0 = k_row[2 * piece];
+      k1 = k_row[2 * piece + 1];
+      v0 = v_row[2 * piece];
+      v1 = v_row[2 * piece + 1];
+    }
+    float kf[16], vf[16];
+    unpack16(k0, k1, kf);
+    unpack16(v0, v1, vf);
+#pragma unroll
+    for (int g = 0; g < kStepHeads; ++g) {
+      if (g >= heads) break;
+      float dot = 0.0f;
+#pragma unroll
+      for (int i = 0; i < 16; ++i) dot = fmaf(qf[g][i], kf[i], dot);
+      dot += __shfl_xor_sync(0xffffffffu, dot, 1);
+      dot += __shfl_xor_sync(0xffffffffu, dot, 2);
+      dot += __shfl_xor_sync(0xffffffffu, dot, 4);
+      if (valid) {
+        dot *= scale;
+        const float new_max = fmaxf(running_max[g], dot);
+        const float rescale = __expf(running_max[g] - new_max);
+        const float weight = __expf(dot - new_max);
+        running_sum[g] = running_sum[g] * rescale + weight;
+#pragma unroll
+        for (int i = 0; i < 16; ++i) acc[g][i] = fmaf(weight, vf[i], acc[g][i] * rescale);
+        running_max[g] = new_max;
+      }
     }
   }
+  // merge the warp's four position streams, then the warps, then (across the cluster) the splits
 #pragma unroll
-  for (int g = 0; g < kUnroll; ++g) {
-    if (g >= group) break;
+  for (int g = 0; g < kStepHeads; ++g) {
+    if (g >= heads) break;
+    float top = fmaxf(running_max[g], __shfl_xor_sync(0xffffffffu, running_max[g], 8));
+    top = fmaxf(top, __shfl_xor_sync(0xffffffffu, top, 16));
+    const float f = running_max[g] == -INFINITY ? 0.0f : __expf(running_max[g] - top);
+    float total = running_sum[g] * f;
+    total += __shfl_xor_sync(0xffffffffu, total, 8);
+    total += __shfl_xor_sync(0xffffffffu, total, 16);
+#pragma unroll
+    for (int i = 0; i < 16; ++i) {
+      float value = acc[g][i] * f;
+      value += __shfl_xor_sync(0xffffffffu, value, 8);
+      value += __shfl_xor_sync(0xffffffffu, value, 16);
+      acc[g][i] = value;
+    }
     if (lane == 0) {
-      shared_max[warp][g] = running_max[g];
-      shared_sum[warp][g] = running_sum[g];
+      warp_max[warp][g] = top;
+      warp_total[warp][g] = total;
     }
-    for (int c = 0; c < 4; ++c) shared_acc[warp][g][4 * lane + c] = acc[g][c];
+    if (sub == 0) {
+#pragma unroll
+      for (int i = 0; i < 16; i += 4)
+        *reinterpret_cast<float4 *>(&warp_acc[warp][g][16 * piece + i]) =
+            make_float4(acc[g][i], acc[g][i + 1], acc[g][i + 2], acc[g][i + 3]);
+    }
   }
   __syncthreads();
-  // combine the warps: thread = (query head of the group, dim); partial layout
-  // [sequence][query head][split][130] = (max, sum, 128 values)
-  for (int item = threadIdx.x; item < group * 128; item += blockDim.x) {
+  for (int item = threadIdx.x; item < heads * 128; item += blockDim.x) {
     const int g = item >> 7, dim = item & 127;
     float top = -INFINITY;
-    for (int w = 0; w < kAttnWarps; ++w) top = fmaxf(top, shared_max[w][g]);
-    float sum = 0.0f, value = 0.0f;
+#pragma unroll
+    for (int w = 0; w < kAttnWarps; ++w) top = fmaxf(top, warp_max[w][g]);
+    float total = 0.0f, value = 0.0f;
+#pragma unroll
     for (int w = 0; w < kAttnWarps; ++w) {
-      const float f = shared_max[w][g] == -INFINITY ? 0.0f : __expf(shared_max[w][g] - top);
-      sum += shared_sum[w][g] * f;
-      value += shared_acc[w][g][dim] * f;
+      const float f = warp_max[w][g] == -INFINITY ? 0.0f : __expf(warp_max[w][g] - top);
+      total += warp_total[w][g] * f;
+      value += warp_acc[w][g][dim] * f;
     }
-    float *slot = partial + ((static_cast<size_t>(m) * q_heads + kv * group + g) * splits + split) * 130;
     if (dim == 0) {
-      slot[0] = top;
-      slot[1] = sum;
+      cta_max[g] = top;
+      cta_total[g] = total;
     }
-    slot[2 + dim] = value;
+    cta_acc[g][dim] = value;
   }
-  // the last CTA of this (sequence, kv head) to get here combines the splits
-  __threadfence();
-  __syncthreads();
-  if (threadIdx.x == 0) {
-    const unsigned ticket = atomicAdd(&counters[m * kv_heads + kv], 1u);
-    is_last = ticket == static_cast<unsigned>(splits - 1);
-    if (is_last) counters[m * kv_heads + kv] = 0u;  // zero again for the next launch
-  }
-  __syncthreads();
-  if (!is_last) return;
-  __threadfence();
-  for (int item = threadIdx.x; item < group * 128; item += blockDim.x) {
+  cluster.sync();  // every CTA's partial is in its shared memory
+  const int items = heads * 128;
+  const int per_cta = (items + splits - 1) / splits;
+  for (int local = threadIdx.x; local < per_cta; local += blockDim.x) {
+    const int item = split * per_cta + local;
+    if (item >= items) break;
     const int g = item >> 7, dim = item & 127;
-    const float *base = partial + (static_cast<size_t>(m) * q_heads + kv * group + g) * splits * 130;
     float top = -INFINITY;
-    for (int s = 0; s < splits; ++s) top = fmaxf(top, __ldcg(base + s * 130));
-    float sum = 0.0f, value = 0.0f;
+    for (int s = 0; s < splits; ++s) top = fmaxf(top, *cluster.map_shared_rank(&cta_max[g], s));
+    float total = 0.0f, value = 0.0f;
     for (int s = 0; s < splits; ++s) {
-      const float mx = __ldcg(base + s * 130);
+      const float mx = *cluster.map_shared_rank(&cta_max[g], s);
       const float f = mx == -INFINITY ? 0.0f : __expf(mx - top);
-      sum += __ldcg(base + s * 130 + 1) * f;
-      value += __ldcg(base + s * 130 + 2 + dim) * f;
+      total += *cluster.map_shared_rank(&cta_total[g], s) * f;
+      value += *cluster.map_shared_rank(&cta_acc[g][dim], s) * f;
     }
-    out[(static_cast<size_t>(m) * q_heads + kv * group + g) * 128 + dim] = __float2half_rn(value / sum);
+    out[(static_cast<size_t>(m) * q_heads + first_head + g) * 128 + dim] = __float2half_rn(value / total);
   }
+  cluster.sync();  // nobody leaves while its shared memory may still be read
 }
 
 // act = silu(gate) * up, FP32 math on FP16 inputs, rounded as the FP16 modules round:
@@ -795,36 +845,37 @@ int sageb200_glue_attention_decode(const void *q, const void *k_cache, const voi
   return launch_status();
 }
 
-size_t sageb200_glue_attention_step_scratch_bytes(int rows, int q_heads, int kv_heads, int splits) {
-  const size_t counters = (static_cast<size_t>(rows) * kv_heads * sizeof(unsigned) + 255) / 256 * 256;
-  return counters + static_cast<size_t>(rows) * q_heads * splits * 130 * sizeof(float);
-}
-
 int sageb200_glue_attention_step(const void *q, const void *k, const void *v, const void *q_weight,
                                  const void *k_weight, const void *cos_table, const void *sin_table,
-                                 const void *positions, void *k_cache, void *v_cache, void *out,
-                                 void *scratch, int rows, int q_heads, int kv_heads, int head_dim,
-                                 int max_seq, int splits, float eps, void *stream) {
-  if (head_dim != 128 || kv_heads < 1 || q_heads % kv_heads || q_heads / kv_heads > kMaxGroup || splits < 1 ||
-      max_seq < 1)
-    return -1;
-  const size_t counters = (static_cast<size_t>(rows) * kv_heads * sizeof(unsigned) + 255) / 256 * 256;
-  const dim3 grid(splits, kv_heads, rows);
+                                 const void *positions, void *k_cache, void *v_cache, void *out, int rows,
+                                 int q_heads, int kv_heads, int head_dim, int max_seq, int splits, float eps,
+                                 void *stream) {
+  if (head_dim != 128 || kv_heads < 1 || q_heads % kv_heads || max_seq < 1 || rows < 1) return -1;
+  if (splits != 1 && splits != 2 && splits != 4 && splits != 8) return -1;  // a portable cluster size
   const int group = q_heads / kv_heads;
-  auto kernel = group == 1   ? attention_step_kernel<1>
-                : group == 2 ? attention_step_kernel<2>
-                : group == 4 ? attention_step_kernel<4>
-                : group == 8 ? attention_step_kernel<8>
-                             : attention_step_kernel<0>;
-  sageb200::launch_dependent<2>(
-      kernel, grid, kAttnWarps * 32, 0, static_cast<cudaStream_t>(stream),
-      static_cast<const __half *>(q), static_cast<const __half *>(k), static_cast<const __half *>(v),
-      static_cast<const __half *>(q_weight), static_cast<const __half *>(k_weight),
-      static_cast<const __half *>(cos_table), static_cast<const __half *>(sin_table),
-      static_cast<const int *>(positions), static_cast<__half *>(k_cache), static_cast<__half *>(v_cache),
-      reinterpret_cast<float *>(static_cast<char *>(scratch) + counters), static_cast<unsigned *>(scratch),
-      static_cast<__half *>(out), q_heads, kv_heads, max_seq, splits, eps, rsqrtf(128.0f));
-  return launch_status();
+  const int parts = (group + kStepHeads - 1) / kStepHeads;
+  cudaLaunchConfig_t config = {};
+  config.gridDim = dim3(splits, kv_heads * parts, rows);
+  config.blockDim = dim3(kAttnWarps * 32);
+  config.stream = static_cast<cudaStream_t>(stream);
+  cudaLaunchAttribute attributes[2];
+  attributes[0].id = cudaLaunchAttributeClusterDimension;
+  attributes[0].val.clusterDim.x = splits;
+  attributes[0].val.clusterDim.y = 1;
+  attributes[0].val.clusterDim.z = 1;
+  attributes[1].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+  attributes[1].val.programmaticStreamSerializationAllowed = 1;
+  config.attrs = attributes;
+  config.numAttrs = (sageb200::g_sageb200_pdl & 2) ? 2 : 1;
+  __atomic_fetch_add(&sageb200::g_sageb200_glue_launches, 1ull, __ATOMIC_RELAXED);
+  const cudaError_t error = cudaLaunchKernelEx(
+      &config, attention_step_kernel, static_cast<const __half *>(q), static_cast<const __half *>(k),
+      static_cast<const __half *>(v), static_cast<const __half *>(q_weight),
+      static_cast<const __half *>(k_weight), static_cast<const __half *>(cos_table),
+      static_cast<const __half *>(sin_table), static_cast<const int *>(positions),
+      static_cast<__half *>(k_cache), static_cast<__half *>(v_cache), static_cast<__half *>(out), q_heads,
+      kv_heads, max_seq, eps, rsqrtf(128.0f));
+  return error == cudaSuccess ? launch_status() : -5;
 }
 
 int sageb200_glue_swiglu(const void *gate, const void *up, void *act, long long count, void *stream) {

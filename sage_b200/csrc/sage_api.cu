@@ -34,6 +34,7 @@ DeviceState g_devices[kMaxDevices];
 Tuning g_tuning{0, 0, 0, 0};
 std::atomic<unsigned long long> g_launches{0};
 long long *g_trace = nullptr;  // profiling aid, see sageb200_debug_trace
+int g_trace_launch = 0;        // launches traced since the buffer was set
 
 size_t align256(size_t bytes) { return (bytes + 255) / 256 * 256; }
 
@@ -171,7 +172,9 @@ int run_skinny(const sageb200_problem *problems, int count, void *workspace,
     params.act_weight = activation->weight;
     params.act_residual_out = activation->residual_out;
   }
-  params.trace = g_trace;
+  // launch i of a traced run writes block min(i, 63) of 512 CTA records
+  params.trace = g_trace ? g_trace + static_cast<size_t>(g_trace_launch < 63 ? g_trace_launch : 63) * 512 * 16 : nullptr;
+  if (g_trace) ++g_trace_launch;
   unsigned char *scratch = static_cast<unsigned char *>(workspace);
   size_t offset = kCounterRegionBytes;
   int counters_used = 0;
@@ -518,6 +521,7 @@ int sageb200_set_pdl(int enabled) {
 
 int sageb200_debug_trace(void *device_buffer) {
   g_trace = static_cast<long long *>(device_buffer);
+  g_trace_launch = 0;
   return SAGEB200_OK;
 }
 

@@ -84,6 +84,12 @@ inline cudaError_t launch_dependent(void (*kernel)(KernelArgs...), dim3 grid, di
   return cudaLaunchKernelEx(&config, kernel, static_cast<KernelArgs>(args)...);
 }
 
+__device__ __forceinline__ long long global_nanoseconds() {
+  long long t;
+  asm volatile("mov.u64 %0, %globaltimer;" : "=l"(t));
+  return t;
+}
+
 __device__ __forceinline__ uint32_t smem_address(const void *p) {
   return static_cast<uint32_t>(__cvta_generic_to_shared(p));
 }

@@ -97,6 +97,7 @@ __global__ void __launch_bounds__(512, 1) sage_skinny_kernel(const __grid_consta
   long long *trace = params.trace ? params.trace + 16 * static_cast<size_t>(blockIdx.x) : nullptr;
 #define SAGE_STAMP(i) do { if (trace && threadIdx.x == 0) trace[i] = clock64(); } while (0)
   SAGE_STAMP(0);
+  if (trace && threadIdx.x == 0) trace[13] = global_nanoseconds();
   pdl_launch_dependents();  // the next kernel may be scheduled as SM resources free up
   int pi = 0;
   if (params.count > 1) {
@@ -297,6 +298,7 @@ __global__ void __launch_bounds__(512, 1) sage_skinny_kernel(const __grid_consta
   // Everything above read only weights, codebook and permutation (never written by a kernel);
   // from here on the activations of the previous kernel are read and global memory is written.
   pdl_wait();
+  SAGE_STAMP(14);
   float square_sum = 0.0f;
   if (fused) {
     // the whole row, in original channel order, into the linear buffer (and the norm
@@ -596,6 +598,7 @@ __global__ void __launch_bounds__(512, 1) sage_skinny_kernel(const __grid_consta
     }
   }
   SAGE_STAMP(8);
+  if (trace && threadIdx.x == 0) trace[15] = global_nanoseconds();
   if (!any_split) return;
 
   // ---- 8. tiles shared with other CTAs: publish, count arrivals, the last one finishes.
@@ -630,6 +633,7 @@ __global__ void __launch_bounds__(512, 1) sage_skinny_kernel(const __grid_consta
   for (int ti = tid; ti < cta_tiles; ti += threads)
     if (tile_last[ti]) p.counters[cta_first_tile + ti] = 0u;
   SAGE_STAMP(10);
+  if (trace && threadIdx.x == 0) trace[15] = global_nanoseconds();
 #undef SAGE_STAMP
 }
 

@@ -211,10 +211,9 @@ class PackedQwen3:
         self.splits = 16
         scratch = self.lib.sageb200_glue_attention_scratch_bytes(batch, self.heads, self.splits)
         self.attn_scratch = torch.zeros(scratch // 4, dtype=torch.float32, device=self.device)
-        # single-launch attention and step tail (`fuse_glue`); their arrival counters start at zero
+        # single-launch attention and step tail (`fuse_glue`); the tail's arrival counter starts at zero
         self.fuse_glue = True
-        scratch = self.lib.sageb200_glue_attention_step_scratch_bytes(batch, self.heads, self.kv_heads, self.splits)
-        self.attn_step_scratch = torch.zeros(scratch // 4, dtype=torch.float32, device=self.device)
+        self.step_splits = 8  # CTAs per cluster in the single-launch attention
         scratch = self.lib.sageb200_glue_lm_head_step_scratch_bytes(batch, self.sm_count)
         self.head_scratch = torch.zeros(scratch // 4, dtype=torch.float32, device=self.device)
         self.graph = None
@@ -266,8 +265,8 @@ class PackedQwen3:
             self._check(lib.sageb200_glue_attention_step(
                 _vp(q), _vp(k), _vp(v), _vp(layer["q_norm"]), _vp(layer["k_norm"]), _vp(self.cos), _vp(self.sin),
                 _vp(self.positions), _vp(layer["k_cache"]), _vp(layer["v_cache"]), _vp(self.attn),
-                _vp(self.attn_step_scratch), b, self.heads, self.kv_heads, c.head_dim, self.max_seq, self.splits,
-                c.eps, s), "attention_step")
+                b, self.heads, self.kv_heads, c.head_dim, self.max_seq, self.step_splits, c.eps, s),
+                "attention_step")
             return self._after_attention(layer)
         self._check(lib.sageb200_glue_qk_norm_rope_cache(
             _vp(q), _vp(k), _vp(v), _vp(layer["q_norm"]), _vp(layer["k_norm"]), _vp(self.cos),

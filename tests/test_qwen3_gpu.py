@@ -170,10 +170,11 @@ def _vp(tensor):
 
 
 @pytest.mark.parametrize("q_heads,kv_heads", [(8, 8), (8, 4), (32, 8), (16, 2), (6, 2)])
-@pytest.mark.parametrize("splits", [1, 5, 16])
-def test_single_launch_attention_is_bit_identical_to_the_three_kernels(q_heads, kv_heads, splits):
-    """norm + RoPE + cache write + split attention + combine in one launch against the same
-    steps as three launches: same cache contents and same attention output, bit for bit, for
+@pytest.mark.parametrize("splits", [1, 4, 8])
+def test_single_launch_attention_matches_the_three_kernels(q_heads, kv_heads, splits):
+    """norm + RoPE + cache write + split attention + combine in one launch (a thread-block
+    cluster per kv head) against the same steps as three launches: the same cache contents bit
+    for bit, the same attention output to FP16 rounding (the FP32 sums run in another order), for
     positions at the start, in the middle, at the end of the cache and beyond it (full cache)."""
     from sage_b200 import _lib
 
@@ -195,32 +196,31 @@ def test_single_launch_attention_is_bit_identical_to_the_three_kernels(q_heads, 
 
     q_a, k_cache_a, v_cache_a = q.clone(), k_cache.clone(), v_cache.clone()
     out_a = torch.zeros(rows, q_heads * 128, **half)
-    scratch_a = torch.zeros(lib.sageb200_glue_attention_scratch_bytes(rows, q_heads, splits) // 4,
+    scratch_a = torch.zeros(lib.sageb200_glue_attention_scratch_bytes(rows, q_heads, 16) // 4,
                             dtype=torch.float32, device=device)
     assert lib.sageb200_glue_qk_norm_rope_cache(
         _vp(q_a), _vp(k), _vp(v), _vp(q_weight), _vp(k_weight), _vp(cos), _vp(sin), _vp(positions),
         _vp(k_cache_a), _vp(v_cache_a), rows, q_heads, kv_heads, 128, max_seq, 1e-6, stream) == 0
     assert lib.sageb200_glue_attention_decode(
         _vp(q_a), _vp(k_cache_a), _vp(v_cache_a), _vp(positions), _vp(out_a), _vp(scratch_a), rows, q_heads,
-        kv_heads, 128, max_seq, splits, stream) == 0
+        kv_heads, 128, max_seq, 16, stream) == 0
 
     k_cache_b, v_cache_b = k_cache.clone(), v_cache.clone()
     out_b = torch.zeros_like(out_a)
-    scratch_b = torch.zeros(lib.sageb200_glue_attention_step_scratch_bytes(rows, q_heads, kv_heads, splits) // 4,
-                            dtype=torch.float32, device=device)
-    for _ in range(2):  # the second call runs on the counters the first one left behind
+    assert lib.sageb200_glue_attention_step(
+        _vp(q), _vp(k), _vp(v), _vp(q_weight), _vp(k_weight), _vp(cos), _vp(sin), _vp(positions),
+        _vp(k_cache_b), _vp(v_cache_b), _vp(out_b), rows, q_heads, kv_heads, 128, max_seq, 5, 1e-6, stream) == -1
+    for _ in range(2):
         out_b.zero_()
         assert lib.sageb200_glue_attention_step(
             _vp(q), _vp(k), _vp(v), _vp(q_weight), _vp(k_weight), _vp(cos), _vp(sin), _vp(positions),
-            _vp(k_cache_b), _vp(v_cache_b), _vp(out_b), _vp(scratch_b), rows, q_heads, kv_heads, 128, max_seq,
-            splits, 1e-6, stream) == 0
+            _vp(k_cache_b), _vp(v_cache_b), _vp(out_b), rows, q_heads, kv_heads, 128, max_seq, splits, 1e-6,
+            stream) == 0
         torch.cuda.synchronize()
         assert torch.equal(k_cache_a, k_cache_b) and torch.equal(v_cache_a, v_cache_b)
         valid = (positions < max_seq).cpu()  # beyond the cache q is not normalised by the old kernels
-        assert torch.equal(out_a[valid], out_b[valid])
+        assert torch.allclose(out_a[valid].float(), out_b[valid].float(), rtol=2e-3, atol=1e-3)
         assert torch.isfinite(out_b.float()).all()
-    counters = rows * kv_heads
-    assert int(scratch_b[:counters].view(torch.int32).abs().sum()) == 0
 
 
 @pytest.mark.parametrize("rows", [1, 3, 16])
