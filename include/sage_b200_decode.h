@@ -58,7 +58,8 @@ int sageb200_glue_attention_decode(const void *q, const void *k_cache, const voi
  * The three calls above in ONE launch: q and the new k are normalised and rotated (q is left
  * untouched in memory), the new k/v go into the cache at positions[row] (bit-identical to
  * sageb200_glue_qk_norm_rope_cache), and each (row, kv head, block of four query heads) is
- * attended by a thread-block cluster of `splits` CTAs (1, 2, 4 or 8) that combine their
+ * attended by a thread-block cluster of `splits` CTAs (1, 2, 4, 8 or - where the GPU can
+ * co-schedule that many - 16; -1 otherwise) that combine their
  * partial results through distributed shared memory: no scratch.  Same FP32 arithmetic as
  * sageb200_glue_attention_decode, summed in another order.
  */

@@ -387,11 +387,11 @@ __global__ void __launch_bounds__(kAttnWarps * 32)
 #pragma unroll
     for (int i = 0; i < 16; ++i) acc[g][i] = 0.0f;
   }
-  for (int base = begin + warp * 4; base < end; base += kAttnWarps * 4) {
+  // the rows of the next four positions are requested before the current ones are used
+  auto fetch = [&](int base, uint4 &k0, uint4 &k1, uint4 &v0, uint4 &v1) {
     const int p = base + sub;
-    const bool valid = p < end;
-    uint4 k0 = make_uint4(0, 0, 0, 0), k1 = k0, v0 = k0, v1 = k0;
-    if (valid) {
+    k0 = k1 = v0 = v1 = make_uint4(0, 0, 0, 0);
+    if (p < end) {
       const bool fresh = owns_new && p == position;
       const uint4 *k_row = fresh ? reinterpret_cast<const uint4 *>(new_k)
                                  : reinterpret_cast<const uint4 *>(k_base + static_cast<size_t>(p) * 128);
@@ -402,6 +402,12 @@ __global__ void __launch_bounds__(kAttnWarps * 32)
       v0 = v_row[2 * piece];
       v1 = v_row[2 * piece + 1];
     }
+  };
+  uint4 k0, k1, v0, v1, next_k0, next_k1, next_v0, next_v1;
+  fetch(begin + warp * 4, k0, k1, v0, v1);
+  for (int base = begin + warp * 4; base < end; base += kAttnWarps * 4) {
+    fetch(base + kAttnWarps * 4, next_k0, next_k1, next_v0, next_v1);
+    const bool valid = base + sub < end;
     float kf[16], vf[16];
     unpack16(k0, k1, kf);
     unpack16(v0, v1, vf);
@@ -425,6 +431,10 @@ __global__ void __launch_bounds__(kAttnWarps * 32)
         running_max[g] = new_max;
       }
     }
+    k0 = next_k0;
+    k1 = next_k1;
+    v0 = next_v0;
+    v1 = next_v1;
   }
   // merge the warp's four position streams, then the warps, then (across the cluster) the splits
 #pragma unroll
@@ -851,7 +861,31 @@ int sageb200_glue_attention_step(const void *q, const void *k, const void *v, co
                                  int q_heads, int kv_heads, int head_dim, int max_seq, int splits, float eps,
                                  void *stream) {
   if (head_dim != 128 || kv_heads < 1 || q_heads % kv_heads || max_seq < 1 || rows < 1) return -1;
-  if (splits != 1 && splits != 2 && splits != 4 && splits != 8) return -1;  // a portable cluster size
+  if (splits != 1 && splits != 2 && splits != 4 && splits != 8 && splits != 16) return -1;
+  if (splits == 16) {  // beyond the portable cluster size: opt in, and check that one fits at all
+    static int fits = -1;
+    if (fits < 0) {
+      fits = 0;
+      if (cudaFuncSetAttribute(attention_step_kernel, cudaFuncAttributeNonPortableClusterSizeAllowed, 1) ==
+          cudaSuccess) {
+        cudaLaunchConfig_t probe = {};
+        probe.gridDim = dim3(16, 1, 1);
+        probe.blockDim = dim3(kAttnWarps * 32);
+        cudaLaunchAttribute shape[1];
+        shape[0].id = cudaLaunchAttributeClusterDimension;
+        shape[0].val.clusterDim.x = 16;
+        shape[0].val.clusterDim.y = 1;
+        shape[0].val.clusterDim.z = 1;
+        probe.attrs = shape;
+        probe.numAttrs = 1;
+        int clusters = 0;
+        if (cudaOccupancyMaxActiveClusters(&clusters, attention_step_kernel, &probe) == cudaSuccess && clusters > 0)
+          fits = 1;
+      }
+      cudaGetLastError();
+    }
+    if (!fits) return -1;
+  }
   const int group = q_heads / kv_heads;
   const int parts = (group + kStepHeads - 1) / kStepHeads;
   cudaLaunchConfig_t config = {};
