@@ -1,7 +1,7 @@
 """Benchmark of the SAGE packed-weight decode path on B200.
 
     python bench.py [--gpus N] [--steps K] [--warmup W] [--impl ours|reference]
-                    [--workload decode_model|decode_linears|tp32b|ep30b|linear:K:N:M] [--prompt P]
+                    [--workload decode_model|decode_linears|tp32b|ep30b|report|linear:K:N:M] [--prompt P]
 
 A step is one decoded token of the full Qwen3-4B architecture at batch 1 (synthetic seeded
 packed weights, ABS split cycling 6/7/8 direction bits per matrix; `decode_linears` times the
@@ -289,7 +289,14 @@ def run_model(args) -> None:
     model.capture()
     prompt = torch.randint(3, QWEN3_4B.vocab, (1, prompt_length),
                            generator=torch.Generator().manual_seed(1000 + rank))
+    model.prefill(prompt)  # warm-up of the prompt path (tensor-core GEMM plans, tensor maps)
+    torch.cuda.synchronize()
+    p0, p1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    p0.record()
     model.prefill(prompt)
+    p1.record()
+    torch.cuda.synchronize()
+    prefill_ms = p0.elapsed_time(p1)
 
     def barrier():
         if world > 1:
@@ -399,6 +406,9 @@ def run_model(args) -> None:
                             f"greedy decode after a {prompt_length}-token prompt; one step = one token "
                             f"(packed linears + norms + RoPE + attention + lm_head + argmax, one CUDA graph)",
                 "prompt_tokens": prompt_length,
+                "prefill_ms": prefill_ms,
+                "prefill_note": "whole prompt through each layer at once (packed linears on the tcgen05 GEMM "
+                                "path), first token included; not part of the timed decode steps",
                 "context_at_midpoint": context,
                 "step_hbm_bytes": step_bytes,
                 "step_hbm_gbs": step_bytes / (ms_per_step / 1000.0) / 1e9,
@@ -440,6 +450,27 @@ def run_model(args) -> None:
         print(json.dumps(line), flush=True)
     if world > 1:
         dist.destroy_process_group()
+
+
+def run_report(args) -> None:
+    """`--workload report`: Qwen3-4B, prompt `--prompt`, 256 generated tokens, measured and
+    written in the reference benchmark's schema (JSON + CSV under gpurun_out/ or ./reports)."""
+    import torch
+
+    from sage_b200.harness import measure, write_report
+    from sage_b200.qwen3 import QWEN3_4B, PackedQwen3
+
+    device = torch.device("cuda", int(os.environ.get("LOCAL_RANK", "0")))
+    torch.cuda.set_device(device)
+    decode = 256
+    model = PackedQwen3(QWEN3_4B, device, seed=0, max_seq=args.prompt + decode + 16, batch=1, max_new=decode + 16)
+    model.capture()
+    prompt = torch.randint(3, QWEN3_4B.vocab, (1, args.prompt), generator=torch.Generator().manual_seed(0))
+    result, rows = measure(model, prompt, decode, samples=max(3, min(args.steps, 10)), warmup=2)
+    folder = pathlib.Path("gpurun_out") if pathlib.Path("gpurun_out").is_dir() else pathlib.Path("reports")
+    path, csv_path = write_report(result, rows, folder, f"qwen3-4b-sage-prefill{args.prompt}-decode{decode}")
+    print(json.dumps({"report": str(path), "csv": str(csv_path),
+                      "rows": [[m, p, metric, round(value, 3), unit] for m, p, metric, value, unit in rows]}), flush=True)
 
 
 def run_tp(args) -> None:
@@ -495,10 +526,24 @@ def run_tp(args) -> None:
         stop.record()
         barrier()
     clocks = sampler.summary()
-    times = torch.tensor([start.elapsed_time(stop)], dtype=torch.float64)
+    tokens = model.log[0, : warmup + args.steps + 1].tolist()
+    # end to end: token id from pinned host memory in, next token read back, every step
+    host_token = torch.zeros(1, dtype=torch.int64).pin_memory()
+    host_next = torch.zeros(1, dtype=torch.int64).pin_memory()
+    host_token.copy_(model.tokens)
+    barrier()
+    e2e_begin = time.perf_counter()
+    for _ in range(args.steps):
+        model.tokens.copy_(host_token, non_blocking=True)
+        model.graph.replay()
+        host_next.copy_(model.tokens, non_blocking=True)
+        torch.cuda.synchronize()
+        host_token.copy_(host_next)
+    e2e_ms = 1000.0 * (time.perf_counter() - e2e_begin)
+    barrier()
+    times = torch.tensor([start.elapsed_time(stop), e2e_ms], dtype=torch.float64)
     if world > 1:
         dist.all_reduce(times, op=dist.ReduceOp.MAX, group=cpu_group)
-    tokens = model.log[0, : warmup + args.steps + 1].tolist()
     if rank == 0:
         ms_per_step = float(times[0]) / args.steps
         peak, peak_kind = measured_peaks()
@@ -532,6 +577,9 @@ def run_tp(args) -> None:
                 "peak_kind": f"of {peak_kind}",
                 "first_tokens": tokens[:8],
             },
+            "e2e": {"value": 1000.0 * args.steps / float(times[1]), "unit": UNIT, "h2d_bytes_per_step": 8,
+                    "d2h_bytes_per_step": 8},
+            "gpu_launches": int((model.sage_launches_per_step + model.glue_launches_per_step) * args.steps),
             "clocks": clocks,
         }
         print(json.dumps(line), flush=True)
@@ -713,6 +761,8 @@ def main() -> None:
         run_reference(args)
     elif args.workload.startswith("linear:"):
         run_single_linear(args)
+    elif args.workload == "report":
+        run_report(args)
     elif args.workload == "decode_model":
         run_model(args)
     elif args.workload in ("tp32b", "ep30b"):

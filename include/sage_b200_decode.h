@@ -69,6 +69,22 @@ int sageb200_glue_attention_step(const void *q, const void *k, const void *v, co
                                  int q_heads, int kv_heads, int head_dim, int max_seq, int splits, float eps,
                                  void *stream);
 
+/*
+ * Prompt processing (many tokens of each sequence at once).  Rows are [sequence][token]:
+ * row s*tokens + t is token t of sequence s and sits at cache position positions[s] + t.
+ * The first call is sageb200_glue_qk_norm_rope_cache for such rows (q normalised and rotated
+ * in place, every token's k/v written to the cache); the second is causal attention of every
+ * row over cache positions 0 .. its own, out[rows][q_heads][128].
+ */
+int sageb200_glue_prefill_qk_norm_rope_cache(void *q, const void *k, const void *v, const void *q_weight,
+                                             const void *k_weight, const void *cos_table,
+                                             const void *sin_table, const void *positions, void *k_cache,
+                                             void *v_cache, int sequences, int tokens, int q_heads,
+                                             int kv_heads, int head_dim, int max_seq, float eps, void *stream);
+int sageb200_glue_prefill_attention(const void *q, const void *k_cache, const void *v_cache,
+                                    const void *positions, void *out, int sequences, int tokens, int q_heads,
+                                    int kv_heads, int head_dim, int max_seq, void *stream);
+
 /* act[i] = fp16(silu(gate[i])) * up[i]. */
 int sageb200_glue_swiglu(const void *gate, const void *up, void *act, long long count, void *stream);
 

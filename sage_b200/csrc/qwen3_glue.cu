@@ -106,7 +106,8 @@ __global__ void qk_norm_rope_cache_kernel(__half *__restrict__ q, const __half *
                                           const __half *__restrict__ sin_table,
                                           const int *__restrict__ positions,
                                           __half *__restrict__ k_cache, __half *__restrict__ v_cache,
-                                          int q_heads, int kv_heads, int max_seq, float eps) {
+                                          int q_heads, int kv_heads, int max_seq, float eps,
+                                          int rows_per_sequence) {
   // programmatic dependent launch: let the next kernel be scheduled, then wait for the
   // previous one before touching memory
   sageb200::pdl_launch_dependents();
@@ -117,12 +118,15 @@ __global__ void qk_norm_rope_cache_kernel(__half *__restrict__ q, const __half *
   const int m = blockIdx.y;
   const int heads = q_heads + 2 * kv_heads;
   if (head >= heads) return;
-  const int position = positions[m];
+  // decode: row = sequence, at positions[row]; prefill: rows_per_sequence consecutive rows are
+  // the tokens of one sequence, at positions[sequence] + token
+  const int sequence = m / rows_per_sequence;
+  const int position = positions[sequence] + (m - sequence * rows_per_sequence);
   if (position < 0 || position >= max_seq) return;  // a full cache: write nothing out of range
   if (head >= q_heads + kv_heads) {  // value head: plain copy into the cache
     const int j = head - q_heads - kv_heads;
     const uint2 value = reinterpret_cast<const uint2 *>(v + (static_cast<size_t>(m) * kv_heads + j) * 128)[lane];
-    reinterpret_cast<uint2 *>(v_cache + ((static_cast<size_t>(m) * kv_heads + j) * max_seq + position) * 128)[lane] = value;
+    reinterpret_cast<uint2 *>(v_cache + ((static_cast<size_t>(sequence) * kv_heads + j) * max_seq + position) * 128)[lane] = value;
     return;
   }
   const bool is_query = head < q_heads;
@@ -146,7 +150,7 @@ __global__ void qk_norm_rope_cache_kernel(__half *__restrict__ q, const __half *
   const __half2 out_lo = __hadd2(__hmul2(nl, c), __hmul2(__hneg2(nh), s));
   const __half2 out_hi = __hadd2(__hmul2(nh, c), __hmul2(nl, s));
   __half *target = is_query ? q + (static_cast<size_t>(m) * q_heads + j) * 128
-                            : k_cache + ((static_cast<size_t>(m) * kv_heads + j) * max_seq + position) * 128;
+                            : k_cache + ((static_cast<size_t>(sequence) * kv_heads + j) * max_seq + position) * 128;
   reinterpret_cast<__half2 *>(target)[lane] = out_lo;
   reinterpret_cast<__half2 *>(target + 64)[lane] = out_hi;
 }
@@ -312,7 +316,7 @@ __global__ void __launch_bounds__(kAttnWarps * 32)
                           const __half *__restrict__ k_weight, const __half *__restrict__ cos_table,
                           const __half *__restrict__ sin_table, const int *__restrict__ positions,
                           __half *k_cache, __half *v_cache, __half *__restrict__ out, int q_heads,
-                          int kv_heads, int max_seq, float eps, float scale) {
+                          int kv_heads, int max_seq, float eps, float scale, int rows_per_sequence) {
   sageb200::pdl_launch_dependents();
   sageb200::pdl_wait();
 
@@ -332,8 +336,14 @@ __global__ void __launch_bounds__(kAttnWarps * 32)
   const int kv = blockIdx.y / parts, part = blockIdx.y - kv * parts;
   const int heads = min(kStepHeads, group - part * kStepHeads);
   const int first_head = kv * group + part * kStepHeads;
-  const int position = positions[m];
-  const bool in_range = position >= 0 && position < max_seq;  // a full cache takes no new token
+  // rows_per_sequence == 0: a decode step (row = sequence; q and the new k are normalised and
+  // rotated here and the new k/v appended).  > 0: prompt rows - that many consecutive rows are
+  // the tokens of one sequence at positions[sequence] + token, q is already normalised and
+  // rotated and the cache already holds every token's k/v.
+  const bool prompt = rows_per_sequence > 0;
+  const int sequence = prompt ? m / rows_per_sequence : m;
+  const int position = positions[sequence] + (prompt ? m - sequence * rows_per_sequence : 0);
+  const bool in_range = !prompt && position >= 0 && position < max_seq;  // a full cache takes no new token
   const int table_row = min(max(position, 0), max_seq - 1);
   const int context = min(position + 1, max_seq);
   const int chunk = (context + splits - 1) / splits;
@@ -342,16 +352,21 @@ __global__ void __launch_bounds__(kAttnWarps * 32)
   const bool owns_new = in_range && begin <= position && position < end;
   const __half *cos_row = cos_table + static_cast<size_t>(table_row) * 64;
   const __half *sin_row = sin_table + static_cast<size_t>(table_row) * 64;
-  __half *k_base = k_cache + (static_cast<size_t>(m) * kv_heads + kv) * max_seq * 128;
-  __half *v_base = v_cache + (static_cast<size_t>(m) * kv_heads + kv) * max_seq * 128;
+  __half *k_base = k_cache + (static_cast<size_t>(sequence) * kv_heads + kv) * max_seq * 128;
+  __half *v_base = v_cache + (static_cast<size_t>(sequence) * kv_heads + kv) * max_seq * 128;
 
   // items 0..heads-1: this CTA's query heads; item `heads`: the new token's key and value
   // (every part needs them, part 0 stores them)
   for (int item = warp; item < heads + (owns_new ? 1 : 0); item += kAttnWarps) {
     __half2 lo, hi;
     if (item < heads) {
-      norm_rope_head(q + (static_cast<size_t>(m) * q_heads + first_head + item) * 128, q_weight, cos_row,
-                     sin_row, eps, lane, lo, hi);
+      const __half *source = q + (static_cast<size_t>(m) * q_heads + first_head + item) * 128;
+      if (prompt) {
+        lo = reinterpret_cast<const __half2 *>(source)[lane];
+        hi = reinterpret_cast<const __half2 *>(source + 64)[lane];
+      } else {
+        norm_rope_head(source, q_weight, cos_row, sin_row, eps, lane, lo, hi);
+      }
       reinterpret_cast<__half2 *>(q_shared[item])[lane] = lo;
       reinterpret_cast<__half2 *>(q_shared[item] + 64)[lane] = hi;
     } else {
@@ -830,7 +845,25 @@ int sageb200_glue_qk_norm_rope_cache(void *q, const void *k, const void *v, cons
       static_cast<const __half *>(q_weight), static_cast<const __half *>(k_weight),
       static_cast<const __half *>(cos_table), static_cast<const __half *>(sin_table),
       static_cast<const int *>(positions), static_cast<__half *>(k_cache),
-      static_cast<__half *>(v_cache), q_heads, kv_heads, max_seq, eps);
+      static_cast<__half *>(v_cache), q_heads, kv_heads, max_seq, eps, 1);
+  return launch_status();
+}
+
+int sageb200_glue_prefill_qk_norm_rope_cache(void *q, const void *k, const void *v, const void *q_weight,
+                                             const void *k_weight, const void *cos_table,
+                                             const void *sin_table, const void *positions, void *k_cache,
+                                             void *v_cache, int sequences, int tokens, int q_heads,
+                                             int kv_heads, int head_dim, int max_seq, float eps, void *stream) {
+  if (head_dim != 128 || sequences < 1 || tokens < 1 || static_cast<long long>(sequences) * tokens > 65535)
+    return -1;
+  const int heads = q_heads + 2 * kv_heads;
+  const dim3 grid((heads + 3) / 4, sequences * tokens);
+  sageb200::launch_dependent<2>(qk_norm_rope_cache_kernel, grid, 128, 0, static_cast<cudaStream_t>(stream),
+      static_cast<__half *>(q), static_cast<const __half *>(k), static_cast<const __half *>(v),
+      static_cast<const __half *>(q_weight), static_cast<const __half *>(k_weight),
+      static_cast<const __half *>(cos_table), static_cast<const __half *>(sin_table),
+      static_cast<const int *>(positions), static_cast<__half *>(k_cache),
+      static_cast<__half *>(v_cache), q_heads, kv_heads, max_seq, eps, tokens);
   return launch_status();
 }
 
@@ -908,7 +941,36 @@ int sageb200_glue_attention_step(const void *q, const void *k, const void *v, co
       static_cast<const __half *>(k_weight), static_cast<const __half *>(cos_table),
       static_cast<const __half *>(sin_table), static_cast<const int *>(positions),
       static_cast<__half *>(k_cache), static_cast<__half *>(v_cache), static_cast<__half *>(out), q_heads,
-      kv_heads, max_seq, eps, rsqrtf(128.0f));
+      kv_heads, max_seq, eps, rsqrtf(128.0f), 0);
+  return error == cudaSuccess ? launch_status() : -5;
+}
+
+int sageb200_glue_prefill_attention(const void *q, const void *k_cache, const void *v_cache,
+                                    const void *positions, void *out, int sequences, int tokens, int q_heads,
+                                    int kv_heads, int head_dim, int max_seq, void *stream) {
+  if (head_dim != 128 || kv_heads < 1 || q_heads % kv_heads || max_seq < 1 || sequences < 1 || tokens < 1 ||
+      static_cast<long long>(sequences) * tokens > 65535)
+    return -1;
+  const int group = q_heads / kv_heads;
+  const int parts = (group + kStepHeads - 1) / kStepHeads;
+  cudaLaunchConfig_t config = {};
+  config.gridDim = dim3(1, kv_heads * parts, sequences * tokens);  // one CTA per cluster: short contexts
+  config.blockDim = dim3(kAttnWarps * 32);
+  config.stream = static_cast<cudaStream_t>(stream);
+  cudaLaunchAttribute attributes[1];
+  attributes[0].id = cudaLaunchAttributeClusterDimension;
+  attributes[0].val.clusterDim.x = 1;
+  attributes[0].val.clusterDim.y = 1;
+  attributes[0].val.clusterDim.z = 1;
+  config.attrs = attributes;
+  config.numAttrs = 1;
+  __atomic_fetch_add(&sageb200::g_sageb200_glue_launches, 1ull, __ATOMIC_RELAXED);
+  const __half *none = nullptr;
+  const cudaError_t error = cudaLaunchKernelEx(
+      &config, attention_step_kernel, static_cast<const __half *>(q), none, none, none, none, none, none,
+      static_cast<const int *>(positions), static_cast<__half *>(const_cast<void *>(k_cache)),
+      static_cast<__half *>(const_cast<void *>(v_cache)), static_cast<__half *>(out), q_heads, kv_heads, max_seq,
+      0.0f, rsqrtf(128.0f), tokens);
   return error == cudaSuccess ? launch_status() : -5;
 }
 

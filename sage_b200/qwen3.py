@@ -23,7 +23,7 @@ import math
 import torch
 
 from . import _lib
-from .ops import sage_dequantize, sage_grouped
+from .ops import sage_dequantize, sage_forward, sage_grouped
 from .experts import SAGEExperts, expert_slice, route, synthetic_expert_stack
 from .parallel import block_permutation, shard_columns, shard_rows, shard_vocab
 from .synthetic import linear_algorithmic_bytes, synthetic_sage_device
@@ -397,17 +397,85 @@ class PackedQwen3:
         self.step_counter.zero_()
         self.log.zero_()
 
-    def prefill(self, prompt: torch.Tensor):
-        """Feed `prompt` [batch, length] through the cache one position at a time (the same
-        kernels as decoding); after it, `self.tokens` holds the first generated token."""
+    def prefill(self, prompt: torch.Tensor, batched: bool | None = None):
+        """Run `prompt` [batch, length] into the cache; after it, `self.tokens` holds the first
+        generated token.  `batched` (the default on one GPU for a dense-MLP config): all
+        prompt tokens go through each layer together - packed linears on the tensor-core GEMM
+        path from 33 rows up, causal attention over the prompt.  Otherwise the prompt is fed
+        one position at a time through the decode graph."""
         if self.graph is None:
             self.capture()
         self.reset()
         prompt = prompt.to(self.device)
         length = prompt.shape[1]
+        if batched is None:
+            batched = (self.tp_world == 1 and self.ep_world == 1 and not self.config.experts and length > 1
+                       and self.batch * length <= 65535)
+        if batched:
+            return self._prefill_batched(prompt)
         for i in range(length):
             self.tokens.copy_(prompt[:, i])
             (self.graph if i == length - 1 else self.graph_no_head).replay()
+
+    def _rows_linears(self, layer, names, x):
+        if self.dense:
+            return [torch.nn.functional.linear(x, layer[name].weight) for name in names]
+        return [sage_forward(*layer[name].problem(x), layer[name].n) for name in names]
+
+    def _prefill_batched(self, prompt: torch.Tensor):
+        if self.tp_world > 1 or self.ep_world > 1 or self.config.experts:
+            raise ValueError("batched prefill runs on one GPU with a dense-MLP config")
+        c, lib, b = self.config, self.lib, self.batch
+        length = prompt.shape[1]
+        rows = b * length  # row = sequence * length + token
+        half = dict(dtype=torch.float16, device=self.device)
+        with torch.cuda.device(self.device):
+            s = self._stream()
+            tokens = prompt.reshape(-1).to(torch.int64).contiguous()
+            h = torch.empty(rows, c.hidden, **half)
+            x = torch.empty_like(h)
+            attn = torch.empty(rows, self.heads * c.head_dim, **half)
+            self._check(lib.sageb200_glue_embed(_vp(self.embed), _vp(tokens), _vp(h), rows, c.hidden, s), "embed")
+            delta = None
+            for layer in self.layers:
+                self._check(lib.sageb200_glue_add_rmsnorm(_vp(h), _vp(delta), _vp(layer["input_norm"]), _vp(x), rows,
+                                                          c.hidden, c.eps, s), "add_rmsnorm")
+                q, k, v = self._rows_linears(layer, ("q", "k", "v"), x)
+                self._check(lib.sageb200_glue_prefill_qk_norm_rope_cache(
+                    _vp(q), _vp(k), _vp(v), _vp(layer["q_norm"]), _vp(layer["k_norm"]), _vp(self.cos), _vp(self.sin),
+                    _vp(self.positions), _vp(layer["k_cache"]), _vp(layer["v_cache"]), b, length, self.heads,
+                    self.kv_heads, c.head_dim, self.max_seq, c.eps, s), "prefill_qk_norm_rope_cache")
+                self._check(lib.sageb200_glue_prefill_attention(
+                    _vp(q), _vp(layer["k_cache"]), _vp(layer["v_cache"]), _vp(self.positions), _vp(attn), b, length,
+                    self.heads, self.kv_heads, c.head_dim, self.max_seq, s), "prefill_attention")
+                (o,) = self._rows_linears(layer, ("o",), attn)
+                self._check(lib.sageb200_glue_add_rmsnorm(_vp(h), _vp(o), _vp(layer["post_norm"]), _vp(x), rows,
+                                                          c.hidden, c.eps, s), "add_rmsnorm")
+                gate, up = self._rows_linears(layer, ("gate", "up"), x)
+                act = torch.empty_like(gate)
+                self._check(lib.sageb200_glue_swiglu(_vp(gate), _vp(up), _vp(act), gate.numel(), s), "swiglu")
+                (delta,) = self._rows_linears(layer, ("down",), act)
+            # the step tail on each sequence's last prompt token
+            last = torch.arange(b, device=self.device) * length + (length - 1)
+            h_last, delta_last = h[last].contiguous(), delta[last].contiguous()
+            self.positions.add_(length - 1)
+            if self.fuse_glue and not self.dense:
+                self._check(lib.sageb200_glue_lm_head_step(
+                    _vp(self.lm_head), _vp(h_last), _vp(delta_last), _vp(self.final_norm), _vp(self.x),
+                    _vp(self.logits), _vp(self.tokens), _vp(self.positions), _vp(self.log), _vp(self.step_counter),
+                    _vp(self.head_scratch), b, c.vocab, c.hidden, c.eps, self.max_new, self.sm_count, s),
+                    "lm_head_step")
+                return
+            self._check(lib.sageb200_glue_add_rmsnorm(_vp(h_last), _vp(delta_last), _vp(self.final_norm),
+                                                      _vp(self.x), b, c.hidden, c.eps, s), "final norm")
+            if self.dense:
+                torch.matmul(self.x, self.lm_head.T, out=self.logits)
+            else:
+                self._check(lib.sageb200_glue_lm_head(_vp(self.lm_head), _vp(self.x), _vp(self.logits), b, c.vocab,
+                                                      c.hidden, self.sm_count, s), "lm_head")
+            self._check(lib.sageb200_glue_argmax_advance(_vp(self.logits), _vp(self.tokens), _vp(self.positions),
+                                                         _vp(self.log), _vp(self.step_counter), b, c.vocab,
+                                                         self.max_new, s), "argmax")
 
     def generate(self, prompt: torch.Tensor, new_tokens: int) -> torch.Tensor:
         """Greedy generation; returns [batch, new_tokens] token ids (device tensor)."""

@@ -123,6 +123,56 @@ def test_generate_is_repeatable_and_batched():
         assert same >= 8, (row, same)
 
 
+@pytest.mark.parametrize("length", [5, 48])
+def test_batched_prefill_matches_token_by_token(length):
+    """The prompt through every layer at once (tensor-core GEMM path from 33 rows up, causal
+    attention over the prompt) against the prompt fed one position at a time through the
+    decode graph: same KV cache and logits to FP16 rounding, then the same greedy tokens."""
+    config = Qwen3Config(layers=3, hidden=512, heads=8, kv_heads=2, intermediate=1024, vocab=2048)
+    prompt = torch.randint(3, config.vocab, (2, length), generator=torch.Generator().manual_seed(length))
+    model = PackedQwen3(config, "cuda:0", seed=5, max_seq=96, batch=2, max_new=16)
+    model.prefill(prompt, batched=False)
+    torch.cuda.synchronize()
+    want_logits, want_token = model.logits.float().clone(), model.tokens.clone()
+    want_cache = [(layer["k_cache"].float().clone(), layer["v_cache"].float().clone()) for layer in model.layers]
+    for layer in model.layers:
+        layer["k_cache"].zero_()
+        layer["v_cache"].zero_()
+    model.prefill(prompt, batched=True)
+    torch.cuda.synchronize()
+    assert int(model.positions[0]) == length and int(model.step_counter) == 1
+    for layer, (k_want, v_want) in zip(model.layers, want_cache):
+        for got, want in ((layer["k_cache"].float(), k_want), (layer["v_cache"].float(), v_want)):
+            assert (got - want).norm() / want.norm() < 5e-3
+            assert torch.equal(got[:, :, length:], want[:, :, length:])  # nothing beyond the prompt
+    error = ((model.logits.float() - want_logits).norm() / want_logits.norm()).item()
+    assert error < 1e-2, error
+    margin = want_logits.topk(2, dim=-1).values
+    clear = (margin[:, 0] - margin[:, 1]) > 0.05 * want_logits.std()
+    assert torch.equal(model.tokens[clear], want_token[clear])
+    tokens = model.generate(prompt, 8)  # batched prefill by default, then the decode graph
+    assert tokens.shape == (2, 8) and int(model.positions[0]) == length + 7
+
+
+def test_report_rows_on_a_small_model():
+    """The reference-schema measurement loop runs end to end and its numbers hang together."""
+    from sage_b200.harness import measure
+
+    config = Qwen3Config(layers=2, hidden=512, heads=4, kv_heads=2, intermediate=1024, vocab=2048)
+    model = PackedQwen3(config, "cuda:0", seed=1, max_seq=128, max_new=16)
+    model.capture()
+    prompt = torch.randint(3, config.vocab, (1, 40), generator=torch.Generator().manual_seed(0))
+    result, rows = measure(model, prompt, decode=9, samples=3, warmup=1)
+    table = {(phase, metric): value for _, phase, metric, value, _ in rows}
+    assert set(table) == {("prefill", "forward_latency"), ("prefill", "input_throughput"),
+                          ("decode", "forward_tpot"), ("decode", "output_throughput"),
+                          ("end_to_end", "generate_latency"), ("end_to_end", "output_throughput"),
+                          ("end_to_end", "ttft"), ("end_to_end", "tpot")}
+    assert all(value > 0 for value in table.values())
+    assert table[("end_to_end", "ttft")] <= table[("end_to_end", "generate_latency")]
+    assert len(result["samples"]["decode"]) == 3
+
+
 def test_routed_experts_match_per_expert_linears():
     """`SAGEExperts` (device-side expert selection, stacked buffers) against one `SAGELinear`
     per routed expert, for one token and for several; and the expert-parallel split: two

@@ -1,5 +1,5 @@
-"""Tensor-parallel decode on two GPUs (NCCL): the TP=2 model must produce the tokens of the
-same model on one GPU.  Skipped when fewer than two GPUs are visible."""
+"""Tensor-parallel and expert-parallel decode on two GPUs (NCCL): the 2-GPU model must produce
+the tokens of the same model on one GPU.  Skipped when fewer than two GPUs are visible."""
 
 import os
 import tempfile
@@ -12,7 +12,7 @@ import torch.multiprocessing as mp
 pytestmark = pytest.mark.gpu
 
 
-def _worker(rank, world, path, results):
+def _worker(rank, world, path, results, experts=False):
     os.environ["NCCL_NVLS_ENABLE"] = "0"
     torch.cuda.set_device(rank)
     dist.init_process_group("nccl", init_method=f"file://{path}", rank=rank, world_size=world,
@@ -21,10 +21,15 @@ def _worker(rank, world, path, results):
     try:
         from sage_b200.qwen3 import PackedQwen3, Qwen3Config
 
-        config = Qwen3Config(layers=3, hidden=1024, heads=8, kv_heads=2, intermediate=2048, vocab=4096)
+        if experts:  # mixture of experts: each rank keeps half of the experts
+            config = Qwen3Config(layers=3, hidden=1024, heads=8, kv_heads=2, intermediate=2048, vocab=4096,
+                                 experts=8, top_k=2, moe_intermediate=256)
+            parallel = dict(ep_group=dist.group.WORLD)
+        else:
+            config = Qwen3Config(layers=3, hidden=1024, heads=8, kv_heads=2, intermediate=2048, vocab=4096)
+            parallel = dict(tp_group=dist.group.WORLD)
         prompt = torch.randint(3, config.vocab, (1, 12), generator=torch.Generator().manual_seed(4))
-        sharded = PackedQwen3(config, f"cuda:{rank}", seed=2, max_seq=96, max_new=40,
-                              tp_group=dist.group.WORLD, perm_blocks=4)
+        sharded = PackedQwen3(config, f"cuda:{rank}", seed=2, max_seq=96, max_new=40, perm_blocks=4, **parallel)
         tokens = sharded.generate(prompt, 40).cpu()
         logits = sharded.logits.float().cpu()
         if rank == 0:
@@ -42,14 +47,15 @@ def _worker(rank, world, path, results):
         os._exit(0)  # no NCCL teardown under live CUDA graphs
 
 
-def test_tp2_matches_single_gpu():
+@pytest.mark.parametrize("experts", [False, True], ids=["tensor_parallel", "expert_parallel"])
+def test_two_gpus_match_single_gpu(experts):
     if torch.cuda.device_count() < 2:
         pytest.skip("needs two GPUs")
     context = mp.get_context("spawn")
     results = context.Queue()
     with tempfile.TemporaryDirectory() as folder:
         path = os.path.join(folder, "rendezvous")
-        procs = [context.Process(target=_worker, args=(r, 2, path, results)) for r in range(2)]
+        procs = [context.Process(target=_worker, args=(r, 2, path, results, experts)) for r in range(2)]
         for p in procs:
             p.start()
         for p in procs:
