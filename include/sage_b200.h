@@ -223,6 +223,27 @@ int sageb200_linear_host(const void *x_host, const void *codes, const void *radi
 int sageb200_set_tuning(int warps, int slices, int ctas_per_sm, int mode);
 
 /*
+ * SPHQuant 64/4 packed linear, y[rows][n] = x[rows][k] . W^T: replaces the reference's
+ * sph_gemv_forward_cuda (csrc/sphquant/sph_gemv_cuda.cu:403-469, declared at
+ * csrc/sphquant/sph_gemv_cuda.h:5-11).  Row-major buffers: codes int16 [n][k/8] (bits 0-7
+ * signs, 8-13 direction index, 14-15 low radius bits; 16-byte aligned), extra int32 [n][k/128]
+ * (sixteen 2-bit high radius fields), scales / mins fp16 [n][k/128], book fp16 [64][8]
+ * (16-byte aligned).  k % 128 == 0, k <= 16384 (the reference's limit); x FP16 contiguous, any
+ * 2-byte alignment; rows <= 65535.  The packed weights are read once per eight activation rows;
+ * sums across vectors are FP32.  No scratch.
+ */
+int sageb200_sph_linear(const void *x, const void *codes, const void *extra, const void *scales,
+                        const void *mins, const void *book, void *y, int rows, int n, int k, void *stream);
+
+/*
+ * Dense FP16 weight w[n][k] = fp16(float(+-book[index][d]) * fmaf(code, scale, min)) of an
+ * SPHQuant matrix, bit-identical to the reference's arithmetic decode
+ * (tests/inference/reference.py:16-22) rounded to FP16.  The reference has no such kernel.
+ */
+int sageb200_sph_dequant(const void *codes, const void *extra, const void *scales, const void *mins,
+                         const void *book, void *w, int n, int k, void *stream);
+
+/*
  * Programmatic dependent launch (on by default): the decode kernel and the decode glue are
  * launched so that they may be scheduled before the previous kernel of the stream has
  * finished; they prefetch packed weights and codebooks, then wait for the previous kernel

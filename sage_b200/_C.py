@@ -1,8 +1,10 @@
-"""Same public signature as the reference's compiled extension
-(weight_vq/inference/_C.pyi:14-22 there), so `from sage_b200 import _C` can stand in
-for `from weight_vq.inference import _C` inside the reference's `wvq::sage` op."""
+"""Same public signatures as the reference's compiled extension
+(weight_vq/inference/_C.pyi there; bindings at csrc/bindings.cpp:85-87), so
+`from sage_b200 import _C` can stand in for `from weight_vq.inference import _C` inside the
+reference's `wvq::sage` and `wvq::sphquant` ops."""
 
 from .ops import sage_forward as sage_gemv_forward_cuda  # noqa: F401
+from .sphquant import sph_gemv_forward as sph_gemv_forward_cuda  # noqa: F401
 
 
 def _set_sage_tuning(value: int) -> None:

@@ -6,13 +6,18 @@ raises if `libsage_b200.so` has not been built (`python -m sage_b200.build`).
 
 from .linear import SAGELinear
 from .ops import sage, sage_dequantize, sage_forward, sage_grouped
-from .synthetic import synthetic_sage
+from .sphquant import SPHQuantLinear, sph_dequantize, sphquant
+from .synthetic import synthetic_sage, synthetic_sphquant
 
 __all__ = [
     "SAGELinear",
+    "SPHQuantLinear",
     "sage",
     "sage_dequantize",
     "sage_forward",
     "sage_grouped",
+    "sph_dequantize",
+    "sphquant",
     "synthetic_sage",
+    "synthetic_sphquant",
 ]

@@ -35,6 +35,8 @@ EXPORTED = (
     "sageb200_set_tuning",
     "sageb200_debug_trace",
     "sageb200_set_pdl",
+    "sageb200_sph_linear",
+    "sageb200_sph_dequant",
     "sageb200_linear_static",
     "sageb200_launch_count",
     "sageb200_glue_launch_count",
@@ -156,6 +158,10 @@ def load() -> ctypes.CDLL:
     lib.sageb200_set_tuning.argtypes = [ci, ci, ci, ci]
     lib.sageb200_linear_static.restype = ci
     lib.sageb200_linear_static.argtypes = [vp, vp, vp, vp, vp, vp, vp, ci, ci, ci, ci, vp]
+    lib.sageb200_sph_linear.restype = ci
+    lib.sageb200_sph_linear.argtypes = [vp] * 7 + [ci] * 3 + [vp]
+    lib.sageb200_sph_dequant.restype = ci
+    lib.sageb200_sph_dequant.argtypes = [vp] * 6 + [ci] * 2 + [vp]
     lib.sageb200_set_pdl.restype = ci
     lib.sageb200_set_pdl.argtypes = [ci]
     lib.sageb200_debug_trace.restype = ci

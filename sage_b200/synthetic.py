@@ -130,3 +130,27 @@ def linear_algorithmic_bytes(rows: int, n: int, k: int, entries: int, permuted: 
     padded rows), codebook, permutation, activations in and out."""
     padded = (n + 15) // 16 * 16
     return padded * k * 5 // 16 + 16 * entries + (4 * k if permuted else 0) + 2 * rows * k + 2 * rows * n
+
+
+def synthetic_sphquant(in_features: int, out_features: int, seed: int = 0) -> dict[str, torch.Tensor]:
+    """Seeded SPHQuant 64/4 buffers on the CPU, drawn in the order of the reference generator
+    (weight_vq/checkpoint.py:35-51) so that equal seeds give equal bits: a unit-norm non-negative
+    [64, 8] codebook, every 16-bit code pattern, every 32-bit high-radius word, FP16
+    (scale, minimum) per (row, 128-channel group) sized for unit-variance outputs."""
+    if in_features <= 0 or in_features % 128 or out_features <= 0:
+        raise ValueError("SPHQuant requires positive N and K divisible by 128")
+    gen = torch.Generator().manual_seed(seed)
+    codebook = torch.nn.functional.normalize(torch.rand(64, 8, generator=gen), dim=-1).half()
+    cells = (out_features, in_features // 128)
+    unit = (8 / in_features) ** 0.5
+    codes = torch.randint(-32768, 32768, (out_features, in_features // 8), generator=gen, dtype=torch.int16)
+    extra = torch.randint(-(2**31), 2**31, cells, generator=gen, dtype=torch.int32)
+    scales = (torch.rand(cells, generator=gen) * unit / 15).half()
+    mins = (torch.rand(cells, generator=gen) * unit).half()
+    return {"packed_codes": codes, "radius_extra": extra, "radius_scales": scales, "radius_mins": mins,
+            "codebook": codebook}
+
+
+def sph_algorithmic_bytes(rows: int, n: int, k: int) -> int:
+    """HBM bytes one SPHQuant linear call has to move: packed buffers once, x and y."""
+    return n * k // 4 + n * (k // 128) * 8 + 64 * 16 + 2 * rows * k + 2 * rows * n
