@@ -1,7 +1,7 @@
 """Benchmark of the SAGE packed-weight decode path on B200.
 
     python bench.py [--gpus N] [--steps K] [--warmup W] [--impl ours|reference]
-                    [--workload decode_model|decode_linears|tp32b|ep30b|report|linear:K:N:M] [--prompt P]
+                    [--workload decode_model|decode_linears|tp32b|ep30b|report|linear:K:N:M|sph:K:N:M] [--prompt P]
 
 A step is one decoded token of the full Qwen3-4B architecture at batch 1 (synthetic seeded
 packed weights, ABS split cycling 6/7/8 direction bits per matrix; `decode_linears` times the
@@ -260,6 +260,52 @@ def run_single_linear(args) -> None:
         "config": {"workload": args.workload, "copies": copies, "launch": "eager, back to back"},
         "us_per_launch": seconds * 1e6, "bytes_per_launch": one, "frac": one / seconds / 1e9 / peak,
         "peak_kind": f"of {kind}", "gpu_launches": int(launches),
+    }), flush=True)
+
+
+def run_sph_linear(args) -> None:
+    """`--workload sph:K:N:M` - one SPHQuant 64/4 shape (the `wvq::sphquant` kernel) cycled over
+    enough distinct weight copies to exceed L2, one CUDA graph of all copies per step."""
+    import torch
+
+    from sage_b200 import SPHQuantLinear, synthetic_sphquant
+    from sage_b200.synthetic import sph_algorithmic_bytes
+
+    _, k, n, rows = args.workload.split(":")
+    k, n, rows = int(k), int(n), int(rows)
+    torch.cuda.set_device(0)
+    device = torch.device("cuda", 0)
+    one = sph_algorithmic_bytes(rows, n, k)
+    copies = max(2, int(200e6 // one) + 1)
+    layers = [SPHQuantLinear({key: t.to(device) for key, t in synthetic_sphquant(k, n, i).items()}) for i in range(copies)]
+    x = torch.randn(rows, k, device=device, dtype=torch.float16)
+    side = torch.cuda.Stream()
+    side.wait_stream(torch.cuda.current_stream())
+    with torch.cuda.stream(side):
+        for layer in layers:
+            layer(x)
+    torch.cuda.current_stream().wait_stream(side)
+    torch.cuda.synchronize()
+    graph = torch.cuda.CUDAGraph()
+    with torch.cuda.graph(graph):
+        for layer in layers:
+            layer(x)
+    for _ in range(max(args.warmup, 3)):
+        graph.replay()
+    start, stop = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    start.record()
+    for _ in range(args.steps):
+        graph.replay()
+    stop.record()
+    torch.cuda.synchronize()
+    passes = (rows + 7) // 8
+    seconds = start.elapsed_time(stop) / 1000.0 / (args.steps * copies)
+    peak, kind = measured_peaks()
+    print(json.dumps({
+        "metric": "sphquant_linear_hbm_gbs", "value": one / seconds / 1e9, "unit": "GB/s",
+        "config": {"workload": args.workload, "copies": copies, "launch": "one CUDA graph of all copies"},
+        "us_per_call": seconds * 1e6, "bytes_per_call": one, "frac": one / seconds / 1e9 / peak,
+        "peak_kind": f"of {kind}", "gpu_launches": int(args.steps * copies * passes),
     }), flush=True)
 
 
@@ -761,6 +807,8 @@ def main() -> None:
         run_reference(args)
     elif args.workload.startswith("linear:"):
         run_single_linear(args)
+    elif args.workload.startswith("sph:"):
+        run_sph_linear(args)
     elif args.workload == "report":
         run_report(args)
     elif args.workload == "decode_model":

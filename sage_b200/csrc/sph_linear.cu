@@ -51,11 +51,12 @@ __device__ __forceinline__ SphChunk load_chunk(const uint16_t *codes, const uint
   return c;
 }
 
-// One warp = four output rows at a time (eight lanes each); a lane walks every eighth 64-weight
+// One warp = 32 / L output rows at a time (L = 8, 16 or 32 lanes each: fewer rows per warp when
+// the matrix has few rows, so that every SM still gets work); a lane walks every L-th 64-weight
 // chunk of its row.  Per code: direction from the replicated codebook (one LDS.128, replica =
 // lane % 8, conflict-free), signs XORed in, FP16 dot with the eight activations per row of x,
 // FP32 multiply by the radius and FP32 accumulation.
-template <int M>
+template <int M, int L>
 __global__ void __launch_bounds__(kSphThreads)
     sph_skinny_kernel(const __half *__restrict__ x, const uint16_t *__restrict__ codes,
                       const uint32_t *__restrict__ extra, const __half *__restrict__ scales,
@@ -96,19 +97,20 @@ __global__ void __launch_bounds__(kSphThreads)
   }
   __syncthreads();
 
-  const int sub = lane >> 3, l = lane & 7;
-  const uint32_t book_base = smem_address(book_shared) + static_cast<uint32_t>(l) * 16u;
-  const int quads = (n + 3) >> 2;
+  constexpr int kRowsPerWarp = 32 / L;
+  const int sub = lane / L, l = lane % L;
+  const uint32_t book_base = smem_address(book_shared) + static_cast<uint32_t>(lane & 7) * 16u;
+  const int quads = (n + kRowsPerWarp - 1) / kRowsPerWarp;
   for (int quad = blockIdx.x * kSphWarps + warp; quad < quads; quad += gridDim.x * kSphWarps) {
-    const int row = quad * 4 + sub;
+    const int row = quad * kRowsPerWarp + sub;
     const bool row_valid = row < n;
     float acc[M];
 #pragma unroll
     for (int m = 0; m < M; ++m) acc[m] = 0.0f;
     SphChunk current = load_chunk(codes, extra, scales, mins, row, l, chunks, groups, row_valid && l < chunks);
-    for (int chunk = l; chunk < chunks; chunk += 8) {
-      const SphChunk next = load_chunk(codes, extra, scales, mins, row, chunk + 8, chunks, groups,
-                                       row_valid && chunk + 8 < chunks);
+    for (int chunk = l; chunk < chunks; chunk += L) {
+      const SphChunk next = load_chunk(codes, extra, scales, mins, row, chunk + L, chunks, groups,
+                                       row_valid && chunk + L < chunks);
       const uint32_t words[4] = {current.codes.x, current.codes.y, current.codes.z, current.codes.w};
       const uint32_t high = current.extra >> ((chunk & 1) * 16);  // this half group's eight fields
 #pragma unroll
@@ -142,9 +144,8 @@ __global__ void __launch_bounds__(kSphThreads)
 #pragma unroll
     for (int m = 0; m < M; ++m) {
       float total = acc[m];
-      total += __shfl_xor_sync(0xffffffffu, total, 1);
-      total += __shfl_xor_sync(0xffffffffu, total, 2);
-      total += __shfl_xor_sync(0xffffffffu, total, 4);
+#pragma unroll
+      for (int o = 1; o < L; o <<= 1) total += __shfl_xor_sync(0xffffffffu, total, o);
       if (l == 0 && row_valid && m < rows) y[static_cast<size_t>(m) * n + row] = __float2half_rn(total);
     }
   }
@@ -178,24 +179,39 @@ __global__ void sph_dequant_kernel(const uint16_t *__restrict__ codes, const uin
   reinterpret_cast<uint4 *>(w)[v] = *reinterpret_cast<const uint4 *>(out);
 }
 
-template <int M>
-cudaError_t launch_sph(const __half *x, const uint16_t *codes, const uint32_t *extra, const __half *scales,
-                       const __half *mins, const uint4 *book, __half *y, int rows, int n, int k, int sm_count,
-                       cudaStream_t stream) {
+template <int M, int L>
+cudaError_t launch_sph_lanes(const __half *x, const uint16_t *codes, const uint32_t *extra, const __half *scales,
+                             const __half *mins, const uint4 *book, __half *y, int rows, int n, int k, int sm_count,
+                             cudaStream_t stream) {
   const size_t shared = kSphBookBytes + static_cast<size_t>(M) * (k / 64) * kSphChunkHalves * sizeof(__half);
   static bool configured = false;  // per instantiation
   if (!configured) {
-    const cudaError_t error = cudaFuncSetAttribute(sph_skinny_kernel<M>, cudaFuncAttributeMaxDynamicSharedMemorySize,
-                                                   200 * 1024);
+    const cudaError_t error = cudaFuncSetAttribute(sph_skinny_kernel<M, L>,
+                                                   cudaFuncAttributeMaxDynamicSharedMemorySize, 200 * 1024);
     if (error != cudaSuccess) return error;
     configured = true;
   }
   const int per_sm = shared <= 100 * 1024 ? 2 : 1;
-  const int quads = (n + 3) / 4;
+  const int quads = (n + 32 / L - 1) / (32 / L);
   int ctas = (quads + kSphWarps - 1) / kSphWarps;
   if (ctas > sm_count * per_sm) ctas = sm_count * per_sm;
-  return launch_dependent(sph_skinny_kernel<M>, dim3(ctas), dim3(kSphThreads), shared, stream, x, codes, extra,
+  return launch_dependent(sph_skinny_kernel<M, L>, dim3(ctas), dim3(kSphThreads), shared, stream, x, codes, extra,
                           scales, mins, book, y, rows, n, k);
+}
+
+// Lanes per output row: as few as keep every SM's warps busy (more rows per warp share the
+// activation reads), never more than the row has chunks.
+template <int M>
+cudaError_t launch_sph(const __half *x, const uint16_t *codes, const uint32_t *extra, const __half *scales,
+                       const __half *mins, const uint4 *book, __half *y, int rows, int n, int k, int sm_count,
+                       cudaStream_t stream) {
+  const long long warps = static_cast<long long>(sm_count) * kSphWarps;
+  const int chunks = k / 64;
+  if (chunks >= 32 && static_cast<long long>(n) < warps * 2)
+    return launch_sph_lanes<M, 32>(x, codes, extra, scales, mins, book, y, rows, n, k, sm_count, stream);
+  if (chunks >= 16 && static_cast<long long>(n) < warps * 4)
+    return launch_sph_lanes<M, 16>(x, codes, extra, scales, mins, book, y, rows, n, k, sm_count, stream);
+  return launch_sph_lanes<M, 8>(x, codes, extra, scales, mins, book, y, rows, n, k, sm_count, stream);
 }
 
 int sph_sm_count() {
