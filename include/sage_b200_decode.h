@@ -112,6 +112,21 @@ int sageb200_glue_lm_head_step(const void *head, const void *residual, const voi
                                void *positions, void *log, void *step, void *scratch, int rows, int vocab,
                                int hidden, float eps, int log_stride, int sm_count, void *stream);
 
+/*
+ * Mixture-of-experts routing of `rows` tokens in one launch: residual += delta (delta may be
+ * NULL), x = rmsnorm(residual) * norm_weight (as sageb200_glue_add_rmsnorm), router logits =
+ * fp16(x . router[experts][hidden]^T), softmax over all experts, the top_k experts per token
+ * (lowest index on ties) as ids int32 [rows][top_k] with renormalised weights float
+ * [rows][top_k] - the routing of Hugging Face Qwen3-MoE.  experts <= 256, top_k <= 32.
+ */
+int sageb200_glue_moe_route(void *residual, const void *delta, const void *norm_weight, const void *router,
+                            void *x, void *ids, void *weights, int rows, int hidden, int experts, int top_k,
+                            float eps, void *stream);
+
+/* out[rows][hidden] = fp16(sum_s weights[row][s] * slot_outputs[row*top_k + s][:]) (FP32 sum). */
+int sageb200_glue_moe_mix(const void *slot_outputs, const void *weights, void *out, int rows, int hidden,
+                          int top_k, void *stream);
+
 #ifdef __cplusplus
 }
 #endif

@@ -55,6 +55,8 @@ EXPORTED_DECODE = (
     "sageb200_glue_prefill_attention",
     "sageb200_glue_lm_head_step_scratch_bytes",
     "sageb200_glue_lm_head_step",
+    "sageb200_glue_moe_route",
+    "sageb200_glue_moe_mix",
     "sageb200_glue_swiglu",
     "sageb200_glue_lm_head",
     "sageb200_glue_argmax_advance",
@@ -186,6 +188,10 @@ def load() -> ctypes.CDLL:
     lib.sageb200_glue_prefill_qk_norm_rope_cache.argtypes = [vp] * 10 + [ci] * 6 + [ctypes.c_float, vp]
     lib.sageb200_glue_prefill_attention.restype = ci
     lib.sageb200_glue_prefill_attention.argtypes = [vp] * 5 + [ci] * 6 + [vp]
+    lib.sageb200_glue_moe_route.restype = ci
+    lib.sageb200_glue_moe_route.argtypes = [vp] * 7 + [ci] * 4 + [ctypes.c_float, vp]
+    lib.sageb200_glue_moe_mix.restype = ci
+    lib.sageb200_glue_moe_mix.argtypes = [vp] * 3 + [ci] * 3 + [vp]
     lib.sageb200_glue_lm_head_step_scratch_bytes.restype = sz
     lib.sageb200_glue_lm_head_step_scratch_bytes.argtypes = [ci, ci]
     lib.sageb200_glue_lm_head_step.restype = ci

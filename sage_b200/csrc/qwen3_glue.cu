@@ -751,6 +751,138 @@ __global__ void __launch_bounds__(kHeadWarps * 32)
   }
 }
 
+// Mixture-of-experts routing for one token per CTA, in one launch: residual add + RMSNorm (the
+// arithmetic and summation order of add_rmsnorm_kernel, run by the CTA's first 256 threads),
+// the FP16 router (logit = fp16(FP32 dot), one warp per four experts at a time), softmax over
+// all experts, top-k (lowest index on ties) and renormalised weights - Qwen3-MoE's routing.
+constexpr int kRouteThreads = 1024;
+constexpr int kMaxExperts = 256;
+
+__global__ void __launch_bounds__(kRouteThreads)
+    moe_route_kernel(__half *__restrict__ residual, const __half *__restrict__ delta,
+                     const __half *__restrict__ norm_weight, const __half *__restrict__ router,
+                     __half *__restrict__ x, int *__restrict__ ids, float *__restrict__ weights, int hidden,
+                     int experts, int top_k, float eps) {
+  sageb200::pdl_launch_dependents();
+  sageb200::pdl_wait();
+
+  extern __shared__ __half row_shared[];
+  __shared__ float scratch[32];
+  __shared__ float logits[kMaxExperts];
+  const int m = blockIdx.x, tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
+  __half *r = residual + static_cast<size_t>(m) * hidden;
+  const __half *d = delta ? delta + static_cast<size_t>(m) * hidden : nullptr;
+  float square = 0.0f;
+  if (tid < kNormThreads) {
+    for (int i = tid; i < hidden; i += kNormThreads) {
+      __half v = r[i];
+      if (d) {
+        v = __hadd(v, d[i]);
+        r[i] = v;
+      }
+      row_shared[i] = v;
+      const float f = __half2float(v);
+      square += f * f;
+    }
+    square = warp_sum(square);
+    if (lane == 0) scratch[warp] = square;
+  }
+  __syncthreads();
+  float total = 0.0f;
+  for (int w = 0; w < kNormThreads / 32; ++w) total += scratch[w];
+  const float scale = rsqrtf(total / hidden + eps);
+  __syncthreads();
+  for (int i = tid; i < hidden; i += kRouteThreads) {
+    const __half normed = __float2half_rn(__half2float(row_shared[i]) * scale);
+    const __half value = __hmul(norm_weight[i], normed);
+    row_shared[i] = value;
+    x[static_cast<size_t>(m) * hidden + i] = value;
+  }
+  __syncthreads();
+  const int pieces = hidden / 8;
+  for (int e = warp; e < experts; e += kRouteThreads / 32) {
+    const uint4 *row = reinterpret_cast<const uint4 *>(router + static_cast<size_t>(e) * hidden);
+    float sum = 0.0f;
+    for (int i = lane; i < pieces; i += 32) {
+      const uint4 w = __ldg(row + i);
+      const uint4 a = reinterpret_cast<const uint4 *>(row_shared)[i];
+      const __half2 *wh = reinterpret_cast<const __half2 *>(&w);
+      const __half2 *ah = reinterpret_cast<const __half2 *>(&a);
+#pragma unroll
+      for (int c = 0; c < 4; ++c) {
+        const float2 wf = __half22float2(wh[c]), af = __half22float2(ah[c]);
+        sum = fmaf(wf.x, af.x, sum);
+        sum = fmaf(wf.y, af.y, sum);
+      }
+    }
+    sum = warp_sum(sum);
+    if (lane == 0) logits[e] = __half2float(__float2half_rn(sum));
+  }
+  __syncthreads();
+  if (warp != 0) return;
+  // warp 0: lane holds experts lane, lane + 32, ...
+  constexpr int kPerLane = kMaxExperts / 32;
+  float mine[kPerLane];
+  float top = -INFINITY;
+#pragma unroll
+  for (int j = 0; j < kPerLane; ++j) {
+    const int e = lane + 32 * j;
+    mine[j] = e < experts ? logits[e] : -INFINITY;
+    top = fmaxf(top, mine[j]);
+  }
+  top = warp_max(top);
+  float chosen_sum = 0.0f;
+  float chosen_weight = 0.0f;  // lane s keeps the s-th choice
+  int chosen_id = 0;
+  for (int s = 0; s < top_k; ++s) {
+    float best = -INFINITY;
+    int best_id = 0x7fffffff;
+#pragma unroll
+    for (int j = 0; j < kPerLane; ++j) {
+      const int e = lane + 32 * j;
+      if (mine[j] > best || (mine[j] == best && e < best_id && mine[j] != -INFINITY)) {
+        best = mine[j];
+        best_id = e;
+      }
+    }
+    for (int o = 16; o; o >>= 1) {
+      const float other = __shfl_xor_sync(0xffffffffu, best, o);
+      const int other_id = __shfl_xor_sync(0xffffffffu, best_id, o);
+      if (other > best || (other == best && other_id < best_id)) {
+        best = other;
+        best_id = other_id;
+      }
+    }
+    const float weight = __expf(best - top);
+    chosen_sum += weight;
+    if (lane == (s & 31)) {
+      chosen_weight = weight;
+      chosen_id = best_id;
+    }
+#pragma unroll
+    for (int j = 0; j < kPerLane; ++j)
+      if (lane + 32 * j == best_id) mine[j] = -INFINITY;
+  }
+  if (lane < top_k) {
+    ids[m * top_k + lane] = chosen_id;
+    weights[m * top_k + lane] = chosen_weight / chosen_sum;
+  }
+}
+
+// out[m][:] = fp16(sum over the token's slots of weight * expert output), FP32 sum in slot order.
+__global__ void moe_mix_kernel(const __half *__restrict__ slot_outputs, const float *__restrict__ weights,
+                               __half *__restrict__ out, int hidden, int top_k) {
+  sageb200::pdl_launch_dependents();
+  sageb200::pdl_wait();
+  const int m = blockIdx.y;
+  const int i = blockIdx.x * blockDim.x + threadIdx.x;
+  if (i >= hidden) return;
+  float sum = 0.0f;
+  for (int s = 0; s < top_k; ++s)
+    sum += weights[m * top_k + s] * __half2float(slot_outputs[(static_cast<size_t>(m) * top_k + s) * hidden + i]);
+  out[static_cast<size_t>(m) * hidden + i] = __float2half_rn(sum);
+}
+
 // next[m] = argmax(logits[m]), lowest index on ties; also appends the token to the output
 // log at column step[0] and advances the sequence's position.
 __global__ void __launch_bounds__(1024)
@@ -1025,6 +1157,30 @@ int sageb200_glue_lm_head_step(const void *head, const void *residual, const voi
       static_cast<long long *>(log), static_cast<int *>(step),
       reinterpret_cast<float2 *>(static_cast<char *>(scratch) + 256), static_cast<unsigned *>(scratch), vocab,
       hidden, rows, eps, log_stride);
+  return launch_status();
+}
+
+int sageb200_glue_moe_route(void *residual, const void *delta, const void *norm_weight, const void *router,
+                            void *x, void *ids, void *weights, int rows, int hidden, int experts, int top_k,
+                            float eps, void *stream) {
+  if (rows < 1 || hidden % 8 || hidden > 24576 || experts < 1 || experts > kMaxExperts || top_k < 1 ||
+      top_k > 32 || top_k > experts)
+    return -1;
+  const size_t shared = static_cast<size_t>(hidden) * sizeof(__half);
+  sageb200::launch_dependent<2>(
+      moe_route_kernel, dim3(rows), dim3(kRouteThreads), shared, static_cast<cudaStream_t>(stream),
+      static_cast<__half *>(residual), static_cast<const __half *>(delta), static_cast<const __half *>(norm_weight),
+      static_cast<const __half *>(router), static_cast<__half *>(x), static_cast<int *>(ids),
+      static_cast<float *>(weights), hidden, experts, top_k, eps);
+  return launch_status();
+}
+
+int sageb200_glue_moe_mix(const void *slot_outputs, const void *weights, void *out, int rows, int hidden,
+                          int top_k, void *stream) {
+  if (rows < 1 || hidden < 1 || top_k < 1) return -1;
+  sageb200::launch_dependent<2>(moe_mix_kernel, dim3((hidden + 255) / 256, rows), dim3(256), 0,
+                                static_cast<cudaStream_t>(stream), static_cast<const __half *>(slot_outputs),
+                                static_cast<const float *>(weights), static_cast<__half *>(out), hidden, top_k);
   return launch_status();
 }
 

@@ -107,7 +107,9 @@ __global__ void __launch_bounds__(512, 1) sage_skinny_kernel(const __grid_consta
   SkinnyProblem p = params.problem[pi];
   if (p.expert_ids) {
     // routed expert: pick this slot's expert out of the stack; an expert that lives on
-    // another rank leaves y as the caller zeroed it
+    // another rank leaves y as the caller zeroed it.  The ids may come from the kernel just
+    // before this one, so they are read only after the wait for it.
+    pdl_wait();
     const int expert = __ldg(p.expert_ids + p.expert_slot) - p.expert_first;
     if (expert < 0 || expert >= p.expert_count) return;
     p.codes += expert * p.codes_stride;

@@ -87,27 +87,36 @@ class SAGEExperts(nn.Module):
             workspace.data_ptr() if workspace is not None else None,
             workspace.numel() if workspace is not None else 0, stream))
 
-    def forward(self, x: torch.Tensor, expert_ids: torch.Tensor, weights: torch.Tensor) -> torch.Tensor:
+    def forward(self, x: torch.Tensor, expert_ids: torch.Tensor, weights: torch.Tensor, *,
+                foreign_experts: bool = True) -> torch.Tensor:
         """x FP16 [tokens, hidden]; expert_ids int32 [tokens, top_k]; weights [tokens, top_k].
-        Returns this rank's experts' share of the MoE output, FP16 [tokens, hidden]."""
+        Returns this rank's experts' share of the MoE output, FP16 [tokens, hidden].
+        `foreign_experts=False` promises that every id belongs to this rank (no expert
+        parallelism), which saves zero-filling the slot buffers."""
         tokens, top_k = expert_ids.shape
         slots = tokens * top_k
         ids = expert_ids.reshape(-1).contiguous()
+        lib = _lib.load()
+        buffer = torch.zeros if foreign_experts else torch.empty
         with torch.cuda.device(x.device):
+            stream = torch.cuda.current_stream(x.device).cuda_stream
             rows = x.contiguous() if tokens == 1 else x.repeat_interleave(top_k, dim=0).contiguous()
-            gate = torch.zeros(slots, self.intermediate, dtype=torch.float16, device=x.device)
-            up = torch.zeros_like(gate)
+            gate = buffer(slots, self.intermediate, dtype=torch.float16, device=x.device)
+            up = buffer(slots, self.intermediate, dtype=torch.float16, device=x.device)
             self._run(rows, 0 if tokens == 1 else self.hidden,
                       [self._stack("gate", self.intermediate, self.hidden),
                        self._stack("up", self.intermediate, self.hidden)], [gate, up], ids, slots)
             act = torch.empty_like(gate)
-            status = _lib.load().sageb200_glue_swiglu(
-                gate.data_ptr(), up.data_ptr(), act.data_ptr(), gate.numel(),
-                torch.cuda.current_stream(x.device).cuda_stream)
+            status = lib.sageb200_glue_swiglu(gate.data_ptr(), up.data_ptr(), act.data_ptr(), gate.numel(), stream)
             if status:
                 raise RuntimeError(f"sage_b200: swiglu failed with status {status}")
-            down = torch.zeros(slots, self.hidden, dtype=torch.float16, device=x.device)
+            down = buffer(slots, self.hidden, dtype=torch.float16, device=x.device)
             self._run(act, self.intermediate, [self._stack("down", self.hidden, self.intermediate)],
                       [down], ids, slots)
-            mixed = (down.view(tokens, top_k, self.hidden).float() * weights[..., None].float()).sum(dim=1)
-        return mixed.to(torch.float16)
+            mixed = torch.empty(tokens, self.hidden, dtype=torch.float16, device=x.device)
+            weights = weights.to(torch.float32).contiguous()
+            status = lib.sageb200_glue_moe_mix(down.data_ptr(), weights.data_ptr(), mixed.data_ptr(), tokens,
+                                               self.hidden, top_k, stream)
+            if status:
+                raise RuntimeError(f"sage_b200: moe_mix failed with status {status}")
+        return mixed

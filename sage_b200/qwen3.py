@@ -216,6 +216,9 @@ class PackedQwen3:
         self.step_splits = 8  # CTAs per cluster in the single-launch attention
         scratch = self.lib.sageb200_glue_lm_head_step_scratch_bytes(batch, self.sm_count)
         self.head_scratch = torch.zeros(scratch // 4, dtype=torch.float32, device=self.device)
+        if c.experts:
+            self.route_ids = torch.zeros(batch, c.top_k, dtype=torch.int32, device=self.device)
+            self.route_weights = torch.zeros(batch, c.top_k, dtype=torch.float32, device=self.device)
         self.graph = None
         self.graph_no_head = None
 
@@ -298,9 +301,15 @@ class PackedQwen3:
         """Mixture-of-experts MLP: norm, FP16 router, top-k routing on the GPU, routed packed
         experts (this rank's block), all-reduce over the expert-parallel group."""
         c, lib, b = self.config, self.lib, self.batch
-        self._check(lib.sageb200_glue_add_rmsnorm(_vp(self.h), _vp(o), _vp(layer["post_norm"]), _vp(self.x), b,
-                                                  c.hidden, c.eps, self._stream()), "add_rmsnorm")
-        ids, weights = route(torch.nn.functional.linear(self.x, layer["router"]), c.top_k)
+        if self.fuse_glue:  # norm + router + top-k in one launch (both the packed and the dense model)
+            ids, weights = self.route_ids, self.route_weights
+            self._check(lib.sageb200_glue_moe_route(
+                _vp(self.h), _vp(o), _vp(layer["post_norm"]), _vp(layer["router"]), _vp(self.x), _vp(ids),
+                _vp(weights), b, c.hidden, c.experts, c.top_k, c.eps, self._stream()), "moe_route")
+        else:
+            self._check(lib.sageb200_glue_add_rmsnorm(_vp(self.h), _vp(o), _vp(layer["post_norm"]), _vp(self.x), b,
+                                                      c.hidden, c.eps, self._stream()), "add_rmsnorm")
+            ids, weights = route(torch.nn.functional.linear(self.x, layer["router"]), c.top_k)
         if self.dense:
             gate_w, up_w, down_w = layer["expert_weights"]
             local = ids.long() - layer["first_expert"]
@@ -313,7 +322,7 @@ class PackedQwen3:
             d = torch.matmul(down_w[index], act[..., None]).squeeze(-1)          # [b, top_k, hidden]
             out = (d.float() * (weights * mine)[..., None]).sum(dim=1).half()
         else:
-            out = layer["experts"](self.x, ids, weights)
+            out = layer["experts"](self.x, ids, weights, foreign_experts=self.ep_world > 1)
         if self.ep_world > 1:
             import torch.distributed as dist
 

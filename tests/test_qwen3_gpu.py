@@ -173,6 +173,52 @@ def test_report_rows_on_a_small_model():
     assert len(result["samples"]["decode"]) == 3
 
 
+@pytest.mark.parametrize("rows,experts,top_k", [(1, 128, 8), (3, 8, 2), (16, 60, 4)])
+def test_single_launch_routing_and_mixing(rows, experts, top_k):
+    """norm + router + softmax/top-k in one launch against the stand-alone norm kernel and the
+    torch routing arithmetic; the weighted mix against its torch formula."""
+    from sage_b200 import _lib
+    from sage_b200.experts import route
+
+    lib = _lib.load()
+    device = torch.device("cuda:0")
+    gen = torch.Generator().manual_seed(rows * 1000 + experts)
+    hidden = 512
+    half = dict(dtype=torch.float16, device=device)
+    rand = lambda *shape: torch.randn(*shape, generator=gen).to(**half)  # noqa: E731
+    residual, delta, weight = rand(rows, hidden), rand(rows, hidden), 1 + 0.1 * rand(hidden)
+    router = (0.2 * torch.randn(experts, hidden, generator=gen)).to(**half)
+    stream = ctypes.c_void_p(torch.cuda.current_stream(device).cuda_stream)
+    want_residual, want_x = residual.clone(), torch.zeros(rows, hidden, **half)
+    assert lib.sageb200_glue_add_rmsnorm(_vp(want_residual), _vp(delta), _vp(weight), _vp(want_x), rows, hidden,
+                                         1e-6, stream) == 0
+    got_residual, x = residual.clone(), torch.zeros(rows, hidden, **half)
+    ids = torch.zeros(rows, top_k, dtype=torch.int32, device=device)
+    weights = torch.zeros(rows, top_k, dtype=torch.float32, device=device)
+    assert lib.sageb200_glue_moe_route(_vp(got_residual), _vp(delta), _vp(weight), _vp(router), _vp(x), _vp(ids),
+                                       _vp(weights), rows, hidden, experts, top_k, 1e-6, stream) == 0
+    torch.cuda.synchronize()
+    assert torch.equal(got_residual, want_residual) and torch.equal(x, want_x)
+    logits = (x.float() @ router.float().T).half().float()  # the FP16 router's output
+    want_ids, want_weights = route(logits, top_k)
+    picked = logits.gather(1, ids.long())
+    threshold = logits.topk(top_k, dim=-1).values[:, -1:]
+    assert (picked >= threshold - 2e-3 * threshold.abs() - 1e-6).all()        # only near ties may differ
+    assert all(len(set(row)) == top_k for row in ids.tolist())                  # k distinct experts
+    assert (picked[:, :-1] >= picked[:, 1:] - 2e-3 * picked[:, 1:].abs() - 1e-6).all()  # best first
+    renormalised = torch.softmax(picked, dim=-1)  # softmax over the chosen = softmax over all, renormalised
+    # a logit may sit one FP16 step from the recomputed one: weights agree to that step
+    assert torch.allclose(weights, renormalised, rtol=5e-3, atol=1e-5)
+    same = (ids == want_ids).all(dim=-1)
+    assert torch.allclose(weights[same], want_weights[same], rtol=5e-3, atol=1e-5)
+    assert torch.allclose(weights.sum(dim=-1), torch.ones(rows, device=device), atol=1e-5)
+    slots = rand(rows * top_k, hidden)
+    mixed = torch.zeros(rows, hidden, **half)
+    assert lib.sageb200_glue_moe_mix(_vp(slots), _vp(weights), _vp(mixed), rows, hidden, top_k, stream) == 0
+    want = (slots.view(rows, top_k, hidden).float() * weights[..., None]).sum(dim=1)
+    assert torch.allclose(mixed.float(), want, rtol=2e-3, atol=1e-3)
+
+
 def test_routed_experts_match_per_expert_linears():
     """`SAGEExperts` (device-side expert selection, stacked buffers) against one `SAGELinear`
     per routed expert, for one token and for several; and the expert-parallel split: two
