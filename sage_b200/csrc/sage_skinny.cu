@@ -81,7 +81,12 @@ __device__ __forceinline__ int split_owner(int u, int q, int r) {
 // Dynamic shared memory: [x | codes | radii | grid | warp partials | x in original order].
 // kLowBits: some problem of the launch has 64 or 128 codebook entries (codes carry low
 // radius bits); a launch whose codebooks all have 256 entries uses the shorter variant.
-template <int NB, bool kLowBits>
+// kPath specialises the once-per-launch code for the decode graph's launches (single activation
+// row, permutation present and 16-byte aligned, K not sliced, no expert indirection, the row fits
+// the linear staging buffer): 1 = fused residual add + RMSNorm, 2 = fused SwiGLU, 3 = plain
+// 16-byte aligned x; 0 = every case.  The special paths are the generic code with those facts
+// known at compile time, so the cold instruction stream after the wait is short and contiguous.
+template <int NB, bool kLowBits, int kPath>
 __global__ void __launch_bounds__(512, 1) sage_skinny_kernel(const __grid_constant__ SkinnyParams params) {
   extern __shared__ __align__(128) unsigned char shared[];
   __shared__ __align__(128) unsigned char book_shared[kBookBytes];
@@ -105,6 +110,11 @@ __global__ void __launch_bounds__(512, 1) sage_skinny_kernel(const __grid_consta
       ++pi;
   }
   SkinnyProblem p = params.problem[pi];
+  if constexpr (kPath != 0) {
+    p.rows = 1;
+    p.slices = 1;
+    p.expert_ids = nullptr;
+  }
   if (p.expert_ids) {
     // routed expert: pick this slot's expert out of the stack; an expert that lives on
     // another rank leaves y as the caller zeroed it.  The ids may come from the kernel just
@@ -253,18 +263,19 @@ __global__ void __launch_bounds__(512, 1) sage_skinny_kernel(const __grid_consta
   //     c. otherwise: gather from global memory, four channels per item
   const int span = group_count * 128;
   const int row_stride = span + 32;  // halves
-  const bool aligned_x = (reinterpret_cast<uintptr_t>(p.x) & 15) == 0;
-  const bool perm_aligned = (reinterpret_cast<uintptr_t>(p.perm) & 15) == 0;
-  const bool linear_gather = p.perm != nullptr && perm_aligned &&
-                             static_cast<size_t>(p.rows) * p.k * 2 <= static_cast<size_t>(params.lin_bytes);
+  const bool aligned_x = kPath != 0 || (reinterpret_cast<uintptr_t>(p.x) & 15) == 0;
+  const bool perm_aligned = kPath != 0 || (reinterpret_cast<uintptr_t>(p.perm) & 15) == 0;
+  const bool linear_gather =
+      kPath != 0 || (p.perm != nullptr && perm_aligned &&
+                     static_cast<size_t>(p.rows) * p.k * 2 <= static_cast<size_t>(params.lin_bytes));
   // Fused producer (single activation row only): the row is computed here from the
   // producer's inputs instead of being read from p.x:
   //   1  x = weight * fp16((a + b) * rsqrt(mean((a + b)^2) + eps)),  a + b also stored as the
   //      new residual by the launch's first CTA                      (residual add + RMSNorm)
   //   2  x = fp16(silu(a)) * b                                        (SwiGLU)
-  const int fused = params.act_kind;
+  const int fused = kPath == 0 ? params.act_kind : (kPath == 3 ? 0 : kPath);
   const bool gather_from_linear = linear_gather || fused != 0;
-  const bool direct_copy = p.perm == nullptr && aligned_x && fused == 0;
+  const bool direct_copy = kPath == 0 && p.perm == nullptr && aligned_x && fused == 0;
   constexpr int kItemBatch = 4;  // permutation items (4 channels each) held in registers
   constexpr int kCopyBatch = 4;  // 16-byte activation pieces held in registers
   int4 held[kItemBatch];
@@ -285,7 +296,7 @@ __global__ void __launch_bounds__(512, 1) sage_skinny_kernel(const __grid_consta
   }
   auto load_item = [&](int q) {  // source channels of quantised channels 4q .. 4q+3
     const int channel = group_begin * 128 + 4 * q;
-    if (p.perm == nullptr) return make_int4(channel, channel + 1, channel + 2, channel + 3);
+    if (kPath == 0 && p.perm == nullptr) return make_int4(channel, channel + 1, channel + 2, channel + 3);
     if (perm_aligned) return __ldg(reinterpret_cast<const int4 *>(p.perm) + (channel >> 2));
     return make_int4(__ldg(p.perm + channel), __ldg(p.perm + channel + 1), __ldg(p.perm + channel + 2),
                      __ldg(p.perm + channel + 3));
@@ -639,9 +650,9 @@ __global__ void __launch_bounds__(512, 1) sage_skinny_kernel(const __grid_consta
 #undef SAGE_STAMP
 }
 
-template <int NB, bool kLowBits>
+template <int NB, bool kLowBits, int kPath = 0>
 cudaError_t configure_variant() {
-  return cudaFuncSetAttribute(sage_skinny_kernel<NB, kLowBits>,
+  return cudaFuncSetAttribute(sage_skinny_kernel<NB, kLowBits, kPath>,
                               cudaFuncAttributeMaxDynamicSharedMemorySize, kMaxDynamicShared);
 }
 
@@ -772,7 +783,22 @@ cudaError_t configure_skinny() {
   if (status == cudaSuccess) status = configure_variant<1, true>();
   if (status == cudaSuccess) status = configure_variant<2, false>();
   if (status == cudaSuccess) status = configure_variant<2, true>();
+  if (status == cudaSuccess) status = configure_variant<1, false, 1>();
+  if (status == cudaSuccess) status = configure_variant<1, true, 1>();
+  if (status == cudaSuccess) status = configure_variant<1, false, 2>();
+  if (status == cudaSuccess) status = configure_variant<1, true, 2>();
+  if (status == cudaSuccess) status = configure_variant<1, false, 3>();
+  if (status == cudaSuccess) status = configure_variant<1, true, 3>();
   return status;
+}
+
+// debug: environment SAGEB200_PATHS=0 keeps every launch on the generic kernel (A/B timing)
+int skinny_path_limit() {
+  static const int limit = [] {
+    const char *text = getenv("SAGEB200_PATHS");
+    return text ? atoi(text) : -1;
+  }();
+  return limit;
 }
 
 cudaError_t launch_skinny(const SkinnyParams &params, int warps, int column_blocks, int total_ctas,
@@ -784,13 +810,29 @@ cudaError_t launch_skinny(const SkinnyParams &params, int warps, int column_bloc
   const int threads = warps * 32;
   bool low_bits = false;
   for (int i = 0; i < params.count; ++i) low_bits = low_bits || params.problem[i].dbits != 8;
-  if (column_blocks == 1) {
-    if (low_bits) return launch_dependent(sage_skinny_kernel<1, true>, total_ctas, threads, shared_bytes, stream, params);
-    return launch_dependent(sage_skinny_kernel<1, false>, total_ctas, threads, shared_bytes, stream, params);
-  } else {
-    if (low_bits) return launch_dependent(sage_skinny_kernel<2, true>, total_ctas, threads, shared_bytes, stream, params);
-    return launch_dependent(sage_skinny_kernel<2, false>, total_ctas, threads, shared_bytes, stream, params);
+  // the decode graph's launches take a specialised instruction stream (see the kernel's comment)
+  int path = column_blocks == 1 ? (params.act_kind == 0 ? 3 : params.act_kind) : 0;
+  for (int i = 0; i < params.count && path != 0; ++i) {
+    const SkinnyProblem &q = params.problem[i];
+    const bool fits = static_cast<size_t>(q.k) * 2 <= static_cast<size_t>(params.lin_bytes);
+    if (q.rows != 1 || q.slices != 1 || q.expert_ids != nullptr || q.perm == nullptr ||
+        (reinterpret_cast<uintptr_t>(q.perm) & 15) != 0 || !fits ||
+        (path == 3 && (reinterpret_cast<uintptr_t>(q.x) & 15) != 0))
+      path = 0;
   }
+  if (skinny_path_limit() >= 0 && path > skinny_path_limit()) path = 0;
+#define SAGE_LAUNCH(NB_, LOW_, PATH_) \
+  launch_dependent(sage_skinny_kernel<NB_, LOW_, PATH_>, total_ctas, threads, shared_bytes, stream, params)
+  if (column_blocks == 1) {
+    switch (path) {
+      case 1: return low_bits ? SAGE_LAUNCH(1, true, 1) : SAGE_LAUNCH(1, false, 1);
+      case 2: return low_bits ? SAGE_LAUNCH(1, true, 2) : SAGE_LAUNCH(1, false, 2);
+      case 3: return low_bits ? SAGE_LAUNCH(1, true, 3) : SAGE_LAUNCH(1, false, 3);
+      default: return low_bits ? SAGE_LAUNCH(1, true, 0) : SAGE_LAUNCH(1, false, 0);
+    }
+  }
+  return low_bits ? SAGE_LAUNCH(2, true, 0) : SAGE_LAUNCH(2, false, 0);
+#undef SAGE_LAUNCH
   return cudaGetLastError();
 }
 

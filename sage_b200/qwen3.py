@@ -104,8 +104,10 @@ class PackedQwen3:
         ranks' expert outputs are summed with an all-reduce."""
         if linear not in ("sage", "dense"):
             raise ValueError("linear must be 'sage' or 'dense'")
-        if batch < 1 or batch > 16:
-            raise ValueError("batch must be 1..16")
+        if batch < 1 or batch > 64:
+            raise ValueError("batch must be 1..64")
+        if batch > 16 and config.experts:
+            raise ValueError("mixture-of-experts configs run with batch 1..16")
         self.config, self.device, self.batch, self.max_seq = config, torch.device(device), batch, max_seq
         self.dense = linear == "dense"
         self.tp_group = tp_group
@@ -234,6 +236,8 @@ class PackedQwen3:
     def _linears(self, layer, names, x, activation=None):
         if self.dense:
             return [torch.nn.functional.linear(x, layer[name].weight) for name in names]
+        if self.batch > 16:  # beyond a grouped launch: one call per linear (decode kernel in two
+            return self._rows_linears(layer, names, x)  # passes up to 32 rows, tensor-core GEMM above)
         return sage_grouped([layer[name].problem(x) for name in names], [layer[name].n for name in names],
                             activation)
 
@@ -243,7 +247,7 @@ class PackedQwen3:
         and the new residual goes to the other of two residual buffers).  Dense oracle: the
         stand-alone norm kernel, then torch matmuls."""
         c, lib, b = self.config, self.lib, self.batch
-        if self.dense or not self.fuse:
+        if self.dense or not self.fuse or b > 16:
             self._check(lib.sageb200_glue_add_rmsnorm(_vp(self.h), _vp(delta), _vp(weight), _vp(self.x), b,
                                                       c.hidden, c.eps, self._stream()), "add_rmsnorm")
             return self._linears(layer, names, self.x)
@@ -289,7 +293,7 @@ class PackedQwen3:
         if c.experts:
             return self._moe(layer, o)
         gate, up = self._norm_linears(layer, ("gate", "up"), o, layer["post_norm"])
-        if self.dense or not self.fuse:
+        if self.dense or not self.fuse or b > 16:
             self._check(lib.sageb200_glue_swiglu(_vp(gate), _vp(up), _vp(self.act), gate.numel(), s), "swiglu")
             (down,) = self._linears(layer, ("down",), self.act)
         else:  # SwiGLU inside the down projection's activation staging
@@ -346,21 +350,30 @@ class PackedQwen3:
         if not head:
             self.positions.add_(1)
             return
-        if self.fuse_glue and not self.dense and self.tp_world == 1:
+        self._tail(self.h, delta)
+
+    def _tail(self, residual, delta):
+        """Final norm of residual + delta, lm_head, greedy argmax, token log and position advance."""
+        c, lib, b = self.config, self.lib, self.batch
+        s = self._stream()
+        if self.fuse_glue and not self.dense and self.tp_world == 1 and b <= 16:
             self._check(lib.sageb200_glue_lm_head_step(
-                _vp(self.lm_head), _vp(self.h), _vp(delta), _vp(self.final_norm), _vp(self.x), _vp(self.logits),
+                _vp(self.lm_head), _vp(residual), _vp(delta), _vp(self.final_norm), _vp(self.x), _vp(self.logits),
                 _vp(self.tokens), _vp(self.positions), _vp(self.log), _vp(self.step_counter),
                 _vp(self.head_scratch), b, c.vocab, c.hidden, c.eps, self.max_new, self.sm_count, s),
                 "lm_head_step")
             return
-        self._check(lib.sageb200_glue_add_rmsnorm(_vp(self.h), _vp(delta), _vp(self.final_norm),
+        self._check(lib.sageb200_glue_add_rmsnorm(_vp(residual), _vp(delta), _vp(self.final_norm),
                                                   _vp(self.x), b, c.hidden, c.eps, s), "final norm")
         local_vocab = c.vocab // self.tp_world
         if self.dense:
             torch.matmul(self.x, self.lm_head.T, out=self.local_logits)
         else:
-            self._check(lib.sageb200_glue_lm_head(_vp(self.lm_head), _vp(self.x), _vp(self.local_logits), b,
-                                                  local_vocab, c.hidden, self.sm_count, s), "lm_head")
+            for first in range(0, b, 16):  # the head kernel takes up to 16 rows at a time
+                rows = min(16, b - first)
+                self._check(lib.sageb200_glue_lm_head(_vp(self.lm_head), _vp(self.x[first:]),
+                                                      _vp(self.local_logits[first:]), rows, local_vocab, c.hidden,
+                                                      self.sm_count, s), "lm_head")
         if self.tp_world > 1:
             import torch.distributed as dist
 
@@ -468,23 +481,7 @@ class PackedQwen3:
             last = torch.arange(b, device=self.device) * length + (length - 1)
             h_last, delta_last = h[last].contiguous(), delta[last].contiguous()
             self.positions.add_(length - 1)
-            if self.fuse_glue and not self.dense:
-                self._check(lib.sageb200_glue_lm_head_step(
-                    _vp(self.lm_head), _vp(h_last), _vp(delta_last), _vp(self.final_norm), _vp(self.x),
-                    _vp(self.logits), _vp(self.tokens), _vp(self.positions), _vp(self.log), _vp(self.step_counter),
-                    _vp(self.head_scratch), b, c.vocab, c.hidden, c.eps, self.max_new, self.sm_count, s),
-                    "lm_head_step")
-                return
-            self._check(lib.sageb200_glue_add_rmsnorm(_vp(h_last), _vp(delta_last), _vp(self.final_norm),
-                                                      _vp(self.x), b, c.hidden, c.eps, s), "final norm")
-            if self.dense:
-                torch.matmul(self.x, self.lm_head.T, out=self.logits)
-            else:
-                self._check(lib.sageb200_glue_lm_head(_vp(self.lm_head), _vp(self.x), _vp(self.logits), b, c.vocab,
-                                                      c.hidden, self.sm_count, s), "lm_head")
-            self._check(lib.sageb200_glue_argmax_advance(_vp(self.logits), _vp(self.tokens), _vp(self.positions),
-                                                         _vp(self.log), _vp(self.step_counter), b, c.vocab,
-                                                         self.max_new, s), "argmax")
+            self._tail(h_last, delta_last)
 
     def generate(self, prompt: torch.Tensor, new_tokens: int) -> torch.Tensor:
         """Greedy generation; returns [batch, new_tokens] token ids (device tensor)."""
