@@ -12,6 +12,7 @@
 #include <cuda_fp16.h>
 #include <cuda_runtime.h>
 #include <stdint.h>
+#include <stdlib.h>
 
 #include <cooperative_groups.h>
 
@@ -295,7 +296,10 @@ __device__ __forceinline__ void norm_rope_head(const __half *source, const __hal
   out_hi = __hadd2(__hmul2(nh, c), __hmul2(nl, s));
 }
 
-constexpr int kStepHeads = 4;  // query heads per CTA (of one kv head)
+// kStepHeads query heads (of one kv head) per CTA: 4, 2 or 1.  kExact: the group size is a
+// multiple of it, so no CTA has fewer (the guards disappear).  kPrompt: prompt rows (see below).
+// The variants only remove code the launch cannot reach: this kernel's cost is mostly the
+// fetch of instructions that run once.
 
 __device__ __forceinline__ void unpack16(const uint4 &a, const uint4 &b, float out[16]) {
   const __half2 *ha = reinterpret_cast<const __half2 *>(&a);
@@ -310,6 +314,7 @@ __device__ __forceinline__ void unpack16(const uint4 &a, const uint4 &b, float o
   }
 }
 
+template <int kStepHeads, bool kExact, bool kPrompt>
 __global__ void __launch_bounds__(kAttnWarps * 32)
     attention_step_kernel(const __half *__restrict__ q, const __half *__restrict__ k,
                           const __half *__restrict__ v, const __half *__restrict__ q_weight,
@@ -334,13 +339,13 @@ __global__ void __launch_bounds__(kAttnWarps * 32)
   const int group = q_heads / kv_heads;
   const int parts = (group + kStepHeads - 1) / kStepHeads;
   const int kv = blockIdx.y / parts, part = blockIdx.y - kv * parts;
-  const int heads = min(kStepHeads, group - part * kStepHeads);
+  const int heads = kExact ? kStepHeads : min(kStepHeads, group - part * kStepHeads);
   const int first_head = kv * group + part * kStepHeads;
   // rows_per_sequence == 0: a decode step (row = sequence; q and the new k are normalised and
   // rotated here and the new k/v appended).  > 0: prompt rows - that many consecutive rows are
   // the tokens of one sequence at positions[sequence] + token, q is already normalised and
   // rotated and the cache already holds every token's k/v.
-  const bool prompt = rows_per_sequence > 0;
+  constexpr bool prompt = kPrompt;
   const int sequence = prompt ? m / rows_per_sequence : m;
   const int position = positions[sequence] + (prompt ? m - sequence * rows_per_sequence : 0);
   const bool in_range = !prompt && position >= 0 && position < max_seq;  // a full cache takes no new token
@@ -428,7 +433,7 @@ __global__ void __launch_bounds__(kAttnWarps * 32)
     unpack16(v0, v1, vf);
 #pragma unroll
     for (int g = 0; g < kStepHeads; ++g) {
-      if (g >= heads) break;
+      if (!kExact && g >= heads) break;
       float dot = 0.0f;
 #pragma unroll
       for (int i = 0; i < 16; ++i) dot = fmaf(qf[g][i], kf[i], dot);
@@ -454,7 +459,7 @@ __global__ void __launch_bounds__(kAttnWarps * 32)
   // merge the warp's four position streams, then the warps, then (across the cluster) the splits
 #pragma unroll
   for (int g = 0; g < kStepHeads; ++g) {
-    if (g >= heads) break;
+    if (!kExact && g >= heads) break;
     float top = fmaxf(running_max[g], __shfl_xor_sync(0xffffffffu, running_max[g], 8));
     top = fmaxf(top, __shfl_xor_sync(0xffffffffu, top, 16));
     const float f = running_max[g] == -INFINITY ? 0.0f : __expf(running_max[g] - top);
@@ -1020,41 +1025,64 @@ int sageb200_glue_attention_decode(const void *q, const void *k_cache, const voi
   return launch_status();
 }
 
-int sageb200_glue_attention_step(const void *q, const void *k, const void *v, const void *q_weight,
-                                 const void *k_weight, const void *cos_table, const void *sin_table,
-                                 const void *positions, void *k_cache, void *v_cache, void *out, int rows,
-                                 int q_heads, int kv_heads, int head_dim, int max_seq, int splits, float eps,
-                                 void *stream) {
-  if (head_dim != 128 || kv_heads < 1 || q_heads % kv_heads || max_seq < 1 || rows < 1) return -1;
-  if (splits != 1 && splits != 2 && splits != 4 && splits != 8 && splits != 16) return -1;
-  if (splits == 16) {  // beyond the portable cluster size: opt in, and check that one fits at all
-    static int fits = -1;
-    if (fits < 0) {
-      fits = 0;
-      if (cudaFuncSetAttribute(attention_step_kernel, cudaFuncAttributeNonPortableClusterSizeAllowed, 1) ==
-          cudaSuccess) {
-        cudaLaunchConfig_t probe = {};
-        probe.gridDim = dim3(16, 1, 1);
-        probe.blockDim = dim3(kAttnWarps * 32);
-        cudaLaunchAttribute shape[1];
-        shape[0].id = cudaLaunchAttributeClusterDimension;
-        shape[0].val.clusterDim.x = 16;
-        shape[0].val.clusterDim.y = 1;
-        shape[0].val.clusterDim.z = 1;
-        probe.attrs = shape;
-        probe.numAttrs = 1;
-        int clusters = 0;
-        if (cudaOccupancyMaxActiveClusters(&clusters, attention_step_kernel, &probe) == cudaSuccess && clusters > 0)
-          fits = 1;
-      }
-      cudaGetLastError();
-    }
-    if (!fits) return -1;
-  }
+}  // extern "C"
+
+namespace {
+
+using AttentionKernel = void (*)(const __half *, const __half *, const __half *, const __half *, const __half *,
+                                 const __half *, const __half *, const int *, __half *, __half *, __half *, int, int,
+                                 int, float, float, int);
+
+// debug: environment SAGEB200_ATTN_HEADS = 1, 2 or 4 forces the query heads per CTA
+int attention_heads_override() {
+  static const int value = [] {
+    const char *text = getenv("SAGEB200_ATTN_HEADS");
+    return text ? atoi(text) : 0;
+  }();
+  return value;
+}
+
+// Query heads per CTA: four when the group allows (K/V rows are read once per four heads),
+// fewer when that leaves most SMs without a CTA.
+int attention_heads_per_cta(int group, int units_at_four, int sm_count) {
+  const int forced = attention_heads_override();
+  if (forced == 1 || forced == 2 || forced == 4) return forced;
+  if (group % 4 == 0 && units_at_four * 2 > sm_count) return 4;
+  if (group % 2 == 0) return group % 4 == 0 && units_at_four * 4 <= sm_count ? 1 : 2;
+  return group >= 3 ? 4 : 1;
+}
+
+template <bool kPrompt>
+AttentionKernel attention_variant(int heads_per_cta, bool exact) {
+  if (heads_per_cta == 4) return exact ? attention_step_kernel<4, true, kPrompt> : attention_step_kernel<4, false, kPrompt>;
+  if (heads_per_cta == 2) return exact ? attention_step_kernel<2, true, kPrompt> : attention_step_kernel<2, false, kPrompt>;
+  return attention_step_kernel<1, true, kPrompt>;
+}
+
+int launch_attention(bool prompt_rows, const void *q, const void *k, const void *v, const void *q_weight,
+                     const void *k_weight, const void *cos_table, const void *sin_table, const void *positions,
+                     void *k_cache, void *v_cache, void *out, int grid_rows, int q_heads, int kv_heads, int max_seq,
+                     int splits, float eps, int rows_per_sequence, bool dependent, void *stream) {
   const int group = q_heads / kv_heads;
-  const int parts = (group + kStepHeads - 1) / kStepHeads;
+  static int sm_count = 0;
+  if (sm_count == 0) {
+    int device = 0;
+    if (cudaGetDevice(&device) != cudaSuccess ||
+        cudaDeviceGetAttribute(&sm_count, cudaDevAttrMultiProcessorCount, device) != cudaSuccess || sm_count <= 0)
+      sm_count = 148;
+  }
+  const int per_cta = attention_heads_per_cta(group, splits * kv_heads * ((group + 3) / 4) * grid_rows, sm_count);
+  const int parts = (group + per_cta - 1) / per_cta;
+  const bool exact = group % per_cta == 0;
+  AttentionKernel kernel = prompt_rows ? attention_variant<true>(per_cta, exact) : attention_variant<false>(per_cta, exact);
+  if (splits == 16) {  // beyond the portable cluster size: opt in, and check that one fits at all
+    if (cudaFuncSetAttribute(kernel, cudaFuncAttributeNonPortableClusterSizeAllowed, 1) != cudaSuccess) {
+      cudaGetLastError();
+      return -1;
+    }
+  }
   cudaLaunchConfig_t config = {};
-  config.gridDim = dim3(splits, kv_heads * parts, rows);
+  config.gridDim = dim3(splits, kv_heads * parts, grid_rows);
   config.blockDim = dim3(kAttnWarps * 32);
   config.stream = static_cast<cudaStream_t>(stream);
   cudaLaunchAttribute attributes[2];
@@ -1065,16 +1093,37 @@ int sageb200_glue_attention_step(const void *q, const void *k, const void *v, co
   attributes[1].id = cudaLaunchAttributeProgrammaticStreamSerialization;
   attributes[1].val.programmaticStreamSerializationAllowed = 1;
   config.attrs = attributes;
-  config.numAttrs = (sageb200::g_sageb200_pdl & 2) ? 2 : 1;
+  config.numAttrs = dependent ? 2 : 1;
+  if (splits == 16) {
+    int clusters = 0;
+    if (cudaOccupancyMaxActiveClusters(&clusters, kernel, &config) != cudaSuccess || clusters <= 0) {
+      cudaGetLastError();
+      return -1;
+    }
+  }
   __atomic_fetch_add(&sageb200::g_sageb200_glue_launches, 1ull, __ATOMIC_RELAXED);
   const cudaError_t error = cudaLaunchKernelEx(
-      &config, attention_step_kernel, static_cast<const __half *>(q), static_cast<const __half *>(k),
-      static_cast<const __half *>(v), static_cast<const __half *>(q_weight),
-      static_cast<const __half *>(k_weight), static_cast<const __half *>(cos_table),
-      static_cast<const __half *>(sin_table), static_cast<const int *>(positions),
-      static_cast<__half *>(k_cache), static_cast<__half *>(v_cache), static_cast<__half *>(out), q_heads,
-      kv_heads, max_seq, eps, rsqrtf(128.0f), 0);
+      &config, kernel, static_cast<const __half *>(q), static_cast<const __half *>(k),
+      static_cast<const __half *>(v), static_cast<const __half *>(q_weight), static_cast<const __half *>(k_weight),
+      static_cast<const __half *>(cos_table), static_cast<const __half *>(sin_table),
+      static_cast<const int *>(positions), static_cast<__half *>(k_cache), static_cast<__half *>(v_cache),
+      static_cast<__half *>(out), q_heads, kv_heads, max_seq, eps, rsqrtf(128.0f), rows_per_sequence);
   return error == cudaSuccess ? launch_status() : -5;
+}
+
+}  // namespace
+
+extern "C" {
+
+int sageb200_glue_attention_step(const void *q, const void *k, const void *v, const void *q_weight,
+                                 const void *k_weight, const void *cos_table, const void *sin_table,
+                                 const void *positions, void *k_cache, void *v_cache, void *out, int rows,
+                                 int q_heads, int kv_heads, int head_dim, int max_seq, int splits, float eps,
+                                 void *stream) {
+  if (head_dim != 128 || kv_heads < 1 || q_heads % kv_heads || max_seq < 1 || rows < 1) return -1;
+  if (splits != 1 && splits != 2 && splits != 4 && splits != 8 && splits != 16) return -1;
+  return launch_attention(false, q, k, v, q_weight, k_weight, cos_table, sin_table, positions, k_cache, v_cache, out,
+                          rows, q_heads, kv_heads, max_seq, splits, eps, 0, (sageb200::g_sageb200_pdl & 2) != 0, stream);
 }
 
 int sageb200_glue_prefill_attention(const void *q, const void *k_cache, const void *v_cache,
@@ -1083,27 +1132,9 @@ int sageb200_glue_prefill_attention(const void *q, const void *k_cache, const vo
   if (head_dim != 128 || kv_heads < 1 || q_heads % kv_heads || max_seq < 1 || sequences < 1 || tokens < 1 ||
       static_cast<long long>(sequences) * tokens > 65535)
     return -1;
-  const int group = q_heads / kv_heads;
-  const int parts = (group + kStepHeads - 1) / kStepHeads;
-  cudaLaunchConfig_t config = {};
-  config.gridDim = dim3(1, kv_heads * parts, sequences * tokens);  // one CTA per cluster: short contexts
-  config.blockDim = dim3(kAttnWarps * 32);
-  config.stream = static_cast<cudaStream_t>(stream);
-  cudaLaunchAttribute attributes[1];
-  attributes[0].id = cudaLaunchAttributeClusterDimension;
-  attributes[0].val.clusterDim.x = 1;
-  attributes[0].val.clusterDim.y = 1;
-  attributes[0].val.clusterDim.z = 1;
-  config.attrs = attributes;
-  config.numAttrs = 1;
-  __atomic_fetch_add(&sageb200::g_sageb200_glue_launches, 1ull, __ATOMIC_RELAXED);
-  const __half *none = nullptr;
-  const cudaError_t error = cudaLaunchKernelEx(
-      &config, attention_step_kernel, static_cast<const __half *>(q), none, none, none, none, none, none,
-      static_cast<const int *>(positions), static_cast<__half *>(const_cast<void *>(k_cache)),
-      static_cast<__half *>(const_cast<void *>(v_cache)), static_cast<__half *>(out), q_heads, kv_heads, max_seq,
-      0.0f, rsqrtf(128.0f), tokens);
-  return error == cudaSuccess ? launch_status() : -5;
+  return launch_attention(true, q, nullptr, nullptr, nullptr, nullptr, nullptr, nullptr, positions,
+                          const_cast<void *>(k_cache), const_cast<void *>(v_cache), out, sequences * tokens, q_heads,
+                          kv_heads, max_seq, 1, 0.0f, tokens, false, stream);
 }
 
 int sageb200_glue_swiglu(const void *gate, const void *up, void *act, long long count, void *stream) {
