@@ -536,7 +536,7 @@ __global__ void swiglu_kernel(const __half *__restrict__ gate, const __half *__r
   const long long i = static_cast<long long>(blockIdx.x) * blockDim.x + threadIdx.x;
   if (i >= count) return;
   const float g = __half2float(gate[i]);
-  const __half silu = __float2half_rn(g / (1.0f + __expf(-g)));
+  const __half silu = __float2half_rn(sageb200::silu_fast(g));
   act[i] = __hmul(silu, up[i]);
 }
 

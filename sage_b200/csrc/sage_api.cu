@@ -277,7 +277,7 @@ __global__ void __launch_bounds__(256)
   if (kind == 2) {
     for (int i = threadIdx.x; i < k; i += 256) {
       const float g = __half2float(a[offset + i]);
-      x[offset + i] = __hmul(__float2half_rn(g / (1.0f + __expf(-g))), b[offset + i]);
+      x[offset + i] = __hmul(__float2half_rn(silu_fast(g)), b[offset + i]);
     }
     return;
   }

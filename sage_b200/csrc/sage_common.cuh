@@ -84,6 +84,10 @@ inline cudaError_t launch_dependent(void (*kernel)(KernelArgs...), dim3 grid, di
   return cudaLaunchKernelEx(&config, kernel, static_cast<KernelArgs>(args)...);
 }
 
+// silu(g) = g / (1 + e^-g) with the fast exponential and the fast division, the same in every
+// kernel that computes it (the fused and the stand-alone SwiGLU must round alike).
+__device__ __forceinline__ float silu_fast(float g) { return __fdividef(g, 1.0f + __expf(-g)); }
+
 __device__ __forceinline__ long long global_nanoseconds() {
   long long t;
   asm volatile("mov.u64 %0, %globaltimer;" : "=l"(t));

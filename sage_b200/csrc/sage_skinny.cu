@@ -350,7 +350,7 @@ __global__ void __launch_bounds__(512, 1) sage_skinny_kernel(const __grid_consta
             square_sum = fmaf(f.x, f.x, fmaf(f.y, f.y, square_sum));
           } else {
             const float2 g2 = __half22float2(ah[c]);
-            const __half2 silu = __floats2half2_rn(g2.x / (1.0f + __expf(-g2.x)), g2.y / (1.0f + __expf(-g2.y)));
+            const __half2 silu = __floats2half2_rn(silu_fast(g2.x), silu_fast(g2.y));
             vh[c] = __hmul2(silu, bh[c]);
           }
         }
