@@ -215,7 +215,8 @@ int sageb200_linear_host(const void *x_host, const void *codes, const void *radi
  * Tuning knob for sweeps (debug): warps per CTA (<= 16), K slices (<= 8) and CTAs per SM
  * of the decode kernel, and how output tiles are shared out (`mode` 1: every CTA gets an
  * even share of the (tile, group) units and shared tiles are finished through scratch;
- * 2: whole tiles per CTA); 0 restores the built-in heuristic for a field.  Not thread
+ * 2: whole tiles per CTA; 3: never stream a CTA's share through shared-memory rings, launch
+ * further waves of CTAs instead); 0 restores the built-in heuristic for a field.  Not thread
  * safe, like its counterpart.
  * Replaces: _set_sage_tuning / sage_gemv_tuning (reference csrc/bindings.cpp:81-84,
  *           csrc/sage/sage_gemv_cuda.cu:3-4).

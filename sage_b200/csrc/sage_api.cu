@@ -136,14 +136,16 @@ void cta_budgets(const sageb200_problem *problems, int count, const DeviceState 
 }
 
 // Scratch bytes (after the counter region) the problems need together.
-size_t grouped_scratch_bytes(const sageb200_problem *problems, int count, const DeviceState &device) {
+size_t grouped_scratch_bytes(const sageb200_problem *problems, int count, const DeviceState &device,
+                             int act_kind = 0) {
   int budgets[kMaxGrouped];
   cta_budgets(problems, count, device, budgets);
   size_t bytes = 0;
   for (int i = 0; i < count; ++i) {
     const sageb200_problem &in = problems[i];
     if (in.rows == 0) continue;
-    const SkinnyPlan plan = plan_skinny(in.rows, in.n, in.k, in.entries, device.sm_count, g_tuning, budgets[i]);
+    const SkinnyPlan plan =
+        plan_skinny(in.rows, in.n, in.k, in.entries, device.sm_count, g_tuning, budgets[i], in.rows == 1 ? act_kind : 0);
     bytes += align256(plan.partial_bytes) + (in.rows > 1 && in.perm ? align256(static_cast<size_t>(in.rows) * in.k * 2) : 0);
   }
   return bytes;
@@ -187,7 +189,7 @@ int run_skinny(const sageb200_problem *problems, int count, void *workspace,
     const sageb200_problem &in = problems[i];
     if (in.rows == 0) continue;
     const SkinnyPlan plan =
-        plan_skinny(in.rows, in.n, in.k, in.entries, device.sm_count, g_tuning, budgets[i]);
+        plan_skinny(in.rows, in.n, in.k, in.entries, device.sm_count, g_tuning, budgets[i], params.act_kind);
     const size_t partial = plan_bytes(plan);
     const size_t gathered = gather_bytes(in.rows, in.k, in.perm != nullptr);
     if (partial || gathered) {
@@ -227,6 +229,7 @@ int run_skinny(const sageb200_problem *problems, int count, void *workspace,
     out.ctas_per_slice = plan.ctas_per_slice;
     out.slots_per_tile = plan.slots_per_tile;
     out.whole_tiles = plan.whole_tiles;
+    out.ring = plan.ring;
     {
       const long long share = plan.whole_tiles ? plan.tiles : static_cast<long long>(plan.tiles) * (in.k / 128);
       out.share_q = static_cast<int>(share / plan.ctas_per_slice);
@@ -527,7 +530,7 @@ int sageb200_debug_trace(void *device_buffer) {
 
 int sageb200_set_tuning(int warps, int slices, int ctas_per_sm, int mode) {
   if (warps < 0 || warps > 16 || slices < 0 || slices > 8 || ctas_per_sm < 0 || ctas_per_sm > 8 ||
-      mode < 0 || mode > 2)
+      mode < 0 || mode > 3)
     return SAGEB200_ERR_INVALID_ARGUMENT;
   g_tuning = Tuning{warps, slices, ctas_per_sm, mode};
   return SAGEB200_OK;
@@ -540,8 +543,18 @@ unsigned long long sageb200_glue_launch_count(void) {
 }
 
 size_t sageb200_fused_workspace_bytes(const sageb200_problem *problems_host, int count) {
-  const size_t grouped = sageb200_grouped_workspace_bytes(problems_host, count);
+  size_t grouped = sageb200_grouped_workspace_bytes(problems_host, count);
   if (!problems_host || count <= 0) return 0;
+  if (count <= SAGEB200_MAX_GROUPED) {  // the plan depends on the fused producer: cover both kinds
+    DeviceState fallback;
+    fallback.sm_count = 148;
+    DeviceState *device = nullptr;
+    if (device_state(&device) != SAGEB200_OK) device = &fallback;
+    for (int kind = 1; kind <= 2; ++kind) {
+      const size_t bytes = grouped_scratch_bytes(problems_host, count, *device, kind);
+      if (bytes && kCounterRegionBytes + bytes > grouped) grouped = kCounterRegionBytes + bytes;
+    }
+  }
   const int rows = problems_host[0].rows, k = problems_host[0].k;
   const size_t staged = rows > 1 ? align256(static_cast<size_t>(rows) * k * 2) : 0;
   if (!staged) return grouped;

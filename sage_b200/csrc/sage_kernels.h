@@ -28,6 +28,7 @@ struct SkinnyProblem {
   int slots_per_tile;
   int whole_tiles;      // 1: CTAs own whole tiles (no sharing); 0: even share of units
   int share_q, share_r; // (tiles or units) / ctas_per_slice and remainder, for slices == 1
+  int ring;             // 1: each warp streams its units through a ring of kRingStages x kRingUnits slots
   int cta_begin;        // first CTA of this problem in the grid
   // expert indirection (null: none): the weights are those of expert expert_ids[expert_slot]
   // inside a stack of expert_count experts starting at global expert expert_first
@@ -64,6 +65,7 @@ struct SkinnyPlan {
   int warp_segments;
   int slots_per_tile;
   int whole_tiles;
+  int ring;             // the CTA's share exceeds its shared memory: warps stream it through rings
   int column_blocks;    // 1 for rows <= 8, 2 for rows <= 16
   int tiles;
   bool needs_scratch;
@@ -78,8 +80,10 @@ struct Tuning {
 };
 
 // cta_budget: CTAs the problem may occupy at once (0: the whole device).
+// act_kind: the producer fused into a single-row launch (0 none, 1 residual add + RMSNorm,
+// 2 SwiGLU); it sizes the linear staging buffer and so takes part in the plan.
 SkinnyPlan plan_skinny(int rows, int n, int k, int entries, int sm_count, const Tuning &tuning,
-                       int cta_budget = 0);
+                       int cta_budget = 0, int act_kind = 0);
 
 // Opts every skinny-kernel variant into large dynamic shared memory on the CURRENT device.
 cudaError_t configure_skinny();

@@ -46,6 +46,11 @@ constexpr int kMaxWholeTiles = 192;   // tiles of one CTA in any mode (unit capa
 constexpr int kMaxSlices = 8;
 constexpr int kUnitBytes = 640;           // 512 codes + 64 radius words + 64 grid
 constexpr int kMaxDynamicShared = 184 * 1024;  // plus ~37 KiB static stays under the 227 KiB limit
+// Ring mode (a CTA's share of the matrix exceeds its shared memory): every warp streams its
+// contiguous units through kRingStages stages of kRingUnits units, refilling a stage as soon
+// as the warp has decoded it, so the HBM stream and the decode arithmetic overlap.
+constexpr int kRingStages = 3;
+constexpr int kRingUnitsMax = 4;  // units per stage: 4, 2 or 1, whatever fits beside the activations
 
 __device__ __forceinline__ void bulk_copy(uint32_t dst, const void *src, uint32_t bytes,
                                           uint32_t bar) {
@@ -87,11 +92,13 @@ __device__ __forceinline__ int split_owner(int u, int q, int r) {
 // 16-byte aligned x; 5 = kind 3 for routed experts (the indirection stays); 4 = one activation
 // row and nothing else assumed; 0 = every case.  The special paths are the generic code with those facts
 // known at compile time, so the cold instruction stream after the wait is short and contiguous.
-template <int NB, bool kLowBits, int kPath>
+// kRing: the CTA's share streams through per-warp rings (see kRingStages); a separate variant so
+// that the resident-share kernels keep their shorter main loop.
+template <int NB, bool kLowBits, int kPath, bool kRing = false>
 __global__ void __launch_bounds__(512, 1) sage_skinny_kernel(const __grid_constant__ SkinnyParams params) {
   extern __shared__ __align__(128) unsigned char shared[];
   __shared__ __align__(128) unsigned char book_shared[kBookBytes];
-  __shared__ __align__(8) unsigned long long barriers[kMaxWarps];
+  __shared__ __align__(8) unsigned long long barriers[kMaxWarps][kRingStages];
   __shared__ int warp_first_tile[kMaxWarps];
   __shared__ float norm_sums[kMaxWarps];
   __shared__ int tile_parts[kMaxCtaTiles];  // CTAs contributing to the tile, all slices
@@ -187,11 +194,36 @@ __global__ void __launch_bounds__(512, 1) sage_skinny_kernel(const __grid_consta
   const int warp_r = unit_count - warp_q * warps;
   const int warp_begin = unit_begin + split_begin(warp, warp_q, warp_r);
   const int warp_end = unit_begin + split_begin(warp + 1, warp_q, warp_r);
-  const uint32_t bar = smem_address(&barriers[warp]);
+  const uint32_t bar = smem_address(&barriers[warp][0]);
+  // (only with an unsliced K); p.ring = units per stage, 0 for a problem of the launch that fits
+  const bool ring = kRing && p.ring != 0;
+  const int kRingUnits = kRing ? p.ring : 1;
+  const int kRingSlots = kRingStages * kRingUnits;
+  const int warp_units = warp_end - warp_begin;
+  // ring: chunk c of the warp = units warp_begin + c*kRingUnits ..., into stage c % kRingStages
+  auto ring_issue = [&](int chunk) {
+    const int first = warp_begin + chunk * kRingUnits;
+    const uint32_t count = static_cast<uint32_t>(min(kRingUnits, warp_end - first));
+    const uint32_t stage = static_cast<uint32_t>(chunk % kRingStages);
+    const uint32_t stage_bar = bar + 8u * stage;
+    const uint32_t slot = static_cast<uint32_t>(warp * kRingSlots) + stage * kRingUnits;
+    const size_t cell = static_cast<size_t>(first) * 16;
+    asm volatile("mbarrier.arrive.expect_tx.shared::cta.b64 _, [%0], %1;" ::"r"(stage_bar), "r"(count * kUnitBytes)
+                 : "memory");
+    bulk_copy(smem_address(codes_shared) + slot * 512u, p.codes + cell * 8, count * 512u, stage_bar);
+    bulk_copy(smem_address(radii_shared) + slot * 64u, p.radii + cell, count * 64u, stage_bar);
+    bulk_copy(smem_address(grid_shared) + slot * 64u, p.grid + cell, count * 64u, stage_bar);
+  };
 
   SAGE_STAMP(11);
   // ---- 1. start the weight stream: lane 0 of each warp copies the warp's units
-  if (lane == 0) {
+  if (lane == 0 && ring) {
+#pragma unroll
+    for (int stage = 0; stage < kRingStages; ++stage)
+      asm volatile("mbarrier.init.shared::cta.b64 [%0], 1;" ::"r"(bar + 8u * stage));
+    asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
+    for (int chunk = 0; chunk < kRingStages && chunk * kRingUnits < warp_units; ++chunk) ring_issue(chunk);
+  } else if (lane == 0) {
     asm volatile("mbarrier.init.shared::cta.b64 [%0], 1;" ::"r"(bar));
     asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
     if (warp_end > warp_begin) {
@@ -505,7 +537,7 @@ __global__ void __launch_bounds__(512, 1) sage_skinny_kernel(const __grid_consta
 
   SAGE_STAMP(4);
   // ---- 4. wait (bounded) for this warp's weights
-  bool ready = barrier_done(bar, 0);
+  bool ready = ring || barrier_done(bar, 0);
   if (!ready) {
     const unsigned long long begin = global_timer();
     unsigned spins = 0;
@@ -546,11 +578,31 @@ __global__ void __launch_bounds__(512, 1) sage_skinny_kernel(const __grid_consta
     const int tile0 = warp_begin / group_count;
     int gi = warp_begin - tile0 * group_count;
     first_tile = tile0;
-    const size_t first_slot = static_cast<size_t>(warp_begin - unit_begin);
-    const unsigned char *code_ptr = codes_shared + first_slot * 512 + g * 32 + t * 8;
-    const unsigned char *radius_ptr = radii_shared + first_slot * 64 + g * 4;
-    const unsigned char *grid_ptr = grid_shared + first_slot * 64 + g * 4;
+    int slot = ring ? warp * kRingSlots : warp_begin - unit_begin;  // shared-memory slot of unit u
+    int chunk = 0, in_chunk = 0;
     for (int u = warp_begin; u < warp_end; ++u) {
+      if (ring && in_chunk == 0) {
+        // wait (bounded) for this chunk's bytes; the stage's phase flips every kRingStages chunks
+        const uint32_t stage_bar = bar + 8u * static_cast<uint32_t>(chunk % kRingStages);
+        const uint32_t parity = static_cast<uint32_t>(chunk / kRingStages) & 1u;
+        bool arrived = barrier_done(stage_bar, parity);
+        if (!arrived) {
+          const unsigned long long begin = global_timer();
+          unsigned spins = 0;
+          while (!(arrived = barrier_done(stage_bar, parity))) {
+            if ((++spins & 255u) == 0 && global_timer() - begin > kWaitLimitNs) break;
+          }
+        }
+        arrived = __all_sync(0xffffffffu, arrived);
+        if (!arrived) {
+          if (lane == 0 && params.status) atomicExch(params.status, -7);
+          break;
+        }
+        slot = warp * kRingSlots + (chunk % kRingStages) * kRingUnits;
+      }
+      const unsigned char *code_ptr = codes_shared + static_cast<size_t>(slot) * 512 + g * 32 + t * 8;
+      const unsigned char *radius_ptr = radii_shared + static_cast<size_t>(slot) * 64 + g * 4;
+      const unsigned char *grid_ptr = grid_shared + static_cast<size_t>(slot) * 64 + g * 4;
       uint2 code[2];
       uint32_t radius_word[2], endpoints[2];
       code[0] = *reinterpret_cast<const uint2 *>(code_ptr);
@@ -563,10 +615,15 @@ __global__ void __launch_bounds__(512, 1) sage_skinny_kernel(const __grid_consta
 #pragma unroll
       for (int nb = 0; nb < NB; ++nb) x_row[nb] = x_row_base[nb] + 256 * gi;
       compute_unit<NB, kLowBits>(code, radius_word, endpoints, acc, f, book_shared, lane_offset, x_row, t);
-      code_ptr += 512;
-      radius_ptr += 64;
-      grid_ptr += 64;
+      ++slot;
       ++gi;
+      if (ring && (++in_chunk == kRingUnits || u + 1 == warp_end)) {
+        // the whole warp is done with this stage: refill it with the chunk kRingStages ahead
+        __syncwarp();
+        if (lane == 0 && (chunk + kRingStages) * kRingUnits < warp_units) ring_issue(chunk + kRingStages);
+        ++chunk;
+        in_chunk = 0;
+      }
       if (gi == group_count || u + 1 == warp_end) {
         // this warp is done with the tile: park its partial sums
         float *dst = my_partial + tile_count * kSegmentFloats;
@@ -658,6 +715,11 @@ __global__ void __launch_bounds__(512, 1) sage_skinny_kernel(const __grid_consta
 
 template <int NB, bool kLowBits, int kPath = 0>
 cudaError_t configure_variant() {
+  if (NB == 1) {  // ring streaming exists for up to eight activation rows
+    const cudaError_t status = cudaFuncSetAttribute(sage_skinny_kernel<1, kLowBits, kPath, true>,
+                                                    cudaFuncAttributeMaxDynamicSharedMemorySize, kMaxDynamicShared);
+    if (status != cudaSuccess) return status;
+  }
   return cudaFuncSetAttribute(sage_skinny_kernel<NB, kLowBits, kPath>,
                               cudaFuncAttributeMaxDynamicSharedMemorySize, kMaxDynamicShared);
 }
@@ -674,7 +736,7 @@ int slice_groups(int groups, int slices, int slice) {
 }  // namespace
 
 SkinnyPlan plan_skinny(int rows, int n, int k, int entries, int sm_count, const Tuning &tuning,
-                       int cta_budget) {
+                       int cta_budget, int act_kind) {
   (void)entries;
   SkinnyPlan plan{};
   const int tiles = (n + 15) / 16;
@@ -689,7 +751,11 @@ SkinnyPlan plan_skinny(int rows, int n, int k, int entries, int sm_count, const 
   const int unit_cap = 192;  // 192 * 640 B = 120 KiB of packed weights per CTA
 
   // K slices: as few as keep one slice's activations within the shared-memory budget
-  const size_t x_budget = 40 * 1024;
+  // (a single row may take more: its launch streams the weights through rings if need be)
+  const size_t x_budget = rows == 1 ? 64 * 1024 : 40 * 1024;
+  // a single row with a permutation is gathered through a linear copy in shared memory; the
+  // fused residual add + RMSNorm keeps the norm weights behind it
+  const size_t lin_bytes = rows == 1 ? (static_cast<size_t>(k) * (act_kind == 1 ? 4 : 2) + 127) / 128 * 128 : 0;
   int slices = tuning.slices > 0 ? tuning.slices : 1;
   if (slices > kMaxSlices) slices = kMaxSlices;
   if (slices > groups) slices = groups;
@@ -709,24 +775,37 @@ SkinnyPlan plan_skinny(int rows, int n, int k, int entries, int sm_count, const 
   if (tuning.mode == 2 && slices == 1) whole = true;
   if (whole) {
     long long ctas = resident < tiles ? resident : tiles;
-    // a CTA's tiles must fit its shared-memory budget without going past one resident wave
-    if (((tiles + ctas - 1) / ctas) * groups > unit_cap) whole = false;
+    const long long cta_tiles = (tiles + ctas - 1) / ctas;
+    const long long cta_units = cta_tiles * groups;
+    // a CTA's tiles either fit its shared memory or (one resident wave kept) stream through rings
+    const bool ring = cta_units > unit_cap;  // (up to eight activation rows only)
+    if (ring && (cta_tiles > kMaxWholeTiles || tuning.mode == 3 || plan.column_blocks != 1)) whole = false;
     if (whole) {
       plan.whole_tiles = 1;
       plan.slices = 1;
       plan.ctas_per_slice = static_cast<int>(ctas);
       plan.ctas = plan.ctas_per_slice;
-      plan.unit_capacity = static_cast<int>((tiles + ctas - 1) / ctas) * groups;
-      const int warp_units = (plan.unit_capacity + plan.warps - 1) / plan.warps;
+      const int warp_units = static_cast<int>((cta_units + plan.warps - 1) / plan.warps);
       plan.warp_segments = warp_units / groups + 2;
       plan.slots_per_tile = 1;
       plan.x_bytes = x_bytes_for(rows, groups);
       plan.needs_scratch = false;
       plan.partial_bytes = 0;
-      const size_t lin = rows == 1 ? (static_cast<size_t>(k) * 4 + 127) / 128 * 128 : 0;
-      const size_t shared = plan.x_bytes + static_cast<size_t>(plan.unit_capacity) * kUnitBytes +
-                            static_cast<size_t>(plan.warps) * plan.warp_segments * plan.column_blocks * 512 + lin;
-      if (shared > static_cast<size_t>(kMaxDynamicShared)) whole = false;
+      const size_t fixed = plan.x_bytes + lin_bytes +
+                           static_cast<size_t>(plan.warps) * plan.warp_segments * plan.column_blocks * 512;
+      plan.ring = 0;
+      plan.unit_capacity = static_cast<int>(cta_units);
+      if (ring) {  // units per ring stage: as many as fit beside the row's buffers
+        int units = kRingUnitsMax;
+        while (units > 0 && fixed + static_cast<size_t>(plan.warps) * kRingStages * units * kUnitBytes >
+                                static_cast<size_t>(kMaxDynamicShared))
+          units >>= 1;
+        plan.ring = units;
+        plan.unit_capacity = plan.warps * kRingStages * units;
+        if (units == 0) whole = false;
+      }
+      if (fixed + static_cast<size_t>(plan.unit_capacity) * kUnitBytes > static_cast<size_t>(kMaxDynamicShared))
+        whole = false;
     }
   }
   if (!whole) {
@@ -744,22 +823,40 @@ SkinnyPlan plan_skinny(int rows, int n, int k, int entries, int sm_count, const 
     const long long max_units = static_cast<long long>(tiles) * max_groups;
     long long per_slice = resident / slices;
     if (per_slice < 1) per_slice = 1;
-    if (per_slice * unit_cap < max_units) per_slice = (max_units + unit_cap - 1) / unit_cap;
+    // more units than one resident wave holds in shared memory: stream them through rings
+    // (unsliced K only), else add CTAs (further waves)
+    bool ring = slices == 1 && per_slice * unit_cap < max_units && tuning.mode != 3 && plan.column_blocks == 1;
+    if (!ring && per_slice * unit_cap < max_units) per_slice = (max_units + unit_cap - 1) / unit_cap;
     const int tile_cap = kMaxCtaTiles - 2;
     while ((max_units + per_slice - 1) / per_slice / min_groups + 2 > tile_cap) ++per_slice;
     if (per_slice > min_units) per_slice = min_units;
-    const size_t fixed = x_bytes_for(rows, max_groups) +
-                         (rows == 1 ? (static_cast<size_t>(k) * 4 + 127) / 128 * 128 : 0);
+    const size_t fixed = x_bytes_for(rows, max_groups) + lin_bytes;
+    int ring_units = 0;
     while (true) {  // more (smaller) CTAs until one CTA's units fit shared memory
-      plan.unit_capacity = static_cast<int>((max_units + per_slice - 1) / per_slice);
-      const int warp_units = (plan.unit_capacity + plan.warps - 1) / plan.warps;
+      const int cta_units = static_cast<int>((max_units + per_slice - 1) / per_slice);
+      if (ring && cta_units <= unit_cap) ring = false;
+      const int warp_units = (cta_units + plan.warps - 1) / plan.warps;
       plan.warp_segments = warp_units / min_groups + 2;
-      const size_t shared = fixed + static_cast<size_t>(plan.unit_capacity) * kUnitBytes +
-                            static_cast<size_t>(plan.warps) * plan.warp_segments * plan.column_blocks * 512;
-      if (shared <= static_cast<size_t>(kMaxDynamicShared) || per_slice >= min_units) break;
+      const size_t tables = static_cast<size_t>(plan.warps) * plan.warp_segments * plan.column_blocks * 512;
+      ring_units = 0;
+      if (ring) {  // units per ring stage: as many as fit beside the row's buffers
+        ring_units = kRingUnitsMax;
+        while (ring_units > 0 && fixed + tables + static_cast<size_t>(plan.warps) * kRingStages * ring_units * kUnitBytes >
+                                     static_cast<size_t>(kMaxDynamicShared))
+          ring_units >>= 1;
+      }
+      plan.unit_capacity = ring ? plan.warps * kRingStages * ring_units : cta_units;
+      const size_t shared = fixed + tables + static_cast<size_t>(plan.unit_capacity) * kUnitBytes;
+      if ((shared <= static_cast<size_t>(kMaxDynamicShared) && (!ring || ring_units > 0)) || (!ring && per_slice >= min_units)) break;
+      if (ring) {  // the rings do not fit beside this row's buffers: back to further waves
+        ring = false;
+        if (per_slice * unit_cap < max_units) per_slice = (max_units + unit_cap - 1) / unit_cap;
+        continue;
+      }
       per_slice += (per_slice + 3) / 4;
       if (per_slice > min_units) per_slice = min_units;
     }
+    plan.ring = ring ? ring_units : 0;
     plan.ctas_per_slice = static_cast<int>(per_slice);
     plan.ctas = plan.ctas_per_slice * slices;
     // pieces per tile: in each slice a tile's units span at most `parts` CTAs
@@ -777,7 +874,7 @@ SkinnyPlan plan_skinny(int rows, int n, int k, int entries, int sm_count, const 
   }
   // a single activation row with a permutation is gathered through a linear copy in
   // shared memory (several rows arrive pre-gathered)
-  plan.lin_bytes = rows == 1 ? (static_cast<size_t>(k) * 4 + 127) / 128 * 128 : 0;  // row + norm weights
+  plan.lin_bytes = lin_bytes;
   plan.shared_bytes = plan.x_bytes + static_cast<size_t>(plan.unit_capacity) * kUnitBytes +
                       static_cast<size_t>(plan.warps) * plan.warp_segments * plan.column_blocks * 512 +
                       plan.lin_bytes;
@@ -824,7 +921,7 @@ cudaError_t launch_skinny(const SkinnyParams &params, int warps, int column_bloc
   int path = column_blocks == 1 ? (params.act_kind == 0 ? 3 : params.act_kind) : 0;
   for (int i = 0; i < params.count && path != 0; ++i) {
     const SkinnyProblem &q = params.problem[i];
-    const bool fits = static_cast<size_t>(q.k) * 2 <= static_cast<size_t>(params.lin_bytes);
+    const bool fits = static_cast<size_t>(q.k) * (params.act_kind == 1 ? 4 : 2) <= static_cast<size_t>(params.lin_bytes);
     if (q.expert_ids != nullptr && path == 3) path = 5;  // routed experts: kind 3 plus the indirection
     if (q.rows != 1 || q.slices != 1 || (q.expert_ids != nullptr && path != 5) || q.perm == nullptr ||
         (reinterpret_cast<uintptr_t>(q.perm) & 15) != 0 || !fits ||
@@ -839,8 +936,14 @@ cudaError_t launch_skinny(const SkinnyParams &params, int warps, int column_bloc
   if (limit == 0) path = 0;
   if (limit == 3 && path >= 4) path = 0;
   if (limit == 4) path = single_rows ? 4 : 0;
-#define SAGE_LAUNCH(NB_, LOW_, PATH_) \
-  launch_dependent(sage_skinny_kernel<NB_, LOW_, PATH_>, total_ctas, threads, shared_bytes, stream, params)
+  bool ring = false;  // (the planner gives every problem of a launch the same answer, or none)
+  for (int i = 0; i < params.count; ++i) ring = ring || params.problem[i].ring != 0;
+  if (ring && column_blocks != 1) return cudaErrorInvalidConfiguration;  // (the planner never asks for it)
+#define SAGE_LAUNCH(NB_, LOW_, PATH_)                                                                       \
+  (ring && NB_ == 1 ? launch_dependent(sage_skinny_kernel<1, LOW_, PATH_, true>, total_ctas, threads,       \
+                                       shared_bytes, stream, params)                                        \
+                    : launch_dependent(sage_skinny_kernel<NB_, LOW_, PATH_>, total_ctas, threads, shared_bytes, \
+                                       stream, params))
   if (column_blocks == 1) {
     switch (path) {
       case 1: return low_bits ? SAGE_LAUNCH(1, true, 1) : SAGE_LAUNCH(1, false, 1);

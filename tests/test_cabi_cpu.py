@@ -77,7 +77,7 @@ def test_invalid_arguments_are_rejected_without_a_device(lib):
     assert lib.sageb200_dequant(one, one, one, one, null, null, 16, 128, 256, null) == -1
     assert lib.sageb200_set_tuning(17, 0, 0, 0) == -1
     assert lib.sageb200_set_tuning(0, 9, 0, 0) == -1
-    assert lib.sageb200_set_tuning(0, 0, 0, 3) == -1
+    assert lib.sageb200_set_tuning(0, 0, 0, 4) == -1
     assert lib.sageb200_set_tuning(0, 0, 0, 0) == 0
     assert lib.sageb200_linear_grouped(None, 1, null, 0, null) == -1
 
