@@ -433,3 +433,50 @@ def test_fused_producers_match_separate_kernels(rows, permuted):
     got = sage_grouped(problem(gate), outs, (2, 0.0, gate, up, None, None))
     for a, b in zip(got, want):
         assert ((a.float() - b.float()).norm() / b.float().norm()).item() < 1e-3
+
+
+@pytest.mark.parametrize("k,n,rows", [(5120, 25600, 1), (5120, 25600, 5), (25600, 5120, 1), (25600, 2560, 2)])
+def test_shares_larger_than_shared_memory_stream_through_rings(k, n, rows):
+    """Qwen3-32B-sized matrices: a CTA's share no longer fits its shared memory and is streamed
+    through per-warp rings (and through further waves of CTAs when that is switched off); both
+    against an FP32 matmul on the kernel-made dense weight, and the fused producers on the same
+    sizes against the separate kernels."""
+    lib = _lib.load()
+    gpu = to_cuda(synthetic_sage(k, n, seed=rows, permuted=True))
+    layer = SAGELinear(gpu, n)
+    weight = layer.dequantize().float()
+    x = torch.randn(rows, k, generator=torch.Generator().manual_seed(k + rows), dtype=torch.float16).cuda()
+    want = x.float() @ weight.T
+    del weight
+    streamed = layer(x)
+    assert_output(streamed, want)
+    assert torch.equal(layer(x), streamed)  # repeatable
+    assert lib.sageb200_set_tuning(0, 0, 0, 3) == 0  # no rings: several waves of CTAs
+    try:
+        assert_output(layer(x), want)
+    finally:
+        assert lib.sageb200_set_tuning(0, 0, 0, 0) == 0
+    if rows == 1:  # fused SwiGLU and fused residual add + RMSNorm feeding the same matrix
+        vp = ctypes.c_void_p
+        stream = vp(torch.cuda.current_stream().cuda_stream)
+        gen = torch.Generator(device="cuda").manual_seed(n)
+        problem = lambda t: [(t, layer.packed_codes, layer.radius_codes, layer.radius_grid, layer.codebook,  # noqa: E731
+                              layer.permutation)]
+        gate = torch.randn(1, k, generator=gen, device="cuda").half()
+        up = torch.randn(1, k, generator=gen, device="cuda").half()
+        act = torch.empty_like(gate)
+        assert lib.sageb200_glue_swiglu(vp(gate.data_ptr()), vp(up.data_ptr()), vp(act.data_ptr()), gate.numel(),
+                                        stream) == 0
+        (plain,) = sage_grouped(problem(act), [n])
+        (fused,) = sage_grouped(problem(gate), [n], (2, 0.0, gate, up, None, None))
+        assert ((fused.float() - plain.float()).norm() / plain.float().norm()).item() < 1e-3
+        if k > 24576:  # wider than the stand-alone norm kernel takes (no model norms such a row)
+            return
+        norm_weight = (1 + 0.1 * torch.randn(k, generator=gen, device="cuda")).half()
+        h, normed, new_residual = gate.clone(), torch.empty_like(gate), torch.zeros_like(gate)
+        assert lib.sageb200_glue_add_rmsnorm(vp(h.data_ptr()), vp(up.data_ptr()), vp(norm_weight.data_ptr()),
+                                             vp(normed.data_ptr()), 1, k, 1e-6, stream) == 0
+        (plain,) = sage_grouped(problem(normed), [n])
+        (fused,) = sage_grouped(problem(gate), [n], (1, 1e-6, gate, up, norm_weight, new_residual))
+        assert torch.equal(new_residual, h)
+        assert ((fused.float() - plain.float()).norm() / plain.float().norm()).item() < 1e-3
