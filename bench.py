@@ -509,7 +509,7 @@ def run_model(args) -> None:
 
 def run_report(args) -> None:
     """`--workload report`: Qwen3-4B, prompt `--prompt`, 256 generated tokens, measured and
-    written in the reference benchmark's schema (JSON + CSV under gpurun_out/ or ./reports)."""
+    written in the reference benchmark's schema (JSON + CSV under `--output`, default ./reports)."""
     import torch
 
     from sage_b200.harness import measure, write_report
@@ -522,7 +522,7 @@ def run_report(args) -> None:
     model.capture()
     prompt = torch.randint(3, QWEN3_4B.vocab, (1, args.prompt), generator=torch.Generator().manual_seed(0))
     result, rows = measure(model, prompt, decode, samples=max(3, min(args.steps, 10)), warmup=2)
-    folder = pathlib.Path("gpurun_out") if pathlib.Path("gpurun_out").is_dir() else pathlib.Path("reports")
+    folder = pathlib.Path(args.output)
     path, csv_path = write_report(result, rows, folder, f"qwen3-4b-sage-prefill{args.prompt}-decode{decode}")
     print(json.dumps({"report": str(path), "csv": str(csv_path),
                       "rows": [[m, p, metric, round(value, 3), unit] for m, p, metric, value, unit in rows]}), flush=True)
@@ -811,6 +811,7 @@ def main() -> None:
     parser.add_argument("--impl", choices=["ours", "reference"], default="ours")
     parser.add_argument("--workload", default="decode_model")
     parser.add_argument("--prompt", type=int, default=512)
+    parser.add_argument("--output", default="reports", help="folder for the files of --workload report")
     args = parser.parse_args()
     if args.impl == "reference":
         run_reference(args)
