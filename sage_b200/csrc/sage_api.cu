@@ -108,6 +108,7 @@ constexpr int kCounterCapacity = static_cast<int>(kCounterRegionBytes / sizeof(u
 
 // Scratch one problem needs at `rows` <= 16: partial pieces, then (rows > 1 with a
 // permutation) the gathered activations.
+// (a fused producer of several rows gives every problem its own staged copy)
 size_t gather_bytes(int rows, int k, bool permuted) {
   return rows > 1 && permuted ? align256(static_cast<size_t>(rows) * k * 2) : 0;
 }
@@ -146,9 +147,85 @@ size_t grouped_scratch_bytes(const sageb200_problem *problems, int count, const 
     if (in.rows == 0) continue;
     const SkinnyPlan plan =
         plan_skinny(in.rows, in.n, in.k, in.entries, device.sm_count, g_tuning, budgets[i], in.rows == 1 ? act_kind : 0);
-    bytes += align256(plan.partial_bytes) + (in.rows > 1 && in.perm ? align256(static_cast<size_t>(in.rows) * in.k * 2) : 0);
+    bytes += align256(plan.partial_bytes) + gather_bytes(in.rows, in.k, in.perm != nullptr || act_kind != 0);
   }
   return bytes;
+}
+
+// Activation rows of a launch of several rows, for every problem in ONE launch: the row is
+// taken from the problem's x (kind 0) or computed from the fused producer's inputs (kind 1
+// residual add + RMSNorm - job 0 also writes the new residual - or kind 2 SwiGLU), staged in
+// shared memory and written out in the problem's quantised channel order.  grid = (rows, jobs).
+struct StageJob {
+  const __half *x;
+  const int32_t *perm;  // null: identity
+  __half *xq;
+  int rows, k;
+};
+struct StageParams {
+  StageJob job[kMaxGrouped];
+  int kind;
+  float eps;
+  const __half *a, *b, *weight;
+  __half *residual_out;
+};
+constexpr size_t kStageSharedLimit = 96 * 1024;  // rows up to 49152 channels
+
+__global__ void __launch_bounds__(256) stage_rows_kernel(const __grid_constant__ StageParams params) {
+  extern __shared__ __half row_shared[];
+  __shared__ float sums[8];
+  const StageJob &job = params.job[blockIdx.y];
+  const int row = blockIdx.x;
+  if (row >= job.rows) return;
+  const int k = job.k;
+  const size_t offset = static_cast<size_t>(row) * k;
+  if (params.kind == 0) {
+    for (int i = threadIdx.x; i < k; i += 256) row_shared[i] = job.x[offset + i];
+  } else if (params.kind == 2) {
+    for (int i = threadIdx.x; i < k; i += 256) {
+      const float g = __half2float(params.a[offset + i]);
+      row_shared[i] = __hmul(__float2half_rn(silu_fast(g)), params.b[offset + i]);
+    }
+  } else {
+    float square = 0.0f;
+    for (int i = threadIdx.x; i < k; i += 256) {
+      const __half v = params.b ? __hadd(params.a[offset + i], params.b[offset + i]) : params.a[offset + i];
+      row_shared[i] = v;
+      if (blockIdx.y == 0) params.residual_out[offset + i] = v;
+      const float f = __half2float(v);
+      square = fmaf(f, f, square);
+    }
+    for (int o = 16; o; o >>= 1) square += __shfl_xor_sync(0xffffffffu, square, o);
+    if ((threadIdx.x & 31) == 0) sums[threadIdx.x >> 5] = square;
+    __syncthreads();
+    float total = 0.0f;
+    for (int w = 0; w < 8; ++w) total += sums[w];
+    const float scale = rsqrtf(total / k + params.eps);
+    for (int i = threadIdx.x; i < k; i += 256)
+      row_shared[i] = __hmul(params.weight[i], __float2half_rn(__half2float(row_shared[i]) * scale));
+  }
+  __syncthreads();
+  const bool aligned = job.perm == nullptr || (reinterpret_cast<uintptr_t>(job.perm) & 15) == 0;
+  for (int v = threadIdx.x; v < (k >> 3); v += 256) {
+    __align__(16) __half out[8];
+    if (job.perm == nullptr) {
+      *reinterpret_cast<uint4 *>(out) = reinterpret_cast<const uint4 *>(row_shared)[v];
+    } else {
+      int source[8];
+      if (aligned) {
+        const int4 lo = __ldg(reinterpret_cast<const int4 *>(job.perm) + 2 * v);
+        const int4 hi = __ldg(reinterpret_cast<const int4 *>(job.perm) + 2 * v + 1);
+        source[0] = lo.x; source[1] = lo.y; source[2] = lo.z; source[3] = lo.w;
+        source[4] = hi.x; source[5] = hi.y; source[6] = hi.z; source[7] = hi.w;
+      } else {
+#pragma unroll
+        for (int c = 0; c < 8; ++c) source[c] = __ldg(job.perm + 8 * v + c);
+      }
+#pragma unroll
+      for (int c = 0; c < 8; ++c) out[c] = row_shared[source[c]];
+    }
+    reinterpret_cast<uint4 *>(job.xq + offset)[v] = *reinterpret_cast<const uint4 *>(out);
+  }
 }
 
 // rows <= 16, one or more problems, one launch (plus one small gather launch for each
@@ -166,7 +243,20 @@ int run_skinny(const sageb200_problem *problems, int count, void *workspace,
   SkinnyParams params;
   std::memset(&params, 0, sizeof(params));
   params.status = device.status;
-  if (activation && activation->kind != 0) {  // single-row launches only (checked by the caller)
+  // a fused producer of several rows runs in the staging launch, of one row inside the decode kernel
+  const bool fused_rows = activation && activation->kind != 0 && count > 0 && problems[0].rows > 1;
+  StageParams staging;
+  std::memset(&staging, 0, sizeof(staging));
+  int jobs = 0, stage_rows = 0, stage_k = 0;
+  if (fused_rows) {
+    staging.kind = activation->kind;
+    staging.eps = activation->eps;
+    staging.a = static_cast<const __half *>(activation->a);
+    staging.b = static_cast<const __half *>(activation->b);
+    staging.weight = static_cast<const __half *>(activation->weight);
+    staging.residual_out = static_cast<__half *>(activation->residual_out);
+  }
+  if (activation && activation->kind != 0 && !fused_rows) {  // one row: inside the decode kernel
     params.act_kind = activation->kind;
     params.act_eps = activation->eps;
     params.act_a = activation->a;
@@ -191,7 +281,7 @@ int run_skinny(const sageb200_problem *problems, int count, void *workspace,
     const SkinnyPlan plan =
         plan_skinny(in.rows, in.n, in.k, in.entries, device.sm_count, g_tuning, budgets[i], params.act_kind);
     const size_t partial = plan_bytes(plan);
-    const size_t gathered = gather_bytes(in.rows, in.k, in.perm != nullptr);
+    const size_t gathered = gather_bytes(in.rows, in.k, in.perm != nullptr || fused_rows);
     if (partial || gathered) {
       if (!workspace || offset + partial + gathered > workspace_bytes) return SAGEB200_ERR_WORKSPACE;
       if (reinterpret_cast<uintptr_t>(workspace) & 255) return SAGEB200_ERR_ALIGNMENT;
@@ -201,13 +291,21 @@ int run_skinny(const sageb200_problem *problems, int count, void *workspace,
     out.x = static_cast<const __half *>(in.x);
     out.perm = in.perm;
     if (gathered) {
-      // several activation rows: gather once here instead of once per CTA
+      // several activation rows: staged (and gathered) once, by one launch for all problems,
+      // instead of once per CTA
       __half *xq = reinterpret_cast<__half *>(scratch + offset + partial);
-      if (launch_gather(out.x, in.perm, xq, in.rows, in.k, stream, device.sm_count) != cudaSuccess) {
-        cudaGetLastError();
-        return SAGEB200_ERR_CUDA;
+      if (static_cast<size_t>(in.k) * 2 <= kStageSharedLimit) {
+        staging.job[jobs++] = StageJob{out.x, in.perm, xq, in.rows, in.k};
+        if (in.rows > stage_rows) stage_rows = in.rows;
+        if (in.k > stage_k) stage_k = in.k;
+      } else {  // a row too long for the staging kernel's shared memory (never with a fused producer)
+        if (fused_rows) return SAGEB200_ERR_RANGE;
+        if (launch_gather(out.x, in.perm, xq, in.rows, in.k, stream, device.sm_count) != cudaSuccess) {
+          cudaGetLastError();
+          return SAGEB200_ERR_CUDA;
+        }
+        g_launches.fetch_add(1, std::memory_order_relaxed);
       }
-      g_launches.fetch_add(1, std::memory_order_relaxed);
       out.x = xq;
       out.perm = nullptr;
     }
@@ -257,6 +355,21 @@ int run_skinny(const sageb200_problem *problems, int count, void *workspace,
     ++live;
   }
   if (live == 0) return SAGEB200_OK;
+  if (jobs > 0) {
+    const size_t shared = static_cast<size_t>(stage_k) * sizeof(__half);
+    static bool configured = false;
+    if (shared > 48 * 1024 && !configured) {
+      if (cudaFuncSetAttribute(stage_rows_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize,
+                               static_cast<int>(kStageSharedLimit)) != cudaSuccess) {
+        cudaGetLastError();
+        return SAGEB200_ERR_CUDA;
+      }
+      configured = true;
+    }
+    stage_rows_kernel<<<dim3(stage_rows, jobs), 256, shared, stream>>>(staging);
+    if (cudaGetLastError() != cudaSuccess) return SAGEB200_ERR_CUDA;
+    g_launches.fetch_add(1, std::memory_order_relaxed);
+  }
   params.count = live;
   // floor(2^32 / warps) + 1; unused (and not representable) for a single warp
   params.warps_reciprocal = warps > 1 ? static_cast<unsigned>((1ull << 32) / static_cast<unsigned>(warps)) + 1u : 0u;
@@ -266,40 +379,6 @@ int run_skinny(const sageb200_problem *problems, int count, void *workspace,
   }
   g_launches.fetch_add(1, std::memory_order_relaxed);
   return SAGEB200_OK;
-}
-
-// Activations of several rows for the fused entry point: kind 1 residual add + RMSNorm
-// (also writes the new residual), kind 2 SwiGLU.  One CTA per row.
-__global__ void __launch_bounds__(256)
-    activation_rows_kernel(int kind, const __half *__restrict__ a, const __half *__restrict__ b,
-                           const __half *__restrict__ weight, __half *__restrict__ residual_out,
-                           __half *__restrict__ x, int k, float eps) {
-  extern __shared__ __half row_shared[];
-  __shared__ float sums[8];
-  const size_t offset = static_cast<size_t>(blockIdx.x) * k;
-  if (kind == 2) {
-    for (int i = threadIdx.x; i < k; i += 256) {
-      const float g = __half2float(a[offset + i]);
-      x[offset + i] = __hmul(__float2half_rn(silu_fast(g)), b[offset + i]);
-    }
-    return;
-  }
-  float square = 0.0f;
-  for (int i = threadIdx.x; i < k; i += 256) {
-    const __half v = b ? __hadd(a[offset + i], b[offset + i]) : a[offset + i];
-    row_shared[i] = v;
-    residual_out[offset + i] = v;
-    const float f = __half2float(v);
-    square = fmaf(f, f, square);
-  }
-  for (int o = 16; o; o >>= 1) square += __shfl_xor_sync(0xffffffffu, square, o);
-  if ((threadIdx.x & 31) == 0) sums[threadIdx.x >> 5] = square;
-  __syncthreads();
-  float total = 0.0f;
-  for (int w = 0; w < 8; ++w) total += sums[w];
-  const float scale = rsqrtf(total / k + eps);
-  for (int i = threadIdx.x; i < k; i += 256)
-    x[offset + i] = __hmul(weight[i], __float2half_rn(__half2float(row_shared[i]) * scale));
 }
 
 int validate_problem(const sageb200_problem &p) {
@@ -590,21 +669,12 @@ int sageb200_linear_grouped_fused(const sageb200_problem *problems_host, int cou
   const int status = device_state(&device);
   if (status) return status;
   cudaStream_t s = static_cast<cudaStream_t>(stream);
-  if (rows == 1) return run_skinny(local, count, workspace, workspace_bytes, s, *device, activation);
-  // several rows: one small kernel materialises the activations, then the plain path
-  const size_t staged = align256(static_cast<size_t>(rows) * k * 2);
-  const size_t need = sageb200_fused_workspace_bytes(problems_host, count);
-  if (!workspace || workspace_bytes < need) return SAGEB200_ERR_WORKSPACE;
-  if (reinterpret_cast<uintptr_t>(workspace) & 255) return SAGEB200_ERR_ALIGNMENT;
-  __half *x = reinterpret_cast<__half *>(static_cast<unsigned char *>(workspace) + need - staged);
-  activation_rows_kernel<<<rows, 256, static_cast<size_t>(k) * sizeof(__half), s>>>(
-      activation->kind, static_cast<const __half *>(activation->a), static_cast<const __half *>(activation->b),
-      static_cast<const __half *>(activation->weight), static_cast<__half *>(activation->residual_out), x, k,
-      activation->eps);
-  if (cudaGetLastError() != cudaSuccess) return SAGEB200_ERR_CUDA;
-  g_launches.fetch_add(1, std::memory_order_relaxed);
-  for (int i = 0; i < count; ++i) local[i].x = x;
-  return run_skinny(local, count, workspace, need - staged, s, *device);
+  if (rows > 1) {  // the staging launch computes the producer's rows; it needs the workspace
+    const size_t need = sageb200_fused_workspace_bytes(problems_host, count);
+    if (!workspace || workspace_bytes < need) return SAGEB200_ERR_WORKSPACE;
+    if (static_cast<size_t>(k) * 2 > kStageSharedLimit) return SAGEB200_ERR_RANGE;
+  }
+  return run_skinny(local, count, workspace, workspace_bytes, s, *device, activation);
 }
 
 size_t sageb200_experts_workspace_bytes(const sageb200_expert_stack *stacks_host, int stack_count,
