@@ -90,7 +90,8 @@ __device__ __forceinline__ int split_owner(int u, int q, int r) {
 // row, permutation present and 16-byte aligned, K not sliced, no expert indirection, the row fits
 // the linear staging buffer): 1 = fused residual add + RMSNorm, 2 = fused SwiGLU, 3 = plain
 // 16-byte aligned x; 5 = kind 3 for routed experts (the indirection stays); 4 = one activation
-// row and nothing else assumed; 0 = every case.  The special paths are the generic code with those facts
+// row and nothing else assumed; 6 = several rows staged beforehand (no permutation left, aligned x,
+// K not sliced, no expert stack); 0 = every case.  The special paths are the generic code with those facts
 // known at compile time, so the cold instruction stream after the wait is short and contiguous.
 // kRing: the CTA's share streams through per-warp rings (see kRingStages); a separate variant so
 // that the resident-share kernels keep their shorter main loop.
@@ -118,7 +119,11 @@ __global__ void __launch_bounds__(512, 1) sage_skinny_kernel(const __grid_consta
       ++pi;
   }
   SkinnyProblem p = params.problem[pi];
-  if constexpr (kPath == 4) {
+  if constexpr (kPath == 6) {
+    p.slices = 1;  // several rows, staged beforehand: no permutation left, x aligned
+    p.expert_ids = nullptr;
+    p.perm = nullptr;
+  } else if constexpr (kPath == 4) {
     p.rows = 1;  // the only fact kind 4 fixes
   } else if constexpr (kPath == 5) {
     p.rows = 1;  // kind 3 with the expert indirection left in
@@ -301,19 +306,19 @@ __global__ void __launch_bounds__(512, 1) sage_skinny_kernel(const __grid_consta
   //     c. otherwise: gather from global memory, four channels per item
   const int span = group_count * 128;
   const int row_stride = span + 32;  // halves
-  const bool aligned_x = (kPath != 0 && kPath != 4) || (reinterpret_cast<uintptr_t>(p.x) & 15) == 0;
+  const bool aligned_x = (kPath != 0 && kPath != 4) || (reinterpret_cast<uintptr_t>(p.x) & 15) == 0;  // (kind 6: checked on the host)
   const bool perm_aligned = (kPath != 0 && kPath != 4) || (reinterpret_cast<uintptr_t>(p.perm) & 15) == 0;
   const bool linear_gather =
-      (kPath != 0 && kPath != 4) || (p.perm != nullptr && perm_aligned &&
+      (kPath != 0 && kPath != 4 && kPath != 6) || (p.perm != nullptr && perm_aligned &&
                      static_cast<size_t>(p.rows) * p.k * 2 <= static_cast<size_t>(params.lin_bytes));
   // Fused producer (single activation row only): the row is computed here from the
   // producer's inputs instead of being read from p.x:
   //   1  x = weight * fp16((a + b) * rsqrt(mean((a + b)^2) + eps)),  a + b also stored as the
   //      new residual by the launch's first CTA                      (residual add + RMSNorm)
   //   2  x = fp16(silu(a)) * b                                        (SwiGLU)
-  const int fused = (kPath == 0 || kPath == 4) ? params.act_kind : ((kPath == 3 || kPath == 5) ? 0 : kPath);
+  const int fused = (kPath == 0 || kPath == 4) ? params.act_kind : ((kPath == 3 || kPath == 5 || kPath == 6) ? 0 : kPath);
   const bool gather_from_linear = linear_gather || fused != 0;
-  const bool direct_copy = (kPath == 0 || kPath == 4) && p.perm == nullptr && aligned_x && fused == 0;
+  const bool direct_copy = kPath == 6 || ((kPath == 0 || kPath == 4) && p.perm == nullptr && aligned_x && fused == 0);
   constexpr int kItemBatch = 4;  // permutation items (4 channels each) held in registers
   constexpr int kCopyBatch = 4;  // 16-byte activation pieces held in registers
   int4 held[kItemBatch];
@@ -334,7 +339,7 @@ __global__ void __launch_bounds__(512, 1) sage_skinny_kernel(const __grid_consta
   }
   auto load_item = [&](int q) {  // source channels of quantised channels 4q .. 4q+3
     const int channel = group_begin * 128 + 4 * q;
-    if ((kPath == 0 || kPath == 4) && p.perm == nullptr) return make_int4(channel, channel + 1, channel + 2, channel + 3);
+    if ((kPath == 0 || kPath == 4 || kPath == 6) && p.perm == nullptr) return make_int4(channel, channel + 1, channel + 2, channel + 3);
     if (perm_aligned) return __ldg(reinterpret_cast<const int4 *>(p.perm) + (channel >> 2));
     return make_int4(__ldg(p.perm + channel), __ldg(p.perm + channel + 1), __ldg(p.perm + channel + 2),
                      __ldg(p.perm + channel + 3));
@@ -896,6 +901,10 @@ cudaError_t configure_skinny() {
   if (status == cudaSuccess) status = configure_variant<1, true, 4>();
   if (status == cudaSuccess) status = configure_variant<1, false, 5>();
   if (status == cudaSuccess) status = configure_variant<1, true, 5>();
+  if (status == cudaSuccess) status = configure_variant<1, false, 6>();
+  if (status == cudaSuccess) status = configure_variant<1, true, 6>();
+  if (status == cudaSuccess) status = configure_variant<2, false, 6>();
+  if (status == cudaSuccess) status = configure_variant<2, true, 6>();
   return status;
 }
 
@@ -931,6 +940,15 @@ cudaError_t launch_skinny(const SkinnyParams &params, int warps, int column_bloc
   bool single_rows = column_blocks == 1;
   for (int i = 0; i < params.count; ++i) single_rows = single_rows && params.problem[i].rows == 1;
   if (path == 0 && single_rows) path = 4;  // one activation row, everything else as it comes
+  if (path == 0 && params.act_kind == 0) {  // several rows staged beforehand (see kind 6)
+    path = 6;
+    for (int i = 0; i < params.count; ++i) {
+      const SkinnyProblem &q = params.problem[i];
+      if (q.slices != 1 || q.expert_ids != nullptr || q.perm != nullptr ||
+          (reinterpret_cast<uintptr_t>(q.x) & 15) != 0)
+        path = 0;
+    }
+  }
   // debug switch: 0 = generic kernel only, 3 = kinds 1-3 only, 4 = kind 4 for every single-row launch
   const int limit = skinny_path_limit();
   if (limit == 0) path = 0;
@@ -951,9 +969,11 @@ cudaError_t launch_skinny(const SkinnyParams &params, int warps, int column_bloc
       case 3: return low_bits ? SAGE_LAUNCH(1, true, 3) : SAGE_LAUNCH(1, false, 3);
       case 4: return low_bits ? SAGE_LAUNCH(1, true, 4) : SAGE_LAUNCH(1, false, 4);
       case 5: return low_bits ? SAGE_LAUNCH(1, true, 5) : SAGE_LAUNCH(1, false, 5);
+      case 6: return low_bits ? SAGE_LAUNCH(1, true, 6) : SAGE_LAUNCH(1, false, 6);
       default: return low_bits ? SAGE_LAUNCH(1, true, 0) : SAGE_LAUNCH(1, false, 0);
     }
   }
+  if (path == 6) return low_bits ? SAGE_LAUNCH(2, true, 6) : SAGE_LAUNCH(2, false, 6);
   return low_bits ? SAGE_LAUNCH(2, true, 0) : SAGE_LAUNCH(2, false, 0);
 #undef SAGE_LAUNCH
   return cudaGetLastError();
