@@ -224,6 +224,16 @@ int sageb200_linear_host(const void *x_host, const void *codes, const void *radi
 int sageb200_set_tuning(int warps, int slices, int ctas_per_sm, int mode);
 
 /*
+ * How the decode kernel would share out one problem of rows <= 16 on a device of `sm_count` SMs
+ * (debug; pure host arithmetic, callable without a GPU).  act_kind: the producer fused into a
+ * single-row launch (0 none, 1 residual add + RMSNorm, 2 SwiGLU).  fields[8] = CTAs, K slices,
+ * whole-tile mode (0/1), units per ring stage (0: the share is resident in shared memory),
+ * shared-memory unit slots per CTA, warps per CTA, dynamic shared bytes, scratch needed (0/1).
+ * No counterpart in the reference.
+ */
+int sageb200_debug_plan(int rows, int n, int k, int sm_count, int act_kind, int *fields);
+
+/*
  * SPHQuant 64/4 packed linear, y[rows][n] = x[rows][k] . W^T: replaces the reference's
  * sph_gemv_forward_cuda (csrc/sphquant/sph_gemv_cuda.cu:403-469, declared at
  * csrc/sphquant/sph_gemv_cuda.h:5-11).  Row-major buffers: codes int16 [n][k/8] (bits 0-7

@@ -35,6 +35,7 @@ EXPORTED = (
     "sageb200_set_tuning",
     "sageb200_debug_trace",
     "sageb200_set_pdl",
+    "sageb200_debug_plan",
     "sageb200_sph_linear",
     "sageb200_sph_dequant",
     "sageb200_linear_static",
@@ -164,6 +165,8 @@ def load() -> ctypes.CDLL:
     lib.sageb200_sph_linear.argtypes = [vp] * 7 + [ci] * 3 + [vp]
     lib.sageb200_sph_dequant.restype = ci
     lib.sageb200_sph_dequant.argtypes = [vp] * 6 + [ci] * 2 + [vp]
+    lib.sageb200_debug_plan.restype = ci
+    lib.sageb200_debug_plan.argtypes = [ci] * 5 + [ctypes.POINTER(ci)]
     lib.sageb200_set_pdl.restype = ci
     lib.sageb200_set_pdl.argtypes = [ci]
     lib.sageb200_debug_trace.restype = ci

@@ -436,6 +436,21 @@ int sageb200_gemm_splits(int rows, int n, int k, int sm_count) {
   return plan_skinny(planned_rows, n, k, 256, sm_count > 0 ? sm_count : 148, g_tuning).slices;
 }
 
+int sageb200_debug_plan(int rows, int n, int k, int sm_count, int act_kind, int *fields) {
+  if (!fields || n <= 0 || k <= 0 || (k % 128) || rows <= 0 || rows > 16 || act_kind < 0 || act_kind > 2)
+    return SAGEB200_ERR_INVALID_ARGUMENT;
+  const SkinnyPlan plan = plan_skinny(rows, n, k, 256, sm_count > 0 ? sm_count : 148, g_tuning, 0, rows == 1 ? act_kind : 0);
+  fields[0] = plan.ctas;
+  fields[1] = plan.slices;
+  fields[2] = plan.whole_tiles;
+  fields[3] = plan.ring;
+  fields[4] = plan.unit_capacity;
+  fields[5] = plan.warps;
+  fields[6] = static_cast<int>(plan.shared_bytes);
+  fields[7] = plan.needs_scratch ? 1 : 0;
+  return SAGEB200_OK;
+}
+
 size_t sageb200_workspace_bytes(int rows, int n, int k) {
   if (n <= 0 || k <= 0 || (k % 128) || rows <= 0) return 0;
   if (rows >= kGemmMinRows)  // counter region (kept for layout uniformity) + gathered activations

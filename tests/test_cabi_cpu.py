@@ -87,3 +87,44 @@ def test_missing_library_fails_loudly(monkeypatch, tmp_path):
     monkeypatch.setattr(_lib, "LIBRARY", tmp_path / "libsage_b200.so")
     with pytest.raises(RuntimeError, match="no CPU or PyTorch fallback"):
         _lib.load()
+
+
+def _plan(lib, rows, n, k, act_kind=0, sm_count=148):
+    import ctypes
+
+    fields = (ctypes.c_int * 8)()
+    assert lib.sageb200_debug_plan(rows, n, k, sm_count, act_kind, fields) == 0
+    names = ("ctas", "slices", "whole", "ring", "slots", "warps", "shared", "scratch")
+    return dict(zip(names, fields))
+
+
+def test_decode_planner_choices():
+    """Host arithmetic of the decode kernel's work split (no GPU): resident shares for the
+    Qwen3-4B shapes, ring streaming in one resident wave for shares larger than shared memory,
+    K slices only where several rows cannot keep their activations in shared memory."""
+    from sage_b200 import _lib
+
+    lib = _lib.load()
+    assert lib.sageb200_set_tuning(0, 0, 0, 0) == 0
+    for k, n in [(2560, 9728), (2560, 4096), (4096, 2560), (9728, 2560)]:  # Qwen3-4B, one row
+        for kind in (0, 1, 2):
+            plan = _plan(lib, 1, n, k, kind)
+            assert plan["ring"] == 0 and plan["slices"] == 1 and plan["ctas"] <= 148, (k, n, kind, plan)
+            assert plan["shared"] <= 184 * 1024 and plan["slots"] <= 192
+    gate = _plan(lib, 1, 25600, 5120, 1)  # Qwen3-32B gate_proj: 433 units per SM against 192 slots
+    assert gate["ring"] == 4 and gate["ctas"] <= 148 and gate["slices"] == 1 and gate["slots"] == 16 * 3 * 4
+    down = _plan(lib, 1, 5120, 25600, 2)  # K = 25600: unsliced for one row, smaller ring stages
+    assert down["slices"] == 1 and down["ctas"] <= 148 and down["ring"] in (1, 2) and down["shared"] <= 184 * 1024
+    assert lib.sageb200_set_tuning(0, 0, 0, 3) == 0  # rings off: further waves of CTAs instead
+    try:
+        waves = _plan(lib, 1, 25600, 5120, 1)
+        assert waves["ring"] == 0 and waves["ctas"] > 148 and waves["slots"] <= 192
+    finally:
+        assert lib.sageb200_set_tuning(0, 0, 0, 0) == 0
+    rows8 = _plan(lib, 8, 2560, 9728)  # eight rows of K = 9728 do not fit: K is cut into slices
+    assert rows8["slices"] > 1 and rows8["ring"] == 0 and rows8["scratch"] == 1
+    rows16 = _plan(lib, 16, 25600, 5120)  # two column blocks never stream through rings
+    assert rows16["ring"] == 0
+    import ctypes
+
+    assert lib.sageb200_debug_plan(17, 16, 128, 148, 0, (ctypes.c_int * 8)()) == -1
