@@ -140,8 +140,9 @@ typedef struct sageb200_activation {
 /*
  * sageb200_linear_grouped with the activations' producer fused in (all problems share rows
  * and k; problem.x is ignored).  With one row the producer runs inside the decode kernel's
- * activation staging, saving a kernel launch per norm / SwiGLU; with more rows one small
- * kernel materialises the activations first.  Workspace: sageb200_fused_workspace_bytes.
+ * activation staging, saving a kernel launch per norm / SwiGLU; with more rows one staging
+ * launch computes the rows and writes them once per problem in that problem's channel order
+ * (rows of up to 49152 channels).  Workspace: sageb200_fused_workspace_bytes.
  * No counterpart in the reference, where these are separate Hugging Face modules.
  */
 size_t sageb200_fused_workspace_bytes(const sageb200_problem *problems_host, int count);
