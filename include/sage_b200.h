@@ -225,16 +225,6 @@ int sageb200_linear_host(const void *x_host, const void *codes, const void *radi
 int sageb200_set_tuning(int warps, int slices, int ctas_per_sm, int mode);
 
 /*
- * How the decode kernel would share out one problem of rows <= 16 on a device of `sm_count` SMs
- * (debug; pure host arithmetic, callable without a GPU).  act_kind: the producer fused into a
- * single-row launch (0 none, 1 residual add + RMSNorm, 2 SwiGLU).  fields[8] = CTAs, K slices,
- * whole-tile mode (0/1), units per ring stage (0: the share is resident in shared memory),
- * shared-memory unit slots per CTA, warps per CTA, dynamic shared bytes, scratch needed (0/1).
- * No counterpart in the reference.
- */
-int sageb200_debug_plan(int rows, int n, int k, int sm_count, int act_kind, int *fields);
-
-/*
  * SPHQuant 64/4 packed linear, y[rows][n] = x[rows][k] . W^T: replaces the reference's
  * sph_gemv_forward_cuda (csrc/sphquant/sph_gemv_cuda.cu:403-469, declared at
  * csrc/sphquant/sph_gemv_cuda.h:5-11).  Row-major buffers: codes int16 [n][k/8] (bits 0-7
@@ -256,26 +246,6 @@ int sageb200_sph_dequant(const void *codes, const void *extra, const void *scale
                          const void *book, void *w, int n, int k, void *stream);
 
 /*
- * Programmatic dependent launch (on by default): the decode kernel and the decode glue are
- * launched so that they may be scheduled before the previous kernel of the stream has
- * finished; they prefetch packed weights and codebooks, then wait for the previous kernel
- * before reading activations or writing anything.  0 switches to plain launches (debug).
- * No counterpart in the reference.
- */
-int sageb200_set_pdl(int enabled);
-
-/*
- * Profiling aid (debug): while `device_buffer` is non-NULL every CTA of the decode kernel
- * writes 16 readings at device_buffer[(512*launch + cta)*16 ...]: SM clocks at the phases of
- * its work ([0..12], [14] = after the wait for the previous kernel) and the global
- * nanosecond timer at its start [13] and end [15].  `launch` counts the decode-kernel launches
- * since this call and stops at 63; the buffer holds 64*512*16*8 bytes (one launch only:
- * 512*16*8).  NULL switches it off.
- * No counterpart in the reference.
- */
-int sageb200_debug_trace(void *device_buffer);
-
-/*
  * Allocation-free form of sageb200_linear for the decode range (rows <= 16).
  *
  * For callers that cannot provide a workspace because they are not in a position to
@@ -289,8 +259,9 @@ int sageb200_debug_trace(void *device_buffer);
  *   - Shapes whose sageb200_workspace_bytes(rows, n, k) exceeds that size, and rows > 16,
  *     are refused with SAGEB200_ERR_STATIC_SCRATCH; nothing is launched.
  *   - It calls no cudaMalloc, cudaFree or any other allocating routine.  The first call on
- *     each device looks up the array's device address (a one-off set-up step that may load
- *     the library's device code): make that first call outside any stream capture.
+ *     each device looks up the array's device address and pins the library's static status
+ *     word (a one-off set-up step that may load the library's device code): make that first
+ *     call outside any stream capture.
  *   - All calls on a device share the one array.  Each call re-zeroes the arrival counters
  *     on `stream` before it launches, so calls ordered on one stream are safe; calls that
  *     can overlap on the GPU (different streams, different threads) race on the array and
@@ -303,6 +274,15 @@ int sageb200_debug_trace(void *device_buffer);
 int sageb200_linear_static(const void *x, const void *codes, const void *radii, const void *grid,
                            const void *book, const int32_t *perm, void *y, int rows, int n, int k,
                            int entries, void *stream);
+
+/*
+ * Every device-side wait of the library is bounded; when one runs out, the kernel records
+ * SAGEB200_ERR_TIMEOUT in a status word of the current device and every later call on that
+ * device returns SAGEB200_ERR_TIMEOUT without launching, until this function clears the
+ * record.  Call it once the stream that reported the time-out is idle (the outputs of the
+ * call that timed out are undefined).  No counterpart in the reference (its kernels never wait).
+ */
+int sageb200_clear_status(void);
 
 /* Number of kernels this library has launched in this process (all entry points). */
 unsigned long long sageb200_launch_count(void);

@@ -22,9 +22,10 @@
 extern "C" {
 #endif
 
-/* h[rows][hidden] = table[tokens[row]][:]; tokens are int64. */
+/* h[rows][hidden] = table[tokens[row]][:]; tokens are int64.  An id outside [0, vocab) reads
+ * row 0 (never memory beyond the table). */
 int sageb200_glue_embed(const void *table, const void *tokens, void *h, int rows, int hidden,
-                        void *stream);
+                        int vocab, void *stream);
 
 /* residual += delta (skipped when delta is NULL); x = weight * rmsnorm(residual, eps). */
 int sageb200_glue_add_rmsnorm(void *residual, const void *delta, const void *weight, void *x,

@@ -33,14 +33,19 @@ EXPORTED = (
     "sageb200_host_staging_bytes",
     "sageb200_linear_host",
     "sageb200_set_tuning",
-    "sageb200_debug_trace",
-    "sageb200_set_pdl",
-    "sageb200_debug_plan",
     "sageb200_sph_linear",
     "sageb200_sph_dequant",
     "sageb200_linear_static",
+    "sageb200_clear_status",
     "sageb200_launch_count",
     "sageb200_glue_launch_count",
+)
+
+# every symbol include/sage_b200_debug.h declares (tuning and profiling aids)
+EXPORTED_DEBUG = (
+    "sageb200_debug_plan",
+    "sageb200_set_pdl",
+    "sageb200_debug_trace",
 )
 
 
@@ -167,6 +172,8 @@ def load() -> ctypes.CDLL:
     lib.sageb200_sph_dequant.argtypes = [vp] * 6 + [ci] * 2 + [vp]
     lib.sageb200_debug_plan.restype = ci
     lib.sageb200_debug_plan.argtypes = [ci] * 5 + [ctypes.POINTER(ci)]
+    lib.sageb200_clear_status.restype = ci
+    lib.sageb200_clear_status.argtypes = []
     lib.sageb200_set_pdl.restype = ci
     lib.sageb200_set_pdl.argtypes = [ci]
     lib.sageb200_debug_trace.restype = ci
@@ -178,7 +185,7 @@ def load() -> ctypes.CDLL:
     # decode glue (include/sage_b200_decode.h)
     fl, ll = ctypes.c_float, ctypes.c_longlong
     lib.sageb200_glue_embed.restype = ci
-    lib.sageb200_glue_embed.argtypes = [vp, vp, vp, ci, ci, vp]
+    lib.sageb200_glue_embed.argtypes = [vp, vp, vp, ci, ci, ci, vp]
     lib.sageb200_glue_add_rmsnorm.restype = ci
     lib.sageb200_glue_add_rmsnorm.argtypes = [vp, vp, vp, vp, ci, ci, fl, vp]
     lib.sageb200_glue_qk_norm_rope_cache.restype = ci

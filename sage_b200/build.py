@@ -53,11 +53,14 @@ def is_stale() -> bool:
     return any(path.stat().st_mtime > built for path in inputs)
 
 
-def build(force: bool = False, verbose: bool = False) -> pathlib.Path:
-    """Compile every .cu under csrc/ into one shared library; returns its path."""
-    if not force and not is_stale():
+def build(force: bool = False, verbose: bool = False, trace: bool = False) -> pathlib.Path:
+    """Compile every .cu under csrc/ into one shared library; returns its path.  `trace` adds
+    -DSAGEB200_TRACE: the decode kernel's phase clocks (sageb200_debug_trace) and the
+    SAGEB200_PATHS switch, both compiled out of the default build."""
+    if not force and not trace and not is_stale():
         return LIBRARY
-    command = [_nvcc(), *NVCC_FLAGS, f"-I{INCLUDE}", "-o", str(LIBRARY), *map(str, sources())]
+    flags = NVCC_FLAGS + (["-DSAGEB200_TRACE"] if trace else [])
+    command = [_nvcc(), *flags, f"-I{INCLUDE}", "-o", str(LIBRARY), *map(str, sources())]
     result = subprocess.run(command, capture_output=True, text=True)
     if verbose or result.returncode:
         sys.stderr.write(" ".join(command) + "\n" + result.stdout + result.stderr)
@@ -71,5 +74,6 @@ if __name__ == "__main__":
     parser = argparse.ArgumentParser()
     parser.add_argument("--force", action="store_true")
     parser.add_argument("--verbose", action="store_true")
+    parser.add_argument("--trace", action="store_true", help="profiling build (-DSAGEB200_TRACE)")
     args = parser.parse_args()
-    print(build(force=args.force, verbose=args.verbose))
+    print(build(force=args.force, verbose=args.verbose, trace=args.trace))

@@ -47,15 +47,19 @@ __device__ float block_sum(float v, float *scratch) {
 }
 
 // h[m][:] = embedding[token[m]][:]
+// A token id outside [0, vocab) (a corrupted id, or the "no candidate" value of an argmax over a
+// row of NaNs) reads row 0 instead of memory far beyond the table.
 __global__ void embed_kernel(const __half *__restrict__ table, const long long *__restrict__ tokens,
-                             __half *__restrict__ h, int hidden) {
+                             __half *__restrict__ h, int hidden, int vocab) {
   // programmatic dependent launch: let the next kernel be scheduled, then wait for the
   // previous one before touching memory
   sageb200::pdl_launch_dependents();
   sageb200::pdl_wait();
 
   const int m = blockIdx.x;
-  const __half *row = table + static_cast<size_t>(tokens[m]) * hidden;
+  long long token = tokens[m];
+  if (token < 0 || token >= vocab) token = 0;
+  const __half *row = table + static_cast<size_t>(token) * hidden;
   for (int i = threadIdx.x; i < hidden / 8; i += blockDim.x)
     reinterpret_cast<uint4 *>(h + static_cast<size_t>(m) * hidden)[i] =
         reinterpret_cast<const uint4 *>(row)[i];
@@ -745,6 +749,7 @@ __global__ void __launch_bounds__(kHeadWarps * 32)
           value = best_value[w][0];
           index = best_index[w][0];
         }
+      if (index == 0x7fffffff) index = 0;  // a row without a single ordered value (all NaN)
       tokens[m] = index;
       if (log && step && step[0] < log_stride) log[static_cast<size_t>(m) * log_stride + step[0]] = index;
       positions[m] += 1;
@@ -932,6 +937,7 @@ __global__ void __launch_bounds__(1024)
         value = best_value[w];
         index = best_index[w];
       }
+    if (index == 0x7fffffff) index = 0;  // a row without a single ordered value (all NaN)
     tokens[m] = index;
     if (log && step[0] < log_stride) log[static_cast<size_t>(m) * log_stride + step[0]] = index;
     positions[m] += 1;
@@ -952,11 +958,11 @@ int launch_status() { return cudaGetLastError() == cudaSuccess ? 0 : -5; }
 extern "C" {
 
 int sageb200_glue_embed(const void *table, const void *tokens, void *h, int rows, int hidden,
-                        void *stream) {
-  if (hidden % 8) return -1;
+                        int vocab, void *stream) {
+  if (hidden % 8 || vocab <= 0) return -1;
   sageb200::launch_dependent<2>(embed_kernel, rows, 128, 0, static_cast<cudaStream_t>(stream),
       static_cast<const __half *>(table), static_cast<const long long *>(tokens),
-      static_cast<__half *>(h), hidden);
+      static_cast<__half *>(h), hidden, vocab);
   return launch_status();
 }
 

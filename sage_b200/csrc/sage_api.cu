@@ -5,10 +5,12 @@
 // 64/128/256-entry codebook, 4-byte aligned grid and codebook, rows <= 65535.
 // Errors come back as negative status codes instead of C++ exceptions.
 #include "../../include/sage_b200.h"
+#include "../../include/sage_b200_debug.h"
 
 #include <atomic>
 #include <climits>
 #include <cstring>
+#include <mutex>
 
 #include "sage_common.cuh"
 #include "sage_kernels.h"
@@ -25,8 +27,20 @@ struct DeviceState {
   std::atomic<int> ready{0};
   int sm_count = 0;
   int major = 0;
-  int *status = nullptr;  // pinned, device-mapped word the kernels write on a timed-out wait
+  int *status = nullptr;       // device-visible address of the word the kernels write on a timed-out wait
+  volatile int *status_host = nullptr;  // the same word as the host reads it
 };
+
+// One page of host memory per device for the status word.  It is static storage pinned and
+// mapped with cudaHostRegister at set-up, so that no entry point of the library allocates
+// memory; only where the platform refuses to pin static storage does set-up fall back to
+// one pinned word from cudaHostAlloc.
+struct alignas(4096) StatusPage {
+  int word;
+  char pad[4096 - sizeof(int)];
+};
+StatusPage g_status_pages[64];
+std::mutex g_setup_mutex;  // first-time set-up of a device may be raced by several host threads
 
 // Activation rows from which the tcgen05 prefill GEMM takes over from 16-row skinny passes.
 constexpr int kGemmMinRows = 33;
@@ -38,6 +52,9 @@ int g_trace_launch = 0;        // launches traced since the buffer was set
 
 size_t align256(size_t bytes) { return (bytes + 255) / 256 * 256; }
 
+constexpr size_t kStageSharedLimit = 96 * 1024;  // rows up to 49152 channels
+cudaError_t configure_stage_rows();  // (defined after the kernel)
+
 // Per-device one-time set-up on the calling thread's current device.
 int device_state(DeviceState **out) {
   int device = 0;
@@ -48,31 +65,48 @@ int device_state(DeviceState **out) {
   if (device < 0 || device >= kMaxDevices) return SAGEB200_ERR_NO_DEVICE;
   DeviceState &state = g_devices[device];
   if (!state.ready.load(std::memory_order_acquire)) {
-    int sms = 0, major = 0;
-    if (cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, device) != cudaSuccess ||
-        cudaDeviceGetAttribute(&major, cudaDevAttrComputeCapabilityMajor, device) != cudaSuccess) {
-      cudaGetLastError();
-      return SAGEB200_ERR_CUDA;
+    std::lock_guard<std::mutex> lock(g_setup_mutex);
+    if (!state.ready.load(std::memory_order_acquire)) {
+      int sms = 0, major = 0;
+      if (cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, device) != cudaSuccess ||
+          cudaDeviceGetAttribute(&major, cudaDevAttrComputeCapabilityMajor, device) != cudaSuccess) {
+        cudaGetLastError();
+        return SAGEB200_ERR_CUDA;
+      }
+      if (major != 10) return SAGEB200_ERR_NO_DEVICE;  // built for sm_100a only
+      if (configure_skinny() != cudaSuccess || configure_gemm_tc() != cudaSuccess ||
+          configure_stage_rows() != cudaSuccess) {
+        cudaGetLastError();
+        return SAGEB200_ERR_CUDA;
+      }
+      // the status word: this device's static page, pinned and mapped in place
+      StatusPage &page = g_status_pages[device];
+      page.word = 0;
+      void *device_view = nullptr;
+      if (cudaHostRegister(&page, sizeof(page), cudaHostRegisterMapped | cudaHostRegisterPortable) == cudaSuccess &&
+          cudaHostGetDevicePointer(&device_view, &page.word, 0) == cudaSuccess && device_view) {
+        state.status = static_cast<int *>(device_view);
+        state.status_host = &page.word;
+      } else {
+        cudaGetLastError();
+        int *word = nullptr;
+        if (cudaHostAlloc(reinterpret_cast<void **>(&word), sizeof(int), cudaHostAllocMapped) != cudaSuccess) {
+          cudaGetLastError();
+          return SAGEB200_ERR_CUDA;
+        }
+        *word = 0;
+        state.status = word;
+        state.status_host = word;
+      }
+      state.sm_count = sms;
+      state.major = major;
+      state.ready.store(1, std::memory_order_release);
     }
-    if (major != 10) return SAGEB200_ERR_NO_DEVICE;  // built for sm_100a only
-    if (configure_skinny() != cudaSuccess || configure_gemm_tc() != cudaSuccess) {
-      cudaGetLastError();
-      return SAGEB200_ERR_CUDA;
-    }
-    // one word of pinned host memory per device, allocated once at set-up
-    if (cudaHostAlloc(reinterpret_cast<void **>(&state.status), sizeof(int), cudaHostAllocMapped) !=
-        cudaSuccess) {
-      cudaGetLastError();
-      return SAGEB200_ERR_CUDA;
-    }
-    *state.status = 0;
-    state.sm_count = sms;
-    state.major = major;
-    state.ready.store(1, std::memory_order_release);
   }
   *out = &state;
   // a kernel of an earlier call reported a timed-out wait
-  if (*static_cast<volatile int *>(state.status) != 0) return SAGEB200_ERR_TIMEOUT;
+  // (it stays recorded until sageb200_clear_status)
+  if (*state.status_host != 0) return SAGEB200_ERR_TIMEOUT;
   return SAGEB200_OK;
 }
 
@@ -169,7 +203,6 @@ struct StageParams {
   const __half *a, *b, *weight;
   __half *residual_out;
 };
-constexpr size_t kStageSharedLimit = 96 * 1024;  // rows up to 49152 channels
 
 __global__ void __launch_bounds__(256) stage_rows_kernel(const __grid_constant__ StageParams params) {
   extern __shared__ __half row_shared[];
@@ -226,6 +259,11 @@ __global__ void __launch_bounds__(256) stage_rows_kernel(const __grid_constant__
     }
     reinterpret_cast<uint4 *>(job.xq + offset)[v] = *reinterpret_cast<const uint4 *>(out);
   }
+}
+
+cudaError_t configure_stage_rows() {
+  return cudaFuncSetAttribute(stage_rows_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize,
+                              static_cast<int>(kStageSharedLimit));
 }
 
 // rows <= 16, one or more problems, one launch (plus one small gather launch for each
@@ -356,16 +394,7 @@ int run_skinny(const sageb200_problem *problems, int count, void *workspace,
   }
   if (live == 0) return SAGEB200_OK;
   if (jobs > 0) {
-    const size_t shared = static_cast<size_t>(stage_k) * sizeof(__half);
-    static bool configured = false;
-    if (shared > 48 * 1024 && !configured) {
-      if (cudaFuncSetAttribute(stage_rows_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize,
-                               static_cast<int>(kStageSharedLimit)) != cudaSuccess) {
-        cudaGetLastError();
-        return SAGEB200_ERR_CUDA;
-      }
-      configured = true;
-    }
+    const size_t shared = static_cast<size_t>(stage_k) * sizeof(__half);  // (limit raised per device at set-up)
     stage_rows_kernel<<<dim3(stage_rows, jobs), 256, shared, stream>>>(staging);
     if (cudaGetLastError() != cudaSuccess) return SAGEB200_ERR_CUDA;
     g_launches.fetch_add(1, std::memory_order_relaxed);
@@ -409,8 +438,8 @@ const char *sageb200_status_string(int status) {
       return "invalid argument: SAGE requires positive N, K divisible by 128, a codebook of "
              "64/128/256 entries and non-null buffers";
     case SAGEB200_ERR_ALIGNMENT:
-      return "alignment: SAGE grid and codebook require 4-byte aligned storage (codes 8, "
-             "workspace 256, dense weight output 16)";
+      return "alignment: SAGE codebook requires 4-byte aligned storage (packed codes, radius "
+             "codes, radius grid and dense weight output 16, workspace 256)";
     case SAGEB200_ERR_RANGE: return "SAGE launch dimensions exceed supported range";
     case SAGEB200_ERR_WORKSPACE: return "workspace missing or smaller than sageb200_workspace_bytes";
     case SAGEB200_ERR_CUDA: return "a CUDA call or kernel launch failed";
@@ -608,6 +637,15 @@ int sageb200_linear_host(const void *x_host, const void *codes, const void *radi
     cudaGetLastError();
     return SAGEB200_ERR_CUDA;
   }
+  return SAGEB200_OK;
+}
+
+int sageb200_clear_status(void) {
+  DeviceState *device = nullptr;
+  const int status = device_state(&device);
+  if (status != SAGEB200_OK && status != SAGEB200_ERR_TIMEOUT) return status;
+  // the caller has dealt with the time-out (the stream that reported it must be idle)
+  *device->status_host = 0;
   return SAGEB200_OK;
 }
 

@@ -108,10 +108,18 @@ __global__ void __launch_bounds__(512, 1) sage_skinny_kernel(const __grid_consta
   __shared__ unsigned char tile_warp_lo[kMaxWholeTiles];  // first and last warp holding a
   __shared__ unsigned char tile_warp_hi[kMaxWholeTiles];  // piece of the CTA's tile
 
+  // Phase clocks for profiling exist only in a build with -DSAGEB200_TRACE (python -m
+  // sage_b200.build --trace); the default build compiles every stamp out.
+#ifdef SAGEB200_TRACE
   long long *trace = params.trace ? params.trace + 16 * static_cast<size_t>(blockIdx.x) : nullptr;
 #define SAGE_STAMP(i) do { if (trace && threadIdx.x == 0) trace[i] = clock64(); } while (0)
+#define SAGE_STAMP_NS(i) do { if (trace && threadIdx.x == 0) trace[i] = global_nanoseconds(); } while (0)
+#else
+#define SAGE_STAMP(i) do { } while (0)
+#define SAGE_STAMP_NS(i) do { } while (0)
+#endif
   SAGE_STAMP(0);
-  if (trace && threadIdx.x == 0) trace[13] = global_nanoseconds();
+  SAGE_STAMP_NS(13);
   pdl_launch_dependents();  // the next kernel may be scheduled as SM resources free up
   int pi = 0;
   if (params.count > 1) {
@@ -679,7 +687,7 @@ __global__ void __launch_bounds__(512, 1) sage_skinny_kernel(const __grid_consta
     }
   }
   SAGE_STAMP(8);
-  if (trace && threadIdx.x == 0) trace[15] = global_nanoseconds();
+  SAGE_STAMP_NS(15);
   if (!any_split) return;
 
   // ---- 8. tiles shared with other CTAs: publish, count arrivals, the last one finishes.
@@ -714,8 +722,9 @@ __global__ void __launch_bounds__(512, 1) sage_skinny_kernel(const __grid_consta
   for (int ti = tid; ti < cta_tiles; ti += threads)
     if (tile_last[ti]) p.counters[cta_first_tile + ti] = 0u;
   SAGE_STAMP(10);
-  if (trace && threadIdx.x == 0) trace[15] = global_nanoseconds();
+  SAGE_STAMP_NS(15);
 #undef SAGE_STAMP
+#undef SAGE_STAMP_NS
 }
 
 template <int NB, bool kLowBits, int kPath = 0>
@@ -908,13 +917,18 @@ cudaError_t configure_skinny() {
   return status;
 }
 
-// debug: environment SAGEB200_PATHS=0 keeps every launch on the generic kernel (A/B timing)
+// Only in a -DSAGEB200_TRACE build: environment SAGEB200_PATHS=0 keeps every launch on the
+// generic kernel (A/B timing); the default build always takes the specialised kernels.
 int skinny_path_limit() {
+#ifdef SAGEB200_TRACE
   static const int limit = [] {
     const char *text = getenv("SAGEB200_PATHS");
     return text ? atoi(text) : -1;
   }();
   return limit;
+#else
+  return -1;
+#endif
 }
 
 cudaError_t launch_skinny(const SkinnyParams &params, int warps, int column_blocks, int total_ctas,

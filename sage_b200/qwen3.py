@@ -336,7 +336,7 @@ class PackedQwen3:
     def _body(self):
         c, lib, b = self.config, self.lib, self.batch
         s = self._stream()
-        self._check(lib.sageb200_glue_embed(_vp(self.embed), _vp(self.tokens), _vp(self.h), b, c.hidden, s), "embed")
+        self._check(lib.sageb200_glue_embed(_vp(self.embed), _vp(self.tokens), _vp(self.h), b, c.hidden, c.vocab, s), "embed")
         delta = None
         for layer in self.layers:
             delta = self._layer(layer, delta)
@@ -427,6 +427,12 @@ class PackedQwen3:
         one position at a time through the decode graph."""
         if self.graph is None:
             self.capture()
+        if prompt.dim() != 2 or prompt.shape[0] != self.batch:
+            raise ValueError("prompt must be [batch, length]")
+        if prompt.shape[1] < 1 or prompt.shape[1] > self.max_seq:
+            raise ValueError(f"prompt length {prompt.shape[1]} does not fit the cache of {self.max_seq} positions")
+        if int(prompt.min()) < 0 or int(prompt.max()) >= self.config.vocab:
+            raise ValueError("prompt token ids must lie in [0, vocab)")
         self.reset()
         prompt = prompt.to(self.device)
         length = prompt.shape[1]
@@ -457,7 +463,7 @@ class PackedQwen3:
             h = torch.empty(rows, c.hidden, **half)
             x = torch.empty_like(h)
             attn = torch.empty(rows, self.heads * c.head_dim, **half)
-            self._check(lib.sageb200_glue_embed(_vp(self.embed), _vp(tokens), _vp(h), rows, c.hidden, s), "embed")
+            self._check(lib.sageb200_glue_embed(_vp(self.embed), _vp(tokens), _vp(h), rows, c.hidden, c.vocab, s), "embed")
             delta = None
             for layer in self.layers:
                 self._check(lib.sageb200_glue_add_rmsnorm(_vp(h), _vp(delta), _vp(layer["input_norm"]), _vp(x), rows,
@@ -487,6 +493,9 @@ class PackedQwen3:
         """Greedy generation; returns [batch, new_tokens] token ids (device tensor)."""
         if new_tokens > self.max_new:
             raise ValueError("new_tokens exceeds max_new")
+        if prompt.shape[1] + new_tokens - 1 > self.max_seq:
+            raise ValueError(f"prompt ({prompt.shape[1]}) + new tokens ({new_tokens}) exceed the cache of "
+                             f"{self.max_seq} positions")
         self.prefill(prompt)  # logs token 0
         for _ in range(new_tokens - 1):
             self.graph.replay()

@@ -22,6 +22,7 @@ from __future__ import annotations
 import argparse
 import hashlib
 import json
+import os
 import pathlib
 import sys
 
@@ -58,7 +59,11 @@ def sha(array: np.ndarray) -> str:
 
 def main() -> None:
     parser = argparse.ArgumentParser()
-    parser.add_argument("--reference", default="/root/reference")
+    parser.add_argument(
+        "--reference",
+        default=os.environ.get("SAGE_REFERENCE_DIR", str(pathlib.Path(__file__).resolve().parents[3] / "reference")),
+        help="checkout of the reference project (default: $SAGE_REFERENCE_DIR, else ../reference beside this repository)",
+    )
     args = parser.parse_args()
     sys.path.insert(0, args.reference)
     from tests.inference.reference import decode_sage, unpack_sage  # type: ignore

@@ -41,6 +41,13 @@ def test_decode_header_symbols_are_exported(lib):
         assert hasattr(lib, name), name
 
 
+def test_debug_header_symbols_are_exported(lib):
+    names = declared_symbols("sage_b200_debug.h")
+    assert set(names) == set(_lib.EXPORTED_DEBUG)
+    for name in names:
+        assert hasattr(lib, name), name
+
+
 def test_version_and_status_strings(lib):
     assert lib.sageb200_version() >= 100
     assert lib.sageb200_status_string(0) == b"ok"

@@ -84,14 +84,17 @@ def lockstep(config, steps, prompt_length, seed, max_seq):
     return mismatches, worst_logit_error
 
 
-def check_lockstep(mismatches, worst_logit_error, steps):
+def check_lockstep(mismatches, worst_logit_error, steps, allowed=0):
+    """`allowed` = how many near-tie flips the case may show.  The contract is identical greedy
+    tokens; the measured count on the fixed seeds below is zero, so zero is what is asserted.
+    Random-init logits over a large vocabulary can put the top two within a few FP16 steps of
+    each other, which is the only disagreement a case may declare (never silently): the flip
+    must then be a near tie (2 % of the logit spread) in the ORACLE's own logits."""
     # logits of the packed model stay within the matmul gate's order of magnitude of the oracle's
     assert worst_logit_error < 2e-2, worst_logit_error
-    # any disagreement must be a near tie in the ORACLE's own logits (random-init logits over a
-    # 150k vocabulary have top-2 gaps of a few FP16 ulps now and then)
     for step, ours, oracle, margin, spread in mismatches:
         assert 0 <= margin <= 0.02 * spread, (step, ours, oracle, margin, spread)
-    assert len(mismatches) <= max(2, steps // 32), mismatches
+    assert len(mismatches) <= allowed, mismatches
 
 
 def test_greedy_tokens_small_model():
@@ -101,10 +104,38 @@ def test_greedy_tokens_small_model():
 
 
 def test_greedy_tokens_qwen3_4b_256_steps():
-    """Full Qwen3-4B shape, 256 greedy steps after a 32-token prompt."""
+    """Full Qwen3-4B shape, 256 greedy steps after a 32-token prompt: identical tokens."""
     mismatches, error = lockstep(QWEN3_4B, steps=256, prompt_length=32, seed=0, max_seq=320)
     print("qwen3-4b lockstep: mismatches", mismatches, "worst relative logit error", error)
     check_lockstep(mismatches, error, 256)
+
+
+def test_greedy_tokens_qwen3_4b_after_batched_512_token_prompt():
+    """The benchmark's configuration: a 512-token prompt through the batched prompt pass (packed
+    linears on the tensor-core GEMM path, causal attention over the prompt), then 256 greedy
+    steps; the dense oracle model takes the same route with FP16 matmuls on the dequantised
+    weights and supplies the tokens both models are fed."""
+    steps, length = 256, 512
+    sage = PackedQwen3(QWEN3_4B, "cuda", seed=0, max_seq=length + steps + 8, linear="sage", max_new=steps + 1)
+    dense = PackedQwen3(QWEN3_4B, "cuda", seed=0, max_seq=length + steps + 8, linear="dense", max_new=steps + 1)
+    prompt = torch.randint(3, QWEN3_4B.vocab, (1, length), generator=torch.Generator().manual_seed(11))
+    mismatches, worst = [], 0.0
+    for model in (sage, dense):
+        model.capture()
+        model.prefill(prompt, batched=True)
+    for i in range(steps):
+        if i > 0:
+            for model in (sage, dense):
+                model.tokens.copy_(token)
+                model.graph.replay()
+        want, got = dense.logits[0].float(), sage.logits[0].float()
+        worst = max(worst, ((got - want).norm() / want.norm()).item())
+        ours, oracle = int(sage.tokens), int(dense.tokens)
+        if ours != oracle:
+            mismatches.append((i, ours, oracle, (want[oracle] - want[ours]).item(), want.std().item()))
+        token = dense.tokens.clone()
+    print("qwen3-4b after a batched 512-token prompt: mismatches", mismatches, "worst logit error", worst)
+    check_lockstep(mismatches, worst, steps)
 
 
 def test_generate_is_repeatable_and_batched():

@@ -480,3 +480,66 @@ def test_shares_larger_than_shared_memory_stream_through_rings(k, n, rows):
         (fused,) = sage_grouped(problem(gate), [n], (1, 1e-6, gate, up, norm_weight, new_residual))
         assert torch.equal(new_residual, h)
         assert ((fused.float() - plain.float()).norm() / plain.float().norm()).item() < 1e-3
+
+
+# ---------------------------------------------------------------- tcgen05 GEMM on real grids
+
+
+def _gemm_case(k, n, rows, seed, permuted, bits=None):
+    kwargs = {} if bits is None else {"direction_bits": bits}
+    cpu = synthetic_sage(k, n, seed=seed, permuted=permuted, **kwargs)
+    layer = SAGELinear(to_cuda(cpu), n)
+    x = torch.randn(rows, k, generator=torch.Generator().manual_seed(rows + n), dtype=torch.float16).cuda()
+    return cpu, layer, x
+
+
+@pytest.mark.parametrize("rows", [33, 257, 300, 513])
+@pytest.mark.parametrize("k,n", [(256, 129), (640, 1025), (2560, 1024), (1280, 2560)])
+@pytest.mark.parametrize("permuted", [False, True])
+def test_gemm_multi_cta_grids_against_oracle(rows, k, n, permuted):
+    """The tensor-core path on grids of several 128-row blocks and several token blocks
+    (rows > 256), N not a multiple of 128 and rows not a multiple of 16, against the C
+    oracle's FP16 weights."""
+    cpu, layer, x = _gemm_case(k, n, rows, seed=rows % 3, permuted=permuted)
+    assert_output(layer(x), expected_output(x, cpu, n))
+
+
+@pytest.mark.parametrize("bits", [6, 7, 8])
+@pytest.mark.parametrize("k,n", [(2560, 9728), (9728, 2560), (4096, 2560), (2560, 1024)])
+def test_gemm_qwen3_4b_shapes_against_oracle(k, n, bits):
+    """Prompt-sized row counts on the Qwen3-4B shapes, every bit split, against the oracle."""
+    cpu = synthetic_sage(k, n, seed=200 + bits, permuted=True, direction_bits=bits)
+    layer = SAGELinear(to_cuda(cpu), n)
+    weight = torch.from_numpy(c_oracle.decode_fp16(cpu, n)).cuda().float()
+    for rows in (33, 257, 512, 2048):
+        x = torch.randn(rows, k, generator=torch.Generator().manual_seed(rows), dtype=torch.float16).cuda()
+        assert_output(layer(x), x.float() @ weight.T)
+
+
+def test_gemm_qwen3_32b_gate_at_2048_rows():
+    """5120 -> 25600 at 2048 rows: an FP32 matmul on the kernel-made dense weight (pinned bit
+    for bit against the reference decoder by the hash tests) keeps the host time down."""
+    k, n, rows = 5120, 25600, 2048
+    gpu = to_cuda(synthetic_sage(k, n, seed=4, permuted=True))
+    layer = SAGELinear(gpu, n)
+    x = torch.randn(rows, k, generator=torch.Generator().manual_seed(9), dtype=torch.float16).cuda()
+    got = layer(x)
+    weight = layer.dequantize().float()
+    for begin in range(0, rows, 512):  # in slices: the FP32 product of the whole is 210 MB
+        assert_output(got[begin : begin + 512], x[begin : begin + 512].float() @ weight.T)
+
+
+@pytest.mark.parametrize("rows", [300, 513])
+def test_gemm_one_hot_rows_across_token_blocks(rows):
+    """x[m] = e_(m mod K) picks weight column (m mod K) for token m: a wrong token-block offset,
+    TMA coordinate or store guard fails element by element, not only in norm."""
+    k, n = 512, 200
+    cpu = synthetic_sage(k, n, seed=2, permuted=True)
+    layer = SAGELinear(to_cuda(cpu), n)
+    weight = torch.from_numpy(c_oracle.decode_fp16(cpu, n)).cuda()
+    x = torch.zeros(rows, k, dtype=torch.float16, device="cuda")
+    columns = torch.arange(rows, device="cuda") * 7 % k
+    x[torch.arange(rows, device="cuda"), columns] = 1.0
+    got = layer(x)
+    want = weight[:, columns].T.float()
+    assert torch.allclose(got.float(), want, rtol=2e-3, atol=1e-6)

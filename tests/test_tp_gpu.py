@@ -14,11 +14,14 @@ pytestmark = pytest.mark.gpu
 
 def _worker(rank, world, path, results, experts=False):
     os.environ["NCCL_NVLS_ENABLE"] = "0"
-    torch.cuda.set_device(rank)
-    dist.init_process_group("nccl", init_method=f"file://{path}", rank=rank, world_size=world,
-                            device_id=torch.device("cuda", rank))
-    cpu_group = dist.new_group(backend="gloo")  # host-side barrier, see bench.py run_tp
+    code = 1
     try:
+        import datetime
+
+        torch.cuda.set_device(rank)
+        dist.init_process_group("nccl", init_method=f"file://{path}", rank=rank, world_size=world,
+                                device_id=torch.device("cuda", rank), timeout=datetime.timedelta(seconds=120))
+        cpu_group = dist.new_group(backend="gloo")  # host-side barrier, see bench.py run_tp
         from sage_b200.qwen3 import PackedQwen3, Qwen3Config
 
         if experts:  # mixture of experts: each rank keeps half of the experts
@@ -29,22 +32,46 @@ def _worker(rank, world, path, results, experts=False):
             config = Qwen3Config(layers=3, hidden=1024, heads=8, kv_heads=2, intermediate=2048, vocab=4096)
             parallel = dict(tp_group=dist.group.WORLD)
         prompt = torch.randint(3, config.vocab, (1, 12), generator=torch.Generator().manual_seed(4))
+
+        def run(model):
+            """Tokens of 40 greedy steps and the logits of the first generated token."""
+            model.prefill(prompt)
+            first_logits = model.logits.float().cpu()
+            for _ in range(39):
+                model.graph.replay()
+            return model.log[:, :40].cpu(), first_logits
+
         sharded = PackedQwen3(config, f"cuda:{rank}", seed=2, max_seq=96, max_new=40, perm_blocks=4, **parallel)
-        tokens = sharded.generate(prompt, 40).cpu()
-        logits = sharded.logits.float().cpu()
+        tokens, logits = run(sharded)
         if rank == 0:
+            # the one-GPU model is fed the sharded model's tokens, so one flip cannot hide later
+            # steps; a disagreement is accepted only as a near tie of the one-GPU logits
             single = PackedQwen3(config, "cuda:0", seed=2, max_seq=96, max_new=40, perm_blocks=4)
-            want = single.generate(prompt, 40).cpu()
+            single.prefill(prompt)
             want_logits = single.logits.float().cpu()
-            same = (tokens[0] == want[0]).long().cumprod(0).sum().item()
-            results.put(("tokens", same, tokens.tolist(), want.tolist(),
+            flips = []
+            for i in range(40):
+                if i > 0:
+                    single.tokens.copy_(tokens[:, i - 1].to(single.device))
+                    single.graph.replay()
+                row = single.logits[0].float()
+                best, got = int(torch.argmax(row)), int(tokens[0, i])
+                if best != got:
+                    flips.append((i, got, best, float(row[best] - row[got]), float(row.std())))
+            results.put(("tokens", flips, tokens.tolist(),
                          ((logits - want_logits).norm() / want_logits.norm()).item()))
         torch.cuda.synchronize()
         dist.barrier(group=cpu_group)
         results.close()
         results.join_thread()
+        code = 0
+    except BaseException:  # noqa: BLE001 - the parent must see a failing rank as a failure
+        import traceback
+
+        traceback.print_exc()
+        code = 1
     finally:
-        os._exit(0)  # no NCCL teardown under live CUDA graphs
+        os._exit(code)  # no NCCL teardown under live CUDA graphs
 
 
 @pytest.mark.parametrize("experts", [False, True], ids=["tensor_parallel", "expert_parallel"])
@@ -60,10 +87,17 @@ def test_two_gpus_match_single_gpu(experts):
             p.start()
         for p in procs:
             p.join(300)
-            assert p.exitcode == 0
-    kind, same, got, want, logit_error = results.get(timeout=10)
-    # summation order differs between one and two GPUs; require a long common prefix and,
-    # if every token agrees, logits within the matmul gate's order of magnitude
-    assert same >= 20, (same, got, want)
-    if same == 40:
-        assert logit_error < 2e-2, logit_error
+        alive = [p for p in procs if p.is_alive()]
+        for p in alive:  # never leave a rank spinning on a GPU
+            p.kill()
+            p.join(30)
+        assert not alive, "a rank did not finish in time"
+        assert all(p.exitcode == 0 for p in procs), [p.exitcode for p in procs]
+    kind, flips, got, logit_error = results.get(timeout=10)
+    # The first generated token's logits are compared unconditionally: one and two GPUs differ
+    # only in summation order there.  Every later token must be the one-GPU model's choice for the
+    # same history, or a near tie (2 % of the logit spread) in the one-GPU model's own logits.
+    assert logit_error < 2e-2, logit_error
+    for step, ours, best, margin, spread in flips:
+        assert 0 <= margin <= 0.02 * spread, (step, ours, best, margin, spread)
+    assert len(flips) <= 1, (flips, got)
