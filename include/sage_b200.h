@@ -199,6 +199,24 @@ int sageb200_dequant(const void *codes, const void *radii, const void *grid, con
                      const int32_t *perm, void *w, int n, int k, int entries, void *stream);
 
 /*
+ * Export-side packing of one trained spherical linear (the step before the path): frozen
+ * signs int8 [n][k] (+1 / -1), direction indices int32 [n][k/8] and radii FP32 [n][k/8]
+ * (after the softplus) into the packed buffers above.  Per (row, 128-channel group) the FP16
+ * grid (min, step) is fitted to the sixteen radii and each radius code is selected against
+ * that rounded grid.  tiled != 0: SAGE's layout (`codes` = packed_codes, `high` = radius_codes,
+ * `grid_or_scales` = radius_grid, rows padded to a multiple of 16 with zero codes and a zero
+ * grid, `mins` unused); tiled == 0 (entries 64 only): SPHQuant's row-major layout (`codes` int16
+ * [n][k/8], `high` int32 [n][k/128], `grid_or_scales` the FP16 scales and `mins` the FP16
+ * minimums, [n][k/128] each).  The codebook and the permutation are not touched here: they are
+ * small tensors the host side derives (see sage_b200/packing.py).  Bit-identical to the
+ * reference's tensor program.
+ * Replaces: pack_spherical (reference weight_vq/sphquant/packing.py:32-75).
+ */
+int sageb200_pack_spherical(const void *signs, const void *indices, const void *radius, void *codes,
+                            void *high, void *grid_or_scales, void *mins, int n, int k, int entries,
+                            int tiled, void *stream);
+
+/*
  * Host-buffer form of sageb200_linear for callers whose activations live in host
  * memory: copies x_host to the device, runs the matmul and copies y back, all on
  * `stream`, then synchronises the stream.  The packed weight buffers are device

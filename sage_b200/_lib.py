@@ -30,6 +30,7 @@ EXPORTED = (
     "sageb200_experts_workspace_bytes",
     "sageb200_experts",
     "sageb200_dequant",
+    "sageb200_pack_spherical",
     "sageb200_host_staging_bytes",
     "sageb200_linear_host",
     "sageb200_set_tuning",
@@ -172,6 +173,8 @@ def load() -> ctypes.CDLL:
     lib.sageb200_sph_dequant.argtypes = [vp] * 6 + [ci] * 2 + [vp]
     lib.sageb200_debug_plan.restype = ci
     lib.sageb200_debug_plan.argtypes = [ci] * 5 + [ctypes.POINTER(ci)]
+    lib.sageb200_pack_spherical.restype = ci
+    lib.sageb200_pack_spherical.argtypes = [vp] * 7 + [ci] * 4 + [vp]
     lib.sageb200_clear_status.restype = ci
     lib.sageb200_clear_status.argtypes = []
     lib.sageb200_set_pdl.restype = ci

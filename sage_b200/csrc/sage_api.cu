@@ -602,6 +602,34 @@ int sageb200_dequant(const void *codes, const void *radii, const void *grid, con
   return SAGEB200_OK;
 }
 
+int sageb200_pack_spherical(const void *signs, const void *indices, const void *radius, void *codes,
+                            void *high, void *grid_or_scales, void *mins, int n, int k, int entries,
+                            int tiled, void *stream) {
+  if (n <= 0 || k <= 0 || (k % 128) != 0 || direction_bits_of(entries) < 0 || (!tiled && entries != 64))
+    return SAGEB200_ERR_INVALID_ARGUMENT;
+  if (!signs || !indices || !radius || !codes || !high || !grid_or_scales || (!tiled && !mins))
+    return SAGEB200_ERR_INVALID_ARGUMENT;
+  if (static_cast<long long>((n + 15) / 16) * (k / 128) * 16 > INT_MAX) return SAGEB200_ERR_RANGE;
+  if ((reinterpret_cast<uintptr_t>(signs) & 15) || (reinterpret_cast<uintptr_t>(indices) & 3) ||
+      (reinterpret_cast<uintptr_t>(radius) & 15) || (reinterpret_cast<uintptr_t>(codes) & 15) ||
+      (reinterpret_cast<uintptr_t>(high) & 3) || (reinterpret_cast<uintptr_t>(grid_or_scales) & 3) ||
+      (reinterpret_cast<uintptr_t>(mins) & 1))
+    return SAGEB200_ERR_ALIGNMENT;
+  DeviceState *device = nullptr;
+  const int status = device_state(&device);
+  if (status) return status;
+  if (launch_pack(static_cast<const int8_t *>(signs), static_cast<const int32_t *>(indices),
+                  static_cast<const float *>(radius), static_cast<uint32_t *>(codes),
+                  static_cast<uint32_t *>(high), static_cast<__half *>(grid_or_scales),
+                  static_cast<__half *>(mins), n, k, direction_bits_of(entries), tiled != 0,
+                  static_cast<cudaStream_t>(stream), device->sm_count) != cudaSuccess) {
+    cudaGetLastError();
+    return SAGEB200_ERR_CUDA;
+  }
+  g_launches.fetch_add(1, std::memory_order_relaxed);
+  return SAGEB200_OK;
+}
+
 size_t sageb200_host_staging_bytes(int rows, int n, int k) {
   if (n <= 0 || k <= 0 || rows <= 0) return 0;
   return align256(static_cast<size_t>(rows) * k * 2) + align256(static_cast<size_t>(rows) * n * 2) +

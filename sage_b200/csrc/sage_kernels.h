@@ -96,6 +96,13 @@ cudaError_t launch_dequant(const uint32_t *codes, const uint32_t *radii, const u
                            const uint32_t *book, const int32_t *perm, __half *w, int n, int k,
                            int entries, cudaStream_t stream, int sm_count);
 
+// Export-side packing (sage_pack.cu): `tiled` = SAGE's [tile][group][16][8] words, grid (min, step)
+// in grid_or_scales and `mins` unused; otherwise SPHQuant's row-major int16 codes with separate
+// scales and minimums.
+cudaError_t launch_pack(const int8_t *signs, const int32_t *indices, const float *radius, uint32_t *codes,
+                        uint32_t *high, __half *grid_or_scales, __half *mins, int n, int k, int dbits,
+                        bool tiled, cudaStream_t stream, int sm_count);
+
 // Launch plan of the tcgen05 prefill GEMM (host side).
 struct GemmPlan {
   int tokens_per_cta;   // MMA N: multiple of 16, at most 256

@@ -543,3 +543,44 @@ def test_gemm_one_hot_rows_across_token_blocks(rows):
     got = layer(x)
     want = weight[:, columns].T.float()
     assert torch.allclose(got.float(), want, rtol=2e-3, atol=1e-6)
+
+
+# ---------------------------------------------------------------- traceability (torch.compile)
+
+
+@pytest.mark.parametrize("k,n", [(2560, 4096), (2560, 9728), (4096, 2560), (9728, 2560)])
+@pytest.mark.parametrize("seed", [0, 1, 2])
+def test_compiled_module_matches_oracle(k, n, seed):
+    """`torch.compile(fullgraph=True, mode="reduce-overhead")` traces through the operator's fake
+    kernel and replays it under Inductor's CUDA graphs (reference tests/inference/test_sage.py:
+    135-151: the four Qwen3-4B shapes, three seeds, three input scales)."""
+    torch.compiler.reset()
+    cpu = synthetic_sage(k, n, seed=seed)
+    layer = SAGELinear(to_cuda(cpu), n)
+    weight = torch.from_numpy(c_oracle.decode_fp16(cpu, n)).cuda().float()
+    compiled = torch.compile(layer, fullgraph=True, dynamic=False, mode="reduce-overhead")
+    x = torch.randn(1, k, generator=torch.Generator().manual_seed(43), dtype=torch.float16).cuda()
+    try:
+        for scale in (0.03125, 1.0, 32.0):
+            scaled = x * scale
+            for _ in range(3):  # warm-up, capture, replay
+                got = compiled(scaled).clone()
+            assert_output(got, scaled.float() @ weight.T)
+            assert torch.equal(got, layer(scaled))
+    finally:
+        torch.compiler.reset()
+
+
+def test_compiled_module_with_rows_and_bias():
+    """The plain `fullgraph` compile of the module at several rows (decode kernel and tensor-core
+    GEMM), with a bias (reference tests/inference/test_sage.py:187-191)."""
+    torch.compiler.reset()
+    cpu = synthetic_sage(256, 17, seed=1)
+    layer = SAGELinear(to_cuda(cpu), 17, bias=torch.ones(17, device="cuda", dtype=torch.float16))
+    compiled = torch.compile(layer, fullgraph=True)
+    try:
+        for rows in (2, 65):
+            x = torch.randn(rows, 256, device="cuda", dtype=torch.float16)
+            assert_output(compiled(x) - 1, expected_output(x, cpu, 17))
+    finally:
+        torch.compiler.reset()
