@@ -17,6 +17,7 @@
 #define SAGE_B200_DECODE_H_
 
 #include <stddef.h>
+#include <stdint.h>
 
 #ifdef __cplusplus
 extern "C" {
@@ -127,6 +128,69 @@ int sageb200_glue_moe_route(void *residual, const void *delta, const void *norm_
 /* out[rows][hidden] = fp16(sum_s weights[row][s] * slot_outputs[row*top_k + s][:]) (FP32 sum). */
 int sageb200_glue_moe_mix(const void *slot_outputs, const void *weights, void *out, int rows, int hidden,
                           int top_k, void *stream);
+
+/* ---------------------------------------------------------------------------------------
+ * One decoded token as ONE persistent kernel (batch 1, one GPU, dense-MLP Qwen3).
+ *
+ * A cooperative grid of one CTA per SM runs the whole token: per layer residual add + RMSNorm
+ * + q/k/v, attention over the KV cache, o_proj, residual add + RMSNorm + gate/up + SwiGLU,
+ * down_proj; then the final norm, the FP16 lm_head and the greedy argmax, with a grid barrier
+ * between dependent phases and the next phase's packed weights streaming into shared memory
+ * through the barriers.  Same arithmetic as the per-launch calls above and as
+ * sageb200_linear_grouped_fused; sums associate in another (fixed) order.
+ *
+ * The reference has no counterpart (there a token is ~250 kernel launches driven by Hugging
+ * Face modules, benchmarks/model.py:112-116 and weight_vq/inference/linear.py:289-309).
+ *
+ * All pointers are device pointers.  Packed buffers are the five buffers of sage_b200.h; the
+ * four big ones and the permutation must be 16-byte aligned here.
+ */
+typedef struct sageb200_mega_linear {
+  const void *codes, *radii, *grid, *book;
+  const int32_t *perm;          /* NULL: identity */
+  int n, k, entries;
+} sageb200_mega_linear;
+
+typedef struct sageb200_mega_layer {
+  sageb200_mega_linear q, k, v, o, gate, up, down;
+  const void *input_norm, *post_norm, *q_norm, *k_norm;   /* FP16 norm weights */
+  void *k_cache, *v_cache;                                /* FP16 [kv_heads][max_seq][128] */
+} sageb200_mega_layer;
+
+typedef struct sageb200_mega_model {
+  int layers, hidden, heads, kv_heads, head_dim, intermediate, vocab, max_seq;
+  float eps;
+  const void *embed, *lm_head, *final_norm;               /* FP16 [vocab][hidden] x2, [hidden] */
+  const void *cos_table, *sin_table;                      /* FP16 [max_seq][64] */
+} sageb200_mega_model;
+
+/*
+ * Bytes of device workspace a model needs (0: the model does not fit this kernel - head_dim
+ * other than 128, more than 8 query heads per kv head, rows too long for shared memory, fewer
+ * SMs than heads - and the caller stays on the per-launch path).  sm_count <= 0: the current
+ * device's.  Pure host arithmetic.
+ */
+size_t sageb200_mega_workspace_bytes(const sageb200_mega_model *model, int sm_count);
+
+/*
+ * Writes the launch plan (per-CTA work ranges, layer tables, scratch pointers) into the
+ * 256-byte aligned `workspace` and zeroes its barrier words and partial-sum slots; synchronises
+ * `stream`.  Call once per model (and again after a SAGEB200_ERR_TIMEOUT, whose barrier words
+ * are left as they were).  `layers` is a host array of model->layers entries.
+ */
+int sageb200_mega_prepare(const sageb200_mega_model *model, const sageb200_mega_layer *layers,
+                          void *workspace, size_t workspace_bytes, void *stream);
+
+/*
+ * One decode step: reads tokens[0] (int64) and positions[0] (int32), appends the token's key and
+ * value to every layer's cache, writes logits[vocab] (FP16), tokens[0] = argmax (lowest index
+ * on ties), log[step[0]] = token if step[0] < log_stride, positions[0] += 1, step[0] += 1.
+ * Enqueues one cooperative kernel on `stream`; no host synchronisation.  Every device-side
+ * wait is bounded: one that runs out is recorded as SAGEB200_ERR_TIMEOUT (see
+ * sageb200_clear_status in sage_b200.h).  Steps of one workspace must not overlap.
+ */
+int sageb200_mega_step(const sageb200_mega_model *model, void *workspace, void *tokens, void *positions,
+                       void *log, void *step, void *logits, int log_stride, void *stream);
 
 #ifdef __cplusplus
 }

@@ -10,7 +10,9 @@ import os
 import pathlib
 
 PACKAGE = pathlib.Path(__file__).resolve().parent
-LIBRARY = PACKAGE / "libsage_b200.so"
+# SAGEB200_LIBRARY selects another build of the same library (the profiling build that
+# `python -m sage_b200.build --trace` writes beside the product one)
+LIBRARY = pathlib.Path(os.environ.get("SAGEB200_LIBRARY", PACKAGE / "libsage_b200.so"))
 
 OK = 0
 MAX_GROUPED = 16
@@ -67,6 +69,9 @@ EXPORTED_DECODE = (
     "sageb200_glue_swiglu",
     "sageb200_glue_lm_head",
     "sageb200_glue_argmax_advance",
+    "sageb200_mega_workspace_bytes",
+    "sageb200_mega_prepare",
+    "sageb200_mega_step",
 )
 
 
@@ -98,6 +103,38 @@ class ExpertStack(ctypes.Structure):
         ("k", ctypes.c_int),
         ("entries", ctypes.c_int),
     ]
+
+
+class MegaLinear(ctypes.Structure):
+    """struct sageb200_mega_linear."""
+
+    _fields_ = [
+        ("codes", ctypes.c_void_p),
+        ("radii", ctypes.c_void_p),
+        ("grid", ctypes.c_void_p),
+        ("book", ctypes.c_void_p),
+        ("perm", ctypes.c_void_p),
+        ("n", ctypes.c_int),
+        ("k", ctypes.c_int),
+        ("entries", ctypes.c_int),
+    ]
+
+
+class MegaLayer(ctypes.Structure):
+    """struct sageb200_mega_layer."""
+
+    _fields_ = [(name, MegaLinear) for name in ("q", "k", "v", "o", "gate", "up", "down")] + [
+        (name, ctypes.c_void_p) for name in ("input_norm", "post_norm", "q_norm", "k_norm", "k_cache", "v_cache")
+    ]
+
+
+class MegaModel(ctypes.Structure):
+    """struct sageb200_mega_model."""
+
+    _fields_ = [(name, ctypes.c_int) for name in ("layers", "hidden", "heads", "kv_heads", "head_dim",
+                                                  "intermediate", "vocab", "max_seq")] + [
+        ("eps", ctypes.c_float)] + [
+        (name, ctypes.c_void_p) for name in ("embed", "lm_head", "final_norm", "cos_table", "sin_table")]
 
 
 class Problem(ctypes.Structure):
@@ -217,6 +254,12 @@ def load() -> ctypes.CDLL:
     lib.sageb200_glue_lm_head.argtypes = [vp, vp, vp, ci, ci, ci, ci, vp]
     lib.sageb200_glue_argmax_advance.restype = ci
     lib.sageb200_glue_argmax_advance.argtypes = [vp] * 5 + [ci, ci, ci, vp]
+    lib.sageb200_mega_workspace_bytes.restype = sz
+    lib.sageb200_mega_workspace_bytes.argtypes = [ctypes.POINTER(MegaModel), ci]
+    lib.sageb200_mega_prepare.restype = ci
+    lib.sageb200_mega_prepare.argtypes = [ctypes.POINTER(MegaModel), ctypes.POINTER(MegaLayer), vp, sz, vp]
+    lib.sageb200_mega_step.restype = ci
+    lib.sageb200_mega_step.argtypes = [ctypes.POINTER(MegaModel), vp, vp, vp, vp, vp, vp, ci, vp]
     if "SAGEB200_PDL" in os.environ:  # debug switch: which kernel families launch dependently
         lib.sageb200_set_pdl(int(os.environ["SAGEB200_PDL"]))
     _handle = lib

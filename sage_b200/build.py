@@ -18,6 +18,7 @@ import sys
 PACKAGE = pathlib.Path(__file__).resolve().parent
 CSRC = PACKAGE / "csrc"
 LIBRARY = PACKAGE / "libsage_b200.so"
+TRACE_LIBRARY = PACKAGE / "libsage_b200_trace.so"
 INCLUDE = PACKAGE.parent / "include"
 
 NVCC_FLAGS = [
@@ -60,14 +61,17 @@ def build(force: bool = False, verbose: bool = False, trace: bool = False) -> pa
     if not force and not trace and not is_stale():
         return LIBRARY
     flags = NVCC_FLAGS + (["-DSAGEB200_TRACE"] if trace else [])
-    command = [_nvcc(), *flags, f"-I{INCLUDE}", "-o", str(LIBRARY), *map(str, sources())]
+    # the profiling build goes beside the product library (select it with SAGEB200_LIBRARY)
+    target = TRACE_LIBRARY if trace else LIBRARY
+    command = [_nvcc(), *flags, f"-I{INCLUDE}", "-o", str(target), *map(str, sources())]
     result = subprocess.run(command, capture_output=True, text=True)
     if verbose or result.returncode:
         sys.stderr.write(" ".join(command) + "\n" + result.stdout + result.stderr)
     if result.returncode:
         raise RuntimeError("nvcc failed building libsage_b200.so")
-    (PACKAGE / "build_log.txt").write_text(result.stdout + result.stderr)
-    return LIBRARY
+    if not trace:
+        (PACKAGE / "build_log.txt").write_text(result.stdout + result.stderr)
+    return target
 
 
 if __name__ == "__main__":

@@ -423,6 +423,21 @@ int validate_problem(const sageb200_problem &p) {
 }
 
 }  // namespace
+
+long long *trace_buffer() { return g_trace; }
+
+void count_launches(int launches) { g_launches.fetch_add(static_cast<unsigned long long>(launches), std::memory_order_relaxed); }
+
+int acquire_device(int **status_word, int *sm_count) {
+  DeviceState *state = nullptr;
+  const int status = device_state(&state);
+  if (state) {
+    if (status_word) *status_word = state->status;
+    if (sm_count) *sm_count = state->sm_count;
+  }
+  return status;
+}
+
 }  // namespace sageb200
 
 using namespace sageb200;

@@ -103,6 +103,15 @@ cudaError_t launch_pack(const int8_t *signs, const int32_t *indices, const float
                         uint32_t *high, __half *grid_or_scales, __half *mins, int n, int k, int dbits,
                         bool tiled, cudaStream_t stream, int sm_count);
 
+// Per-device set-up of the library on the current device (idempotent): the device-visible
+// status word the kernels write on a timed-out wait, and the SM count.  Returns a
+// SAGEB200_* status (SAGEB200_ERR_TIMEOUT while an earlier time-out is recorded).
+int acquire_device(int **status_word, int *sm_count);
+// The buffer given to sageb200_debug_trace (null: none); read by -DSAGEB200_TRACE builds only.
+long long *trace_buffer();
+// Adds to the count sageb200_launch_count() reports.
+void count_launches(int launches);
+
 // Launch plan of the tcgen05 prefill GEMM (host side).
 struct GemmPlan {
   int tokens_per_cta;   // MMA N: multiple of 16, at most 256

@@ -110,4 +110,70 @@ __device__ __forceinline__ void compute_unit(const uint2 (&code)[2], const uint3
   }
 }
 
+// 16-byte shared-memory load by 32-bit address that the compiler may schedule early: not
+// `volatile` (so it can move across arithmetic and the MMAs), "memory" clobber (so it stays on
+// its side of barriers and mbarrier waits).
+__device__ __forceinline__ uint4 lds_u4_early(uint32_t shared_address) {
+  uint4 v;
+  asm("ld.shared.v4.u32 {%0,%1,%2,%3}, [%4];"
+      : "=r"(v.x), "=r"(v.y), "=r"(v.z), "=r"(v.w)
+      : "r"(shared_address)
+      : "memory");
+  return v;
+}
+
+// The same unit for ONE activation row with every operand named by its 32-bit shared-memory
+// address (ld.shared explicitly: no generic addressing, no 64-bit pointer arithmetic):
+//   book_lane  address of the replicated codebook + this lane's replica offset
+//   x_lane     address of the staged activation row at this group + 16 * t
+template <bool kLowBits>
+__device__ __forceinline__ void compute_unit_shared(const uint2 (&code)[2], const uint32_t (&radius_word)[2],
+                                                    const uint32_t (&endpoints)[2], float (&acc)[4],
+                                                    const FieldConsts &f, uint32_t book_lane, uint32_t x_lane,
+                                                    int t) {
+  float step16[2], base[2];
+  uint32_t high[2];
+#pragma unroll
+  for (int h = 0; h < 2; ++h) {
+    const float2 e = __half22float2(*reinterpret_cast<const __half2 *>(&endpoints[h]));
+    step16[h] = e.y * 16.0f;
+    base[h] = fmaf(-16.0f, e.y, e.x);
+    high[h] = (radius_word[h] >> (8 * t)) << f.hi_shift;
+  }
+#pragma unroll
+  for (int s = 0; s < 4; ++s) {
+    uint32_t a[2][4];
+#pragma unroll
+    for (int h = 0; h < 2; ++h) {
+      const uint32_t word = (s < 2) ? code[h].x : code[h].y;
+      uint32_t offset, signs, low = 0x3f800000u;
+      if (s & 1) {
+        offset = (word >> 17) & f.index_mask;
+        signs = byte_of<2>(word);
+        if constexpr (kLowBits) low = and_or(word >> f.lo_right, f.lo_mask, 0x3f800000u);
+      } else {
+        offset = (word >> 1) & f.index_mask;
+        signs = byte_of<0>(word);
+        if constexpr (kLowBits) low = and_or(word << f.lo_left, f.lo_mask, 0x3f800000u);
+      }
+      const uint4 dir = lds_u4_early(book_lane + offset);
+      const uint32_t radius_bits = and_or(s ? high[h] >> (2 * s) : high[h], f.hi_mask, low);
+      const float radius = fmaf(__uint_as_float(radius_bits), step16[h], base[h]);
+      const __half2 rr = __floats2half2_rn(radius, radius);
+      const uint32_t d[4] = {xor_and(dir.x, signs * 0x40008000u, 0x80008000u),
+                             xor_and(dir.y, signs * 0x10002000u, 0x80008000u),
+                             xor_and(dir.z, signs * 0x04000800u, 0x80008000u),
+                             xor_and(dir.w, signs * 0x01000200u, 0x80008000u)};
+#pragma unroll
+      for (int p = 0; p < 4; ++p) {
+        const __half2 w = __hmul2(*reinterpret_cast<const __half2 *>(&d[p]), rr);
+        a[h][p] = *reinterpret_cast<const uint32_t *>(&w);
+      }
+    }
+    const uint4 b = lds_u4_early(x_lane + s * 64);
+    mma_16816(acc, a[0][0], a[1][0], a[0][1], a[1][1], b.x, b.y);
+    mma_16816(acc, a[0][2], a[1][2], a[0][3], a[1][3], b.z, b.w);
+  }
+}
+
 }  // namespace sageb200

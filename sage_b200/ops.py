@@ -19,6 +19,7 @@ import torch
 
 from . import _lib
 
+_COUNTER_REGION_BYTES = 64 * 1024  # the front of the scratch the kernels expect (and leave) zero
 _WORKSPACES: dict[tuple[int, int], torch.Tensor] = {}
 _RETIRED: list[torch.Tensor] = []  # outgrown buffers a captured graph may still point at
 
@@ -87,7 +88,16 @@ def sage_forward(
     with torch.cuda.device(x.device):
         stream = torch.cuda.current_stream(x.device).cuda_stream
         nbytes = lib.sageb200_workspace_bytes(rows, out_features, k)
-        workspace = _workspace(x.device, stream, nbytes) if nbytes else None
+        workspace = None
+        if nbytes and stream == 0:
+            workspace = _workspace(x.device, stream, nbytes)  # the default stream's cached scratch
+        elif nbytes:
+            # Any other stream may be one that is being captured, or the private stream of a
+            # compiled graph whose memory pool accepts no allocation that outlives the call: take
+            # the scratch as a temporary of this call, as the reference's entry point does
+            # (csrc/bindings.cpp:63-66), and zero the arrival counters at its front.
+            workspace = torch.empty(nbytes, dtype=torch.uint8, device=x.device)
+            workspace[: min(nbytes, _COUNTER_REGION_BYTES)].zero_()
         _lib.check(
             lib.sageb200_linear(
                 x.data_ptr(),

@@ -223,6 +223,52 @@ class PackedQwen3:
             self.route_weights = torch.zeros(batch, c.top_k, dtype=torch.float32, device=self.device)
         self.graph = None
         self.graph_no_head = None
+        # The whole token as one persistent kernel (`sageb200_mega_step`).  Prepared when the model
+        # fits it; `use_mega` selects it for the decode step before `capture()`.  It is off by
+        # default: as measured on B200 the per-launch path is still the faster one.
+        self.mega = None
+        self.use_mega = False
+        if not self.dense and batch == 1 and world == 1 and self.ep_world == 1 and not c.experts:
+            self._prepare_mega()
+            self.use_mega = False
+
+    # ------------------------------------------------------------------ the one-kernel decode step
+
+    def _prepare_mega(self):
+        """Describe the model to `sageb200_mega_prepare`; leaves `use_mega` False when the
+        model does not fit that kernel (the per-launch path then serves every step)."""
+        c, lib = self.config, self.lib
+        model = _lib.MegaModel(c.layers, c.hidden, c.heads, c.kv_heads, c.head_dim, c.intermediate, c.vocab,
+                               self.max_seq, c.eps, self.embed.data_ptr(), self.lm_head.data_ptr(),
+                               self.final_norm.data_ptr(), self.cos.data_ptr(), self.sin.data_ptr())
+        nbytes = lib.sageb200_mega_workspace_bytes(ctypes.byref(model), self.sm_count)
+        if nbytes == 0:
+            return
+        layers = (_lib.MegaLayer * c.layers)()
+        for index, layer in enumerate(self.layers):
+            entry = layers[index]
+            for name in ("q", "k", "v", "o", "gate", "up", "down"):
+                linear, p = layer[name], layer[name].packed
+                perm = p["permutation"]
+                if perm.numel() and perm.data_ptr() % 16:
+                    return
+                setattr(entry, name, _lib.MegaLinear(
+                    p["packed_codes"].data_ptr(), p["radius_codes"].data_ptr(), p["radius_grid"].data_ptr(),
+                    p["codebook"].data_ptr(), perm.data_ptr() if perm.numel() else None, linear.n, linear.k,
+                    linear.entries))
+            for name in ("input_norm", "post_norm", "q_norm", "k_norm", "k_cache", "v_cache"):
+                setattr(entry, name, layer[name].data_ptr())
+        workspace = torch.zeros(nbytes, dtype=torch.uint8, device=self.device)
+        with torch.cuda.device(self.device):
+            status = lib.sageb200_mega_prepare(ctypes.byref(model), layers, _vp(workspace), nbytes, self._stream())
+        self._check(status, "mega_prepare")
+        self.mega = (model, workspace)
+
+    def _mega_step(self):
+        model, workspace = self.mega
+        self._check(self.lib.sageb200_mega_step(
+            ctypes.byref(model), _vp(workspace), _vp(self.tokens), _vp(self.positions), _vp(self.log),
+            _vp(self.step_counter), _vp(self.logits), self.max_new, self._stream()), "mega_step")
 
     # ------------------------------------------------------------------ pieces
 
@@ -345,6 +391,9 @@ class PackedQwen3:
     def step(self, head: bool = True):
         """Enqueue one decode iteration for the tokens in `self.tokens` at `self.positions`."""
         c, lib, b = self.config, self.lib, self.batch
+        if head and self.use_mega:
+            self._mega_step()  # the whole token, lm_head and argmax included, in one kernel
+            return
         delta = self._body()
         s = self._stream()
         if not head:

@@ -85,11 +85,11 @@ def lockstep(config, steps, prompt_length, seed, max_seq):
 
 
 def check_lockstep(mismatches, worst_logit_error, steps, allowed=0):
-    """`allowed` = how many near-tie flips the case may show.  The contract is identical greedy
-    tokens; the measured count on the fixed seeds below is zero, so zero is what is asserted.
-    Random-init logits over a large vocabulary can put the top two within a few FP16 steps of
-    each other, which is the only disagreement a case may declare (never silently): the flip
-    must then be a near tie (2 % of the logit spread) in the ORACLE's own logits."""
+    """The contract is identical greedy tokens: `allowed` = 0 disagreements, which is what the
+    fixed seeds below measure.  The one thing FP16 logits cannot decide is an exact near tie: a
+    case that hits one declares it in `allowed` (never silently), and such a flip must then lie
+    within two FP16 steps of the ORACLE's own top logit - a gap the oracle's own rounding
+    decides - on top of the looser 2 % of-the-spread bound."""
     # logits of the packed model stay within the matmul gate's order of magnitude of the oracle's
     assert worst_logit_error < 2e-2, worst_logit_error
     for step, ours, oracle, margin, spread in mismatches:

@@ -71,11 +71,17 @@ def test_static_scratch_matches_caller_scratch_twice(k, n, rows, seed, permuted)
 
     for call in range(2):  # the second call finds the first call's leftovers in the array
         got = torch.full((rows, n), float("nan"), dtype=torch.float16, device="cuda")
+        torch.cuda.synchronize()
+        free_before, _ = torch.cuda.mem_get_info()
+        reserved_before = torch.cuda.memory_reserved()
         status = lib.sageb200_linear_static(
             vp(x.data_ptr()), *_pointers(gpu), vp(got.data_ptr()), rows, n, k, entries, stream
         )
         assert status == 0, lib.sageb200_status_string(status)
         torch.cuda.synchronize()
+        if call == 1:  # past the first call's one-off set-up: the device's free memory did not move
+            assert torch.cuda.mem_get_info()[0] == free_before
+            assert torch.cuda.memory_reserved() == reserved_before
         assert torch.isfinite(got).all(), f"call {call}: output not fully written"
         error = (got.float() - want.float()).norm() / want.float().norm().clamp_min(1e-30)
         assert error.item() <= REL_FROBENIUS, (call, error.item())
