@@ -59,6 +59,16 @@ def measured_peaks() -> tuple[float, str]:
     return 6650.0, "fallback"
 
 
+def all_peaks() -> dict:
+    """HBM copy GB/s and dense BF16 TFLOP/s (burst) of this pool's B200s, measured where the
+    file exists, else the earlier measurement used as the stated fallback."""
+    path = ROOT / "MEASURED_PEAKS.json"
+    if path.exists():
+        data = json.loads(path.read_text())
+        return {"hbm_gbs": float(data["hbm_gbs"]), "bf16_tflops": float(data.get("bf16_tflops", 1590.0)), "kind": "measured"}
+    return {"hbm_gbs": 6650.0, "bf16_tflops": 1590.0, "kind": "fallback"}
+
+
 class ClockSampler:
     """Samples SM clocks and throttle reasons with nvidia-smi while a region runs."""
 
@@ -222,6 +232,96 @@ def build_decode_linears(device):
     return layers, inputs, total_bytes
 
 
+
+def time_linear(k: int, n: int, rows: int, device, steps: int = 5, reference: bool = False):
+    """Microseconds per call of one packed-linear shape on cold weights: enough distinct weight
+    copies to exceed L2, all copies back to back in ONE CUDA graph, CUDA events around `steps`
+    replays.  `reference`: the reference project's own kernels compiled for sm_100a
+    (oracle/_ref/libsage_ref.so, dispatch of csrc/bindings.cpp:49-76) instead of this library;
+    None when that comparator was not built."""
+    import ctypes
+
+    import torch
+
+    from sage_b200 import SAGELinear
+    from sage_b200.synthetic import linear_algorithmic_bytes, synthetic_sage_device
+
+    one = linear_algorithmic_bytes(rows, n, k, 256, True)
+    copies = max(2, int(200e6 // one) + 1)
+    layers = [SAGELinear(synthetic_sage_device(k, n, 3 * i, device, direction_bits=8), n) for i in range(copies)]
+    x = torch.randn(rows, k, device=device, dtype=torch.float16)
+    if reference:
+        from oracle import c_oracle  # the comparator lives with the checker code
+
+        ref = c_oracle.reference_kernels()
+        if ref is None:
+            return None
+        vp = ctypes.c_void_p
+        sm_count = torch.cuda.get_device_properties(device).multi_processor_count
+        fused = rows < 16 and ref.sage_ref_fuses_permutation(n, k)
+        parts = ref.sage_ref_gemm_splits(rows, n, k, sm_count) if rows >= 16 else 1
+        workspace = torch.empty(max(parts * rows * n, 1), dtype=torch.float32, device=device)
+        out = torch.empty(rows, n, dtype=torch.float16, device=device)
+
+        def call(layer):
+            stream = vp(torch.cuda.current_stream(device).cuda_stream)
+            # (the reference gathers with index_select when its kernel does not fuse the permutation)
+            xin = x if fused else x.index_select(-1, layer.permutation.long())
+            common = (vp(xin.data_ptr()), vp(layer.packed_codes.data_ptr()), vp(layer.radius_codes.data_ptr()),
+                      vp(layer.radius_grid.data_ptr()), vp(layer.codebook.data_ptr()), vp(out.data_ptr()))
+            if rows < 16:
+                ref.sage_ref_gemv(*common, vp(layer.permutation.data_ptr()) if fused else None, rows, n, k, 256, stream)
+            else:
+                ref.sage_ref_gemm(*common, vp(workspace.data_ptr()), parts, rows, n, k, 256, stream)
+    else:
+        def call(layer):
+            layer(x)
+
+    side = torch.cuda.Stream(device=device)
+    side.wait_stream(torch.cuda.current_stream(device))
+    with torch.cuda.stream(side):
+        for layer in layers:
+            call(layer)
+    torch.cuda.current_stream(device).wait_stream(side)
+    torch.cuda.synchronize(device)
+    graph = torch.cuda.CUDAGraph()
+    with torch.cuda.graph(graph):
+        for layer in layers:
+            call(layer)
+    for _ in range(3):
+        graph.replay()
+    start, stop = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    start.record()
+    for _ in range(steps):
+        graph.replay()
+    stop.record()
+    torch.cuda.synchronize(device)
+    return {"us": start.elapsed_time(stop) * 1000.0 / (steps * copies), "bytes": one, "copies": copies}
+
+
+def kernel_records(device, peaks: dict) -> dict:
+    """The per-kernel figures the headline line carries beside the model number: the batch-1
+    GEMV and a 16-row decode call on the Qwen3-4B gate_proj shape (HBM roofline), the prompt GEMM
+    on two shapes (tensor roofline, activation gather included), and the reference project's own
+    kernels on the same inputs where that comparator was built."""
+    hbm, tensor = peaks["hbm_gbs"], peaks["bf16_tflops"]
+    records = {}
+    for name, (k, n, rows) in {"gemv_2560x9728_m1": (2560, 9728, 1), "gemv_9728x2560_m1": (9728, 2560, 1),
+                               "skinny_2560x9728_m16": (2560, 9728, 16)}.items():
+        ours = time_linear(k, n, rows, device)
+        theirs = time_linear(k, n, rows, device, reference=True)
+        gbs = ours["bytes"] / ours["us"] / 1e3
+        records[name] = {"us": round(ours["us"], 3), "gb_s": round(gbs, 1), "frac_of_hbm_peak": round(gbs / hbm, 4),
+                         "reference_kernel_us": round(theirs["us"], 3) if theirs else None}
+    for name, (k, n, rows) in {"gemm_2560x9728_m512": (2560, 9728, 512), "gemm_5120x25600_m2048": (5120, 25600, 2048)}.items():
+        ours = time_linear(k, n, rows, device, steps=3)
+        theirs = time_linear(k, n, rows, device, steps=3, reference=True)
+        tflops = 2.0 * rows * k * n / ours["us"] / 1e6
+        records[name] = {"us": round(ours["us"], 2), "tflop_s": round(tflops, 1),
+                         "frac_of_tensor_peak": round(tflops / tensor, 4), "gather_pass_included": True,
+                         "reference_kernel_us": round(theirs["us"], 2) if theirs else None}
+    return records
+
 def run_single_linear(args) -> None:
     """`--workload linear:K:N:M` - one packed-linear shape cycled over enough distinct weight
     copies to exceed L2, one CUDA graph of all copies per step.  This is the small case used for
@@ -369,9 +469,9 @@ def run_model(args) -> None:
         stop.record()
         barrier()
         elapsed_ms = start.elapsed_time(stop)
-        if elapsed_ms < 500:  # keep the GPU busy long enough for a few clock samples
+        if elapsed_ms < 1500:  # keep the GPU under the same load long enough for several clock samples
             hold = model.positions.clone()
-            for _ in range(int(500 / max(elapsed_ms / args.steps, 1e-3))):
+            for _ in range(int((1500 - elapsed_ms) / max(elapsed_ms / args.steps, 1e-3))):
                 model.positions.copy_(hold)  # stay inside the KV cache
                 model.graph_no_head.replay()
             model.positions.copy_(hold)
@@ -436,11 +536,50 @@ def run_model(args) -> None:
     if world > 1:
         dist.all_reduce(times, op=dist.ReduceOp.MAX)
     elapsed_ms, e2e_ms = (float(v) for v in times.tolist())
+    # figures that explain the headline, measured in this same process (rank 0's GPU)
+    kernels, batch8, sharded = None, None, None
+    packed_bytes, launches_per_step = model.packed_bytes, (model.sage_launches_per_step, model.glue_launches_per_step)
+    step_bytes = model.bytes_per_token(context)
+    del model, sage_graph
+    torch.cuda.empty_cache()
+    if rank == 0 and not args.quick:
+        kernels = kernel_records(device, all_peaks())
+        many = PackedQwen3(QWEN3_4B, device, seed=0, max_seq=160, batch=8, max_new=96)
+        many.capture()
+        many.prefill(torch.randint(3, QWEN3_4B.vocab, (8, 64), generator=torch.Generator().manual_seed(5)))
+        for _ in range(3):
+            many.graph.replay()
+        b0, b1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        b0.record()
+        for _ in range(32):
+            many.graph.replay()
+        b1.record()
+        torch.cuda.synchronize()
+        batch8 = {"ms_per_step": b0.elapsed_time(b1) / 32, "tok_s": 8 * 32 * 1000.0 / b0.elapsed_time(b1),
+                  "note": "Qwen3-4B, 8 sequences decoded together after 64-token prompts, one CUDA graph per step"}
+        del many
+        torch.cuda.empty_cache()
+    if world > 1 and not args.quick:
+        # the sharded configurations in the same job: tensor parallel (Qwen3-32B shape) and expert
+        # parallel (Qwen3-30B-A3B shape) over all ranks, and rank 0's own one-GPU runs of the same
+        # models for the strong-scaling efficiency
+        cpu_group = dist.new_group(backend="gloo")
+        sharded = {}
+        for kind, batch in (("tp32b", 1), ("ep30b", 1), ("ep30b", 32)):
+            many_gpus = measure_sharded(kind, args, device, dist.group.WORLD, cpu_group, world, rank, batch=batch)
+            torch.cuda.synchronize()
+            dist.barrier(group=cpu_group)
+            one_gpu = measure_sharded(kind, args, device, None, None, 1, 0, batch=batch) if rank == 0 else None
+            dist.barrier(group=cpu_group)
+            if rank == 0:
+                many_gpus["one_gpu_tok_s"] = one_gpu["value"]
+                many_gpus["one_gpu_ms_per_step"] = one_gpu["ms_per_step"]
+                many_gpus["strong_scaling_efficiency"] = many_gpus["value"] / one_gpu["value"] / world
+                sharded[f"{kind}_batch{batch}"] = many_gpus
     if rank == 0:
         ms_per_step = elapsed_ms / args.steps
         peak, peak_kind = measured_peaks()
-        achieved = (model.packed_bytes / sage_launches) / sage_seconds / 1e9
-        step_bytes = model.bytes_per_token(context)
+        achieved = (packed_bytes / sage_launches) / sage_seconds / 1e9
         cpu_seconds, cores = cpu_layer_seconds(3, 0)
         line = {
             "metric": METRIC,
@@ -467,8 +606,9 @@ def run_model(args) -> None:
                 "context_at_midpoint": context,
                 "step_hbm_bytes": step_bytes,
                 "step_hbm_gbs": step_bytes / (ms_per_step / 1000.0) / 1e9,
-                "kernels_per_step": {"sage_linear": int(model.sage_launches_per_step),
-                                     "glue": int(model.glue_launches_per_step)},
+                "kernels_per_step": {"sage_linear": int(launches_per_step[0]), "glue": int(launches_per_step[1])},
+                "timed_steps_note": f"{args.steps} consecutive decode steps timed (the configuration's 256-token "
+                                    "generation is a matter of --steps 256); the context grows by one position per step",
                 "l2_policy": "inputs larger than L2: 1.92 GB of weights stream per step",
                 "parallelism": f"replicas x{world}" if world > 1 else "single GPU",
             },
@@ -478,13 +618,19 @@ def run_model(args) -> None:
                 "peak": peak,
                 "unit": "GB/s",
                 "frac": achieved / peak,
-                "traffic": None,
+                # DRAM bytes per launch: the ncu capture of one gate_proj launch read 1.003 x its
+                # algorithmic bytes and wrote none (profiles/); scaled to this graph's average launch
+                "traffic": 1.003 * packed_bytes / sage_launches,
+                "traffic_how": "ncu dram__bytes_read+write of one 2560->9728 M=1 launch = 1.003 x algorithmic, scaled by bytes",
                 "kernel": "sage_skinny_kernel",
                 "peak_kind": f"of {peak_kind}",
-                "bytes_per_launch": model.packed_bytes / sage_launches,
+                "bytes_per_launch": packed_bytes / sage_launches,
                 "us_per_launch": sage_seconds * 1e6,
                 "how": "CUDA events around 20 replays of a graph holding only the model's packed-linear launches",
             },
+            "kernels": kernels,
+            "decode_batch8": batch8,
+            "sharded": sharded,
             "cpu_baseline": {
                 "value": 1.0 / (cpu_seconds * QWEN3_4B_LAYERS),
                 "unit": UNIT,
@@ -499,12 +645,17 @@ def run_model(args) -> None:
                 "h2d_bytes_per_step": 8,
                 "d2h_bytes_per_step": 8,
             },
-            "gpu_launches": int((model.sage_launches_per_step + model.glue_launches_per_step) * args.steps),
+            "gpu_launches": int((launches_per_step[0] + launches_per_step[1]) * args.steps),
             "clocks": clocks,
         }
         print(json.dumps(line), flush=True)
     if world > 1:
-        dist.destroy_process_group()
+        if sharded is None:
+            dist.destroy_process_group()
+        else:  # no NCCL teardown under live CUDA graphs that captured collectives (see run_tp)
+            sys.stdout.flush()
+            dist.barrier(group=cpu_group)
+            os._exit(0)
 
 
 def run_report(args) -> None:
@@ -528,18 +679,108 @@ def run_report(args) -> None:
                       "rows": [[m, p, metric, round(value, 3), unit] for m, p, metric, value, unit in rows]}), flush=True)
 
 
-def run_tp(args) -> None:
-    """`--workload tp32b`: Qwen3-32B shape, SAGE-packed, batch-1 decode with the linears
-    tensor-parallel over all ranks (q/k/v/gate/up column-parallel, o/down row-parallel +
-    NCCL all-reduce, vocabulary-parallel lm_head + all-gather).  One sequence for the whole
-    job, so `scaling` is "strong"."""
+def measure_sharded(kind: str, args, device, group, cpu_group, world: int, rank: int, batch: int = 1):
+    """One strong-scaling measurement: `kind` "tp32b" (Qwen3-32B shape, column/row tensor
+    parallel, NCCL all-reduce) or "ep30b" (Qwen3-30B-A3B shape, expert parallel) on the ranks of
+    `group` (None: this GPU alone), batch-`batch` greedy decode.  Returns the record of rank 0's
+    line (every rank gets the timing fields)."""
     import torch
     import torch.distributed as dist
 
     from sage_b200.qwen3 import QWEN3_30B_A3B, QWEN3_32B, PackedQwen3
 
-    expert_parallel = args.workload == "ep30b"
+    expert_parallel = kind == "ep30b"
     config = QWEN3_30B_A3B if expert_parallel else QWEN3_32B
+    sharded = group is not None and world > 1
+    warmup = max(args.warmup, 3)
+    prompt_length = min(args.prompt, 64)
+    steps = args.steps
+    model = PackedQwen3(config, device, seed=0, max_seq=prompt_length + 2 * (steps + warmup) + 16,
+                        batch=batch, max_new=2 * (steps + warmup) + 16,
+                        tp_group=group if sharded and not expert_parallel else None,
+                        perm_blocks=1 if expert_parallel else 8,
+                        ep_group=group if sharded and expert_parallel else None)
+    model.capture()
+    prompt = torch.randint(3, config.vocab, (batch, prompt_length), generator=torch.Generator().manual_seed(7))
+    model.prefill(prompt)
+
+    def barrier():
+        torch.cuda.synchronize()
+        if sharded:
+            dist.barrier(group=cpu_group)
+        torch.cuda.synchronize()
+
+    for _ in range(warmup):
+        model.graph.replay()
+    start, stop = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    barrier()
+    with ClockSampler(device.index) as sampler:
+        start.record()
+        for _ in range(steps):
+            model.graph.replay()
+        stop.record()
+        barrier()
+    clocks = sampler.summary()
+    tokens = model.log[0, : warmup + steps + 1].tolist()
+    # end to end: token ids from pinned host memory in, next tokens read back, every step
+    host_token = torch.zeros(batch, dtype=torch.int64).pin_memory()
+    host_next = torch.zeros(batch, dtype=torch.int64).pin_memory()
+    host_token.copy_(model.tokens)
+    barrier()
+    e2e_begin = time.perf_counter()
+    for _ in range(steps):
+        model.tokens.copy_(host_token, non_blocking=True)
+        model.graph.replay()
+        host_next.copy_(model.tokens, non_blocking=True)
+        torch.cuda.synchronize()
+        host_token.copy_(host_next)
+    e2e_ms = 1000.0 * (time.perf_counter() - e2e_begin)
+    barrier()
+    times = torch.tensor([start.elapsed_time(stop), e2e_ms], dtype=torch.float64)
+    if sharded:
+        dist.all_reduce(times, op=dist.ReduceOp.MAX, group=cpu_group)
+    ms_per_step = float(times[0]) / steps
+    peak, peak_kind = measured_peaks()
+    step_bytes = model.bytes_per_token(prompt_length + warmup + steps // 2)
+    collective = "none"
+    calls = 0
+    if sharded and expert_parallel:
+        collective = model.ep_collective
+        calls = model.collective_calls_per_step
+    elif sharded:
+        collective, calls = "nccl all_reduce (row-parallel partial sums) + all_gather (logits)", 2 * config.layers + 1
+    record = {
+        "metric": ("qwen3_30b_a3b" if expert_parallel else "qwen3_32b") + f"_sage_2.25bpw_batch{batch}_decode_tok_s",
+        "value": batch * 1000.0 / ms_per_step,
+        "unit": UNIT,
+        "n_gpus": world if sharded else 1,
+        "steps": steps,
+        "warmup": warmup,
+        "ms_per_step": ms_per_step,
+        "batch": batch,
+        "parallelism": (f"ep{world}" if expert_parallel else f"tp{world}") if sharded else "single GPU",
+        "collective": collective,
+        "collective_calls_per_step": calls,
+        "per_rank_hbm_bytes_per_step": step_bytes,
+        "per_rank_hbm_gbs": step_bytes / (ms_per_step / 1000.0) / 1e9,
+        "hbm_frac": step_bytes / (ms_per_step / 1000.0) / 1e9 / peak,
+        "peak_kind": f"of {peak_kind}",
+        "e2e_tok_s": batch * 1000.0 * steps / float(times[1]),
+        "first_tokens": tokens[:8],
+        "gpu_launches": int((model.sage_launches_per_step + model.glue_launches_per_step) * steps),
+        "clocks": clocks,
+    }
+    del model
+    torch.cuda.empty_cache()
+    return record
+
+
+def run_tp(args) -> None:
+    """`--workload tp32b` / `ep30b`: the strong-scaling runs on their own (one sequence for the
+    whole job).  Qwen3-32B shape: q/k/v/gate/up column-parallel, o/down row-parallel + NCCL
+    all-reduce, vocabulary-parallel lm_head + all-gather.  Qwen3-30B-A3B shape: expert parallel."""
+    import torch
+    import torch.distributed as dist
 
     rank = int(os.environ.get("RANK", "0"))
     world = int(os.environ.get("WORLD_SIZE", "1"))
@@ -554,89 +795,27 @@ def run_tp(args) -> None:
         # NCCL collective issued after NCCL collectives were captured into CUDA graphs did not
         # return on this software stack (seen with a 2-GPU run), a CPU group does.
         cpu_group = dist.new_group(backend="gloo")
-    warmup = max(args.warmup, 3)
-    prompt_length = min(args.prompt, 64)
-    model = PackedQwen3(config, device, seed=0, max_seq=prompt_length + 2 * (args.steps + warmup) + 16,
-                        batch=1, max_new=2 * (args.steps + warmup) + 16,
-                        tp_group=None if expert_parallel else group, perm_blocks=1 if expert_parallel else 8,
-                        ep_group=group if expert_parallel else None)
-    model.capture()
-    prompt = torch.randint(3, config.vocab, (1, prompt_length), generator=torch.Generator().manual_seed(7))
-    model.prefill(prompt)
-
-    def barrier():
-        torch.cuda.synchronize()
-        if world > 1:
-            dist.barrier(group=cpu_group)
-        torch.cuda.synchronize()
-
-    for _ in range(warmup):
-        model.graph.replay()
-    start, stop = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
-    barrier()
-    with ClockSampler(local) as sampler:
-        start.record()
-        for _ in range(args.steps):
-            model.graph.replay()
-        stop.record()
-        barrier()
-    clocks = sampler.summary()
-    tokens = model.log[0, : warmup + args.steps + 1].tolist()
-    # end to end: token id from pinned host memory in, next token read back, every step
-    host_token = torch.zeros(1, dtype=torch.int64).pin_memory()
-    host_next = torch.zeros(1, dtype=torch.int64).pin_memory()
-    host_token.copy_(model.tokens)
-    barrier()
-    e2e_begin = time.perf_counter()
-    for _ in range(args.steps):
-        model.tokens.copy_(host_token, non_blocking=True)
-        model.graph.replay()
-        host_next.copy_(model.tokens, non_blocking=True)
-        torch.cuda.synchronize()
-        host_token.copy_(host_next)
-    e2e_ms = 1000.0 * (time.perf_counter() - e2e_begin)
-    barrier()
-    times = torch.tensor([start.elapsed_time(stop), e2e_ms], dtype=torch.float64)
-    if world > 1:
-        dist.all_reduce(times, op=dist.ReduceOp.MAX, group=cpu_group)
+    expert_parallel = args.workload == "ep30b"
+    record = measure_sharded(args.workload, args, device, group, cpu_group, world, rank, batch=args.batch)
     if rank == 0:
-        ms_per_step = float(times[0]) / args.steps
-        peak, peak_kind = measured_peaks()
-        step_bytes = model.bytes_per_token(prompt_length + warmup + args.steps // 2)
-        line = {
-            "metric": ("qwen3_30b_a3b" if expert_parallel else "qwen3_32b") + "_sage_2.25bpw_batch1_decode_tok_s",
-            "value": 1000.0 / ms_per_step,
-            "unit": UNIT,
-            "n_gpus": world,
-            "steps": args.steps,
-            "warmup": warmup,
-            "ms_per_step": ms_per_step,
-            "higher_is_better": True,
-            "scaling": "strong",
-            "vs_baseline": None,
-            "dtype": "f16 products, f32 accumulate",
-            "data": "synthetic",
+        line = dict(record)
+        line.update({
+            "higher_is_better": True, "scaling": "strong", "vs_baseline": None,
+            "dtype": "f16 products, f32 accumulate", "data": "synthetic",
             "config": {
                 "workload": ("Qwen3-30B-A3B shape (48 layers, hidden 2048, 32/4 heads, 128 experts top-8, "
                              "moe_inter 768), random-init, attention and expert linears SAGE-packed, FP16 router, "
-                             "batch 1 greedy decode, expert parallel (attention and router replicated, each "
-                             "rank runs its block of experts, outputs summed with an all-reduce)"
+                             "greedy decode, expert parallel (attention and router replicated, each rank runs its "
+                             "block of experts)"
                              if expert_parallel else
                              "Qwen3-32B shape (64 layers, hidden 5120, 64/8 heads, inter 25600), random-init, "
-                             "SAGE-packed, batch 1 greedy decode, tensor parallel"),
-                "parallelism": f"ep{world}" if expert_parallel else f"tp{world}",
+                             "SAGE-packed, greedy decode, tensor parallel"),
+                "parallelism": record["parallelism"], "batch": record["batch"],
                 "row_parallel_permutation": "block permutation, 8 blocks (each rank gathers inside its slice)",
-                "per_rank_hbm_bytes_per_step": step_bytes,
-                "per_rank_hbm_gbs": step_bytes / (ms_per_step / 1000.0) / 1e9,
-                "hbm_frac": step_bytes / (ms_per_step / 1000.0) / 1e9 / peak,
-                "peak_kind": f"of {peak_kind}",
-                "first_tokens": tokens[:8],
             },
-            "e2e": {"value": 1000.0 * args.steps / float(times[1]), "unit": UNIT, "h2d_bytes_per_step": 8,
-                    "d2h_bytes_per_step": 8},
-            "gpu_launches": int((model.sage_launches_per_step + model.glue_launches_per_step) * args.steps),
-            "clocks": clocks,
-        }
+            "e2e": {"value": record["e2e_tok_s"], "unit": UNIT, "h2d_bytes_per_step": 8 * record["batch"],
+                    "d2h_bytes_per_step": 8 * record["batch"]},
+        })
         print(json.dumps(line), flush=True)
     if world > 1:
         # leave without tearing the NCCL communicator down under live graphs (see above)
@@ -811,7 +990,10 @@ def main() -> None:
     parser.add_argument("--impl", choices=["ours", "reference"], default="ours")
     parser.add_argument("--workload", default="decode_model")
     parser.add_argument("--prompt", type=int, default=512)
+    parser.add_argument("--batch", type=int, default=1, help="sequences decoded together (tp32b / ep30b workloads)")
     parser.add_argument("--output", default="reports", help="folder for the files of --workload report")
+    parser.add_argument("--quick", action="store_true",
+                        help="headline measurement only: skip the per-kernel, batch-8 and sharded sub-records")
     args = parser.parse_args()
     if args.impl == "reference":
         run_reference(args)

@@ -50,9 +50,10 @@ struct GemmParams {
   int *status;          // device-visible status word (0 = ok)
   int rows, n, k, groups, tiles;
   int entries, dbits;
-  int tokens_per_cta;   // TN: multiple of 16, 16..256
+  int tokens_per_cta;   // TN: multiple of 16, 16..256 (tokens of ONE accumulator)
   int stages;
-  int tmem_columns;     // power of two >= max(32, TN)
+  int tmem_columns;     // power of two >= max(32, TN); 512 with two accumulators
+  int accumulators;     // 1 or 2 token blocks per CTA: one decoded weight stage feeds both
 };
 
 // ---------------------------------------------------------------- PTX wrappers
@@ -182,7 +183,9 @@ __global__ void __launch_bounds__(kGemmThreads, 1)
   const uint32_t base = (raw + 1023u) & ~1023u;
   unsigned char *aligned = raw_shared + (base - raw);
   const int tn = p.tokens_per_cta;
-  const int b_stage_bytes = tn * kStageK * 2;
+  const int accumulators = p.accumulators;
+  const int b_tile_bytes = tn * kStageK * 2;          // one token block's activations of a stage
+  const int b_stage_bytes = accumulators * b_tile_bytes;
   const uint32_t a_base = base;
   const uint32_t b_base = a_base + p.stages * kAStageBytes;
   const uint32_t book_address = b_base + p.stages * b_stage_bytes;
@@ -197,7 +200,7 @@ __global__ void __launch_bounds__(kGemmThreads, 1)
   const int warp = tid >> 5;
   const int lane = tid & 31;
   const int row_block = blockIdx.x;   // 128 output rows
-  const int token_block = blockIdx.y; // TN tokens
+  const int token_block = blockIdx.y * accumulators;  // first of this CTA's blocks of TN tokens
   const int stages_k = p.k / kStageK;
 
   if (tid == 0) {
@@ -302,16 +305,18 @@ __global__ void __launch_bounds__(kGemmThreads, 1)
       const int column_begin = column_half * columns_per_half;
       const int column_end = min(tn, column_begin + columns_per_half);
       const int out = row_block * kTileRows + quarter * 32 + lane;
-      for (int c = column_begin; c < column_end; c += 16) {
-        uint32_t r[16];
-        tmem_load_16(tmem_base + (static_cast<uint32_t>(quarter * 32) << 16) + c, r);
-        tmem_load_wait();
-        if (out < p.n) {
+      for (int a = 0; a < accumulators; ++a) {
+        for (int c = column_begin; c < column_end; c += 16) {
+          uint32_t r[16];
+          tmem_load_16(tmem_base + (static_cast<uint32_t>(quarter * 32) << 16) + a * 256 + c, r);
+          tmem_load_wait();
+          if (out < p.n) {
 #pragma unroll
-          for (int i = 0; i < 16; ++i) {
-            const int token = token_block * tn + c + i;
-            if (token < p.rows)
-              p.y[static_cast<size_t>(token) * p.n + out] = __float2half_rn(__uint_as_float(r[i]));
+            for (int i = 0; i < 16; ++i) {
+              const int token = (token_block + a) * tn + c + i;
+              if (token < p.rows)
+                p.y[static_cast<size_t>(token) * p.n + out] = __float2half_rn(__uint_as_float(r[i]));
+            }
           }
         }
       }
@@ -326,7 +331,9 @@ __global__ void __launch_bounds__(kGemmThreads, 1)
         alive = bounded_wait(empty_bar(s), phase ^ 1u, abort_ptr, p.status);
         if (!alive) break;
         mbarrier_arrive_expect_tx(full_bar(s), static_cast<uint32_t>(b_stage_bytes));
-        tma_load_2d(b_base + s * b_stage_bytes, &x_map, ks * kStageK, token_block * tn, full_bar(s));
+        for (int a = 0; a < accumulators; ++a)  // (a block past the last token reads the fill value)
+          tma_load_2d(b_base + s * b_stage_bytes + a * b_tile_bytes, &x_map, ks * kStageK,
+                      (token_block + a) * tn, full_bar(s));
       }
     }
   } else {
@@ -341,11 +348,13 @@ __global__ void __launch_bounds__(kGemmThreads, 1)
         if (!alive) break;
         tcgen05_fence_after();
         const uint64_t a_desc = smem_descriptor(a_base + s * kAStageBytes);
-        const uint64_t b_desc = smem_descriptor(b_base + s * b_stage_bytes);
+        for (int a = 0; a < accumulators; ++a) {
+          const uint64_t b_desc = smem_descriptor(b_base + s * b_stage_bytes + a * b_tile_bytes);
 #pragma unroll
-        for (int j = 0; j < kStageK / 16; ++j) {
-          // advancing 16 channels = 32 bytes = 2 units of the descriptor's address field
-          umma_f16(tmem_base, a_desc + 2 * j, b_desc + 2 * j, idesc, (ks > 0 || j > 0) ? 1u : 0u);
+          for (int j = 0; j < kStageK / 16; ++j) {
+            // advancing 16 channels = 32 bytes = 2 units of the descriptor's address field
+            umma_f16(tmem_base + a * 256, a_desc + 2 * j, b_desc + 2 * j, idesc, (ks > 0 || j > 0) ? 1u : 0u);
+          }
         }
         umma_commit(empty_bar(s));
       }
@@ -424,6 +433,7 @@ cudaError_t launch_gather(const __half *x, const int32_t *perm, __half *xq, int 
 
 GemmPlan plan_gemm_tc(int rows, int n, int k, int sm_count) {
   (void)k;
+  (void)sm_count;
   GemmPlan plan{};
   int tn = (rows + 15) / 16 * 16;
   if (tn > 256) {
@@ -434,16 +444,19 @@ GemmPlan plan_gemm_tc(int rows, int n, int k, int sm_count) {
   plan.tokens_per_cta = tn;
   plan.token_blocks = (rows + tn - 1) / tn;
   plan.row_blocks = (n + kTileRows - 1) / kTileRows;
-  const int stage_bytes = kAStageBytes + tn * kStageK * 2;
+  // Two token blocks per CTA share every decoded weight stage (two accumulators in tensor
+  // memory): the decode work per output halves.  Worth it as soon as there are two blocks; the
+  // activation stage doubles, so the pipeline is shallower.
+  plan.accumulators = plan.token_blocks >= 2 ? 2 : 1;
+  const int stage_bytes = kAStageBytes + plan.accumulators * tn * kStageK * 2;
   int stages = (200 * 1024) / stage_bytes;
   if (stages > kMaxStages) stages = kMaxStages;
   if (stages < 2) stages = 2;
   plan.stages = stages;
   int columns = 32;
   while (columns < tn) columns *= 2;
-  plan.tmem_columns = columns;
+  plan.tmem_columns = plan.accumulators == 2 ? 512 : columns;
   plan.shared_bytes = static_cast<size_t>(stages) * stage_bytes + 256 * 16 + (2 * kMaxStages + 1) * 8 + 1024;
-  (void)sm_count;
   return plan;
 }
 
@@ -486,7 +499,8 @@ cudaError_t launch_gemm_tc(const __half *xq, const uint32_t *codes, const uint32
   p.tokens_per_cta = plan.tokens_per_cta;
   p.stages = plan.stages;
   p.tmem_columns = plan.tmem_columns;
-  const dim3 blocks(plan.row_blocks, plan.token_blocks);
+  p.accumulators = plan.accumulators;
+  const dim3 blocks(plan.row_blocks, (plan.token_blocks + plan.accumulators - 1) / plan.accumulators);
   sage_gemm_tc_kernel<<<blocks, kGemmThreads, plan.shared_bytes, stream>>>(p, map);
   return cudaGetLastError();
 }

@@ -119,6 +119,7 @@ struct GemmPlan {
   int row_blocks;       // blocks of 128 output rows
   int stages;
   int tmem_columns;
+  int accumulators;     // token blocks per CTA (1 or 2) sharing each decoded weight stage
   size_t shared_bytes;
 };
 

@@ -766,7 +766,16 @@ SkinnyPlan plan_skinny(int rows, int n, int k, int entries, int sm_count, const 
 
   // K slices: as few as keep one slice's activations within the shared-memory budget
   // (a single row may take more: its launch streams the weights through rings if need be)
-  const size_t x_budget = rows == 1 ? 64 * 1024 : 40 * 1024;
+  // Several rows: whatever one resident wave's packed share and the warps' tables leave of the
+  // CTA's shared memory (at least 40 KiB) - slicing K costs a trip through scratch per tile.
+  size_t x_budget = 64 * 1024;
+  if (rows > 1) {
+    long long share_units = (static_cast<long long>(tiles) * groups + resident - 1) / resident;
+    if (share_units > unit_cap) share_units = unit_cap;
+    const size_t tables = static_cast<size_t>(plan.warps) * 4 * plan.column_blocks * 512;
+    const size_t taken = static_cast<size_t>(share_units) * kUnitBytes + tables + 4096;
+    x_budget = taken + 40 * 1024 < static_cast<size_t>(kMaxDynamicShared) ? kMaxDynamicShared - taken : 40 * 1024;
+  }
   // a single row with a permutation is gathered through a linear copy in shared memory; the
   // fused residual add + RMSNorm keeps the norm weights behind it
   const size_t lin_bytes = rows == 1 ? (static_cast<size_t>(k) * (act_kind == 1 ? 4 : 2) + 127) / 128 * 128 : 0;

@@ -223,6 +223,9 @@ class PackedQwen3:
             self.route_weights = torch.zeros(batch, c.top_k, dtype=torch.float32, device=self.device)
         self.graph = None
         self.graph_no_head = None
+        # what the expert-parallel exchange of a step is, for reports
+        self.ep_collective = "nccl all_reduce of the ranks' expert outputs (every rank holds every token)"
+        self.collective_calls_per_step = c.layers if self.ep_world > 1 else 0
         # The whole token as one persistent kernel (`sageb200_mega_step`).  Prepared when the model
         # fits it; `use_mega` selects it for the decode step before `capture()`.  It is off by
         # default: as measured on B200 the per-launch path is still the faster one.
