@@ -695,13 +695,20 @@ def measure_sharded(kind: str, args, device, group, cpu_group, world: int, rank:
     warmup = max(args.warmup, 3)
     prompt_length = min(args.prompt, 64)
     steps = args.steps
+    # Expert parallelism beyond 16 sequences: every rank decodes its own share of the sequences and
+    # the (token, expert) slots travel by all-to-all; up to 16 every rank decodes all of them and the
+    # expert outputs are summed by all-reduce.  `batch` is the whole job's either way.
+    exchange = expert_parallel and batch > 16
+    local_batch = batch // world if exchange and sharded else batch
     model = PackedQwen3(config, device, seed=0, max_seq=prompt_length + 2 * (steps + warmup) + 16,
-                        batch=batch, max_new=2 * (steps + warmup) + 16,
+                        batch=local_batch, max_new=2 * (steps + warmup) + 16,
                         tp_group=group if sharded and not expert_parallel else None,
                         perm_blocks=1 if expert_parallel else 8,
-                        ep_group=group if sharded and expert_parallel else None)
+                        ep_group=group if sharded and expert_parallel else None,
+                        ep_mode="all_to_all" if exchange else "all_reduce")
     model.capture()
-    prompt = torch.randint(3, config.vocab, (batch, prompt_length), generator=torch.Generator().manual_seed(7))
+    prompt = torch.randint(3, config.vocab, (local_batch, prompt_length),
+                           generator=torch.Generator().manual_seed(7 + (rank if exchange else 0)))
     model.prefill(prompt)
 
     def barrier():
@@ -723,8 +730,8 @@ def measure_sharded(kind: str, args, device, group, cpu_group, world: int, rank:
     clocks = sampler.summary()
     tokens = model.log[0, : warmup + steps + 1].tolist()
     # end to end: token ids from pinned host memory in, next tokens read back, every step
-    host_token = torch.zeros(batch, dtype=torch.int64).pin_memory()
-    host_next = torch.zeros(batch, dtype=torch.int64).pin_memory()
+    host_token = torch.zeros(local_batch, dtype=torch.int64).pin_memory()
+    host_next = torch.zeros(local_batch, dtype=torch.int64).pin_memory()
     host_token.copy_(model.tokens)
     barrier()
     e2e_begin = time.perf_counter()

@@ -189,6 +189,23 @@ int sageb200_experts(const void *x, long long x_slot_stride, const sageb200_expe
                      void *workspace, size_t workspace_bytes, void *stream);
 
 /*
+ * Routed experts, a block of up to 16 activation rows per expert visit (the compute of an
+ * all-to-all expert-parallel exchange, where the rows an expert received have been sorted
+ * together): for every block b and stack t
+ *   ys[t][b][r][:] = W(stack t, expert block_expert_ids[b]) . x[b][r][:]      r < rows
+ * x is [blocks][rows][k], ys[t] is [blocks][rows][n_t]; `block_expert_ids` is a DEVICE array of
+ * `blocks` global expert indices.  A block whose id is negative or outside the stack is skipped
+ * (its outputs are left untouched), so a caller sizes `blocks` for the worst case and marks the
+ * unused ones with -1.  An expert that received more than `rows` rows simply owns several
+ * blocks.  The packed weights of an expert are read once per block.
+ * No counterpart in the reference (no packed MoE module).
+ */
+size_t sageb200_expert_blocks_workspace_bytes(const sageb200_expert_stack *stacks_host, int stack_count, int rows);
+int sageb200_expert_blocks(const void *x, const sageb200_expert_stack *stacks_host, void *const *ys_host,
+                           int stack_count, const int32_t *block_expert_ids, int blocks, int rows, void *workspace,
+                           size_t workspace_bytes, void *stream);
+
+/*
  * Dequantise to a dense fp16 matrix w[n][k]: bit-exact
  *   w = fp16_rn(float(+-dir) * fmaf(float(radius_code), step, min))
  * (reference csrc/sage/sage_gemm_cuda.cu:117-131 and tests/inference/reference.py:39-49).

@@ -31,6 +31,8 @@ EXPORTED = (
     "sageb200_linear_grouped_fused",
     "sageb200_experts_workspace_bytes",
     "sageb200_experts",
+    "sageb200_expert_blocks_workspace_bytes",
+    "sageb200_expert_blocks",
     "sageb200_dequant",
     "sageb200_pack_spherical",
     "sageb200_host_staging_bytes",
@@ -210,6 +212,10 @@ def load() -> ctypes.CDLL:
     lib.sageb200_sph_dequant.argtypes = [vp] * 6 + [ci] * 2 + [vp]
     lib.sageb200_debug_plan.restype = ci
     lib.sageb200_debug_plan.argtypes = [ci] * 5 + [ctypes.POINTER(ci)]
+    lib.sageb200_expert_blocks_workspace_bytes.restype = sz
+    lib.sageb200_expert_blocks_workspace_bytes.argtypes = [ctypes.POINTER(ExpertStack), ci, ci]
+    lib.sageb200_expert_blocks.restype = ci
+    lib.sageb200_expert_blocks.argtypes = [vp, ctypes.POINTER(ExpertStack), ctypes.POINTER(vp), ci, vp, ci, ci, vp, sz, vp]
     lib.sageb200_pack_spherical.restype = ci
     lib.sageb200_pack_spherical.argtypes = [vp] * 7 + [ci] * 4 + [vp]
     lib.sageb200_clear_status.restype = ci

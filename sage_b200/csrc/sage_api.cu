@@ -195,6 +195,11 @@ struct StageJob {
   const int32_t *perm;  // null: identity
   __half *xq;
   int rows, k;
+  // routed experts (null: none): the permutation is that of expert expert_ids[expert_slot] inside
+  // a stack of expert_count experts starting at global expert expert_first; a slot whose expert
+  // lives elsewhere (or is negative: an empty block) is skipped
+  const int *expert_ids;
+  int expert_slot, expert_first, expert_count;
 };
 struct StageParams {
   StageJob job[kMaxGrouped];
@@ -207,10 +212,15 @@ struct StageParams {
 __global__ void __launch_bounds__(256) stage_rows_kernel(const __grid_constant__ StageParams params) {
   extern __shared__ __half row_shared[];
   __shared__ float sums[8];
-  const StageJob &job = params.job[blockIdx.y];
+  StageJob job = params.job[blockIdx.y];
   const int row = blockIdx.x;
   if (row >= job.rows) return;
   const int k = job.k;
+  if (job.expert_ids) {
+    const int expert = __ldg(job.expert_ids + job.expert_slot) - job.expert_first;
+    if (expert < 0 || expert >= job.expert_count) return;
+    if (job.perm) job.perm += static_cast<long long>(expert) * k;
+  }
   const size_t offset = static_cast<size_t>(row) * k;
   if (params.kind == 0) {
     for (int i = threadIdx.x; i < k; i += 256) row_shared[i] = job.x[offset + i];
@@ -333,11 +343,18 @@ int run_skinny(const sageb200_problem *problems, int count, void *workspace,
       // instead of once per CTA
       __half *xq = reinterpret_cast<__half *>(scratch + offset + partial);
       if (static_cast<size_t>(in.k) * 2 <= kStageSharedLimit) {
-        staging.job[jobs++] = StageJob{out.x, in.perm, xq, in.rows, in.k};
+        staging.job[jobs] = StageJob{out.x, in.perm, xq, in.rows, in.k, nullptr, 0, 0, 0};
+        if (experts) {
+          staging.job[jobs].expert_ids = experts[i].ids;
+          staging.job[jobs].expert_slot = experts[i].slot;
+          staging.job[jobs].expert_first = experts[i].first;
+          staging.job[jobs].expert_count = experts[i].count;
+        }
+        ++jobs;
         if (in.rows > stage_rows) stage_rows = in.rows;
         if (in.k > stage_k) stage_k = in.k;
       } else {  // a row too long for the staging kernel's shared memory (never with a fused producer)
-        if (fused_rows) return SAGEB200_ERR_RANGE;
+        if (fused_rows || experts) return SAGEB200_ERR_RANGE;
         if (launch_gather(out.x, in.perm, xq, in.rows, in.k, stream, device.sm_count) != cudaSuccess) {
           cudaGetLastError();
           return SAGEB200_ERR_CUDA;
@@ -817,6 +834,56 @@ int sageb200_experts(const void *x, long long x_slot_stride, const sageb200_expe
         if (status) return status;
         const long long tiles = (stack.n + 15) / 16, groups = stack.k / 128;
         refs[count] = ExpertRef{expert_ids, slot, stack.first_expert, stack.experts,
+                                tiles * groups * 128, tiles * groups * 16, 4ll * stack.entries};
+        ++count;
+      }
+    status = run_skinny(problems, count, workspace, workspace_bytes, s, *device, nullptr, refs);
+    if (status) return status;
+  }
+  return SAGEB200_OK;
+}
+
+size_t sageb200_expert_blocks_workspace_bytes(const sageb200_expert_stack *stacks_host, int stack_count, int rows) {
+  if (!stacks_host || stack_count <= 0 || stack_count > SAGEB200_MAX_GROUPED || rows <= 0 || rows > 16) return 0;
+  sageb200_problem problems[SAGEB200_MAX_GROUPED];
+  const int per_launch = SAGEB200_MAX_GROUPED / stack_count;
+  int count = 0;
+  for (int b = 0; b < per_launch; ++b)
+    for (int t = 0; t < stack_count; ++t)
+      problems[count++] = sageb200_problem{nullptr, nullptr, nullptr, nullptr, nullptr, stacks_host[t].perm, nullptr,
+                                           rows, stacks_host[t].n, stacks_host[t].k, stacks_host[t].entries};
+  return sageb200_grouped_workspace_bytes(problems, count);
+}
+
+int sageb200_expert_blocks(const void *x, const sageb200_expert_stack *stacks_host, void *const *ys_host,
+                           int stack_count, const int32_t *block_expert_ids, int blocks, int rows, void *workspace,
+                           size_t workspace_bytes, void *stream) {
+  if (!x || !stacks_host || !ys_host || !block_expert_ids || stack_count <= 0 || stack_count > SAGEB200_MAX_GROUPED ||
+      blocks < 0 || rows < 1 || rows > 16)
+    return SAGEB200_ERR_INVALID_ARGUMENT;
+  if (blocks == 0) return SAGEB200_OK;
+  DeviceState *device = nullptr;
+  int status = device_state(&device);
+  if (status) return status;
+  cudaStream_t s = static_cast<cudaStream_t>(stream);
+  const int per_launch = SAGEB200_MAX_GROUPED / stack_count;
+  for (int begin = 0; begin < blocks; begin += per_launch) {
+    sageb200_problem problems[SAGEB200_MAX_GROUPED];
+    ExpertRef refs[SAGEB200_MAX_GROUPED];
+    int count = 0;
+    for (int block = begin; block < blocks && block < begin + per_launch; ++block)
+      for (int t = 0; t < stack_count; ++t) {
+        const sageb200_expert_stack &stack = stacks_host[t];
+        if (stack.experts <= 0 || !ys_host[t]) return SAGEB200_ERR_INVALID_ARGUMENT;
+        sageb200_problem &p = problems[count];
+        p = sageb200_problem{static_cast<const __half *>(x) + static_cast<size_t>(block) * rows * stack.k, stack.codes,
+                             stack.radii, stack.grid, stack.book, stack.perm,
+                             static_cast<__half *>(ys_host[t]) + static_cast<size_t>(block) * rows * stack.n, rows,
+                             stack.n, stack.k, stack.entries};
+        status = validate_problem(p);
+        if (status) return status;
+        const long long tiles = (stack.n + 15) / 16, groups = stack.k / 128;
+        refs[count] = ExpertRef{block_expert_ids, block, stack.first_expert, stack.experts,
                                 tiles * groups * 128, tiles * groups * 16, 4ll * stack.entries};
         ++count;
       }

@@ -10,9 +10,15 @@ packed buffers of each projection stacked along a leading expert dimension, and 
 routing arithmetic of Hugging Face `Qwen3MoeSparseMoeBlock` (softmax over all experts, top-k,
 renormalise, weighted sum of the selected experts' SwiGLU MLPs).
 
-Expert parallelism: a rank constructs the module with its contiguous block of experts
-(`first_expert`); slots routed to other ranks' experts contribute zeros, and the caller sums
-the ranks' outputs (all-reduce) — every rank sees every token, so no dispatch is needed.
+Expert parallelism, two exchanges:
+  * every rank sees every token (small batches): a rank constructs the module with its
+    contiguous block of experts (`first_expert`); slots routed to other ranks' experts
+    contribute zeros, and the caller sums the ranks' outputs (all-reduce) - no dispatch;
+  * every rank owns its own tokens (`dispatch_combine`): each (token, expert) slot travels to
+    the rank that owns the expert with `all_to_all_single`, the owner sorts what it received by
+    expert, runs each local expert over its rows (`SAGEExperts.forward_blocks`), and a second
+    `all_to_all_single` brings the outputs back.  All shapes are fixed (no host round trip), so
+    the whole exchange is captured in the decode CUDA graph.
 """
 
 from __future__ import annotations
@@ -53,6 +59,84 @@ def route(logits: torch.Tensor, top_k: int) -> tuple[torch.Tensor, torch.Tensor]
     return ids.to(torch.int32), weights
 
 
+ROWS_PER_EXPERT = 16  # rows one expert takes per step (the decode kernel's row limit)
+
+
+def dispatch_combine(x: torch.Tensor, expert_ids: torch.Tensor, weights: torch.Tensor, run_blocks, *,
+                     first_expert: int, local_experts: int, group=None, world: int = 1,
+                     rows_per_block: int = ROWS_PER_EXPERT, state: dict | None = None) -> torch.Tensor:
+    """Mixture-of-experts output of this rank's own tokens with the experts spread over `world`
+    ranks: dispatch all-to-all, per-expert compute on the owners, combine all-to-all.
+
+    x [tokens, hidden]; expert_ids int32 [tokens, top_k] (global ids); weights [tokens, top_k].
+    What a rank receives is sorted by expert and cut into blocks of `rows_per_block` rows, every
+    block belonging to one expert (an expert with many rows owns several blocks); the number of
+    blocks is fixed at its worst case, local_experts + received / rows_per_block, so nothing
+    depends on the routing and no slot is ever dropped.
+    `run_blocks(rows, block_experts)`: rows [blocks, rows_per_block, hidden], block_experts int32
+    [blocks] (global expert id, -1 for an unused block) -> [blocks, rows_per_block, hidden], row r
+    of block b being that expert's MLP of that row (rows that carry no slot hold stale values and
+    their outputs are never read).
+    Returns [tokens, hidden] in x's dtype: sum_j weights[t, j] * expert_{ids[t, j]}(x[t])."""
+    tokens, top_k = expert_ids.shape
+    hidden = x.shape[1]
+    slots = tokens * top_k
+    device = x.device
+    flat = expert_ids.reshape(slots).to(torch.int64)
+    owner = torch.div(flat, local_experts, rounding_mode="floor")                      # rank that owns the slot's expert
+    peers = torch.arange(world, device=device)[:, None]
+    send_ids = torch.where(owner[None, :] == peers, flat[None, :], flat.new_full((), -1)).to(torch.int32).contiguous()
+    send_x = x.repeat_interleave(top_k, dim=0)[None].expand(world, slots, hidden).contiguous()
+    if world > 1:
+        import torch.distributed as dist
+
+        recv_x, recv_ids = torch.empty_like(send_x), torch.empty_like(send_ids)
+        dist.all_to_all_single(recv_x, send_x, group=group)
+        dist.all_to_all_single(recv_ids, send_ids, group=group)
+    else:
+        recv_x, recv_ids = send_x, send_ids
+    received = world * slots
+    blocks = local_experts + (received + rows_per_block - 1) // rows_per_block          # worst case, fixed
+    local = recv_ids.reshape(received).to(torch.int64) - first_expert
+    key = torch.where(recv_ids.reshape(received) >= 0, local, local.new_full((), local_experts))  # empty slots sort last
+    order = torch.argsort(key, stable=True)
+    sorted_key = key[order]
+    first_index = torch.searchsorted(sorted_key, torch.arange(local_experts + 1, device=device))
+    counts = first_index[1:] - first_index[:-1]                                         # rows per local expert
+    expert_blocks = torch.div(counts + rows_per_block - 1, rows_per_block, rounding_mode="floor")
+    block_start = torch.cumsum(expert_blocks, 0) - expert_blocks                        # first block of each expert
+    live = sorted_key < local_experts
+    safe_key = torch.where(live, sorted_key, torch.zeros_like(sorted_key))
+    position = torch.arange(received, device=device) - first_index[safe_key]
+    block = block_start[safe_key] + torch.div(position, rows_per_block, rounding_mode="floor")
+    dump = blocks * rows_per_block                                                      # a row nobody reads
+    target = torch.where(live, block * rows_per_block + position % rows_per_block, position.new_full((), dump))
+    # which expert each block serves: the blocks' first rows say so; the rest stay -1
+    block_experts = torch.full((blocks + 1,), -1, dtype=torch.int32, device=device)
+    heads = live & (position % rows_per_block == 0)
+    block_experts.index_copy_(0, torch.where(heads, block, block.new_full((), blocks)),
+                              torch.where(heads, sorted_key + first_expert, sorted_key.new_full((), -1)).to(torch.int32))
+    if state is None:
+        state = {}
+    rows = state.get("rows")
+    if rows is None or rows.shape != (dump + 1, hidden) or rows.device != device or rows.dtype != x.dtype:
+        rows = state["rows"] = torch.zeros(dump + 1, hidden, dtype=x.dtype, device=device)
+    rows.index_copy_(0, target, recv_x.reshape(received, hidden)[order])
+    outputs = run_blocks(rows[:dump].view(blocks, rows_per_block, hidden), block_experts[:blocks])
+    padded = torch.cat((outputs.reshape(dump, hidden), outputs.new_zeros(1, hidden)))
+    back = torch.empty(received, hidden, dtype=x.dtype, device=device)
+    back.index_copy_(0, order, padded[target])                                          # received order again
+    back = back.view(world, slots, hidden)
+    if world > 1:
+        returned = torch.empty_like(back)
+        dist.all_to_all_single(returned, back.contiguous(), group=group)
+    else:
+        returned = back
+    slot_outputs = returned.sum(dim=0) if world > 1 else returned[0]                    # one block holds the value, the rest zeros
+    mixed = (slot_outputs.view(tokens, top_k, hidden).float() * weights.to(torch.float32)[..., None]).sum(dim=1)
+    return mixed.to(x.dtype)
+
+
 class SAGEExperts(nn.Module):
     """gate/up/down stacks of the experts [first_expert, first_expert + experts) of one layer."""
 
@@ -86,6 +170,40 @@ class SAGEExperts(nn.Module):
             x.data_ptr(), stride, array, ys, len(stacks), ids.data_ptr(), slots,
             workspace.data_ptr() if workspace is not None else None,
             workspace.numel() if workspace is not None else 0, stream))
+
+    def forward_blocks(self, rows: torch.Tensor, block_experts: torch.Tensor) -> torch.Tensor:
+        """rows FP16 [blocks, r <= 16, hidden], block_experts int32 [blocks] (global expert ids on the
+        GPU, -1 = unused block): the SwiGLU MLP of each block's expert over the block's rows
+        (gate and up, SwiGLU, down), the expert picked on the device."""
+        blocks, count, hidden = rows.shape
+        lib = _lib.load()
+        half = dict(dtype=torch.float16, device=rows.device)
+        gate = torch.zeros(blocks, count, self.intermediate, **half)
+        up = torch.zeros(blocks, count, self.intermediate, **half)
+        down = torch.zeros(blocks, count, self.hidden, **half)
+        ids = block_experts.to(torch.int32).contiguous()
+
+        def run(x, stacks, outputs):
+            array = (_lib.ExpertStack * len(stacks))(*stacks)
+            ys = (ctypes.c_void_p * len(outputs))(*[out.data_ptr() for out in outputs])
+            stream = torch.cuda.current_stream(x.device).cuda_stream
+            need = lib.sageb200_expert_blocks_workspace_bytes(array, len(stacks), count)
+            workspace = _workspace(x.device, stream, need) if need else None
+            _lib.check(lib.sageb200_expert_blocks(
+                x.data_ptr(), array, ys, len(stacks), ids.data_ptr(), blocks, count,
+                workspace.data_ptr() if workspace is not None else None,
+                workspace.numel() if workspace is not None else 0, stream))
+
+        with torch.cuda.device(rows.device):
+            stream = torch.cuda.current_stream(rows.device).cuda_stream
+            run(rows.contiguous(), [self._stack("gate", self.intermediate, self.hidden),
+                                    self._stack("up", self.intermediate, self.hidden)], [gate, up])
+            act = torch.empty_like(gate)
+            status = lib.sageb200_glue_swiglu(gate.data_ptr(), up.data_ptr(), act.data_ptr(), gate.numel(), stream)
+            if status:
+                raise RuntimeError(f"sage_b200: swiglu failed with status {status}")
+            run(act, [self._stack("down", self.hidden, self.intermediate)], [down])
+        return down
 
     def forward(self, x: torch.Tensor, expert_ids: torch.Tensor, weights: torch.Tensor, *,
                 foreign_experts: bool = True) -> torch.Tensor:

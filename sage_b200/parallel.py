@@ -13,6 +13,20 @@ are "col", o/down are "row").  This module applies those tags to the packed layo
                    that the rank can gather from its local activations; partial outputs are
                    summed with an all-reduce
 
+A checkpoint exported by the reference stores one GLOBAL permutation per matrix
+(weight_vq/sphquant/packing.py:68-70), which mixes the channels of all ranks.  Two load-time
+remedies keep such matrices row-parallel:
+
+  fold (down_proj)   the permutation of down_proj's input moves into the ROW ORDER of gate_proj
+                     and up_proj (`permute_output_rows`): SwiGLU is elementwise, so the MLP
+                     then produces its intermediate activations directly in down_proj's
+                     quantised channel order, down_proj needs no gather, and a contiguous
+                     K split lines up with the column split of gate/up.  No extra exchange.
+  gather (o_proj)    the attention output of all ranks is all-gathered (a few KB per token) and
+                     each rank picks its K slice's source channels out of the full row
+                     (`shard_rows_global` returns the index list); the shard itself carries no
+                     permutation.
+
 Everything here is plain tensor slicing and runs on CPU tensors as well as CUDA tensors.
 """
 
@@ -77,6 +91,70 @@ def shard_rows(packed: dict, rank: int, world: int) -> dict:
         "codebook": packed["codebook"],
         "permutation": permutation,
     }
+
+
+def permute_output_rows(packed: dict, out_features: int, order: torch.Tensor) -> dict:
+    """The same packed linear with its output rows re-ordered: new row i = old row order[i]
+    (`order` a permutation of range(out_features), out_features a multiple of 16).  Pure
+    re-tiling of the three row-indexed buffers; codebook and permutation are shared."""
+    tiles, groups = packed["packed_codes"].shape[:2]
+    if out_features != tiles * 16 or order.numel() != out_features:
+        raise ValueError("row re-ordering needs out_features = 16 * tiles and a full permutation")
+    order = order.to(torch.int64).to(packed["packed_codes"].device)
+
+    def rows_first(t):  # [tiles, groups, 16, ...] -> [tiles * 16, groups, ...]
+        return t.transpose(1, 2).reshape(tiles * 16, groups, *t.shape[3:])
+
+    def tiled(t):       # back to [tiles, groups, 16, ...]
+        return t.reshape(tiles, 16, groups, *t.shape[2:]).transpose(1, 2).contiguous()
+
+    return {
+        "packed_codes": tiled(rows_first(packed["packed_codes"])[order]),
+        "radius_codes": tiled(rows_first(packed["radius_codes"])[order]),
+        "radius_grid": tiled(rows_first(packed["radius_grid"])[order]),
+        "codebook": packed["codebook"],
+        "permutation": packed["permutation"],
+    }
+
+
+def fold_input_permutation(producers: list[tuple[dict, int]], consumer: dict) -> tuple[list[dict], dict]:
+    """Move `consumer`'s input permutation into the output-row order of the packed linears that
+    (through an elementwise function) produce its input: returns (re-ordered producers, the
+    consumer with an empty permutation).  y = consumer(f(producers(x))) is unchanged."""
+    permutation = consumer["permutation"]
+    if permutation.numel() == 0:
+        return [p for p, _ in producers], consumer
+    folded = [permute_output_rows(p, n, permutation) for p, n in producers]
+    plain = dict(consumer)
+    plain["permutation"] = permutation[:0]
+    return folded, plain
+
+
+def shard_rows_global(packed: dict, rank: int, world: int) -> tuple[dict, torch.Tensor]:
+    """Row-parallel share under ANY permutation: the rank's K / world quantised channels, plus
+    the source channel (in the full activation row) of each of them.  The shard carries no
+    permutation; the caller gathers x_full[..., index] itself (after an all-gather when the
+    activations are spread over the ranks)."""
+    groups = packed["packed_codes"].shape[1]
+    if groups % world:
+        raise ValueError("row parallelism needs K to be a multiple of 128 * world")
+    per = groups // world
+    lo, hi = rank * per, (rank + 1) * per
+    permutation = packed["permutation"]
+    k = groups * 128
+    if permutation.numel():
+        index = permutation[lo * 128 : hi * 128].to(torch.int64)
+    else:
+        index = torch.arange(lo * 128, hi * 128, device=permutation.device)
+    shard = {
+        "packed_codes": packed["packed_codes"][:, lo:hi].contiguous(),
+        "radius_codes": packed["radius_codes"][:, lo:hi].contiguous(),
+        "radius_grid": packed["radius_grid"][:, lo:hi].contiguous(),
+        "codebook": packed["codebook"],
+        "permutation": permutation[:0],
+    }
+    assert int(index.max()) < k
+    return shard, index
 
 
 def row_parallel_input(x: torch.Tensor, rank: int, world: int) -> torch.Tensor:

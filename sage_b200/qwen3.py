@@ -24,8 +24,9 @@ import torch
 
 from . import _lib
 from .ops import sage_dequantize, sage_forward, sage_grouped
-from .experts import SAGEExperts, expert_slice, route, synthetic_expert_stack
-from .parallel import block_permutation, shard_columns, shard_rows, shard_vocab
+from .experts import SAGEExperts, dispatch_combine, expert_slice, route, synthetic_expert_stack
+from .parallel import (block_permutation, fold_input_permutation, shard_columns, shard_rows, shard_rows_global,
+                       shard_vocab)
 from .synthetic import linear_algorithmic_bytes, synthetic_sage_device
 
 
@@ -61,19 +62,22 @@ class PackedLinear:
     this rank's column- or row-parallel shard of it."""
 
     def __init__(self, k: int, n: int, seed: int, device, dense: bool, *, kind: str | None = None,
-                 rank: int = 0, world: int = 1, perm_blocks: int = 1):
-        packed = synthetic_sage_device(k, n, seed, device, permuted=True)
-        if kind == "row" and perm_blocks > 1:
-            # row-parallel linears gather inside each rank's slice of the activations
-            packed["permutation"] = block_permutation(k, perm_blocks, seed, device)
-        if world > 1 and kind == "col":
-            packed, n = shard_columns(packed, n, rank, world)
-        elif world > 1 and kind == "row":
-            packed = shard_rows(packed, rank, world)
-            k //= world
+                 rank: int = 0, world: int = 1, perm_blocks: int = 1, packed: dict | None = None):
+        """`packed`: this rank's buffers ready-made (k, n are then the shard's sizes); otherwise a
+        seeded synthetic matrix is drawn and, under tensor parallelism, sharded by `kind`."""
+        if packed is None:
+            packed = synthetic_sage_device(k, n, seed, device, permuted=True)
+            if kind == "row" and perm_blocks > 1:
+                # row-parallel linears gather inside each rank's slice of the activations
+                packed["permutation"] = block_permutation(k, perm_blocks, seed, device)
+            if world > 1 and kind == "col":
+                packed, n = shard_columns(packed, n, rank, world)
+            elif world > 1 and kind == "row":
+                packed = shard_rows(packed, rank, world)
+                k //= world
         self.k, self.n = k, n
         self.entries = packed["codebook"].shape[1]
-        self.bytes = linear_algorithmic_bytes(1, n, k, self.entries, True)
+        self.bytes = linear_algorithmic_bytes(1, n, k, self.entries, packed["permutation"].numel() > 0)
         if dense:
             self.weight = sage_dequantize(
                 packed["packed_codes"], packed["radius_codes"], packed["radius_grid"],
@@ -94,20 +98,27 @@ class PackedQwen3:
 
     def __init__(self, config: Qwen3Config, device, *, seed: int = 0, max_seq: int = 2560,
                  batch: int = 1, linear: str = "sage", max_new: int = 512, tp_group=None,
-                 perm_blocks: int = 1, ep_group=None):
+                 perm_blocks: int = 1, ep_group=None, ep_mode: str = "all_reduce"):
         """`tp_group`: a torch.distributed process group for tensor parallelism (q/k/v/gate/up
         column-parallel, o/down row-parallel with an all-reduce, vocabulary-parallel lm_head
         with an all-gather); every rank must pass the same seed.  `perm_blocks`: o/down use
-        a block permutation with this many blocks (a multiple of the group size).
+        a block permutation with this many blocks (a multiple of the group size); 0 keeps the
+        GLOBAL permutations an exported checkpoint has: down_proj's is folded into the row order
+        of gate/up at load time, o_proj's is applied to the all-gathered attention output.
         `ep_group`: process group for expert parallelism of a mixture-of-experts config: each
-        rank keeps experts/world contiguous experts, attention and router are replicated, the
-        ranks' expert outputs are summed with an all-reduce."""
+        rank keeps experts/world contiguous experts.  `ep_mode` "all_reduce": every rank decodes
+        the same `batch` sequences (attention and router replicated) and the ranks' expert outputs
+        are summed with an all-reduce.  "all_to_all": every rank decodes its OWN `batch` sequences
+        (data-parallel attention); each (token, expert) slot travels to the expert's owner with
+        `all_to_all_single`, each local expert runs once over its rows, and a second all-to-all
+        returns the outputs.  The same sorted per-expert compute serves one GPU when more than 16
+        sequences decode together."""
         if linear not in ("sage", "dense"):
             raise ValueError("linear must be 'sage' or 'dense'")
         if batch < 1 or batch > 64:
             raise ValueError("batch must be 1..64")
-        if batch > 16 and config.experts:
-            raise ValueError("mixture-of-experts configs run with batch 1..16")
+        if ep_mode not in ("all_reduce", "all_to_all"):
+            raise ValueError("ep_mode must be 'all_reduce' or 'all_to_all'")
         self.config, self.device, self.batch, self.max_seq = config, torch.device(device), batch, max_seq
         self.dense = linear == "dense"
         self.tp_group = tp_group
@@ -125,12 +136,18 @@ class PackedQwen3:
             self.ep_world, self.ep_rank = dist.get_world_size(ep_group), dist.get_rank(ep_group)
         else:
             self.ep_world, self.ep_rank = 1, 0
+        # (token, expert) slots sorted by expert and each expert run once over its rows: the
+        # all-to-all exchange, and any mixture-of-experts batch beyond one grouped launch
+        self.ep_dispatch = bool(config.experts) and (ep_mode == "all_to_all" or batch > 16)
+        if self.ep_dispatch and ep_group is not None and ep_mode != "all_to_all":
+            raise ValueError("more than 16 sequences under expert parallelism need ep_mode='all_to_all'")
         if config.experts and (config.experts % self.ep_world or world != 1):
             raise ValueError("experts must divide by the EP size; MoE configs do not combine with TP here")
         if config.heads % world or config.kv_heads % world or config.intermediate % (128 * world) or config.vocab % world:
             raise ValueError("heads, kv heads, intermediate/128 and vocabulary must divide by the TP size")
         if world > 1 and perm_blocks % world:
             raise ValueError("perm_blocks must be a multiple of the TP size")
+        self.global_permutations = world > 1 and perm_blocks == 0
         self.heads, self.kv_heads = config.heads // world, config.kv_heads // world
         self.lib = _lib.load()
         self.sm_count = torch.cuda.get_device_properties(self.device).multi_processor_count
@@ -153,13 +170,35 @@ class PackedQwen3:
         self.packed_bytes = 0
         for _ in range(c.layers):
             layer = {}
+            drawn = {}
             for name, k, n, kind in shapes:
                 if c.experts and name in ("gate", "up", "down"):
                     continue
-                layer[name] = PackedLinear(k, n, seed * 100003 + index, self.device, self.dense, kind=kind,
-                                           rank=rank, world=world, perm_blocks=perm_blocks)
-                self.packed_bytes += layer[name].bytes
+                if self.global_permutations:  # the full matrices first: they are transformed together below
+                    drawn[name] = synthetic_sage_device(k, n, seed * 100003 + index, self.device, permuted=True)
+                else:
+                    layer[name] = PackedLinear(k, n, seed * 100003 + index, self.device, self.dense, kind=kind,
+                                               rank=rank, world=world, perm_blocks=perm_blocks)
+                    self.packed_bytes += layer[name].bytes
                 index += 1
+            if self.global_permutations:
+                if not c.experts:
+                    (drawn["gate"], drawn["up"]), drawn["down"] = fold_input_permutation(
+                        [(drawn["gate"], c.intermediate), (drawn["up"], c.intermediate)], drawn["down"])
+                for name, k, n, kind in shapes:
+                    if name not in drawn:
+                        continue
+                    if kind == "col":
+                        shard, n = shard_columns(drawn[name], n, rank, world)
+                    elif name == "o":
+                        shard, layer["o_index"] = shard_rows_global(drawn[name], rank, world)
+                        k //= world
+                    else:
+                        shard = shard_rows(drawn[name], rank, world)  # down: identity after the fold
+                        k //= world
+                    layer[name] = PackedLinear(k, n, 0, self.device, self.dense, packed=shard)
+                    self.packed_bytes += layer[name].bytes
+                del drawn
             if c.experts:
                 local = c.experts // self.ep_world
                 first = self.ep_rank * local
@@ -206,6 +245,7 @@ class PackedQwen3:
         self.fuse = True
         self.x = torch.zeros(batch, c.hidden, **half)
         self.attn = torch.zeros(batch, q_out // world, **half)
+        self.attn_all = torch.zeros(world, batch, q_out // world, **half) if self.global_permutations else None
         self.act = torch.zeros(batch, c.intermediate // world, **half)
         self.logits = torch.zeros(batch, c.vocab, **half)
         self.local_logits = torch.zeros(batch, c.vocab // world, **half) if world > 1 else self.logits
@@ -226,6 +266,11 @@ class PackedQwen3:
         # what the expert-parallel exchange of a step is, for reports
         self.ep_collective = "nccl all_reduce of the ranks' expert outputs (every rank holds every token)"
         self.collective_calls_per_step = c.layers if self.ep_world > 1 else 0
+        if self.ep_dispatch and self.ep_world > 1:
+            self.ep_collective = ("nccl all_to_all_single: dispatch of (token, expert) slots (rows and ids) to the "
+                                  "experts' owners, combine of their outputs (every rank owns its own tokens)")
+            self.collective_calls_per_step = 3 * c.layers
+        self._dispatch_state = {}
         # The whole token as one persistent kernel (`sageb200_mega_step`).  Prepared when the model
         # fits it; `use_mega` selects it for the decode step before `capture()`.  It is off by
         # default: as measured on B200 the per-launch path is still the faster one.
@@ -337,7 +382,15 @@ class PackedQwen3:
     def _after_attention(self, layer):
         c, lib, b = self.config, self.lib, self.batch
         s = self._stream()
-        (o,) = self._linears(layer, ("o",), self.attn)
+        attn = self.attn
+        if self.global_permutations:
+            # o_proj's global permutation: every rank's heads gathered (a few KB), then this rank's
+            # K slice picks its source channels out of the full row
+            import torch.distributed as dist
+
+            dist.all_gather_into_tensor(self.attn_all, self.attn, group=self.tp_group)
+            attn = self.attn_all.permute(1, 0, 2).reshape(b, -1).index_select(-1, layer["o_index"])
+        (o,) = self._linears(layer, ("o",), attn)
         self._all_reduce(o)
         if c.experts:
             return self._moe(layer, o)
@@ -363,6 +416,22 @@ class PackedQwen3:
             self._check(lib.sageb200_glue_add_rmsnorm(_vp(self.h), _vp(o), _vp(layer["post_norm"]), _vp(self.x), b,
                                                       c.hidden, c.eps, self._stream()), "add_rmsnorm")
             ids, weights = route(torch.nn.functional.linear(self.x, layer["router"]), c.top_k)
+        if self.ep_dispatch:
+            if self.dense:
+                gate_w, up_w, down_w = layer["expert_weights"]
+                first, count = layer["first_expert"], layer["local_experts"]
+
+                def run_blocks(rows, block_experts):  # FP16 matmuls on the dequantised experts
+                    index = (block_experts.long() - first).clamp(0, count - 1)
+                    g = torch.bmm(rows, gate_w[index].transpose(1, 2))
+                    u = torch.bmm(rows, up_w[index].transpose(1, 2))
+                    act = torch.nn.functional.silu(g.float()).half() * u
+                    return torch.bmm(act, down_w[index].transpose(1, 2))
+            else:
+                run_blocks = layer["experts"].forward_blocks
+            return dispatch_combine(self.x, ids, weights, run_blocks, first_expert=layer["first_expert"],
+                                    local_experts=layer["local_experts"], group=self.ep_group, world=self.ep_world,
+                                    state=self._dispatch_state)
         if self.dense:
             gate_w, up_w, down_w = layer["expert_weights"]
             local = ids.long() - layer["first_expert"]

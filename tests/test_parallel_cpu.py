@@ -12,7 +12,8 @@ import torch.distributed as dist
 import torch.multiprocessing as mp
 
 from oracle import c_oracle
-from sage_b200.parallel import block_permutation, row_parallel_input, shard_columns, shard_rows, shard_vocab
+from sage_b200.parallel import (block_permutation, fold_input_permutation, permute_output_rows, row_parallel_input,
+                                shard_columns, shard_rows, shard_rows_global, shard_vocab)
 from sage_b200.synthetic import synthetic_sage
 
 
@@ -60,6 +61,58 @@ def test_row_shards_recombine(world):
     assert torch.equal(row_parallel_input(x, 1, world), x[:, per : 2 * per])
     table = torch.arange(64 * 8).reshape(64, 8)
     assert torch.equal(shard_vocab(table, 1, 4), table[16:32])
+
+
+def test_output_rows_reorder_and_fold_keep_the_mlp():
+    """A reference-style GLOBAL permutation on down_proj folded into gate/up's row order: the
+    intermediate activations are the same values born in down_proj's quantised order, the MLP
+    output is unchanged (FP32 sums in another order) and down_proj needs no gather."""
+    hidden, inter = 256, 768
+    gate, up = synthetic_sage(hidden, inter, seed=1), synthetic_sage(hidden, inter, seed=2)
+    down = synthetic_sage(inter, hidden, seed=3)  # permutation: a global randperm of `inter`
+    assert down["permutation"].numel() == inter
+    order = torch.randperm(inter, generator=torch.Generator().manual_seed(0))
+    moved = permute_output_rows(gate, inter, order)
+    np.testing.assert_array_equal(c_oracle.decode_fp16(moved, inter).view(np.uint16),
+                                  c_oracle.decode_fp16(gate, inter)[order.numpy()].view(np.uint16))
+    x = torch.randn(2, hidden, generator=torch.Generator().manual_seed(5), dtype=torch.float16)
+
+    def mlp(gate_p, up_p, down_p):
+        g = torch.from_numpy(c_oracle.linear_fp32(x, gate_p, inter)).half()
+        u = torch.from_numpy(c_oracle.linear_fp32(x, up_p, inter)).half()
+        act = torch.nn.functional.silu(g.float()).half() * u
+        return c_oracle.linear_fp32(act, down_p, hidden), act
+
+    want, act = mlp(gate, up, down)
+    (gate_f, up_f), down_f = fold_input_permutation([(gate, inter), (up, inter)], down)
+    assert down_f["permutation"].numel() == 0
+    got, act_f = mlp(gate_f, up_f, down_f)
+    assert torch.equal(act_f, act[:, down["permutation"].long()])  # the intermediate is born in quantised order
+    assert np.abs(got - want).max() <= 1e-5 * np.abs(want).max()
+    # and a contiguous K split of the folded down_proj lines up with the column split of gate/up
+    for world in (2, 3):
+        total = np.zeros_like(want)
+        for rank in range(world):
+            (gate_r, n_r), (up_r, _) = shard_columns(gate_f, inter, rank, world), shard_columns(up_f, inter, rank, world)
+            g = torch.from_numpy(c_oracle.linear_fp32(x, gate_r, n_r)).half()
+            u = torch.from_numpy(c_oracle.linear_fp32(x, up_r, n_r)).half()
+            local_act = torch.nn.functional.silu(g.float()).half() * u
+            total += c_oracle.linear_fp32(local_act, shard_rows(down_f, rank, world), hidden)
+        assert np.abs(total - want).max() <= 1e-5 * np.abs(want).max()
+
+
+def test_global_permutation_row_shards_gather_from_the_full_row():
+    k, n = 1024, 48
+    packed = synthetic_sage(k, n, seed=2)  # a global permutation
+    x = torch.randn(3, k, generator=torch.Generator().manual_seed(1), dtype=torch.float16)
+    want = c_oracle.linear_fp32(x, packed, n)
+    for world in (2, 4):
+        total = np.zeros_like(want)
+        for rank in range(world):
+            shard, index = shard_rows_global(packed, rank, world)
+            assert shard["permutation"].numel() == 0 and index.numel() == k // world
+            total += c_oracle.linear_fp32(x[:, index].contiguous(), shard, n)
+        assert np.abs(total - want).max() <= 1e-5 * np.abs(want).max()
 
 
 def _worker(rank, world, path, k, n, results):

@@ -204,6 +204,39 @@ def test_decode_batches_beyond_one_grouped_launch(batch):
         assert (tokens[:, 0] == want_tokens[0, 0]).float().mean() > 0.9
 
 
+def test_moe_batches_beyond_one_grouped_launch_sort_slots_by_expert():
+    """The compute of the all-to-all exchange on one GPU: the (token, expert) slots sorted by
+    expert and each expert run once over its rows, against the slot-by-slot path on the same
+    batch (packed model and dense oracle model alike), and the packed model against batch 1."""
+    config = Qwen3Config(layers=2, hidden=512, heads=4, kv_heads=2, intermediate=1024, vocab=2048,
+                         experts=8, top_k=2, moe_intermediate=256)
+    batch = 6  # 12 slots over 8 experts: well within an expert's 16 rows
+    prompt = torch.randint(3, config.vocab, (1, 6), generator=torch.Generator().manual_seed(2))
+    prompts = prompt.expand(batch, -1).contiguous()
+    single = PackedQwen3(config, "cuda:0", seed=4, max_seq=32, batch=1, max_new=8)
+    want_single = single.generate(prompt, 4)
+    for linear in ("sage", "dense"):
+        plain = PackedQwen3(config, "cuda:0", seed=4, max_seq=32, batch=batch, max_new=8, linear=linear)
+        assert not plain.ep_dispatch
+        want_tokens = plain.generate(prompts, 4)
+        want_logits = plain.logits.float().clone()
+        # (the exchange mode on one GPU forces the sorted path at a batch the other path also serves)
+        many = PackedQwen3(config, "cuda:0", seed=4, max_seq=32, batch=batch, max_new=8, linear=linear,
+                           ep_mode="all_to_all")
+        assert many.ep_dispatch
+        tokens = many.generate(prompts, 4)
+        assert torch.equal(tokens, want_tokens), (linear, tokens.tolist(), want_tokens.tolist())
+        error = (many.logits.float() - want_logits).norm(dim=-1) / want_logits.norm(dim=-1)
+        assert float(error.max()) < 1e-2, (linear, error)
+        if linear == "sage":
+            assert torch.equal(tokens, want_single.expand(batch, -1))
+    # all 24 rows name the same two experts per token: 24 rows for one expert = two blocks of it
+    crowded = PackedQwen3(config, "cuda:0", seed=4, max_seq=32, batch=24, max_new=8)
+    assert crowded.ep_dispatch
+    tokens = crowded.generate(prompt.expand(24, -1).contiguous(), 4)
+    assert torch.equal(tokens, want_single.expand(24, -1))
+
+
 def test_report_rows_on_a_small_model():
     """The reference-schema measurement loop runs end to end and its numbers hang together."""
     from sage_b200.harness import measure

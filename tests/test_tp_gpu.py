@@ -12,7 +12,82 @@ import torch.multiprocessing as mp
 pytestmark = pytest.mark.gpu
 
 
-def _worker(rank, world, path, results, experts=False):
+def _worker_all_to_all(rank, world, path, results):
+    """Expert parallelism with all-to-all: every rank decodes its OWN sequences; the tokens of a
+    rank's sequences must be those of the same model on one GPU (all experts local)."""
+    os.environ["NCCL_NVLS_ENABLE"] = "0"
+    code = 1
+    try:
+        import datetime
+
+        torch.cuda.set_device(rank)
+        dist.init_process_group("nccl", init_method=f"file://{path}", rank=rank, world_size=world,
+                                device_id=torch.device("cuda", rank), timeout=datetime.timedelta(seconds=120))
+        cpu_group = dist.new_group(backend="gloo")
+        from sage_b200.qwen3 import PackedQwen3, Qwen3Config
+
+        config = Qwen3Config(layers=3, hidden=1024, heads=8, kv_heads=2, intermediate=2048, vocab=4096,
+                             experts=8, top_k=2, moe_intermediate=256)
+        local_batch, steps = 3, 24
+        prompt = torch.randint(3, config.vocab, (local_batch, 10), generator=torch.Generator().manual_seed(40 + rank))
+        sharded = PackedQwen3(config, f"cuda:{rank}", seed=2, max_seq=64, max_new=steps, batch=local_batch,
+                              ep_group=dist.group.WORLD, ep_mode="all_to_all")
+        tokens = sharded.generate(prompt, steps).cpu()
+        torch.cuda.synchronize()
+        dist.barrier(group=cpu_group)
+        # the same model with every expert local, fed the sharded run's tokens row by row
+        single = PackedQwen3(config, f"cuda:{rank}", seed=2, max_seq=64, max_new=steps, batch=local_batch)
+        single.prefill(prompt)
+        flips = []
+        for i in range(steps):
+            if i > 0:
+                single.tokens.copy_(tokens[:, i - 1].to(single.device))
+                single.graph.replay()
+            rows = single.logits.float()
+            for b in range(local_batch):
+                best, got = int(torch.argmax(rows[b])), int(tokens[b, i])
+                if best != got:
+                    flips.append((i, b, got, best, float(rows[b, best] - rows[b, got]), float(rows[b].std())))
+        results.put((rank, flips, tokens.tolist()))
+        dist.barrier(group=cpu_group)
+        results.close()
+        results.join_thread()
+        code = 0
+    except BaseException:  # noqa: BLE001
+        import traceback
+
+        traceback.print_exc()
+        code = 1
+    finally:
+        os._exit(code)
+
+
+def test_expert_all_to_all_matches_single_gpu():
+    if torch.cuda.device_count() < 2:
+        pytest.skip("needs two GPUs")
+    context = mp.get_context("spawn")
+    results = context.Queue()
+    with tempfile.TemporaryDirectory() as folder:
+        path = os.path.join(folder, "rendezvous")
+        procs = [context.Process(target=_worker_all_to_all, args=(r, 2, path, results)) for r in range(2)]
+        for p in procs:
+            p.start()
+        for p in procs:
+            p.join(300)
+        alive = [p for p in procs if p.is_alive()]
+        for p in alive:
+            p.kill()
+            p.join(30)
+        assert not alive, "a rank did not finish in time"
+        assert all(p.exitcode == 0 for p in procs), [p.exitcode for p in procs]
+    for _ in range(2):
+        rank, flips, got = results.get(timeout=10)
+        for step, row, ours, best, margin, spread in flips:
+            assert 0 <= margin <= 0.02 * spread, (rank, step, row, ours, best, margin, spread)
+        assert len(flips) <= 1, (rank, flips, got)
+
+
+def _worker(rank, world, path, results, mode="tp"):
     os.environ["NCCL_NVLS_ENABLE"] = "0"
     code = 1
     try:
@@ -24,13 +99,16 @@ def _worker(rank, world, path, results, experts=False):
         cpu_group = dist.new_group(backend="gloo")  # host-side barrier, see bench.py run_tp
         from sage_b200.qwen3 import PackedQwen3, Qwen3Config
 
-        if experts:  # mixture of experts: each rank keeps half of the experts
+        blocks = single_blocks = 4
+        if mode == "ep":  # mixture of experts: each rank keeps half of the experts
             config = Qwen3Config(layers=3, hidden=1024, heads=8, kv_heads=2, intermediate=2048, vocab=4096,
                                  experts=8, top_k=2, moe_intermediate=256)
             parallel = dict(ep_group=dist.group.WORLD)
         else:
             config = Qwen3Config(layers=3, hidden=1024, heads=8, kv_heads=2, intermediate=2048, vocab=4096)
             parallel = dict(tp_group=dist.group.WORLD)
+            if mode == "tp_global":  # the global permutations of an exported checkpoint (fold + gather)
+                blocks, single_blocks = 0, 1
         prompt = torch.randint(3, config.vocab, (1, 12), generator=torch.Generator().manual_seed(4))
 
         def run(model):
@@ -41,12 +119,12 @@ def _worker(rank, world, path, results, experts=False):
                 model.graph.replay()
             return model.log[:, :40].cpu(), first_logits
 
-        sharded = PackedQwen3(config, f"cuda:{rank}", seed=2, max_seq=96, max_new=40, perm_blocks=4, **parallel)
+        sharded = PackedQwen3(config, f"cuda:{rank}", seed=2, max_seq=96, max_new=40, perm_blocks=blocks, **parallel)
         tokens, logits = run(sharded)
         if rank == 0:
             # the one-GPU model is fed the sharded model's tokens, so one flip cannot hide later
             # steps; a disagreement is accepted only as a near tie of the one-GPU logits
-            single = PackedQwen3(config, "cuda:0", seed=2, max_seq=96, max_new=40, perm_blocks=4)
+            single = PackedQwen3(config, "cuda:0", seed=2, max_seq=96, max_new=40, perm_blocks=single_blocks)
             single.prefill(prompt)
             want_logits = single.logits.float().cpu()
             flips = []
@@ -74,15 +152,16 @@ def _worker(rank, world, path, results, experts=False):
         os._exit(code)  # no NCCL teardown under live CUDA graphs
 
 
-@pytest.mark.parametrize("experts", [False, True], ids=["tensor_parallel", "expert_parallel"])
-def test_two_gpus_match_single_gpu(experts):
+@pytest.mark.parametrize("mode", ["tp", "ep", "tp_global"],
+                         ids=["tensor_parallel", "expert_parallel", "tensor_parallel_global_permutations"])
+def test_two_gpus_match_single_gpu(mode):
     if torch.cuda.device_count() < 2:
         pytest.skip("needs two GPUs")
     context = mp.get_context("spawn")
     results = context.Queue()
     with tempfile.TemporaryDirectory() as folder:
         path = os.path.join(folder, "rendezvous")
-        procs = [context.Process(target=_worker, args=(r, 2, path, results, experts)) for r in range(2)]
+        procs = [context.Process(target=_worker, args=(r, 2, path, results, mode)) for r in range(2)]
         for p in procs:
             p.start()
         for p in procs:
