@@ -41,8 +41,8 @@ namespace {
 
 constexpr int kThreads = 512;
 constexpr int kWarps = 16;
-constexpr int kStages = 4;        // ring stages per warp
-constexpr int kStageUnits = 2;    // units per stage
+constexpr int kStages = 2;        // ring stages per warp
+constexpr int kStageUnits = 4;    // units per stage (one bulk copy per array and stage)
 constexpr int kRingUnits = kStages * kStageUnits;
 constexpr int kUnitBytes = 640;   // 512 codes + 64 radius words + 64 grid
 constexpr int kBookBytes = 256 * 8 * 16;  // one codebook, 8 replicas
@@ -743,8 +743,6 @@ __global__ void __launch_bounds__(kThreads, 1)
         S.warp_tiles[warp] = segment;
       }
       if (!alive) S.abort = 1;
-      // this phase is consumed: stream the next linear phase's share into the ring
-      if (alive && P + 1 < phases) start_stream(P + 1);
     }
     __syncthreads();
     MEGA_STAMP();  // main loops of all warps done
@@ -754,9 +752,12 @@ __global__ void __launch_bounds__(kThreads, 1)
     }
 
     // ---- combine the warps (warp order = channel order) and write the outputs; meanwhile the
-    //      last warp fetches the metadata of the phase after the next
+    //      last warp fetches the metadata of the phase after the next.  The small latency-bound
+    //      loads go out first, then the next linear phase's weight stream (megabytes per SM wave
+    //      that would otherwise queue in front of them).
     if (warp == kWarps - 1 && P + 2 < phases) load_meta(P + 2);
     if (kind != kQkv && P + 1 < phases) prestage_load(P + 1);  // (in flight during the combination)
+    if (P + 1 < phases) start_stream(P + 1);
 #pragma unroll 1
     for (int e = tid; e < cta_tiles * 16; e += kThreads) {
       const int cta_tile = e >> 4, row = e & 15;
