@@ -755,7 +755,7 @@ def measure_sharded(kind: str, args, device, group, cpu_group, world: int, rank:
         collective = model.ep_collective
         calls = model.collective_calls_per_step
     elif sharded:
-        collective, calls = "nccl all_reduce (row-parallel partial sums) + all_gather (logits)", 2 * config.layers + 1
+        collective, calls = model.tp_collective, 2 * config.layers + 1
     record = {
         "metric": ("qwen3_30b_a3b" if expert_parallel else "qwen3_32b") + f"_sage_2.25bpw_batch{batch}_decode_tok_s",
         "value": batch * 1000.0 / ms_per_step,

@@ -77,6 +77,19 @@ EXPORTED_DECODE = (
 )
 
 
+# every symbol include/sage_b200_peer.h declares
+EXPORTED_PEER = (
+    "sageb200_peer_exchange_bytes",
+    "sageb200_peer_create",
+    "sageb200_peer_open",
+    "sageb200_peer_close",
+    "sageb200_peer_destroy",
+    "sageb200_peer_all_reduce",
+)
+PEER_MAX_WORLD = 8
+PEER_HANDLE_BYTES = 64
+
+
 class Activation(ctypes.Structure):
     """struct sageb200_activation."""
 
@@ -266,6 +279,19 @@ def load() -> ctypes.CDLL:
     lib.sageb200_mega_prepare.argtypes = [ctypes.POINTER(MegaModel), ctypes.POINTER(MegaLayer), vp, sz, vp]
     lib.sageb200_mega_step.restype = ci
     lib.sageb200_mega_step.argtypes = [ctypes.POINTER(MegaModel), vp, vp, vp, vp, vp, vp, ci, vp]
+    # all-reduce over peer memory (include/sage_b200_peer.h)
+    lib.sageb200_peer_exchange_bytes.restype = sz
+    lib.sageb200_peer_exchange_bytes.argtypes = [ci, ll]
+    lib.sageb200_peer_create.restype = ci
+    lib.sageb200_peer_create.argtypes = [ci, ll, ctypes.POINTER(vp), ctypes.POINTER(ctypes.c_ubyte)]
+    lib.sageb200_peer_open.restype = ci
+    lib.sageb200_peer_open.argtypes = [ctypes.POINTER(ctypes.c_ubyte), ctypes.POINTER(vp)]
+    lib.sageb200_peer_close.restype = ci
+    lib.sageb200_peer_close.argtypes = [vp]
+    lib.sageb200_peer_destroy.restype = ci
+    lib.sageb200_peer_destroy.argtypes = [vp]
+    lib.sageb200_peer_all_reduce.restype = ci
+    lib.sageb200_peer_all_reduce.argtypes = [ctypes.POINTER(vp), ci, ci, ll, vp, ll, vp]
     if "SAGEB200_PDL" in os.environ:  # debug switch: which kernel families launch dependently
         lib.sageb200_set_pdl(int(os.environ["SAGEB200_PDL"]))
     _handle = lib

@@ -98,7 +98,8 @@ class PackedQwen3:
 
     def __init__(self, config: Qwen3Config, device, *, seed: int = 0, max_seq: int = 2560,
                  batch: int = 1, linear: str = "sage", max_new: int = 512, tp_group=None,
-                 perm_blocks: int = 1, ep_group=None, ep_mode: str = "all_reduce"):
+                 perm_blocks: int = 1, ep_group=None, ep_mode: str = "all_reduce",
+                 collective: str = "peer"):
         """`tp_group`: a torch.distributed process group for tensor parallelism (q/k/v/gate/up
         column-parallel, o/down row-parallel with an all-reduce, vocabulary-parallel lm_head
         with an all-gather); every rank must pass the same seed.  `perm_blocks`: o/down use
@@ -112,7 +113,13 @@ class PackedQwen3:
         (data-parallel attention); each (token, expert) slot travels to the expert's owner with
         `all_to_all_single`, each local expert runs once over its rows, and a second all-to-all
         returns the outputs.  The same sorted per-expert compute serves one GPU when more than 16
-        sequences decode together."""
+        sequences decode together.
+        `collective`: how the decode step's all-reduces run: "peer" = this library's one-kernel
+        all-reduce over the peers' memory (sage_b200/peer.py; the GPUs of one node), "nccl" =
+        `torch.distributed.all_reduce`.  Tensors larger than a decode step's (the prompt pass) always
+        take NCCL."""
+        if collective not in ("peer", "nccl"):
+            raise ValueError("collective must be 'peer' or 'nccl'")
         if linear not in ("sage", "dense"):
             raise ValueError("linear must be 'sage' or 'dense'")
         if batch < 1 or batch > 64:
@@ -148,6 +155,14 @@ class PackedQwen3:
         if world > 1 and perm_blocks % world:
             raise ValueError("perm_blocks must be a multiple of the TP size")
         self.global_permutations = world > 1 and perm_blocks == 0
+        # exchange buffers of the one-kernel all-reduce (row-parallel outputs, replicated-token
+        # expert outputs): one decode step's [batch, hidden] rows
+        self.peer = None
+        reduce_group = tp_group if world > 1 else (ep_group if self.ep_world > 1 and ep_mode == "all_reduce" else None)
+        if collective == "peer" and reduce_group is not None and not self.dense:
+            from .peer import PeerExchange
+
+            self.peer = PeerExchange(reduce_group, self.device, batch * config.hidden)
         self.heads, self.kv_heads = config.heads // world, config.kv_heads // world
         self.lib = _lib.load()
         self.sm_count = torch.cuda.get_device_properties(self.device).multi_processor_count
@@ -265,6 +280,12 @@ class PackedQwen3:
         self.graph_no_head = None
         # what the expert-parallel exchange of a step is, for reports
         self.ep_collective = "nccl all_reduce of the ranks' expert outputs (every rank holds every token)"
+        if self.peer is not None and self.ep_world > 1:
+            self.ep_collective = ("one-kernel all-reduce of the ranks' expert outputs over peer memory "
+                                  "(push over NVLink, epoch flags, rank-order sum; every rank holds every token)")
+        self.tp_collective = ("one-kernel all-reduce over peer memory (row-parallel partial sums: push over NVLink, "
+                              "epoch flags, rank-order sum) + nccl all_gather (logits)" if self.peer is not None
+                              else "nccl all_reduce (row-parallel partial sums) + all_gather (logits)")
         self.collective_calls_per_step = c.layers if self.ep_world > 1 else 0
         if self.ep_dispatch and self.ep_world > 1:
             self.ep_collective = ("nccl all_to_all_single: dispatch of (token, expert) slots (rows and ids) to the "
@@ -350,8 +371,12 @@ class PackedQwen3:
         return out
 
     def _all_reduce(self, tensor):
-        """Sum the row-parallel partial outputs over the tensor-parallel group (NCCL)."""
+        """Sum the row-parallel partial outputs over the tensor-parallel group: one kernel over
+        the peers' memory for a decode step's rows, NCCL for anything larger."""
         if self.tp_world > 1:
+            if self.peer is not None and self.peer.fits(tensor):
+                self.peer.all_reduce(tensor)
+                return
             import torch.distributed as dist
 
             dist.all_reduce(tensor, group=self.tp_group)
@@ -446,6 +471,9 @@ class PackedQwen3:
         else:
             out = layer["experts"](self.x, ids, weights, foreign_experts=self.ep_world > 1)
         if self.ep_world > 1:
+            if self.peer is not None and self.peer.fits(out):
+                self.peer.all_reduce(out)
+                return out
             import torch.distributed as dist
 
             dist.all_reduce(out, group=self.ep_group)

@@ -48,6 +48,18 @@ def test_debug_header_symbols_are_exported(lib):
         assert hasattr(lib, name), name
 
 
+def test_peer_header_symbols_are_exported(lib):
+    names = declared_symbols("sage_b200_peer.h")
+    assert set(names) == set(_lib.EXPORTED_PEER)
+    for name in names:
+        assert hasattr(lib, name), name
+    # sizes only (no device work): header, flags, two slots per rank
+    assert lib.sageb200_peer_exchange_bytes(2, 5120) == 8192 + 2 * 2 * 5120 * 2
+    assert lib.sageb200_peer_exchange_bytes(1, 5120) == 0
+    assert lib.sageb200_peer_exchange_bytes(9, 5120) == 0
+    assert lib.sageb200_peer_exchange_bytes(2, 5121) == 0
+
+
 def test_version_and_status_strings(lib):
     assert lib.sageb200_version() >= 100
     assert lib.sageb200_status_string(0) == b"ok"

@@ -109,6 +109,8 @@ def _worker(rank, world, path, results, mode="tp"):
             parallel = dict(tp_group=dist.group.WORLD)
             if mode == "tp_global":  # the global permutations of an exported checkpoint (fold + gather)
                 blocks, single_blocks = 0, 1
+            if mode == "tp_nccl":  # the library collective instead of the one-kernel all-reduce
+                parallel["collective"] = "nccl"
         prompt = torch.randint(3, config.vocab, (1, 12), generator=torch.Generator().manual_seed(4))
 
         def run(model):
@@ -120,7 +122,15 @@ def _worker(rank, world, path, results, mode="tp"):
             return model.log[:, :40].cpu(), first_logits
 
         sharded = PackedQwen3(config, f"cuda:{rank}", seed=2, max_seq=96, max_new=40, perm_blocks=blocks, **parallel)
+        assert (sharded.peer is not None) == (mode != "tp_nccl")
         tokens, logits = run(sharded)
+        if mode == "tp":
+            # two ranks: FP32 sum of two FP16 partials rounded once = the FP16 sum NCCL forms, so
+            # the two collectives must give the same tokens and logits bit for bit
+            other = PackedQwen3(config, f"cuda:{rank}", seed=2, max_seq=96, max_new=40, perm_blocks=blocks,
+                                collective="nccl", **parallel)
+            other_tokens, other_logits = run(other)
+            assert torch.equal(tokens, other_tokens) and torch.equal(logits, other_logits)
         if rank == 0:
             # the one-GPU model is fed the sharded model's tokens, so one flip cannot hide later
             # steps; a disagreement is accepted only as a near tie of the one-GPU logits
@@ -152,8 +162,9 @@ def _worker(rank, world, path, results, mode="tp"):
         os._exit(code)  # no NCCL teardown under live CUDA graphs
 
 
-@pytest.mark.parametrize("mode", ["tp", "ep", "tp_global"],
-                         ids=["tensor_parallel", "expert_parallel", "tensor_parallel_global_permutations"])
+@pytest.mark.parametrize("mode", ["tp", "ep", "tp_global", "tp_nccl"],
+                         ids=["tensor_parallel", "expert_parallel", "tensor_parallel_global_permutations",
+                              "tensor_parallel_nccl"])
 def test_two_gpus_match_single_gpu(mode):
     if torch.cuda.device_count() < 2:
         pytest.skip("needs two GPUs")
@@ -180,3 +191,100 @@ def test_two_gpus_match_single_gpu(mode):
     for step, ours, best, margin, spread in flips:
         assert 0 <= margin <= 0.02 * spread, (step, ours, best, margin, spread)
     assert len(flips) <= 1, (flips, got)
+
+
+def _worker_peer(rank, world, path, results):
+    os.environ["NCCL_NVLS_ENABLE"] = "0"
+    code = 1
+    try:
+        import datetime
+
+        torch.cuda.set_device(rank)
+        device = torch.device("cuda", rank)
+        dist.init_process_group("nccl", init_method=f"file://{path}", rank=rank, world_size=world,
+                                device_id=device, timeout=datetime.timedelta(seconds=120))
+        cpu_group = dist.new_group(backend="gloo")
+        from sage_b200 import _lib
+        from sage_b200.peer import PeerExchange
+
+        capacity = 16 * 5120
+        exchange = PeerExchange(dist.group.WORLD, device, capacity)
+        gen = torch.Generator(device=device).manual_seed(100 + rank)
+        checked = 0
+        # eager calls of many sizes back to back (both slot parities, CTAs with and without work)
+        for round_index in range(6):
+            for elements in (8, 2560, 5120, 5128, 8 * 5120, capacity):
+                mine = torch.randn(elements, generator=gen, device=device).half()
+                want = mine.clone()
+                dist.all_reduce(want)  # two ranks: one rounding, the same as FP32-sum-then-round
+                got = exchange.all_reduce(mine.clone())
+                assert torch.equal(got, want), (round_index, elements, (got.float() - want.float()).abs().max())
+                checked += 1
+        # the same call captured in a CUDA graph and replayed: epochs and parity live on the device
+        rows = torch.zeros(4, 5120, dtype=torch.float16, device=device)
+        source = torch.randn(4, 5120, generator=gen, device=device).half()
+        stream = torch.cuda.Stream(device=device)
+        stream.wait_stream(torch.cuda.current_stream(device))
+        graph = torch.cuda.CUDAGraph()
+        with torch.cuda.stream(stream):
+            for _ in range(2):  # warm-up on the capture stream
+                rows.copy_(source)
+                for row in rows:
+                    exchange.all_reduce(row)
+            with torch.cuda.graph(graph, stream=stream):
+                rows.copy_(source)
+                for row in rows[:3]:  # an ODD number of calls per replay: parity must not be host state
+                    exchange.all_reduce(row)
+        want = source.clone()
+        dist.all_reduce(want)
+        for _ in range(25):
+            graph.replay()
+        torch.cuda.synchronize()
+        assert torch.equal(rows[:3], want[:3]) and torch.equal(rows[3], source[3])
+        # arguments the entry point refuses (nothing is launched)
+        import ctypes
+
+        lib = _lib.load()
+        bad = lib.sageb200_peer_all_reduce(exchange.exchanges, world, rank, capacity, ctypes.c_void_p(rows.data_ptr()),
+                                           capacity + 8, None)
+        assert bad == -1
+        bad = lib.sageb200_peer_all_reduce(exchange.exchanges, world, rank, capacity,
+                                           ctypes.c_void_p(rows.data_ptr() + 2), 8, None)
+        assert bad == -2
+        torch.cuda.synchronize()
+        dist.barrier(group=cpu_group)
+        exchange.close()
+        if rank == 0:
+            results.put(("peer", checked))
+        results.close()
+        results.join_thread()
+        code = 0
+    except BaseException:  # noqa: BLE001
+        import traceback
+
+        traceback.print_exc()
+        code = 1
+    finally:
+        os._exit(code)
+
+
+def test_peer_all_reduce_matches_nccl_on_two_gpus():
+    if torch.cuda.device_count() < 2:
+        pytest.skip("needs two GPUs")
+    context = mp.get_context("spawn")
+    results = context.Queue()
+    with tempfile.TemporaryDirectory() as folder:
+        path = os.path.join(folder, "rendezvous")
+        procs = [context.Process(target=_worker_peer, args=(r, 2, path, results)) for r in range(2)]
+        for p in procs:
+            p.start()
+        for p in procs:
+            p.join(300)
+        alive = [p for p in procs if p.is_alive()]
+        for p in alive:
+            p.kill()
+            p.join(30)
+        assert not alive, "a rank did not finish in time"
+        assert all(p.exitcode == 0 for p in procs), [p.exitcode for p in procs]
+    kind, checked = results.get(timeout=10)
+    assert kind == "peer" and checked == 36
