@@ -292,6 +292,7 @@ class PackedQwen3:
                                   "experts' owners, combine of their outputs (every rank owns its own tokens)")
             self.collective_calls_per_step = 3 * c.layers
         self._dispatch_state = {}
+        self.ep_rows_per_block = 8  # rows of one expert block in the sorted expert compute (one MMA column block)
         # The whole token as one persistent kernel (`sageb200_mega_step`).  Prepared when the model
         # fits it; `use_mega` selects it for the decode step before `capture()`.  It is off by
         # default: as measured on B200 the per-launch path is still the faster one.
@@ -456,7 +457,7 @@ class PackedQwen3:
                 run_blocks = layer["experts"].forward_blocks
             return dispatch_combine(self.x, ids, weights, run_blocks, first_expert=layer["first_expert"],
                                     local_experts=layer["local_experts"], group=self.ep_group, world=self.ep_world,
-                                    state=self._dispatch_state)
+                                    rows_per_block=self.ep_rows_per_block, state=self._dispatch_state)
         if self.dense:
             gate_w, up_w, down_w = layer["expert_weights"]
             local = ids.long() - layer["first_expert"]

@@ -237,6 +237,52 @@ def test_moe_batches_beyond_one_grouped_launch_sort_slots_by_expert():
     assert torch.equal(tokens, want_single.expand(24, -1))
 
 
+def test_expert_blocks_at_qwen3_30b_a3b_dimensions_against_dense_experts():
+    """128 experts of 2048 -> 768 -> 2048, 32 tokens x top-8 with distinct experts per token: the
+    sorted block path (4, 8 and 16 rows per block) and the slot path against FP32 matmuls on the
+    dequantised experts.  A whole random-init mixture-of-experts model is chaotic in its routing
+    (near-tied router logits flip experts), so the full-size check is made at the operator."""
+    from sage_b200.experts import SAGEExperts, dispatch_combine, expert_slice, synthetic_expert_stack
+    from sage_b200.ops import sage_dequantize
+
+    device = "cuda:0"
+    experts_count, hidden, inter, top_k, tokens = 128, 2048, 768, 8, 32
+    stacks = [synthetic_expert_stack(hidden, inter, experts_count, 11, device),
+              synthetic_expert_stack(hidden, inter, experts_count, 12, device),
+              synthetic_expert_stack(inter, hidden, experts_count, 13, device)]
+    experts = SAGEExperts(*stacks, first_expert=0)
+    gen = torch.Generator(device=device).manual_seed(0)
+    x = torch.randn(tokens, hidden, generator=gen, device=device).half()
+    ids = torch.stack([torch.randperm(experts_count, generator=gen, device=device)[:top_k]
+                       for _ in range(tokens)]).to(torch.int32)
+    weights = torch.rand(tokens, top_k, generator=gen, device=device)
+    weights = weights / weights.sum(-1, keepdim=True)
+
+    def dense(stack, expert, n):
+        one = expert_slice(stack, expert)
+        return sage_dequantize(one["packed_codes"], one["radius_codes"], one["radius_grid"], one["codebook"],
+                               one["permutation"], n).float()
+
+    want = torch.zeros(tokens, hidden, device=device)
+    for t in range(tokens):
+        for j in range(top_k):
+            e = int(ids[t, j])
+            g, u = dense(stacks[0], e, inter) @ x[t].float(), dense(stacks[1], e, inter) @ x[t].float()
+            act = (torch.nn.functional.silu(g) * u).half().float()
+            want[t] += float(weights[t, j]) * (dense(stacks[2], e, hidden) @ act)
+
+    def error(out):
+        return float(((out.float() - want).norm(dim=-1) / want.norm(dim=-1)).max())
+
+    slot = torch.cat([experts(x[:16], ids[:16], weights[:16], foreign_experts=False),
+                      experts(x[16:], ids[16:], weights[16:], foreign_experts=False)])
+    assert error(slot) < 2e-3, error(slot)
+    for rows_per_block in (4, 8, 16):
+        out = dispatch_combine(x, ids, weights, experts.forward_blocks, first_expert=0,
+                               local_experts=experts_count, rows_per_block=rows_per_block, state={})
+        assert error(out) < 2e-3, (rows_per_block, error(out))
+
+
 def test_report_rows_on_a_small_model():
     """The reference-schema measurement loop runs end to end and its numbers hang together."""
     from sage_b200.harness import measure
