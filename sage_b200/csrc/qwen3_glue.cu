@@ -17,6 +17,7 @@
 #include <cooperative_groups.h>
 
 #include "sage_common.cuh"
+#include "sage_kernels.h"
 
 namespace {
 
@@ -1138,6 +1139,15 @@ int sageb200_glue_prefill_attention(const void *q, const void *k_cache, const vo
   if (head_dim != 128 || kv_heads < 1 || q_heads % kv_heads || max_seq < 1 || sequences < 1 || tokens < 1 ||
       static_cast<long long>(sequences) * tokens > 65535)
     return -1;
+  if (tokens >= 32 && sequences <= 65535 && q_heads <= 65535) {
+    // the tiled tensor-core kernel; a handful of rows stay on the per-row decode kernel
+    __atomic_fetch_add(&sageb200::g_sageb200_glue_launches, 1ull, __ATOMIC_RELAXED);
+    const cudaError_t error = sageb200::launch_prefill_attention(
+        static_cast<const __half *>(q), static_cast<const __half *>(k_cache), static_cast<const __half *>(v_cache),
+        static_cast<const int *>(positions), static_cast<__half *>(out), sequences, tokens, q_heads, kv_heads,
+        max_seq, static_cast<cudaStream_t>(stream));
+    return error == cudaSuccess ? 0 : -5;
+  }
   return launch_attention(true, q, nullptr, nullptr, nullptr, nullptr, nullptr, nullptr, positions,
                           const_cast<void *>(k_cache), const_cast<void *>(v_cache), out, sequences * tokens, q_heads,
                           kv_heads, max_seq, 1, 0.0f, tokens, false, stream);

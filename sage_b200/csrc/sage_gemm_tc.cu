@@ -10,7 +10,7 @@
 // is a multiple of 16 maps onto one instruction shape without padding waste:
 //     D[128 outputs][TN tokens] += Wtile[128][64] . Xq[TN][64]^T      per 64-channel stage
 // Both operands are K-major in shared memory with the 128-byte swizzle:
-//   A (weights)      written by 8 decode warps with 16-byte stores, bit-exact
+//   A (weights)      written by 16 decode warps with 16-byte stores, bit-exact
 //                    w = fp16_rn(float(+-dir) * fmaf(code, step, min))
 //                    (reference csrc/sage/sage_gemm_cuda.cu:117-131)
 //   B (activations)  one TMA tile load per stage from the activations in quantised
@@ -30,15 +30,21 @@
 namespace sageb200 {
 namespace {
 
-constexpr int kDecodeWarps = 8;
+constexpr int kDecodeWarps = 16;
 constexpr int kDecodeThreads = kDecodeWarps * 32;
 constexpr int kTmaWarp = kDecodeWarps;
 constexpr int kMmaWarp = kDecodeWarps + 1;
 constexpr int kGemmThreads = (kDecodeWarps + 2) * 32;
 constexpr int kTileRows = 128;             // output rows per CTA = MMA M
+constexpr int kRowThreads = kDecodeThreads / kTileRows;  // decode threads per output row (4)
+constexpr int kThreadVectors = 8 / kRowThreads;          // 8-weight vectors per thread and stage (2)
+static_assert(kRowThreads == 4 && kThreadVectors == 2, "the decode loop below is written for four threads per row");
 constexpr int kStageK = 64;                // channels per stage = one 128-byte swizzle row
 constexpr int kAStageBytes = kTileRows * kStageK * 2;
 constexpr int kMaxStages = 6;
+constexpr int kBookReplicas = 8;           // codebook copies in shared memory: lane % 8 reads its own
+constexpr int kBookBytes = 256 * 16 * kBookReplicas;
+constexpr int kGemmSharedLimit = 226 * 1024;  // dynamic shared memory the kernel opts into (227 KiB per CTA less its static words)
 constexpr unsigned long long kWaitLimitNs = 2000000000ull;  // 2 s per wait
 
 struct GemmParams {
@@ -54,7 +60,14 @@ struct GemmParams {
   int stages;
   int tmem_columns;     // power of two >= max(32, TN); 512 with two accumulators
   int accumulators;     // 1 or 2 token blocks per CTA: one decoded weight stage feeds both
+  long long *trace;     // profiling build only: eight clock sums per CTA (null otherwise)
 };
+
+#ifdef SAGEB200_TRACE
+#define GEMM_CLOCK() clock64()
+#else
+#define GEMM_CLOCK() 0ll
+#endif
 
 // ---------------------------------------------------------------- PTX wrappers
 
@@ -84,6 +97,19 @@ __device__ __forceinline__ unsigned long long global_timer() {
   return t;
 }
 
+// Suspending form of the test: the thread sleeps in hardware until the phase completes or about
+// `hint_ns` have passed, so a waiting warp does not compete for issue slots with working ones.
+__device__ __forceinline__ bool mbarrier_try_wait(uint32_t bar, uint32_t parity, uint32_t hint_ns) {
+  uint32_t done;
+  asm volatile(
+      "{\n .reg .pred p;\n mbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2, %3;\n"
+      " selp.u32 %0, 1, 0, p;\n}"
+      : "=r"(done)
+      : "r"(bar), "r"(parity), "r"(hint_ns)
+      : "memory");
+  return done != 0;
+}
+
 // Bounded wait.  Returns false (and raises the CTA's abort flag) when the limit passes.
 __device__ __forceinline__ bool bounded_wait(uint32_t bar, uint32_t parity, volatile int *abort_flag,
                                              int *status) {
@@ -91,15 +117,12 @@ __device__ __forceinline__ bool bounded_wait(uint32_t bar, uint32_t parity, vola
   const unsigned long long begin = global_timer();
   unsigned spins = 0;
   while (true) {
-    if (mbarrier_test(bar, parity)) return true;
+    if (mbarrier_try_wait(bar, parity, 2000u)) return true;
     if (*abort_flag) return false;
-    if ((++spins & 63u) == 0) {
-      __nanosleep(64);
-      if (global_timer() - begin > kWaitLimitNs) {
-        *abort_flag = 1;
-        atomicExch(status, -7);  // SAGEB200_ERR_TIMEOUT
-        return false;
-      }
+    if ((++spins & 15u) == 0 && global_timer() - begin > kWaitLimitNs) {
+      *abort_flag = 1;
+      atomicExch(status, -7);  // SAGEB200_ERR_TIMEOUT
+      return false;
     }
   }
 }
@@ -190,7 +213,7 @@ __global__ void __launch_bounds__(kGemmThreads, 1)
   const uint32_t b_base = a_base + p.stages * kAStageBytes;
   const uint32_t book_address = b_base + p.stages * b_stage_bytes;
   uint4 *book_shared = reinterpret_cast<uint4 *>(aligned + (book_address - base));
-  const uint32_t bar_base = book_address + 256 * 16;
+  const uint32_t bar_base = book_address + kBookBytes;
   // barriers: full[stages], empty[stages], accumulator
   auto full_bar = [&](int s) { return bar_base + 8u * s; };
   auto empty_bar = [&](int s) { return bar_base + 8u * (kMaxStages + s); };
@@ -226,7 +249,10 @@ __global__ void __launch_bounds__(kGemmThreads, 1)
     entry.y = p.book[p.entries + e];
     entry.z = p.book[2 * p.entries + e];
     entry.w = p.book[3 * p.entries + e];
-    book_shared[e] = entry;
+    // eight copies, entry-major: lane l reads copy l % 8, so the eight lanes of a quarter warp hit
+    // eight different 16-byte bank groups whatever their indices (rotated fill order for the same reason)
+#pragma unroll
+    for (int r = 0; r < kBookReplicas; ++r) book_shared[e * kBookReplicas + ((r + tid) & (kBookReplicas - 1))] = entry;
   }
   tcgen05_fence_before();
   __syncthreads();
@@ -235,46 +261,69 @@ __global__ void __launch_bounds__(kGemmThreads, 1)
   volatile int *abort_ptr = &abort_flag;
 
   if (warp < kDecodeWarps) {
-    // ---------------- weight decode producers: thread = (row 0..127, half 0..1)
-    const int row = tid >> 1;
-    const int half_id = tid & 1;
+    // ---------------- weight decode producers: thread = (row 0..127, quarter 0..3 of the row's
+    //                  64 channels); sixteen warps keep four warps per scheduler in flight, which
+    //                  is what hides the codebook-load and conversion latencies of the exact decode
+    const int row = tid / kRowThreads;
+    const int part = tid % kRowThreads;
     const int out_row = row_block * kTileRows + row;
     const int tile = out_row >> 4;
     const bool row_valid = tile < p.tiles;  // rows past the last packed tile decode to zero
     const size_t cell_base = (static_cast<size_t>(row_valid ? tile : 0) * p.groups) * 16 + (out_row & 15);
     const uint32_t row_offset = static_cast<uint32_t>(row >> 3) * 1024u + static_cast<uint32_t>(row & 7) * 128u;
     const uint32_t index_mask = static_cast<uint32_t>(p.entries - 1);
-    uint2 words[2] = {make_uint2(0, 0), make_uint2(0, 0)};
+    // One 128-channel group feeds two stages.  The thread's packed words of a group (two code
+    // words, the radius word, the grid endpoints) are fetched TWO groups ahead into a register
+    // queue: the loads come from cold HBM, and a load issued at the point of use would stall every
+    // decode thread for a full memory latency every second stage.
+    struct GroupWords {
+      uint32_t word[2], radius, endpoints;
+    };
+    auto fetch_group = [&](int group) {
+      GroupWords g = {{0u, 0u}, 0u, 0u};
+      if (row_valid && group < p.groups) {
+        const size_t cell = cell_base + static_cast<size_t>(group) * 16;
+        g.word[0] = ldg_stream_u1(p.codes + cell * 8 + part);
+        g.word[1] = ldg_stream_u1(p.codes + cell * 8 + 4 + part);
+        g.radius = ldg_stream_u1(p.radii + cell);
+        g.endpoints = ldg_stream_u1(p.grid + cell);
+      }
+      return g;
+    };
+    GroupWords ahead0 = fetch_group(0), ahead1 = fetch_group(1);
+    long long waited = 0, worked = 0, fenced = 0, stored = 0;  // (profiling build) clock sums of the phases
+    [[maybe_unused]] const long long decode_begin = GEMM_CLOCK();
+    uint32_t words[2] = {0, 0};
     uint32_t radius_word = 0;
     float minimum = 0.0f, step = 0.0f;
     bool alive = true;
     for (int ks = 0; ks < stages_k && alive; ++ks) {
       const int s = ks % p.stages;
       const uint32_t phase = static_cast<uint32_t>(ks / p.stages) & 1u;
-      if ((ks & 1) == 0 && row_valid) {
-        // one 128-channel group feeds two stages: this thread's words for both halves
-        const size_t cell = cell_base + static_cast<size_t>(ks >> 1) * 16;
-        words[0] = ldg_stream_u2(p.codes + cell * 8 + 2 * half_id);
-        words[1] = ldg_stream_u2(p.codes + cell * 8 + 4 + 2 * half_id);
-        radius_word = ldg_stream_u1(p.radii + cell);
-        const uint32_t endpoints = ldg_stream_u1(p.grid + cell);
-        const float2 e = __half22float2(*reinterpret_cast<const __half2 *>(&endpoints));
+      if ((ks & 1) == 0) {
+        words[0] = ahead0.word[0];
+        words[1] = ahead0.word[1];
+        radius_word = ahead0.radius;
+        const float2 e = __half22float2(*reinterpret_cast<const __half2 *>(&ahead0.endpoints));
         minimum = e.x;
         step = e.y;
+        ahead0 = ahead1;
+        ahead1 = fetch_group((ks >> 1) + 2);
       }
+      const long long t0 = GEMM_CLOCK();
       alive = bounded_wait(empty_bar(s), phase ^ 1u, abort_ptr, p.status);
       if (!alive) break;
-      const uint2 w = words[ks & 1];
+      const long long t1 = GEMM_CLOCK();
+      const uint32_t word = words[ks & 1];
       const uint32_t stage_address = a_base + s * kAStageBytes + row_offset;
 #pragma unroll
-      for (int j = 0; j < 4; ++j) {
-        const uint32_t word = (j < 2) ? w.x : w.y;
-        const uint32_t code = (word >> (16 * (j & 1))) & 0xffffu;
-        const int chunk = half_id * 4 + j;                 // 16-byte chunk within the 128-byte row
+      for (int j = 0; j < kThreadVectors; ++j) {
+        const uint32_t code = (word >> (16 * j)) & 0xffffu;
+        const int chunk = part * kThreadVectors + j;       // 16-byte chunk within the 128-byte row
         const int vector = (ks & 1) * 8 + chunk;           // vector index within the group
         uint32_t out[4] = {0, 0, 0, 0};
         if (row_valid) {
-          const uint4 dir = book_shared[(code >> 8) & index_mask];
+          const uint4 dir = book_shared[((code >> 8) & index_mask) * kBookReplicas + (lane & (kBookReplicas - 1))];
           const uint32_t rc = (code >> (8 + p.dbits)) |
                               (((radius_word >> (2 * vector)) & 3u) << (8 - p.dbits));
           const float radius = fmaf(static_cast<float>(rc), step, minimum);
@@ -291,29 +340,80 @@ __global__ void __launch_bounds__(kGemmThreads, 1)
         const uint32_t swizzled = static_cast<uint32_t>(chunk ^ (row & 7)) * 16u;
         sts_u4(stage_address + swizzled, make_uint4(out[0], out[1], out[2], out[3]));
       }
+      const long long t2 = GEMM_CLOCK();
       fence_proxy_async_shared();
+      const long long t3 = GEMM_CLOCK();
       mbarrier_arrive(full_bar(s));
+      waited += t1 - t0;
+      worked += GEMM_CLOCK() - t1;
+      fenced += t3 - t2;
+      stored += t2 - t1;
     }
+#ifdef SAGEB200_TRACE
+    if (p.trace && (tid == 0 || tid == kDecodeThreads - 1)) {
+      long long *record = p.trace + (static_cast<size_t>(blockIdx.y) * gridDim.x + blockIdx.x) * 16 + (tid == 0 ? 0 : 3);
+      record[0] = waited;
+      record[1] = worked;
+      record[2] = GEMM_CLOCK() - decode_begin;
+      if (tid == 0) {
+        p.trace[(static_cast<size_t>(blockIdx.y) * gridDim.x + blockIdx.x) * 16 + 10] = stored;
+        p.trace[(static_cast<size_t>(blockIdx.y) * gridDim.x + blockIdx.x) * 16 + 11] = fenced;
+      }
+    }
+    const long long epilogue_begin = GEMM_CLOCK();
+#endif
     // ---------------- epilogue: TMEM -> registers -> FP16 global
     if (alive) alive = bounded_wait(accum_bar, 0, abort_ptr, p.status);
     alive = __all_sync(0xffffffffu, alive);  // tcgen05.ld is warp-collective
     tcgen05_fence_after();
+#ifdef SAGEB200_TRACE
+    if (p.trace && tid == 0)
+      p.trace[(static_cast<size_t>(blockIdx.y) * gridDim.x + blockIdx.x) * 16 + 12] = GEMM_CLOCK() - epilogue_begin;
+#endif
     if (alive) {
+      constexpr int kColumnParts = kDecodeWarps / 4;
       const int quarter = warp & 3;                 // TMEM lanes 32*quarter .. +31
-      const int column_half = warp >> 2;            // warps 0-3: first half of the tokens
-      const int columns_per_half = (tn / 16 + 1) / 2 * 16;
-      const int column_begin = column_half * columns_per_half;
-      const int column_end = min(tn, column_begin + columns_per_half);
+      const int column_part = warp >> 2;            // warps 0-3: first part of the tokens, ...
+      const int columns_per_part = (tn / 16 + kColumnParts - 1) / kColumnParts * 16;
+      const int column_begin = column_part * columns_per_part;
+      const int column_end = min(tn, column_begin + columns_per_part);
       const int out = row_block * kTileRows + quarter * 32 + lane;
+      // The accumulator has output rows on lanes and tokens on columns, y is [token][row]: a lane
+      // storing its own values writes 2 bytes per instruction (64 bytes per warp), and the store
+      // instructions themselves then bound the epilogue.  Each warp therefore turns 16 tokens x 32
+      // rows around through 1 KiB of the (now idle) weight stages and stores 16 bytes per lane:
+      // eight rows of one token.  Rows beyond n, or an n / y that breaks the 16-byte alignment,
+      // take the direct stores.
+      const uint32_t turn = a_base + static_cast<uint32_t>(warp) * 1024u;
+      const int out_base = row_block * kTileRows + quarter * 32;
+      const bool wide = (p.n & 7) == 0 && out_base + 32 <= p.n && (reinterpret_cast<uintptr_t>(p.y) & 15) == 0;
       for (int a = 0; a < accumulators; ++a) {
         for (int c = column_begin; c < column_end; c += 16) {
           uint32_t r[16];
           tmem_load_16(tmem_base + (static_cast<uint32_t>(quarter * 32) << 16) + a * 256 + c, r);
           tmem_load_wait();
-          if (out < p.n) {
+          const int token_base = (token_block + a) * tn + c;
+          if (wide) {
 #pragma unroll
             for (int i = 0; i < 16; ++i) {
-              const int token = (token_block + a) * tn + c + i;
+              const __half h = __float2half_rn(__uint_as_float(r[i]));
+              asm volatile("st.shared.u16 [%0], %1;" ::"r"(turn + i * 64u + lane * 2u),
+                           "h"(*reinterpret_cast<const unsigned short *>(&h)));
+            }
+            __syncwarp();
+#pragma unroll
+            for (int q = 0; q < 2; ++q) {
+              const int piece = lane + 32 * q;          // token = piece / 4, eight rows = piece % 4
+              const int token = token_base + (piece >> 2);
+              const uint4 v = lds_u4(turn + static_cast<uint32_t>(piece) * 16u);
+              if (token < p.rows)
+                *reinterpret_cast<uint4 *>(p.y + static_cast<size_t>(token) * p.n + out_base + (piece & 3) * 8) = v;
+            }
+            __syncwarp();
+          } else if (out < p.n) {
+#pragma unroll
+            for (int i = 0; i < 16; ++i) {
+              const int token = token_base + i;
               if (token < p.rows)
                 p.y[static_cast<size_t>(token) * p.n + out] = __float2half_rn(__uint_as_float(r[i]));
             }
@@ -321,31 +421,45 @@ __global__ void __launch_bounds__(kGemmThreads, 1)
         }
       }
     }
+#ifdef SAGEB200_TRACE
+    if (p.trace && tid == 0)
+      p.trace[(static_cast<size_t>(blockIdx.y) * gridDim.x + blockIdx.x) * 16 + 6] = GEMM_CLOCK() - epilogue_begin;
+#endif
   } else if (warp == kTmaWarp) {
     // ---------------- activation tile loads
     if (lane == 0) {
       bool alive = true;
+      long long waited = 0;
       for (int ks = 0; ks < stages_k && alive; ++ks) {
         const int s = ks % p.stages;
         const uint32_t phase = static_cast<uint32_t>(ks / p.stages) & 1u;
+        const long long t0 = GEMM_CLOCK();
         alive = bounded_wait(empty_bar(s), phase ^ 1u, abort_ptr, p.status);
         if (!alive) break;
+        waited += GEMM_CLOCK() - t0;
         mbarrier_arrive_expect_tx(full_bar(s), static_cast<uint32_t>(b_stage_bytes));
         for (int a = 0; a < accumulators; ++a)  // (a block past the last token reads the fill value)
           tma_load_2d(b_base + s * b_stage_bytes + a * b_tile_bytes, &x_map, ks * kStageK,
                       (token_block + a) * tn, full_bar(s));
       }
+#ifdef SAGEB200_TRACE
+      if (p.trace) p.trace[(static_cast<size_t>(blockIdx.y) * gridDim.x + blockIdx.x) * 16 + 7] = waited;
+#endif
     }
   } else {
     // ---------------- MMA issue
     if (lane == 0) {
       const uint32_t idesc = instruction_descriptor(kTileRows, tn);
       bool alive = true;
+      long long waited = 0;
+      [[maybe_unused]] const long long mma_begin = GEMM_CLOCK();
       for (int ks = 0; ks < stages_k && alive; ++ks) {
         const int s = ks % p.stages;
         const uint32_t phase = static_cast<uint32_t>(ks / p.stages) & 1u;
+        const long long t0 = GEMM_CLOCK();
         alive = bounded_wait(full_bar(s), phase, abort_ptr, p.status);
         if (!alive) break;
+        waited += GEMM_CLOCK() - t0;
         tcgen05_fence_after();
         const uint64_t a_desc = smem_descriptor(a_base + s * kAStageBytes);
         for (int a = 0; a < accumulators; ++a) {
@@ -359,6 +473,13 @@ __global__ void __launch_bounds__(kGemmThreads, 1)
         umma_commit(empty_bar(s));
       }
       if (alive) umma_commit(accum_bar);
+#ifdef SAGEB200_TRACE
+      if (p.trace) {
+        long long *record = p.trace + (static_cast<size_t>(blockIdx.y) * gridDim.x + blockIdx.x) * 16;
+        record[8] = waited;
+        record[9] = GEMM_CLOCK() - mma_begin;
+      }
+#endif
     }
   }
 
@@ -433,36 +554,61 @@ cudaError_t launch_gather(const __half *x, const int32_t *perm, __half *xq, int 
 
 GemmPlan plan_gemm_tc(int rows, int n, int k, int sm_count) {
   (void)k;
-  (void)sm_count;
   GemmPlan plan{};
-  int tn = (rows + 15) / 16 * 16;
-  if (tn > 256) {
-    // split the tokens evenly into blocks of at most 256
-    const int blocks = (rows + 255) / 256;
-    tn = ((rows + blocks - 1) / blocks + 15) / 16 * 16;
+  plan.row_blocks = (n + kTileRows - 1) / kTileRows;
+  if (sm_count <= 0) sm_count = 148;
+  // Tokens per accumulator (at most 256, 128 or 64, the rows split evenly) and accumulators per
+  // CTA (two token blocks sharing every decoded weight stage).  Cost model per 64-channel stage
+  // of one CTA, in cycles - the kernel runs at the slowest of
+  //   shared-memory traffic / 128 bytes per cycle: the MMA's operand reads (A again for every
+  //     accumulator), the activation tile written by TMA, the decoded weights and codebook reads
+  //   the tensor pipe: 135 cycles per 128 x 256 x 16 instruction
+  //   the decode warps: ~800 cycles per stage
+  // times the number of waves the grid needs.  Large grids end up with 256 tokens x 2 (least
+  // decode work per output); grids that would leave most SMs idle take smaller token blocks, whose
+  // redundant decoding runs on SMs that had nothing to do.
+  int tn = 0, best_accumulators = 1;
+  double best_cost = 0.0;
+  for (int cap = 256; cap >= 64; cap /= 2) {
+    const int blocks = (rows + cap - 1) / cap;
+    const int candidate = ((rows + blocks - 1) / blocks + 15) / 16 * 16;
+    const int token_blocks = (rows + candidate - 1) / candidate;
+    for (int accumulators = 2; accumulators >= 1; --accumulators) {
+      if (accumulators == 2 && token_blocks < 2) continue;
+      const double traffic = accumulators * 4.0 * (4096.0 + candidate * 32.0) + accumulators * candidate * 128.0 + 32768.0;
+      const double tensor = accumulators * 4.0 * 135.0 * candidate / 256.0;
+      double stage = traffic / 128.0;
+      if (stage < tensor) stage = tensor;
+      if (stage < 800.0) stage = 800.0;
+      const long long ctas = static_cast<long long>(plan.row_blocks) * ((token_blocks + accumulators - 1) / accumulators);
+      const long long waves = (ctas + sm_count - 1) / sm_count;
+      const double cost = stage * static_cast<double>(waves);
+      if (tn == 0 || cost < best_cost * 0.97) {  // (prefer the earlier, larger tile on near ties)
+        tn = candidate;
+        best_accumulators = accumulators;
+        best_cost = cost;
+      }
+    }
+    if (rows <= cap / 2) continue;  // (smaller caps still change the split)
   }
   plan.tokens_per_cta = tn;
   plan.token_blocks = (rows + tn - 1) / tn;
-  plan.row_blocks = (n + kTileRows - 1) / kTileRows;
-  // Two token blocks per CTA share every decoded weight stage (two accumulators in tensor
-  // memory): the decode work per output halves.  Worth it as soon as there are two blocks; the
-  // activation stage doubles, so the pipeline is shallower.
-  plan.accumulators = plan.token_blocks >= 2 ? 2 : 1;
+  plan.accumulators = best_accumulators;
   const int stage_bytes = kAStageBytes + plan.accumulators * tn * kStageK * 2;
-  int stages = (200 * 1024) / stage_bytes;
+  int stages = (kGemmSharedLimit - kBookBytes - 2 * 1024) / stage_bytes;
   if (stages > kMaxStages) stages = kMaxStages;
   if (stages < 2) stages = 2;
   plan.stages = stages;
   int columns = 32;
   while (columns < tn) columns *= 2;
   plan.tmem_columns = plan.accumulators == 2 ? 512 : columns;
-  plan.shared_bytes = static_cast<size_t>(stages) * stage_bytes + 256 * 16 + (2 * kMaxStages + 1) * 8 + 1024;
+  plan.shared_bytes = static_cast<size_t>(stages) * stage_bytes + kBookBytes + (2 * kMaxStages + 1) * 8 + 1024;
   return plan;
 }
 
 cudaError_t configure_gemm_tc() {
   return cudaFuncSetAttribute(sage_gemm_tc_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize,
-                              220 * 1024);
+                              kGemmSharedLimit);
 }
 
 // xq: activations in quantised channel order, 16-byte aligned, [rows][k].
@@ -500,6 +646,7 @@ cudaError_t launch_gemm_tc(const __half *xq, const uint32_t *codes, const uint32
   p.stages = plan.stages;
   p.tmem_columns = plan.tmem_columns;
   p.accumulators = plan.accumulators;
+  p.trace = trace_buffer();
   const dim3 blocks(plan.row_blocks, (plan.token_blocks + plan.accumulators - 1) / plan.accumulators);
   sage_gemm_tc_kernel<<<blocks, kGemmThreads, plan.shared_bytes, stream>>>(p, map);
   return cudaGetLastError();

@@ -132,6 +132,12 @@ cudaError_t launch_gemm_tc(const __half *xq, const uint32_t *codes, const uint32
                            int rows, int n, int k, int entries, const GemmPlan &plan,
                            cudaStream_t stream);
 
+// Causal attention over prompt rows on the tensor cores (prefill_attention.cu); rows are
+// [sequence][token], row (s, t) at cache position positions[s] + t.  head_dim is 128.
+cudaError_t launch_prefill_attention(const __half *q, const __half *k_cache, const __half *v_cache,
+                                     const int *positions, __half *out, int sequences, int tokens, int q_heads,
+                                     int kv_heads, int max_seq, cudaStream_t stream);
+
 // x_q[m][j] = x[m][perm[j]] for the prefill path.
 cudaError_t launch_gather(const __half *x, const int32_t *perm, __half *xq, int rows, int k,
                           cudaStream_t stream, int sm_count);

@@ -89,12 +89,15 @@ def check_lockstep(mismatches, worst_logit_error, steps, allowed=0):
     fixed seeds below measure.  The one thing FP16 logits cannot decide is an exact near tie: a
     case that hits one declares it in `allowed` (never silently), and such a flip must then lie
     within two FP16 steps of the ORACLE's own top logit - a gap the oracle's own rounding
-    decides - on top of the looser 2 % of-the-spread bound."""
+    decides - on top of the looser 2 % of-the-spread bound.
+    A margin of exactly 0 is not a disagreement at all: the oracle's own FP16 logits of the two
+    tokens are bit-equal, so both are arg-maxima of the oracle and only the index order differs."""
     # logits of the packed model stay within the matmul gate's order of magnitude of the oracle's
     assert worst_logit_error < 2e-2, worst_logit_error
     for step, ours, oracle, margin, spread in mismatches:
         assert 0 <= margin <= 0.02 * spread, (step, ours, oracle, margin, spread)
-    assert len(mismatches) <= allowed, mismatches
+    decided = [m for m in mismatches if m[3] != 0.0]
+    assert len(decided) <= allowed, mismatches
 
 
 def test_greedy_tokens_small_model():
@@ -281,6 +284,49 @@ def test_expert_blocks_at_qwen3_30b_a3b_dimensions_against_dense_experts():
         out = dispatch_combine(x, ids, weights, experts.forward_blocks, first_expert=0,
                                local_experts=experts_count, rows_per_block=rows_per_block, state={})
         assert error(out) < 2e-3, (rows_per_block, error(out))
+
+
+@pytest.mark.parametrize("tokens,first,heads,kv_heads", [(64, 0, 4, 2), (100, 37, 8, 2), (512, 0, 8, 8), (33, 5, 2, 1),
+                                                       (257, 64, 4, 1)])
+def test_prompt_attention_on_tensor_cores_against_torch(tokens, first, heads, kv_heads):
+    """The tiled prompt attention (rows [sequence][token], row (s, t) at cache position
+    first + t, causal over positions 0 .. its own) against an FP32 torch softmax over the same
+    caches: ragged last query block, a prompt that continues an existing context, grouped heads."""
+    import ctypes
+
+    from sage_b200 import _lib
+
+    lib = _lib.load()
+    device = "cuda:0"
+    sequences, max_seq = 2, 640
+    gen = torch.Generator(device=device).manual_seed(tokens + first)
+    q = torch.randn(sequences * tokens, heads, 128, generator=gen, device=device).half()
+    k_cache = torch.randn(sequences, kv_heads, max_seq, 128, generator=gen, device=device).half()
+    v_cache = torch.randn(sequences, kv_heads, max_seq, 128, generator=gen, device=device).half()
+    positions = torch.tensor([first, first + 3], dtype=torch.int32, device=device)
+    out = torch.zeros_like(q)
+    vp = ctypes.c_void_p
+    status = lib.sageb200_glue_prefill_attention(vp(q.data_ptr()), vp(k_cache.data_ptr()), vp(v_cache.data_ptr()),
+                                                 vp(positions.data_ptr()), vp(out.data_ptr()), sequences, tokens,
+                                                 heads, kv_heads, 128, max_seq, None)
+    assert status == 0
+    torch.cuda.synchronize()
+    group = heads // kv_heads
+    for s in range(sequences):
+        start = int(positions[s])
+        context = start + tokens
+        keys = k_cache[s, :, :context].float().repeat_interleave(group, dim=0)       # [heads, context, 128]
+        values = v_cache[s, :, :context].float().repeat_interleave(group, dim=0)
+        queries = q[s * tokens:(s + 1) * tokens].float().permute(1, 0, 2)             # [heads, tokens, 128]
+        scores = queries @ keys.transpose(1, 2) / 128 ** 0.5
+        column = torch.arange(context, device=device)[None, None, :]
+        row = (start + torch.arange(tokens, device=device))[None, :, None]
+        scores = scores.masked_fill(column > row, float("-inf"))
+        want = (torch.softmax(scores, dim=-1) @ values).permute(1, 0, 2)              # [tokens, heads, 128]
+        got = out[s * tokens:(s + 1) * tokens].float()
+        error = (got - want).norm() / want.norm()
+        assert float(error) < 2e-3, (s, float(error))
+        assert float((got - want).abs().max()) < 2e-2
 
 
 def test_report_rows_on_a_small_model():
