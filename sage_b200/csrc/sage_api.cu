@@ -514,8 +514,9 @@ int sageb200_debug_plan(int rows, int n, int k, int sm_count, int act_kind, int 
 
 size_t sageb200_workspace_bytes(int rows, int n, int k) {
   if (n <= 0 || k <= 0 || (k % 128) || rows <= 0) return 0;
-  if (rows >= kGemmMinRows)  // counter region (kept for layout uniformity) + gathered activations
-    return kCounterRegionBytes + align256(static_cast<size_t>(rows) * k * 2);
+  if (rows >= kGemmMinRows)  // arrival counters of split tiles + gathered activations + FP32 split tiles
+    return kCounterRegionBytes + align256(static_cast<size_t>(rows) * k * 2) +
+           align256(plan_gemm_tc(rows, n, k, planning_sm_count()).partial_bytes);
   const int sms = planning_sm_count();
   size_t bytes = 0;
   // rows > 16 run as 16-row passes plus a tail pass; reserve for the larger of the two
@@ -574,10 +575,11 @@ int sageb200_linear(const void *x, const void *codes, const void *radii, const v
     // Prefill: tcgen05 GEMM over activations in quantised channel order.  The gather (or
     // a re-alignment copy) lands in the workspace so the TMA loads see contiguous rows.
     const __half *xq = static_cast<const __half *>(x);
+    const size_t gathered_bytes = align256(static_cast<size_t>(rows) * k * 2);
+    if (workspace && (reinterpret_cast<uintptr_t>(workspace) & 255)) return SAGEB200_ERR_ALIGNMENT;
     if (perm || (reinterpret_cast<uintptr_t>(x) & 15)) {
-      const size_t need = kCounterRegionBytes + align256(static_cast<size_t>(rows) * k * 2);
+      const size_t need = kCounterRegionBytes + gathered_bytes;
       if (!workspace || workspace_bytes < need) return SAGEB200_ERR_WORKSPACE;
-      if (reinterpret_cast<uintptr_t>(workspace) & 255) return SAGEB200_ERR_ALIGNMENT;
       __half *gathered =
           reinterpret_cast<__half *>(static_cast<unsigned char *>(workspace) + kCounterRegionBytes);
       if (launch_gather(xq, perm, gathered, rows, k, s, device->sm_count) != cudaSuccess) {
@@ -587,11 +589,25 @@ int sageb200_linear(const void *x, const void *codes, const void *radii, const v
       g_launches.fetch_add(1, std::memory_order_relaxed);
       xq = gathered;
     }
-    const GemmPlan plan = plan_gemm_tc(rows, n, k, device->sm_count);
+    // K is split over several CTAs per output tile when the grid would otherwise leave most SMs
+    // idle; that needs the FP32 scratch behind the gathered activations (a caller whose workspace
+    // predates it, or who passes none for unpermuted input, gets the unsplit plan)
+    GemmPlan plan = plan_gemm_tc(rows, n, k, device->sm_count);
+    float *partial = nullptr;
+    unsigned *counters = nullptr;
+    if (plan.k_splits > 1) {
+      const size_t need = kCounterRegionBytes + gathered_bytes + align256(plan.partial_bytes);
+      if (workspace && workspace_bytes >= need) {
+        counters = static_cast<unsigned *>(workspace);
+        partial = reinterpret_cast<float *>(static_cast<unsigned char *>(workspace) + kCounterRegionBytes + gathered_bytes);
+      } else {
+        plan = plan_gemm_tc(rows, n, k, device->sm_count, false);
+      }
+    }
     if (launch_gemm_tc(xq, static_cast<const uint32_t *>(codes), static_cast<const uint32_t *>(radii),
                        static_cast<const uint32_t *>(grid), static_cast<const uint32_t *>(book),
-                       static_cast<__half *>(y), device->status, rows, n, k, entries, plan,
-                       s) != cudaSuccess) {
+                       static_cast<__half *>(y), device->status, rows, n, k, entries, plan, s, partial,
+                       counters) != cudaSuccess) {
       cudaGetLastError();
       return SAGEB200_ERR_CUDA;
     }

@@ -61,6 +61,12 @@ struct GemmParams {
   int tmem_columns;     // power of two >= max(32, TN); 512 with two accumulators
   int accumulators;     // 1 or 2 token blocks per CTA: one decoded weight stage feeds both
   long long *trace;     // profiling build only: eight clock sums per CTA (null otherwise)
+  // split K (k_splits > 1): CTA z runs the 128-channel groups [z * groups_per_split, ...), leaves
+  // its FP32 tile in `partial`, and the last CTA of a tile to arrive (counter) adds the splits in
+  // index order and writes the FP16 output
+  int k_splits, groups_per_split;
+  float *partial;       // [k_splits][tiles][accumulators * TN tokens][128 rows]
+  unsigned *counters;   // [tiles], zero before and after the launch
 };
 
 #ifdef SAGEB200_TRACE
@@ -201,6 +207,7 @@ __global__ void __launch_bounds__(kGemmThreads, 1)
   extern __shared__ unsigned char raw_shared[];
   __shared__ uint32_t tmem_base_holder;
   __shared__ int abort_flag;
+  __shared__ int split_last;
 
   const uint32_t raw = smem_address(raw_shared);
   const uint32_t base = (raw + 1023u) & ~1023u;
@@ -224,7 +231,10 @@ __global__ void __launch_bounds__(kGemmThreads, 1)
   const int lane = tid & 31;
   const int row_block = blockIdx.x;   // 128 output rows
   const int token_block = blockIdx.y * accumulators;  // first of this CTA's blocks of TN tokens
-  const int stages_k = p.k / kStageK;
+  const int group_begin = blockIdx.z * p.groups_per_split;
+  const int group_end = min(p.groups, group_begin + p.groups_per_split);
+  const int stage_first = 2 * group_begin;            // first 64-channel stage of this CTA's K range
+  const int stages_k = 2 * (group_end - group_begin); // stages this CTA runs
 
   if (tid == 0) {
     abort_flag = 0;
@@ -281,7 +291,7 @@ __global__ void __launch_bounds__(kGemmThreads, 1)
     };
     auto fetch_group = [&](int group) {
       GroupWords g = {{0u, 0u}, 0u, 0u};
-      if (row_valid && group < p.groups) {
+      if (row_valid && group < group_end) {
         const size_t cell = cell_base + static_cast<size_t>(group) * 16;
         g.word[0] = ldg_stream_u1(p.codes + cell * 8 + part);
         g.word[1] = ldg_stream_u1(p.codes + cell * 8 + 4 + part);
@@ -290,7 +300,7 @@ __global__ void __launch_bounds__(kGemmThreads, 1)
       }
       return g;
     };
-    GroupWords ahead0 = fetch_group(0), ahead1 = fetch_group(1);
+    GroupWords ahead0 = fetch_group(group_begin), ahead1 = fetch_group(group_begin + 1);
     long long waited = 0, worked = 0, fenced = 0, stored = 0;  // (profiling build) clock sums of the phases
     [[maybe_unused]] const long long decode_begin = GEMM_CLOCK();
     uint32_t words[2] = {0, 0};
@@ -308,7 +318,7 @@ __global__ void __launch_bounds__(kGemmThreads, 1)
         minimum = e.x;
         step = e.y;
         ahead0 = ahead1;
-        ahead1 = fetch_group((ks >> 1) + 2);
+        ahead1 = fetch_group(group_begin + (ks >> 1) + 2);
       }
       const long long t0 = GEMM_CLOCK();
       alive = bounded_wait(empty_bar(s), phase ^ 1u, abort_ptr, p.status);
@@ -370,7 +380,7 @@ __global__ void __launch_bounds__(kGemmThreads, 1)
     if (p.trace && tid == 0)
       p.trace[(static_cast<size_t>(blockIdx.y) * gridDim.x + blockIdx.x) * 16 + 12] = GEMM_CLOCK() - epilogue_begin;
 #endif
-    if (alive) {
+    {
       constexpr int kColumnParts = kDecodeWarps / 4;
       const int quarter = warp & 3;                 // TMEM lanes 32*quarter .. +31
       const int column_part = warp >> 2;            // warps 0-3: first part of the tokens, ...
@@ -387,35 +397,90 @@ __global__ void __launch_bounds__(kGemmThreads, 1)
       const uint32_t turn = a_base + static_cast<uint32_t>(warp) * 1024u;
       const int out_base = row_block * kTileRows + quarter * 32;
       const bool wide = (p.n & 7) == 0 && out_base + 32 <= p.n && (reinterpret_cast<uintptr_t>(p.y) & 15) == 0;
-      for (int a = 0; a < accumulators; ++a) {
-        for (int c = column_begin; c < column_end; c += 16) {
-          uint32_t r[16];
-          tmem_load_16(tmem_base + (static_cast<uint32_t>(quarter * 32) << 16) + a * 256 + c, r);
-          tmem_load_wait();
-          const int token_base = (token_block + a) * tn + c;
-          if (wide) {
+      auto store_chunk = [&](const uint32_t (&r)[16], int a, int c) {
+        const int token_base = (token_block + a) * tn + c;
+        if (wide) {
 #pragma unroll
-            for (int i = 0; i < 16; ++i) {
-              const __half h = __float2half_rn(__uint_as_float(r[i]));
-              asm volatile("st.shared.u16 [%0], %1;" ::"r"(turn + i * 64u + lane * 2u),
-                           "h"(*reinterpret_cast<const unsigned short *>(&h)));
+          for (int i = 0; i < 16; ++i) {
+            const __half h = __float2half_rn(__uint_as_float(r[i]));
+            asm volatile("st.shared.u16 [%0], %1;" ::"r"(turn + i * 64u + lane * 2u),
+                         "h"(*reinterpret_cast<const unsigned short *>(&h)));
+          }
+          __syncwarp();
+#pragma unroll
+          for (int q = 0; q < 2; ++q) {
+            const int piece = lane + 32 * q;          // token = piece / 4, eight rows = piece % 4
+            const int token = token_base + (piece >> 2);
+            const uint4 v = lds_u4(turn + static_cast<uint32_t>(piece) * 16u);
+            if (token < p.rows)
+              *reinterpret_cast<uint4 *>(p.y + static_cast<size_t>(token) * p.n + out_base + (piece & 3) * 8) = v;
+          }
+          __syncwarp();
+        } else if (out < p.n) {
+#pragma unroll
+          for (int i = 0; i < 16; ++i) {
+            const int token = token_base + i;
+            if (token < p.rows)
+              p.y[static_cast<size_t>(token) * p.n + out] = __float2half_rn(__uint_as_float(r[i]));
+          }
+        }
+      };
+      if (p.k_splits == 1) {
+        if (alive) {
+          for (int a = 0; a < accumulators; ++a) {
+            for (int c = column_begin; c < column_end; c += 16) {
+              uint32_t r[16];
+              tmem_load_16(tmem_base + (static_cast<uint32_t>(quarter * 32) << 16) + a * 256 + c, r);
+              tmem_load_wait();
+              store_chunk(r, a, c);
             }
-            __syncwarp();
+          }
+        }
+      } else {
+        // ---- split K: FP32 tile to scratch; the last split of the tile to arrive adds them all
+        const int tile_id = blockIdx.y * gridDim.x + blockIdx.x;
+        const size_t tile_floats = static_cast<size_t>(accumulators) * tn * kTileRows;
+        const size_t split_stride = static_cast<size_t>(gridDim.x) * gridDim.y * tile_floats;
+        float *tile_partial = p.partial + static_cast<size_t>(tile_id) * tile_floats;
+        if (alive) {
+          float *mine = tile_partial + blockIdx.z * split_stride;
+          for (int a = 0; a < accumulators; ++a) {
+            for (int c = column_begin; c < column_end; c += 16) {
+              uint32_t r[16];
+              tmem_load_16(tmem_base + (static_cast<uint32_t>(quarter * 32) << 16) + a * 256 + c, r);
+              tmem_load_wait();
 #pragma unroll
-            for (int q = 0; q < 2; ++q) {
-              const int piece = lane + 32 * q;          // token = piece / 4, eight rows = piece % 4
-              const int token = token_base + (piece >> 2);
-              const uint4 v = lds_u4(turn + static_cast<uint32_t>(piece) * 16u);
-              if (token < p.rows)
-                *reinterpret_cast<uint4 *>(p.y + static_cast<size_t>(token) * p.n + out_base + (piece & 3) * 8) = v;
+              for (int i = 0; i < 16; ++i)
+                mine[static_cast<size_t>(a * tn + c + i) * kTileRows + quarter * 32 + lane] = __uint_as_float(r[i]);
             }
-            __syncwarp();
-          } else if (out < p.n) {
+          }
+        }
+        __threadfence();
+        asm volatile("bar.sync 1, %0;" ::"n"(kDecodeThreads) : "memory");  // (decode warps only, all of them)
+        if (tid == 0) {
+          const unsigned arrived = atomicAdd(p.counters + tile_id, 1u);
+          const bool last = arrived == static_cast<unsigned>(p.k_splits - 1);
+          if (last) p.counters[tile_id] = 0u;  // (zero again for the next launch)
+          split_last = last && abort_flag == 0;
+        }
+        asm volatile("bar.sync 1, %0;" ::"n"(kDecodeThreads) : "memory");
+        if (split_last) {
+          __threadfence();
+          for (int a = 0; a < accumulators; ++a) {
+            for (int c = column_begin; c < column_end; c += 16) {
+              float sum[16];
 #pragma unroll
-            for (int i = 0; i < 16; ++i) {
-              const int token = token_base + i;
-              if (token < p.rows)
-                p.y[static_cast<size_t>(token) * p.n + out] = __float2half_rn(__uint_as_float(r[i]));
+              for (int i = 0; i < 16; ++i) sum[i] = 0.0f;
+              for (int z = 0; z < p.k_splits; ++z) {  // (index order: the result does not depend on who came last)
+                const float *theirs = tile_partial + z * split_stride;
+#pragma unroll
+                for (int i = 0; i < 16; ++i)
+                  sum[i] += __ldcg(theirs + static_cast<size_t>(a * tn + c + i) * kTileRows + quarter * 32 + lane);
+              }
+              uint32_t r[16];
+#pragma unroll
+              for (int i = 0; i < 16; ++i) r[i] = __float_as_uint(sum[i]);
+              store_chunk(r, a, c);
             }
           }
         }
@@ -439,7 +504,7 @@ __global__ void __launch_bounds__(kGemmThreads, 1)
         waited += GEMM_CLOCK() - t0;
         mbarrier_arrive_expect_tx(full_bar(s), static_cast<uint32_t>(b_stage_bytes));
         for (int a = 0; a < accumulators; ++a)  // (a block past the last token reads the fill value)
-          tma_load_2d(b_base + s * b_stage_bytes + a * b_tile_bytes, &x_map, ks * kStageK,
+          tma_load_2d(b_base + s * b_stage_bytes + a * b_tile_bytes, &x_map, (stage_first + ks) * kStageK,
                       (token_block + a) * tn, full_bar(s));
       }
 #ifdef SAGEB200_TRACE
@@ -552,23 +617,26 @@ cudaError_t launch_gather(const __half *x, const int32_t *perm, __half *xq, int 
   return cudaGetLastError();
 }
 
-GemmPlan plan_gemm_tc(int rows, int n, int k, int sm_count) {
-  (void)k;
+GemmPlan plan_gemm_tc(int rows, int n, int k, int sm_count, bool allow_split) {
   GemmPlan plan{};
   plan.row_blocks = (n + kTileRows - 1) / kTileRows;
   if (sm_count <= 0) sm_count = 148;
-  // Tokens per accumulator (at most 256, 128 or 64, the rows split evenly) and accumulators per
-  // CTA (two token blocks sharing every decoded weight stage).  Cost model per 64-channel stage
-  // of one CTA, in cycles - the kernel runs at the slowest of
+  const int groups = k / 128;
+  // Tokens per accumulator (at most 256, 128 or 64, the rows split evenly), accumulators per CTA
+  // (two token blocks sharing every decoded weight stage) and CTAs per output tile along K.
+  // Cost model per 64-channel stage of one CTA, in cycles - the kernel runs at the slowest of
   //   shared-memory traffic / 128 bytes per cycle: the MMA's operand reads (A again for every
   //     accumulator), the activation tile written by TMA, the decoded weights and codebook reads
   //   the tensor pipe: 135 cycles per 128 x 256 x 16 instruction
-  //   the decode warps: ~800 cycles per stage
-  // times the number of waves the grid needs.  Large grids end up with 256 tokens x 2 (least
-  // decode work per output); grids that would leave most SMs idle take smaller token blocks, whose
-  // redundant decoding runs on SMs that had nothing to do.
-  int tn = 0, best_accumulators = 1;
+  //   the decode warps: ~1200 cycles per stage (measured with the per-role clock sums of the
+  //     profiling build)
+  // times the stages per CTA and the waves the grid needs, plus, with a K split, the last CTA's
+  // pass over all splits' FP32 tiles.  Large grids end up with 256 tokens x 2 (least decode work
+  // per output); grids that would leave most SMs idle split K, so the decode work of one weight
+  // tile is spread over several SMs.
+  int tn = 0, best_accumulators = 1, best_splits = 1;
   double best_cost = 0.0;
+  const int split_choices[] = {1, 2, 3, 4, 5, 6, 8};
   for (int cap = 256; cap >= 64; cap /= 2) {
     const int blocks = (rows + cap - 1) / cap;
     const int candidate = ((rows + blocks - 1) / blocks + 15) / 16 * 16;
@@ -579,21 +647,37 @@ GemmPlan plan_gemm_tc(int rows, int n, int k, int sm_count) {
       const double tensor = accumulators * 4.0 * 135.0 * candidate / 256.0;
       double stage = traffic / 128.0;
       if (stage < tensor) stage = tensor;
-      if (stage < 800.0) stage = 800.0;
-      const long long ctas = static_cast<long long>(plan.row_blocks) * ((token_blocks + accumulators - 1) / accumulators);
-      const long long waves = (ctas + sm_count - 1) / sm_count;
-      const double cost = stage * static_cast<double>(waves);
-      if (tn == 0 || cost < best_cost * 0.97) {  // (prefer the earlier, larger tile on near ties)
-        tn = candidate;
-        best_accumulators = accumulators;
-        best_cost = cost;
+      if (stage < 1200.0) stage = 1200.0;
+      const long long tiles = static_cast<long long>(plan.row_blocks) * ((token_blocks + accumulators - 1) / accumulators);
+      for (int wanted : split_choices) {
+        // (a split only where the split grid still fits one wave: it exists to fill idle SMs, and
+        //  its FP32 tiles would cost more HBM traffic than they save on a grid of several waves)
+        if (wanted > 1 && (!allow_split || wanted * 2 > groups || tiles * wanted > sm_count)) continue;
+        const int per_split = (groups + wanted - 1) / wanted;
+        const int splits = (groups + per_split - 1) / per_split;  // (no empty split)
+        if (splits != wanted) continue;
+        const long long waves = (tiles * splits + sm_count - 1) / sm_count;
+        double cost = 2.0 * per_split * stage * static_cast<double>(waves);
+        if (splits > 1)  // tile written once per split, then read back by the last CTA (~64 bytes per cycle)
+          cost += 2000.0 + (splits + 1.0) * accumulators * candidate * 128.0 * 4.0 / 64.0;
+        if (tn == 0 || cost < best_cost * 0.97) {  // (prefer the earlier, simpler choice on near ties)
+          tn = candidate;
+          best_accumulators = accumulators;
+          best_splits = splits;
+          best_cost = cost;
+        }
       }
     }
-    if (rows <= cap / 2) continue;  // (smaller caps still change the split)
   }
   plan.tokens_per_cta = tn;
   plan.token_blocks = (rows + tn - 1) / tn;
   plan.accumulators = best_accumulators;
+  plan.k_splits = best_splits;
+  plan.groups_per_split = (groups + best_splits - 1) / best_splits;
+  {
+    const size_t tiles = static_cast<size_t>(plan.row_blocks) * ((plan.token_blocks + plan.accumulators - 1) / plan.accumulators);
+    plan.partial_bytes = best_splits > 1 ? tiles * best_splits * plan.accumulators * tn * kTileRows * sizeof(float) : 0;
+  }
   const int stage_bytes = kAStageBytes + plan.accumulators * tn * kStageK * 2;
   int stages = (kGemmSharedLimit - kBookBytes - 2 * 1024) / stage_bytes;
   if (stages > kMaxStages) stages = kMaxStages;
@@ -615,7 +699,8 @@ cudaError_t configure_gemm_tc() {
 cudaError_t launch_gemm_tc(const __half *xq, const uint32_t *codes, const uint32_t *radii,
                            const uint32_t *grid, const uint32_t *book, __half *y, int *status,
                            int rows, int n, int k, int entries, const GemmPlan &plan,
-                           cudaStream_t stream) {
+                           cudaStream_t stream, float *partial, unsigned *counters) {
+  if (plan.k_splits > 1 && (!partial || !counters)) return cudaErrorInvalidValue;
   EncodeTiledFn encode = encode_tiled();
   if (!encode) return cudaErrorNotSupported;
   CUtensorMap map;
@@ -647,7 +732,11 @@ cudaError_t launch_gemm_tc(const __half *xq, const uint32_t *codes, const uint32
   p.tmem_columns = plan.tmem_columns;
   p.accumulators = plan.accumulators;
   p.trace = trace_buffer();
-  const dim3 blocks(plan.row_blocks, (plan.token_blocks + plan.accumulators - 1) / plan.accumulators);
+  p.k_splits = plan.k_splits;
+  p.groups_per_split = plan.groups_per_split;
+  p.partial = partial;
+  p.counters = counters;
+  const dim3 blocks(plan.row_blocks, (plan.token_blocks + plan.accumulators - 1) / plan.accumulators, plan.k_splits);
   sage_gemm_tc_kernel<<<blocks, kGemmThreads, plan.shared_bytes, stream>>>(p, map);
   return cudaGetLastError();
 }

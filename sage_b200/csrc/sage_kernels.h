@@ -120,17 +120,23 @@ struct GemmPlan {
   int stages;
   int tmem_columns;
   int accumulators;     // token blocks per CTA (1 or 2) sharing each decoded weight stage
+  int k_splits;         // CTAs that share one output tile along K (1: none)
+  int groups_per_split; // 128-channel groups per K split
+  size_t partial_bytes; // FP32 scratch of the split tiles (0 without a split)
   size_t shared_bytes;
 };
 
-GemmPlan plan_gemm_tc(int rows, int n, int k, int sm_count);
+// `allow_split`: false plans without a K split (no scratch available).
+GemmPlan plan_gemm_tc(int rows, int n, int k, int sm_count, bool allow_split = true);
 cudaError_t configure_gemm_tc();
 // xq: activations already in quantised channel order, 16-byte aligned.  `status` is a
 // device-visible word that receives SAGEB200_ERR_TIMEOUT if a bounded wait runs out.
+// `partial` (plan.partial_bytes) and `counters` (one zeroed word per output tile, left zero) are
+// needed when plan.k_splits > 1.
 cudaError_t launch_gemm_tc(const __half *xq, const uint32_t *codes, const uint32_t *radii,
                            const uint32_t *grid, const uint32_t *book, __half *y, int *status,
                            int rows, int n, int k, int entries, const GemmPlan &plan,
-                           cudaStream_t stream);
+                           cudaStream_t stream, float *partial = nullptr, unsigned *counters = nullptr);
 
 // Causal attention over prompt rows on the tensor cores (prefill_attention.cu); rows are
 // [sequence][token], row (s, t) at cache position positions[s] + t.  head_dim is 128.
