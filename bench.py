@@ -1,7 +1,8 @@
 """Benchmark of the SAGE packed-weight decode path on B200.
 
     python bench.py [--gpus N] [--steps K] [--warmup W] [--impl ours|reference]
-                    [--workload decode_model|decode_linears|tp32b|ep30b|report|linear:K:N:M|sph:K:N:M] [--prompt P]
+                    [--workload decode_model|decode_linears|prompt|tp32b|ep30b|report|linear:K:N:M|sph:K:N:M|
+                               gemm_roles:K:N:M|mega_phases] [--prompt P]
 
 A step is one decoded token of the full Qwen3-4B architecture at batch 1 (synthetic seeded
 packed weights, ABS split cycling 6/7/8 direction bits per matrix; `decode_linears` times the
@@ -140,6 +141,16 @@ class ClockSampler:
 
 
 _CPU_LAYER = None
+_CPU_HEAD = None
+QWEN3_4B_VOCAB = 151936
+
+
+def decode_workload_text(prompt_length: int) -> str:
+    """The default workload in words; both arms print it."""
+    return (f"Qwen3-4B (36 layers, hidden 2560, 32/8 heads, inter 9728, vocab 151936), "
+            f"random-init, all 252 linears SAGE-packed (2.25 bpw), FP16 KV cache, batch 1, "
+            f"greedy decode after a {prompt_length}-token prompt; one step = one token "
+            f"(packed linears + norms + RoPE + attention + lm_head + argmax, one CUDA graph)")
 
 
 def cpu_layer_seconds(repeats: int, threads: int) -> tuple[float, int]:
@@ -167,6 +178,38 @@ def cpu_layer_seconds(repeats: int, threads: int) -> tuple[float, int]:
     return best, cores
 
 
+def cpu_head_seconds(repeats: int, threads: int) -> float:
+    """Best time of the token's unpacked tail on the host cores: the 151936 x 2560 lm_head
+    product and the argmax (torch, FP32 copy of the FP16 matrix, all threads)."""
+    import torch
+
+    global _CPU_HEAD
+    if threads > 0:
+        torch.set_num_threads(threads)
+    if _CPU_HEAD is None:
+        gen = torch.Generator().manual_seed(7)
+        head = (torch.randn(QWEN3_4B_VOCAB, 2560, generator=gen) * 0.02).half().float()
+        x = torch.randn(2560, generator=gen).half().float()
+        _CPU_HEAD = (head, x)
+    head, x = _CPU_HEAD
+    best = float("inf")
+    for _ in range(repeats):
+        begin = time.perf_counter()
+        int(torch.argmax(torch.mv(head, x)))
+        best = min(best, time.perf_counter() - begin)
+    return best
+
+
+def cpu_token_rate(layer_seconds: float, head_seconds: float) -> float:
+    """Tokens per second of the CPU path: 36 decoder layers' packed linears plus the lm_head."""
+    return 1.0 / (layer_seconds * QWEN3_4B_LAYERS + head_seconds)
+
+
+CPU_SAMPLE = ("packed linears of one decoder layer (7 matmuls, M=1, dequantise + FP32 product) timed and scaled by "
+              "36 layers, plus the FP16 lm_head product and argmax timed once per token; norms, RoPE and "
+              "attention over the cache are not included (they favour the CPU number)")
+
+
 def run_reference(args) -> None:
     rank = int(os.environ.get("RANK", "0"))
     if rank != 0:
@@ -174,12 +217,14 @@ def run_reference(args) -> None:
     cores = os.cpu_count() or 1
     for _ in range(max(args.warmup, 1)):
         cpu_layer_seconds(1, cores)
+        cpu_head_seconds(1, cores)
     begin = time.perf_counter()
-    times = [cpu_layer_seconds(1, cores)[0] for _ in range(args.steps)]
+    times = [(cpu_layer_seconds(1, cores)[0], cpu_head_seconds(1, cores)) for _ in range(args.steps)]
     wall = time.perf_counter() - begin
-    layer_seconds = sum(times) / len(times)
-    value = 1.0 / (layer_seconds * QWEN3_4B_LAYERS)
-    sample = "one Qwen3-4B decoder layer (7 packed linears, M=1) per step, scaled by 36 layers"
+    layer_seconds = sum(t[0] for t in times) / len(times)
+    head_seconds = sum(t[1] for t in times) / len(times)
+    value = cpu_token_rate(layer_seconds, head_seconds)
+    prompt_length = args.prompt if args.prompt else 512
     line = {
         "impl": "reference",
         "metric": METRIC,
@@ -194,9 +239,13 @@ def run_reference(args) -> None:
         "vs_baseline": None,
         "dtype": "f16 weights, f32 accumulate",
         "data": "synthetic",
-        "config": {"workload": args.workload, "model": "Qwen3-4B shapes", "batch": 1,
-                   "note": "reference CPU path (dequantise + FP32 matmul) via the C oracle port"},
-        "cpu_baseline": {"value": value, "unit": UNIT, "cores": cores, "kind": "port", "sample": sample},
+        "config": {"workload": decode_workload_text(prompt_length), "prompt_tokens": prompt_length,
+                   "parallelism": "host cores of rank 0",
+                   "note": "the reference's CPU implementation of the path (dequantise, FP32 matmul: "
+                           "tests/inference/reference.py:25-49) restated in C with OpenMP (oracle/); each step "
+                           "times a bounded sample of one token: " + CPU_SAMPLE,
+                   "ms_per_token_estimate": 1000.0 / value},
+        "cpu_baseline": {"value": value, "unit": UNIT, "cores": cores, "kind": "port", "sample": CPU_SAMPLE},
         "e2e": {"value": value, "unit": UNIT, "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0},
         "gpu_launches": 0,
     }
@@ -581,6 +630,7 @@ def run_model(args) -> None:
         peak, peak_kind = measured_peaks()
         achieved = (packed_bytes / sage_launches) / sage_seconds / 1e9
         cpu_seconds, cores = cpu_layer_seconds(3, 0)
+        cpu_head = cpu_head_seconds(3, 0)
         line = {
             "metric": METRIC,
             "value": world * 1000.0 / ms_per_step,
@@ -595,10 +645,7 @@ def run_model(args) -> None:
             "dtype": "f16 products, f32 accumulate",
             "data": "synthetic",
             "config": {
-                "workload": f"Qwen3-4B (36 layers, hidden 2560, 32/8 heads, inter 9728, vocab 151936), "
-                            f"random-init, all 252 linears SAGE-packed (2.25 bpw), FP16 KV cache, batch 1, "
-                            f"greedy decode after a {prompt_length}-token prompt; one step = one token "
-                            f"(packed linears + norms + RoPE + attention + lm_head + argmax, one CUDA graph)",
+                "workload": decode_workload_text(prompt_length),
                 "prompt_tokens": prompt_length,
                 "prefill_ms": prefill_ms,
                 "prefill_note": "whole prompt through each layer at once (packed linears on the tcgen05 GEMM "
@@ -632,12 +679,11 @@ def run_model(args) -> None:
             "decode_batch8": batch8,
             "sharded": sharded,
             "cpu_baseline": {
-                "value": 1.0 / (cpu_seconds * QWEN3_4B_LAYERS),
+                "value": cpu_token_rate(cpu_seconds, cpu_head),
                 "unit": UNIT,
                 "cores": cores,
                 "kind": "port",
-                "sample": "packed linears of one decoder layer (7 matmuls, M=1), best of 3, scaled by 36 "
-                          "layers; norms, attention and lm_head not included (they favour the CPU number)",
+                "sample": CPU_SAMPLE + " (best of 3)",
             },
             "e2e": {
                 "value": world * 1000.0 * args.steps / e2e_ms,
@@ -989,6 +1035,145 @@ def run_ours(args) -> None:
         dist.destroy_process_group()
 
 
+def run_prompt(args) -> None:
+    """`--workload prompt`: the batched prompt pass of Qwen3-4B (`--prompt` tokens through every
+    layer at once: packed linears on the tcgen05 GEMM path, tensor-core causal attention, first
+    token included), timed with CUDA events over `--steps` passes after `--warmup`."""
+    import torch
+
+    from sage_b200.qwen3 import QWEN3_4B, PackedQwen3
+
+    device = torch.device("cuda", 0)
+    model = PackedQwen3(QWEN3_4B, device, seed=0, max_seq=args.prompt + 16, max_new=8)
+    model.capture()
+    prompt = torch.randint(3, QWEN3_4B.vocab, (1, args.prompt), generator=torch.Generator().manual_seed(1))
+    lib = model.lib
+    for _ in range(max(args.warmup, 1)):
+        model.prefill(prompt)
+    torch.cuda.synchronize(device)
+    before = lib.sageb200_launch_count() + lib.sageb200_glue_launch_count()
+    start, stop = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    start.record()
+    for _ in range(args.steps):
+        model.prefill(prompt)
+    stop.record()
+    torch.cuda.synchronize(device)
+    ms = start.elapsed_time(stop) / args.steps
+    print(json.dumps({
+        "metric": "qwen3_4b_sage_2.25bpw_prompt_pass_ms", "value": ms, "unit": "ms", "higher_is_better": False,
+        "prompt_tokens": args.prompt, "prompt_tok_s": args.prompt * 1000.0 / ms, "steps": args.steps,
+        "warmup": args.warmup,
+        "gpu_launches": int(lib.sageb200_launch_count() + lib.sageb200_glue_launch_count() - before),
+        "config": {"workload": f"Qwen3-4B prompt pass, {args.prompt} tokens, batch 1, host-side reset and token "
+                               "copy included"},
+    }), flush=True)
+
+
+def run_gemm_roles(args) -> None:
+    """`--workload gemm_roles:K:N:M` (profiling build of the library only: SAGEB200_LIBRARY =
+    libsage_b200_trace.so): one tcgen05 GEMM call with the per-role clock sums of its CTAs -
+    how long the decode warps wait for a free stage and decode, how long the MMA thread waits
+    for a full stage, the epilogue - as mean SM cycles per CTA and per 64-channel stage."""
+    import ctypes
+
+    import torch
+
+    from sage_b200 import SAGELinear, _lib
+    from sage_b200.synthetic import synthetic_sage_device
+
+    _, k, n, rows = args.workload.split(":")
+    k, n, rows = int(k), int(n), int(rows)
+    lib = _lib.load()
+    device = torch.device("cuda", 0)
+    layer = SAGELinear(synthetic_sage_device(k, n, 3, device, direction_bits=8), n)
+    x = torch.randn(rows, k, device=device, dtype=torch.float16)
+    for _ in range(3):
+        layer(x)
+    torch.cuda.synchronize(device)
+    trace = torch.zeros(1024 * 16, dtype=torch.int64, device=device)
+    lib.sageb200_debug_trace(ctypes.c_void_p(trace.data_ptr()))
+    layer(x)
+    torch.cuda.synchronize(device)
+    lib.sageb200_debug_trace(None)
+    records = trace.view(-1, 16).cpu()
+    records = records[records[:, 2] != 0].double()
+    if records.numel() == 0:
+        print(json.dumps({"workload": args.workload, "error": "no clock sums: load the profiling build "
+                          "(python -m sage_b200.build --trace; SAGEB200_LIBRARY=sage_b200/libsage_b200_trace.so)"}))
+        return
+    names = ["decode_thread0_wait_free_stage", "decode_thread0_decode_store_arrive", "decode_thread0_main_loop",
+             "decode_last_thread_wait_free_stage", "decode_last_thread_decode_store_arrive",
+             "decode_last_thread_main_loop", "epilogue", "tma_thread_wait_free_stage", "mma_thread_wait_full_stage",
+             "mma_thread_main_loop", "decode_thread0_decode_and_store", "decode_thread0_proxy_fence",
+             "epilogue_wait_for_accumulator"]
+    print(json.dumps({"workload": args.workload, "tiles_traced": int(records.shape[0]), "k_stages_total": k // 64,
+                      "mean_sm_cycles_per_cta": {name: float(records[:, i].mean()) for i, name in enumerate(names)}}),
+          flush=True)
+
+
+def run_mega_phases(args) -> None:
+    """`--workload mega_phases` (profiling build only): one Qwen3-4B token through the one-kernel
+    decode step with %globaltimer stamps at every phase boundary of every CTA; prints the median
+    duration of each phase over CTAs and layers, in microseconds, and the graph-replay time."""
+    import ctypes
+    import statistics
+
+    import torch
+
+    from sage_b200 import _lib
+    from sage_b200.qwen3 import QWEN3_4B, PackedQwen3
+
+    lib = _lib.load()
+    device = torch.device("cuda", 0)
+    model = PackedQwen3(QWEN3_4B, device, seed=0, max_seq=args.prompt + 64, max_new=64)
+    if model.mega is None:
+        print(json.dumps({"workload": args.workload, "error": "the one-kernel step does not fit this model"}))
+        return
+    model.use_mega = True
+    model.capture()
+    prompt = torch.randint(3, QWEN3_4B.vocab, (1, args.prompt), generator=torch.Generator().manual_seed(1))
+    model.prefill(prompt)
+    for _ in range(5):
+        model.graph.replay()
+    torch.cuda.synchronize(device)
+    ctas = model.sm_count
+    trace = torch.zeros(ctas * 2048, dtype=torch.int64, device=device)
+    lib.sageb200_debug_trace(ctypes.c_void_p(trace.data_ptr()))
+    model.step(head=True)
+    torch.cuda.synchronize(device)
+    lib.sageb200_debug_trace(None)
+    stamps = trace.view(ctas, 2048).cpu()
+    count = int((stamps[0] != 0).sum())
+    names = ["linear0.staging", "linear0.main_loops", "linear0.combine_and_prefetch", "barrier_to_attention",
+             "attention.partial", "barrier_to_combine", "attention.combine", "barrier_to_linear1", "linear1.staging",
+             "linear1.main_loops", "linear1.combine_and_prefetch", "barrier_to_linear2", "linear2.staging",
+             "linear2.main_loops", "linear2.combine_and_prefetch", "barrier_to_linear3", "linear3.staging",
+             "linear3.main_loops", "linear3.combine_and_prefetch"]
+    per_layer = len(names) + 1
+    layers = QWEN3_4B.layers
+    if count < 1 + layers * per_layer:
+        print(json.dumps({"workload": args.workload, "error": "no phase stamps: load the profiling build "
+                          "(python -m sage_b200.build --trace; SAGEB200_LIBRARY=sage_b200/libsage_b200_trace.so)"}))
+        return
+    microseconds = (stamps[:, :count] - stamps[:, 0].min()).double() / 1000.0
+    phases = {}
+    for i, name in enumerate(names):
+        values = [float((microseconds[:, 1 + layer * per_layer + i + 1] - microseconds[:, 1 + layer * per_layer + i]).median())
+                  for layer in range(2, layers)]
+        phases[name] = statistics.mean(values)
+    start, stop = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    start.record()
+    for _ in range(50):
+        model.graph.replay()
+    stop.record()
+    torch.cuda.synchronize(device)
+    print(json.dumps({"workload": args.workload, "prompt_tokens": args.prompt,
+                      "phase_us_median_over_ctas_mean_over_layers": phases,
+                      "layer_us": sum(phases.values()),
+                      "token_us_traced": float(microseconds[:, count - 1].max()),
+                      "graph_replay_ms_per_token": start.elapsed_time(stop) / 50}), flush=True)
+
+
 def main() -> None:
     parser = argparse.ArgumentParser()
     parser.add_argument("--gpus", type=int, default=1)
@@ -1006,6 +1191,12 @@ def main() -> None:
         run_reference(args)
     elif args.workload.startswith("linear:"):
         run_single_linear(args)
+    elif args.workload.startswith("gemm_roles:"):
+        run_gemm_roles(args)
+    elif args.workload == "mega_phases":
+        run_mega_phases(args)
+    elif args.workload == "prompt":
+        run_prompt(args)
     elif args.workload.startswith("sph:"):
         run_sph_linear(args)
     elif args.workload == "report":
