@@ -1105,7 +1105,8 @@ def run_gemm_roles(args) -> None:
              "decode_last_thread_wait_free_stage", "decode_last_thread_decode_store_arrive",
              "decode_last_thread_main_loop", "epilogue", "tma_thread_wait_free_stage", "mma_thread_wait_full_stage",
              "mma_thread_main_loop", "decode_thread0_decode_and_store", "decode_thread0_proxy_fence",
-             "epilogue_wait_for_accumulator"]
+             "epilogue_wait_for_accumulator", "split_epilogue_write_tiles", "split_epilogue_fence_and_barriers",
+             "split_epilogue_reduce_parts"]
     print(json.dumps({"workload": args.workload, "tiles_traced": int(records.shape[0]), "k_stages_total": k // 64,
                       "mean_sm_cycles_per_cta": {name: float(records[:, i].mean()) for i, name in enumerate(names)}}),
           flush=True)

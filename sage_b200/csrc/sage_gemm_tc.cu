@@ -66,7 +66,7 @@ struct GemmParams {
   // index order and writes the FP16 output
   int k_splits, groups_per_split;
   float *partial;       // [k_splits][tiles][accumulators * TN tokens][128 rows]
-  unsigned *counters;   // [tiles], zero before and after the launch
+  unsigned *counters;   // [tiles][8]: one word per part of a tile, zero before and after the launch
 };
 
 #ifdef SAGEB200_TRACE
@@ -437,45 +437,72 @@ __global__ void __launch_bounds__(kGemmThreads, 1)
           }
         }
       } else {
-        // ---- split K: FP32 tile to scratch; the last split of the tile to arrive adds them all
+        // ---- split K: FP32 tile to scratch, in up to three PARTS (runs of 16-token chunks).  Split z
+        //      writes the parts in the order z, z+1, ...; whoever completes a part's arrival
+        //      counter adds that part's splits in index order and stores it.  CTAs that finish
+        //      together are each the last writer of a different part, so the reduction spreads over
+        //      the tile's CTAs without anyone waiting (a straggler simply reduces more parts).
         const int tile_id = blockIdx.y * gridDim.x + blockIdx.x;
         const size_t tile_floats = static_cast<size_t>(accumulators) * tn * kTileRows;
         const size_t split_stride = static_cast<size_t>(gridDim.x) * gridDim.y * tile_floats;
         float *tile_partial = p.partial + static_cast<size_t>(tile_id) * tile_floats;
-        if (alive) {
-          float *mine = tile_partial + blockIdx.z * split_stride;
-          for (int a = 0; a < accumulators; ++a) {
-            for (int c = column_begin; c < column_end; c += 16) {
+        float *mine = tile_partial + blockIdx.z * split_stride;
+        const int chunks_per_accumulator = tn / 16;
+        const int chunks = accumulators * chunks_per_accumulator;
+        const size_t lane_row = static_cast<size_t>(quarter) * 32 + lane;
+        [[maybe_unused]] long long wrote = 0, synced = 0, reduced = 0;
+        const int parts = min(p.k_splits, 3);  // (each part costs a fence and two barriers)
+        for (int step = 0; step < parts; ++step) {
+          const long long e0 = GEMM_CLOCK();
+          const int part = (static_cast<int>(blockIdx.z) + step) % parts;
+          const int chunk_begin = part * chunks / parts, chunk_end = (part + 1) * chunks / parts;
+          if (alive) {
+            for (int chunk = chunk_begin + column_part; chunk < chunk_end; chunk += kColumnParts) {
+              const int a = chunk / chunks_per_accumulator, c = (chunk % chunks_per_accumulator) * 16;
               uint32_t r[16];
               tmem_load_16(tmem_base + (static_cast<uint32_t>(quarter * 32) << 16) + a * 256 + c, r);
               tmem_load_wait();
 #pragma unroll
               for (int i = 0; i < 16; ++i)
-                mine[static_cast<size_t>(a * tn + c + i) * kTileRows + quarter * 32 + lane] = __uint_as_float(r[i]);
+                mine[static_cast<size_t>(a * tn + c + i) * kTileRows + lane_row] = __uint_as_float(r[i]);
             }
           }
-        }
-        __threadfence();
-        asm volatile("bar.sync 1, %0;" ::"n"(kDecodeThreads) : "memory");  // (decode warps only, all of them)
-        if (tid == 0) {
-          const unsigned arrived = atomicAdd(p.counters + tile_id, 1u);
-          const bool last = arrived == static_cast<unsigned>(p.k_splits - 1);
-          if (last) p.counters[tile_id] = 0u;  // (zero again for the next launch)
-          split_last = last && abort_flag == 0;
-        }
-        asm volatile("bar.sync 1, %0;" ::"n"(kDecodeThreads) : "memory");
-        if (split_last) {
+          const long long e1 = GEMM_CLOCK();
           __threadfence();
-          for (int a = 0; a < accumulators; ++a) {
-            for (int c = column_begin; c < column_end; c += 16) {
+          asm volatile("bar.sync 1, %0;" ::"n"(kDecodeThreads) : "memory");  // (decode warps only, all of them)
+          if (tid == 0) {
+            unsigned *counter = p.counters + tile_id * 8 + part;
+            const bool last = atomicAdd(counter, 1u) == static_cast<unsigned>(p.k_splits - 1);
+            if (last) *counter = 0u;  // (zero again for the next launch)
+            split_last = last && abort_flag == 0;
+          }
+          asm volatile("bar.sync 1, %0;" ::"n"(kDecodeThreads) : "memory");
+          const long long e2 = GEMM_CLOCK();
+          wrote += e1 - e0;
+          synced += e2 - e1;
+          if (split_last) {
+            __threadfence();
+            for (int chunk = chunk_begin + column_part; chunk < chunk_end; chunk += kColumnParts) {
+              const int a = chunk / chunks_per_accumulator, c = (chunk % chunks_per_accumulator) * 16;
               float sum[16];
 #pragma unroll
               for (int i = 0; i < 16; ++i) sum[i] = 0.0f;
-              for (int z = 0; z < p.k_splits; ++z) {  // (index order: the result does not depend on who came last)
-                const float *theirs = tile_partial + z * split_stride;
+              // (index order: the result does not depend on who came last; two splits' loads in
+              //  flight at a time, the adds still in index order)
+              const float *base = tile_partial + static_cast<size_t>(a * tn + c) * kTileRows + lane_row;
+              int z = 0;
+              for (; z + 1 < p.k_splits; z += 2) {
+                float first[16], second[16];
 #pragma unroll
-                for (int i = 0; i < 16; ++i)
-                  sum[i] += __ldcg(theirs + static_cast<size_t>(a * tn + c + i) * kTileRows + quarter * 32 + lane);
+                for (int i = 0; i < 16; ++i) first[i] = __ldcg(base + z * split_stride + static_cast<size_t>(i) * kTileRows);
+#pragma unroll
+                for (int i = 0; i < 16; ++i) second[i] = __ldcg(base + (z + 1) * split_stride + static_cast<size_t>(i) * kTileRows);
+#pragma unroll
+                for (int i = 0; i < 16; ++i) sum[i] = (sum[i] + first[i]) + second[i];
+              }
+              if (z < p.k_splits) {
+#pragma unroll
+                for (int i = 0; i < 16; ++i) sum[i] += __ldcg(base + z * split_stride + static_cast<size_t>(i) * kTileRows);
               }
               uint32_t r[16];
 #pragma unroll
@@ -483,7 +510,16 @@ __global__ void __launch_bounds__(kGemmThreads, 1)
               store_chunk(r, a, c);
             }
           }
+          reduced += GEMM_CLOCK() - e2;
         }
+#ifdef SAGEB200_TRACE
+        if (p.trace && tid == 0) {
+          long long *record = p.trace + static_cast<size_t>(tile_id) * 16;
+          record[13] = wrote;
+          record[14] = synced;
+          record[15] = reduced;
+        }
+#endif
       }
     }
 #ifdef SAGEB200_TRACE
@@ -652,7 +688,7 @@ GemmPlan plan_gemm_tc(int rows, int n, int k, int sm_count, bool allow_split) {
       for (int wanted : split_choices) {
         // (a split only where the split grid still fits one wave: it exists to fill idle SMs, and
         //  its FP32 tiles would cost more HBM traffic than they save on a grid of several waves)
-        if (wanted > 1 && (!allow_split || wanted * 2 > groups || tiles * wanted > sm_count)) continue;
+        if (wanted > 1 && (!allow_split || wanted * 2 > groups || tiles * wanted > sm_count || tiles > 2048)) continue;
         const int per_split = (groups + wanted - 1) / wanted;
         const int splits = (groups + per_split - 1) / per_split;  // (no empty split)
         if (splits != wanted) continue;

@@ -131,7 +131,7 @@ GemmPlan plan_gemm_tc(int rows, int n, int k, int sm_count, bool allow_split = t
 cudaError_t configure_gemm_tc();
 // xq: activations already in quantised channel order, 16-byte aligned.  `status` is a
 // device-visible word that receives SAGEB200_ERR_TIMEOUT if a bounded wait runs out.
-// `partial` (plan.partial_bytes) and `counters` (one zeroed word per output tile, left zero) are
+// `partial` (plan.partial_bytes) and `counters` (eight zeroed words per output tile, left zero) are
 // needed when plan.k_splits > 1.
 cudaError_t launch_gemm_tc(const __half *xq, const uint32_t *codes, const uint32_t *radii,
                            const uint32_t *grid, const uint32_t *book, __half *y, int *status,
