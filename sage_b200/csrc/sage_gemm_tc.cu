@@ -601,25 +601,47 @@ __global__ void __launch_bounds__(kGemmThreads, 1)
   }
 }
 
-// x_q[m][j] = x[m][perm[j]]  (or a plain copy when perm is null): 2-byte loads, 16-byte stores.
-__global__ void __launch_bounds__(256) sage_gather_kernel(const __half *__restrict__ x,
-                                                          const int32_t *__restrict__ perm,
-                                                          __half *__restrict__ xq, int rows, int k) {
+// x_q[m][j] = x[m][perm[j]]  (or a plain copy when perm is null).  One CTA per activation row at a
+// time: the row is brought into shared memory with 16-byte (or, for an odd base address, 2-byte)
+// loads, the permutation is read eight indices at a time, the gathered values come out of shared
+// memory and leave as 16-byte stores - no 2-byte global loads, which cost a sector each.
+constexpr int kGatherThreads = 256;
+__global__ void __launch_bounds__(kGatherThreads) sage_gather_kernel(const __half *__restrict__ x,
+                                                                     const int32_t *__restrict__ perm,
+                                                                     __half *__restrict__ xq, int rows, int k) {
+  extern __shared__ __align__(16) unsigned char gather_shared[];
+  __half *row_shared = reinterpret_cast<__half *>(gather_shared);
   const int vectors = k >> 3;
-  const long long total = static_cast<long long>(rows) * vectors;
-  for (long long item = static_cast<long long>(blockIdx.x) * 256 + threadIdx.x; item < total;
-       item += static_cast<long long>(gridDim.x) * 256) {
-    const int m = static_cast<int>(item / vectors);
-    const int v = static_cast<int>(item - static_cast<long long>(m) * vectors);
+  const bool perm_wide = (reinterpret_cast<uintptr_t>(perm) & 15) == 0;
+  for (int m = blockIdx.x; m < rows; m += gridDim.x) {
     const __half *source = x + static_cast<size_t>(m) * k;
-    __align__(16) __half values[8];
-#pragma unroll
-    for (int d = 0; d < 8; ++d) {
-      const int j = v * 8 + d;
-      values[d] = source[perm ? perm[j] : j];
+    if ((reinterpret_cast<uintptr_t>(source) & 15) == 0) {
+      for (int v = threadIdx.x; v < vectors; v += kGatherThreads)
+        reinterpret_cast<uint4 *>(row_shared)[v] = reinterpret_cast<const uint4 *>(source)[v];
+    } else {
+      for (int j = threadIdx.x; j < k; j += kGatherThreads) row_shared[j] = source[j];
     }
-    *reinterpret_cast<uint4 *>(xq + static_cast<size_t>(m) * k + static_cast<size_t>(v) * 8) =
-        *reinterpret_cast<const uint4 *>(values);
+    __syncthreads();
+    uint4 *destination = reinterpret_cast<uint4 *>(xq + static_cast<size_t>(m) * k);
+    for (int v = threadIdx.x; v < vectors; v += kGatherThreads) {
+      if (perm == nullptr) {
+        destination[v] = reinterpret_cast<const uint4 *>(row_shared)[v];
+        continue;
+      }
+      int index[8];
+      if (perm_wide) {
+        *reinterpret_cast<int4 *>(index) = reinterpret_cast<const int4 *>(perm)[2 * v];
+        *reinterpret_cast<int4 *>(index + 4) = reinterpret_cast<const int4 *>(perm)[2 * v + 1];
+      } else {
+#pragma unroll
+        for (int d = 0; d < 8; ++d) index[d] = perm[v * 8 + d];
+      }
+      __align__(16) __half values[8];
+#pragma unroll
+      for (int d = 0; d < 8; ++d) values[d] = row_shared[index[d]];
+      destination[v] = *reinterpret_cast<const uint4 *>(values);
+    }
+    __syncthreads();
   }
 }
 
@@ -645,11 +667,22 @@ EncodeTiledFn encode_tiled() {
 
 cudaError_t launch_gather(const __half *x, const int32_t *perm, __half *xq, int rows, int k,
                           cudaStream_t stream, int sm_count) {
-  const long long total = static_cast<long long>(rows) * (k >> 3);
-  long long blocks = (total + 255) / 256;
-  if (blocks > static_cast<long long>(sm_count) * 8) blocks = static_cast<long long>(sm_count) * 8;
+  const size_t shared = static_cast<size_t>(k) * sizeof(__half);
+  if (shared > 200 * 1024) return cudaErrorInvalidValue;  // (K beyond 102400 channels)
+  static bool configured[64] = {};
+  int device = 0;
+  cudaError_t error = cudaGetDevice(&device);
+  if (error != cudaSuccess) return error;
+  if (shared > 48 * 1024 && device >= 0 && device < 64 && !configured[device]) {
+    error = cudaFuncSetAttribute(sage_gather_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, 200 * 1024);
+    if (error != cudaSuccess) return error;
+    configured[device] = true;
+  }
+  int blocks = rows;
+  const int cap = (sm_count > 0 ? sm_count : 148) * 8;
+  if (blocks > cap) blocks = cap;
   if (blocks < 1) blocks = 1;
-  sage_gather_kernel<<<static_cast<unsigned>(blocks), 256, 0, stream>>>(x, perm, xq, rows, k);
+  sage_gather_kernel<<<static_cast<unsigned>(blocks), kGatherThreads, shared, stream>>>(x, perm, xq, rows, k);
   return cudaGetLastError();
 }
 
