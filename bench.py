@@ -813,6 +813,7 @@ def measure_sharded(kind: str, args, device, group, cpu_group, world: int, rank:
         "batch": batch,
         "parallelism": (f"ep{world}" if expert_parallel else f"tp{world}") if sharded else "single GPU",
         "collective": collective,
+        "collective_note": getattr(model, "peer_error", "") or None,
         "collective_calls_per_step": calls,
         "per_rank_hbm_bytes_per_step": step_bytes,
         "per_rank_hbm_gbs": step_bytes / (ms_per_step / 1000.0) / 1e9,

@@ -33,25 +33,51 @@ class PeerExchange:
             raise ValueError(f"a peer exchange serves 2..{_lib.PEER_MAX_WORLD} ranks")
         self.capacity = (int(capacity) + 7) // 8 * 8
         self.own = ctypes.c_void_p()
+        self.exchanges = (ctypes.c_void_p * _lib.PEER_MAX_WORLD)()
+        self.opened = []
         handle = (ctypes.c_ubyte * _lib.PEER_HANDLE_BYTES)()
         with torch.cuda.device(self.device):
-            _lib.check(self.lib.sageb200_peer_create(self.world, self.capacity, ctypes.byref(self.own), handle))
+            # Every rank runs every collective below whatever happens to it, and the ranks agree on
+            # the outcome at the end, so that a rank that cannot allocate or map (IPC not permitted
+            # in this container, peer access unavailable) makes ALL ranks raise together instead
+            # of leaving the others waiting on flags nobody will publish.
+            failure = ""
+            status = self.lib.sageb200_peer_create(self.world, self.capacity, ctypes.byref(self.own), handle)
+            if status != _lib.OK:
+                failure = f"sageb200_peer_create failed with status {status}"
+                self.own = ctypes.c_void_p()
             mine = torch.tensor(list(handle), dtype=torch.uint8, device=self.device)
             everyone = torch.empty(self.world * _lib.PEER_HANDLE_BYTES, dtype=torch.uint8, device=self.device)
             dist.all_gather_into_tensor(everyone, mine, group=group)
             handles = everyone.cpu().view(self.world, _lib.PEER_HANDLE_BYTES)
-            self.exchanges = (ctypes.c_void_p * _lib.PEER_MAX_WORLD)()
-            self.opened = []
-            for r in range(self.world):
-                if r == self.rank:
-                    self.exchanges[r] = self.own.value
-                    continue
-                raw = (ctypes.c_ubyte * _lib.PEER_HANDLE_BYTES)(*handles[r].tolist())
-                mapped = ctypes.c_void_p()
-                _lib.check(self.lib.sageb200_peer_open(raw, ctypes.byref(mapped)))
-                self.exchanges[r] = mapped.value
-                self.opened.append(mapped.value)
+            created = torch.tensor([0 if failure else 1], dtype=torch.int32, device=self.device)
+            dist.all_reduce(created, op=dist.ReduceOp.MIN, group=group)
+            if int(created) == 1:
+                for r in range(self.world):
+                    if r == self.rank:
+                        self.exchanges[r] = self.own.value
+                        continue
+                    raw = (ctypes.c_ubyte * _lib.PEER_HANDLE_BYTES)(*handles[r].tolist())
+                    mapped = ctypes.c_void_p()
+                    status = self.lib.sageb200_peer_open(raw, ctypes.byref(mapped))
+                    if status != _lib.OK:
+                        failure = failure or f"sageb200_peer_open of rank {r}'s exchange failed with status {status}"
+                        continue
+                    self.exchanges[r] = mapped.value
+                    self.opened.append(mapped.value)
+            elif not failure:
+                failure = "another rank could not allocate its exchange"
             # nobody launches before every rank has mapped every exchange
+            agreed = torch.tensor([0 if failure else 1], dtype=torch.int32, device=self.device)
+            dist.all_reduce(agreed, op=dist.ReduceOp.MIN, group=group)
+            if int(agreed) != 1:
+                for mapped in self.opened:
+                    self.lib.sageb200_peer_close(ctypes.c_void_p(mapped))
+                dist.barrier(group=group)
+                if self.own.value:
+                    self.lib.sageb200_peer_destroy(self.own)
+                self.own = None
+                raise RuntimeError("sage_b200: peer exchange unavailable: " + (failure or "another rank failed to map a peer"))
             dist.barrier(group=group)
         self.calls = 0
 

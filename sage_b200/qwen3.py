@@ -158,11 +158,16 @@ class PackedQwen3:
         # exchange buffers of the one-kernel all-reduce (row-parallel outputs, replicated-token
         # expert outputs): one decode step's [batch, hidden] rows
         self.peer = None
+        self.peer_error = ""
         reduce_group = tp_group if world > 1 else (ep_group if self.ep_world > 1 and ep_mode == "all_reduce" else None)
         if collective == "peer" and reduce_group is not None and not self.dense:
             from .peer import PeerExchange
 
-            self.peer = PeerExchange(reduce_group, self.device, batch * config.hidden)
+            try:  # (all ranks succeed or all ranks raise, see PeerExchange)
+                self.peer = PeerExchange(reduce_group, self.device, batch * config.hidden)
+            except RuntimeError as error:  # the GPUs cannot map each other's memory here: NCCL serves
+                self.peer = None
+                self.peer_error = str(error)
         self.heads, self.kv_heads = config.heads // world, config.kv_heads // world
         self.lib = _lib.load()
         self.sm_count = torch.cuda.get_device_properties(self.device).multi_processor_count
