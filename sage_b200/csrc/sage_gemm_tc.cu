@@ -65,6 +65,11 @@ struct GemmParams {
   // its FP32 tile in `partial`, and the last CTA of a tile to arrive (counter) adds the splits in
   // index order and writes the FP16 output
   int k_splits, groups_per_split;
+  // packed format: 0 = SAGE (tiled words, planar codebook, (min, step) grid); 1 = SPHQuant
+  // (row-major 16-bit codes in `codes`, per-(row, group) high radius word in `radii`, FP16 scales
+  // in `grid` and minimums in `mins`, entry-major 64 x 8 codebook, n rows need no padding)
+  int format;
+  const __half *mins;
   float *partial;       // [k_splits][tiles][accumulators * TN tokens][128 rows]
   unsigned *counters;   // [tiles][8]: one word per part of a tile, zero before and after the launch
 };
@@ -255,10 +260,14 @@ __global__ void __launch_bounds__(kGemmThreads, 1)
   // codebook, interleaved: entry e = 16 bytes (dims 0..7)
   for (int e = tid; e < p.entries; e += kGemmThreads) {
     uint4 entry;
-    entry.x = p.book[e];
-    entry.y = p.book[p.entries + e];
-    entry.z = p.book[2 * p.entries + e];
-    entry.w = p.book[3 * p.entries + e];
+    if (p.format == 1) {
+      entry = reinterpret_cast<const uint4 *>(p.book)[e];
+    } else {
+      entry.x = p.book[e];
+      entry.y = p.book[p.entries + e];
+      entry.z = p.book[2 * p.entries + e];
+      entry.w = p.book[3 * p.entries + e];
+    }
     // eight copies, entry-major: lane l reads copy l % 8, so the eight lanes of a quarter warp hit
     // eight different 16-byte bank groups whatever their indices (rotated fill order for the same reason)
 #pragma unroll
@@ -278,8 +287,10 @@ __global__ void __launch_bounds__(kGemmThreads, 1)
     const int part = tid % kRowThreads;
     const int out_row = row_block * kTileRows + row;
     const int tile = out_row >> 4;
-    const bool row_valid = tile < p.tiles;  // rows past the last packed tile decode to zero
+    // rows past the last packed tile (SAGE) / past n (SPHQuant) decode to zero
+    const bool row_valid = p.format == 1 ? out_row < p.n : tile < p.tiles;
     const size_t cell_base = (static_cast<size_t>(row_valid ? tile : 0) * p.groups) * 16 + (out_row & 15);
+    const size_t sph_row = static_cast<size_t>(row_valid ? out_row : 0);
     const uint32_t row_offset = static_cast<uint32_t>(row >> 3) * 1024u + static_cast<uint32_t>(row & 7) * 128u;
     const uint32_t index_mask = static_cast<uint32_t>(p.entries - 1);
     // One 128-channel group feeds two stages.  The thread's packed words of a group (two code
@@ -292,11 +303,23 @@ __global__ void __launch_bounds__(kGemmThreads, 1)
     auto fetch_group = [&](int group) {
       GroupWords g = {{0u, 0u}, 0u, 0u};
       if (row_valid && group < group_end) {
-        const size_t cell = cell_base + static_cast<size_t>(group) * 16;
-        g.word[0] = ldg_stream_u1(p.codes + cell * 8 + part);
-        g.word[1] = ldg_stream_u1(p.codes + cell * 8 + 4 + part);
-        g.radius = ldg_stream_u1(p.radii + cell);
-        g.endpoints = ldg_stream_u1(p.grid + cell);
+        if (p.format == 1) {
+          // sixteen 16-bit codes per group and row; this thread's two of each 64-channel half
+          const uint32_t *row_codes = p.codes + (sph_row * p.groups + group) * 8;
+          const size_t cell = sph_row * p.groups + group;
+          g.word[0] = ldg_stream_u1(row_codes + part);
+          g.word[1] = ldg_stream_u1(row_codes + 4 + part);
+          g.radius = ldg_stream_u1(p.radii + cell);
+          const uint32_t minimum = reinterpret_cast<const unsigned short *>(p.mins)[cell];
+          const uint32_t scale = reinterpret_cast<const unsigned short *>(p.grid)[cell];
+          g.endpoints = minimum | (scale << 16);  // (min, step) as in the SAGE grid
+        } else {
+          const size_t cell = cell_base + static_cast<size_t>(group) * 16;
+          g.word[0] = ldg_stream_u1(p.codes + cell * 8 + part);
+          g.word[1] = ldg_stream_u1(p.codes + cell * 8 + 4 + part);
+          g.radius = ldg_stream_u1(p.radii + cell);
+          g.endpoints = ldg_stream_u1(p.grid + cell);
+        }
       }
       return g;
     };
@@ -768,7 +791,7 @@ cudaError_t configure_gemm_tc() {
 cudaError_t launch_gemm_tc(const __half *xq, const uint32_t *codes, const uint32_t *radii,
                            const uint32_t *grid, const uint32_t *book, __half *y, int *status,
                            int rows, int n, int k, int entries, const GemmPlan &plan,
-                           cudaStream_t stream, float *partial, unsigned *counters) {
+                           cudaStream_t stream, float *partial, unsigned *counters, const __half *sph_mins) {
   if (plan.k_splits > 1 && (!partial || !counters)) return cudaErrorInvalidValue;
   EncodeTiledFn encode = encode_tiled();
   if (!encode) return cudaErrorNotSupported;
@@ -805,6 +828,8 @@ cudaError_t launch_gemm_tc(const __half *xq, const uint32_t *codes, const uint32
   p.groups_per_split = plan.groups_per_split;
   p.partial = partial;
   p.counters = counters;
+  p.format = sph_mins ? 1 : 0;
+  p.mins = sph_mins;
   const dim3 blocks(plan.row_blocks, (plan.token_blocks + plan.accumulators - 1) / plan.accumulators, plan.k_splits);
   sage_gemm_tc_kernel<<<blocks, kGemmThreads, plan.shared_bytes, stream>>>(p, map);
   return cudaGetLastError();

@@ -131,12 +131,16 @@ GemmPlan plan_gemm_tc(int rows, int n, int k, int sm_count, bool allow_split = t
 cudaError_t configure_gemm_tc();
 // xq: activations already in quantised channel order, 16-byte aligned.  `status` is a
 // device-visible word that receives SAGEB200_ERR_TIMEOUT if a bounded wait runs out.
+// `sph_mins` non-null selects the SPHQuant format: `codes` = row-major 16-bit codes, `radii` = the
+// per-(row, group) high radius words, `grid` = FP16 scales, `sph_mins` = FP16 minimums, `book` =
+// the entry-major 64 x 8 codebook, entries = 64.
 // `partial` (plan.partial_bytes) and `counters` (eight zeroed words per output tile, left zero) are
 // needed when plan.k_splits > 1.
 cudaError_t launch_gemm_tc(const __half *xq, const uint32_t *codes, const uint32_t *radii,
                            const uint32_t *grid, const uint32_t *book, __half *y, int *status,
                            int rows, int n, int k, int entries, const GemmPlan &plan,
-                           cudaStream_t stream, float *partial = nullptr, unsigned *counters = nullptr);
+                           cudaStream_t stream, float *partial = nullptr, unsigned *counters = nullptr,
+                           const __half *sph_mins = nullptr);
 
 // Causal attention over prompt rows on the tensor cores (prefill_attention.cu); rows are
 // [sequence][token], row (s, t) at cache position positions[s] + t.  head_dim is 128.

@@ -19,6 +19,7 @@
 
 #include "../../include/sage_b200.h"
 #include "sage_common.cuh"
+#include "sage_kernels.h"
 
 namespace sageb200 {
 namespace {
@@ -242,6 +243,24 @@ int sageb200_sph_linear(const void *x, const void *codes, const void *extra, con
     return SAGEB200_ERR_ALIGNMENT;
   cudaStream_t s = static_cast<cudaStream_t>(stream);
   const int sm_count = sph_sm_count();
+  if (rows >= 33 && (reinterpret_cast<uintptr_t>(x) & 15) == 0 && (reinterpret_cast<uintptr_t>(y) & 1) == 0) {
+    // Prompt-sized calls: the tcgen05 GEMM with this format's decode (no permutation, so the
+    // activations are used where they lie; no scratch in this interface, so K is not split).
+    int *status_word = nullptr;
+    int device_sms = 0;
+    const int state = acquire_device(&status_word, &device_sms);
+    if (state != SAGEB200_OK) return state;
+    const GemmPlan plan = plan_gemm_tc(rows, n, k, device_sms, false);
+    if (launch_gemm_tc(static_cast<const __half *>(x), static_cast<const uint32_t *>(codes),
+                       static_cast<const uint32_t *>(extra), static_cast<const uint32_t *>(scales),
+                       static_cast<const uint32_t *>(book), static_cast<__half *>(y), status_word, rows, n, k, 64,
+                       plan, s, nullptr, nullptr, static_cast<const __half *>(mins)) != cudaSuccess) {
+      cudaGetLastError();
+      return SAGEB200_ERR_CUDA;
+    }
+    count_launches(1);
+    return SAGEB200_OK;
+  }
   // activation rows per pass: as many as fit shared memory, at most eight
   int per_pass = 8;
   while (per_pass > 1 && kSphBookBytes + static_cast<size_t>(per_pass) * (k / 64) * kSphChunkHalves * 2 > 192 * 1024)

@@ -38,6 +38,32 @@ def test_matches_oracle(shape, n):
     assert relative_error(actual, expected) < (GATE if actual.numel() >= 64 else REFERENCE_GATE)
 
 
+@pytest.mark.parametrize("rows,k,n", [(33, 256, 129), (257, 1024, 640), (300, 2560, 333), (512, 2560, 4096),
+                                      (513, 1280, 2560), (2048, 4096, 2560)])
+def test_prompt_rows_on_the_tensor_core_path_match_oracle(rows, k, n):
+    """33 rows and more run the tcgen05 GEMM with this format's decode (row-major codes, n not
+    padded to 16, several token blocks and both accumulators): same gate as the decode kernel,
+    and every output row equal to the 8-row decode path's to FP16 rounding."""
+    cpu_packed = synthetic_sphquant(k, n, seed=rows)
+    layer = SPHQuantLinear({key: tensor.cuda() for key, tensor in cpu_packed.items()})
+    x = torch.randn(rows, k, generator=torch.Generator().manual_seed(rows + 1), dtype=torch.float16)
+    with torch.inference_mode():
+        actual = layer(x.cuda())
+        few = layer(x[:8].cuda())  # the decode kernel on the first rows
+    expected = sph_oracle.linear_fp32(x, cpu_packed)
+    assert relative_error(actual, expected) < GATE
+    row_error = (actual[:8].float() - few.float()).norm() / few.float().norm()
+    assert float(row_error) < 2e-3
+    # one-hot rows: a token routed to the wrong block or accumulator shows as a wrong row
+    hot = torch.zeros(rows, k, dtype=torch.float16)
+    columns = torch.arange(rows) % k
+    hot[torch.arange(rows), columns] = 1.0
+    with torch.inference_mode():
+        picked = layer(hot.cuda()).float().cpu()
+    dense = torch.from_numpy(np.asarray(sph_oracle.decode_fp16(cpu_packed), dtype=np.float32))  # [n, k]
+    assert torch.equal(picked, dense[:, columns].T.contiguous())  # x = 1 picks a weight: bit-exact
+
+
 def test_zero_and_constant_grid():
     packed = synthetic_sphquant(128, 9)
     packed["radius_scales"].zero_()
