@@ -545,6 +545,35 @@ def test_gemm_one_hot_rows_across_token_blocks(rows):
     assert torch.allclose(got.float(), want, rtol=2e-3, atol=1e-6)
 
 
+def test_gemm_maximum_rows_and_split_k_repeatability():
+    """65535 activation rows (the interface's maximum: 256 token blocks) checked at the first, a
+    middle and the last rows through the one-hot property, one more row refused; and a shape whose
+    K is split over several CTAs per tile gives the same bits on every call (the splits are added in
+    index order whoever arrives last)."""
+    k, n = 256, 129
+    cpu = synthetic_sage(k, n, seed=5, permuted=True)
+    layer = SAGELinear(to_cuda(cpu), n)
+    weight = torch.from_numpy(c_oracle.decode_fp16(cpu, n)).cuda().float()
+    rows = 65535
+    x = torch.zeros(rows, k, dtype=torch.float16, device="cuda")
+    columns = torch.arange(rows, device="cuda") * 5 % k
+    x[torch.arange(rows, device="cuda"), columns] = 1.0
+    got = layer(x)
+    for block in (slice(0, 300), slice(32700, 33000), slice(rows - 300, rows)):
+        assert torch.allclose(got[block].float(), weight[:, columns[block]].T, rtol=2e-3, atol=1e-6)
+    with pytest.raises(RuntimeError):
+        layer(torch.zeros(rows + 1, k, dtype=torch.float16, device="cuda"))
+    del x, got
+    # K split: 9728 -> 2560 at 512 rows runs six CTAs per output tile
+    cpu = synthetic_sage(9728, 2560, seed=6, permuted=True)
+    layer = SAGELinear(to_cuda(cpu), 2560)
+    x = torch.randn(512, 9728, generator=torch.Generator().manual_seed(7), dtype=torch.float16).cuda()
+    first = layer(x).clone()
+    for _ in range(5):
+        assert torch.equal(layer(x), first)
+    assert_output(first, expected_output(x, cpu, 2560))
+
+
 # ---------------------------------------------------------------- traceability (torch.compile)
 
 
