@@ -42,6 +42,13 @@ int sageb200_set_pdl(int enabled);
  */
 int sageb200_debug_trace(void *device_buffer);
 
+/*
+ * The tcgen05 GEMM (rows >= 33) runs as clusters of two CTAs with cta_group::2 MMAs whenever the
+ * shape allows it; 0 switches that off for A/B timing (process-wide, not thread-safe).
+ * No counterpart in the reference.
+ */
+int sageb200_debug_gemm_pairs(int enabled);
+
 #ifdef __cplusplus
 }
 #endif

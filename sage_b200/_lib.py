@@ -51,6 +51,7 @@ EXPORTED_DEBUG = (
     "sageb200_debug_plan",
     "sageb200_set_pdl",
     "sageb200_debug_trace",
+    "sageb200_debug_gemm_pairs",
 )
 
 
@@ -237,6 +238,8 @@ def load() -> ctypes.CDLL:
     lib.sageb200_set_pdl.argtypes = [ci]
     lib.sageb200_debug_trace.restype = ci
     lib.sageb200_debug_trace.argtypes = [vp]
+    lib.sageb200_debug_gemm_pairs.restype = ci
+    lib.sageb200_debug_gemm_pairs.argtypes = [ci]
     lib.sageb200_launch_count.restype = ctypes.c_ulonglong
     lib.sageb200_launch_count.argtypes = []
     lib.sageb200_glue_launch_count.restype = ctypes.c_ulonglong

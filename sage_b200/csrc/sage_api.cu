@@ -725,6 +725,11 @@ int sageb200_clear_status(void) {
   return SAGEB200_OK;
 }
 
+int sageb200_debug_gemm_pairs(int enabled) {
+  g_gemm_pairs = enabled ? 1 : 0;
+  return SAGEB200_OK;
+}
+
 int sageb200_set_pdl(int enabled) {
   g_sageb200_pdl = enabled & 3;
   return SAGEB200_OK;

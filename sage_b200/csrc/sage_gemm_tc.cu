@@ -190,6 +190,48 @@ __device__ __forceinline__ void umma_commit(uint32_t bar) {
                : "memory");
 }
 
+// ---- the same for a PAIR of CTAs (cta_group::2): one MMA covers 256 output rows (128 per CTA), each
+//      CTA supplies its own weight tile and HALF of the activation tile, so an SM reads half the B
+//      operand from its shared memory.  Barrier addresses with bit 24 cleared name the even CTA of
+//      the pair in the cluster's shared window.
+constexpr uint32_t kPeerBitMask = 0xFEFFFFFFu;
+__device__ __forceinline__ void tma_load_2d_pair(uint32_t dst, const CUtensorMap *map, int x, int y,
+                                                 uint32_t leader_bar) {
+  asm volatile(
+      "cp.async.bulk.tensor.2d.cta_group::2.shared::cluster.global.mbarrier::complete_tx::bytes"
+      " [%0], [%1, {%2, %3}], [%4];" ::"r"(dst),
+      "l"(reinterpret_cast<uint64_t>(map)), "r"(x), "r"(y), "r"(leader_bar & kPeerBitMask)
+      : "memory");
+}
+__device__ __forceinline__ void umma_f16_pair(uint32_t tmem_d, uint64_t a_desc, uint64_t b_desc,
+                                              uint32_t idesc, uint32_t accumulate) {
+  const uint32_t zero = 0;
+  asm volatile(
+      "{\n .reg .pred p;\n setp.ne.b32 p, %4, 0;\n"
+      " tcgen05.mma.cta_group::2.kind::f16 [%0], %1, %2, %3, {%5, %5, %5, %5, %5, %5, %5, %5}, p;\n}" ::"r"(tmem_d),
+      "l"(a_desc), "l"(b_desc), "r"(idesc), "r"(accumulate), "r"(zero)
+      : "memory");
+}
+// arrives on the barrier at this shared-memory offset in BOTH CTAs of the pair
+__device__ __forceinline__ void umma_commit_pair(uint32_t bar) {
+  const unsigned short both = 3;
+  asm volatile(
+      "tcgen05.commit.cta_group::2.mbarrier::arrive::one.shared::cluster.multicast::cluster.b64 [%0], %1;" ::"r"(bar),
+      "h"(both)
+      : "memory");
+}
+__device__ __forceinline__ void mbarrier_arrive_leader(uint32_t bar) {
+  asm volatile("mbarrier.arrive.shared::cluster.b64 _, [%0];" ::"r"(bar & kPeerBitMask) : "memory");
+}
+__device__ __forceinline__ void cluster_sync_all() {
+  asm volatile("barrier.cluster.arrive.release.aligned;\n barrier.cluster.wait.acquire.aligned;" ::: "memory");
+}
+__device__ __forceinline__ uint32_t cluster_cta_rank() {
+  uint32_t rank;
+  asm volatile("mov.u32 %0, %%cluster_ctarank;" : "=r"(rank));
+  return rank;
+}
+
 __device__ __forceinline__ void tmem_load_16(uint32_t taddr, uint32_t (&r)[16]) {
   asm volatile(
       "tcgen05.ld.sync.aligned.32x32b.x16.b32 "
@@ -207,6 +249,14 @@ __device__ __forceinline__ void tmem_load_wait() {
 
 // Dynamic shared memory, 1024-byte aligned by hand:
 //   [A stages: stages x 16 KiB][B stages: stages x TN*128][codebook 4 KiB][barriers]
+// kPair: the grid is launched in clusters of two CTAs along x (two neighbouring row blocks) that
+// run cta_group::2 MMAs.  Both CTAs decode their own 128 rows and load their own half of every
+// activation tile; the even CTA (the leader) issues the MMAs and owns the "stage full" barriers:
+// its own decode warps arrive there, its TMA thread announces both CTAs' bytes, the odd CTA's
+// loads complete on it remotely, and the odd CTA's otherwise idle MMA warp forwards ONE arrival
+// per stage once its own decode warps are done.  Stage-free and accumulator-ready arrivals are
+// multicast to both CTAs by tcgen05.commit.
+template <bool kPair>
 __global__ void __launch_bounds__(kGemmThreads, 1)
     sage_gemm_tc_kernel(const GemmParams p, const __grid_constant__ CUtensorMap x_map) {
   extern __shared__ unsigned char raw_shared[];
@@ -219,7 +269,10 @@ __global__ void __launch_bounds__(kGemmThreads, 1)
   unsigned char *aligned = raw_shared + (base - raw);
   const int tn = p.tokens_per_cta;
   const int accumulators = p.accumulators;
-  const int b_tile_bytes = tn * kStageK * 2;          // one token block's activations of a stage
+  const int tile_tokens = kPair ? tn / 2 : tn;        // tokens of one accumulator this CTA loads
+  const int b_tile_bytes = tile_tokens * kStageK * 2; // one token block's activations of a stage (this CTA's part)
+  const uint32_t pair_rank = kPair ? cluster_cta_rank() : 0u;
+  const bool leader = pair_rank == 0;
   const int b_stage_bytes = accumulators * b_tile_bytes;
   const uint32_t a_base = base;
   const uint32_t b_base = a_base + p.stages * kAStageBytes;
@@ -244,18 +297,28 @@ __global__ void __launch_bounds__(kGemmThreads, 1)
   if (tid == 0) {
     abort_flag = 0;
     for (int s = 0; s < p.stages; ++s) {
-      mbarrier_init(full_bar(s), kDecodeThreads + 1);
+      // full: this CTA's decode threads; + the TMA thread's announcement (and, for a leader, the
+      // odd CTA's forwarded arrival)
+      mbarrier_init(full_bar(s), kDecodeThreads + (kPair ? (leader ? 2 : 0) : 1));
       mbarrier_init(empty_bar(s), 1);
     }
     mbarrier_init(accum_bar, 1);
     asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
   }
   if (warp == kTmaWarp) {
-    asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(
-                     smem_address(&tmem_base_holder)),
-                 "r"(static_cast<uint32_t>(p.tmem_columns))
-                 : "memory");
-    asm volatile("tcgen05.relinquish_alloc_permit.cta_group::1.sync.aligned;" ::: "memory");
+    if constexpr (kPair) {  // (both CTAs, the same warp, the same holder address)
+      asm volatile("tcgen05.alloc.cta_group::2.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(
+                       smem_address(&tmem_base_holder)),
+                   "r"(static_cast<uint32_t>(p.tmem_columns))
+                   : "memory");
+      asm volatile("tcgen05.relinquish_alloc_permit.cta_group::2.sync.aligned;" ::: "memory");
+    } else {
+      asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(
+                       smem_address(&tmem_base_holder)),
+                   "r"(static_cast<uint32_t>(p.tmem_columns))
+                   : "memory");
+      asm volatile("tcgen05.relinquish_alloc_permit.cta_group::1.sync.aligned;" ::: "memory");
+    }
   }
   // codebook, interleaved: entry e = 16 bytes (dims 0..7)
   for (int e = tid; e < p.entries; e += kGemmThreads) {
@@ -275,6 +338,7 @@ __global__ void __launch_bounds__(kGemmThreads, 1)
   }
   tcgen05_fence_before();
   __syncthreads();
+  if constexpr (kPair) cluster_sync_all();  // (no remote arrival before the other CTA's barriers exist)
   tcgen05_fence_after();
   const uint32_t tmem_base = tmem_base_holder;
   volatile int *abort_ptr = &abort_flag;
@@ -361,10 +425,12 @@ __global__ void __launch_bounds__(kGemmThreads, 1)
                               (((radius_word >> (2 * vector)) & 3u) << (8 - p.dbits));
           const float radius = fmaf(static_cast<float>(rc), step, minimum);
           const uint32_t planes[4] = {dir.x, dir.y, dir.z, dir.w};
+          const uint32_t signs = code & 0xffu;
 #pragma unroll
           for (int q = 0; q < 4; ++q) {
-            uint32_t bits = planes[q];
-            bits ^= (((code >> (2 * q)) & 1u) << 15) | (((code >> (2 * q + 1)) & 1u) << 31);
+            // sign bits 2q and 2q+1 land on bits 15 and 31 of one product (one multiply and one
+            // three-input logic operation per pair of weights; the other product bits are masked)
+            uint32_t bits = planes[q] ^ ((signs * ((1u + (1u << 15)) << (15 - 2 * q))) & 0x80008000u);
             const float2 d = __half22float2(*reinterpret_cast<const __half2 *>(&bits));
             const __half2 v = __floats2half2_rn(d.x * radius, d.y * radius);
             out[q] = *reinterpret_cast<const uint32_t *>(&v);
@@ -561,10 +627,19 @@ __global__ void __launch_bounds__(kGemmThreads, 1)
         alive = bounded_wait(empty_bar(s), phase ^ 1u, abort_ptr, p.status);
         if (!alive) break;
         waited += GEMM_CLOCK() - t0;
-        mbarrier_arrive_expect_tx(full_bar(s), static_cast<uint32_t>(b_stage_bytes));
-        for (int a = 0; a < accumulators; ++a)  // (a block past the last token reads the fill value)
-          tma_load_2d(b_base + s * b_stage_bytes + a * b_tile_bytes, &x_map, (stage_first + ks) * kStageK,
-                      (token_block + a) * tn, full_bar(s));
+        if constexpr (kPair) {
+          // the leader announces both CTAs' bytes; each CTA loads its half of every token block and
+          // the copies complete on the leader's barrier
+          if (leader) mbarrier_arrive_expect_tx(full_bar(s), static_cast<uint32_t>(2 * b_stage_bytes));
+          for (int a = 0; a < accumulators; ++a)
+            tma_load_2d_pair(b_base + s * b_stage_bytes + a * b_tile_bytes, &x_map, (stage_first + ks) * kStageK,
+                             (token_block + a) * tn + static_cast<int>(pair_rank) * tile_tokens, full_bar(s));
+        } else {
+          mbarrier_arrive_expect_tx(full_bar(s), static_cast<uint32_t>(b_stage_bytes));
+          for (int a = 0; a < accumulators; ++a)  // (a block past the last token reads the fill value)
+            tma_load_2d(b_base + s * b_stage_bytes + a * b_tile_bytes, &x_map, (stage_first + ks) * kStageK,
+                        (token_block + a) * tn, full_bar(s));
+        }
       }
 #ifdef SAGEB200_TRACE
       if (p.trace) p.trace[(static_cast<size_t>(blockIdx.y) * gridDim.x + blockIdx.x) * 16 + 7] = waited;
@@ -572,8 +647,20 @@ __global__ void __launch_bounds__(kGemmThreads, 1)
     }
   } else {
     // ---------------- MMA issue
-    if (lane == 0) {
-      const uint32_t idesc = instruction_descriptor(kTileRows, tn);
+    if (kPair && !leader) {
+      // ---------------- odd CTA of a pair: forward "my decode warps have filled the stage"
+      if (lane == 0) {
+        bool alive = true;
+        for (int ks = 0; ks < stages_k && alive; ++ks) {
+          const int s = ks % p.stages;
+          const uint32_t phase = static_cast<uint32_t>(ks / p.stages) & 1u;
+          alive = bounded_wait(full_bar(s), phase, abort_ptr, p.status);
+          if (!alive) break;
+          mbarrier_arrive_leader(full_bar(s));
+        }
+      }
+    } else if (lane == 0) {
+      const uint32_t idesc = instruction_descriptor(kPair ? 2 * kTileRows : kTileRows, tn);
       bool alive = true;
       long long waited = 0;
       [[maybe_unused]] const long long mma_begin = GEMM_CLOCK();
@@ -591,12 +678,19 @@ __global__ void __launch_bounds__(kGemmThreads, 1)
 #pragma unroll
           for (int j = 0; j < kStageK / 16; ++j) {
             // advancing 16 channels = 32 bytes = 2 units of the descriptor's address field
-            umma_f16(tmem_base + a * 256, a_desc + 2 * j, b_desc + 2 * j, idesc, (ks > 0 || j > 0) ? 1u : 0u);
+            if constexpr (kPair)
+              umma_f16_pair(tmem_base + a * 256, a_desc + 2 * j, b_desc + 2 * j, idesc, (ks > 0 || j > 0) ? 1u : 0u);
+            else
+              umma_f16(tmem_base + a * 256, a_desc + 2 * j, b_desc + 2 * j, idesc, (ks > 0 || j > 0) ? 1u : 0u);
           }
         }
-        umma_commit(empty_bar(s));
+        if constexpr (kPair) umma_commit_pair(empty_bar(s));
+        else umma_commit(empty_bar(s));
       }
-      if (alive) umma_commit(accum_bar);
+      if (alive) {
+        if constexpr (kPair) umma_commit_pair(accum_bar);
+        else umma_commit(accum_bar);
+      }
 #ifdef SAGEB200_TRACE
       if (p.trace) {
         long long *record = p.trace + (static_cast<size_t>(blockIdx.y) * gridDim.x + blockIdx.x) * 16;
@@ -612,15 +706,23 @@ __global__ void __launch_bounds__(kGemmThreads, 1)
   // abort, wait (bounded) for each stage's barrier once more.
   tcgen05_fence_before();
   __syncthreads();
+  // (a pair leaves together: the leader's MMAs read the other CTA's shared memory, and both CTAs'
+  //  barriers receive remote arrivals until the last commit)
+  if constexpr (kPair) cluster_sync_all();
   if (warp == kTmaWarp) {
     if (abort_flag && lane == 0) {
       const unsigned long long begin = global_timer();
       while (global_timer() - begin < 2000000ull) __nanosleep(1000);  // 2 ms grace for copies in flight
     }
     __syncwarp();
-    asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(tmem_base),
-                 "r"(static_cast<uint32_t>(p.tmem_columns))
-                 : "memory");
+    if constexpr (kPair)
+      asm volatile("tcgen05.dealloc.cta_group::2.sync.aligned.b32 %0, %1;" ::"r"(tmem_base),
+                   "r"(static_cast<uint32_t>(p.tmem_columns))
+                   : "memory");
+    else
+      asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(tmem_base),
+                   "r"(static_cast<uint32_t>(p.tmem_columns))
+                   : "memory");
   }
 }
 
@@ -709,6 +811,8 @@ cudaError_t launch_gather(const __half *x, const int32_t *perm, __half *xq, int 
   return cudaGetLastError();
 }
 
+int g_gemm_pairs = 1;  // debug switch (sageb200_debug_gemm_pairs): 0 = never pair CTAs
+
 GemmPlan plan_gemm_tc(int rows, int n, int k, int sm_count, bool allow_split) {
   GemmPlan plan{};
   plan.row_blocks = (n + kTileRows - 1) / kTileRows;
@@ -764,13 +868,16 @@ GemmPlan plan_gemm_tc(int rows, int n, int k, int sm_count, bool allow_split) {
   plan.tokens_per_cta = tn;
   plan.token_blocks = (rows + tn - 1) / tn;
   plan.accumulators = best_accumulators;
+  // Pairs of CTAs (cta_group::2) whenever the row blocks pair up and each CTA's half of a token
+  // block is a whole number of 16-token MMA columns: half the B operand per SM.
+  plan.pair = g_gemm_pairs && (plan.row_blocks % 2 == 0) && (tn % 32 == 0) ? 1 : 0;
   plan.k_splits = best_splits;
   plan.groups_per_split = (groups + best_splits - 1) / best_splits;
   {
     const size_t tiles = static_cast<size_t>(plan.row_blocks) * ((plan.token_blocks + plan.accumulators - 1) / plan.accumulators);
     plan.partial_bytes = best_splits > 1 ? tiles * best_splits * plan.accumulators * tn * kTileRows * sizeof(float) : 0;
   }
-  const int stage_bytes = kAStageBytes + plan.accumulators * tn * kStageK * 2;
+  const int stage_bytes = kAStageBytes + plan.accumulators * (plan.pair ? tn / 2 : tn) * kStageK * 2;
   int stages = (kGemmSharedLimit - kBookBytes - 2 * 1024) / stage_bytes;
   if (stages > kMaxStages) stages = kMaxStages;
   if (stages < 2) stages = 2;
@@ -783,7 +890,10 @@ GemmPlan plan_gemm_tc(int rows, int n, int k, int sm_count, bool allow_split) {
 }
 
 cudaError_t configure_gemm_tc() {
-  return cudaFuncSetAttribute(sage_gemm_tc_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize,
+  cudaError_t error = cudaFuncSetAttribute(sage_gemm_tc_kernel<false>, cudaFuncAttributeMaxDynamicSharedMemorySize,
+                                           kGemmSharedLimit);
+  if (error != cudaSuccess) return error;
+  return cudaFuncSetAttribute(sage_gemm_tc_kernel<true>, cudaFuncAttributeMaxDynamicSharedMemorySize,
                               kGemmSharedLimit);
 }
 
@@ -798,7 +908,7 @@ cudaError_t launch_gemm_tc(const __half *xq, const uint32_t *codes, const uint32
   CUtensorMap map;
   const cuuint64_t dims[2] = {static_cast<cuuint64_t>(k), static_cast<cuuint64_t>(rows)};
   const cuuint64_t strides[1] = {static_cast<cuuint64_t>(k) * 2};
-  const cuuint32_t box[2] = {kStageK, static_cast<cuuint32_t>(plan.tokens_per_cta)};
+  const cuuint32_t box[2] = {kStageK, static_cast<cuuint32_t>(plan.pair ? plan.tokens_per_cta / 2 : plan.tokens_per_cta)};
   const cuuint32_t element_strides[2] = {1, 1};
   const CUresult encoded = encode(
       &map, CU_TENSOR_MAP_DATA_TYPE_FLOAT16, 2, const_cast<__half *>(xq), dims, strides, box,
@@ -831,7 +941,22 @@ cudaError_t launch_gemm_tc(const __half *xq, const uint32_t *codes, const uint32
   p.format = sph_mins ? 1 : 0;
   p.mins = sph_mins;
   const dim3 blocks(plan.row_blocks, (plan.token_blocks + plan.accumulators - 1) / plan.accumulators, plan.k_splits);
-  sage_gemm_tc_kernel<<<blocks, kGemmThreads, plan.shared_bytes, stream>>>(p, map);
+  if (plan.pair) {
+    cudaLaunchConfig_t config = {};
+    config.gridDim = blocks;
+    config.blockDim = dim3(kGemmThreads);
+    config.dynamicSmemBytes = plan.shared_bytes;
+    config.stream = stream;
+    cudaLaunchAttribute attribute[1];
+    attribute[0].id = cudaLaunchAttributeClusterDimension;
+    attribute[0].val.clusterDim.x = 2;
+    attribute[0].val.clusterDim.y = 1;
+    attribute[0].val.clusterDim.z = 1;
+    config.attrs = attribute;
+    config.numAttrs = 1;
+    return cudaLaunchKernelEx(&config, sage_gemm_tc_kernel<true>, p, map);
+  }
+  sage_gemm_tc_kernel<false><<<blocks, kGemmThreads, plan.shared_bytes, stream>>>(p, map);
   return cudaGetLastError();
 }
 

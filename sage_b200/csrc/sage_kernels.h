@@ -120,6 +120,7 @@ struct GemmPlan {
   int stages;
   int tmem_columns;
   int accumulators;     // token blocks per CTA (1 or 2) sharing each decoded weight stage
+  int pair;             // 1: clusters of two CTAs (two row blocks) run cta_group::2 MMAs
   int k_splits;         // CTAs that share one output tile along K (1: none)
   int groups_per_split; // 128-channel groups per K split
   size_t partial_bytes; // FP32 scratch of the split tiles (0 without a split)
@@ -128,6 +129,7 @@ struct GemmPlan {
 
 // `allow_split`: false plans without a K split (no scratch available).
 GemmPlan plan_gemm_tc(int rows, int n, int k, int sm_count, bool allow_split = true);
+extern int g_gemm_pairs;  // debug switch: 0 = never pair CTAs (sageb200_debug_gemm_pairs)
 cudaError_t configure_gemm_tc();
 // xq: activations already in quantised channel order, 16-byte aligned.  `status` is a
 // device-visible word that receives SAGEB200_ERR_TIMEOUT if a bounded wait runs out.
