@@ -2,7 +2,7 @@
 
     python bench.py [--gpus N] [--steps K] [--warmup W] [--impl ours|reference]
                     [--workload decode_model|decode_linears|prompt|tp32b|ep30b|report|linear:K:N:M|sph:K:N:M|
-                               gemm_roles:K:N:M|mega_phases] [--prompt P]
+                               gemm_roles:K:N:M|skinny_phases:K:N:M|mega_phases] [--prompt P]
 
 A step is one decoded token of the full Qwen3-4B architecture at batch 1 (synthetic seeded
 packed weights, ABS split cycling 6/7/8 direction bits per matrix; `decode_linears` times the
@@ -1113,6 +1113,62 @@ def run_gemm_roles(args) -> None:
           flush=True)
 
 
+def run_skinny_phases(args) -> None:
+    """`--workload skinny_phases:K:N:M` (profiling build only): one decode-kernel call (M <= 16 rows)
+    with the SM clock read at each phase boundary by every CTA; prints the median duration of each
+    phase over the CTAs in microseconds (at the device's SM clock) and the call's CUDA-event time."""
+    import ctypes
+
+    import torch
+
+    from sage_b200 import SAGELinear, _lib
+    from sage_b200.synthetic import synthetic_sage_device
+
+    _, k, n, rows = args.workload.split(":")
+    k, n, rows = int(k), int(n), int(rows)
+    lib = _lib.load()
+    device = torch.device("cuda", 0)
+    layer = SAGELinear(synthetic_sage_device(k, n, 3, device, direction_bits=8), n)
+    x = torch.randn(rows, k, device=device, dtype=torch.float16)
+    for _ in range(3):
+        layer(x)
+    torch.cuda.synchronize(device)
+    trace = torch.zeros(64 * 512 * 16, dtype=torch.int64, device=device)
+    lib.sageb200_debug_trace(ctypes.c_void_p(trace.data_ptr()))
+    layer(x)
+    torch.cuda.synchronize(device)
+    lib.sageb200_debug_trace(None)
+    records = trace.view(64, 512, 16)[0].cpu()
+    records = records[records[:, 0] != 0].double()
+    if records.numel() == 0:
+        print(json.dumps({"workload": args.workload, "error": "no phase clocks: load the profiling build "
+                          "(python -m sage_b200.build --trace; SAGEB200_LIBRARY=sage_b200/libsage_b200_trace.so)"}))
+        return
+    mhz = torch.cuda.clock_rate() if hasattr(torch.cuda, "clock_rate") else 1965
+    order = [0, 11, 12, 1, 14, 2, 3, 4, 5, 6, 7, 8, 9, 10]
+    names = ["partition_arithmetic", "barrier_init_and_bulk_copies", "tile_tables", "wait_for_previous_kernel",
+             "activation_staging", "barrier", "permutation_gather", "wait_for_weight_bytes", "main_loop", "barrier_2",
+             "combine_warps_and_store", "shared_tile_fix_up", "counter_reset"]
+    phases = {}
+    for i, name in enumerate(names):
+        live = (records[:, order[i + 1]] != 0) & (records[:, order[i]] != 0)  # (phases a launch kind skips stay 0)
+        if not bool(live.any()):
+            continue
+        delta = records[live][:, order[i + 1]] - records[live][:, order[i]]
+        phases[name] = {"median_us": float(delta.median()) / mhz, "max_us": float(delta.max()) / mhz}
+    last = torch.where(records[:, 10] != 0, records[:, 10], records[:, 8])
+    total = last - records[:, 0]
+    start, stop = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    start.record()
+    for _ in range(20):
+        layer(x)
+    stop.record()
+    torch.cuda.synchronize(device)
+    print(json.dumps({"workload": args.workload, "ctas": int(records.shape[0]), "sm_mhz": mhz, "phases": phases,
+                      "cta_total_us": {"median": float(total.median()) / mhz, "max": float(total.max()) / mhz},
+                      "eager_call_us_warm_weights": start.elapsed_time(stop) * 1000.0 / 20}), flush=True)
+
+
 def run_mega_phases(args) -> None:
     """`--workload mega_phases` (profiling build only): one Qwen3-4B token through the one-kernel
     decode step with %globaltimer stamps at every phase boundary of every CTA; prints the median
@@ -1195,6 +1251,8 @@ def main() -> None:
         run_single_linear(args)
     elif args.workload.startswith("gemm_roles:"):
         run_gemm_roles(args)
+    elif args.workload.startswith("skinny_phases:"):
+        run_skinny_phases(args)
     elif args.workload == "mega_phases":
         run_mega_phases(args)
     elif args.workload == "prompt":
