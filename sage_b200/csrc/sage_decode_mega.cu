@@ -818,7 +818,6 @@ __global__ void __launch_bounds__(kThreads, 1)
       const int chunks = max(1, min(chunks_max, (context + 31) / 32));
       const int kv = cta / chunks, split = cta - kv * chunks;
       float *partial_out = H.attn_partial;
-#ifndef MEGA_EXPERIMENT_NO_ATTENTION
       if (cta < chunks * H.kv_heads) {
         __half *q_shared = reinterpret_cast<__half *>(work);                      // [group][128]
         __half *new_k = q_shared + kMaxGroup * 128, *new_v = new_k + 128;
@@ -990,7 +989,6 @@ __global__ void __launch_bounds__(kThreads, 1)
           __stcg(out + 2 + dim, value);
         }
       }
-#endif
       MEGA_STAMP();  // partial attention done
       if (!grid_sync()) {
         bail_out();
