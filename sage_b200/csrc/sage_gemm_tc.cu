@@ -284,6 +284,11 @@ __global__ void __launch_bounds__(kGemmThreads, 1)
   auto empty_bar = [&](int s) { return bar_base + 8u * (kMaxStages + s); };
   const uint32_t accum_bar = bar_base + 8u * (2 * kMaxStages);
 
+  // Programmatic dependent launch: the next kernel of the stream may be scheduled at once; this
+  // kernel's set-up, and its decode warps' first stages (packed weights and codebook: data no
+  // kernel writes), run while the previous kernel (the gather pre-pass) still works.  Only the
+  // activation loads and every global write wait for the previous kernel.
+  pdl_launch_dependents();
   const int tid = threadIdx.x;
   const int warp = tid >> 5;
   const int lane = tid & 31;
@@ -462,6 +467,7 @@ __global__ void __launch_bounds__(kGemmThreads, 1)
     const long long epilogue_begin = GEMM_CLOCK();
 #endif
     // ---------------- epilogue: TMEM -> registers -> FP16 global
+    pdl_wait();  // (long since satisfied: the MMAs needed the activations; required before global writes)
     if (alive) alive = bounded_wait(accum_bar, 0, abort_ptr, p.status);
     alive = __all_sync(0xffffffffu, alive);  // tcgen05.ld is warp-collective
     tcgen05_fence_after();
@@ -618,6 +624,7 @@ __global__ void __launch_bounds__(kGemmThreads, 1)
   } else if (warp == kTmaWarp) {
     // ---------------- activation tile loads
     if (lane == 0) {
+      pdl_wait();  // the activations are the previous kernel's output
       bool alive = true;
       long long waited = 0;
       for (int ks = 0; ks < stages_k && alive; ++ks) {
@@ -736,6 +743,8 @@ __global__ void __launch_bounds__(kGatherThreads) sage_gather_kernel(const __hal
                                                                      __half *__restrict__ xq, int rows, int k) {
   extern __shared__ __align__(16) unsigned char gather_shared[];
   __half *row_shared = reinterpret_cast<__half *>(gather_shared);
+  pdl_launch_dependents();  // (the GEMM behind this kernel sets up and decodes its first stages meanwhile)
+  pdl_wait();               // the activations are the previous kernel's output
   const int vectors = k >> 3;
   const bool perm_wide = (reinterpret_cast<uintptr_t>(perm) & 15) == 0;
   for (int m = blockIdx.x; m < rows; m += gridDim.x) {
@@ -807,8 +816,8 @@ cudaError_t launch_gather(const __half *x, const int32_t *perm, __half *xq, int 
   const int cap = (sm_count > 0 ? sm_count : 148) * 8;
   if (blocks > cap) blocks = cap;
   if (blocks < 1) blocks = 1;
-  sage_gather_kernel<<<static_cast<unsigned>(blocks), kGatherThreads, shared, stream>>>(x, perm, xq, rows, k);
-  return cudaGetLastError();
+  return launch_dependent<1>(sage_gather_kernel, dim3(static_cast<unsigned>(blocks)), dim3(kGatherThreads), shared,
+                             stream, x, perm, xq, rows, k);
 }
 
 int g_gemm_pairs = 1;  // debug switch (sageb200_debug_gemm_pairs): 0 = never pair CTAs
@@ -941,23 +950,29 @@ cudaError_t launch_gemm_tc(const __half *xq, const uint32_t *codes, const uint32
   p.format = sph_mins ? 1 : 0;
   p.mins = sph_mins;
   const dim3 blocks(plan.row_blocks, (plan.token_blocks + plan.accumulators - 1) / plan.accumulators, plan.k_splits);
-  if (plan.pair) {
-    cudaLaunchConfig_t config = {};
-    config.gridDim = blocks;
-    config.blockDim = dim3(kGemmThreads);
-    config.dynamicSmemBytes = plan.shared_bytes;
-    config.stream = stream;
-    cudaLaunchAttribute attribute[1];
-    attribute[0].id = cudaLaunchAttributeClusterDimension;
-    attribute[0].val.clusterDim.x = 2;
-    attribute[0].val.clusterDim.y = 1;
-    attribute[0].val.clusterDim.z = 1;
-    config.attrs = attribute;
-    config.numAttrs = 1;
-    return cudaLaunchKernelEx(&config, sage_gemm_tc_kernel<true>, p, map);
+  cudaLaunchConfig_t config = {};
+  config.gridDim = blocks;
+  config.blockDim = dim3(kGemmThreads);
+  config.dynamicSmemBytes = plan.shared_bytes;
+  config.stream = stream;
+  cudaLaunchAttribute attribute[2];
+  unsigned attributes = 0;
+  if (g_sageb200_pdl & 1) {  // (the same switch as the decode kernels: sageb200_set_pdl)
+    attribute[attributes].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+    attribute[attributes].val.programmaticStreamSerializationAllowed = 1;
+    ++attributes;
   }
-  sage_gemm_tc_kernel<false><<<blocks, kGemmThreads, plan.shared_bytes, stream>>>(p, map);
-  return cudaGetLastError();
+  if (plan.pair) {
+    attribute[attributes].id = cudaLaunchAttributeClusterDimension;
+    attribute[attributes].val.clusterDim.x = 2;
+    attribute[attributes].val.clusterDim.y = 1;
+    attribute[attributes].val.clusterDim.z = 1;
+    ++attributes;
+  }
+  config.attrs = attribute;
+  config.numAttrs = attributes;
+  return plan.pair ? cudaLaunchKernelEx(&config, sage_gemm_tc_kernel<true>, p, map)
+                   : cudaLaunchKernelEx(&config, sage_gemm_tc_kernel<false>, p, map);
 }
 
 }  // namespace sageb200
