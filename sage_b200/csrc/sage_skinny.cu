@@ -772,7 +772,10 @@ SkinnyPlan plan_skinny(int rows, int n, int k, int entries, int sm_count, const 
   if (rows > 1) {
     long long share_units = (static_cast<long long>(tiles) * groups + resident - 1) / resident;
     if (share_units > unit_cap) share_units = unit_cap;
-    const size_t tables = static_cast<size_t>(plan.warps) * 4 * plan.column_blocks * 512;
+    // (the warps' partial-sum tables: a warp touches its units / groups + 2 tiles at most)
+    const long long warp_units = (share_units + plan.warps - 1) / plan.warps;
+    const size_t tables = static_cast<size_t>(plan.warps) * static_cast<size_t>(warp_units / groups + 2) *
+                          plan.column_blocks * 512;
     const size_t taken = static_cast<size_t>(share_units) * kUnitBytes + tables + 4096;
     x_budget = taken + 40 * 1024 < static_cast<size_t>(kMaxDynamicShared) ? kMaxDynamicShared - taken : 40 * 1024;
   }
