@@ -212,6 +212,10 @@ struct StageParams {
 __global__ void __launch_bounds__(256) stage_rows_kernel(const __grid_constant__ StageParams params) {
   extern __shared__ __half row_shared[];
   __shared__ float sums[8];
+  // (the decode kernel behind this launch sets up and prefetches its weights meanwhile; this
+  //  launch itself was scheduled while its producer still ran)
+  pdl_launch_dependents();
+  pdl_wait();
   StageJob job = params.job[blockIdx.y];
   const int row = blockIdx.x;
   if (row >= job.rows) return;
@@ -222,21 +226,67 @@ __global__ void __launch_bounds__(256) stage_rows_kernel(const __grid_constant__
     if (job.perm) job.perm += static_cast<long long>(expert) * k;
   }
   const size_t offset = static_cast<size_t>(row) * k;
+  // eight values per thread and load where the inputs are 16-byte aligned (k is a multiple of 128)
+  auto wide = [&](const __half *p) { return p == nullptr || (reinterpret_cast<uintptr_t>(p + offset) & 15) == 0; };
+  const int vectors = k >> 3;
   if (params.kind == 0) {
-    for (int i = threadIdx.x; i < k; i += 256) row_shared[i] = job.x[offset + i];
+    if (wide(job.x)) {
+      for (int v = threadIdx.x; v < vectors; v += 256)
+        reinterpret_cast<uint4 *>(row_shared)[v] = reinterpret_cast<const uint4 *>(job.x + offset)[v];
+    } else {
+      for (int i = threadIdx.x; i < k; i += 256) row_shared[i] = job.x[offset + i];
+    }
   } else if (params.kind == 2) {
-    for (int i = threadIdx.x; i < k; i += 256) {
-      const float g = __half2float(params.a[offset + i]);
-      row_shared[i] = __hmul(__float2half_rn(silu_fast(g)), params.b[offset + i]);
+    if (wide(params.a) && wide(params.b)) {
+      for (int v = threadIdx.x; v < vectors; v += 256) {
+        const uint4 g4 = reinterpret_cast<const uint4 *>(params.a + offset)[v];
+        const uint4 u4 = reinterpret_cast<const uint4 *>(params.b + offset)[v];
+        const __half2 *g2 = reinterpret_cast<const __half2 *>(&g4), *u2 = reinterpret_cast<const __half2 *>(&u4);
+        uint4 out;
+        __half2 *o2 = reinterpret_cast<__half2 *>(&out);
+#pragma unroll
+        for (int q = 0; q < 4; ++q) {
+          const float2 g = __half22float2(g2[q]);
+          o2[q] = __hmul2(__halves2half2(__float2half_rn(silu_fast(g.x)), __float2half_rn(silu_fast(g.y))), u2[q]);
+        }
+        reinterpret_cast<uint4 *>(row_shared)[v] = out;
+      }
+    } else {
+      for (int i = threadIdx.x; i < k; i += 256) {
+        const float g = __half2float(params.a[offset + i]);
+        row_shared[i] = __hmul(__float2half_rn(silu_fast(g)), params.b[offset + i]);
+      }
     }
   } else {
     float square = 0.0f;
-    for (int i = threadIdx.x; i < k; i += 256) {
-      const __half v = params.b ? __hadd(params.a[offset + i], params.b[offset + i]) : params.a[offset + i];
-      row_shared[i] = v;
-      if (blockIdx.y == 0) params.residual_out[offset + i] = v;
-      const float f = __half2float(v);
-      square = fmaf(f, f, square);
+    if (wide(params.a) && wide(params.b) && wide(params.residual_out)) {
+      for (int v = threadIdx.x; v < vectors; v += 256) {
+        uint4 sum4 = reinterpret_cast<const uint4 *>(params.a + offset)[v];
+        __half2 *s2 = reinterpret_cast<__half2 *>(&sum4);
+        if (params.b) {
+          const uint4 b4 = reinterpret_cast<const uint4 *>(params.b + offset)[v];
+          const __half2 *b2 = reinterpret_cast<const __half2 *>(&b4);
+#pragma unroll
+          for (int q = 0; q < 4; ++q) s2[q] = __hadd2(s2[q], b2[q]);
+        }
+        reinterpret_cast<uint4 *>(row_shared)[v] = sum4;
+        if (blockIdx.y == 0) reinterpret_cast<uint4 *>(params.residual_out + offset)[v] = sum4;
+      }
+      __syncthreads();
+      // the squares in the scalar loop's order (element i in thread i % 256), out of shared memory:
+      // the norm is then bit-identical whichever way the row was loaded
+      for (int i = threadIdx.x; i < k; i += 256) {
+        const float f = __half2float(row_shared[i]);
+        square = fmaf(f, f, square);
+      }
+    } else {
+      for (int i = threadIdx.x; i < k; i += 256) {
+        const __half v = params.b ? __hadd(params.a[offset + i], params.b[offset + i]) : params.a[offset + i];
+        row_shared[i] = v;
+        if (blockIdx.y == 0) params.residual_out[offset + i] = v;
+        const float f = __half2float(v);
+        square = fmaf(f, f, square);
+      }
     }
     for (int o = 16; o; o >>= 1) square += __shfl_xor_sync(0xffffffffu, square, o);
     if ((threadIdx.x & 31) == 0) sums[threadIdx.x >> 5] = square;
@@ -412,7 +462,7 @@ int run_skinny(const sageb200_problem *problems, int count, void *workspace,
   if (live == 0) return SAGEB200_OK;
   if (jobs > 0) {
     const size_t shared = static_cast<size_t>(stage_k) * sizeof(__half);  // (limit raised per device at set-up)
-    stage_rows_kernel<<<dim3(stage_rows, jobs), 256, shared, stream>>>(staging);
+    launch_dependent<1>(stage_rows_kernel, dim3(stage_rows, jobs), dim3(256), shared, stream, staging);
     if (cudaGetLastError() != cudaSuccess) return SAGEB200_ERR_CUDA;
     g_launches.fetch_add(1, std::memory_order_relaxed);
   }
