@@ -567,6 +567,55 @@ __global__ void swiglu_kernel(const __half *__restrict__ gate, const __half *__r
   }
 }
 
+// ---- logits of 2..16 sequences on the tensor cores.  mma.sync.m16n8k16 with 16 vocabulary rows as
+// the A operand and 8 sequences as the B operand per column block.  K runs in blocks of 32 in a
+// permuted order (slot 2t+e of step j <-> channel 8t+4j+e, slot 2t+8+e <-> channel 8t+4j+2+e), the
+// same for both operands, so that a lane's fragments of both steps are ONE 16-byte load: 16
+// contiguous bytes of a head row from global memory, and 16 bytes of a sequence's row from the
+// blocked shared copy xs[k block][column block][8 sequences][32 channels] (a quarter warp reads 128
+// contiguous bytes: no bank conflicts).  HBM-bound on the head matrix for any row count.
+__device__ __forceinline__ int head_x_index(int m, int i, int column_blocks) {
+  return (((i >> 5) * column_blocks + (m >> 3)) * 8 + (m & 7)) * 32 + (i & 31);
+}
+__device__ __forceinline__ void head_mma(float (&d)[4], uint32_t a0, uint32_t a1, uint32_t a2, uint32_t a3,
+                                         uint32_t b0, uint32_t b1) {
+  asm volatile(
+      "mma.sync.aligned.m16n8k16.row.col.f32.f16.f16.f32 {%0,%1,%2,%3}, {%4,%5,%6,%7}, {%8,%9}, {%0,%1,%2,%3};"
+      : "+f"(d[0]), "+f"(d[1]), "+f"(d[2]), "+f"(d[3])
+      : "r"(a0), "r"(a1), "r"(a2), "r"(a3), "r"(b0), "r"(b1));
+}
+// acc[nb][e]: vocabulary row v0 + g + 8 * (e >> 1), sequence nb * 8 + 2 * t + (e & 1)
+template <int kColumnBlocks>
+__device__ __forceinline__ void head_rows_mma(const __half *__restrict__ head, const __half *xs, int v0, int vocab,
+                                              int hidden, int lane, float (&acc)[kColumnBlocks][4]) {
+  const int g = lane >> 2, t = lane & 3;
+#pragma unroll
+  for (int nb = 0; nb < kColumnBlocks; ++nb) acc[nb][0] = acc[nb][1] = acc[nb][2] = acc[nb][3] = 0.0f;
+  const uint4 *row0 = reinterpret_cast<const uint4 *>(head + static_cast<size_t>(min(v0 + g, vocab - 1)) * hidden) + t;
+  const uint4 *row1 = reinterpret_cast<const uint4 *>(head + static_cast<size_t>(min(v0 + g + 8, vocab - 1)) * hidden) + t;
+  const uint4 *x_lane = reinterpret_cast<const uint4 *>(xs) + g * 4 + t;  // + (kb * blocks + nb) * 32
+  const int blocks = hidden >> 5;
+  for (int first = 0; first < blocks; first += 4) {  // eight 16-byte loads in flight per lane
+    uint4 w0[4], w1[4];
+#pragma unroll
+    for (int u = 0; u < 4; ++u)
+      if (first + u < blocks) {
+        w0[u] = sageb200::ldg_stream_u4(row0 + (first + u) * 4);
+        w1[u] = sageb200::ldg_stream_u4(row1 + (first + u) * 4);
+      }
+#pragma unroll
+    for (int u = 0; u < 4; ++u) {
+      if (first + u >= blocks) break;
+#pragma unroll
+      for (int nb = 0; nb < kColumnBlocks; ++nb) {
+        const uint4 xb = x_lane[((first + u) * kColumnBlocks + nb) * 32];
+        head_mma(acc[nb], w0[u].x, w1[u].x, w0[u].y, w1[u].y, xb.x, xb.y);
+        head_mma(acc[nb], w0[u].z, w1[u].z, w0[u].w, w1[u].w, xb.z, xb.w);
+      }
+    }
+  }
+}
+
 // logits[m][v] = dot(head[v][:], x[m][:]) in FP32, rounded to FP16.  One warp per vocabulary
 // row; the (up to 16) activation rows sit in shared memory.  HBM-bound on the head matrix.
 constexpr int kHeadWarps = 8;
@@ -580,10 +629,38 @@ __global__ void __launch_bounds__(kHeadWarps * 32)
   sageb200::pdl_wait();
 
   extern __shared__ __half x_shared[];
+  const int lane = threadIdx.x & 31;
+  if (rows > 1 && (hidden & 31) == 0) {
+    // several sequences: blocked copy of the rows, then 16 vocabulary rows per warp and step
+    const int column_blocks = rows > 8 ? 2 : 1;
+    for (int e = threadIdx.x; e < column_blocks * 8 * hidden; e += blockDim.x) {
+      const int m = e / hidden, i = e - m * hidden;
+      x_shared[head_x_index(m, i, column_blocks)] = m < rows ? x[static_cast<size_t>(m) * hidden + i] : __float2half_rn(0.0f);
+    }
+    __syncthreads();
+    const int g = lane >> 2, t = lane & 3;
+    for (int v0 = (blockIdx.x * kHeadWarps + (threadIdx.x >> 5)) * 16; v0 < vocab; v0 += gridDim.x * kHeadWarps * 16) {
+      float acc[2][4];
+      if (column_blocks == 2) {
+        head_rows_mma<2>(head, x_shared, v0, vocab, hidden, lane, acc);
+      } else {
+        float one[1][4];
+        head_rows_mma<1>(head, x_shared, v0, vocab, hidden, lane, one);
+#pragma unroll
+        for (int e = 0; e < 4; ++e) acc[0][e] = one[0][e];
+      }
+      for (int nb = 0; nb < column_blocks; ++nb)
+#pragma unroll
+        for (int e = 0; e < 4; ++e) {
+          const int v = v0 + g + 8 * (e >> 1), m = nb * 8 + 2 * t + (e & 1);
+          if (v < vocab && m < rows) logits[static_cast<size_t>(m) * vocab + v] = __float2half_rn(acc[nb][e]);
+        }
+    }
+    return;
+  }
   for (int i = threadIdx.x; i < rows * hidden / 8; i += blockDim.x)
     reinterpret_cast<uint4 *>(x_shared)[i] = reinterpret_cast<const uint4 *>(x)[i];
   __syncthreads();
-  const int lane = threadIdx.x & 31;
   const int pieces = hidden / 8;
   for (int v = blockIdx.x * kHeadWarps + (threadIdx.x >> 5); v < vocab; v += gridDim.x * kHeadWarps) {
     const uint4 *row = reinterpret_cast<const uint4 *>(head + static_cast<size_t>(v) * hidden);
@@ -625,7 +702,8 @@ __device__ __forceinline__ bool better(float value, int index, float than_value,
   return value > than_value || (value == than_value && index < than_index);
 }
 
-// kRows bounds `rows` (1, 4 or 16) so that the per-row sums stay in registers.
+// kRows bounds `rows` (1, 8 or 16): one sequence runs the FP32 dot products below, several run the
+// tensor-core path with one (8) or two (16) column blocks.
 template <int kRows>
 __global__ void __launch_bounds__(kHeadWarps * 32)
     lm_head_step_kernel(const __half *__restrict__ head, const __half *__restrict__ residual,
@@ -643,29 +721,84 @@ __global__ void __launch_bounds__(kHeadWarps * 32)
   __shared__ int best_index[kHeadWarps][16];
   __shared__ int is_last;
   static_assert(kHeadWarps * 32 == kNormThreads, "the norm must sum in add_rmsnorm_kernel's order");
+  // several sequences: the rows live in the blocked layout of head_rows_mma (same arithmetic and
+  // summation order of the norm either way)
+  constexpr int kColumnBlocks = kRows > 8 ? 2 : 1;
+  const bool blocked = kRows > 1 && (hidden & 31) == 0;
+  auto at = [&](int m, int i) { return blocked ? head_x_index(m, i, kColumnBlocks) : m * hidden + i; };
+  if (blocked)
+    for (int e = rows * hidden + threadIdx.x; e < kColumnBlocks * 8 * hidden; e += kNormThreads)
+      x_shared[head_x_index(e / hidden, e % hidden, kColumnBlocks)] = __float2half_rn(0.0f);  // unused sequences
   for (int m = 0; m < rows; ++m) {
     const __half *r = residual + static_cast<size_t>(m) * hidden;
     const __half *d = delta ? delta + static_cast<size_t>(m) * hidden : nullptr;
-    __half *row_shared = x_shared + static_cast<size_t>(m) * hidden;
     float square = 0.0f;
     for (int i = threadIdx.x; i < hidden; i += kNormThreads) {
       __half v = r[i];
       if (d) v = __hadd(v, d[i]);
-      row_shared[i] = v;
+      x_shared[at(m, i)] = v;
       const float f = __half2float(v);
       square += f * f;
     }
     const float total = block_sum(square, scratch);
     const float scale = rsqrtf(total / hidden + eps);
     for (int i = threadIdx.x; i < hidden; i += kNormThreads) {
-      const __half normed = __float2half_rn(__half2float(row_shared[i]) * scale);
+      const __half normed = __float2half_rn(__half2float(x_shared[at(m, i)]) * scale);
       const __half value = __hmul(norm_weight[i], normed);
-      row_shared[i] = value;
+      x_shared[at(m, i)] = value;
       if (blockIdx.x == 0) x_out[static_cast<size_t>(m) * hidden + i] = value;
     }
   }
   __syncthreads();
   const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
+  if (blocked) {
+    // ---- tensor-core path: 16 vocabulary rows per warp and step, best (value, index) per sequence
+    const int g = lane >> 2, t = lane & 3;
+    float slot_value[kColumnBlocks * 2];
+    int slot_index[kColumnBlocks * 2];
+#pragma unroll
+    for (int q = 0; q < kColumnBlocks * 2; ++q) {
+      slot_value[q] = -INFINITY;
+      slot_index[q] = 0x7fffffff;
+    }
+    for (int v0 = (blockIdx.x * kHeadWarps + warp) * 16; v0 < vocab; v0 += gridDim.x * kHeadWarps * 16) {
+      float acc[kColumnBlocks][4];
+      head_rows_mma<kColumnBlocks>(head, x_shared, v0, vocab, hidden, lane, acc);
+#pragma unroll
+      for (int nb = 0; nb < kColumnBlocks; ++nb)
+#pragma unroll
+        for (int e = 0; e < 4; ++e) {  // (e = 0, 1: row v0 + g; e = 2, 3: row v0 + g + 8: increasing index per slot)
+          const int v = v0 + g + 8 * (e >> 1), m = nb * 8 + 2 * t + (e & 1);
+          if (v < vocab && m < rows) {
+            const __half rounded = __float2half_rn(acc[nb][e]);
+            logits[static_cast<size_t>(m) * vocab + v] = rounded;
+            const float f = __half2float(rounded);
+            const int q = nb * 2 + (e & 1);
+            if (better(f, v, slot_value[q], slot_index[q])) {
+              slot_value[q] = f;
+              slot_index[q] = v;
+            }
+          }
+        }
+    }
+    // the eight lanes that share t hold the same sequences: best over them, then lanes 0..3 publish
+#pragma unroll
+    for (int q = 0; q < kColumnBlocks * 2; ++q) {
+      for (int o = 4; o < 32; o <<= 1) {
+        const float other = __shfl_xor_sync(0xffffffffu, slot_value[q], o);
+        const int other_index = __shfl_xor_sync(0xffffffffu, slot_index[q], o);
+        if (better(other, other_index, slot_value[q], slot_index[q])) {
+          slot_value[q] = other;
+          slot_index[q] = other_index;
+        }
+      }
+      const int m = (q >> 1) * 8 + 2 * t + (q & 1);
+      if (g == 0 && m < rows) {
+        best_value[warp][m] = slot_value[q];
+        best_index[warp][m] = slot_index[q];
+      }
+    }
+  } else {
   const int pieces = hidden / 8;
   float top_value[kRows];
   int top_index[kRows];
@@ -724,6 +857,7 @@ __global__ void __launch_bounds__(kHeadWarps * 32)
       best_value[warp][m] = top_value[m];
       best_index[warp][m] = top_index[m];
     }
+  }  // (scalar path)
   __syncthreads();
   if (threadIdx.x < rows) {
     const int m = threadIdx.x;
@@ -1186,7 +1320,8 @@ int sageb200_glue_swiglu(const void *gate, const void *up, void *act, long long 
 int sageb200_glue_lm_head(const void *head, const void *x, void *logits, int rows, int vocab,
                           int hidden, int sm_count, void *stream) {
   if (rows > 16 || hidden % 8) return -1;
-  const size_t shared = static_cast<size_t>(rows) * hidden * sizeof(__half);
+  const int staged_rows = rows > 1 && hidden % 32 == 0 ? (rows > 8 ? 16 : 8) : rows;  // (blocked copy: whole column blocks)
+  const size_t shared = static_cast<size_t>(staged_rows) * hidden * sizeof(__half);
   static bool configured = false;
   if (shared > 48 * 1024 && !configured) {
     if (cudaFuncSetAttribute(lm_head_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, 200 * 1024) !=
@@ -1211,9 +1346,10 @@ int sageb200_glue_lm_head_step(const void *head, const void *residual, const voi
                                void *positions, void *log, void *step, void *scratch, int rows, int vocab,
                                int hidden, float eps, int log_stride, int sm_count, void *stream) {
   if (rows < 1 || rows > 16 || hidden % 8 || vocab < 1) return -1;
-  const size_t shared = static_cast<size_t>(rows) * hidden * sizeof(__half);
+  const int staged_rows = rows > 1 && hidden % 32 == 0 ? (rows > 8 ? 16 : 8) : rows;  // (blocked copy: whole column blocks)
+  const size_t shared = static_cast<size_t>(staged_rows) * hidden * sizeof(__half);
   if (shared > 200 * 1024) return -1;
-  auto kernel = rows == 1 ? lm_head_step_kernel<1> : rows <= 4 ? lm_head_step_kernel<4> : lm_head_step_kernel<16>;
+  auto kernel = rows == 1 ? lm_head_step_kernel<1> : rows <= 8 ? lm_head_step_kernel<8> : lm_head_step_kernel<16>;
   if (shared > 40 * 1024 &&
       cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, 200 * 1024) != cudaSuccess)
     return -5;

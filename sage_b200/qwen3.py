@@ -275,7 +275,11 @@ class PackedQwen3:
         self.attn_scratch = torch.zeros(scratch // 4, dtype=torch.float32, device=self.device)
         # single-launch attention and step tail (`fuse_glue`); the tail's arrival counter starts at zero
         self.fuse_glue = True
-        self.step_splits = 8  # CTAs per cluster in the single-launch attention
+        # CTAs per cluster in the single-launch attention (each takes a share of the context): as many
+        # as keep (sequences x kv heads x splits) within about one wave of SMs, 8 at most
+        self.step_splits = 8
+        while self.step_splits > 1 and batch * self.kv_heads * self.step_splits > self.sm_count:
+            self.step_splits //= 2
         scratch = self.lib.sageb200_glue_lm_head_step_scratch_bytes(batch, self.sm_count)
         self.head_scratch = torch.zeros(scratch // 4, dtype=torch.float32, device=self.device)
         if c.experts:
