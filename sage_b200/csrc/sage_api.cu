@@ -579,8 +579,19 @@ size_t sageb200_workspace_bytes(int rows, int n, int k) {
   return bytes ? kCounterRegionBytes + bytes : 0;
 }
 
+namespace {
+// (`limit`: the public entry points take SAGEB200_MAX_GROUPED problems, the expert entry points fill
+//  launches up to the kernel's own capacity)
+size_t grouped_workspace_bytes(const sageb200_problem *problems_host, int count, int limit);
+}  // namespace
+
 size_t sageb200_grouped_workspace_bytes(const sageb200_problem *problems_host, int count) {
-  if (!problems_host || count <= 0 || count > SAGEB200_MAX_GROUPED) return 0;
+  return grouped_workspace_bytes(problems_host, count, SAGEB200_MAX_GROUPED);
+}
+
+namespace {
+size_t grouped_workspace_bytes(const sageb200_problem *problems_host, int count, int limit) {
+  if (!problems_host || count <= 0 || count > limit) return 0;
   for (int i = 0; i < count; ++i)
     if (check_shape(problems_host[i].rows, problems_host[i].n, problems_host[i].k, problems_host[i].entries) ||
         problems_host[i].rows > 16)
@@ -592,6 +603,7 @@ size_t sageb200_grouped_workspace_bytes(const sageb200_problem *problems_host, i
   const size_t bytes = grouped_scratch_bytes(problems_host, count, *device);
   return bytes ? kCounterRegionBytes + bytes : 0;
 }
+}  // namespace
 
 int sageb200_linear_grouped(const sageb200_problem *problems_host, int count, void *workspace,
                             size_t workspace_bytes, void *stream) {
@@ -864,16 +876,16 @@ int sageb200_linear_grouped_fused(const sageb200_problem *problems_host, int cou
 size_t sageb200_experts_workspace_bytes(const sageb200_expert_stack *stacks_host, int stack_count,
                                         int slots) {
   if (!stacks_host || stack_count <= 0 || slots <= 0) return 0;
-  sageb200_problem problems[SAGEB200_MAX_GROUPED];
+  sageb200_problem problems[kMaxGrouped];
   int count = 0;
-  for (int s = 0; s < slots && count < SAGEB200_MAX_GROUPED; ++s)
-    for (int t = 0; t < stack_count && count < SAGEB200_MAX_GROUPED; ++t) {
+  for (int s = 0; s < slots && count < kMaxGrouped; ++s)
+    for (int t = 0; t < stack_count && count < kMaxGrouped; ++t) {
       problems[count] = sageb200_problem{nullptr, nullptr, nullptr, nullptr, nullptr, stacks_host[t].perm,
                                          nullptr, 1, stacks_host[t].n, stacks_host[t].k,
                                          stacks_host[t].entries};
       ++count;
     }
-  return sageb200_grouped_workspace_bytes(problems, count);
+  return grouped_workspace_bytes(problems, count, kMaxGrouped);
 }
 
 int sageb200_experts(const void *x, long long x_slot_stride, const sageb200_expert_stack *stacks_host,
@@ -887,10 +899,10 @@ int sageb200_experts(const void *x, long long x_slot_stride, const sageb200_expe
   int status = device_state(&device);
   if (status) return status;
   cudaStream_t s = static_cast<cudaStream_t>(stream);
-  const int slots_per_launch = SAGEB200_MAX_GROUPED / stack_count;
+  const int slots_per_launch = kMaxGrouped / stack_count;
   for (int begin = 0; begin < slots; begin += slots_per_launch) {
-    sageb200_problem problems[SAGEB200_MAX_GROUPED];
-    ExpertRef refs[SAGEB200_MAX_GROUPED];
+    sageb200_problem problems[kMaxGrouped];
+    ExpertRef refs[kMaxGrouped];
     int count = 0;
     for (int slot = begin; slot < slots && slot < begin + slots_per_launch; ++slot)
       for (int t = 0; t < stack_count; ++t) {
@@ -916,14 +928,14 @@ int sageb200_experts(const void *x, long long x_slot_stride, const sageb200_expe
 
 size_t sageb200_expert_blocks_workspace_bytes(const sageb200_expert_stack *stacks_host, int stack_count, int rows) {
   if (!stacks_host || stack_count <= 0 || stack_count > SAGEB200_MAX_GROUPED || rows <= 0 || rows > 16) return 0;
-  sageb200_problem problems[SAGEB200_MAX_GROUPED];
-  const int per_launch = SAGEB200_MAX_GROUPED / stack_count;
+  sageb200_problem problems[kMaxGrouped];
+  const int per_launch = kMaxGrouped / stack_count;
   int count = 0;
   for (int b = 0; b < per_launch; ++b)
     for (int t = 0; t < stack_count; ++t)
       problems[count++] = sageb200_problem{nullptr, nullptr, nullptr, nullptr, nullptr, stacks_host[t].perm, nullptr,
                                            rows, stacks_host[t].n, stacks_host[t].k, stacks_host[t].entries};
-  return sageb200_grouped_workspace_bytes(problems, count);
+  return grouped_workspace_bytes(problems, count, kMaxGrouped);
 }
 
 int sageb200_expert_blocks(const void *x, const sageb200_expert_stack *stacks_host, void *const *ys_host,
@@ -937,10 +949,10 @@ int sageb200_expert_blocks(const void *x, const sageb200_expert_stack *stacks_ho
   int status = device_state(&device);
   if (status) return status;
   cudaStream_t s = static_cast<cudaStream_t>(stream);
-  const int per_launch = SAGEB200_MAX_GROUPED / stack_count;
+  const int per_launch = kMaxGrouped / stack_count;
   for (int begin = 0; begin < blocks; begin += per_launch) {
-    sageb200_problem problems[SAGEB200_MAX_GROUPED];
-    ExpertRef refs[SAGEB200_MAX_GROUPED];
+    sageb200_problem problems[kMaxGrouped];
+    ExpertRef refs[kMaxGrouped];
     int count = 0;
     for (int block = begin; block < blocks && block < begin + per_launch; ++block)
       for (int t = 0; t < stack_count; ++t) {

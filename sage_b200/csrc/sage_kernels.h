@@ -8,7 +8,10 @@
 
 namespace sageb200 {
 
-constexpr int kMaxGrouped = 16;
+// Problems one launch can hold.  The public grouped entry points take SAGEB200_MAX_GROUPED (16);
+// the expert entry points fill launches up to this internal limit (the kernel's parameter block
+// grows with it: ~12 KB, within the 32 KB the driver accepts).
+constexpr int kMaxGrouped = 64;
 
 // One packed linear as the skinny kernel sees it.
 struct SkinnyProblem {
