@@ -125,6 +125,26 @@ int sageb200_glue_moe_route(void *residual, const void *delta, const void *norm_
                             void *x, void *ids, void *weights, int rows, int hidden, int experts, int top_k,
                             float eps, void *stream);
 
+/*
+ * The sorted expert compute behind an all-to-all dispatch (or any batch beyond one grouped launch):
+ * `received` (token, expert) slots with global expert ids int32 `ids` (-1 = none) are packed into
+ * blocks of rows_per_block rows, every block belonging to one of this rank's experts
+ * [first_expert, first_expert + local_experts), the slots of an expert in received order.
+ *   dispatch_plan  target[j] = row of the block buffer slot j takes (blocks * rows_per_block = "dump"
+ *                  for a slot without a local expert), block_experts[b] = global expert id of block b
+ *                  (-1 unused); one launch; received <= 4096, local_experts <= 256; `blocks` at least
+ *                  local_experts + ceil(received / rows_per_block) places every slot
+ *   dispatch_rows  rows[target[j]][:] = x[j / source_div][:]       (source_div = top_k when x holds tokens)
+ *   combine_rows   back[j][:] = outputs[target[j]][:], zeros for a slot without a row
+ * No counterpart in the reference (no packed mixture of experts there).
+ */
+int sageb200_glue_dispatch_plan(const void *ids, void *target, void *block_experts, int received,
+                                int first_expert, int local_experts, int rows_per_block, int blocks, void *stream);
+int sageb200_glue_dispatch_rows(const void *x, const void *target, void *rows, int received, int hidden, int dump,
+                                int source_div, void *stream);
+int sageb200_glue_combine_rows(const void *outputs, const void *target, void *back, int received, int hidden,
+                               int dump, void *stream);
+
 /* out[rows][hidden] = fp16(sum_s weights[row][s] * slot_outputs[row*top_k + s][:]) (FP32 sum). */
 int sageb200_glue_moe_mix(const void *slot_outputs, const void *weights, void *out, int rows, int hidden,
                           int top_k, void *stream);

@@ -69,6 +69,9 @@ EXPORTED_DECODE = (
     "sageb200_glue_lm_head_step",
     "sageb200_glue_moe_route",
     "sageb200_glue_moe_mix",
+    "sageb200_glue_dispatch_plan",
+    "sageb200_glue_dispatch_rows",
+    "sageb200_glue_combine_rows",
     "sageb200_glue_swiglu",
     "sageb200_glue_lm_head",
     "sageb200_glue_argmax_advance",
@@ -262,6 +265,12 @@ def load() -> ctypes.CDLL:
     lib.sageb200_glue_prefill_attention.argtypes = [vp] * 5 + [ci] * 6 + [vp]
     lib.sageb200_glue_moe_route.restype = ci
     lib.sageb200_glue_moe_route.argtypes = [vp] * 7 + [ci] * 4 + [ctypes.c_float, vp]
+    lib.sageb200_glue_dispatch_plan.restype = ci
+    lib.sageb200_glue_dispatch_plan.argtypes = [vp, vp, vp, ci, ci, ci, ci, ci, vp]
+    lib.sageb200_glue_dispatch_rows.restype = ci
+    lib.sageb200_glue_dispatch_rows.argtypes = [vp, vp, vp, ci, ci, ci, ci, vp]
+    lib.sageb200_glue_combine_rows.restype = ci
+    lib.sageb200_glue_combine_rows.argtypes = [vp, vp, vp, ci, ci, ci, vp]
     lib.sageb200_glue_moe_mix.restype = ci
     lib.sageb200_glue_moe_mix.argtypes = [vp] * 3 + [ci] * 3 + [vp]
     lib.sageb200_glue_lm_head_step_scratch_bytes.restype = sz

@@ -1050,6 +1050,116 @@ __global__ void moe_mix_kernel(const __half *__restrict__ slot_outputs, const fl
   out[static_cast<size_t>(m) * hidden + i] = __float2half_rn(sum);
 }
 
+
+// ---- sorted expert compute: where each received (token, expert) slot goes.
+// One CTA.  Slot j (received order) of local expert e takes position p = number of earlier slots of
+// e (a stable counting sort: warp votes, per-warp counts, a scan over the warps per expert);
+// expert e owns ceil(count_e / rows_per_block) consecutive blocks starting at the running sum;
+// target[j] = row of the block buffer, block_experts[b] = the global expert id of block b (-1 for a
+// block nobody uses).  Slots without a local expert go to the row `dump` = blocks * rows_per_block.
+constexpr int kPlanThreads = 1024;
+constexpr int kPlanMaxExperts = 256;
+constexpr int kPlanMaxChunks = 4;  // received <= 4096
+
+__global__ void __launch_bounds__(kPlanThreads)
+    dispatch_plan_kernel(const int *__restrict__ ids, int *__restrict__ target, int *__restrict__ block_experts,
+                         int received, int first_expert, int local_experts, int rows_per_block, int blocks) {
+  sageb200::pdl_launch_dependents();
+  sageb200::pdl_wait();
+  __shared__ int running[kPlanMaxExperts];          // slots of the expert seen so far, then its first block
+  __shared__ unsigned short warp_counts[32][kPlanMaxExperts];
+  const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
+  for (int e = tid; e < kPlanMaxExperts; e += kPlanThreads) running[e] = 0;
+  for (int b = tid; b < blocks; b += kPlanThreads) block_experts[b] = -1;
+  int expert[kPlanMaxChunks], position[kPlanMaxChunks];
+#pragma unroll
+  for (int c = 0; c < kPlanMaxChunks; ++c) {
+    const int j = c * kPlanThreads + tid;
+    int e = -1;
+    if (j < received) {
+      const int id = ids[j];
+      if (id >= first_expert && id < first_expert + local_experts) e = id - first_expert;
+    }
+    expert[c] = e;
+    position[c] = 0;
+    if (c * kPlanThreads >= received) continue;  // (uniform: the whole chunk is past the end)
+    for (int i = tid; i < 32 * kPlanMaxExperts; i += kPlanThreads) (&warp_counts[0][0])[i] = 0;
+    __syncthreads();
+    const unsigned same = __match_any_sync(0xffffffffu, e >= 0 ? e : -1 - lane);
+    const int rank = __popc(same & ((1u << lane) - 1u));
+    if (e >= 0 && rank == 0) warp_counts[warp][e] = static_cast<unsigned short>(__popc(same));
+    __syncthreads();
+    if (tid < local_experts) {  // exclusive scan over the warps, continuing the expert's running count
+      int sum = running[tid];
+      for (int w = 0; w < 32; ++w) {
+        const int count = warp_counts[w][tid];
+        warp_counts[w][tid] = static_cast<unsigned short>(sum);
+        sum += count;
+      }
+      running[tid] = sum;
+    }
+    __syncthreads();
+    if (e >= 0) position[c] = warp_counts[warp][e] + rank;
+    __syncthreads();
+  }
+  // counts -> first block of each expert (one thread: at most 256 experts)
+  if (tid == 0) {
+    int next = 0;
+    for (int e = 0; e < local_experts; ++e) {
+      const int count = running[e];
+      running[e] = next;
+      next += (count + rows_per_block - 1) / rows_per_block;
+    }
+  }
+  __syncthreads();
+  const int dump = blocks * rows_per_block;
+#pragma unroll
+  for (int c = 0; c < kPlanMaxChunks; ++c) {
+    const int j = c * kPlanThreads + tid;
+    if (j >= received) continue;
+    const int e = expert[c];
+    if (e < 0) {
+      target[j] = dump;
+      continue;
+    }
+    const int block = running[e] + position[c] / rows_per_block;
+    const int within = position[c] % rows_per_block;
+    target[j] = block < blocks ? block * rows_per_block + within : dump;
+    if (within == 0 && block < blocks) block_experts[block] = e + first_expert;
+  }
+}
+
+// rows[target[j]][:] = x[j / source_div][:] for every slot that has a row (16-byte copies)
+__global__ void __launch_bounds__(128)
+    dispatch_rows_kernel(const __half *__restrict__ x, const int *__restrict__ target, __half *__restrict__ rows,
+                         int hidden, int dump, int source_div) {
+  sageb200::pdl_launch_dependents();
+  sageb200::pdl_wait();
+  const int j = blockIdx.x;
+  const int row = target[j];
+  if (row >= dump) return;
+  const uint4 *source = reinterpret_cast<const uint4 *>(x + static_cast<size_t>(j / source_div) * hidden);
+  uint4 *destination = reinterpret_cast<uint4 *>(rows + static_cast<size_t>(row) * hidden);
+  for (int v = threadIdx.x; v < (hidden >> 3); v += 128) destination[v] = source[v];
+}
+
+// back[j][:] = outputs[target[j]][:], zeros for a slot without a row
+__global__ void __launch_bounds__(128)
+    combine_rows_kernel(const __half *__restrict__ outputs, const int *__restrict__ target, __half *__restrict__ back,
+                        int hidden, int dump) {
+  sageb200::pdl_launch_dependents();
+  sageb200::pdl_wait();
+  const int j = blockIdx.x;
+  const int row = target[j];
+  uint4 *destination = reinterpret_cast<uint4 *>(back + static_cast<size_t>(j) * hidden);
+  if (row >= dump) {
+    for (int v = threadIdx.x; v < (hidden >> 3); v += 128) destination[v] = make_uint4(0, 0, 0, 0);
+    return;
+  }
+  const uint4 *source = reinterpret_cast<const uint4 *>(outputs + static_cast<size_t>(row) * hidden);
+  for (int v = threadIdx.x; v < (hidden >> 3); v += 128) destination[v] = source[v];
+}
+
 // next[m] = argmax(logits[m]), lowest index on ties; also appends the token to the output
 // log at column step[0] and advances the sequence's position.
 __global__ void __launch_bounds__(1024)
@@ -1386,6 +1496,40 @@ int sageb200_glue_moe_mix(const void *slot_outputs, const void *weights, void *o
   sageb200::launch_dependent<2>(moe_mix_kernel, dim3((hidden + 255) / 256, rows), dim3(256), 0,
                                 static_cast<cudaStream_t>(stream), static_cast<const __half *>(slot_outputs),
                                 static_cast<const float *>(weights), static_cast<__half *>(out), hidden, top_k);
+  return launch_status();
+}
+
+int sageb200_glue_dispatch_plan(const void *ids, void *target, void *block_experts, int received,
+                                int first_expert, int local_experts, int rows_per_block, int blocks, void *stream) {
+  if (!ids || !target || !block_experts || received < 1 || received > kPlanThreads * kPlanMaxChunks ||
+      local_experts < 1 || local_experts > kPlanMaxExperts || rows_per_block < 1 || blocks < 1)
+    return -1;
+  sageb200::launch_dependent<2>(dispatch_plan_kernel, 1, kPlanThreads, 0, static_cast<cudaStream_t>(stream),
+                                static_cast<const int *>(ids), static_cast<int *>(target),
+                                static_cast<int *>(block_experts), received, first_expert, local_experts,
+                                rows_per_block, blocks);
+  return launch_status();
+}
+
+int sageb200_glue_dispatch_rows(const void *x, const void *target, void *rows, int received, int hidden, int dump,
+                                int source_div, void *stream) {
+  if (!x || !target || !rows || received < 1 || hidden < 8 || hidden % 8 || source_div < 1 ||
+      ((reinterpret_cast<uintptr_t>(x) | reinterpret_cast<uintptr_t>(rows)) & 15))
+    return -1;
+  sageb200::launch_dependent<2>(dispatch_rows_kernel, received, 128, 0, static_cast<cudaStream_t>(stream),
+                                static_cast<const __half *>(x), static_cast<const int *>(target),
+                                static_cast<__half *>(rows), hidden, dump, source_div);
+  return launch_status();
+}
+
+int sageb200_glue_combine_rows(const void *outputs, const void *target, void *back, int received, int hidden,
+                               int dump, void *stream) {
+  if (!outputs || !target || !back || received < 1 || hidden < 8 || hidden % 8 ||
+      ((reinterpret_cast<uintptr_t>(outputs) | reinterpret_cast<uintptr_t>(back)) & 15))
+    return -1;
+  sageb200::launch_dependent<2>(combine_rows_kernel, received, 128, 0, static_cast<cudaStream_t>(stream),
+                                static_cast<const __half *>(outputs), static_cast<const int *>(target),
+                                static_cast<__half *>(back), hidden, dump);
   return launch_status();
 }
 

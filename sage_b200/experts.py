@@ -64,7 +64,8 @@ ROWS_PER_EXPERT = 16  # rows one expert takes per step (the decode kernel's row 
 
 def dispatch_combine(x: torch.Tensor, expert_ids: torch.Tensor, weights: torch.Tensor, run_blocks, *,
                      first_expert: int, local_experts: int, group=None, world: int = 1,
-                     rows_per_block: int = ROWS_PER_EXPERT, state: dict | None = None) -> torch.Tensor:
+                     rows_per_block: int = ROWS_PER_EXPERT, state: dict | None = None,
+                     use_kernels: bool | None = None) -> torch.Tensor:
     """Mixture-of-experts output of this rank's own tokens with the experts spread over `world`
     ranks: dispatch all-to-all, per-expert compute on the owners, combine all-to-all.
 
@@ -77,7 +78,10 @@ def dispatch_combine(x: torch.Tensor, expert_ids: torch.Tensor, weights: torch.T
     [blocks] (global expert id, -1 for an unused block) -> [blocks, rows_per_block, hidden], row r
     of block b being that expert's MLP of that row (rows that carry no slot hold stale values and
     their outputs are never read).
-    Returns [tokens, hidden] in x's dtype: sum_j weights[t, j] * expert_{ids[t, j]}(x[t])."""
+    Returns [tokens, hidden] in x's dtype: sum_j weights[t, j] * expert_{ids[t, j]}(x[t]).
+    On the GPU the receive side (plan, scatter into blocks, gather back, mix) runs as four kernels of
+    this library; `use_kernels=False` keeps the tensor program below (the CPU path, and the
+    reference the kernels are tested against)."""
     tokens, top_k = expert_ids.shape
     hidden = x.shape[1]
     slots = tokens * top_k
@@ -86,7 +90,14 @@ def dispatch_combine(x: torch.Tensor, expert_ids: torch.Tensor, weights: torch.T
     owner = torch.div(flat, local_experts, rounding_mode="floor")                      # rank that owns the slot's expert
     peers = torch.arange(world, device=device)[:, None]
     send_ids = torch.where(owner[None, :] == peers, flat[None, :], flat.new_full((), -1)).to(torch.int32).contiguous()
-    send_x = x.repeat_interleave(top_k, dim=0)[None].expand(world, slots, hidden).contiguous()
+    received = world * slots
+    kernels = (use_kernels is not False and x.is_cuda and x.dtype == torch.float16 and received <= 4096
+               and local_experts <= 256 and hidden % 8 == 0)
+    if use_kernels and not kernels:
+        raise ValueError("the dispatch kernels take FP16 CUDA rows, at most 4096 received slots and 256 local experts")
+    # (one GPU with the kernels: the scatter reads the tokens' rows directly, no per-slot copy)
+    send_x = None if world == 1 and kernels else \
+        x.repeat_interleave(top_k, dim=0)[None].expand(world, slots, hidden).contiguous()
     if world > 1:
         import torch.distributed as dist
 
@@ -95,8 +106,12 @@ def dispatch_combine(x: torch.Tensor, expert_ids: torch.Tensor, weights: torch.T
         dist.all_to_all_single(recv_ids, send_ids, group=group)
     else:
         recv_x, recv_ids = send_x, send_ids
-    received = world * slots
     blocks = local_experts + (received + rows_per_block - 1) // rows_per_block          # worst case, fixed
+    if kernels:
+        # on the GPU the plan, the scatter into blocks, the gather back and the mix are four launches
+        return _dispatch_combine_kernels(x, recv_x if world > 1 else None, recv_ids, weights, run_blocks, tokens, top_k,
+                                         hidden, received, blocks, first_expert, local_experts, rows_per_block,
+                                         group, world, state)
     local = recv_ids.reshape(received).to(torch.int64) - first_expert
     key = torch.where(recv_ids.reshape(received) >= 0, local, local.new_full((), local_experts))  # empty slots sort last
     order = torch.argsort(key, stable=True)
@@ -135,6 +150,51 @@ def dispatch_combine(x: torch.Tensor, expert_ids: torch.Tensor, weights: torch.T
     slot_outputs = returned.sum(dim=0) if world > 1 else returned[0]                    # one block holds the value, the rest zeros
     mixed = (slot_outputs.view(tokens, top_k, hidden).float() * weights.to(torch.float32)[..., None]).sum(dim=1)
     return mixed.to(x.dtype)
+
+
+def _dispatch_combine_kernels(x, recv_x, recv_ids, weights, run_blocks, tokens, top_k, hidden, received, blocks,
+                              first_expert, local_experts, rows_per_block, group, world, state):
+    """The receive side of `dispatch_combine` with this library's kernels (the same layout as the
+    tensor program above: slots of an expert in received order, blocks in expert order)."""
+    lib = _lib.load()
+    device = x.device
+    dump = blocks * rows_per_block
+    if state is None:
+        state = {}
+    rows = state.get("rows")
+    if rows is None or rows.shape != (dump + 1, hidden) or rows.device != device or rows.dtype != x.dtype:
+        rows = state["rows"] = torch.zeros(dump + 1, hidden, dtype=x.dtype, device=device)
+    target = torch.empty(received, dtype=torch.int32, device=device)
+    block_experts = torch.empty(blocks, dtype=torch.int32, device=device)
+    ids = recv_ids.reshape(received).contiguous()
+    source = x.contiguous() if recv_x is None else recv_x.reshape(received, hidden)
+    with torch.cuda.device(device):
+        stream = torch.cuda.current_stream(device).cuda_stream
+
+        def check(status, what):
+            if status:
+                raise RuntimeError(f"sage_b200: {what} failed with status {status}")
+
+        check(lib.sageb200_glue_dispatch_plan(ids.data_ptr(), target.data_ptr(), block_experts.data_ptr(), received,
+                                              first_expert, local_experts, rows_per_block, blocks, stream), "dispatch_plan")
+        check(lib.sageb200_glue_dispatch_rows(source.data_ptr(), target.data_ptr(), rows.data_ptr(), received, hidden,
+                                              dump, top_k if recv_x is None else 1, stream), "dispatch_rows")
+        outputs = run_blocks(rows[:dump].view(blocks, rows_per_block, hidden), block_experts).contiguous()
+        back = torch.empty(received, hidden, dtype=x.dtype, device=device)
+        check(lib.sageb200_glue_combine_rows(outputs.data_ptr(), target.data_ptr(), back.data_ptr(), received, hidden,
+                                             dump, stream), "combine_rows")
+        if world > 1:
+            import torch.distributed as dist
+
+            returned = torch.empty_like(back)
+            dist.all_to_all_single(returned, back, group=group)
+            slot_outputs = returned.view(world, tokens * top_k, hidden).sum(dim=0)  # one rank holds the value, the rest zeros
+        else:
+            slot_outputs = back
+        mixed = torch.empty(tokens, hidden, dtype=x.dtype, device=device)
+        check(lib.sageb200_glue_moe_mix(slot_outputs.data_ptr(), weights.to(torch.float32).contiguous().data_ptr(),
+                                        mixed.data_ptr(), tokens, hidden, top_k, stream), "moe_mix")
+    return mixed
 
 
 class SAGEExperts(nn.Module):

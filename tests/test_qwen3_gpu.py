@@ -329,6 +329,45 @@ def test_prompt_attention_on_tensor_cores_against_torch(tokens, first, heads, kv
         assert float((got - want).abs().max()) < 2e-2
 
 
+@pytest.mark.parametrize("tokens,top_k,experts,rows_per_block", [(32, 8, 128, 8), (5, 2, 8, 4), (24, 2, 8, 16),
+                                                                 (300, 8, 64, 8), (7, 4, 256, 8)])
+def test_dispatch_kernels_match_the_tensor_program(tokens, top_k, experts, rows_per_block):
+    """Plan, scatter, gather and mix kernels against the torch tensor program on the same routing
+    (random, and crowded: every token on the same experts), with a block function that shows which
+    expert and which row served a slot."""
+    from sage_b200.experts import dispatch_combine
+
+    device = "cuda:0"
+    hidden = 64
+    gen = torch.Generator(device=device).manual_seed(tokens * 31 + top_k)
+    x = torch.randn(tokens, hidden, generator=gen, device=device).half()
+    weights = torch.rand(tokens, top_k, generator=gen, device=device)
+    random_ids = torch.stack([torch.randperm(experts, generator=gen, device=device)[:top_k]
+                              for _ in range(tokens)]).to(torch.int32)
+    crowded_ids = random_ids[:1].expand(tokens, -1).contiguous()
+
+    def run_blocks(rows, block_experts):  # expert e scales its rows by (1 + e / 8); unused blocks return garbage
+        scale = torch.where(block_experts >= 0, 1.0 + block_experts.float() / 8.0, torch.full_like(block_experts, 1e4).float())
+        return (rows.float() * scale[:, None, None]).half()
+
+    for ids in (random_ids, crowded_ids):
+        want = dispatch_combine(x, ids, weights, run_blocks, first_expert=0, local_experts=experts,
+                                rows_per_block=rows_per_block, state={}, use_kernels=False)
+        got = dispatch_combine(x, ids, weights, run_blocks, first_expert=0, local_experts=experts,
+                               rows_per_block=rows_per_block, state={}, use_kernels=True)
+        direct = (x.float()[:, None, :] * (1.0 + ids.float() / 8.0)[..., None]).half().float()
+        direct = (direct * weights[..., None]).sum(dim=1)
+        assert torch.allclose(got.float(), want.float(), rtol=2e-3, atol=2e-3)
+        assert torch.allclose(got.float(), direct, rtol=4e-3, atol=4e-3)
+    # a rank that owns only the lower half of the experts: the other slots contribute zeros
+    half = experts // 2
+    lower = dispatch_combine(x, random_ids, weights, run_blocks, first_expert=0, local_experts=half,
+                             rows_per_block=rows_per_block, state={}, use_kernels=True)
+    direct = (x.float()[:, None, :] * (1.0 + random_ids.float() / 8.0)[..., None]).half().float()
+    direct = (direct * (weights * (random_ids < half))[..., None]).sum(dim=1)
+    assert torch.allclose(lower.float(), direct, rtol=4e-3, atol=4e-3)
+
+
 def test_report_rows_on_a_small_model():
     """The reference-schema measurement loop runs end to end and its numbers hang together."""
     from sage_b200.harness import measure
