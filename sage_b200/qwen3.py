@@ -158,13 +158,17 @@ class PackedQwen3:
         # exchange buffers of the one-kernel all-reduce (row-parallel outputs, replicated-token
         # expert outputs): one decode step's [batch, hidden] rows
         self.peer = None
+        self.prompt_chunk_rows = 0
         self.peer_error = ""
         reduce_group = tp_group if world > 1 else (ep_group if self.ep_world > 1 and ep_mode == "all_reduce" else None)
         if collective == "peer" and reduce_group is not None and not self.dense:
             from .peer import PeerExchange
 
             try:  # (all ranks succeed or all ranks raise, see PeerExchange)
-                self.peer = PeerExchange(reduce_group, self.device, batch * config.hidden)
+                # (tensor parallelism also reduces chunks of prompt rows through the same exchange)
+                self.prompt_chunk_rows = 512 if world > 1 else 0
+                self.peer = PeerExchange(reduce_group, self.device,
+                                         max(batch, self.prompt_chunk_rows) * config.hidden)
             except RuntimeError as error:  # the GPUs cannot map each other's memory here: NCCL serves
                 self.peer = None
                 self.peer_error = str(error)
@@ -596,13 +600,74 @@ class PackedQwen3:
         prompt = prompt.to(self.device)
         length = prompt.shape[1]
         if batched is None:
-            batched = (self.tp_world == 1 and self.ep_world == 1 and not self.config.experts and length > 1
-                       and self.batch * length <= 65535)
+            batched = (self.ep_world == 1 and not self.config.experts and length > 1
+                       and self.batch * length <= 65535 and (self.tp_world == 1 or self._tp_prompt_ok()))
+        if batched and self.tp_world > 1:
+            return self._prefill_batched_tp(prompt)
         if batched:
             return self._prefill_batched(prompt)
         for i in range(length):
             self.tokens.copy_(prompt[:, i])
             (self.graph if i == length - 1 else self.graph_no_head).replay()
+
+    def _tp_prompt_ok(self) -> bool:
+        """Batched prompt rows under tensor parallelism need the one-kernel all-reduce (an eager NCCL
+        collective after the decode graphs were captured is not an option here) and per-rank
+        permutations (no all-gather of the attention output)."""
+        return (self.peer is not None and self.prompt_chunk_rows > 0 and not self.global_permutations
+                and not self.dense)
+
+    def _prefill_batched_tp(self, prompt: torch.Tensor):
+        """The prompt under tensor parallelism: all tokens but the last go through every layer in
+        chunks of rows (column-parallel q/k/v/gate/up and row-parallel o/down on the tensor-core GEMM
+        path, this rank's heads in the tensor-core attention, the row-parallel partial sums reduced by
+        the one-kernel all-reduce over peer memory), which fills the KV cache; the last prompt token
+        then takes the captured decode step, whose tail (vocabulary-parallel lm_head, all-gather of
+        the logits, argmax) yields the first generated token."""
+        if not self._tp_prompt_ok():
+            raise ValueError("batched prompt rows under tensor parallelism need the peer all-reduce and block permutations")
+        c, lib, b = self.config, self.lib, self.batch
+        length = prompt.shape[1]
+        half = dict(dtype=torch.float16, device=self.device)
+        body = length - 1
+        per_chunk = max(1, self.prompt_chunk_rows // b)  # tokens of every sequence per chunk
+        with torch.cuda.device(self.device):
+            s = self._stream()
+            first = 0
+            while first < body:
+                count = min(per_chunk, body - first)
+                rows = b * count  # row = sequence * count + token
+                tokens = prompt[:, first:first + count].reshape(-1).to(torch.int64).contiguous()
+                h = torch.empty(rows, c.hidden, **half)
+                x = torch.empty_like(h)
+                attn = torch.empty(rows, self.heads * c.head_dim, **half)
+                self._check(lib.sageb200_glue_embed(_vp(self.embed), _vp(tokens), _vp(h), rows, c.hidden, c.vocab, s), "embed")
+                delta = None
+                for layer in self.layers:
+                    self._check(lib.sageb200_glue_add_rmsnorm(_vp(h), _vp(delta), _vp(layer["input_norm"]), _vp(x), rows,
+                                                              c.hidden, c.eps, s), "add_rmsnorm")
+                    q, k, v = self._rows_linears(layer, ("q", "k", "v"), x)
+                    self._check(lib.sageb200_glue_prefill_qk_norm_rope_cache(
+                        _vp(q), _vp(k), _vp(v), _vp(layer["q_norm"]), _vp(layer["k_norm"]), _vp(self.cos), _vp(self.sin),
+                        _vp(self.positions), _vp(layer["k_cache"]), _vp(layer["v_cache"]), b, count, self.heads,
+                        self.kv_heads, c.head_dim, self.max_seq, c.eps, s), "prefill_qk_norm_rope_cache")
+                    self._check(lib.sageb200_glue_prefill_attention(
+                        _vp(q), _vp(layer["k_cache"]), _vp(layer["v_cache"]), _vp(self.positions), _vp(attn), b, count,
+                        self.heads, self.kv_heads, c.head_dim, self.max_seq, s), "prefill_attention")
+                    (o,) = self._rows_linears(layer, ("o",), attn)
+                    self.peer.all_reduce(o)
+                    self._check(lib.sageb200_glue_add_rmsnorm(_vp(h), _vp(o), _vp(layer["post_norm"]), _vp(x), rows,
+                                                              c.hidden, c.eps, s), "add_rmsnorm")
+                    gate, up = self._rows_linears(layer, ("gate", "up"), x)
+                    act = torch.empty_like(gate)
+                    self._check(lib.sageb200_glue_swiglu(_vp(gate), _vp(up), _vp(act), gate.numel(), s), "swiglu")
+                    (delta,) = self._rows_linears(layer, ("down",), act)
+                    self.peer.all_reduce(delta)
+                self.positions.add_(count)
+                first += count
+            # the last prompt token: one captured decode step on top of the filled cache
+            self.tokens.copy_(prompt[:, length - 1])
+            self.graph.replay()
 
     def _rows_linears(self, layer, names, x):
         if self.dense:

@@ -115,7 +115,7 @@ def _worker(rank, world, path, results, mode="tp"):
 
         def run(model):
             """Tokens of 40 greedy steps and the logits of the first generated token."""
-            model.prefill(prompt)
+            model.prefill(prompt, batched=False)  # (token by token: the same arithmetic on one and two GPUs)
             first_logits = model.logits.float().cpu()
             for _ in range(39):
                 model.graph.replay()
@@ -131,6 +131,25 @@ def _worker(rank, world, path, results, mode="tp"):
                                 collective="nccl", **parallel)
             other_tokens, other_logits = run(other)
             assert torch.equal(tokens, other_tokens) and torch.equal(logits, other_logits)
+        if mode == "tp":
+            # a longer prompt: all tokens but the last in rows (tensor-core GEMM path, tensor-core
+            # attention over this rank's heads, the partial sums reduced over peer memory), against the
+            # same prompt fed one position at a time through the decode graph
+            long_prompt = torch.randint(3, config.vocab, (1, 70), generator=torch.Generator().manual_seed(9))
+            assert sharded._tp_prompt_ok()
+            sharded.prefill(long_prompt)
+            rows_logits = sharded.logits.float().cpu()
+            for _ in range(5):
+                sharded.graph.replay()
+            rows_tokens = sharded.log[:, :6].cpu()
+            sharded.prefill(long_prompt, batched=False)
+            steps_logits = sharded.logits.float().cpu()
+            for _ in range(5):
+                sharded.graph.replay()
+            steps_tokens = sharded.log[:, :6].cpu()
+            error = ((rows_logits - steps_logits).norm() / steps_logits.norm()).item()
+            assert error < 1e-2, error
+            assert torch.equal(rows_tokens, steps_tokens), (rows_tokens.tolist(), steps_tokens.tolist())
         if rank == 0:
             # the one-GPU model is fed the sharded model's tokens, so one flip cannot hide later
             # steps; a disagreement is accepted only as a near tie of the one-GPU logits
