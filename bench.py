@@ -746,7 +746,8 @@ def measure_sharded(kind: str, args, device, group, cpu_group, world: int, rank:
     # expert outputs are summed by all-reduce.  `batch` is the whole job's either way.
     exchange = expert_parallel and batch > 16
     local_batch = batch // world if exchange and sharded else batch
-    model = PackedQwen3(config, device, seed=0, max_seq=prompt_length + 2 * (steps + warmup) + 16,
+    long_prompt = 512 if not expert_parallel and batch == 1 else 0  # (the dense-MLP model also times a prompt pass)
+    model = PackedQwen3(config, device, seed=0, max_seq=max(prompt_length + 2 * (steps + warmup), long_prompt) + 16,
                         batch=local_batch, max_new=2 * (steps + warmup) + 16,
                         tp_group=group if sharded and not expert_parallel else None,
                         perm_blocks=1 if expert_parallel else 8,
@@ -789,7 +790,20 @@ def measure_sharded(kind: str, args, device, group, cpu_group, world: int, rank:
         host_token.copy_(host_next)
     e2e_ms = 1000.0 * (time.perf_counter() - e2e_begin)
     barrier()
-    times = torch.tensor([start.elapsed_time(stop), e2e_ms], dtype=torch.float64)
+    prompt_ms = 0.0
+    if long_prompt:
+        # a 512-token prompt pass of the same model (rows through the tcgen05 GEMM path; under tensor
+        # parallelism the partial sums of o/down are reduced by the one-kernel all-reduce)
+        long = torch.randint(3, config.vocab, (local_batch, long_prompt), generator=torch.Generator().manual_seed(11))
+        model.prefill(long)
+        barrier()
+        begin, end = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        begin.record()
+        model.prefill(long)
+        end.record()
+        barrier()
+        prompt_ms = begin.elapsed_time(end)
+    times = torch.tensor([start.elapsed_time(stop), e2e_ms, prompt_ms], dtype=torch.float64)
     if sharded:
         dist.all_reduce(times, op=dist.ReduceOp.MAX, group=cpu_group)
     ms_per_step = float(times[0]) / steps
@@ -815,6 +829,8 @@ def measure_sharded(kind: str, args, device, group, cpu_group, world: int, rank:
         "collective": collective,
         "collective_note": getattr(model, "peer_error", "") or None,
         "collective_calls_per_step": calls,
+        "prompt_pass_ms_512_tokens": float(times[2]) if long_prompt else None,
+        "prompt_pass_batched": bool(long_prompt and (not sharded or model._tp_prompt_ok())) if long_prompt else None,
         "per_rank_hbm_bytes_per_step": step_bytes,
         "per_rank_hbm_gbs": step_bytes / (ms_per_step / 1000.0) / 1e9,
         "hbm_frac": step_bytes / (ms_per_step / 1000.0) / 1e9 / peak,
