@@ -7,7 +7,7 @@
 //   [4096, 8192)         flags[world][kPeerCtas]      flags[r][c]: last epoch rank r's CTA c published
 //   [8192, ...)          slots[2][world][capacity]    FP16 partials; [parity][r] is written by rank r
 //
-// CTA c of every rank owns the same 16-byte chunks (c * 512 + t, stride 16 * 512), so the
+// CTA c of every rank owns the same 16-byte chunks (c * 512 + t, stride 64 * 512), so the
 // handshake is per CTA: no grid-wide step.  A call moves (world - 1) * 2 * elements bytes out of
 // and into every GPU; for a decode row (a few KB) it is bound by one NVLink store latency plus one
 // flag store, not by bandwidth.
@@ -21,7 +21,7 @@
 namespace sageb200 {
 namespace {
 
-constexpr int kPeerCtas = 16;
+constexpr int kPeerCtas = 64;  // (a decode row uses the first one or two; a chunk of prompt rows all of them)
 constexpr int kPeerThreads = 512;
 constexpr size_t kFlagOffset = 4096;
 constexpr size_t kSlotOffset = 8192;
