@@ -49,6 +49,15 @@ int sageb200_debug_trace(void *device_buffer);
  */
 int sageb200_debug_gemm_pairs(int enabled);
 
+/*
+ * The tile plan the tcgen05 GEMM would use for a shape (host arithmetic, no GPU needed), rows >= 33:
+ * fields[0] tokens per accumulator, [1] token blocks, [2] blocks of 128 output rows, [3]
+ * accumulators per CTA, [4] CTA pairs (cta_group::2), [5] K splits, [6] 128-channel groups per
+ * split, [7] pipeline stages, [8] dynamic shared memory bytes, [9] FP32 scratch of the split tiles in
+ * KiB.  `allow_split` = 0 plans for a caller without that scratch.  fields holds 10 ints.
+ */
+int sageb200_debug_gemm_plan(int rows, int n, int k, int sm_count, int allow_split, int *fields);
+
 #ifdef __cplusplus
 }
 #endif

@@ -52,6 +52,7 @@ EXPORTED_DEBUG = (
     "sageb200_set_pdl",
     "sageb200_debug_trace",
     "sageb200_debug_gemm_pairs",
+    "sageb200_debug_gemm_plan",
 )
 
 
@@ -243,6 +244,8 @@ def load() -> ctypes.CDLL:
     lib.sageb200_debug_trace.argtypes = [vp]
     lib.sageb200_debug_gemm_pairs.restype = ci
     lib.sageb200_debug_gemm_pairs.argtypes = [ci]
+    lib.sageb200_debug_gemm_plan.restype = ci
+    lib.sageb200_debug_gemm_plan.argtypes = [ci] * 5 + [ctypes.POINTER(ci)]
     lib.sageb200_launch_count.restype = ctypes.c_ulonglong
     lib.sageb200_launch_count.argtypes = []
     lib.sageb200_glue_launch_count.restype = ctypes.c_ulonglong

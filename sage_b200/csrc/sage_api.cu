@@ -787,6 +787,22 @@ int sageb200_clear_status(void) {
   return SAGEB200_OK;
 }
 
+int sageb200_debug_gemm_plan(int rows, int n, int k, int sm_count, int allow_split, int *fields) {
+  if (!fields || rows < 33 || rows > 65535 || n <= 0 || k <= 0 || (k % 128)) return SAGEB200_ERR_INVALID_ARGUMENT;
+  const GemmPlan plan = plan_gemm_tc(rows, n, k, sm_count > 0 ? sm_count : 148, allow_split != 0);
+  fields[0] = plan.tokens_per_cta;
+  fields[1] = plan.token_blocks;
+  fields[2] = plan.row_blocks;
+  fields[3] = plan.accumulators;
+  fields[4] = plan.pair;
+  fields[5] = plan.k_splits;
+  fields[6] = plan.groups_per_split;
+  fields[7] = plan.stages;
+  fields[8] = static_cast<int>(plan.shared_bytes);
+  fields[9] = static_cast<int>(plan.partial_bytes >> 10);  // KiB
+  return SAGEB200_OK;
+}
+
 int sageb200_debug_gemm_pairs(int enabled) {
   g_gemm_pairs = enabled ? 1 : 0;
   return SAGEB200_OK;

@@ -84,6 +84,42 @@ def test_planning_is_deterministic_and_sane(lib):
     assert lib.sageb200_workspace_bytes(1, 16, 100) == 0
 
 
+def _gemm_plan(lib, rows, n, k, allow_split=1, sm_count=148):
+    fields = (ctypes.c_int * 10)()
+    assert lib.sageb200_debug_gemm_plan(rows, n, k, sm_count, allow_split, fields) == 0
+    names = ("tokens", "token_blocks", "row_blocks", "accumulators", "pair", "k_splits", "groups_per_split",
+             "stages", "shared_bytes", "partial_kib")
+    return dict(zip(names, fields))
+
+
+def test_gemm_planner_choices(lib):
+    """The tcgen05 GEMM's tile plan (host arithmetic): big grids take 256 tokens x 2 accumulators on
+    CTA pairs without a K split; grids that would leave most of 148 SMs idle split K within one
+    wave; without scratch nothing is split; every plan fits the kernel's shared memory."""
+    gate = _gemm_plan(lib, 512, 9728, 2560)
+    assert (gate["tokens"], gate["accumulators"], gate["pair"], gate["k_splits"]) == (256, 2, 1, 1)
+    assert gate["row_blocks"] == 76 and gate["stages"] >= 3
+    big = _gemm_plan(lib, 2048, 25600, 5120)
+    assert (big["tokens"], big["accumulators"], big["pair"], big["k_splits"], big["partial_kib"]) == (256, 2, 1, 1, 0)
+    down = _gemm_plan(lib, 512, 2560, 9728)
+    assert down["k_splits"] > 1 and down["partial_kib"] > 0
+    tiles = down["row_blocks"] * -(-down["token_blocks"] // down["accumulators"])
+    assert tiles * down["k_splits"] <= 148                      # the split grid is one wave
+    assert down["groups_per_split"] * down["k_splits"] >= 9728 // 128
+    assert down["groups_per_split"] * (down["k_splits"] - 1) < 9728 // 128  # no empty split
+    assert _gemm_plan(lib, 512, 2560, 9728, allow_split=0)["k_splits"] == 1
+    odd = _gemm_plan(lib, 300, 1152, 640)                       # nine row blocks: no pairs
+    assert odd["row_blocks"] == 9 and odd["pair"] == 0
+    for rows, n, k in [(33, 129, 256), (257, 640, 1024), (513, 2560, 1280), (4096, 9728, 2560), (65535, 129, 256)]:
+        for allow in (0, 1):
+            plan = _gemm_plan(lib, rows, n, k, allow)
+            assert plan["tokens"] % 16 == 0 and 16 <= plan["tokens"] <= 256
+            assert plan["token_blocks"] * plan["tokens"] >= rows
+            assert plan["shared_bytes"] <= 226 * 1024 and 2 <= plan["stages"] <= 6
+            assert plan["pair"] in (0, 1) and (not plan["pair"] or plan["row_blocks"] % 2 == 0)
+    assert lib.sageb200_debug_gemm_plan(16, 128, 128, 148, 1, (ctypes.c_int * 10)()) == -1
+
+
 def test_invalid_arguments_are_rejected_without_a_device(lib):
     null = ctypes.c_void_p(None)
     one = ctypes.c_void_p(256)  # never dereferenced: validation fails first
