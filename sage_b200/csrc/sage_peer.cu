@@ -5,7 +5,11 @@
 // Exchange layout (one allocation per rank, mapped by all peers):
 //   [0, 4096)            epochs[kPeerCtas]            calls made so far, per CTA (local use only)
 //   [4096, 8192)         flags[world][kPeerCtas]      flags[r][c]: last epoch rank r's CTA c published
-//   [8192, ...)          slots[2][world][capacity]    FP16 partials; [parity][r] is written by rank r
+//   [8192, ...)          slots                        FP16 partials of both parities and all ranks, interleaved in
+//                                                     512-byte blocks: block b of the data sits at
+//                                                     ((b * 2 + parity) * world + rank) * 512 bytes, so a small
+//                                                     message stays within a few pages however large the
+//                                                     exchange is, and a warp still moves 512 contiguous bytes
 //
 // CTA c of every rank owns the same 16-byte chunks (c * 512 + t, stride 64 * 512), so the
 // handshake is per CTA: no grid-wide step.  A call moves (world - 1) * 2 * elements bytes out of
@@ -76,8 +80,11 @@ __global__ void __launch_bounds__(kPeerThreads) peer_all_reduce_kernel(const __g
   }
   __syncthreads();
   const unsigned epoch = epoch_shared;
-  const size_t slot_chunks = static_cast<size_t>(p.capacity) >> 3;
-  const size_t parity_base = static_cast<size_t>(epoch & 1u) * p.world * slot_chunks;
+  const unsigned parity = epoch & 1u;
+  // 16-byte chunk i of rank r's partial, this call's parity (see the layout above)
+  auto slot_index = [&](int i, int r) {
+    return ((static_cast<size_t>(i >> 5) * 2 + parity) * p.world + r) * 32 + (i & 31);
+  };
 
   // ---- push this rank's chunks into slot [parity][rank] of every peer
   for (int i = cta * kPeerThreads + tid; i < p.chunks; i += kPeerCtas * kPeerThreads) {
@@ -85,7 +92,7 @@ __global__ void __launch_bounds__(kPeerThreads) peer_all_reduce_kernel(const __g
     for (int w = 0; w < p.world; ++w) {
       if (w == p.rank) continue;
       uint4 *slots = reinterpret_cast<uint4 *>(p.exchange[w] + kSlotOffset);
-      slots[parity_base + static_cast<size_t>(p.rank) * slot_chunks + i] = v;
+      slots[slot_index(i, p.rank)] = v;
     }
   }
   __syncthreads();
@@ -112,11 +119,11 @@ __global__ void __launch_bounds__(kPeerThreads) peer_all_reduce_kernel(const __g
   if (abort_shared) return;  // (the output keeps this rank's partial; the status word says so)
 
   // ---- reduce in rank order
-  const uint4 *own_slots = reinterpret_cast<const uint4 *>(own + kSlotOffset) + parity_base;
+  const uint4 *own_slots = reinterpret_cast<const uint4 *>(own + kSlotOffset);
   for (int i = cta * kPeerThreads + tid; i < p.chunks; i += kPeerCtas * kPeerThreads) {
     float acc[8] = {0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f};
     for (int w = 0; w < p.world; ++w) {
-      const uint4 v = w == p.rank ? p.data[i] : __ldcg(own_slots + static_cast<size_t>(w) * slot_chunks + i);
+      const uint4 v = w == p.rank ? p.data[i] : __ldcg(own_slots + slot_index(i, w));
       add_halves(acc, v);
     }
     uint4 out;
@@ -141,7 +148,8 @@ extern "C" {
 
 size_t sageb200_peer_exchange_bytes(int world, long long capacity) {
   if (!exchange_arguments_ok(world, capacity)) return 0;
-  return kSlotOffset + static_cast<size_t>(2) * world * capacity * sizeof(__half);
+  const size_t padded = (static_cast<size_t>(capacity) + 255) / 256 * 256;  // whole 512-byte blocks
+  return kSlotOffset + static_cast<size_t>(2) * world * padded * sizeof(__half);
 }
 
 int sageb200_peer_create(int world, long long capacity, void **exchange, unsigned char *handle) {
