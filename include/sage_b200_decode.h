@@ -33,6 +33,20 @@ int sageb200_glue_add_rmsnorm(void *residual, const void *delta, const void *wei
                               int rows, int hidden, float eps, void *stream);
 
 /*
+ * The same with the normalised row also written once per consumer in that consumer's quantised
+ * channel order: outs[j][row][c] = x[row][perms[j][c]] for j < count <= 4 (int32 permutations and
+ * outputs 16-byte aligned; x may be NULL).  The packed linears behind it then take their
+ * activations as they lie (no permutation argument, no gather pre-pass).
+ */
+int sageb200_glue_add_rmsnorm_permuted(void *residual, const void *delta, const void *weight, void *x,
+                                       const void *const *perms, void *const *outs, int count, int rows,
+                                       int hidden, float eps, void *stream);
+
+/* act[row][c] = silu(gate[row][perm[c]]) * up[row][perm[c]] (the rounding of sageb200_glue_swiglu). */
+int sageb200_glue_swiglu_permuted(const void *gate, const void *up, const void *perm, void *act, int rows, int k,
+                                  int sm_count, void *stream);
+
+/*
  * q[rows][q_heads][128] is normalised and rotated in place; k is normalised, rotated and
  * written to k_cache[row][kv_head][positions[row]][:]; v is copied to v_cache likewise.
  * cos/sin tables are FP16 [max_seq][64]; positions are int32 [rows].

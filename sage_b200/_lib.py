@@ -60,6 +60,8 @@ EXPORTED_DEBUG = (
 EXPORTED_DECODE = (
     "sageb200_glue_embed",
     "sageb200_glue_add_rmsnorm",
+    "sageb200_glue_add_rmsnorm_permuted",
+    "sageb200_glue_swiglu_permuted",
     "sageb200_glue_qk_norm_rope_cache",
     "sageb200_glue_attention_scratch_bytes",
     "sageb200_glue_attention_decode",
@@ -256,6 +258,10 @@ def load() -> ctypes.CDLL:
     lib.sageb200_glue_embed.argtypes = [vp, vp, vp, ci, ci, ci, vp]
     lib.sageb200_glue_add_rmsnorm.restype = ci
     lib.sageb200_glue_add_rmsnorm.argtypes = [vp, vp, vp, vp, ci, ci, fl, vp]
+    lib.sageb200_glue_add_rmsnorm_permuted.restype = ci
+    lib.sageb200_glue_add_rmsnorm_permuted.argtypes = [vp, vp, vp, vp, ctypes.POINTER(vp), ctypes.POINTER(vp), ci, ci, ci, fl, vp]
+    lib.sageb200_glue_swiglu_permuted.restype = ci
+    lib.sageb200_glue_swiglu_permuted.argtypes = [vp, vp, vp, vp, ci, ci, ci, vp]
     lib.sageb200_glue_qk_norm_rope_cache.restype = ci
     lib.sageb200_glue_qk_norm_rope_cache.argtypes = [vp] * 10 + [ci] * 5 + [fl, vp]
     lib.sageb200_glue_attention_scratch_bytes.restype = sz

@@ -101,6 +101,97 @@ __global__ void __launch_bounds__(kNormThreads)
   }
 }
 
+
+// add_rmsnorm_kernel with the normalised row written once per consumer, each in that consumer's
+// quantised channel order (out[j][m][c] = x[m][perm[j][c]]): the packed linears behind it then
+// take their activations as they lie and need no gather pre-pass.  Same arithmetic and summation
+// order as add_rmsnorm_kernel; `x` (plain order) is written as well when non-null.
+struct PermutedOutputs {
+  const int *perm[4];
+  __half *out[4];
+  int count;
+};
+__global__ void __launch_bounds__(kNormThreads)
+    add_rmsnorm_permuted_kernel(__half *__restrict__ residual, const __half *__restrict__ delta,
+                                const __half *__restrict__ weight, __half *__restrict__ x,
+                                const __grid_constant__ PermutedOutputs outputs, int hidden, float eps) {
+  sageb200::pdl_launch_dependents();
+  sageb200::pdl_wait();
+  __shared__ float scratch[32];
+  extern __shared__ __half row_shared[];
+  const int m = blockIdx.x;
+  __half *r = residual + static_cast<size_t>(m) * hidden;
+  const __half *d = delta ? delta + static_cast<size_t>(m) * hidden : nullptr;
+  float square = 0.0f;
+  for (int i = threadIdx.x; i < hidden; i += kNormThreads) {
+    __half v = r[i];
+    if (d) {
+      v = __hadd(v, d[i]);
+      r[i] = v;
+    }
+    row_shared[i] = v;
+    const float f = __half2float(v);
+    square += f * f;
+  }
+  const float total = block_sum(square, scratch);
+  const float scale = rsqrtf(total / hidden + eps);
+  for (int i = threadIdx.x; i < hidden; i += kNormThreads) {
+    const __half normed = __float2half_rn(__half2float(row_shared[i]) * scale);
+    const __half value = __hmul(weight[i], normed);
+    row_shared[i] = value;
+    if (x) x[static_cast<size_t>(m) * hidden + i] = value;
+  }
+  __syncthreads();
+  for (int j = 0; j < outputs.count; ++j) {
+    const int4 *perm = reinterpret_cast<const int4 *>(outputs.perm[j]);
+    uint4 *destination = reinterpret_cast<uint4 *>(outputs.out[j] + static_cast<size_t>(m) * hidden);
+    for (int v = threadIdx.x; v < (hidden >> 3); v += kNormThreads) {
+      const int4 lo = __ldg(perm + 2 * v), hi = __ldg(perm + 2 * v + 1);
+      __align__(16) __half values[8] = {row_shared[lo.x], row_shared[lo.y], row_shared[lo.z], row_shared[lo.w],
+                                        row_shared[hi.x], row_shared[hi.y], row_shared[hi.z], row_shared[hi.w]};
+      destination[v] = *reinterpret_cast<const uint4 *>(values);
+    }
+  }
+}
+
+// act_q[m][c] = silu(gate[m][perm[c]]) * up[m][perm[c]]: SwiGLU written in the consumer's
+// quantised channel order (one CTA per row at a time; the row is formed in shared memory with the
+// rounding of swiglu_kernel, then gathered).
+__global__ void __launch_bounds__(256)
+    swiglu_permuted_kernel(const __half *__restrict__ gate, const __half *__restrict__ up,
+                           const int *__restrict__ perm, __half *__restrict__ act, int rows, int k) {
+  sageb200::pdl_launch_dependents();
+  sageb200::pdl_wait();
+  extern __shared__ __half row_shared[];
+  for (int m = blockIdx.x; m < rows; m += gridDim.x) {
+    const uint4 *g4 = reinterpret_cast<const uint4 *>(gate + static_cast<size_t>(m) * k);
+    const uint4 *u4 = reinterpret_cast<const uint4 *>(up + static_cast<size_t>(m) * k);
+    for (int v = threadIdx.x; v < (k >> 3); v += 256) {
+      const uint4 g = g4[v], u = u4[v];
+      const __half2 *g2 = reinterpret_cast<const __half2 *>(&g), *u2 = reinterpret_cast<const __half2 *>(&u);
+      uint4 out;
+      __half2 *o2 = reinterpret_cast<__half2 *>(&out);
+#pragma unroll
+      for (int q = 0; q < 4; ++q) {
+        const float2 f = __half22float2(g2[q]);
+        o2[q] = __hmul2(__halves2half2(__float2half_rn(sageb200::silu_fast(f.x)),
+                                       __float2half_rn(sageb200::silu_fast(f.y))), u2[q]);
+      }
+      reinterpret_cast<uint4 *>(row_shared)[v] = out;
+    }
+    __syncthreads();
+    uint4 *destination = reinterpret_cast<uint4 *>(act + static_cast<size_t>(m) * k);
+    for (int v = threadIdx.x; v < (k >> 3); v += 256) {
+      const int4 lo = __ldg(reinterpret_cast<const int4 *>(perm) + 2 * v);
+      const int4 hi = __ldg(reinterpret_cast<const int4 *>(perm) + 2 * v + 1);
+      __align__(16) __half values[8] = {row_shared[lo.x], row_shared[lo.y], row_shared[lo.z], row_shared[lo.w],
+                                        row_shared[hi.x], row_shared[hi.y], row_shared[hi.z], row_shared[hi.w]};
+      destination[v] = *reinterpret_cast<const uint4 *>(values);
+    }
+    __syncthreads();
+  }
+}
+
 // One warp per (sequence, head): per-head RMSNorm of q or k (head_dim 128), rotate-half
 // RoPE at the sequence's position, q written in place, k and v written into the cache.
 // Heads 0..q_heads-1 are query heads, then kv_heads key heads, then kv_heads value heads.
@@ -1417,6 +1508,56 @@ int sageb200_glue_prefill_attention(const void *q, const void *k_cache, const vo
   return launch_attention(true, q, nullptr, nullptr, nullptr, nullptr, nullptr, nullptr, positions,
                           const_cast<void *>(k_cache), const_cast<void *>(v_cache), out, sequences * tokens, q_heads,
                           kv_heads, max_seq, 1, 0.0f, tokens, false, stream);
+}
+
+int sageb200_glue_add_rmsnorm_permuted(void *residual, const void *delta, const void *weight, void *x,
+                                       const void *const *perms, void *const *outs, int count, int rows,
+                                       int hidden, float eps, void *stream) {
+  if (hidden > 24576 || hidden % 8 || count < 1 || count > 4 || !perms || !outs || rows < 1) return -1;
+  PermutedOutputs outputs = {};
+  outputs.count = count;
+  for (int j = 0; j < count; ++j) {
+    if (!perms[j] || !outs[j] || ((reinterpret_cast<uintptr_t>(perms[j]) | reinterpret_cast<uintptr_t>(outs[j])) & 15))
+      return -1;
+    outputs.perm[j] = static_cast<const int *>(perms[j]);
+    outputs.out[j] = static_cast<__half *>(outs[j]);
+  }
+  const size_t shared = hidden * sizeof(__half);
+  static bool configured = false;
+  if (shared > 40 * 1024 && !configured) {
+    if (cudaFuncSetAttribute(add_rmsnorm_permuted_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, 64 * 1024) !=
+        cudaSuccess)
+      return -5;
+    configured = true;
+  }
+  sageb200::launch_dependent<2>(add_rmsnorm_permuted_kernel, rows, kNormThreads, shared,
+                                static_cast<cudaStream_t>(stream), static_cast<__half *>(residual),
+                                static_cast<const __half *>(delta), static_cast<const __half *>(weight),
+                                static_cast<__half *>(x), outputs, hidden, eps);
+  return launch_status();
+}
+
+int sageb200_glue_swiglu_permuted(const void *gate, const void *up, const void *perm, void *act, int rows, int k,
+                                  int sm_count, void *stream) {
+  if (rows < 1 || k < 8 || k % 8 || k > 100 * 1024 || !gate || !up || !perm || !act ||
+      ((reinterpret_cast<uintptr_t>(gate) | reinterpret_cast<uintptr_t>(up) | reinterpret_cast<uintptr_t>(perm) |
+        reinterpret_cast<uintptr_t>(act)) & 15))
+    return -1;
+  const size_t shared = static_cast<size_t>(k) * sizeof(__half);
+  static bool configured = false;
+  if (shared > 40 * 1024 && !configured) {
+    if (cudaFuncSetAttribute(swiglu_permuted_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, 200 * 1024) !=
+        cudaSuccess)
+      return -5;
+    configured = true;
+  }
+  int blocks = rows;
+  const int cap = (sm_count > 0 ? sm_count : 148) * 4;
+  if (blocks > cap) blocks = cap;
+  sageb200::launch_dependent<2>(swiglu_permuted_kernel, blocks, 256, shared, static_cast<cudaStream_t>(stream),
+                                static_cast<const __half *>(gate), static_cast<const __half *>(up),
+                                static_cast<const int *>(perm), static_cast<__half *>(act), rows, k);
+  return launch_status();
 }
 
 int sageb200_glue_swiglu(const void *gate, const void *up, void *act, long long count, void *stream) {

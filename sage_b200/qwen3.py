@@ -639,14 +639,11 @@ class PackedQwen3:
                 rows = b * count  # row = sequence * count + token
                 tokens = prompt[:, first:first + count].reshape(-1).to(torch.int64).contiguous()
                 h = torch.empty(rows, c.hidden, **half)
-                x = torch.empty_like(h)
                 attn = torch.empty(rows, self.heads * c.head_dim, **half)
                 self._check(lib.sageb200_glue_embed(_vp(self.embed), _vp(tokens), _vp(h), rows, c.hidden, c.vocab, s), "embed")
                 delta = None
                 for layer in self.layers:
-                    self._check(lib.sageb200_glue_add_rmsnorm(_vp(h), _vp(delta), _vp(layer["input_norm"]), _vp(x), rows,
-                                                              c.hidden, c.eps, s), "add_rmsnorm")
-                    q, k, v = self._rows_linears(layer, ("q", "k", "v"), x)
+                    q, k, v = self._norm_rows_linears(layer, ("q", "k", "v"), h, delta, layer["input_norm"], rows)
                     self._check(lib.sageb200_glue_prefill_qk_norm_rope_cache(
                         _vp(q), _vp(k), _vp(v), _vp(layer["q_norm"]), _vp(layer["k_norm"]), _vp(self.cos), _vp(self.sin),
                         _vp(self.positions), _vp(layer["k_cache"]), _vp(layer["v_cache"]), b, count, self.heads,
@@ -656,18 +653,55 @@ class PackedQwen3:
                         self.heads, self.kv_heads, c.head_dim, self.max_seq, s), "prefill_attention")
                     (o,) = self._rows_linears(layer, ("o",), attn)
                     self.peer.all_reduce(o)
-                    self._check(lib.sageb200_glue_add_rmsnorm(_vp(h), _vp(o), _vp(layer["post_norm"]), _vp(x), rows,
-                                                              c.hidden, c.eps, s), "add_rmsnorm")
-                    gate, up = self._rows_linears(layer, ("gate", "up"), x)
-                    act = torch.empty_like(gate)
-                    self._check(lib.sageb200_glue_swiglu(_vp(gate), _vp(up), _vp(act), gate.numel(), s), "swiglu")
-                    (delta,) = self._rows_linears(layer, ("down",), act)
+                    gate, up = self._norm_rows_linears(layer, ("gate", "up"), h, o, layer["post_norm"], rows)
+                    delta = self._swiglu_rows_linear(layer, "down", gate, up)
                     self.peer.all_reduce(delta)
                 self.positions.add_(count)
                 first += count
             # the last prompt token: one captured decode step on top of the filled cache
             self.tokens.copy_(prompt[:, length - 1])
             self.graph.replay()
+
+    def _pregathered(self, linear, xq):
+        """A packed linear on activations that already lie in its quantised channel order."""
+        p = linear.packed
+        return sage_forward(xq, p["packed_codes"], p["radius_codes"], p["radius_grid"], p["codebook"],
+                            p["permutation"][:0], linear.n)
+
+    def _norm_rows_linears(self, layer, names, h, delta, weight, rows):
+        """Prompt rows: h += delta, x = rmsnorm(h) * weight, then the packed linears `names` on x.  The
+        norm kernel writes x once per linear in that linear's quantised channel order, so the
+        linears need no gather pre-pass (dense oracle model, or a linear without a permutation: the
+        plain norm kernel and the usual call)."""
+        c, lib = self.config, self.lib
+        s = self._stream()
+        permutations = [] if self.dense else [layer[name].packed["permutation"] for name in names]
+        if self.dense or len(names) > 4 or any(p.numel() != c.hidden or p.data_ptr() % 16 for p in permutations):
+            x = torch.empty_like(h)
+            self._check(lib.sageb200_glue_add_rmsnorm(_vp(h), _vp(delta), _vp(weight), _vp(x), rows, c.hidden, c.eps, s),
+                        "add_rmsnorm")
+            return self._rows_linears(layer, names, x)
+        outs = [torch.empty_like(h) for _ in names]
+        perm_array = (ctypes.c_void_p * len(names))(*[p.data_ptr() for p in permutations])
+        out_array = (ctypes.c_void_p * len(names))(*[o.data_ptr() for o in outs])
+        self._check(lib.sageb200_glue_add_rmsnorm_permuted(_vp(h), _vp(delta), _vp(weight), None, perm_array, out_array,
+                                                           len(names), rows, c.hidden, c.eps, s), "add_rmsnorm_permuted")
+        return [self._pregathered(layer[name], xq) for name, xq in zip(names, outs)]
+
+    def _swiglu_rows_linear(self, layer, name, gate, up):
+        """Prompt rows: the packed linear `name` on SwiGLU(gate, up), the activation written directly
+        in the linear's quantised channel order where it has a permutation."""
+        lib = self.lib
+        s = self._stream()
+        act = torch.empty_like(gate)
+        permutation = None if self.dense else layer[name].packed["permutation"]
+        k = gate.shape[-1]
+        if permutation is None or permutation.numel() != k or permutation.data_ptr() % 16:
+            self._check(lib.sageb200_glue_swiglu(_vp(gate), _vp(up), _vp(act), gate.numel(), s), "swiglu")
+            return self._rows_linears(layer, (name,), act)[0]
+        self._check(lib.sageb200_glue_swiglu_permuted(_vp(gate), _vp(up), _vp(permutation), _vp(act), gate.numel() // k, k,
+                                                      self.sm_count, s), "swiglu_permuted")
+        return self._pregathered(layer[name], act)
 
     def _rows_linears(self, layer, names, x):
         if self.dense:
@@ -685,14 +719,11 @@ class PackedQwen3:
             s = self._stream()
             tokens = prompt.reshape(-1).to(torch.int64).contiguous()
             h = torch.empty(rows, c.hidden, **half)
-            x = torch.empty_like(h)
             attn = torch.empty(rows, self.heads * c.head_dim, **half)
             self._check(lib.sageb200_glue_embed(_vp(self.embed), _vp(tokens), _vp(h), rows, c.hidden, c.vocab, s), "embed")
             delta = None
             for layer in self.layers:
-                self._check(lib.sageb200_glue_add_rmsnorm(_vp(h), _vp(delta), _vp(layer["input_norm"]), _vp(x), rows,
-                                                          c.hidden, c.eps, s), "add_rmsnorm")
-                q, k, v = self._rows_linears(layer, ("q", "k", "v"), x)
+                q, k, v = self._norm_rows_linears(layer, ("q", "k", "v"), h, delta, layer["input_norm"], rows)
                 self._check(lib.sageb200_glue_prefill_qk_norm_rope_cache(
                     _vp(q), _vp(k), _vp(v), _vp(layer["q_norm"]), _vp(layer["k_norm"]), _vp(self.cos), _vp(self.sin),
                     _vp(self.positions), _vp(layer["k_cache"]), _vp(layer["v_cache"]), b, length, self.heads,
@@ -701,12 +732,8 @@ class PackedQwen3:
                     _vp(q), _vp(layer["k_cache"]), _vp(layer["v_cache"]), _vp(self.positions), _vp(attn), b, length,
                     self.heads, self.kv_heads, c.head_dim, self.max_seq, s), "prefill_attention")
                 (o,) = self._rows_linears(layer, ("o",), attn)
-                self._check(lib.sageb200_glue_add_rmsnorm(_vp(h), _vp(o), _vp(layer["post_norm"]), _vp(x), rows,
-                                                          c.hidden, c.eps, s), "add_rmsnorm")
-                gate, up = self._rows_linears(layer, ("gate", "up"), x)
-                act = torch.empty_like(gate)
-                self._check(lib.sageb200_glue_swiglu(_vp(gate), _vp(up), _vp(act), gate.numel(), s), "swiglu")
-                (delta,) = self._rows_linears(layer, ("down",), act)
+                gate, up = self._norm_rows_linears(layer, ("gate", "up"), h, o, layer["post_norm"], rows)
+                delta = self._swiglu_rows_linear(layer, "down", gate, up)
             # the step tail on each sequence's last prompt token
             last = torch.arange(b, device=self.device) * length + (length - 1)
             h_last, delta_last = h[last].contiguous(), delta[last].contiguous()
