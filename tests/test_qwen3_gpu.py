@@ -368,6 +368,61 @@ def test_dispatch_kernels_match_the_tensor_program(tokens, top_k, experts, rows_
     assert torch.allclose(lower.float(), direct, rtol=4e-3, atol=4e-3)
 
 
+@pytest.mark.parametrize("rows,hidden,count", [(1, 256, 1), (33, 2560, 3), (7, 5120, 2), (512, 2560, 4)])
+def test_norm_with_permuted_outputs_is_the_norm_then_a_gather(rows, hidden, count):
+    """`add_rmsnorm_permuted` against `add_rmsnorm` followed by index_select per consumer: bit for
+    bit, residual update included; with and without a delta."""
+    import ctypes
+
+    from sage_b200 import _lib
+
+    lib = _lib.load()
+    device = "cuda:0"
+    gen = torch.Generator(device=device).manual_seed(rows + hidden)
+    vp = ctypes.c_void_p
+    for with_delta in (True, False):
+        residual = torch.randn(rows, hidden, generator=gen, device=device).half()
+        delta = torch.randn(rows, hidden, generator=gen, device=device).half() if with_delta else None
+        weight = (1.0 + 0.1 * torch.randn(hidden, generator=gen, device=device)).half()
+        perms = [torch.randperm(hidden, generator=gen, device=device).to(torch.int32) for _ in range(count)]
+        want_residual, want_x = residual.clone(), torch.empty_like(residual)
+        assert lib.sageb200_glue_add_rmsnorm(vp(want_residual.data_ptr()), vp(delta.data_ptr()) if with_delta else None,
+                                             vp(weight.data_ptr()), vp(want_x.data_ptr()), rows, hidden, 1e-6, None) == 0
+        got_residual, got_x = residual.clone(), torch.empty_like(residual)
+        outs = [torch.empty_like(residual) for _ in range(count)]
+        perm_array = (vp * count)(*[p.data_ptr() for p in perms])
+        out_array = (vp * count)(*[o.data_ptr() for o in outs])
+        assert lib.sageb200_glue_add_rmsnorm_permuted(vp(got_residual.data_ptr()), vp(delta.data_ptr()) if with_delta else None,
+                                                      vp(weight.data_ptr()), vp(got_x.data_ptr()), perm_array, out_array,
+                                                      count, rows, hidden, 1e-6, None) == 0
+        torch.cuda.synchronize()
+        assert torch.equal(got_residual, want_residual) and torch.equal(got_x, want_x)
+        for perm, out in zip(perms, outs):
+            assert torch.equal(out, want_x.index_select(-1, perm.long()))
+    assert lib.sageb200_glue_add_rmsnorm_permuted(None, None, None, None, None, None, 5, 1, 256, 1e-6, None) == -1
+
+
+@pytest.mark.parametrize("rows,k", [(1, 128), (33, 9728), (512, 9728), (9, 25600)])
+def test_swiglu_with_permuted_output_is_swiglu_then_a_gather(rows, k):
+    import ctypes
+
+    from sage_b200 import _lib
+
+    lib = _lib.load()
+    device = "cuda:0"
+    gen = torch.Generator(device=device).manual_seed(rows + k)
+    vp = ctypes.c_void_p
+    gate = torch.randn(rows, k, generator=gen, device=device).half()
+    up = torch.randn(rows, k, generator=gen, device=device).half()
+    perm = torch.randperm(k, generator=gen, device=device).to(torch.int32)
+    want, got = torch.empty_like(gate), torch.empty_like(gate)
+    assert lib.sageb200_glue_swiglu(vp(gate.data_ptr()), vp(up.data_ptr()), vp(want.data_ptr()), gate.numel(), None) == 0
+    assert lib.sageb200_glue_swiglu_permuted(vp(gate.data_ptr()), vp(up.data_ptr()), vp(perm.data_ptr()),
+                                             vp(got.data_ptr()), rows, k, 148, None) == 0
+    torch.cuda.synchronize()
+    assert torch.equal(got, want.index_select(-1, perm.long()))
+
+
 def test_report_rows_on_a_small_model():
     """The reference-schema measurement loop runs end to end and its numbers hang together."""
     from sage_b200.harness import measure
