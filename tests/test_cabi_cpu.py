@@ -183,10 +183,9 @@ def test_decode_planner_choices():
     # several rows that fit beside whole tiles run without K slices and without scratch: 8 rows of
     # K = 2560 / 4096, 16 rows of K = 2560
     for rows, k, n in [(8, 2560, 9728), (8, 2560, 4096), (8, 4096, 2560), (16, 2560, 9728), (16, 2560, 4096)]:
-        if True:
-            plan = _plan(lib, rows, n, k)
-            assert plan["slices"] == 1 and plan["whole"] == 1 and plan["scratch"] == 0, (rows, k, n, plan)
-            assert plan["shared"] <= 184 * 1024
+        plan = _plan(lib, rows, n, k)
+        assert plan["slices"] == 1 and plan["whole"] == 1 and plan["scratch"] == 0, (rows, k, n, plan)
+        assert plan["shared"] <= 184 * 1024
     import ctypes
 
     assert lib.sageb200_debug_plan(17, 16, 128, 148, 0, (ctypes.c_int * 8)()) == -1
