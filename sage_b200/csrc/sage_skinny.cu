@@ -91,7 +91,7 @@ __device__ __forceinline__ int split_owner(int u, int q, int r) {
 // the linear staging buffer): 1 = fused residual add + RMSNorm, 2 = fused SwiGLU, 3 = plain
 // 16-byte aligned x; 5 = kind 3 for routed experts (the indirection stays); 4 = one activation
 // row and nothing else assumed; 6 = several rows staged beforehand (no permutation left, aligned x,
-// K not sliced, no expert stack); 0 = every case.  The special paths are the generic code with those facts
+// K not sliced, no expert stack); 7 = kind 6 with K cut into slices; 0 = every case.  The special paths are the generic code with those facts
 // known at compile time, so the cold instruction stream after the wait is short and contiguous.
 // kRing: the CTA's share streams through per-warp rings (see kRingStages); a separate variant so
 // that the resident-share kernels keep their shorter main loop.
@@ -130,6 +130,9 @@ __global__ void __launch_bounds__(512, 1) sage_skinny_kernel(const __grid_consta
   if constexpr (kPath == 6) {
     p.slices = 1;  // several rows, staged beforehand: no permutation left, x aligned
     p.expert_ids = nullptr;
+    p.perm = nullptr;
+  } else if constexpr (kPath == 7) {
+    p.expert_ids = nullptr;  // kind 6 with the K slices left in
     p.perm = nullptr;
   } else if constexpr (kPath == 4) {
     p.rows = 1;  // the only fact kind 4 fixes
@@ -317,16 +320,16 @@ __global__ void __launch_bounds__(512, 1) sage_skinny_kernel(const __grid_consta
   const bool aligned_x = (kPath != 0 && kPath != 4) || (reinterpret_cast<uintptr_t>(p.x) & 15) == 0;  // (kind 6: checked on the host)
   const bool perm_aligned = (kPath != 0 && kPath != 4) || (reinterpret_cast<uintptr_t>(p.perm) & 15) == 0;
   const bool linear_gather =
-      (kPath != 0 && kPath != 4 && kPath != 6) || (p.perm != nullptr && perm_aligned &&
+      (kPath != 0 && kPath != 4 && kPath != 6 && kPath != 7) || (p.perm != nullptr && perm_aligned &&
                      static_cast<size_t>(p.rows) * p.k * 2 <= static_cast<size_t>(params.lin_bytes));
   // Fused producer (single activation row only): the row is computed here from the
   // producer's inputs instead of being read from p.x:
   //   1  x = weight * fp16((a + b) * rsqrt(mean((a + b)^2) + eps)),  a + b also stored as the
   //      new residual by the launch's first CTA                      (residual add + RMSNorm)
   //   2  x = fp16(silu(a)) * b                                        (SwiGLU)
-  const int fused = (kPath == 0 || kPath == 4) ? params.act_kind : ((kPath == 3 || kPath == 5 || kPath == 6) ? 0 : kPath);
+  const int fused = (kPath == 0 || kPath == 4) ? params.act_kind : ((kPath == 3 || kPath >= 5) ? 0 : kPath);
   const bool gather_from_linear = linear_gather || fused != 0;
-  const bool direct_copy = kPath == 6 || ((kPath == 0 || kPath == 4) && p.perm == nullptr && aligned_x && fused == 0);
+  const bool direct_copy = kPath == 6 || kPath == 7 || ((kPath == 0 || kPath == 4) && p.perm == nullptr && aligned_x && fused == 0);
   constexpr int kItemBatch = 4;  // permutation items (4 channels each) held in registers
   constexpr int kCopyBatch = 4;  // 16-byte activation pieces held in registers
   int4 held[kItemBatch];
@@ -347,7 +350,7 @@ __global__ void __launch_bounds__(512, 1) sage_skinny_kernel(const __grid_consta
   }
   auto load_item = [&](int q) {  // source channels of quantised channels 4q .. 4q+3
     const int channel = group_begin * 128 + 4 * q;
-    if ((kPath == 0 || kPath == 4 || kPath == 6) && p.perm == nullptr) return make_int4(channel, channel + 1, channel + 2, channel + 3);
+    if ((kPath == 0 || kPath == 4 || kPath == 6 || kPath == 7) && p.perm == nullptr) return make_int4(channel, channel + 1, channel + 2, channel + 3);
     if (perm_aligned) return __ldg(reinterpret_cast<const int4 *>(p.perm) + (channel >> 2));
     return make_int4(__ldg(p.perm + channel), __ldg(p.perm + channel + 1), __ldg(p.perm + channel + 2),
                      __ldg(p.perm + channel + 3));
@@ -926,6 +929,10 @@ cudaError_t configure_skinny() {
   if (status == cudaSuccess) status = configure_variant<1, true, 6>();
   if (status == cudaSuccess) status = configure_variant<2, false, 6>();
   if (status == cudaSuccess) status = configure_variant<2, true, 6>();
+  if (status == cudaSuccess) status = configure_variant<1, false, 7>();
+  if (status == cudaSuccess) status = configure_variant<1, true, 7>();
+  if (status == cudaSuccess) status = configure_variant<2, false, 7>();
+  if (status == cudaSuccess) status = configure_variant<2, true, 7>();
   return status;
 }
 
@@ -966,19 +973,22 @@ cudaError_t launch_skinny(const SkinnyParams &params, int warps, int column_bloc
   bool single_rows = column_blocks == 1;
   for (int i = 0; i < params.count; ++i) single_rows = single_rows && params.problem[i].rows == 1;
   if (path == 0 && single_rows) path = 4;  // one activation row, everything else as it comes
-  if (path == 0 && params.act_kind == 0) {  // several rows staged beforehand (see kind 6)
+  if (path == 0 && params.act_kind == 0) {  // several rows staged beforehand (kind 6; 7 with K slices)
     path = 6;
-    for (int i = 0; i < params.count; ++i) {
+    for (int i = 0; i < params.count && path != 0; ++i) {
       const SkinnyProblem &q = params.problem[i];
-      if (q.slices != 1 || q.expert_ids != nullptr || q.perm != nullptr ||
-          (reinterpret_cast<uintptr_t>(q.x) & 15) != 0)
+      if (q.expert_ids != nullptr || q.perm != nullptr || (reinterpret_cast<uintptr_t>(q.x) & 15) != 0)
         path = 0;
+      else if (q.slices != 1)
+        path = 7;
     }
   }
-  // debug switch: 0 = generic kernel only, 3 = kinds 1-3 only, 4 = kind 4 for every single-row launch
+  // debug switch: 0 = generic kernel only, 3 = kinds 1-3 only, 4 = kind 4 for every single-row launch,
+  // 6 = no kind 7
   const int limit = skinny_path_limit();
   if (limit == 0) path = 0;
   if (limit == 3 && path >= 4) path = 0;
+  if (limit == 6 && path == 7) path = 0;
   if (limit == 4) path = single_rows ? 4 : 0;
   bool ring = false;  // (the planner gives every problem of a launch the same answer, or none)
   for (int i = 0; i < params.count; ++i) ring = ring || params.problem[i].ring != 0;
@@ -996,10 +1006,12 @@ cudaError_t launch_skinny(const SkinnyParams &params, int warps, int column_bloc
       case 4: return low_bits ? SAGE_LAUNCH(1, true, 4) : SAGE_LAUNCH(1, false, 4);
       case 5: return low_bits ? SAGE_LAUNCH(1, true, 5) : SAGE_LAUNCH(1, false, 5);
       case 6: return low_bits ? SAGE_LAUNCH(1, true, 6) : SAGE_LAUNCH(1, false, 6);
+      case 7: return low_bits ? SAGE_LAUNCH(1, true, 7) : SAGE_LAUNCH(1, false, 7);
       default: return low_bits ? SAGE_LAUNCH(1, true, 0) : SAGE_LAUNCH(1, false, 0);
     }
   }
   if (path == 6) return low_bits ? SAGE_LAUNCH(2, true, 6) : SAGE_LAUNCH(2, false, 6);
+  if (path == 7) return low_bits ? SAGE_LAUNCH(2, true, 7) : SAGE_LAUNCH(2, false, 7);
   return low_bits ? SAGE_LAUNCH(2, true, 0) : SAGE_LAUNCH(2, false, 0);
 #undef SAGE_LAUNCH
   return cudaGetLastError();
