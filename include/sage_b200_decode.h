@@ -86,6 +86,18 @@ int sageb200_glue_attention_step(const void *q, const void *k, const void *v, co
                                  void *stream);
 
 /*
+ * The same, with each output row written through `out_index` (int32 [q_heads * head_dim], or
+ * null for the plain order): channel c of a row lands at out[row][out_index[c]].  Given the
+ * inverse of the output projection's channel permutation, the rows arrive in that linear's
+ * quantised channel order and it is called with an empty permutation (no gather of its own).
+ */
+int sageb200_glue_attention_step_permuted(const void *q, const void *k, const void *v, const void *q_weight,
+                                          const void *k_weight, const void *cos_table, const void *sin_table,
+                                          const void *positions, void *k_cache, void *v_cache, void *out,
+                                          const void *out_index, int rows, int q_heads, int kv_heads, int head_dim,
+                                          int max_seq, int splits, float eps, void *stream);
+
+/*
  * Prompt processing (many tokens of each sequence at once).  Rows are [sequence][token]:
  * row s*tokens + t is token t of sequence s and sits at cache position positions[s] + t.
  * The first call is sageb200_glue_qk_norm_rope_cache for such rows (q normalised and rotated

@@ -5,7 +5,7 @@ raises if `libsage_b200.so` has not been built (`python -m sage_b200.build`).
 """
 
 from .linear import SAGELinear
-from .ops import sage, sage_dequantize, sage_forward, sage_grouped
+from .ops import sage, sage_dequantize, sage_forward, sage_forward_scratch, sage_grouped
 from .sphquant import SPHQuantLinear, sph_dequantize, sphquant
 from .synthetic import synthetic_sage, synthetic_sphquant
 
@@ -15,6 +15,7 @@ __all__ = [
     "sage",
     "sage_dequantize",
     "sage_forward",
+    "sage_forward_scratch",
     "sage_grouped",
     "sph_dequantize",
     "sphquant",

@@ -66,6 +66,7 @@ EXPORTED_DECODE = (
     "sageb200_glue_attention_scratch_bytes",
     "sageb200_glue_attention_decode",
     "sageb200_glue_attention_step",
+    "sageb200_glue_attention_step_permuted",
     "sageb200_glue_prefill_qk_norm_rope_cache",
     "sageb200_glue_prefill_attention",
     "sageb200_glue_lm_head_step_scratch_bytes",
@@ -268,6 +269,8 @@ def load() -> ctypes.CDLL:
     lib.sageb200_glue_attention_scratch_bytes.argtypes = [ci, ci, ci]
     lib.sageb200_glue_attention_step.restype = ci
     lib.sageb200_glue_attention_step.argtypes = [vp] * 11 + [ci] * 6 + [ctypes.c_float, vp]
+    lib.sageb200_glue_attention_step_permuted.restype = ci
+    lib.sageb200_glue_attention_step_permuted.argtypes = [vp] * 12 + [ci] * 6 + [ctypes.c_float, vp]
     lib.sageb200_glue_prefill_qk_norm_rope_cache.restype = ci
     lib.sageb200_glue_prefill_qk_norm_rope_cache.argtypes = [vp] * 10 + [ci] * 6 + [ctypes.c_float, vp]
     lib.sageb200_glue_prefill_attention.restype = ci

@@ -410,14 +410,15 @@ __device__ __forceinline__ void unpack16(const uint4 &a, const uint4 &b, float o
   }
 }
 
-template <int kStepHeads, bool kExact, bool kPrompt>
+template <int kStepHeads, bool kExact, bool kPrompt, bool kIndexed = false>
 __global__ void __launch_bounds__(kAttnWarps * 32)
     attention_step_kernel(const __half *__restrict__ q, const __half *__restrict__ k,
                           const __half *__restrict__ v, const __half *__restrict__ q_weight,
                           const __half *__restrict__ k_weight, const __half *__restrict__ cos_table,
                           const __half *__restrict__ sin_table, const int *__restrict__ positions,
                           __half *k_cache, __half *v_cache, __half *__restrict__ out, int q_heads,
-                          int kv_heads, int max_seq, float eps, float scale, int rows_per_sequence) {
+                          int kv_heads, int max_seq, float eps, float scale, int rows_per_sequence,
+                          const int *__restrict__ out_index) {
   sageb200::pdl_launch_dependents();
   sageb200::pdl_wait();
 
@@ -615,7 +616,15 @@ __global__ void __launch_bounds__(kAttnWarps * 32)
       total += *cluster.map_shared_rank(&cta_total[g], s) * f;
       value += *cluster.map_shared_rank(&cta_acc[g][dim], s) * f;
     }
-    out[(static_cast<size_t>(m) * q_heads + first_head + g) * 128 + dim] = __float2half_rn(value / total);
+    // kIndexed: out_index says where each channel of a row goes - the consumer's quantised channel
+    // order, so the packed linear behind this kernel needs no gather of its own (a variant of its
+    // own: the plain kernel keeps its registers and instruction stream)
+    if constexpr (kIndexed) {
+      const int target = __ldg(out_index + (first_head + g) * 128 + dim);
+      out[static_cast<size_t>(m) * q_heads * 128 + target] = __float2half_rn(value / total);
+    } else {
+      out[(static_cast<size_t>(m) * q_heads + first_head + g) * 128 + dim] = __float2half_rn(value / total);
+    }
   }
   cluster.sync();  // nobody leaves while its shared memory may still be read
 }
@@ -1395,7 +1404,7 @@ namespace {
 
 using AttentionKernel = void (*)(const __half *, const __half *, const __half *, const __half *, const __half *,
                                  const __half *, const __half *, const int *, __half *, __half *, __half *, int, int,
-                                 int, float, float, int);
+                                 int, float, float, int, const int *);
 
 // debug: environment SAGEB200_ATTN_HEADS = 1, 2 or 4 forces the query heads per CTA
 int attention_heads_override() {
@@ -1416,17 +1425,20 @@ int attention_heads_per_cta(int group, int units_at_four, int sm_count) {
   return group >= 3 ? 4 : 1;
 }
 
-template <bool kPrompt>
+template <bool kPrompt, bool kIndexed = false>
 AttentionKernel attention_variant(int heads_per_cta, bool exact) {
-  if (heads_per_cta == 4) return exact ? attention_step_kernel<4, true, kPrompt> : attention_step_kernel<4, false, kPrompt>;
-  if (heads_per_cta == 2) return exact ? attention_step_kernel<2, true, kPrompt> : attention_step_kernel<2, false, kPrompt>;
-  return attention_step_kernel<1, true, kPrompt>;
+  if (heads_per_cta == 4)
+    return exact ? attention_step_kernel<4, true, kPrompt, kIndexed> : attention_step_kernel<4, false, kPrompt, kIndexed>;
+  if (heads_per_cta == 2)
+    return exact ? attention_step_kernel<2, true, kPrompt, kIndexed> : attention_step_kernel<2, false, kPrompt, kIndexed>;
+  return attention_step_kernel<1, true, kPrompt, kIndexed>;
 }
 
 int launch_attention(bool prompt_rows, const void *q, const void *k, const void *v, const void *q_weight,
                      const void *k_weight, const void *cos_table, const void *sin_table, const void *positions,
                      void *k_cache, void *v_cache, void *out, int grid_rows, int q_heads, int kv_heads, int max_seq,
-                     int splits, float eps, int rows_per_sequence, bool dependent, void *stream) {
+                     int splits, float eps, int rows_per_sequence, bool dependent, void *stream,
+                     const void *out_index = nullptr) {
   const int group = q_heads / kv_heads;
   static int sm_count = 0;
   if (sm_count == 0) {
@@ -1438,7 +1450,9 @@ int launch_attention(bool prompt_rows, const void *q, const void *k, const void 
   const int per_cta = attention_heads_per_cta(group, splits * kv_heads * ((group + 3) / 4) * grid_rows, sm_count);
   const int parts = (group + per_cta - 1) / per_cta;
   const bool exact = group % per_cta == 0;
-  AttentionKernel kernel = prompt_rows ? attention_variant<true>(per_cta, exact) : attention_variant<false>(per_cta, exact);
+  AttentionKernel kernel = prompt_rows  ? attention_variant<true>(per_cta, exact)
+                           : out_index ? attention_variant<false, true>(per_cta, exact)
+                                       : attention_variant<false>(per_cta, exact);
   if (splits == 16) {  // beyond the portable cluster size: opt in, and check that one fits at all
     if (cudaFuncSetAttribute(kernel, cudaFuncAttributeNonPortableClusterSizeAllowed, 1) != cudaSuccess) {
       cudaGetLastError();
@@ -1471,7 +1485,8 @@ int launch_attention(bool prompt_rows, const void *q, const void *k, const void 
       static_cast<const __half *>(v), static_cast<const __half *>(q_weight), static_cast<const __half *>(k_weight),
       static_cast<const __half *>(cos_table), static_cast<const __half *>(sin_table),
       static_cast<const int *>(positions), static_cast<__half *>(k_cache), static_cast<__half *>(v_cache),
-      static_cast<__half *>(out), q_heads, kv_heads, max_seq, eps, rsqrtf(128.0f), rows_per_sequence);
+      static_cast<__half *>(out), q_heads, kv_heads, max_seq, eps, rsqrtf(128.0f), rows_per_sequence,
+      static_cast<const int *>(out_index));
   return error == cudaSuccess ? launch_status() : -5;
 }
 
@@ -1488,6 +1503,19 @@ int sageb200_glue_attention_step(const void *q, const void *k, const void *v, co
   if (splits != 1 && splits != 2 && splits != 4 && splits != 8 && splits != 16) return -1;
   return launch_attention(false, q, k, v, q_weight, k_weight, cos_table, sin_table, positions, k_cache, v_cache, out,
                           rows, q_heads, kv_heads, max_seq, splits, eps, 0, (sageb200::g_sageb200_pdl & 2) != 0, stream);
+}
+
+int sageb200_glue_attention_step_permuted(const void *q, const void *k, const void *v, const void *q_weight,
+                                          const void *k_weight, const void *cos_table, const void *sin_table,
+                                          const void *positions, void *k_cache, void *v_cache, void *out,
+                                          const void *out_index, int rows, int q_heads, int kv_heads, int head_dim,
+                                          int max_seq, int splits, float eps, void *stream) {
+  if (head_dim != 128 || kv_heads < 1 || q_heads % kv_heads || max_seq < 1 || rows < 1) return -1;
+  if (splits != 1 && splits != 2 && splits != 4 && splits != 8 && splits != 16) return -1;
+  if (reinterpret_cast<uintptr_t>(out_index) & 3) return -1;
+  return launch_attention(false, q, k, v, q_weight, k_weight, cos_table, sin_table, positions, k_cache, v_cache, out,
+                          rows, q_heads, kv_heads, max_seq, splits, eps, 0, (sageb200::g_sageb200_pdl & 2) != 0, stream,
+                          out_index);
 }
 
 int sageb200_glue_prefill_attention(const void *q, const void *k_cache, const void *v_cache,

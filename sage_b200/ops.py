@@ -77,6 +77,28 @@ def sage_forward(
     out_features: int,
 ) -> torch.Tensor:
     """The native entry point's Python twin (reference csrc/bindings.cpp:8-79)."""
+    return _forward(x, packed_codes, radius_codes, radius_grid, codebook, permutation, out_features, None)
+
+
+def sage_forward_scratch(
+    x: torch.Tensor,
+    packed_codes: torch.Tensor,
+    radius_codes: torch.Tensor,
+    radius_grid: torch.Tensor,
+    codebook: torch.Tensor,
+    permutation: torch.Tensor,
+    out_features: int,
+    scratch: torch.Tensor,
+) -> torch.Tensor:
+    """`sage_forward` with scratch memory the caller owns: a zero-filled uint8 tensor on x's device of
+    at least `sageb200_workspace_bytes(rows, out_features, K)` bytes, 256-byte aligned, used by one
+    stream at a time (the kernels leave its arrival counters at zero).  A caller that runs many
+    linears on a stream of its own - a decode step being captured in a CUDA graph - thereby avoids
+    the temporary and its fill kernel that `sage_forward` takes on any stream but the default one."""
+    return _forward(x, packed_codes, radius_codes, radius_grid, codebook, permutation, out_features, scratch)
+
+
+def _forward(x, packed_codes, radius_codes, radius_grid, codebook, permutation, out_features, scratch):
     k = _check_layout(x, packed_codes, radius_codes, radius_grid, codebook, permutation, out_features)
     output = torch.empty((*x.shape[:-1], out_features), dtype=x.dtype, device=x.device)
     rows = x.numel() // k
@@ -89,7 +111,11 @@ def sage_forward(
         stream = torch.cuda.current_stream(x.device).cuda_stream
         nbytes = lib.sageb200_workspace_bytes(rows, out_features, k)
         workspace = None
-        if nbytes and stream == 0:
+        if nbytes and scratch is not None:
+            if scratch.device != x.device or scratch.dtype != torch.uint8 or scratch.numel() < nbytes:
+                raise RuntimeError(f"SAGE scratch must be a uint8 tensor of at least {nbytes} bytes on the input device")
+            workspace = scratch
+        elif nbytes and stream == 0:
             workspace = _workspace(x.device, stream, nbytes)  # the default stream's cached scratch
         elif nbytes:
             # Any other stream may be one that is being captured, or the private stream of a

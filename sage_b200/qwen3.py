@@ -23,7 +23,7 @@ import math
 import torch
 
 from . import _lib
-from .ops import sage_dequantize, sage_forward, sage_grouped
+from .ops import sage_dequantize, sage_forward_scratch, sage_grouped
 from .experts import SAGEExperts, dispatch_combine, expert_slice, route, synthetic_expert_stack
 from .parallel import (block_permutation, fold_input_permutation, shard_columns, shard_rows, shard_rows_global,
                        shard_vocab)
@@ -253,6 +253,16 @@ class PackedQwen3:
             layer["k_norm"] = norm_weight(c.head_dim)
             layer["k_cache"] = torch.zeros(batch, self.kv_heads, max_seq, c.head_dim, **half)
             layer["v_cache"] = torch.zeros(batch, self.kv_heads, max_seq, c.head_dim, **half)
+            # several sequences per step: the attention kernel writes its rows through the inverse of
+            # o_proj's permutation, i.e. in o_proj's quantised channel order, and o_proj is then called
+            # without a permutation (no staging launch in front of it)
+            layer["o_inverse"] = None
+            if batch > 1 and not self.dense and not self.global_permutations:
+                perm = layer["o"].packed["permutation"]
+                if perm.numel() == q_out // world:
+                    inverse = torch.empty_like(perm)
+                    inverse[perm.long()] = torch.arange(perm.numel(), dtype=perm.dtype, device=perm.device)
+                    layer["o_inverse"] = inverse
             self.layers.append(layer)
         # rotary tables, computed in FP32 and rounded to FP16 as the HF module does
         inv_freq = 1.0 / (c.rope_theta ** (torch.arange(0, c.head_dim, 2, device=self.device).float() / c.head_dim))
@@ -267,6 +277,8 @@ class PackedQwen3:
         self.h = torch.zeros(batch, c.hidden, **half)
         self.h_other = torch.zeros(batch, c.hidden, **half)  # residual ping-pong for fused norms
         self.fuse = True
+        self.scratch = None  # zero-filled scratch of the packed linears above 16 rows (see _packed_rows)
+        self.retired_scratch = []
         self.x = torch.zeros(batch, c.hidden, **half)
         self.attn = torch.zeros(batch, q_out // world, **half)
         self.attn_all = torch.zeros(world, batch, q_out // world, **half) if self.global_permutations else None
@@ -401,6 +413,13 @@ class PackedQwen3:
         c, lib, b = self.config, self.lib, self.batch
         s = self._stream()
         q, k, v = self._norm_linears(layer, ("q", "k", "v"), delta, layer["input_norm"])
+        if self.fuse_glue and layer["o_inverse"] is not None:
+            self._check(lib.sageb200_glue_attention_step_permuted(
+                _vp(q), _vp(k), _vp(v), _vp(layer["q_norm"]), _vp(layer["k_norm"]), _vp(self.cos), _vp(self.sin),
+                _vp(self.positions), _vp(layer["k_cache"]), _vp(layer["v_cache"]), _vp(self.attn),
+                _vp(layer["o_inverse"]), b, self.heads, self.kv_heads, c.head_dim, self.max_seq, self.step_splits,
+                c.eps, s), "attention_step_permuted")
+            return self._after_attention(layer, pregathered=True)
         if self.fuse_glue:
             self._check(lib.sageb200_glue_attention_step(
                 _vp(q), _vp(k), _vp(v), _vp(layer["q_norm"]), _vp(layer["k_norm"]), _vp(self.cos), _vp(self.sin),
@@ -418,7 +437,7 @@ class PackedQwen3:
             "attention_decode")
         return self._after_attention(layer)
 
-    def _after_attention(self, layer):
+    def _after_attention(self, layer, pregathered=False):
         c, lib, b = self.config, self.lib, self.batch
         s = self._stream()
         attn = self.attn
@@ -429,7 +448,10 @@ class PackedQwen3:
 
             dist.all_gather_into_tensor(self.attn_all, self.attn, group=self.tp_group)
             attn = self.attn_all.permute(1, 0, 2).reshape(b, -1).index_select(-1, layer["o_index"])
-        (o,) = self._linears(layer, ("o",), attn)
+        if pregathered:  # (the rows already lie in o_proj's quantised channel order)
+            o = self._pregathered(layer["o"], attn)
+        else:
+            (o,) = self._linears(layer, ("o",), attn)
         self._all_reduce(o)
         if c.experts:
             return self._moe(layer, o)
@@ -662,11 +684,26 @@ class PackedQwen3:
             self.tokens.copy_(prompt[:, length - 1])
             self.graph.replay()
 
+    def _packed_rows(self, linear, x, permutation):
+        """One packed linear on rows `x`, with scratch memory the model owns (zero-filled, grown by the
+        eager warm-up that precedes every capture), so that a captured step holds no temporary and
+        no fill kernel per call."""
+        p = linear.packed
+        rows = x.numel() // x.shape[-1]
+        if rows <= 16:  # (the grouped entry keeps its own scratch per stream)
+            return sage_grouped([(x, p["packed_codes"], p["radius_codes"], p["radius_grid"], p["codebook"],
+                                  permutation)], [linear.n])[0]
+        nbytes = self.lib.sageb200_workspace_bytes(rows, linear.n, x.shape[-1])
+        if self.scratch is None or self.scratch.numel() < nbytes:
+            if self.scratch is not None:  # (a captured graph may still point at the smaller one)
+                self.retired_scratch.append(self.scratch)
+            self.scratch = torch.zeros(max(nbytes, 1 << 20), dtype=torch.uint8, device=self.device)
+        return sage_forward_scratch(x, p["packed_codes"], p["radius_codes"], p["radius_grid"], p["codebook"],
+                                    permutation, linear.n, self.scratch)
+
     def _pregathered(self, linear, xq):
         """A packed linear on activations that already lie in its quantised channel order."""
-        p = linear.packed
-        return sage_forward(xq, p["packed_codes"], p["radius_codes"], p["radius_grid"], p["codebook"],
-                            p["permutation"][:0], linear.n)
+        return self._packed_rows(linear, xq, linear.packed["permutation"][:0])
 
     def _norm_rows_linears(self, layer, names, h, delta, weight, rows):
         """Prompt rows: h += delta, x = rmsnorm(h) * weight, then the packed linears `names` on x.  The
@@ -706,7 +743,7 @@ class PackedQwen3:
     def _rows_linears(self, layer, names, x):
         if self.dense:
             return [torch.nn.functional.linear(x, layer[name].weight) for name in names]
-        return [sage_forward(*layer[name].problem(x), layer[name].n) for name in names]
+        return [self._packed_rows(layer[name], x, layer[name].packed["permutation"]) for name in names]
 
     def _prefill_batched(self, prompt: torch.Tensor):
         if self.tp_world > 1 or self.ep_world > 1 or self.config.experts:

@@ -157,6 +157,25 @@ def test_generate_is_repeatable_and_batched():
         assert same >= 8, (row, same)
 
 
+@pytest.mark.parametrize("batch", [3, 16, 24])
+def test_attention_rows_in_o_proj_order_change_nothing(batch):
+    """Several sequences per step: the attention kernel writes its rows in o_proj's quantised
+    channel order and o_proj runs without a permutation.  Against the same model with the plain
+    attention output and o_proj's own staging: same tokens and logits, bit for bit."""
+    config = Qwen3Config(layers=2, hidden=512, heads=4, kv_heads=2, intermediate=1024, vocab=2048)
+    prompt = torch.randint(3, config.vocab, (batch, 7), generator=torch.Generator().manual_seed(batch))
+    model = PackedQwen3(config, "cuda:0", seed=9, max_seq=48, batch=batch, max_new=12)
+    assert all(layer["o_inverse"] is not None for layer in model.layers)
+    got_tokens = model.generate(prompt, 10)
+    got_logits = model.logits.clone()
+    plain = PackedQwen3(config, "cuda:0", seed=9, max_seq=48, batch=batch, max_new=12)
+    for layer in plain.layers:
+        layer["o_inverse"] = None
+    want_tokens = plain.generate(prompt, 10)
+    assert torch.equal(got_tokens, want_tokens)
+    assert torch.equal(got_logits, plain.logits)
+
+
 @pytest.mark.parametrize("length", [5, 48])
 def test_batched_prefill_matches_token_by_token(length):
     """The prompt through every layer at once (tensor-core GEMM path from 33 rows up, causal
@@ -586,6 +605,21 @@ def test_single_launch_attention_matches_the_three_kernels(q_heads, kv_heads, sp
         valid = (positions < max_seq).cpu()  # beyond the cache q is not normalised by the old kernels
         assert torch.allclose(out_a[valid].float(), out_b[valid].float(), rtol=2e-3, atol=1e-3)
         assert torch.isfinite(out_b.float()).all()
+    # the same launch writing each row through an index (the consumer's channel order): the plain
+    # output with its columns moved, bit for bit, and the same cache
+    width = q_heads * 128
+    permutation = torch.randperm(width, generator=gen).to(torch.int32).to(device)
+    inverse = torch.empty_like(permutation)
+    inverse[permutation.long()] = torch.arange(width, dtype=torch.int32, device=device)
+    k_cache_c, v_cache_c = k_cache.clone(), v_cache.clone()
+    out_c = torch.zeros_like(out_a)
+    assert lib.sageb200_glue_attention_step_permuted(
+        _vp(q), _vp(k), _vp(v), _vp(q_weight), _vp(k_weight), _vp(cos), _vp(sin), _vp(positions),
+        _vp(k_cache_c), _vp(v_cache_c), _vp(out_c), _vp(inverse), rows, q_heads, kv_heads, 128, max_seq, splits,
+        1e-6, stream) == 0
+    torch.cuda.synchronize()
+    assert torch.equal(out_c, out_b[:, permutation.long()])
+    assert torch.equal(k_cache_c, k_cache_b) and torch.equal(v_cache_c, v_cache_b)
 
 
 @pytest.mark.parametrize("rows", [1, 3, 16])
