@@ -131,7 +131,7 @@ int sageb200_glue_argmax_advance(const void *logits, void *tokens, void *positio
  * The tail of a decode step in ONE launch: x = rmsnorm(residual + delta) * norm_weight (the
  * arithmetic of sageb200_glue_add_rmsnorm; `residual` itself is not updated, `delta` may be
  * NULL), logits = x . head^T, then what sageb200_glue_argmax_advance does.  `scratch` holds
- * sageb200_glue_lm_head_step_scratch_bytes() bytes whose first 256 (an arrival counter) must
+ * sageb200_glue_lm_head_step_scratch_bytes() bytes whose first 256 (arrival and ticket counters) must
  * be zero before the first call; every call leaves them zero.
  */
 size_t sageb200_glue_lm_head_step_scratch_bytes(int rows, int sm_count);

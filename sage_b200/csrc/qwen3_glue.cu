@@ -829,28 +829,102 @@ __global__ void __launch_bounds__(kHeadWarps * 32)
   if (blocked)
     for (int e = rows * hidden + threadIdx.x; e < kColumnBlocks * 8 * hidden; e += kNormThreads)
       x_shared[head_x_index(e / hidden, e % hidden, kColumnBlocks)] = __float2half_rn(0.0f);  // unused sequences
-  for (int m = 0; m < rows; ++m) {
-    const __half *r = residual + static_cast<size_t>(m) * hidden;
-    const __half *d = delta ? delta + static_cast<size_t>(m) * hidden : nullptr;
-    float square = 0.0f;
-    for (int i = threadIdx.x; i < hidden; i += kNormThreads) {
-      __half v = r[i];
-      if (d) v = __hadd(v, d[i]);
-      x_shared[at(m, i)] = v;
-      const float f = __half2float(v);
-      square += f * f;
+  const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
+  const bool wide = ((reinterpret_cast<uintptr_t>(residual) | reinterpret_cast<uintptr_t>(delta) |
+                      reinterpret_cast<uintptr_t>(norm_weight) | reinterpret_cast<uintptr_t>(x_out)) & 15) == 0;
+  if (kRows > 1 && blocked && wide) {
+    // Several sequences: all rows at once instead of one row after the other (every CTA does this,
+    // so a serial pass per row - a trip to L2, two barriers - times the rows sat in front of the
+    // whole head).  1. residual + delta of every row with 16-byte loads, none depending on another;
+    // 2. each row's squares summed by thread and element exactly as the scalar loop does, out of
+    // shared memory, and the block sums in block_sum's order; 3. scaling and weights, eight values
+    // at a time.  Bit-identical to the loop below.
+    __shared__ float row_sums[kRows][kHeadWarps];
+    __shared__ float row_scale[kRows];
+    const int vectors = hidden >> 3;
+    const int total_vectors = rows * vectors;
+    const uint4 *residual4 = reinterpret_cast<const uint4 *>(residual);
+    const uint4 *delta4 = reinterpret_cast<const uint4 *>(delta);
+    for (int base = 0; base < total_vectors; base += 4 * kNormThreads) {
+      uint4 rv[4], dv[4];
+#pragma unroll
+      for (int u = 0; u < 4; ++u) {
+        const int e = base + threadIdx.x + u * kNormThreads;
+        if (e < total_vectors) {
+          rv[u] = residual4[e];
+          if (delta4) dv[u] = delta4[e];
+        }
+      }
+#pragma unroll
+      for (int u = 0; u < 4; ++u) {
+        const int e = base + threadIdx.x + u * kNormThreads;
+        if (e >= total_vectors) break;
+        if (delta4) {
+          __half2 *a = reinterpret_cast<__half2 *>(&rv[u]);
+          const __half2 *b = reinterpret_cast<const __half2 *>(&dv[u]);
+#pragma unroll
+          for (int c = 0; c < 4; ++c) a[c] = __hadd2(a[c], b[c]);
+        }
+        const int m = e / vectors;
+        *reinterpret_cast<uint4 *>(x_shared + at(m, (e - m * vectors) * 8)) = rv[u];
+      }
     }
-    const float total = block_sum(square, scratch);
-    const float scale = rsqrtf(total / hidden + eps);
-    for (int i = threadIdx.x; i < hidden; i += kNormThreads) {
-      const __half normed = __float2half_rn(__half2float(x_shared[at(m, i)]) * scale);
-      const __half value = __hmul(norm_weight[i], normed);
-      x_shared[at(m, i)] = value;
-      if (blockIdx.x == 0) x_out[static_cast<size_t>(m) * hidden + i] = value;
+    __syncthreads();
+    float square[kRows];
+#pragma unroll
+    for (int m = 0; m < kRows; ++m) {
+      square[m] = 0.0f;
+      if (m < rows) {
+        for (int i = threadIdx.x; i < hidden; i += kNormThreads) {
+          const float f = __half2float(x_shared[at(m, i)]);
+          square[m] += f * f;
+        }
+        square[m] = warp_sum(square[m]);
+        if (lane == 0) row_sums[m][warp] = square[m];
+      }
+    }
+    __syncthreads();
+    if (threadIdx.x < rows) {
+      float total = 0.0f;
+      for (int w = 0; w < kHeadWarps; ++w) total += row_sums[threadIdx.x][w];
+      row_scale[threadIdx.x] = rsqrtf(total / hidden + eps);
+    }
+    __syncthreads();
+    for (int e = threadIdx.x; e < total_vectors; e += kNormThreads) {
+      const int m = e / vectors, i = (e - m * vectors) * 8;
+      const float scale = row_scale[m];
+      uint4 value = *reinterpret_cast<const uint4 *>(x_shared + at(m, i));
+      const uint4 weight4 = *reinterpret_cast<const uint4 *>(norm_weight + i);
+      __half *v = reinterpret_cast<__half *>(&value);
+      const __half *w = reinterpret_cast<const __half *>(&weight4);
+#pragma unroll
+      for (int c = 0; c < 8; ++c) v[c] = __hmul(w[c], __float2half_rn(__half2float(v[c]) * scale));
+      *reinterpret_cast<uint4 *>(x_shared + at(m, i)) = value;
+      if (blockIdx.x == 0) *reinterpret_cast<uint4 *>(x_out + static_cast<size_t>(m) * hidden + i) = value;
+    }
+  } else {
+    for (int m = 0; m < rows; ++m) {
+      const __half *r = residual + static_cast<size_t>(m) * hidden;
+      const __half *d = delta ? delta + static_cast<size_t>(m) * hidden : nullptr;
+      float square = 0.0f;
+      for (int i = threadIdx.x; i < hidden; i += kNormThreads) {
+        __half v = r[i];
+        if (d) v = __hadd(v, d[i]);
+        x_shared[at(m, i)] = v;
+        const float f = __half2float(v);
+        square += f * f;
+      }
+      const float total = block_sum(square, scratch);
+      const float scale = rsqrtf(total / hidden + eps);
+      for (int i = threadIdx.x; i < hidden; i += kNormThreads) {
+        const __half normed = __float2half_rn(__half2float(x_shared[at(m, i)]) * scale);
+        const __half value = __hmul(norm_weight[i], normed);
+        x_shared[at(m, i)] = value;
+        if (blockIdx.x == 0) x_out[static_cast<size_t>(m) * hidden + i] = value;
+      }
     }
   }
   __syncthreads();
-  const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
   if (blocked) {
     // ---- tensor-core path: 16 vocabulary rows per warp and step, best (value, index) per sequence
     const int g = lane >> 2, t = lane & 3;
@@ -861,13 +935,25 @@ __global__ void __launch_bounds__(kHeadWarps * 32)
       slot_value[q] = -INFINITY;
       slot_index[q] = 0x7fffffff;
     }
-    for (int v0 = (blockIdx.x * kHeadWarps + warp) * 16; v0 < vocab; v0 += gridDim.x * kHeadWarps * 16) {
+    // The warps take 16-row tiles of the vocabulary in turn off a ticket counter (the word behind
+    // the arrival counter; the last CTA zeroes both): the grid is one resident wave, and a static
+    // split of ~2.7 tiles per warp would leave a third of the warps idle for the last pass.  The
+    // next ticket is requested before the current tile is computed.  Which warp computes a tile
+    // changes nothing in the logits, and the argmax does not depend on the order (lowest index on
+    // ties).
+    const int tiles = (vocab + 15) / 16;
+    unsigned ticket = lane == 0 ? atomicAdd(counter + 1, 1u) : 0u;
+    for (;;) {
+      const int tile = static_cast<int>(__shfl_sync(0xffffffffu, ticket, 0));
+      if (tile >= tiles) break;
+      if (lane == 0) ticket = atomicAdd(counter + 1, 1u);
+      const int v0 = tile * 16;
       float acc[kColumnBlocks][4];
       head_rows_mma<kColumnBlocks>(head, x_shared, v0, vocab, hidden, lane, acc);
 #pragma unroll
       for (int nb = 0; nb < kColumnBlocks; ++nb)
 #pragma unroll
-        for (int e = 0; e < 4; ++e) {  // (e = 0, 1: row v0 + g; e = 2, 3: row v0 + g + 8: increasing index per slot)
+        for (int e = 0; e < 4; ++e) {  // (e = 0, 1: row v0 + g; e = 2, 3: row v0 + g + 8)
           const int v = v0 + g + 8 * (e >> 1), m = nb * 8 + 2 * t + (e & 1);
           if (v < vocab && m < rows) {
             const __half rounded = __float2half_rn(acc[nb][e]);
@@ -1014,7 +1100,8 @@ __global__ void __launch_bounds__(kHeadWarps * 32)
   }
   if (threadIdx.x == 0) {
     if (step) step[0] += 1;
-    *counter = 0u;  // zero again for the next launch
+    counter[0] = 0u;  // zero again for the next launch: arrivals and tile tickets
+    counter[1] = 0u;
   }
 }
 
@@ -1632,7 +1719,16 @@ int sageb200_glue_lm_head_step(const void *head, const void *residual, const voi
   if (shared > 40 * 1024 &&
       cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, 200 * 1024) != cudaSuccess)
     return -5;
-  const int blocks = (sm_count > 0 ? sm_count : 148) * 4;
+  int blocks = (sm_count > 0 ? sm_count : 148) * 4;
+  if (rows > 1 && hidden % 32 == 0) {
+    // several sequences (tiles handed out by ticket): exactly the CTAs that are resident at once
+    int per_sm = 0;
+    if (cudaOccupancyMaxActiveBlocksPerMultiprocessor(&per_sm, kernel, kHeadWarps * 32, shared) != cudaSuccess) {
+      cudaGetLastError();
+      per_sm = 0;
+    }
+    if (per_sm >= 1 && per_sm < 4) blocks = (sm_count > 0 ? sm_count : 148) * per_sm;
+  }
   sageb200::launch_dependent<2>(
       kernel, blocks, kHeadWarps * 32, shared, static_cast<cudaStream_t>(stream),
       static_cast<const __half *>(head), static_cast<const __half *>(residual),
