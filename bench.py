@@ -1090,6 +1090,45 @@ def run_prompt(args) -> None:
     }), flush=True)
 
 
+def run_decode_batch(args) -> None:
+    """`--workload decode_batch` with `--batch N` (2..64): N sequences of Qwen3-4B decoded together
+    after `--prompt`-token prompts, one CUDA graph per step, timed with CUDA events over `--steps`
+    steps after `--warmup`.  One more step runs between cudaProfilerStart/Stop, so a profiler
+    started with its capture off records exactly one step."""
+    import torch
+
+    from sage_b200.qwen3 import QWEN3_4B, PackedQwen3
+
+    device = torch.device("cuda", 0)
+    batch = args.batch
+    model = PackedQwen3(QWEN3_4B, device, seed=0, max_seq=args.prompt + args.steps + args.warmup + 8, batch=batch,
+                        max_new=args.steps + args.warmup + 8)
+    model.capture()
+    model.prefill(torch.randint(3, QWEN3_4B.vocab, (batch, args.prompt), generator=torch.Generator().manual_seed(5)))
+    lib = model.lib
+    for _ in range(max(args.warmup, 1)):
+        model.graph.replay()
+    start, stop = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    start.record()
+    for _ in range(args.steps):
+        model.graph.replay()
+    stop.record()
+    torch.cuda.synchronize(device)
+    ms = start.elapsed_time(stop) / args.steps
+    torch.cuda.profiler.start()
+    model.graph.replay()
+    torch.cuda.synchronize(device)
+    torch.cuda.profiler.stop()
+    print(json.dumps({
+        "metric": "qwen3_4b_sage_2.25bpw_batched_decode_tok_s", "value": batch * 1000.0 / ms, "unit": "tok/s",
+        "higher_is_better": True, "batch": batch, "ms_per_step": ms, "steps": args.steps, "warmup": args.warmup,
+        "prompt_tokens": args.prompt,
+        "kernels_per_step": {"sage_linear": model.sage_launches_per_step, "glue": model.glue_launches_per_step},
+        "config": {"workload": f"Qwen3-4B, {batch} sequences decoded together after {args.prompt}-token prompts, "
+                               "one CUDA graph per step"},
+    }), flush=True)
+
+
 def run_gemm_roles(args) -> None:
     """`--workload gemm_roles:K:N:M` (profiling build of the library only: SAGEB200_LIBRARY =
     libsage_b200_trace.so): one tcgen05 GEMM call with the per-role clock sums of its CTAs -
@@ -1260,7 +1299,7 @@ def main() -> None:
     parser.add_argument("--impl", choices=["ours", "reference"], default="ours")
     parser.add_argument("--workload", default="decode_model")
     parser.add_argument("--prompt", type=int, default=512)
-    parser.add_argument("--batch", type=int, default=1, help="sequences decoded together (tp32b / ep30b workloads)")
+    parser.add_argument("--batch", type=int, default=1, help="sequences decoded together (tp32b / ep30b / decode_batch workloads)")
     parser.add_argument("--output", default="reports", help="folder for the files of --workload report")
     parser.add_argument("--quick", action="store_true",
                         help="headline measurement only: skip the per-kernel, batch-8 and sharded sub-records")
@@ -1277,6 +1316,8 @@ def main() -> None:
         run_mega_phases(args)
     elif args.workload == "prompt":
         run_prompt(args)
+    elif args.workload == "decode_batch":
+        run_decode_batch(args)
     elif args.workload.startswith("sph:"):
         run_sph_linear(args)
     elif args.workload == "report":

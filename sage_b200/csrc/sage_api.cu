@@ -215,11 +215,33 @@ __global__ void __launch_bounds__(256) stage_rows_kernel(const __grid_constant__
   // (the decode kernel behind this launch sets up and prefetches its weights meanwhile; this
   //  launch itself was scheduled while its producer still ran)
   pdl_launch_dependents();
-  pdl_wait();
   StageJob job = params.job[blockIdx.y];
   const int row = blockIdx.x;
-  if (row >= job.rows) return;
   const int k = job.k;
+  // The permutation and the norm weights are never written by a kernel, and a decode step streams
+  // far more than the L2 holds, so they tend to come from HBM: each thread requests its first two
+  // 8-channel vectors of both before the wait for the producer, not at the point of use.
+  constexpr int kHeld = 2;
+  int4 held_lo[kHeld], held_hi[kHeld];
+  uint4 held_weight[kHeld];
+  const bool hold_perm = job.perm != nullptr && job.expert_ids == nullptr && row < job.rows &&
+                         (reinterpret_cast<uintptr_t>(job.perm) & 15) == 0;
+  const bool hold_weight = params.kind == 1 && row < job.rows && (reinterpret_cast<uintptr_t>(params.weight) & 15) == 0;
+#pragma unroll
+  for (int u = 0; u < kHeld; ++u) {
+    const int v = threadIdx.x + 256 * u;
+    held_lo[u] = held_hi[u] = make_int4(0, 0, 0, 0);
+    held_weight[u] = make_uint4(0, 0, 0, 0);
+    if (v < (k >> 3)) {
+      if (hold_perm) {
+        held_lo[u] = __ldg(reinterpret_cast<const int4 *>(job.perm) + 2 * v);
+        held_hi[u] = __ldg(reinterpret_cast<const int4 *>(job.perm) + 2 * v + 1);
+      }
+      if (hold_weight) held_weight[u] = __ldg(reinterpret_cast<const uint4 *>(params.weight) + v);
+    }
+  }
+  pdl_wait();
+  if (row >= job.rows) return;
   if (job.expert_ids) {
     const int expert = __ldg(job.expert_ids + job.expert_slot) - job.expert_first;
     if (expert < 0 || expert >= job.expert_count) return;
@@ -294,20 +316,36 @@ __global__ void __launch_bounds__(256) stage_rows_kernel(const __grid_constant__
     float total = 0.0f;
     for (int w = 0; w < 8; ++w) total += sums[w];
     const float scale = rsqrtf(total / k + params.eps);
-    for (int i = threadIdx.x; i < k; i += 256)
-      row_shared[i] = __hmul(params.weight[i], __float2half_rn(__half2float(row_shared[i]) * scale));
+    if (hold_weight) {  // eight values at a time, the same arithmetic per value
+      auto scale_vector = [&](int v, const uint4 &weight4) {
+        uint4 value = reinterpret_cast<const uint4 *>(row_shared)[v];
+        __half *h = reinterpret_cast<__half *>(&value);
+        const __half *w = reinterpret_cast<const __half *>(&weight4);
+#pragma unroll
+        for (int c = 0; c < 8; ++c) h[c] = __hmul(w[c], __float2half_rn(__half2float(h[c]) * scale));
+        reinterpret_cast<uint4 *>(row_shared)[v] = value;
+      };
+#pragma unroll
+      for (int u = 0; u < kHeld; ++u)
+        if (threadIdx.x + 256 * u < vectors) scale_vector(threadIdx.x + 256 * u, held_weight[u]);
+      for (int v = threadIdx.x + 256 * kHeld; v < vectors; v += 256)
+        scale_vector(v, __ldg(reinterpret_cast<const uint4 *>(params.weight) + v));
+    } else {
+      for (int i = threadIdx.x; i < k; i += 256)
+        row_shared[i] = __hmul(params.weight[i], __float2half_rn(__half2float(row_shared[i]) * scale));
+    }
   }
   __syncthreads();
   const bool aligned = job.perm == nullptr || (reinterpret_cast<uintptr_t>(job.perm) & 15) == 0;
-  for (int v = threadIdx.x; v < (k >> 3); v += 256) {
+  auto write_vector = [&](int v, bool held, const int4 &held_low, const int4 &held_high) {
     __align__(16) __half out[8];
     if (job.perm == nullptr) {
       *reinterpret_cast<uint4 *>(out) = reinterpret_cast<const uint4 *>(row_shared)[v];
     } else {
       int source[8];
       if (aligned) {
-        const int4 lo = __ldg(reinterpret_cast<const int4 *>(job.perm) + 2 * v);
-        const int4 hi = __ldg(reinterpret_cast<const int4 *>(job.perm) + 2 * v + 1);
+        const int4 lo = held ? held_low : __ldg(reinterpret_cast<const int4 *>(job.perm) + 2 * v);
+        const int4 hi = held ? held_high : __ldg(reinterpret_cast<const int4 *>(job.perm) + 2 * v + 1);
         source[0] = lo.x; source[1] = lo.y; source[2] = lo.z; source[3] = lo.w;
         source[4] = hi.x; source[5] = hi.y; source[6] = hi.z; source[7] = hi.w;
       } else {
@@ -318,7 +356,11 @@ __global__ void __launch_bounds__(256) stage_rows_kernel(const __grid_constant__
       for (int c = 0; c < 8; ++c) out[c] = row_shared[source[c]];
     }
     reinterpret_cast<uint4 *>(job.xq + offset)[v] = *reinterpret_cast<const uint4 *>(out);
-  }
+  };
+#pragma unroll
+  for (int u = 0; u < kHeld; ++u)
+    if (threadIdx.x + 256 * u < (k >> 3)) write_vector(threadIdx.x + 256 * u, hold_perm, held_lo[u], held_hi[u]);
+  for (int v = threadIdx.x + 256 * kHeld; v < (k >> 3); v += 256) write_vector(v, false, held_lo[0], held_hi[0]);
 }
 
 cudaError_t configure_stage_rows() {
