@@ -25,8 +25,9 @@ int sageb200_debug_plan(int rows, int n, int k, int sm_count, int act_kind, int 
  * Programmatic dependent launch (on by default): the decode kernel and the decode glue are
  * launched so that they may be scheduled before the previous kernel of the stream has
  * finished; they prefetch packed weights and codebooks, then wait for the previous kernel
- * before reading activations or writing anything.  0 switches to plain launches (debug).
- * No counterpart in the reference.
+ * before reading activations or writing anything.  `enabled` is a bit mask: 1 the packed-linear
+ * kernels, 2 every decode glue kernel, 4 the attention step alone (default 5); 0 switches to plain
+ * launches (debug).  No counterpart in the reference.
  */
 int sageb200_set_pdl(int enabled);
 

@@ -78,6 +78,9 @@ int sageb200_glue_attention_decode(const void *q, const void *k_cache, const voi
  * co-schedule that many - 16; -1 otherwise) that combine their
  * partial results through distributed shared memory: no scratch.  Same FP32 arithmetic as
  * sageb200_glue_attention_decode, summed in another order.
+ * The kernel is launched as a programmatic dependent and reads cache rows below `positions`
+ * before it waits for the previous kernel of the stream: that kernel may produce q, k and v (as
+ * the q/k/v projection does) but must not be the one that wrote those cache rows.
  */
 int sageb200_glue_attention_step(const void *q, const void *k, const void *v, const void *q_weight,
                                  const void *k_weight, const void *cos_table, const void *sin_table,

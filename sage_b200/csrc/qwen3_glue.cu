@@ -410,8 +410,10 @@ __device__ __forceinline__ void unpack16(const uint4 &a, const uint4 &b, float o
   }
 }
 
+// (one or two heads per CTA: at most 128 registers, so that two CTAs fit an SM and the clusters of a
+//  step always find room at once - with 142 the one-sequence step was measured 8 % slower)
 template <int kStepHeads, bool kExact, bool kPrompt, bool kIndexed = false>
-__global__ void __launch_bounds__(kAttnWarps * 32)
+__global__ void __launch_bounds__(kAttnWarps * 32, kStepHeads <= 2 ? 2 : 0)
     attention_step_kernel(const __half *__restrict__ q, const __half *__restrict__ k,
                           const __half *__restrict__ v, const __half *__restrict__ q_weight,
                           const __half *__restrict__ k_weight, const __half *__restrict__ cos_table,
@@ -420,7 +422,9 @@ __global__ void __launch_bounds__(kAttnWarps * 32)
                           int kv_heads, int max_seq, float eps, float scale, int rows_per_sequence,
                           const int *__restrict__ out_index) {
   sageb200::pdl_launch_dependents();
-  sageb200::pdl_wait();
+  // Prompt rows read a cache the previous kernel filled: wait at once.  A decode step waits
+  // further down, after it has requested its first cache rows (written by earlier steps).
+  if (kPrompt) sageb200::pdl_wait();
 
   namespace cg = cooperative_groups;
   cg::cluster_group cluster = cg::this_cluster();
@@ -457,6 +461,27 @@ __global__ void __launch_bounds__(kAttnWarps * 32)
   __half *k_base = k_cache + (static_cast<size_t>(sequence) * kv_heads + kv) * max_seq * 128;
   __half *v_base = v_cache + (static_cast<size_t>(sequence) * kv_heads + kv) * max_seq * 128;
 
+  // A warp takes four consecutive positions at a time: lanes 8s..8s+7 share position s and hold
+  // 16 dims each (dims 16*piece .. 16*piece+15), so a dot product needs three shuffles.
+  const int sub = lane >> 3, piece = lane & 7;
+  // Decode step: the warp's first four cache rows are requested now, before the wait for the
+  // kernel that produced q, k and v - earlier steps wrote them (the position being appended is
+  // patched in from shared memory below) - so their trip to memory overlaps the producer's tail.
+  uint4 k0, k1, v0, v1;
+  k0 = k1 = v0 = v1 = make_uint4(0, 0, 0, 0);
+  if (!kPrompt) {
+    const int p = begin + warp * 4 + sub;
+    if (p < end) {
+      const uint4 *k_row = reinterpret_cast<const uint4 *>(k_base + static_cast<size_t>(p) * 128);
+      const uint4 *v_row = reinterpret_cast<const uint4 *>(v_base + static_cast<size_t>(p) * 128);
+      k0 = k_row[2 * piece];
+      k1 = k_row[2 * piece + 1];
+      v0 = v_row[2 * piece];
+      v1 = v_row[2 * piece + 1];
+    }
+    sageb200::pdl_wait();
+  }
+
   // items 0..heads-1: this CTA's query heads; item `heads`: the new token's key and value
   // (every part needs them, part 0 stores them)
   for (int item = warp; item < heads + (owns_new ? 1 : 0); item += kAttnWarps) {
@@ -487,9 +512,6 @@ __global__ void __launch_bounds__(kAttnWarps * 32)
   }
   __syncthreads();
 
-  // A warp takes four consecutive positions at a time: lanes 8s..8s+7 share position s and hold
-  // 16 dims each (dims 16*piece .. 16*piece+15), so a dot product needs three shuffles.
-  const int sub = lane >> 3, piece = lane & 7;
   float qf[kStepHeads][16];
 #pragma unroll
   for (int g = 0; g < kStepHeads; ++g) {
@@ -520,8 +542,9 @@ __global__ void __launch_bounds__(kAttnWarps * 32)
       v1 = v_row[2 * piece + 1];
     }
   };
-  uint4 k0, k1, v0, v1, next_k0, next_k1, next_v0, next_v1;
-  fetch(begin + warp * 4, k0, k1, v0, v1);
+  uint4 next_k0, next_k1, next_v0, next_v1;
+  if (kPrompt || (owns_new && begin + warp * 4 + sub == position))
+    fetch(begin + warp * 4, k0, k1, v0, v1);  // (decode: only the appended position, from shared memory)
   for (int base = begin + warp * 4; base < end; base += kAttnWarps * 4) {
     fetch(base + kAttnWarps * 4, next_k0, next_k1, next_v0, next_v1);
     const bool valid = base + sub < end;
@@ -1589,7 +1612,7 @@ int sageb200_glue_attention_step(const void *q, const void *k, const void *v, co
   if (head_dim != 128 || kv_heads < 1 || q_heads % kv_heads || max_seq < 1 || rows < 1) return -1;
   if (splits != 1 && splits != 2 && splits != 4 && splits != 8 && splits != 16) return -1;
   return launch_attention(false, q, k, v, q_weight, k_weight, cos_table, sin_table, positions, k_cache, v_cache, out,
-                          rows, q_heads, kv_heads, max_seq, splits, eps, 0, (sageb200::g_sageb200_pdl & 2) != 0, stream);
+                          rows, q_heads, kv_heads, max_seq, splits, eps, 0, (sageb200::g_sageb200_pdl & 6) != 0, stream);
 }
 
 int sageb200_glue_attention_step_permuted(const void *q, const void *k, const void *v, const void *q_weight,
@@ -1601,7 +1624,7 @@ int sageb200_glue_attention_step_permuted(const void *q, const void *k, const vo
   if (splits != 1 && splits != 2 && splits != 4 && splits != 8 && splits != 16) return -1;
   if (reinterpret_cast<uintptr_t>(out_index) & 3) return -1;
   return launch_attention(false, q, k, v, q_weight, k_weight, cos_table, sin_table, positions, k_cache, v_cache, out,
-                          rows, q_heads, kv_heads, max_seq, splits, eps, 0, (sageb200::g_sageb200_pdl & 2) != 0, stream,
+                          rows, q_heads, kv_heads, max_seq, splits, eps, 0, (sageb200::g_sageb200_pdl & 6) != 0, stream,
                           out_index);
 }
 

@@ -16,7 +16,10 @@
 #include "sage_kernels.h"
 
 namespace sageb200 {
-int g_sageb200_pdl = 1;  // packed-linear kernels only: measured slower with the glue included
+// bit 0: the packed-linear kernels; bit 1: every glue kernel (measured slower: most have nothing to
+// do before their wait); bit 2: the attention step alone, which requests its first cache rows
+// before the wait (measured +0.5 % on the one-sequence step)
+int g_sageb200_pdl = 5;
 unsigned long long g_sageb200_glue_launches = 0;
 namespace {
 
@@ -851,7 +854,7 @@ int sageb200_debug_gemm_pairs(int enabled) {
 }
 
 int sageb200_set_pdl(int enabled) {
-  g_sageb200_pdl = enabled & 3;
+  g_sageb200_pdl = enabled & 7;
   return SAGEB200_OK;
 }
 
