@@ -469,6 +469,13 @@ __global__ void __launch_bounds__(kAttnWarps * 32, kStepHeads <= 2 ? 2 : 0)
   // patched in from shared memory below) - so their trip to memory overlaps the producer's tail.
   uint4 k0, k1, v0, v1;
   k0 = k1 = v0 = v1 = make_uint4(0, 0, 0, 0);
+  // (the same for the output index of this thread's first output value: a constant of the model)
+  [[maybe_unused]] int first_target = 0;
+  if constexpr (kIndexed) {
+    const int items_all = heads * 128;
+    const int item = split * ((items_all + splits - 1) / splits) + static_cast<int>(threadIdx.x);
+    if (item < items_all) first_target = __ldg(out_index + (first_head + (item >> 7)) * 128 + (item & 127));
+  }
   if (!kPrompt) {
     const int p = begin + warp * 4 + sub;
     if (p < end) {
@@ -643,7 +650,8 @@ __global__ void __launch_bounds__(kAttnWarps * 32, kStepHeads <= 2 ? 2 : 0)
     // order, so the packed linear behind this kernel needs no gather of its own (a variant of its
     // own: the plain kernel keeps its registers and instruction stream)
     if constexpr (kIndexed) {
-      const int target = __ldg(out_index + (first_head + g) * 128 + dim);
+      const int target = local == static_cast<int>(threadIdx.x) ? first_target
+                                                                 : __ldg(out_index + (first_head + g) * 128 + dim);
       out[static_cast<size_t>(m) * q_heads * 128 + target] = __float2half_rn(value / total);
     } else {
       out[(static_cast<size_t>(m) * q_heads + first_head + g) * 128 + dim] = __float2half_rn(value / total);
