@@ -174,19 +174,47 @@ void cta_budgets(const sageb200_problem *problems, int count, const DeviceState 
 }
 
 // Scratch bytes (after the counter region) the problems need together.
+// `fits` (optional): whether the plans' shared-memory needs - the launch reserves the largest of
+// each kind over its problems - fit one launch together.
 size_t grouped_scratch_bytes(const sageb200_problem *problems, int count, const DeviceState &device,
-                             int act_kind = 0) {
+                             int act_kind = 0, bool *fits = nullptr) {
   int budgets[kMaxGrouped];
   cta_budgets(problems, count, device, budgets);
   size_t bytes = 0;
+  size_t x_bytes = 0, lin_bytes = 0;
+  int unit_capacity = 0, warps = 0, warp_segments = 0, column_blocks = 1;
+  bool ring = false;
   for (int i = 0; i < count; ++i) {
     const sageb200_problem &in = problems[i];
     if (in.rows == 0) continue;
     const SkinnyPlan plan =
         plan_skinny(in.rows, in.n, in.k, in.entries, device.sm_count, g_tuning, budgets[i], in.rows == 1 ? act_kind : 0);
     bytes += align256(plan.partial_bytes) + gather_bytes(in.rows, in.k, in.perm != nullptr || act_kind != 0);
+    if (plan.x_bytes > x_bytes) x_bytes = plan.x_bytes;
+    if (plan.lin_bytes > lin_bytes) lin_bytes = plan.lin_bytes;
+    if (plan.unit_capacity > unit_capacity) unit_capacity = plan.unit_capacity;
+    if (plan.warps > warps) warps = plan.warps;
+    if (plan.warp_segments > warp_segments) warp_segments = plan.warp_segments;
+    if (plan.column_blocks > column_blocks) column_blocks = plan.column_blocks;
+    ring = ring || plan.ring != 0;
   }
+  // (ring streaming exists for one column block only: a problem of up to eight rows that streams
+  //  cannot share a launch with one of more than eight rows)
+  if (fits)
+    *fits = skinny_shared_fits(x_bytes, unit_capacity, warps, warp_segments, column_blocks, lin_bytes) &&
+            !(ring && column_blocks != 1);
   return bytes;
+}
+
+// Problems whose plans do not fit one launch together run as two launches, first half and second
+// half, each planned for the whole device (and so on); the scratch is the larger need.
+size_t grouped_scratch_split(const sageb200_problem *problems, int count, const DeviceState &device) {
+  bool fits = true;
+  const size_t bytes = grouped_scratch_bytes(problems, count, device, 0, &fits);
+  if (fits || count <= 1) return bytes;
+  const size_t first = grouped_scratch_split(problems, count / 2, device);
+  const size_t second = grouped_scratch_split(problems + count / 2, count - count / 2, device);
+  return first > second ? first : second;
 }
 
 // Activation rows of a launch of several rows, for every problem in ONE launch: the row is
@@ -383,6 +411,19 @@ struct ExpertRef {
 int run_skinny(const sageb200_problem *problems, int count, void *workspace,
                size_t workspace_bytes, cudaStream_t stream, const DeviceState &device,
                const sageb200_activation *activation = nullptr, const ExpertRef *experts = nullptr) {
+  if (!activation && count > 1) {
+    // plans that do not fit one launch together (the launch reserves the largest share, tables and
+    // activation rows of any problem): two launches, as grouped_scratch_split sizes them
+    bool fits = true;
+    grouped_scratch_bytes(problems, count, device, 0, &fits);
+    if (!fits) {
+      const int half = count / 2;
+      const int status = run_skinny(problems, half, workspace, workspace_bytes, stream, device, nullptr, experts);
+      if (status) return status;
+      return run_skinny(problems + half, count - half, workspace, workspace_bytes, stream, device, nullptr,
+                        experts ? experts + half : nullptr);
+    }
+  }
   SkinnyParams params;
   std::memset(&params, 0, sizeof(params));
   params.status = device.status;
@@ -645,7 +686,7 @@ size_t grouped_workspace_bytes(const sageb200_problem *problems_host, int count,
   fallback.sm_count = 148;
   DeviceState *device = nullptr;
   if (device_state(&device) != SAGEB200_OK) device = &fallback;
-  const size_t bytes = grouped_scratch_bytes(problems_host, count, *device);
+  const size_t bytes = grouped_scratch_split(problems_host, count, *device);
   return bytes ? kCounterRegionBytes + bytes : 0;
 }
 }  // namespace

@@ -78,6 +78,10 @@ struct SkinnyPlan {
   size_t partial_bytes;
 };
 
+// Whether one launch can hold problems whose plans need these maxima of shared memory together.
+bool skinny_shared_fits(size_t x_bytes, int unit_capacity, int warps, int warp_segments, int column_blocks,
+                        size_t lin_bytes);
+
 struct Tuning {
   int warps, slices, ctas_per_sm, mode;  // mode: 0 auto, 1 even units, 2 whole tiles
 };

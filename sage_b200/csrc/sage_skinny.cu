@@ -910,6 +910,13 @@ SkinnyPlan plan_skinny(int rows, int n, int k, int entries, int sm_count, const 
   return plan;
 }
 
+bool skinny_shared_fits(size_t x_bytes, int unit_capacity, int warps, int warp_segments, int column_blocks,
+                        size_t lin_bytes) {
+  return x_bytes + static_cast<size_t>(unit_capacity) * kUnitBytes +
+             static_cast<size_t>(warps) * warp_segments * column_blocks * 512 + lin_bytes <=
+         static_cast<size_t>(kMaxDynamicShared);
+}
+
 cudaError_t configure_skinny() {
   cudaError_t status = configure_variant<1, false>();
   if (status == cudaSuccess) status = configure_variant<1, true>();

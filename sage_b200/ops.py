@@ -199,8 +199,12 @@ def sage_dequantize(
     return weight
 
 
-def sage_grouped(problems: list[tuple], out_features: list[int], activation: tuple | None = None) -> list[torch.Tensor]:
+def sage_grouped(problems: list[tuple], out_features: list[int], activation: tuple | None = None,
+                 outputs: list[torch.Tensor] | None = None) -> list[torch.Tensor]:
     """Several packed linears (rows <= 16 each) in one launch.
+
+    `outputs` (optional): contiguous FP16 tensors to write into, one per problem, instead of fresh
+    ones - e.g. row ranges of one tensor when the problems are row blocks of the same linear.
 
     `problems[i]` = (x, packed_codes, radius_codes, radius_grid, codebook, permutation).
     `activation` = (kind, eps, a, b, weight, residual_out) fuses the producer of the shared
@@ -211,12 +215,17 @@ def sage_grouped(problems: list[tuple], out_features: list[int], activation: tup
         raise RuntimeError("too many problems for one grouped launch")
     lib = _lib.load()
     array = (_lib.Problem * len(problems))()
-    outputs = []
+    given, outputs = outputs, []
     device = problems[0][0].device
     for i, ((x, codes, radii, grid, book, perm), n) in enumerate(zip(problems, out_features)):
         k = _check_layout(x, codes, radii, grid, book, perm, n)
         rows = x.numel() // k
-        y = torch.empty((*x.shape[:-1], n), dtype=x.dtype, device=x.device)
+        if given is None:
+            y = torch.empty((*x.shape[:-1], n), dtype=x.dtype, device=x.device)
+        else:
+            y = given[i]
+            if not (y.is_contiguous() and y.dtype == x.dtype and y.device == x.device and y.numel() == rows * n):
+                raise RuntimeError("SAGE grouped outputs must be contiguous FP16 tensors of rows x out_features")
         outputs.append(y)
         array[i] = _lib.Problem(
             x.data_ptr(), codes.data_ptr(), radii.data_ptr(), grid.data_ptr(), book.data_ptr(),

@@ -701,8 +701,29 @@ class PackedQwen3:
         return sage_forward_scratch(x, p["packed_codes"], p["radius_codes"], p["radius_grid"], p["codebook"],
                                     permutation, linear.n, self.scratch)
 
+    def _grouped_row_blocks(self, linears, x, permutations):
+        """17..32 rows: every linear as two row blocks of 9..16 rows, all blocks of all linears
+        in ONE grouped launch of the decode kernel (and one staging launch for their permutations)
+        instead of two launches and two staging launches per linear."""
+        rows = x.shape[0]
+        outs = [torch.empty(rows, linear.n, dtype=x.dtype, device=x.device) for linear in linears]
+        problems, widths, targets = [], [], []
+        for linear, permutation, out in zip(linears, permutations, outs):
+            p = linear.packed
+            half = (rows + 1) // 2  # (two blocks of the same kind: both above eight rows)
+            for first in range(0, rows, half):
+                block = slice(first, min(first + half, rows))
+                problems.append((x[block], p["packed_codes"], p["radius_codes"], p["radius_grid"], p["codebook"],
+                                 permutation))
+                widths.append(linear.n)
+                targets.append(out[block])
+        sage_grouped(problems, widths, outputs=targets)
+        return outs
+
     def _pregathered(self, linear, xq):
         """A packed linear on activations that already lie in its quantised channel order."""
+        if xq.dim() == 2 and 16 < xq.shape[0] <= 32:
+            return self._grouped_row_blocks([linear], xq, [linear.packed["permutation"][:0]])[0]
         return self._packed_rows(linear, xq, linear.packed["permutation"][:0])
 
     def _norm_rows_linears(self, layer, names, h, delta, weight, rows):
@@ -743,6 +764,9 @@ class PackedQwen3:
     def _rows_linears(self, layer, names, x):
         if self.dense:
             return [torch.nn.functional.linear(x, layer[name].weight) for name in names]
+        if x.dim() == 2 and 16 < x.shape[0] <= 32 and 2 * len(names) <= _lib.MAX_GROUPED:
+            linears = [layer[name] for name in names]
+            return self._grouped_row_blocks(linears, x, [linear.packed["permutation"] for linear in linears])
         return [self._packed_rows(layer[name], x, layer[name].packed["permutation"]) for name in names]
 
     def _prefill_batched(self, prompt: torch.Tensor):

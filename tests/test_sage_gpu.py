@@ -343,6 +343,36 @@ def test_grouped_launch_matches_oracle_and_is_repeatable():
             assert ((many.float() - single.float()).norm() / single.float().norm()).item() < 1e-3
 
 
+@pytest.mark.parametrize("blocks", [(16, 8), (12, 12), (16, 16), (9, 8)])
+def test_grouped_launch_of_row_blocks_with_given_outputs(blocks):
+    """Row blocks of several linears in one grouped launch, written into row ranges of one output
+    tensor per linear (`outputs=`).  Blocks of more than eight rows next to blocks of at most eight
+    need different kernel shapes; the library then runs the group as two launches instead of
+    failing.  Every output passes the oracle gate."""
+    k = 2560
+    shapes = [(4096, 0), (1024, 1), (1024, 2)]
+    rows = sum(blocks)
+    x = torch.randn(rows, k, generator=torch.Generator().manual_seed(rows), dtype=torch.float16).cuda()
+    cpus = [synthetic_sage(k, n, seed=s) for n, s in shapes]
+    layers = [SAGELinear(to_cuda(cpu), n) for cpu, (n, _) in zip(cpus, shapes)]
+    outs = [torch.full((rows, n), float("nan"), dtype=torch.float16, device="cuda") for n, _ in shapes]
+    problems, widths, targets = [], [], []
+    for layer, (n, _), out in zip(layers, shapes, outs):
+        first = 0
+        for count in blocks:
+            problems.append((x[first:first + count], layer.packed_codes, layer.radius_codes, layer.radius_grid,
+                             layer.codebook, layer.permutation))
+            widths.append(n)
+            targets.append(out[first:first + count])
+            first += count
+    returned = sage_grouped(problems, widths, outputs=targets)
+    assert all(r.data_ptr() == t.data_ptr() for r, t in zip(returned, targets))
+    for cpu, (n, _), out in zip(cpus, shapes, outs):
+        assert_output(out, expected_output(x, cpu, n))
+    with pytest.raises(RuntimeError):
+        sage_grouped(problems, widths, outputs=[t[:, :-1] for t in targets])
+
+
 def test_tuning_knob_sweep_stays_within_tolerance():
     """Every launch geometry the knob can select gives the same answer within the gate."""
     lib = _lib.load()
