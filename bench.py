@@ -615,16 +615,28 @@ def run_model(args) -> None:
         cpu_group = dist.new_group(backend="gloo")
         sharded = {}
         for kind, batch in (("tp32b", 1), ("ep30b", 1), ("ep30b", 32)):
-            many_gpus = measure_sharded(kind, args, device, dist.group.WORLD, cpu_group, world, rank, batch=batch)
-            torch.cuda.synchronize()
+            # (a sub-record that fails is reported as such; the headline line is printed either way)
+            many_gpus, one_gpu, failure = None, None, None
+            try:
+                many_gpus = measure_sharded(kind, args, device, dist.group.WORLD, cpu_group, world, rank, batch=batch)
+                torch.cuda.synchronize()
+            except Exception as error:  # noqa: BLE001
+                failure = f"{type(error).__name__}: {error}"
             dist.barrier(group=cpu_group)
-            one_gpu = measure_sharded(kind, args, device, None, None, 1, 0, batch=batch) if rank == 0 else None
+            if rank == 0 and failure is None:
+                try:
+                    one_gpu = measure_sharded(kind, args, device, None, None, 1, 0, batch=batch)
+                except Exception as error:  # noqa: BLE001
+                    failure = f"one-GPU run: {type(error).__name__}: {error}"
             dist.barrier(group=cpu_group)
             if rank == 0:
-                many_gpus["one_gpu_tok_s"] = one_gpu["value"]
-                many_gpus["one_gpu_ms_per_step"] = one_gpu["ms_per_step"]
-                many_gpus["strong_scaling_efficiency"] = many_gpus["value"] / one_gpu["value"] / world
-                sharded[f"{kind}_batch{batch}"] = many_gpus
+                if failure is None:
+                    many_gpus["one_gpu_tok_s"] = one_gpu["value"]
+                    many_gpus["one_gpu_ms_per_step"] = one_gpu["ms_per_step"]
+                    many_gpus["strong_scaling_efficiency"] = many_gpus["value"] / one_gpu["value"] / world
+                    sharded[f"{kind}_batch{batch}"] = many_gpus
+                else:
+                    sharded[f"{kind}_batch{batch}"] = {"error": failure[:300]}
     if rank == 0:
         ms_per_step = elapsed_ms / args.steps
         peak, peak_kind = measured_peaks()
