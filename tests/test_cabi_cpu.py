@@ -189,3 +189,27 @@ def test_decode_planner_choices():
     import ctypes
 
     assert lib.sageb200_debug_plan(17, 16, 128, 148, 0, (ctypes.c_int * 8)()) == -1
+
+
+def test_grouped_scratch_of_a_group_that_runs_as_two_launches():
+    """Host arithmetic only.  Row blocks of Qwen3-4B's q, k and v in one grouped call: blocks of 16
+    rows (two MMA column blocks) next to blocks of 8 (one column block, which may stream through
+    rings under a small CTA share) cannot share a launch - the library runs the group as its first
+    and its second half, and the scratch it asks for is the larger half's, not the sum."""
+    from sage_b200 import _lib
+
+    lib = _lib.load()
+    assert lib.sageb200_set_tuning(0, 0, 0, 0) == 0
+
+    def need(blocks):
+        array = (_lib.Problem * len(blocks))()
+        for i, (rows, n, k) in enumerate(blocks):
+            array[i] = _lib.Problem(None, None, None, None, None, 1, None, rows, n, k, 256)  # (a permutation is present)
+        return lib.sageb200_grouped_workspace_bytes(array, len(blocks))
+
+    mixed = [(rows, n, 2560) for n in (4096, 1024, 1024) for rows in (16, 8)]
+    assert need(mixed) == max(need(mixed[:3]), need(mixed[3:])) > 0
+    even = [(rows, n, 2560) for n in (4096, 1024, 1024) for rows in (12, 12)]  # one launch: the sum of the needs
+    assert need(even) > max(need(even[:3]), need(even[3:]))
+    assert need(even) == need(even) and need(mixed) % 256 == 0
+    assert need([(17, 4096, 2560)]) == 0  # more than 16 rows: not a grouped problem
